@@ -1,0 +1,378 @@
+// Python bindings: validate tensors, pick the current CUDA stream, call the raw launchers.
+// Every check that could otherwise become a device fault (dtype, contiguity, alignment, extents)
+// happens here, before anything is launched.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "attention.cuh"
+#include "comm.cuh"
+#include "gemm_sm100.cuh"
+#include "ops.cuh"
+
+namespace {
+
+using torch::Tensor;
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_launch(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, what, " failed: ", cudaGetErrorString(e));
+}
+
+bool is_bf16(const Tensor& t) { return t.scalar_type() == at::kBFloat16; }
+
+void check_act(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kFloat, name, " must be bf16 or fp32");
+}
+
+void check_rowmajor_2d(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 2, name, " must be a 2-D CUDA tensor");
+  TORCH_CHECK(t.stride(1) == 1, name, " must have a contiguous last dimension");
+}
+
+// One status word per device, zeroed at creation; kernels raise it with atomicMax.
+Tensor& status_word(int device) {
+  static std::vector<Tensor> words(64);
+  TORCH_CHECK(device >= 0 && device < 64, "unexpected device index");
+  if (!words[device].defined())
+    words[device] = torch::zeros({4}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+  return words[device];
+}
+
+// ---------------- memory-bound ops ----------------
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
+  check_act(x, "x");
+  TORCH_CHECK(x.is_contiguous(), "x must be contiguous");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kFloat && w.is_contiguous(), "weight must be contiguous fp32");
+  const int64_t H = x.size(-1);
+  TORCH_CHECK(w.numel() == H && H % 8 == 0, "hidden size must match the weight and be a multiple of 8");
+  const int64_t rows = x.numel() / H;
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  Tensor rstd = torch::empty({rows}, x.options().dtype(torch::kFloat));
+  check_launch(mts::launch_rmsnorm_fwd(x.data_ptr(), w.data_ptr<float>(), y.data_ptr(), rstd.data_ptr<float>(), rows, int(H),
+                                       float(eps), is_bf16(x), cur_stream()), "rmsnorm_fwd");
+  return {y, rstd};
+}
+
+std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, bool need_dw) {
+  check_act(x, "x");
+  TORCH_CHECK(dy.scalar_type() == x.scalar_type() && dy.is_contiguous() && x.is_contiguous(), "dy/x mismatch");
+  const int64_t H = x.size(-1);
+  TORCH_CHECK(H % 8 == 0 && H <= 1024, "rmsnorm backward supports hidden sizes up to 1024 (multiple of 8)");
+  const int64_t rows = x.numel() / H;
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx = torch::empty_like(x);
+  Tensor dw = need_dw ? torch::zeros({H}, x.options().dtype(torch::kFloat)) : Tensor();
+  check_launch(mts::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr(),
+                                       need_dw ? dw.data_ptr<float>() : nullptr, rows, int(H), is_bf16(x), cur_stream()),
+               "rmsnorm_bwd");
+  return {dx, dw};
+}
+
+// x: [B, Hh, S, D] view (any strides, unit inner stride) -> contiguous [B, Hh, S, D]
+Tensor rope(const Tensor& x, const Tensor& cosv, const Tensor& sinv, bool backward) {
+  check_act(x, "x");
+  TORCH_CHECK(x.dim() == 4 && x.stride(3) == 1, "rope expects [B, H, S, D] with a contiguous last dimension");
+  const int64_t B = x.size(0), Hh = x.size(1), S = x.size(2), D = x.size(3);
+  TORCH_CHECK(D % 16 == 0, "head_dim must be a multiple of 16");
+  TORCH_CHECK(cosv.scalar_type() == x.scalar_type() && sinv.scalar_type() == x.scalar_type(), "cos/sin dtype mismatch");
+  TORCH_CHECK(cosv.is_contiguous() && sinv.is_contiguous() && cosv.size(0) >= S && cosv.size(1) == D, "bad cos/sin tables");
+  const int64_t vec = is_bf16(x) ? 8 : 4;
+  TORCH_CHECK(x.stride(0) % vec == 0 && x.stride(1) % vec == 0 && x.stride(2) % vec == 0 &&
+                  (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0,
+              "rope input must be 16-byte aligned in every row");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({B, Hh, S, D}, x.options());
+  check_launch(mts::launch_rope(x.data_ptr(), out.data_ptr(), cosv.data_ptr(), sinv.data_ptr(), int(B), int(Hh), int(S), int(D),
+                                x.stride(0), x.stride(1), x.stride(2), out.stride(0), out.stride(1), out.stride(2), backward,
+                                is_bf16(x), cur_stream()), "rope");
+  return out;
+}
+
+Tensor swiglu_fwd(const Tensor& g, const Tensor& u) {
+  check_act(g, "gate");
+  TORCH_CHECK(g.is_contiguous() && u.is_contiguous() && g.sizes() == u.sizes() && g.scalar_type() == u.scalar_type() &&
+                  g.numel() % 8 == 0, "swiglu needs contiguous same-shaped inputs with numel % 8 == 0");
+  c10::cuda::CUDAGuard guard(g.device());
+  Tensor out = torch::empty_like(g);
+  check_launch(mts::launch_swiglu_fwd(g.data_ptr(), u.data_ptr(), out.data_ptr(), g.numel(), is_bf16(g), cur_stream()), "swiglu_fwd");
+  return out;
+}
+
+std::vector<Tensor> swiglu_bwd(const Tensor& dy, const Tensor& g, const Tensor& u) {
+  TORCH_CHECK(dy.is_contiguous() && g.is_contiguous() && u.is_contiguous() && dy.scalar_type() == g.scalar_type(), "bad inputs");
+  c10::cuda::CUDAGuard guard(g.device());
+  Tensor dg = torch::empty_like(g), du = torch::empty_like(u);
+  check_launch(mts::launch_swiglu_bwd(dy.data_ptr(), g.data_ptr(), u.data_ptr(), dg.data_ptr(), du.data_ptr(), g.numel(), is_bf16(g),
+                                      cur_stream()), "swiglu_bwd");
+  return {dg, du};
+}
+
+Tensor cast_bf16(const Tensor& src) {
+  TORCH_CHECK(src.is_cuda() && src.scalar_type() == at::kFloat && src.is_contiguous(), "cast_bf16 expects contiguous fp32");
+  c10::cuda::CUDAGuard guard(src.device());
+  Tensor dst = torch::empty(src.sizes(), src.options().dtype(torch::kBFloat16));
+  check_launch(mts::launch_cast_f32_to_bf16(src.data_ptr<float>(), dst.data_ptr(), src.numel(), cur_stream()), "cast");
+  return dst;
+}
+
+void cast_bf16_into(const Tensor& src, Tensor dst) {
+  TORCH_CHECK(src.is_cuda() && src.scalar_type() == at::kFloat && src.is_contiguous(), "cast expects contiguous fp32");
+  TORCH_CHECK(dst.is_cuda() && dst.scalar_type() == at::kBFloat16 && dst.is_contiguous() && dst.numel() == src.numel(), "bad dst");
+  c10::cuda::CUDAGuard guard(src.device());
+  check_launch(mts::launch_cast_f32_to_bf16(src.data_ptr<float>(), dst.data_ptr(), src.numel(), cur_stream()), "cast");
+}
+
+// ---------------- GEMM ----------------
+void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t M, int64_t N, int64_t K, bool a_mn, bool b_mn, int64_t mode,
+          int64_t epilogue, bool accumulate, bool atomic_out, const c10::optional<Tensor>& aux,
+          const c10::optional<Tensor>& tile_group, const c10::optional<Tensor>& num_row_tiles,
+          const c10::optional<Tensor>& group_rows, int64_t num_groups, int64_t b_group_stride_rows, int64_t out_group_stride,
+          int64_t ldo, int64_t sm_limit) {
+  check_rowmajor_2d(a, "a");
+  check_rowmajor_2d(b, "b");
+  TORCH_CHECK(is_bf16(a) && is_bf16(b), "GEMM operands must be bf16");
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "operand leading dimensions must be multiples of 8");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0,
+              "operands must be 16-byte aligned");
+  TORCH_CHECK(out.is_cuda() && (out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat), "bad output dtype");
+  TORCH_CHECK(M > 0 && N > 0, "empty problem");
+  c10::cuda::CUDAGuard guard(a.device());
+  mts::GemmArgs g;
+  g.a = a.data_ptr(); g.a_rows = a.size(0); g.a_cols = a.size(1); g.lda = a.stride(0);
+  g.b = b.data_ptr(); g.b_rows = b.size(0); g.b_cols = b.size(1); g.ldb = b.stride(0);
+  g.a_mn_major = a_mn; g.b_mn_major = b_mn;
+  g.M = M; g.N = N; g.K = K; g.mode = int(mode); g.epilogue = int(epilogue);
+  g.out = out.data_ptr(); g.ldo = ldo; g.out_fp32 = out.scalar_type() == at::kFloat;
+  g.accumulate = accumulate; g.atomic_out = atomic_out;
+  if (aux.has_value() && aux->defined()) {
+    TORCH_CHECK(is_bf16(*aux) && aux->dim() == 2 && aux->stride(1) == 1, "aux must be a row-major bf16 matrix");
+    g.aux = aux->data_ptr(); g.ld_aux = aux->stride(0);
+  }
+  auto int_ptr = [](const c10::optional<Tensor>& t) -> const int* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous(), "index tensors must be contiguous int32");
+    return t->data_ptr<int>();
+  };
+  g.tile_group = int_ptr(tile_group); g.num_row_tiles = int_ptr(num_row_tiles); g.group_rows = int_ptr(group_rows);
+  if (mode == mts::GEMM_GROUPED_M) {
+    TORCH_CHECK(g.tile_group && g.num_row_tiles, "grouped-M needs tile_group and num_row_tiles");
+    TORCH_CHECK(M % 128 == 0 && tile_group->numel() >= M / 128, "grouped-M capacity must be a multiple of 128");
+    TORCH_CHECK(!a_mn, "grouped-M expects a K-major A operand");
+  }
+  if (mode == mts::GEMM_GROUPED_K) {
+    TORCH_CHECK(g.group_rows && group_rows->numel() >= num_groups + 1, "grouped-K needs group_rows[groups + 1]");
+    TORCH_CHECK(a_mn && b_mn, "grouped-K expects MN-major operands");
+  }
+  g.num_groups = int(num_groups); g.b_group_stride_rows = b_group_stride_rows; g.out_group_stride = out_group_stride;
+  // extents that the epilogue may touch must lie inside `out`
+  const int64_t out_rows = (mode == mts::GEMM_GROUPED_K) ? M : M;
+  const int64_t out_cols = epilogue == mts::EPI_SWIGLU ? N / 2 : (epilogue == mts::EPI_SWIGLU_BWD ? 2 * N : N);
+  const int64_t groups_out = (mode == mts::GEMM_GROUPED_K && !atomic_out && out_group_stride > 0) ? num_groups : 1;
+  TORCH_CHECK(ldo >= out_cols, "output leading dimension too small");
+  TORCH_CHECK((groups_out - 1) * out_group_stride + (out_rows - 1) * ldo + out_cols <= out.numel(), "output buffer too small");
+  if (g.aux) {
+    const int64_t aux_cols = epilogue == mts::EPI_SWIGLU ? N : 2 * N;
+    TORCH_CHECK(aux->size(0) >= M && aux->size(1) >= aux_cols, "aux buffer too small");
+  }
+  g.status = status_word(a.get_device()).data_ptr<int>();
+  g.sm_limit = int(sm_limit);
+  g.stream = cur_stream();
+  check_launch(mts::launch_gemm_sm100(g), "tcgen05 gemm");
+}
+
+// ---------------- cross entropy ----------------
+void ce_forward(const Tensor& logits, const Tensor& targets, Tensor row_lse, Tensor stats, int64_t vocab) {
+  check_rowmajor_2d(logits, "logits");
+  check_act(logits, "logits");
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == logits.size(0),
+              "targets must be contiguous int64 with one entry per row");
+  TORCH_CHECK(vocab <= logits.size(1) && row_lse.numel() >= logits.size(0) && stats.numel() >= 2, "bad ce buffers");
+  TORCH_CHECK(row_lse.scalar_type() == at::kFloat && stats.scalar_type() == at::kFloat, "lse/stats must be fp32");
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_launch(mts::launch_ce_forward(logits.data_ptr(), logits.stride(0), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), row_lse.data_ptr<float>(),
+                                      stats.data_ptr<float>(), logits.size(0), int(vocab), is_bf16(logits), cur_stream()), "ce_forward");
+}
+
+void ce_backward(Tensor logits, const Tensor& targets, const Tensor& row_lse, const Tensor& valid_count,
+                 const c10::optional<Tensor>& grad_scale, int64_t vocab) {
+  check_rowmajor_2d(logits, "logits");
+  check_act(logits, "logits");
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == logits.size(0), "bad targets");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const float* gs = (grad_scale.has_value() && grad_scale->defined()) ? grad_scale->data_ptr<float>() : nullptr;
+  check_launch(mts::launch_ce_backward(logits.data_ptr(), logits.stride(0), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), row_lse.data_ptr<float>(),
+                                       valid_count.data_ptr<float>(), gs, logits.size(0), int(vocab), int(logits.size(1)),
+                                       is_bf16(logits), cur_stream()), "ce_backward");
+}
+
+void count_valid(const Tensor& targets, Tensor out) {
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous(), "bad targets");
+  c10::cuda::CUDAGuard guard(targets.device());
+  check_launch(mts::launch_count_valid_targets(reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()), targets.numel(), out.data_ptr<float>(), cur_stream()), "count_valid");
+}
+
+// ---------------- router / MoE ----------------
+std::vector<Tensor> router_forward(const Tensor& logits, int64_t K, bool normalize) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.scalar_type() == at::kFloat && logits.is_contiguous(),
+              "router logits must be a contiguous 2-D fp32 CUDA tensor");
+  const int64_t T = logits.size(0), E = logits.size(1);
+  TORCH_CHECK(E <= 64 && K <= 8 && K <= E && T > 0, "router supports up to 64 experts and top-8");
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto f32 = logits.options();
+  Tensor w = torch::empty({T, K}, f32), idx = torch::empty({T, K}, f32.dtype(torch::kInt32));
+  Tensor lse = torch::empty({T}, f32), sums = torch::zeros({E + 2}, f32);
+  check_launch(mts::launch_router_forward(logits.data_ptr<float>(), int(T), int(E), int(K), normalize, w.data_ptr<float>(),
+                                          idx.data_ptr<int>(), lse.data_ptr<float>(), sums.data_ptr<float>(), cur_stream()), "router_forward");
+  return {w, idx, lse, sums};
+}
+
+Tensor router_backward(const Tensor& logits, const Tensor& lse, const Tensor& idx, const Tensor& w,
+                       const c10::optional<Tensor>& g_w, const c10::optional<Tensor>& g_mp, const c10::optional<Tensor>& g_z,
+                       bool normalize) {
+  const int64_t T = logits.size(0), E = logits.size(1), K = idx.size(1);
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor out = torch::empty_like(logits);
+  auto opt = [](const c10::optional<Tensor>& t) -> const float* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous(), "router grads must be contiguous fp32");
+    return t->data_ptr<float>();
+  };
+  check_launch(mts::launch_router_backward(logits.data_ptr<float>(), lse.data_ptr<float>(), idx.data_ptr<int>(), w.data_ptr<float>(),
+                                           opt(g_w), opt(g_mp), opt(g_z), int(T), int(E), int(K), normalize, out.data_ptr<float>(),
+                                           cur_stream()), "router_backward");
+  return out;
+}
+
+int64_t moe_capacity_rows(int64_t T, int64_t K, int64_t E) { return ((T * K + E * 127) + 127) / 128 * 128; }
+
+// returns row_token[cap], token_rows[T*K], tile_group[cap/128], group_rows[E+1], meta[4]
+std::vector<Tensor> moe_plan(const Tensor& indices, int64_t E) {
+  TORCH_CHECK(indices.is_cuda() && indices.dim() == 2 && indices.scalar_type() == at::kInt && indices.is_contiguous(),
+              "expert indices must be contiguous int32 [T, K]");
+  const int64_t T = indices.size(0), K = indices.size(1);
+  const int64_t cap = moe_capacity_rows(T, K, E);
+  c10::cuda::CUDAGuard guard(indices.device());
+  auto i32 = indices.options();
+  Tensor row_token = torch::empty({cap}, i32), token_rows = torch::empty({T * K}, i32);
+  Tensor tile_group = torch::empty({cap / 128}, i32), group_rows = torch::empty({E + 1}, i32), meta = torch::zeros({4}, i32);
+  Tensor ws = torch::empty({int64_t(mts::moe_plan_workspace_ints(int(T), int(K), int(E))) + 1}, i32);
+  check_launch(mts::launch_moe_plan(indices.data_ptr<int>(), int(T), int(K), int(E), int(cap), row_token.data_ptr<int>(),
+                                    token_rows.data_ptr<int>(), tile_group.data_ptr<int>(), group_rows.data_ptr<int>(),
+                                    meta.data_ptr<int>(), ws.data_ptr<int>(), cur_stream()), "moe_plan");
+  return {row_token, token_rows, tile_group, group_rows, meta};
+}
+
+void moe_gather(const Tensor& x, const Tensor& row_token, Tensor xs, const Tensor& meta) {
+  TORCH_CHECK(is_bf16(x) && x.is_contiguous() && is_bf16(xs) && xs.is_contiguous() && x.size(1) == xs.size(1) && x.size(1) % 8 == 0, "bad gather tensors");
+  TORCH_CHECK(xs.size(0) >= row_token.numel(), "sorted buffer smaller than the plan capacity");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(mts::launch_moe_gather(x.data_ptr(), row_token.data_ptr<int>(), xs.data_ptr(), int(row_token.numel()), int(x.size(1)),
+                                      meta.data_ptr<int>(), cur_stream()), "moe_gather");
+}
+
+void moe_combine(const Tensor& y, const Tensor& token_rows, const c10::optional<Tensor>& weights, Tensor out, int64_t K) {
+  TORCH_CHECK(is_bf16(y) && y.is_contiguous() && is_bf16(out) && out.is_contiguous() && y.size(1) == out.size(1), "bad combine tensors");
+  const void* w = nullptr;
+  if (weights.has_value() && weights->defined()) {
+    TORCH_CHECK(is_bf16(*weights) && weights->is_contiguous() && weights->numel() == out.size(0) * K, "weights must be bf16 [T, K]");
+    w = weights->data_ptr();
+  }
+  TORCH_CHECK(token_rows.numel() == out.size(0) * K, "token_rows must have T*K entries");
+  c10::cuda::CUDAGuard guard(y.device());
+  check_launch(mts::launch_moe_combine(y.data_ptr(), token_rows.data_ptr<int>(), w, out.data_ptr(), int(out.size(0)), int(K),
+                                       int(out.size(1)), cur_stream()), "moe_combine");
+}
+
+void moe_combine_bwd(const Tensor& dout, const Tensor& y, const Tensor& row_token, const Tensor& token_rows, const Tensor& weights,
+                     Tensor dys, Tensor dweights, const Tensor& meta, int64_t K) {
+  TORCH_CHECK(is_bf16(dout) && dout.is_contiguous() && is_bf16(y) && y.is_contiguous() && is_bf16(dys) && dys.is_contiguous(), "bad tensors");
+  TORCH_CHECK(is_bf16(weights) && weights.is_contiguous() && dweights.scalar_type() == at::kFloat && dweights.is_contiguous(), "bad weights");
+  TORCH_CHECK(dys.size(0) >= row_token.numel() && y.size(0) >= row_token.numel(), "sorted buffers smaller than the plan capacity");
+  c10::cuda::CUDAGuard guard(y.device());
+  check_launch(mts::launch_moe_combine_bwd(dout.data_ptr(), y.data_ptr(), row_token.data_ptr<int>(), token_rows.data_ptr<int>(),
+                                           weights.data_ptr(), dys.data_ptr(), dweights.data_ptr<float>(), int(dout.size(0)), int(K),
+                                           int(dout.size(1)), int(row_token.numel()), meta.data_ptr<int>(), cur_stream()), "moe_combine_bwd");
+}
+
+// ---------------- optimizer ----------------
+void adamw_step(Tensor param, const Tensor& grad, Tensor exp_avg, Tensor exp_avg_sq, const c10::optional<Tensor>& shadow, double lr,
+                double beta1, double beta2, double eps, double weight_decay, int64_t step, const c10::optional<Tensor>& grad_scale,
+                double static_scale) {
+  TORCH_CHECK(param.is_cuda() && param.scalar_type() == at::kFloat && param.is_contiguous(), "param must be contiguous fp32");
+  TORCH_CHECK(grad.scalar_type() == at::kFloat && grad.is_contiguous() && grad.numel() == param.numel(), "grad mismatch");
+  TORCH_CHECK(exp_avg.numel() == param.numel() && exp_avg_sq.numel() == param.numel(), "state mismatch");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(param.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(grad.data_ptr()) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(exp_avg.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(exp_avg_sq.data_ptr()) & 15) == 0,
+              "adamw buffers must be 16-byte aligned");
+  c10::cuda::CUDAGuard guard(param.device());
+  mts::AdamWArgs a{};
+  a.param = param.data_ptr<float>(); a.grad = grad.data_ptr<float>();
+  a.exp_avg = exp_avg.data_ptr<float>(); a.exp_avg_sq = exp_avg_sq.data_ptr<float>();
+  a.shadow_bf16 = nullptr;
+  if (shadow.has_value() && shadow->defined()) {
+    TORCH_CHECK(is_bf16(*shadow) && shadow->is_contiguous() && shadow->numel() == param.numel() &&
+                    (reinterpret_cast<uintptr_t>(shadow->data_ptr()) & 7) == 0, "bad bf16 shadow");
+    a.shadow_bf16 = shadow->data_ptr();
+  }
+  a.n = param.numel(); a.lr = float(lr); a.beta1 = float(beta1); a.beta2 = float(beta2); a.eps = float(eps);
+  a.weight_decay = float(weight_decay);
+  a.bias_correction1 = float(1.0 - std::pow(beta1, double(step)));
+  a.bias_correction2 = float(1.0 - std::pow(beta2, double(step)));
+  a.grad_scale = (grad_scale.has_value() && grad_scale->defined()) ? grad_scale->data_ptr<float>() : nullptr;
+  a.static_grad_scale = float(static_scale);
+  check_launch(mts::launch_adamw(a, cur_stream()), "adamw");
+}
+
+void sumsq(const Tensor& x, Tensor out) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous() && out.scalar_type() == at::kFloat, "sumsq expects fp32");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0, "sumsq input must be 16-byte aligned");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_launch(mts::launch_sumsq(x.data_ptr<float>(), x.numel(), out.data_ptr<float>(), cur_stream()), "sumsq");
+}
+
+void clip_coef(const Tensor& sumsq_in, double max_norm, double extra, Tensor coef, Tensor norm_out) {
+  c10::cuda::CUDAGuard guard(sumsq_in.device());
+  check_launch(mts::launch_clip_coef(sumsq_in.data_ptr<float>(), float(max_norm), float(extra), coef.data_ptr<float>(),
+                                     norm_out.data_ptr<float>(), cur_stream()), "clip_coef");
+}
+
+int64_t launch_count() { return int64_t(mts::g_launch_count); }
+
+Tensor status_tensor(int64_t device) { return status_word(int(device)); }
+
+}  // namespace
+
+void bind_attention(pybind11::module_& m);
+void bind_comm(pybind11::module_& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rope", &rope);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("cast_bf16", &cast_bf16);
+  m.def("cast_bf16_into", &cast_bf16_into);
+  m.def("gemm", &gemm);
+  m.def("ce_forward", &ce_forward);
+  m.def("ce_backward", &ce_backward);
+  m.def("count_valid", &count_valid);
+  m.def("router_forward", &router_forward);
+  m.def("router_backward", &router_backward);
+  m.def("moe_capacity_rows", &moe_capacity_rows);
+  m.def("moe_plan", &moe_plan);
+  m.def("moe_gather", &moe_gather);
+  m.def("moe_combine", &moe_combine);
+  m.def("moe_combine_bwd", &moe_combine_bwd);
+  m.def("adamw_step", &adamw_step);
+  m.def("sumsq", &sumsq);
+  m.def("clip_coef", &clip_coef);
+  m.def("launch_count", &launch_count);
+  m.def("status_tensor", &status_tensor);
+  bind_attention(m);
+  bind_comm(m);
+}

@@ -1,0 +1,351 @@
+// Memory-bound operators for sm_100a: RMSNorm, RoPE, SwiGLU (forward and backward), dtype casts.
+// All use 128-bit global accesses, keep one row per warp in registers where it fits, and reduce
+// with warp shuffles.  They are bounded by HBM bandwidth; the launchers size grids from the SM count.
+//
+// Reference counterparts: minitrain/kernels/triton/rmsnorm.py:101-301, rope.py:193-292,
+// swiglu.py:75-157 (Triton, architecture-neutral).
+#include "ops.cuh"
+
+#include <cuda_bf16.h>
+
+namespace mts {
+
+namespace {
+
+template <typename T> struct Vec8;   // eight elements moved as 16 B (bf16) or 32 B (fp32)
+
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+      v[2 * i] = __low2float(h);
+      v[2 * i + 1] = __high2float(h);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0];
+    const float4 b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+constexpr int kNormWarps = 8;        // rows per CTA per iteration
+constexpr int kMaxVecPerLane = 4;    // register-resident rows up to 32 lanes * 4 * 8 = 1024 columns
+
+// ---------------- RMSNorm forward: y = x * rsqrt(mean(x^2) + eps) * w ----------------
+template <typename T>
+__global__ void __launch_bounds__(kNormWarps * 32)
+rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __restrict__ y, float* __restrict__ rstd,
+                   long long rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nvec = H / 8;
+  for (long long row = (long long)blockIdx.x * kNormWarps + warp; row < rows; row += (long long)gridDim.x * kNormWarps) {
+    const T* xr = x + row * H;
+    T* yr = y + row * H;
+    float cache[kMaxVecPerLane][8];
+    float ss = 0.f;
+    const bool resident = nvec <= 32 * kMaxVecPerLane;
+#pragma unroll
+    for (int i = 0; i < kMaxVecPerLane; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        Vec8<T>::load(xr + v * 8, cache[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += cache[i][j] * cache[i][j];
+      }
+    }
+    for (int v = lane + 32 * kMaxVecPerLane; v < nvec; v += 32) {
+      float t[8];
+      Vec8<T>::load(xr + v * 8, t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += t[j] * t[j];
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / float(H) + eps);
+    if (lane == 0 && rstd != nullptr) rstd[row] = inv;
+#pragma unroll
+    for (int i = 0; i < kMaxVecPerLane; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float wv[8], o[8];
+        Vec8<float>::load(w + v * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = cache[i][j] * inv * wv[j];
+        Vec8<T>::store(yr + v * 8, o);
+      }
+    }
+    if (!resident) {
+      for (int v = lane + 32 * kMaxVecPerLane; v < nvec; v += 32) {
+        float t[8], wv[8];
+        Vec8<T>::load(xr + v * 8, t);
+        Vec8<float>::load(w + v * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t[j] = t[j] * inv * wv[j];
+        Vec8<T>::store(yr + v * 8, t);
+      }
+    }
+  }
+}
+
+// ---------------- RMSNorm backward ----------------
+// m = dy * w ; dx = rstd * (m - x * rstd^2 * mean(m * x)) ; dw += sum_rows dy * x * rstd
+// Persistent grid; each warp keeps its dw slice in registers, CTA-reduces through shared memory and
+// issues one fp32 atomic per column per CTA.  Supports H <= 1024 (register path) — larger H is
+// handled by the host by splitting columns is not needed for the shipped presets.
+template <typename T>
+__global__ void __launch_bounds__(kNormWarps * 32)
+rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ w,
+                   const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw, long long rows, int H) {
+  extern __shared__ float red[];   // [kNormWarps][H]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nvec = H / 8;
+  float acc[kMaxVecPerLane][8];
+  float wv[kMaxVecPerLane][8];
+#pragma unroll
+  for (int i = 0; i < kMaxVecPerLane; ++i) {
+    const int v = lane + 32 * i;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    if (v < nvec) Vec8<float>::load(w + v * 8, wv[i]);
+  }
+  for (long long row = (long long)blockIdx.x * kNormWarps + warp; row < rows; row += (long long)gridDim.x * kNormWarps) {
+    const float inv = rstd[row];
+    float xs[kMaxVecPerLane][8], ds[kMaxVecPerLane][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVecPerLane; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        Vec8<T>::load(x + row * H + v * 8, xs[i]);
+        Vec8<T>::load(dy + row * H + v * 8, ds[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc[i][j] += ds[i][j] * xs[i][j] * inv;
+          ds[i][j] *= wv[i][j];          // m
+          dot += ds[i][j] * xs[i][j];
+        }
+      }
+    }
+    dot = warp_sum(dot);
+    const float coef = dot / float(H) * inv * inv;
+#pragma unroll
+    for (int i = 0; i < kMaxVecPerLane; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = inv * (ds[i][j] - xs[i][j] * coef);
+        Vec8<T>::store(dx + row * H + v * 8, o);
+      }
+    }
+  }
+  if (dw == nullptr) return;
+#pragma unroll
+  for (int i = 0; i < kMaxVecPerLane; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) red[warp * H + v * 8 + j] = acc[i][j];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < kNormWarps; ++wi) s += red[wi * H + c];
+    atomicAdd(dw + c, s);
+  }
+}
+
+// ---------------- RoPE (half-split pairs (d, d + D/2)) ----------------
+// in : [B, Hh, S, D] view with arbitrary strides (innermost contiguous); out: contiguous [B, Hh, S, D].
+// sign = +1 forward, -1 backward (inverse rotation applied to the incoming gradient).
+template <typename T>
+__global__ void rope_kernel(const T* __restrict__ in, T* __restrict__ out, const T* __restrict__ cosp,
+                            const T* __restrict__ sinp, int B, int Hh, int S, int D, long long sb, long long sh,
+                            long long ss, float sign, long long osb, long long osh, long long oss) {
+  const int vec_per_half = D / 16;                     // 8 elements per vector, D/2 elements per half
+  const long long total = (long long)B * Hh * S * vec_per_half;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int v = int(idx % vec_per_half);
+    long long r = idx / vec_per_half;
+    const int s = int(r % S); r /= S;
+    const int h = int(r % Hh);
+    const int b = int(r / Hh);
+    const T* src = in + b * sb + h * sh + s * ss;
+    T* dst = out + b * osb + h * osh + s * oss;
+    float lo[8], hi[8], c[8], sn[8], olo[8], ohi[8];
+    Vec8<T>::load(src + v * 8, lo);
+    Vec8<T>::load(src + D / 2 + v * 8, hi);
+    Vec8<T>::load(cosp + (long long)s * D + v * 8, c);
+    Vec8<T>::load(sinp + (long long)s * D + v * 8, sn);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sj = sn[j] * sign;
+      olo[j] = lo[j] * c[j] - hi[j] * sj;
+      ohi[j] = hi[j] * c[j] + lo[j] * sj;
+    }
+    Vec8<T>::store(dst + v * 8, olo);
+    Vec8<T>::store(dst + D / 2 + v * 8, ohi);
+  }
+}
+
+// ---------------- SwiGLU ----------------
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ g, const T* __restrict__ u, T* __restrict__ out, long long nvec) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float a[8], b[8];
+    Vec8<T>::load(g + i * 8, a);
+    Vec8<T>::load(u + i * 8, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = a[j] / (1.f + __expf(-a[j])) * b[j];
+    Vec8<T>::store(out + i * 8, a);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ g, const T* __restrict__ u,
+                                  T* __restrict__ dg, T* __restrict__ du, long long nvec) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float d[8], a[8], b[8];
+    Vec8<T>::load(dy + i * 8, d);
+    Vec8<T>::load(g + i * 8, a);
+    Vec8<T>::load(u + i * 8, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = 1.f / (1.f + __expf(-a[j]));
+      const float silu = a[j] * s;
+      a[j] = d[j] * b[j] * (s + silu * (1.f - s));
+      b[j] = d[j] * silu;
+    }
+    Vec8<T>::store(dg + i * 8, a);
+    Vec8<T>::store(du + i * 8, b);
+  }
+}
+
+// ---------------- casts ----------------
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  const long long nvec = n / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float v[8];
+    Vec8<float>::load(src + i * 8, v);
+    Vec8<__nv_bfloat16>::store(dst + i * 8, v);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < n - nvec * 8) dst[nvec * 8 + threadIdx.x] = __float2bfloat16(src[nvec * 8 + threadIdx.x]);
+}
+
+int grid_for(long long work_items, int block, int per_sm) {
+  long long blocks = (work_items + block - 1) / block;
+  const long long cap = (long long)device_sm_count() * per_sm;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : int(blocks);
+}
+
+}  // namespace
+
+int device_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+#define MTS_DISPATCH_FLOAT(is_bf16, ...)            \
+  if (is_bf16) { using T = __nv_bfloat16; __VA_ARGS__ } \
+  else { using T = float; __VA_ARGS__ }
+
+cudaError_t launch_rmsnorm_fwd(const void* x, const float* w, void* y, float* rstd, long long rows, int H, float eps,
+                               bool bf16, cudaStream_t stream) {
+  if (H % 8 != 0) return cudaErrorInvalidValue;
+  const int grid = grid_for(rows, kNormWarps, 16);
+  MTS_DISPATCH_FLOAT(bf16, rmsnorm_fwd_kernel<T><<<grid, kNormWarps * 32, 0, stream>>>(
+      static_cast<const T*>(x), w, static_cast<T*>(y), rstd, rows, H, eps);)
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, void* dx, float* dw,
+                               long long rows, int H, bool bf16, cudaStream_t stream) {
+  if (H % 8 != 0 || H > 32 * kMaxVecPerLane * 8) return cudaErrorInvalidValue;
+  const int grid = grid_for(rows, kNormWarps, 4);
+  const size_t smem = dw != nullptr ? sizeof(float) * kNormWarps * H : 0;
+  MTS_DISPATCH_FLOAT(bf16, rmsnorm_bwd_kernel<T><<<grid, kNormWarps * 32, smem, stream>>>(
+      static_cast<const T*>(dy), static_cast<const T*>(x), w, rstd, static_cast<T*>(dx), dw, rows, H);)
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rope(const void* in, void* out, const void* cosp, const void* sinp, int B, int Hh, int S, int D,
+                        long long sb, long long sh, long long ss, long long osb, long long osh, long long oss,
+                        bool backward, bool bf16, cudaStream_t stream) {
+  if (D % 16 != 0) return cudaErrorInvalidValue;
+  const long long total = (long long)B * Hh * S * (D / 16);
+  const int grid = grid_for(total, 256, 16);
+  const float sign = backward ? -1.f : 1.f;
+  MTS_DISPATCH_FLOAT(bf16, rope_kernel<T><<<grid, 256, 0, stream>>>(
+      static_cast<const T*>(in), static_cast<T*>(out), static_cast<const T*>(cosp), static_cast<const T*>(sinp), B, Hh, S,
+      D, sb, sh, ss, sign, osb, osh, oss);)
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu_fwd(const void* g, const void* u, void* out, long long n, bool bf16, cudaStream_t stream) {
+  if (n % 8 != 0) return cudaErrorInvalidValue;
+  const int grid = grid_for(n / 8, 256, 16);
+  MTS_DISPATCH_FLOAT(bf16, swiglu_fwd_kernel<T><<<grid, 256, 0, stream>>>(
+      static_cast<const T*>(g), static_cast<const T*>(u), static_cast<T*>(out), n / 8);)
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu_bwd(const void* dy, const void* g, const void* u, void* dg, void* du, long long n, bool bf16,
+                              cudaStream_t stream) {
+  if (n % 8 != 0) return cudaErrorInvalidValue;
+  const int grid = grid_for(n / 8, 256, 16);
+  MTS_DISPATCH_FLOAT(bf16, swiglu_bwd_kernel<T><<<grid, 256, 0, stream>>>(
+      static_cast<const T*>(dy), static_cast<const T*>(g), static_cast<const T*>(u), static_cast<T*>(dg),
+      static_cast<T*>(du), n / 8);)
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_cast_f32_to_bf16(const float* src, void* dst, long long n, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  const int grid = grid_for(n / 8 + 1, 256, 16);
+  cast_f32_to_bf16_kernel<<<grid, 256, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+}  // namespace mts

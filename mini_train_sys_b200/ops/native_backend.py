@@ -1,0 +1,496 @@
+"""sm_100a operator backend: every hot op runs a hand-written CUDA kernel from ``csrc``.
+
+* GEMM-shaped work (projections, fused linear cross-entropy, the grouped expert GEMMs and all
+  of their dgrad / wgrad passes) goes through the tcgen05 + TMA kernel in ``gemm_sm100.cu``;
+  no cuBLAS call is made on these paths.
+* RMSNorm, RoPE, SwiGLU, cross entropy, the router and the MoE permutation kernels are
+  bandwidth-bound kernels with 128-bit accesses.
+* Attention runs the tcgen05 FlashAttention kernels in ``attention.cu``.
+
+Inputs the kernels do not cover (CPU tensors, fp16, odd alignments) take the library path of
+``TorchOpsBackend`` and are counted in ``dispatch_summary()`` so that a silent fallback shows
+up in tests and benchmark records (the reference keeps similar counters for its CUDA attention:
+minitrain/kernels/cuda_ext/__init__.py:43-50).
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from collections import Counter
+
+import torch
+
+from mini_train_sys_b200.models.ops import RouterPostprocessOutput
+from mini_train_sys_b200.ops.build import load_extension
+from mini_train_sys_b200.ops.torch_backend import TorchOpsBackend, check_router_args
+
+GEMM_DENSE, GEMM_GROUPED_M, GEMM_GROUPED_K = 0, 1, 2
+EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_BWD = 0, 1, 2
+
+_ext = None
+
+
+def ext():
+    global _ext
+    if _ext is None:
+        _ext = load_extension()
+    return _ext
+
+
+def check_kernel_status(device: torch.device | int | None = None) -> None:
+    """Raise if any kernel on ``device`` reported a bounded-wait timeout (synchronises)."""
+
+    index = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    word = int(ext().status_tensor(index)[0].item())
+    if word != 0:
+        raise RuntimeError(f"a native kernel reported status {word} (1 = wait timeout)")
+
+
+# ---------------------------------------------------------------------------------------------
+# GEMM wrappers
+# ---------------------------------------------------------------------------------------------
+_weight_cache: dict[int, tuple[int, torch.Tensor]] = {}
+_rows_cache: dict[tuple, torch.Tensor] = {}
+
+
+def bf16_weight(weight: torch.Tensor) -> torch.Tensor:
+    """bf16 copy of a (usually fp32) parameter, refreshed only when the parameter changes."""
+
+    if weight.dtype == torch.bfloat16:
+        return weight if weight.is_contiguous() else weight.contiguous()
+    key = weight.data_ptr()
+    hit = _weight_cache.get(key)
+    version = weight._version
+    if hit is not None and hit[0] == version and hit[1].shape == weight.shape:
+        return hit[1]
+    src = weight.detach()
+    if not src.is_contiguous():
+        src = src.contiguous()
+    out = ext().cast_bf16(src.float() if src.dtype != torch.float32 else src)
+    _weight_cache[key] = (version, out)
+    return out
+
+
+def _gemm(a, b, out, M, N, K, *, a_mn=False, b_mn=False, mode=GEMM_DENSE, epilogue=EPI_STORE, accumulate=False,
+          atomic_out=False, aux=None, tile_group=None, num_row_tiles=None, group_rows=None, num_groups=1,
+          b_group_stride_rows=0, out_group_stride=0, ldo=None, sm_limit=0) -> None:
+    ext().gemm(a, b, out, M, N, K, a_mn, b_mn, mode, epilogue, accumulate, atomic_out, aux, tile_group, num_row_tiles,
+               group_rows, num_groups, b_group_stride_rows, out_group_stride, out.stride(-2) if ldo is None else ldo,
+               sm_limit)
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, out_dtype=torch.bfloat16
+            ) -> torch.Tensor:
+    """``a[M, K] @ b[N, K]^T`` (both K-major)."""
+
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    _gemm(a, b, out, M, N, K)
+    return out
+
+
+def gemm_nn(a: torch.Tensor, b_kn: torch.Tensor, out: torch.Tensor | None = None, *, K: int | None = None,
+            out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``a[M, K] @ b_kn[K, N]`` (B is MN-major: no transpose is materialised)."""
+
+    M = a.shape[0]
+    K = a.shape[1] if K is None else K
+    N = b_kn.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    _gemm(a, b_kn, out, M, N, K, b_mn=True)
+    return out
+
+
+def _split_rows(k_rows: int, tiles: int, device: torch.device) -> tuple[torch.Tensor, int]:
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    splits = max(1, min(round(2 * sms / max(tiles, 1)), k_rows // 512 if k_rows >= 512 else 1))
+    key = (k_rows, splits, device.index)
+    hit = _rows_cache.get(key)
+    if hit is None:
+        per = -(-k_rows // splits)
+        per = -(-per // 64) * 64
+        bounds = [min(i * per, k_rows) for i in range(splits)] + [k_rows]
+        hit = torch.tensor(bounds, dtype=torch.int32, device=device)
+        _rows_cache[key] = hit
+    return hit, splits
+
+
+def gemm_tn(a_km: torch.Tensor, b_kn: torch.Tensor, out: torch.Tensor | None = None, *, accumulate: bool = False,
+            M: int | None = None) -> torch.Tensor:
+    """``a_km[K, M]^T @ b_kn[K, N]`` -> fp32 ``[M, N]`` (weight gradients; split-K with fp32 atomics)."""
+
+    k_rows = a_km.shape[0]
+    M = a_km.shape[1] if M is None else M
+    N = b_kn.shape[1]
+    tiles = -(-M // 128) * -(-N // 256)
+    rows, splits = _split_rows(k_rows, tiles, a_km.device)
+    if out is None:
+        out = (torch.zeros if splits > 1 else torch.empty)(M, N, dtype=torch.float32, device=a_km.device)
+        accumulate = False
+    atomic = splits > 1
+    _gemm(a_km, b_kn, out, M, N, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=rows, num_groups=splits,
+          accumulate=accumulate and not atomic, atomic_out=atomic, out_group_stride=0)
+    return out
+
+
+def _gemm_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.is_cuda and weight.dim() == 2
+            and x.shape[-1] == weight.shape[1] and x.shape[-1] % 8 == 0 and x.numel() > 0)
+
+
+class _LinearFn(torch.autograd.Function):
+    """``y = x @ W^T`` with the weight kept in fp32 (bf16 copy cached) and fp32 weight gradients."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        w16 = bf16_weight(weight)
+        n_out, k_in = w16.shape
+        x2 = x.reshape(-1, k_in)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        ld = -(-n_out // 8) * 8   # padded row pitch keeps the epilogue on 16-byte stores
+        buf = torch.empty(x2.shape[0], ld, dtype=torch.bfloat16, device=x.device)
+        _gemm(x2, w16, buf, x2.shape[0], n_out, k_in, ldo=ld)
+        ctx.save_for_backward(x2, weight)
+        ctx.in_shape = x.shape
+        y = buf if ld == n_out else buf[:, :n_out]
+        return y.view(*x.shape[:-1], n_out) if ld == n_out else y.reshape(*x.shape[:-1], n_out)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        w16 = bf16_weight(weight)
+        n_out, k_in = w16.shape
+        dy2 = dy.reshape(-1, n_out)
+        if n_out % 8 != 0:   # operand pitch must be a multiple of 8 elements
+            pad = torch.zeros(dy2.shape[0], -(-n_out // 8) * 8, dtype=dy2.dtype, device=dy2.device)
+            pad[:, :n_out] = dy2
+            dy2 = pad
+        elif not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_nn(dy2, w16, K=dy2.shape[1]).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm_tn(dy2, x2, M=n_out).to(weight.dtype)
+        return dx, dw
+
+
+# ---------------------------------------------------------------------------------------------
+# memory-bound operators
+# ---------------------------------------------------------------------------------------------
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        xc = x if x.is_contiguous() else x.contiguous()
+        w32 = weight if weight.dtype == torch.float32 else weight.float()
+        y, rstd = ext().rmsnorm_fwd(xc, w32.contiguous(), eps)
+        ctx.save_for_backward(xc, w32, rstd)
+        ctx.w_dtype = weight.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w32, rstd = ctx.saved_tensors
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        dx, dw = ext().rmsnorm_bwd(dyc, x, w32, rstd, ctx.needs_input_grad[1])
+        return dx, (dw.to(ctx.w_dtype) if dw is not None and dw.numel() else None), None
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        return ext().rope(q, cos, sin, False), ext().rope(k, cos, sin, False)
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        cos, sin = ctx.saved_tensors
+        fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()  # noqa: E731
+        return ext().rope(fix(dq), cos, sin, True), ext().rope(fix(dk), cos, sin, True), None, None
+
+
+class _SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        g, u = gate.contiguous(), up.contiguous()
+        ctx.save_for_backward(g, u)
+        return ext().swiglu_fwd(g, u)
+
+    @staticmethod
+    def backward(ctx, dy):
+        g, u = ctx.saved_tensors
+        dg, du = ext().swiglu_bwd(dy.contiguous(), g, u)
+        return dg, du
+
+
+class _CrossEntropyFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets):
+        rows, vocab = logits.shape
+        lg = logits if logits.stride(1) == 1 else logits.contiguous()
+        tg = targets.contiguous()
+        lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        stats = torch.zeros(2, dtype=torch.float32, device=logits.device)
+        ext().ce_forward(lg, tg, lse, stats, vocab)
+        ctx.save_for_backward(lg, tg, lse, stats)
+        return stats[0] / stats[1]
+
+    @staticmethod
+    def backward(ctx, g):
+        lg, tg, lse, stats = ctx.saved_tensors
+        grad = lg.clone()
+        ext().ce_backward(grad, tg, lse, stats[1:2], g.reshape(1).float().contiguous(), lg.shape[1])
+        return grad, None
+
+
+def _ce_chunk_rows() -> int:
+    return int(os.environ.get("MTS_FUSED_CE_CHUNK_ROWS", "8192"))
+
+
+class _FusedLinearCEFn(torch.autograd.Function):
+    """Linear + cross entropy without ever holding ``[tokens, vocab]``.
+
+    Rows are processed in chunks: logits GEMM into a reused bf16 buffer, cross entropy with the
+    gradient written in place, then ``dX = dZ W`` and ``dW += dZ^T X`` straight from that buffer.
+    Gradients are produced during the forward pass (as the reference's chunk loop does,
+    minitrain/kernels/triton/fused_linear_cross_entropy.py:52-170); backward only scales them.
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, targets):
+        e = ext()
+        w16 = bf16_weight(weight)
+        vocab, hidden = w16.shape
+        rows = x.shape[0]
+        vp = -(-vocab // 8) * 8
+        chunk = min(_ce_chunk_rows(), rows)
+        xc = x if x.is_contiguous() else x.contiguous()
+        tg = targets.contiguous()
+        dev = x.device
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        stats = torch.zeros(2, dtype=torch.float32, device=dev)
+        valid = torch.zeros(1, dtype=torch.float32, device=dev)
+        e.count_valid(tg, valid)
+        lse = torch.empty(rows, dtype=torch.float32, device=dev)
+        logits = torch.empty(chunk, vp, dtype=torch.bfloat16, device=dev)
+        dx = torch.empty_like(xc) if need_dx else None
+        dw = torch.zeros(vocab, hidden, dtype=torch.float32, device=dev) if need_dw else None
+        one_group: dict[int, torch.Tensor] = {}
+        for lo in range(0, rows, chunk):
+            n = min(chunk, rows - lo)
+            xs, ts, ls = xc[lo:lo + n], tg[lo:lo + n], lse[lo:lo + n]
+            z = logits[:n]
+            _gemm(xs, w16, z, n, vocab, hidden, ldo=vp)
+            e.ce_forward(z, ts, ls, stats, vocab)
+            if not (need_dx or need_dw):
+                continue
+            e.ce_backward(z, ts, ls, valid, None, vocab)
+            if need_dx:
+                _gemm(z, w16, dx[lo:lo + n], n, hidden, vp, b_mn=True, ldo=hidden)
+            if need_dw:
+                if n not in one_group:
+                    one_group[n] = torch.tensor([0, n], dtype=torch.int32, device=dev)
+                _gemm(z, xs, dw, vocab, hidden, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=one_group[n],
+                      num_groups=1, accumulate=True, ldo=hidden)
+        ctx.save_for_backward(dx, dw)
+        ctx.w_dtype = weight.dtype
+        return stats[0] / stats[1]
+
+    @staticmethod
+    def backward(ctx, g):
+        dx, dw = ctx.saved_tensors
+        gx = dx * g.to(dx.dtype) if dx is not None else None
+        gw = (dw * g).to(ctx.w_dtype) if dw is not None else None
+        return gx, gw, None
+
+
+class _RouterFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, top_k, normalize):
+        lg = logits.contiguous()
+        w, idx, lse, sums = ext().router_forward(lg, top_k, normalize)
+        tokens, experts = lg.shape
+        ctx.save_for_backward(lg, lse, idx, w)
+        ctx.normalize = normalize
+        ctx.mark_non_differentiable(idx)
+        inv = 1.0 / tokens
+        return w, idx, sums[:experts] * inv, sums[experts] * inv, sums[experts + 1] * inv
+
+    @staticmethod
+    def backward(ctx, g_w, _g_idx, g_mp, g_z, _g_ent):
+        lg, lse, idx, w = ctx.saved_tensors
+        opt = lambda t: None if t is None else t.float().contiguous()  # noqa: E731
+        gz = None if g_z is None else g_z.float().reshape(1).contiguous()
+        return ext().router_backward(lg, lse, idx, w, opt(g_w), opt(g_mp), gz, ctx.normalize), None, None
+
+
+class _FusedMoEFn(torch.autograd.Function):
+    """Routed SwiGLU experts as four grouped tcgen05 GEMMs around an expert-sorted, 128-row padded layout."""
+
+    @staticmethod
+    def forward(ctx, x, gate_up_proj, down_proj, top_k_index, top_k_weights):
+        e = ext()
+        n_exp, two_i, hidden = gate_up_proj.shape
+        inter = two_i // 2
+        tokens, k = top_k_index.shape
+        xc = x if x.is_contiguous() else x.contiguous()
+        idx = top_k_index.to(torch.int32).contiguous()
+        w16 = top_k_weights.to(torch.bfloat16).contiguous()
+        gu16 = bf16_weight(gate_up_proj).view(n_exp * two_i, hidden)
+        dn16 = bf16_weight(down_proj).view(n_exp * hidden, inter)
+        row_token, token_rows, tile_group, group_rows, meta = e.moe_plan(idx, n_exp)
+        cap = row_token.numel()
+        dev = x.device
+        xs = torch.empty(cap, hidden, dtype=torch.bfloat16, device=dev)
+        e.moe_gather(xc, row_token, xs, meta)
+        post = torch.empty(cap, inter, dtype=torch.bfloat16, device=dev)
+        pre = torch.empty(cap, two_i, dtype=torch.bfloat16, device=dev)
+        tiles = meta[0:1]
+        _gemm(xs, gu16, post, cap, two_i, hidden, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU, aux=pre,
+              tile_group=tile_group, num_row_tiles=tiles, b_group_stride_rows=two_i, ldo=inter)
+        y = torch.empty(cap, hidden, dtype=torch.bfloat16, device=dev)
+        _gemm(post, dn16, y, cap, hidden, inter, mode=GEMM_GROUPED_M, tile_group=tile_group, num_row_tiles=tiles,
+              b_group_stride_rows=hidden, ldo=hidden)
+        out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
+        e.moe_combine(y, token_rows, w16, out, k)
+        ctx.save_for_backward(xs, pre, post, y, w16, row_token, token_rows, tile_group, group_rows, meta,
+                              gate_up_proj, down_proj)
+        ctx.dims = (n_exp, inter, hidden, tokens, k)
+        ctx.w_dtype = top_k_weights.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        e = ext()
+        (xs, pre, post, y, w16, row_token, token_rows, tile_group, group_rows, meta, gate_up_proj,
+         down_proj) = ctx.saved_tensors
+        n_exp, inter, hidden, tokens, k = ctx.dims
+        two_i = 2 * inter
+        cap = row_token.numel()
+        dev = dout.device
+        gu16 = bf16_weight(gate_up_proj).view(n_exp * two_i, hidden)
+        dn16 = bf16_weight(down_proj).view(n_exp * hidden, inter)
+        tiles = meta[0:1]
+        go = dout.contiguous()
+        dys = torch.empty(cap, hidden, dtype=torch.bfloat16, device=dev)
+        dwts = torch.zeros(tokens * k, dtype=torch.float32, device=dev)
+        e.moe_combine_bwd(go, y, row_token, token_rows, w16, dys, dwts, meta, k)
+        # d(post) = dys @ W_down, fused with the SwiGLU derivative -> d(pre) = [d gate | d up]
+        d_pre = torch.empty(cap, two_i, dtype=torch.bfloat16, device=dev)
+        _gemm(dys, dn16, d_pre, cap, inter, hidden, b_mn=True, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU_BWD, aux=pre,
+              tile_group=tile_group, num_row_tiles=tiles, b_group_stride_rows=hidden, ldo=two_i)
+        dx = dgu = ddn = None
+        if ctx.needs_input_grad[0]:
+            dxs = torch.empty(cap, hidden, dtype=torch.bfloat16, device=dev)
+            _gemm(d_pre, gu16, dxs, cap, hidden, two_i, b_mn=True, mode=GEMM_GROUPED_M, tile_group=tile_group,
+                  num_row_tiles=tiles, b_group_stride_rows=two_i, ldo=hidden)
+            dx = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
+            e.moe_combine(dxs, token_rows, None, dx, k)
+        if ctx.needs_input_grad[1]:
+            dgu = torch.empty(n_exp, two_i, hidden, dtype=torch.float32, device=dev)
+            _gemm(d_pre, xs, dgu, two_i, hidden, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=group_rows,
+                  num_groups=n_exp, out_group_stride=two_i * hidden, ldo=hidden)
+            dgu = dgu.to(gate_up_proj.dtype)
+        if ctx.needs_input_grad[2]:
+            ddn = torch.empty(n_exp, hidden, inter, dtype=torch.float32, device=dev)
+            _gemm(dys, post, ddn, hidden, inter, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=group_rows,
+                  num_groups=n_exp, out_group_stride=hidden * inter, ldo=inter)
+            ddn = ddn.to(down_proj.dtype)
+        dw = dwts.view(tokens, k).to(ctx.w_dtype) if ctx.needs_input_grad[4] else None
+        return dx, dgu, ddn, None, dw
+
+
+# ---------------------------------------------------------------------------------------------
+# backend
+# ---------------------------------------------------------------------------------------------
+def _native_act(*tensors: torch.Tensor) -> bool:
+    return all(t.is_cuda and t.dtype in (torch.bfloat16, torch.float32) for t in tensors)
+
+
+class NativeOpsBackend(TorchOpsBackend):
+    name = "native"
+
+    def __init__(self) -> None:
+        ext()
+        self.dispatch = Counter()
+
+    def _count(self, op: str, native: bool) -> bool:
+        self.dispatch[f"{op}:{'native' if native else 'fallback'}"] += 1
+        return native
+
+    def dispatch_summary(self) -> dict[str, int]:
+        return dict(self.dispatch)
+
+    # -- projections ------------------------------------------------------------------------
+    def linear(self, x, weight):
+        if self._count("linear", _gemm_ok(x, weight)):
+            return _LinearFn.apply(x, weight)
+        return torch.nn.functional.linear(x, weight.to(x.dtype) if weight.dtype != x.dtype and not torch.is_autocast_enabled() else weight)
+
+    # -- memory-bound ops ---------------------------------------------------------------------
+    def rmsnorm(self, x, weight, eps):
+        ok = _native_act(x) and weight.is_cuda and x.shape[-1] % 8 == 0 and x.shape[-1] <= 1024
+        if self._count("rmsnorm", ok):
+            return _RMSNormFn.apply(x, weight, eps)
+        return super().rmsnorm(x, weight, eps)
+
+    def rope(self, q, k, cos, sin):
+        def aligned(t):
+            vec = 8 if t.dtype == torch.bfloat16 else 4
+            return (t.dim() == 4 and t.stride(3) == 1 and t.shape[3] % 16 == 0 and t.data_ptr() % 16 == 0
+                    and all(s % vec == 0 for s in t.stride()[:3]))
+        ok = (_native_act(q, k) and q.dtype == k.dtype and cos.dtype == q.dtype and cos.is_contiguous()
+              and sin.is_contiguous() and aligned(q) and aligned(k))
+        if self._count("rope", ok):
+            return _RopeFn.apply(q, k, cos, sin)
+        return super().rope(q, k, cos, sin)
+
+    def swiglu(self, gate, up):
+        ok = _native_act(gate, up) and gate.dtype == up.dtype and gate.shape == up.shape and gate.numel() % 8 == 0
+        if self._count("swiglu", ok):
+            return _SwigluFn.apply(gate, up)
+        return super().swiglu(gate, up)
+
+    def cross_entropy(self, logits, targets):
+        ok = _native_act(logits) and logits.dim() == 2 and targets.is_cuda and targets.dtype == torch.long
+        if self._count("cross_entropy", ok):
+            return _CrossEntropyFn.apply(logits, targets)
+        return super().cross_entropy(logits, targets)
+
+    def fused_linear_cross_entropy(self, x, weight, targets):
+        ok = _gemm_ok(x, weight) and x.dim() == 2 and targets.is_cuda and targets.dtype == torch.long
+        if self._count("fused_linear_cross_entropy", ok):
+            return _FusedLinearCEFn.apply(x, weight, targets)
+        return super().fused_linear_cross_entropy(x, weight, targets)
+
+    def router_postprocess(self, logits, top_k, *, normalize):
+        check_router_args(logits, top_k)
+        ok = logits.is_cuda and logits.shape[1] <= 64 and top_k <= 8
+        if self._count("router_postprocess", ok):
+            w, idx, mean_prob, z, ent = _RouterFn.apply(logits, top_k, normalize)
+            return RouterPostprocessOutput(w, idx, mean_prob, z, ent.detach())
+        return super().router_postprocess(logits, top_k, normalize=normalize)
+
+    def fused_moe(self, x, gate_up_proj, down_proj, top_k_index, top_k_weights):
+        n_exp, two_i, hidden = gate_up_proj.shape
+        ok = (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and hidden % 8 == 0 and two_i % 256 == 0
+              and n_exp <= 64 and gate_up_proj.is_cuda)
+        if self._count("fused_moe", ok):
+            return _FusedMoEFn.apply(x, gate_up_proj, down_proj, top_k_index, top_k_weights)
+        return super().fused_moe(x, gate_up_proj, down_proj, top_k_index, top_k_weights)
+
+    def attention(self, q, k, v, *, is_causal, dropout_p):
+        from mini_train_sys_b200.ops import native_attention
+
+        if self._count("attention", native_attention.supported(q, k, v, is_causal=is_causal, dropout_p=dropout_p)):
+            return native_attention.flash_attention(q, k, v, is_causal=is_causal, dropout_p=dropout_p)
+        return super().attention(q, k, v, is_causal=is_causal, dropout_p=dropout_p)
+
+
+def scaled_dot_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)

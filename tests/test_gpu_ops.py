@@ -1,0 +1,311 @@
+"""sm_100a kernels against the fp32 oracle (``ops/reference.py``).  All tests need a GPU."""
+
+import math
+
+import pytest
+import torch
+
+from mini_train_sys_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def nb():
+    from mini_train_sys_b200.ops import native_backend
+
+    return native_backend
+
+
+@pytest.fixture(scope="module")
+def ops(nb):
+    return nb.NativeOpsBackend()
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    got, want = got.float(), want.float()
+    return float((got - want).norm() / want.norm().clamp_min(1e-12))
+
+
+def assert_close(got, want, tol, what=""):
+    err = rel_err(got, want)
+    assert math.isfinite(err) and err <= tol, f"{what}: relative L2 error {err:.3e} > {tol:.1e}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,hidden", [(1000, 768), (37, 128), (513, 1024)])
+def test_rmsnorm(ops, dtype, rows, hidden):
+    torch.manual_seed(0)
+    x = torch.randn(rows, hidden, device=DEV, dtype=dtype, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV)).requires_grad_()
+    dy = torch.randn(rows, hidden, device=DEV, dtype=dtype)
+    y = ops.rmsnorm(x, w, 1e-5)
+    gx, gw = torch.autograd.grad(y, (x, w), dy)
+    x64 = x.detach().double().requires_grad_()
+    w64 = w.detach().double().requires_grad_()
+    y64 = x64 * torch.rsqrt(x64.pow(2).mean(-1, keepdim=True) + 1e-5) * w64
+    rx, rw = torch.autograd.grad(y64, (x64, w64), dy.double())
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    assert_close(y, y64, tol, "y")
+    assert_close(gx, rx, tol, "dx")
+    assert_close(gw, rw, 5e-3 if dtype == torch.bfloat16 else 1e-4, "dw")
+    assert ops.dispatch["rmsnorm:native"] > 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rope_strided(ops, dtype):
+    from mini_train_sys_b200.models.rotary import rope_tables
+
+    torch.manual_seed(1)
+    b, s, h, d = 3, 130, 4, 64
+    fused = torch.randn(b, s, 3, h, d, device=DEV, dtype=dtype, requires_grad=True)
+    q, k = fused[:, :, 0].transpose(1, 2), fused[:, :, 1].transpose(1, 2)
+    cos, sin = (t.to(DEV).to(dtype) for t in rope_tables(d, 256, 10000.0))
+    qo, ko = ops.rope(q, k, cos[:s], sin[:s])
+    assert qo.is_contiguous() and qo.shape == (b, h, s, d)
+    dq, dk = torch.randn_like(qo), torch.randn_like(ko)
+    (g,) = torch.autograd.grad((qo, ko), fused, (dq, dk))
+    f64 = fused.detach().double().requires_grad_()
+    q64, k64 = f64[:, :, 0].transpose(1, 2), f64[:, :, 1].transpose(1, 2)
+    rq, rk = ref.rope_ref(q64, cos[:s].double(), sin[:s].double()), ref.rope_ref(k64, cos[:s].double(), sin[:s].double())
+    (rg,) = torch.autograd.grad((rq.double(), rk.double()), f64, (dq.double(), dk.double()))
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    assert_close(qo, rq, tol, "q")
+    assert_close(ko, rk, tol, "k")
+    assert_close(g, rg, tol, "grad")
+
+
+def test_swiglu(ops):
+    torch.manual_seed(2)
+    g = torch.randn(777, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    u = torch.randn(777, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn_like(g)
+    y = ops.swiglu(g, u)
+    gg, gu = torch.autograd.grad(y, (g, u), dy)
+    g64, u64 = g.detach().double().requires_grad_(), u.detach().double().requires_grad_()
+    y64 = torch.nn.functional.silu(g64) * u64
+    rg, ru = torch.autograd.grad(y64, (g64, u64), dy.double())
+    assert_close(y, y64, 1e-2, "y")
+    assert_close(gg, rg, 1e-2, "dgate")
+    assert_close(gu, ru, 1e-2, "dup")
+
+
+@pytest.mark.parametrize("rows,vocab,dtype", [(64, 50257, torch.bfloat16), (33, 1000, torch.float32), (8, 7, torch.float32)])
+def test_cross_entropy(ops, rows, vocab, dtype):
+    torch.manual_seed(3)
+    logits = (2 * torch.randn(rows, vocab, device=DEV)).to(dtype).requires_grad_()
+    targets = torch.randint(0, vocab, (rows,), device=DEV)
+    targets[::5] = -100
+    loss = ops.cross_entropy(logits, targets)
+    (g,) = torch.autograd.grad(loss, logits)
+    l64 = logits.detach().double().requires_grad_()
+    want = torch.nn.functional.cross_entropy(l64, targets)
+    (rg,) = torch.autograd.grad(want, l64)
+    assert abs(float(loss) - float(want)) < 2e-3 * max(1.0, abs(float(want)))
+    assert_close(g, rg, 2e-2 if dtype == torch.bfloat16 else 1e-4, "dlogits")
+
+
+@pytest.mark.parametrize("tokens,experts,k,normalize", [(257, 64, 2, True), (4096, 8, 2, True), (100, 4, 1, False), (50, 8, 3, False)])
+def test_router(ops, tokens, experts, k, normalize):
+    torch.manual_seed(4)
+    logits = torch.randn(tokens, experts, device=DEV, requires_grad=True)
+    out = ops.router_postprocess(logits, k, normalize=normalize)
+    want = ref.router_ref(logits.detach().double().float().requires_grad_(), k, normalize)
+    assert torch.equal(out.expert_indices.sort(-1).values, want.expert_indices.sort(-1).values)
+    assert_close(out.expert_weights, want.expert_weights, 1e-5, "weights")
+    assert_close(out.probability_per_expert, want.probability_per_expert, 1e-5, "mean prob")
+    assert abs(float(out.z_loss) - float(want.z_loss)) < 1e-4 * max(1.0, float(want.z_loss))
+    assert abs(float(out.entropy) - float(want.entropy)) < 1e-4
+    # combined gradient through all three differentiable outputs
+    gw = torch.randn_like(out.expert_weights)
+    gp = torch.randn(experts, device=DEV)
+    l32 = logits.detach().clone().requires_grad_()
+    w2 = ref.router_ref(l32, k, normalize)
+    obj_ref = (w2.expert_weights * gw).sum() + (w2.probability_per_expert * gp).sum() + 0.7 * w2.z_loss
+    (rg,) = torch.autograd.grad(obj_ref, l32)
+    obj = (out.expert_weights * gw).sum() + (out.probability_per_expert * gp).sum() + 0.7 * out.z_loss
+    (g,) = torch.autograd.grad(obj, logits)
+    assert_close(g, rg, 1e-4, "dlogits")
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (300, 520, 136), (1024, 768, 768), (4096, 2304, 768), (77, 8, 8),
+               (129, 257, 72)]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+def test_gemm_nt(nb, m, n, k):
+    torch.manual_seed(5)
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(n, k, device=DEV, dtype=torch.bfloat16)
+    n_pad = -(-n // 8) * 8
+    out = torch.full((m, n_pad), 7.0, device=DEV, dtype=torch.bfloat16)
+    nb._gemm(a, b, out, m, n, k, ldo=n_pad)
+    want = a.float() @ b.float().t()
+    assert_close(out[:, :n], want, 1e-2, f"nt {m}x{n}x{k}")
+    assert bool((out[:, n:] == 7.0).all()), "columns beyond N were written"
+    nb.check_kernel_status()
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+def test_gemm_nn(nb, m, n, k):
+    torch.manual_seed(6)
+    n8 = -(-n // 8) * 8
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(k, n8, device=DEV, dtype=torch.bfloat16)
+    out = nb.gemm_nn(a, b)
+    assert_close(out, a.float() @ b.float(), 1e-2, f"nn {m}x{n8}x{k}")
+    nb.check_kernel_status()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (768, 2304, 4096), (200, 136, 1000), (2304, 768, 20000), (50, 72, 130)])
+def test_gemm_tn(nb, m, n, k):
+    torch.manual_seed(7)
+    m8, n8 = -(-m // 8) * 8, -(-n // 8) * 8
+    a = torch.randn(k, m8, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(k, n8, device=DEV, dtype=torch.bfloat16)
+    out = nb.gemm_tn(a, b)
+    assert out.dtype == torch.float32
+    assert_close(out, a.float().t() @ b.float(), 1e-2, f"tn {m8}x{n8}x{k}")
+    nb.check_kernel_status()
+
+
+def test_linear_autograd(ops):
+    torch.manual_seed(8)
+    x = torch.randn(4, 130, 768, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (0.02 * torch.randn(2304, 768, device=DEV)).requires_grad_()
+    dy = torch.randn(4, 130, 2304, device=DEV, dtype=torch.bfloat16)
+    y = ops.linear(x, w)
+    gx, gw = torch.autograd.grad(y, (x, w), dy)
+    x64, w64 = x.detach().double().requires_grad_(), w.detach().double().requires_grad_()
+    y64 = x64 @ w64.t()
+    rx, rw = torch.autograd.grad(y64, (x64, w64), dy.double())
+    assert gw.dtype == torch.float32
+    assert_close(y, y64, 1e-2, "y")
+    assert_close(gx, rx, 1.5e-2, "dx")
+    assert_close(gw, rw, 1e-2, "dw")
+    assert ops.dispatch["linear:native"] > 0
+
+
+@pytest.mark.parametrize("rows,vocab,hidden,chunk", [(300, 1000, 128, 128), (1024, 50257, 768, 512)])
+def test_fused_linear_cross_entropy(ops, monkeypatch, rows, vocab, hidden, chunk):
+    monkeypatch.setenv("MTS_FUSED_CE_CHUNK_ROWS", str(chunk))
+    torch.manual_seed(9)
+    x = torch.randn(rows, hidden, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(vocab, hidden, device=DEV)).requires_grad_()
+    t = torch.randint(0, vocab, (rows,), device=DEV)
+    t[::7] = -100
+    loss = ops.fused_linear_cross_entropy(x, w, t)
+    gx, gw = torch.autograd.grad(loss * 1.5, (x, w))
+    x64, w64 = x.detach().double().requires_grad_(), w.detach().to(torch.bfloat16).double().requires_grad_()
+    want = torch.nn.functional.cross_entropy(x64 @ w64.t(), t)
+    rx, rw = torch.autograd.grad(want * 1.5, (x64, w64))
+    assert abs(float(loss) - float(want)) < 5e-3 * max(1.0, abs(float(want)))
+    assert_close(gx, rx, 3e-2, "dx")
+    assert_close(gw, rw, 3e-2, "dw")
+
+
+def _skewed_routes(tokens, experts, k, mode):
+    if mode == "uniform":
+        scores = torch.rand(tokens, experts, device=DEV)
+    elif mode == "one_expert":
+        scores = torch.rand(tokens, experts, device=DEV)
+        scores[:, 1] += 10
+    else:  # "empty": experts 0 and 3 never chosen
+        scores = torch.rand(tokens, experts, device=DEV)
+        scores[:, 0] -= 10
+        scores[:, 3] -= 10
+    idx = scores.topk(k, -1).indices.to(torch.int32)
+    w = torch.rand(tokens, k, device=DEV)
+    return idx, w / w.sum(-1, keepdim=True)
+
+
+@pytest.mark.parametrize("mode", ["uniform", "one_expert", "empty"])
+def test_moe_plan(nb, mode):
+    torch.manual_seed(10)
+    tokens, experts, k = 1500, 8, 2
+    idx, _ = _skewed_routes(tokens, experts, k, mode)
+    row_token, token_rows, tile_group, group_rows, meta = nb.ext().moe_plan(idx.contiguous(), experts)
+    rt, tr, tg, gr, mt = (t.cpu() for t in (row_token, token_rows, tile_group, group_rows, meta))
+    counts = torch.bincount(idx.flatten().long().cpu(), minlength=experts)
+    assert int(mt[2]) == 0
+    padded = (counts + 127) // 128 * 128
+    assert gr.tolist() == [0, *padded.cumsum(0).tolist()]
+    assert int(mt[1]) == int(padded.sum()) and int(mt[0]) == int(padded.sum()) // 128
+    flat = idx.flatten().cpu()
+    assert tr.min() >= 0 and tr.unique().numel() == tokens * k
+    for route in range(0, tokens * k, 97):
+        row = int(tr[route])
+        e = int(flat[route])
+        assert gr[e] <= row < gr[e] + counts[e]
+        assert int(rt[row]) == route // k
+        assert int(tg[row // 128]) == e
+    live = rt[: int(mt[1])]
+    assert int((live >= 0).sum()) == tokens * k
+    # token order is preserved inside every expert
+    for e in range(experts):
+        seg = rt[int(gr[e]): int(gr[e]) + int(counts[e])]
+        assert bool((seg[1:] >= seg[:-1]).all())
+
+
+@pytest.mark.parametrize("mode", ["uniform", "one_expert", "empty"])
+@pytest.mark.parametrize("tokens,hidden,inter,experts", [(1000, 128, 128, 4), (2048, 768, 1024, 8)])
+def test_fused_moe(ops, mode, tokens, hidden, inter, experts):
+    torch.manual_seed(11)
+    k = 2
+    x = torch.randn(tokens, hidden, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    gu = (0.05 * torch.randn(experts, 2 * inter, hidden, device=DEV)).requires_grad_()
+    dn = (0.05 * torch.randn(experts, hidden, inter, device=DEV)).requires_grad_()
+    idx, w = _skewed_routes(tokens, experts, k, mode)
+    w = w.to(torch.bfloat16).requires_grad_()
+    dout = torch.randn(tokens, hidden, device=DEV, dtype=torch.bfloat16)
+    out = ops.fused_moe(x, gu, dn, idx, w)
+    gx, ggu, gdn, gw = torch.autograd.grad(out, (x, gu, dn, w), dout)
+    leaves = [t.detach().float().requires_grad_() for t in (x, gu.to(torch.bfloat16), dn.to(torch.bfloat16), w)]
+    want = ref.moe_ref(*leaves[:3], idx, leaves[3])
+    rx, rgu, rdn, rw = torch.autograd.grad(want, leaves, dout.float())
+    assert_close(out, want, 2e-2, "out")
+    assert_close(gx, rx, 3e-2, "dx")
+    assert_close(ggu, rgu, 3e-2, "d gate_up")
+    assert_close(gdn, rdn, 3e-2, "d down")
+    assert_close(gw, rw, 3e-2, "d route weights")
+    assert ops.dispatch["fused_moe:native"] > 0
+
+
+def test_adamw_matches_torch(nb):
+    torch.manual_seed(12)
+    n = 100_003
+    p = torch.randn(n + 1, device=DEV)[:n].clone()
+    g = torch.randn(n, device=DEV)
+    ref_p = p.clone().requires_grad_()
+    opt = torch.optim.AdamW([ref_p], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    shadow = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    for step in (1, 2, 3):
+        ref_p.grad = g.clone() * 0.5
+        opt.step()
+        nb.ext().adamw_step(p, g, m, v, shadow, 1e-3, 0.9, 0.95, 1e-8, 0.1, step, None, 0.5)
+    assert_close(p, ref_p.detach(), 1e-5, "adamw params")
+    assert_close(shadow, ref_p.detach(), 1e-2, "bf16 shadow")
+
+
+def test_tiny_model_matches_torch_backend():
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+
+    cfg = ModelConfig(vocab_size=1000, seq_len=128, n_layers=2, n_heads=4, hidden_size=256, intermediate_size=256,
+                      ffn_type="moe", num_experts=4, experts_per_token=2, tie_word_embeddings=True)
+    tokens = torch.randint(0, 1000, (4, 129), device=DEV)
+    losses, grads = {}, {}
+    for name in ("torch", "native"):
+        torch.manual_seed(0)
+        model = MiniTransformer(cfg, get_ops_backend(name), activation_dtype=torch.bfloat16).to(DEV)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss, _ = model(tokens[:, :-1], targets=tokens[:, 1:], use_fused_loss=True)
+        loss.backward()
+        losses[name] = float(loss)
+        grads[name] = {n: p.grad.float().clone() for n, p in model.named_parameters()}
+    assert abs(losses["torch"] - losses["native"]) < 2e-2, losses
+    for n, g in grads["torch"].items():
+        err = rel_err(grads["native"][n], g)
+        assert err < 0.1, f"{n}: {err}"
