@@ -181,7 +181,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t M, int64_t N, in
   g.status = status_word(a.get_device()).data_ptr<int>();
   g.sm_limit = int(sm_limit);
   g.stream = cur_stream();
-  check_launch(mts::launch_gemm_sm100(g), "tcgen05 gemm");
+  const cudaError_t gemm_err = mts::launch_gemm_sm100(g);
+  TORCH_CHECK(gemm_err == cudaSuccess, "tcgen05 gemm failed: ", cudaGetErrorString(gemm_err), " (", mts::g_last_error, ")");
 }
 
 // ---------------- cross entropy ----------------

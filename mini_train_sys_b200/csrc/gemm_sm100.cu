@@ -11,11 +11,13 @@
 #include "ptx_sm100.cuh"
 
 #include <cudaTypedefs.h>
+#include <cstdio>
 #include <mutex>
 
 namespace mts {
 
 unsigned long long g_launch_count = 0;
+const char* g_last_error = "";
 
 namespace {
 
@@ -462,8 +464,11 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 // 2-D bf16 tensor [rows, cols] (cols contiguous), box = [box_rows, 64 cols], 128-byte swizzle.
 bool encode_bf16_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
   auto fn = encode_fn();
-  if (fn == nullptr) return false;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0) return false;
+  if (fn == nullptr) { g_last_error = "cuTensorMapEncodeTiled entry point not found"; return false; }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0 || rows <= 0 || cols <= 0) {
+    g_last_error = "operand base/pitch not 16-byte aligned or empty";
+    return false;
+  }
   const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
   const cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
   const cuuint32_t box[2] = {64u, cuuint32_t(box_rows)};
@@ -471,6 +476,12 @@ bool encode_bf16_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t co
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    static char msg[160];
+    snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled error %d (rows=%lld cols=%lld ld=%lld box_rows=%d)", int(r),
+             (long long)rows, (long long)cols, (long long)ld, box_rows);
+    g_last_error = msg;
+  }
   return r == CUDA_SUCCESS;
 }
 
@@ -504,9 +515,11 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
   p.status = a.status;
   p.tiles_m = int((a.M + BM - 1) / BM);
   p.tiles_n = int((a.N + BN - 1) / BN);
+  g_last_error = "inconsistent epilogue arguments";
   if (a.epilogue == EPI_SWIGLU && (a.N % 256 != 0 || a.mode != GEMM_GROUPED_M || a.b_mn_major)) return cudaErrorInvalidValue;
   if (a.epilogue == EPI_SWIGLU_BWD && a.aux == nullptr) return cudaErrorInvalidValue;
   if (a.atomic_out && !a.out_fp32) return cudaErrorInvalidValue;
+  g_last_error = "";
 
   long long total = (long long)p.tiles_m * p.tiles_n;
   if (a.mode == GEMM_GROUPED_K) total *= a.num_groups;
@@ -521,9 +534,12 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
+  (void)cudaGetLastError();   // do not attribute an earlier sticky error to this launch
   gemm_tcgen05_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, a.stream>>>(tm_a, tm_b, p);
   ++g_launch_count;
-  return cudaGetLastError();
+  const cudaError_t launch_err = cudaGetLastError();
+  if (launch_err != cudaSuccess) g_last_error = "kernel launch failed";
+  return launch_err;
 }
 
 }  // namespace mts

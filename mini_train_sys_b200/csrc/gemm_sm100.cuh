@@ -71,5 +71,7 @@ cudaError_t launch_gemm_sm100(const GemmArgs& args);
 
 // Number of kernels launched through this library since load (the benchmark reports it).
 extern unsigned long long g_launch_count;
+// Human-readable reason of the most recent launch_gemm_sm100 failure ("" when none).
+extern const char* g_last_error;
 
 }  // namespace mts

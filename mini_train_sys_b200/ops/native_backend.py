@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import math
 import os
+import weakref
 from collections import Counter
 
 import torch
@@ -50,25 +51,32 @@ def check_kernel_status(device: torch.device | int | None = None) -> None:
 # ---------------------------------------------------------------------------------------------
 # GEMM wrappers
 # ---------------------------------------------------------------------------------------------
-_weight_cache: dict[int, tuple[int, torch.Tensor]] = {}
+_weight_cache: dict[int, tuple] = {}
 _rows_cache: dict[tuple, torch.Tensor] = {}
 
 
 def bf16_weight(weight: torch.Tensor) -> torch.Tensor:
-    """bf16 copy of a (usually fp32) parameter, refreshed only when the parameter changes."""
+    """bf16 copy of a (usually fp32) parameter, refreshed only when the parameter changes.
+
+    Entries are keyed by object identity and validated with a weak reference plus the tensor's
+    version counter and storage address, so a recycled address can never return a stale copy.
+    """
 
     if weight.dtype == torch.bfloat16:
         return weight if weight.is_contiguous() else weight.contiguous()
-    key = weight.data_ptr()
+    key = id(weight)
     hit = _weight_cache.get(key)
-    version = weight._version
-    if hit is not None and hit[0] == version and hit[1].shape == weight.shape:
-        return hit[1]
+    version, ptr = weight._version, weight.data_ptr()
+    if hit is not None and hit[0]() is weight and hit[1] == version and hit[2] == ptr:
+        return hit[3]
     src = weight.detach()
     if not src.is_contiguous():
         src = src.contiguous()
     out = ext().cast_bf16(src.float() if src.dtype != torch.float32 else src)
-    _weight_cache[key] = (version, out)
+    if len(_weight_cache) > 4096:
+        for k in [k for k, v in _weight_cache.items() if v[0]() is None]:
+            del _weight_cache[k]
+    _weight_cache[key] = (weakref.ref(weight), version, ptr, out)
     return out
 
 
