@@ -1,0 +1,820 @@
+// FlashAttention forward / backward for sm_100a (head_dim 64, bf16); interface in attention.cuh.
+//
+// Every CTA has 192 threads: warp 0 drives TMA, warp 1 issues tcgen05.mma, warps 2-5 (one thread per
+// tile row) do the softmax arithmetic on accumulators read from tensor memory.  Probability / dS
+// tiles that feed a second MMA are written to shared memory in the 128-byte swizzled K-major layout
+// the UMMA descriptors expect.  Shared memory and TMEM budgets are sized for two CTAs per SM so one
+// CTA's exponentials overlap the other's MMAs.
+//
+//   forward : 128 queries x 128 keys per step;  S = Q K^T -> softmax -> P V, running O in registers.
+//   backward: two atomic-free sweeps.
+//     dK/dV sweep: CTA owns 128 keys, streams 64-query tiles: S^T = K Q^T, dP^T = V dO^T,
+//                  dV += P^T dO, dK += dS^T Q   (accumulators stay in TMEM for the whole sweep)
+//     dQ sweep   : CTA owns 128 queries, streams 64-key tiles: S = Q K^T, dP = dO V^T, dQ += dS K
+//
+// Reference counterparts: vendored FlashAttention-2 sm80 kernels (minitrain/kernels/cuda_ext/csrc/
+// third_party/flash_attn/src/flash_fwd_kernel.h:51-494, flash_bwd_kernel.h:80-841) and the Triton
+// kernels in minitrain/kernels/triton/flash_attention.py:213-938.
+#include "attention.cuh"
+#include "ops.cuh"
+#include "ptx_sm100.cuh"
+
+#include <cudaTypedefs.h>
+#include <cstdio>
+#include <math_constants.h>
+#include <mutex>
+
+namespace mts {
+
+const char* g_attn_last_error = "";
+
+namespace {
+
+constexpr int D = kAttnHeadDim;
+constexpr int TILE128 = 128 * D * 2;   // bytes of a [128 x 64] bf16 tile
+constexpr int TILE64 = 64 * D * 2;
+constexpr int THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __host__ __forceinline__ uint32_t fmix32(uint32_t h) {
+  h ^= h >> 16; h *= 0x85ebca6bu; h ^= h >> 13; h *= 0xc2b2ae35u; h ^= h >> 16;
+  return h;
+}
+
+struct Dropout {
+  uint32_t key;       // per (seed, batch*head)
+  uint32_t thresh;    // drop when byte < thresh ; 0 disables
+  float inv_keep;
+  uint32_t words_per_row;
+  __device__ __forceinline__ uint32_t word(uint32_t q, uint32_t kword) const {
+    return fmix32(((q * words_per_row + kword) * 0x9E3779B1u) ^ key);
+  }
+  __device__ __forceinline__ bool keep(uint32_t q, uint32_t k) const {
+    return ((word(q, k >> 2) >> ((k & 3u) * 8u)) & 0xFFu) >= thresh;
+  }
+};
+
+__device__ __host__ __forceinline__ uint32_t dropout_key(unsigned long long seed, uint32_t bh) {
+  return fmix32(uint32_t(seed) ^ fmix32(uint32_t(seed >> 32) + bh * 0x9E3779B9u));
+}
+
+__device__ __forceinline__ Dropout make_dropout(float p, unsigned long long seed, uint32_t bh, int S) {
+  Dropout d;
+  d.thresh = p > 0.f ? uint32_t(p * 256.f + 0.5f) : 0u;
+  d.inv_keep = 1.f / (1.f - float(d.thresh) * (1.f / 256.f));
+  d.key = dropout_key(seed, bh);
+  d.words_per_row = uint32_t((S + 3) / 4);
+  return d;
+}
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// 16-byte chunk `chunk` (0..7) of row `row` in a 128-byte-swizzled tile with 128-byte rows
+__device__ __forceinline__ void st_swizzled(uint8_t* tile, int row, int chunk, uint4 v) {
+  *reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = v;
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int kstep) {   // kstep: 16 contraction elements
+  return make_smem_desc_sw128(tile_addr + kstep * 32, 16, 1024);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int kstep) {  // tile = [K rows x 64], rows of 128 B
+  return make_smem_desc_sw128(tile_addr + kstep * 2048, 8192, 1024);
+}
+
+__device__ __forceinline__ void epilogue_arrive(uint64_t* bar, int lane) {
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
+__device__ __forceinline__ void store_row64(__nv_bfloat16* dst, const float (&v)[64], float mul) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint4 q;
+    q.x = pack2(v[8 * j + 0] * mul, v[8 * j + 1] * mul);
+    q.y = pack2(v[8 * j + 2] * mul, v[8 * j + 3] * mul);
+    q.z = pack2(v[8 * j + 4] * mul, v[8 * j + 5] * mul);
+    q.w = pack2(v[8 * j + 6] * mul, v[8 * j + 7] * mul);
+    reinterpret_cast<uint4*>(dst)[j] = q;
+  }
+}
+
+struct Params {
+  __nv_bfloat16 *o, *dq, *dk, *dv;
+  long long o_sb, o_sh, o_ss, dq_sb, dq_sh, dq_ss, dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
+  float* lse;
+  const float* delta;
+  int B, H, S, causal;
+  float scale, dropout_p;
+  unsigned long long seed;
+  int* status;
+};
+
+// =====================================================================================================
+// forward
+// =====================================================================================================
+constexpr int FWD_SMEM = TILE128 /*Q*/ + 3 * TILE128 /*K,V ring*/ + 2 * TILE128 /*P*/ + 1024;
+
+__global__ void __launch_bounds__(THREADS, 2)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sRing = smem + TILE128;
+  uint8_t* sP = smem + 4 * TILE128;
+
+  __shared__ __align__(8) uint64_t q_full, slot_full[3], slot_empty[3], s_full, s_free, p_ready, pv_full;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_word;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_q_tiles = (p.S + 127) / 128;
+  const int q_tile = n_q_tiles - 1 - int(blockIdx.x);      // heavy (late) causal tiles are scheduled first
+  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int q0 = q_tile * 128;
+  const int n_kv = p.causal ? min((p.S + 127) / 128, q_tile + 1) : (p.S + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(&slot_full[i], 1); mbar_init(&slot_empty[i], 1); }
+    mbar_init(&s_full, 1); mbar_init(&s_free, 4); mbar_init(&p_ready, 4); mbar_init(&pv_full, 1);
+    abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_s = tmem_slot, tmem_pv = tmem_slot + 128;
+  volatile int* abort_ptr = &abort_word;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&q_full, TILE128);
+      tma_load_4d(sQ, &tm_q, &q_full, 0, q0, h, b);
+      for (int i = 0; i < 2 * n_kv; ++i) {
+        const int slot = i % 3;
+        if (!mbar_wait(&slot_empty[slot], ((i / 3) & 1) ^ 1, abort_ptr)) break;
+        mbar_expect_tx(&slot_full[slot], TILE128);
+        tma_load_4d(sRing + slot * TILE128, (i & 1) ? &tm_v : &tm_k, &slot_full[slot], 0, (i >> 1) * 128, h, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      const uint32_t idesc_pv = make_idesc_bf16(128, 64, false, true);
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      bool ok = mbar_wait(&q_full, 0, abort_ptr);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int ik = 2 * j, iv = 2 * j + 1;
+        if (!mbar_wait(&slot_full[ik % 3], (ik / 3) & 1, abort_ptr)) break;
+        if (!mbar_wait(&s_free, (j & 1) ^ 1, abort_ptr)) break;
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(sRing + (ik % 3) * TILE128);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_bf16_ss(tmem_s, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_s, kk != 0);
+        umma_commit(&s_full);
+        umma_commit(&slot_empty[ik % 3]);
+        if (!mbar_wait(&p_ready, j & 1, abort_ptr)) break;
+        if (!mbar_wait(&slot_full[iv % 3], (iv / 3) & 1, abort_ptr)) break;
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(sRing + (iv % 3) * TILE128);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16_ss(tmem_pv, desc_kmajor(p_addr + (kk >> 2) * TILE128, kk & 3), desc_mnmajor(v_addr, kk), idesc_pv, kk != 0);
+        umma_commit(&pv_full);
+        umma_commit(&slot_empty[iv % 3]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int q_row = q0 + r;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const float scale_log2 = p.scale * LOG2E;
+    const Dropout drop = make_dropout(p.dropout_p, p.seed, uint32_t(bh), p.S);
+    float m = -CUDART_INF_F, l = 0.f;
+    float o[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait(&s_full, j & 1, abort_ptr)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int k0 = j * 128;
+      const bool need_mask = (p.causal && k0 + 127 > q0) || (k0 + 128 > p.S);
+      float mx = -CUDART_INF_F;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rr[32];
+        tmem_ld_32x32(tmem_s + lane_base + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(rr[i]);
+          if (need_mask) {
+            const int kidx = k0 + c * 32 + i;
+            if (kidx >= p.S || (p.causal && kidx > q_row)) v = -CUDART_INF_F;
+          }
+          mx = fmaxf(mx, v);
+        }
+      }
+      const float m_new = fmaxf(m, mx * scale_log2);
+      const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
+      const float alpha = ex2(m - m_use);
+      float rowsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rr[32];
+        tmem_ld_32x32(tmem_s + lane_base + c * 32, rr);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kidx = k0 + c * 32 + i;
+          float e = ex2(__uint_as_float(rr[i]) * scale_log2 - m_use);
+          if (need_mask && (kidx >= p.S || (p.causal && kidx > q_row))) e = 0.f;
+          rowsum += e;
+          pv[i] = e;
+        }
+        if (drop.thresh != 0u) {
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            const uint32_t bits = drop.word(uint32_t(q_row), uint32_t(k0 + c * 32 + 4 * w) >> 2);
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+              pv[4 * w + t] = ((bits >> (8 * t)) & 0xFFu) >= drop.thresh ? pv[4 * w + t] * drop.inv_keep : 0.f;
+          }
+        }
+        uint8_t* half = sP + (c >> 1) * TILE128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 q4;
+          q4.x = pack2(pv[8 * g + 0], pv[8 * g + 1]); q4.y = pack2(pv[8 * g + 2], pv[8 * g + 3]);
+          q4.z = pack2(pv[8 * g + 4], pv[8 * g + 5]); q4.w = pack2(pv[8 * g + 6], pv[8 * g + 7]);
+          st_swizzled(half, r, (c & 1) * 4 + g, q4);
+        }
+      }
+      epilogue_arrive(&s_free, lane);            // S may be overwritten by the next Q K^T
+      l = l * alpha + rowsum;
+      m = m_new;
+      fence_proxy_async_smem();                  // P (generic-proxy stores) -> visible to the tensor core
+      epilogue_arrive(&p_ready, lane);
+      if (!mbar_wait(&pv_full, j & 1, abort_ptr)) { ok = false; break; }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rr[32];
+        tmem_ld_32x32(tmem_pv + lane_base + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(rr[i]);
+      }
+    }
+    if (ok && q_row < p.S) {
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      store_row64(p.o + (long long)b * p.o_sb + (long long)h * p.o_sh + (long long)q_row * p.o_ss, o, inv_l);
+      p.lse[((long long)bh) * p.S + q_row] = (m + log2f(l)) * LN2;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_word != 0) {
+    __nanosleep(50000);   // bounded grace period for bulk copies still in flight
+    if (p.status != nullptr) atomicMax(p.status, abort_word);
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_slot, 256);
+}
+
+// =====================================================================================================
+// backward, sweep 1: dK / dV.  CTA = 128 keys; streams 64-query tiles.
+// =====================================================================================================
+constexpr int BWD_KV_SMEM = 2 * TILE128 /*K,V*/ + 4 * TILE64 /*Q,dO x 2 stages*/ + 2 * TILE128 /*P^T, dS^T*/ + 1024;
+
+__global__ void __launch_bounds__(THREADS, 2)
+flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do64, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + TILE128;
+  uint8_t* sQ = smem + 2 * TILE128;                 // 2 stages x 8 KB
+  uint8_t* sDO = smem + 2 * TILE128 + 2 * TILE64;   // 2 stages x 8 KB
+  uint8_t* sP = smem + 2 * TILE128 + 4 * TILE64;    // [128 keys x 64 q]
+  uint8_t* sDS = sP + TILE128;
+
+  __shared__ __align__(8) uint64_t kv_full, qd_full[2], qd_empty[2], st_full, st_free, pds_ready, pds_free, acc_full;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_word;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_k_tiles = (p.S + 127) / 128;
+  const int k_tile = int(blockIdx.x);   // early key tiles see the most queries and are scheduled first
+  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int k0 = k_tile * 128;
+  const int n_q64 = (p.S + 63) / 64;
+  const int first_q = p.causal ? k0 / 64 : 0;
+  const int n_iter = n_q64 - first_q;
+  (void)n_k_tiles;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&kv_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&qd_full[i], 1); mbar_init(&qd_empty[i], 1); }
+    mbar_init(&st_full, 1); mbar_init(&st_free, 4); mbar_init(&pds_ready, 4); mbar_init(&pds_free, 1); mbar_init(&acc_full, 1);
+    abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t t_st = tmem_slot, t_dp = tmem_slot + 64, t_dv = tmem_slot + 128, t_dk = tmem_slot + 192;
+  volatile int* abort_ptr = &abort_word;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&kv_full, 2 * TILE128);
+      tma_load_4d(sK, &tm_k, &kv_full, 0, k0, h, b);
+      tma_load_4d(sV, &tm_v, &kv_full, 0, k0, h, b);
+      for (int i = 0; i < n_iter; ++i) {
+        const int s = i & 1;
+        if (!mbar_wait(&qd_empty[s], ((i >> 1) & 1) ^ 1, abort_ptr)) break;
+        mbar_expect_tx(&qd_full[s], 2 * TILE64);
+        tma_load_4d(sQ + s * TILE64, &tm_q64, &qd_full[s], 0, (first_q + i) * 64, h, b);
+        tma_load_4d(sDO + s * TILE64, &tm_do64, &qd_full[s], 0, (first_q + i) * 64, h, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);   // [128 keys x 64 q], both K-major
+      const uint32_t idesc_acc = make_idesc_bf16(128, 64, false, true);   // B = [q rows x 64 d] read MN-major
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
+      bool ok = mbar_wait(&kv_full, 0, abort_ptr);
+      for (int i = 0; i < n_iter && ok; ++i) {
+        const int s = i & 1;
+        if (!mbar_wait(&qd_full[s], (i >> 1) & 1, abort_ptr)) break;
+        if (!mbar_wait(&st_free, (i & 1) ^ 1, abort_ptr)) break;
+        tc_fence_after_sync();
+        const uint32_t q_addr = smem_u32(sQ + s * TILE64), do_addr = smem_u32(sDO + s * TILE64);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(t_st, desc_kmajor(k_addr, kk), desc_kmajor(q_addr, kk), idesc_st, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(t_dp, desc_kmajor(v_addr, kk), desc_kmajor(do_addr, kk), idesc_st, kk != 0);
+        umma_commit(&st_full);
+        if (!mbar_wait(&pds_ready, i & 1, abort_ptr)) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ss(t_dv, desc_kmajor(p_addr, kk), desc_mnmajor(do_addr, kk), idesc_acc, (i | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ss(t_dk, desc_kmajor(ds_addr, kk), desc_mnmajor(q_addr, kk), idesc_acc, (i | kk) != 0);
+        umma_commit(&qd_empty[s]);
+        umma_commit(&pds_free);
+      }
+      umma_commit(&acc_full);
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;           // key row inside the tile
+    const int key = k0 + r;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const float scale_log2 = p.scale * LOG2E;
+    const Dropout drop = make_dropout(p.dropout_p, p.seed, uint32_t(bh), p.S);
+    const float* lse_bh = p.lse + (long long)bh * p.S;
+    const float* delta_bh = p.delta + (long long)bh * p.S;
+    bool ok = true;
+    for (int i = 0; i < n_iter; ++i) {
+      const int qbase = (first_q + i) * 64;
+      // lse / delta of the 64 queries of this tile live in registers, two per lane, and are
+      // broadcast with shuffles (no shared staging, so no CTA-level barrier inside the loop)
+      float lse_reg[2], delta_reg[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int qi = qbase + c * 32 + lane;
+        lse_reg[c] = qi < p.S ? lse_bh[qi] * LOG2E : 0.f;
+        delta_reg[c] = qi < p.S ? delta_bh[qi] : 0.f;
+      }
+      if (!mbar_wait(&st_full, i & 1, abort_ptr)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (!mbar_wait(&pds_free, (i & 1) ^ 1, abort_ptr)) { ok = false; break; }
+      const bool need_mask = (p.causal && qbase < k0 + 127) || (qbase + 64 > p.S) || (k0 + 128 > p.S);
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32(t_st + lane_base + c * 32, rs);
+        tmem_ld_32x32(t_dp + lane_base + c * 32, rd);
+        tmem_ld_wait();
+        float pv[32], ds[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int qi = qbase + c * 32 + j;
+          const float lse_q = __shfl_sync(0xffffffffu, lse_reg[c], j);
+          const float delta_q = __shfl_sync(0xffffffffu, delta_reg[c], j);
+          float e = ex2(__uint_as_float(rs[j]) * scale_log2 - lse_q);
+          if (need_mask && (qi >= p.S || key >= p.S || (p.causal && key > qi))) e = 0.f;
+          float dp = __uint_as_float(rd[j]);
+          float pd = e;
+          if (drop.thresh != 0u) {
+            const bool kept = drop.keep(uint32_t(qi), uint32_t(key));
+            pd = kept ? e * drop.inv_keep : 0.f;
+            dp = kept ? dp * drop.inv_keep : 0.f;
+          }
+          pv[j] = pd;
+          ds[j] = e * (dp - delta_q) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 a, d4;
+          a.x = pack2(pv[8 * g + 0], pv[8 * g + 1]); a.y = pack2(pv[8 * g + 2], pv[8 * g + 3]);
+          a.z = pack2(pv[8 * g + 4], pv[8 * g + 5]); a.w = pack2(pv[8 * g + 6], pv[8 * g + 7]);
+          d4.x = pack2(ds[8 * g + 0], ds[8 * g + 1]); d4.y = pack2(ds[8 * g + 2], ds[8 * g + 3]);
+          d4.z = pack2(ds[8 * g + 4], ds[8 * g + 5]); d4.w = pack2(ds[8 * g + 6], ds[8 * g + 7]);
+          st_swizzled(sP, r, c * 4 + g, a);
+          st_swizzled(sDS, r, c * 4 + g, d4);
+        }
+      }
+      epilogue_arrive(&st_free, lane);
+      fence_proxy_async_smem();
+      epilogue_arrive(&pds_ready, lane);
+    }
+    if (ok && mbar_wait(&acc_full, 0, abort_ptr)) {
+      tc_fence_after_sync();
+      float acc[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rr[32];
+        tmem_ld_32x32(t_dv + lane_base + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
+      }
+      if (key < p.S) store_row64(p.dv + (long long)b * p.dv_sb + (long long)h * p.dv_sh + (long long)key * p.dv_ss, acc, 1.f);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rr[32];
+        tmem_ld_32x32(t_dk + lane_base + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
+      }
+      if (key < p.S) store_row64(p.dk + (long long)b * p.dk_sb + (long long)h * p.dk_sh + (long long)key * p.dk_ss, acc, 1.f);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_word != 0) {
+    __nanosleep(50000);   // bounded grace period for bulk copies still in flight
+    if (p.status != nullptr) atomicMax(p.status, abort_word);
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_slot, 256);
+}
+
+// =====================================================================================================
+// backward, sweep 2: dQ.  CTA = 128 queries; streams 64-key tiles.
+// =====================================================================================================
+constexpr int BWD_Q_SMEM = 2 * TILE128 /*Q,dO*/ + 4 * TILE64 /*K,V x 2 stages*/ + TILE128 /*dS*/ + 1024;
+
+__global__ void __launch_bounds__(THREADS, 2)
+flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k64,
+                    const __grid_constant__ CUtensorMap tm_v64, const __grid_constant__ CUtensorMap tm_do, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = smem + TILE128;
+  uint8_t* sK = smem + 2 * TILE128;
+  uint8_t* sV = smem + 2 * TILE128 + 2 * TILE64;
+  uint8_t* sDS = smem + 2 * TILE128 + 4 * TILE64;    // [128 q x 64 keys]
+
+  __shared__ __align__(8) uint64_t qd_full, kv_full[2], kv_empty[2], st_full, st_free, ds_ready, ds_free, acc_full;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_word;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_q_tiles = (p.S + 127) / 128;
+  const int q_tile = n_q_tiles - 1 - int(blockIdx.x);
+  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int q0 = q_tile * 128;
+  const int n_k64 = (p.S + 63) / 64;
+  const int n_iter = p.causal ? min(n_k64, (q0 + 127) / 64 + 1) : n_k64;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&qd_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    mbar_init(&st_full, 1); mbar_init(&st_free, 4); mbar_init(&ds_ready, 4); mbar_init(&ds_free, 1); mbar_init(&acc_full, 1);
+    abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) { tmem_alloc(&tmem_slot, 256); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t t_s = tmem_slot, t_dp = tmem_slot + 64, t_dq = tmem_slot + 128;
+  volatile int* abort_ptr = &abort_word;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&qd_full, 2 * TILE128);
+      tma_load_4d(sQ, &tm_q, &qd_full, 0, q0, h, b);
+      tma_load_4d(sDO, &tm_do, &qd_full, 0, q0, h, b);
+      for (int i = 0; i < n_iter; ++i) {
+        const int s = i & 1;
+        if (!mbar_wait(&kv_empty[s], ((i >> 1) & 1) ^ 1, abort_ptr)) break;
+        mbar_expect_tx(&kv_full[s], 2 * TILE64);
+        tma_load_4d(sK + s * TILE64, &tm_k64, &kv_full[s], 0, i * 64, h, b);
+        tma_load_4d(sV + s * TILE64, &tm_v64, &kv_full[s], 0, i * 64, h, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
+      const uint32_t idesc_dq = make_idesc_bf16(128, 64, false, true);
+      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO), ds_addr = smem_u32(sDS);
+      bool ok = mbar_wait(&qd_full, 0, abort_ptr);
+      for (int i = 0; i < n_iter && ok; ++i) {
+        const int s = i & 1;
+        if (!mbar_wait(&kv_full[s], (i >> 1) & 1, abort_ptr)) break;
+        if (!mbar_wait(&st_free, (i & 1) ^ 1, abort_ptr)) break;
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(sK + s * TILE64), v_addr = smem_u32(sV + s * TILE64);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(t_s, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_s, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(t_dp, desc_kmajor(do_addr, kk), desc_kmajor(v_addr, kk), idesc_s, kk != 0);
+        umma_commit(&st_full);
+        if (!mbar_wait(&ds_ready, i & 1, abort_ptr)) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ss(t_dq, desc_kmajor(ds_addr, kk), desc_mnmajor(k_addr, kk), idesc_dq, (i | kk) != 0);
+        umma_commit(&kv_empty[s]);
+        umma_commit(&ds_free);
+      }
+      umma_commit(&acc_full);
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int q_row = q0 + r;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const float scale_log2 = p.scale * LOG2E;
+    const Dropout drop = make_dropout(p.dropout_p, p.seed, uint32_t(bh), p.S);
+    const float lse2 = q_row < p.S ? p.lse[(long long)bh * p.S + q_row] * LOG2E : 0.f;
+    const float delta = q_row < p.S ? p.delta[(long long)bh * p.S + q_row] : 0.f;
+    bool ok = true;
+    for (int i = 0; i < n_iter; ++i) {
+      const int kbase = i * 64;
+      if (!mbar_wait(&st_full, i & 1, abort_ptr)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (!mbar_wait(&ds_free, (i & 1) ^ 1, abort_ptr)) { ok = false; break; }
+      const bool need_mask = (p.causal && kbase + 63 > q0) || (kbase + 64 > p.S) || (q0 + 128 > p.S);
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32(t_s + lane_base + c * 32, rs);
+        tmem_ld_32x32(t_dp + lane_base + c * 32, rd);
+        tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int kidx = kbase + c * 32 + j;
+          float e = ex2(__uint_as_float(rs[j]) * scale_log2 - lse2);
+          if (need_mask && (kidx >= p.S || q_row >= p.S || (p.causal && kidx > q_row))) e = 0.f;
+          ds[j] = e;   // probability; turned into dS below once the keep bits are known
+        }
+        if (drop.thresh != 0u) {
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            const uint32_t bits = drop.word(uint32_t(q_row), uint32_t(kbase + c * 32 + 4 * w) >> 2);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const bool kept = ((bits >> (8 * t)) & 0xFFu) >= drop.thresh;
+              const float dp = kept ? __uint_as_float(rd[4 * w + t]) * drop.inv_keep : 0.f;
+              ds[4 * w + t] = ds[4 * w + t] * (dp - delta) * p.scale;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ds[j] = ds[j] * (__uint_as_float(rd[j]) - delta) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 d4;
+          d4.x = pack2(ds[8 * g + 0], ds[8 * g + 1]); d4.y = pack2(ds[8 * g + 2], ds[8 * g + 3]);
+          d4.z = pack2(ds[8 * g + 4], ds[8 * g + 5]); d4.w = pack2(ds[8 * g + 6], ds[8 * g + 7]);
+          st_swizzled(sDS, r, c * 4 + g, d4);
+        }
+      }
+      epilogue_arrive(&st_free, lane);
+      fence_proxy_async_smem();
+      epilogue_arrive(&ds_ready, lane);
+    }
+    if (ok && mbar_wait(&acc_full, 0, abort_ptr)) {
+      tc_fence_after_sync();
+      float acc[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rr[32];
+        tmem_ld_32x32(t_dq + lane_base + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
+      }
+      if (q_row < p.S) store_row64(p.dq + (long long)b * p.dq_sb + (long long)h * p.dq_sh + (long long)q_row * p.dq_ss, acc, 1.f);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_word != 0) {
+    __nanosleep(50000);   // bounded grace period for bulk copies still in flight
+    if (p.status != nullptr) atomicMax(p.status, abort_word);
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_slot, 256);
+}
+
+// ---- delta = rowsum(dO * O): 8 threads per row ----
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long o_sb, long long o_sh, long long o_ss,
+                  const __nv_bfloat16* __restrict__ d_o, long long d_sb, long long d_sh, long long d_ss,
+                  float* __restrict__ delta, int B, int H, int S) {
+  const long long rows = (long long)B * H * S;
+  const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+  const int part = threadIdx.x & 7;
+  float acc = 0.f;
+  if (row < rows) {
+    const int s = int(row % S);
+    const int h = int((row / S) % H);
+    const int b = int(row / ((long long)S * H));
+    const uint4 a = *reinterpret_cast<const uint4*>(o + b * o_sb + h * o_sh + s * o_ss + part * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(d_o + b * d_sb + h * d_sh + s * d_ss + part * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&aw[i]);
+      const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&gw[i]);
+      acc += __low2float(x) * __low2float(y) + __high2float(x) * __high2float(y);
+    }
+  }
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (row < rows && part == 0) delta[row] = acc;
+}
+
+__global__ void dropout_mask_kernel(unsigned char* __restrict__ keep, int BH, int S, float p, unsigned long long seed) {
+  const long long total = (long long)BH * S * S;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int k = int(i % S);
+    const int q = int((i / S) % S);
+    const int bh = int(i / ((long long)S * S));
+    const Dropout d = make_dropout(p, seed, uint32_t(bh), S);
+    keep[i] = d.thresh == 0u || d.keep(uint32_t(q), uint32_t(k)) ? 1 : 0;
+  }
+}
+
+// ---- host ----
+PFN_cuTensorMapEncodeTiled_v12000 attn_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  });
+  return fn;
+}
+
+bool encode_bhsd(CUtensorMap* map, const StridedBHSD& t, int B, int H, int S, int box_rows) {
+  auto fn = attn_encode_fn();
+  if (fn == nullptr) { g_attn_last_error = "cuTensorMapEncodeTiled entry point not found"; return false; }
+  if ((reinterpret_cast<uintptr_t>(t.ptr) & 15) != 0 || t.sb % 8 != 0 || t.sh % 8 != 0 || t.ss % 8 != 0) {
+    g_attn_last_error = "attention operand is not 16-byte aligned in every row";
+    return false;
+  }
+  const cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(S), cuuint64_t(H), cuuint64_t(B)};
+  const cuuint64_t strides[3] = {cuuint64_t(t.ss) * 2, cuuint64_t(t.sh) * 2, cuuint64_t(t.sb) * 2};
+  const cuuint32_t box[4] = {cuuint32_t(D), cuuint32_t(box_rows), 1u, 1u};
+  const cuuint32_t elem[4] = {1u, 1u, 1u, 1u};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.ptr, dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    static char msg[200];
+    snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled (4-D) error %d: B=%d H=%d S=%d strides=(%lld,%lld,%lld) box_rows=%d",
+             int(r), B, H, S, t.sb, t.sh, t.ss, box_rows);
+    g_attn_last_error = msg;
+    return false;
+  }
+  return true;
+}
+
+Params make_params(const AttentionArgs& a) {
+  Params p{};
+  p.o = static_cast<__nv_bfloat16*>(a.o.ptr); p.o_sb = a.o.sb; p.o_sh = a.o.sh; p.o_ss = a.o.ss;
+  p.dq = static_cast<__nv_bfloat16*>(a.dq.ptr); p.dq_sb = a.dq.sb; p.dq_sh = a.dq.sh; p.dq_ss = a.dq.ss;
+  p.dk = static_cast<__nv_bfloat16*>(a.dk.ptr); p.dk_sb = a.dk.sb; p.dk_sh = a.dk.sh; p.dk_ss = a.dk.ss;
+  p.dv = static_cast<__nv_bfloat16*>(a.dv.ptr); p.dv_sb = a.dv.sb; p.dv_sh = a.dv.sh; p.dv_ss = a.dv.ss;
+  p.lse = a.lse; p.delta = a.delta;
+  p.B = a.B; p.H = a.H; p.S = a.S; p.causal = a.causal;
+  p.scale = a.scale; p.dropout_p = a.dropout_p; p.seed = a.seed; p.status = a.status;
+  return p;
+}
+
+template <typename K>
+cudaError_t set_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+}  // namespace
+
+cudaError_t launch_flash_fwd(const AttentionArgs& a) {
+  g_attn_last_error = "";
+  if (a.B <= 0 || a.H <= 0 || a.S <= 0 || (long long)a.B * a.H > 65535) { g_attn_last_error = "bad attention extents"; return cudaErrorInvalidValue; }
+  CUtensorMap tq, tk, tv;
+  if (!encode_bhsd(&tq, a.q, a.B, a.H, a.S, 128) || !encode_bhsd(&tk, a.k, a.B, a.H, a.S, 128) ||
+      !encode_bhsd(&tv, a.v, a.B, a.H, a.S, 128))
+    return cudaErrorInvalidValue;
+  static bool once = false;
+  if (!once) {
+    cudaError_t e = set_smem(flash_fwd_kernel, FWD_SMEM);
+    if (e != cudaSuccess) return e;
+    once = true;
+  }
+  const dim3 grid((a.S + 127) / 128, a.B * a.H);
+  (void)cudaGetLastError();
+  flash_fwd_kernel<<<grid, THREADS, FWD_SMEM, a.stream>>>(tq, tk, tv, make_params(a));
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_flash_bwd(const AttentionArgs& a) {
+  g_attn_last_error = "";
+  if (a.B <= 0 || a.H <= 0 || a.S <= 0 || (long long)a.B * a.H > 65535) { g_attn_last_error = "bad attention extents"; return cudaErrorInvalidValue; }
+  CUtensorMap tq128, tq64, tk128, tk64, tv128, tv64, tdo128, tdo64;
+  if (!encode_bhsd(&tq128, a.q, a.B, a.H, a.S, 128) || !encode_bhsd(&tq64, a.q, a.B, a.H, a.S, 64) ||
+      !encode_bhsd(&tk128, a.k, a.B, a.H, a.S, 128) || !encode_bhsd(&tk64, a.k, a.B, a.H, a.S, 64) ||
+      !encode_bhsd(&tv128, a.v, a.B, a.H, a.S, 128) || !encode_bhsd(&tv64, a.v, a.B, a.H, a.S, 64) ||
+      !encode_bhsd(&tdo128, a.d_o, a.B, a.H, a.S, 128) || !encode_bhsd(&tdo64, a.d_o, a.B, a.H, a.S, 64))
+    return cudaErrorInvalidValue;
+  static bool once = false;
+  if (!once) {
+    cudaError_t e = set_smem(flash_bwd_dkdv_kernel, BWD_KV_SMEM);
+    if (e == cudaSuccess) e = set_smem(flash_bwd_dq_kernel, BWD_Q_SMEM);
+    if (e != cudaSuccess) return e;
+    once = true;
+  }
+  (void)cudaGetLastError();
+  const long long rows = (long long)a.B * a.H * a.S;
+  attn_delta_kernel<<<unsigned((rows * 8 + 255) / 256), 256, 0, a.stream>>>(
+      static_cast<const __nv_bfloat16*>(a.o.ptr), a.o.sb, a.o.sh, a.o.ss, static_cast<const __nv_bfloat16*>(a.d_o.ptr),
+      a.d_o.sb, a.d_o.sh, a.d_o.ss, a.delta, a.B, a.H, a.S);
+  const Params p = make_params(a);
+  const dim3 grid((a.S + 127) / 128, a.B * a.H);
+  flash_bwd_dkdv_kernel<<<grid, THREADS, BWD_KV_SMEM, a.stream>>>(tq64, tk128, tv128, tdo64, p);
+  flash_bwd_dq_kernel<<<grid, THREADS, BWD_Q_SMEM, a.stream>>>(tq128, tk64, tv64, tdo128, p);
+  g_launch_count += 3;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dropout_keep_mask(unsigned char* keep, int BH, int S, float dropout_p, unsigned long long seed,
+                                     cudaStream_t stream) {
+  dropout_mask_kernel<<<device_sm_count() * 8, 256, 0, stream>>>(keep, BH, S, dropout_p, seed);
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+}  // namespace mts

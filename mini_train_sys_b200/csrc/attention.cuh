@@ -1,4 +1,11 @@
-// FlashAttention kernels for sm_100a (implemented in attention.cu).
+// FlashAttention for sm_100a, head_dim 64, bf16, self-attention (Sq == Sk), optional causal mask and
+// dropout.  Implemented in attention.cu with tcgen05 MMAs (accumulators in tensor memory) and TMA
+// loads through 4-D tensor maps, so q/k/v may be arbitrary [B, H, S, D] views with unit inner stride.
+//
+// Saved for backward: O and the natural-log row log-sum-exp `lse[B, H, S]` (no probabilities).
+// Dropout is a stateless function of (seed, batch*head, query, key); `dropout_keep_mask` materialises
+// the same pattern for tests.  The drop probability is quantised to p_eff = round(p * 256) / 256 and
+// kept values are scaled by 1 / (1 - p_eff).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -6,18 +13,32 @@
 
 namespace mts {
 
+struct StridedBHSD {
+  void* ptr;
+  long long sb, sh, ss;   // element strides of batch, head, sequence (inner stride is 1)
+};
+
 struct AttentionArgs {
-  // q, k, v, o: bf16 [B, H, S, D] addressed through element strides (innermost stride 1)
-  const void* q; const void* k; const void* v; void* o;
-  long long q_sb, q_sh, q_ss, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss, o_sb, o_sh, o_ss;
-  float* lse;            // [B, H, S] natural-log sum-exp of the scaled scores
-  int B, H, S, D;
+  StridedBHSD q, k, v, o;      // bf16
+  StridedBHSD d_o, dq, dk, dv; // bf16 (backward only)
+  float* lse;                  // [B, H, S]
+  float* delta;                // [B, H, S] rowsum(dO * O) (backward scratch)
+  int B, H, S;
   int causal;
-  float scale;
+  float scale;                 // 1 / sqrt(D)
   float dropout_p;
   unsigned long long seed;
   int* status;
   cudaStream_t stream;
 };
+
+constexpr int kAttnHeadDim = 64;
+
+cudaError_t launch_flash_fwd(const AttentionArgs& a);
+cudaError_t launch_flash_bwd(const AttentionArgs& a);
+// keep[b*h, q, k] as uint8 (1 = kept)
+cudaError_t launch_dropout_keep_mask(unsigned char* keep, int BH, int S, float dropout_p, unsigned long long seed,
+                                     cudaStream_t stream);
+extern const char* g_attn_last_error;
 
 }  // namespace mts

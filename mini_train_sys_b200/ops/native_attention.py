@@ -1,15 +1,79 @@
-"""Autograd bridge for the tcgen05 FlashAttention kernels (``csrc/attention.cu``)."""
+"""Autograd bridge for the tcgen05 FlashAttention kernels (``csrc/attention.cu``).
+
+Contract kept from the reference's CUDA attention bridge (minitrain/kernels/cuda_ext/flash_attention.py:110-300):
+a no-load capability predicate that rejects unsupported inputs before any kernel runs (the same checks are
+repeated at the C++ boundary), ``(B, H, S, D)`` inputs that only need a unit inner stride (so views of a fused
+QKV projection are consumed without copies), a stride-0 ``dout`` is materialised, and only ``O`` plus the fp32
+log-sum-exp are saved for backward.  The dropout pattern is a stateless function of (seed, head, query, key);
+``keep_mask`` reproduces it for tests.
+"""
 
 from __future__ import annotations
 
 import torch
 
+HEAD_DIM = 64
+
+
+def _rows_aligned(t: torch.Tensor) -> bool:
+    return (t.stride(3) == 1 and t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3]))
+
 
 def supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool, dropout_p: float) -> bool:
-    """No-load capability predicate, mirrored by the checks at the C++ boundary."""
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        return False
+    if not (q.dtype == k.dtype == v.dtype == torch.bfloat16):
+        return False
+    if q.dim() != 4 or q.shape != k.shape or q.shape != v.shape or q.shape[-1] != HEAD_DIM:
+        return False
+    b, h, s, _ = q.shape
+    if b * h == 0 or s == 0 or b * h > 65535 or s > 65535:
+        return False
+    if not 0.0 <= float(dropout_p) < 1.0:
+        return False
+    return all(_rows_aligned(t) for t in (q, k, v))
 
-    return False
+
+def effective_dropout(p: float) -> float:
+    """Drop probability actually applied: ``p`` quantised to 1/256."""
+
+    return round(p * 256.0) / 256.0 if p > 0 else 0.0
 
 
-def flash_attention(q, k, v, *, is_causal: bool, dropout_p: float) -> torch.Tensor:
-    raise NotImplementedError
+def keep_mask(batch_heads: int, seq: int, dropout_p: float, seed: int, device) -> torch.Tensor:
+    from mini_train_sys_b200.ops.native_backend import ext
+
+    like = torch.empty(0, device=device)
+    return ext().dropout_keep_mask(batch_heads, seq, dropout_p, seed, like).bool()
+
+
+class _FlashAttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, is_causal, dropout_p, seed):
+        from mini_train_sys_b200.ops.native_backend import ext
+
+        status = ext().status_tensor(q.device.index or 0)
+        o, lse = ext().flash_fwd(q, k, v, is_causal, dropout_p, seed, status)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.meta = (is_causal, dropout_p, seed)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        from mini_train_sys_b200.ops.native_backend import ext
+
+        q, k, v, o, lse = ctx.saved_tensors
+        is_causal, dropout_p, seed = ctx.meta
+        if not _rows_aligned(d_o) or 0 in d_o.stride()[:3]:
+            d_o = d_o.contiguous()   # expanded (stride-0) or misaligned upstream gradients
+        status = ext().status_tensor(q.device.index or 0)
+        dq, dk, dv = ext().flash_bwd(d_o, q, k, v, o, lse, is_causal, dropout_p, seed, status)
+        return dq, dk, dv, None, None, None
+
+
+def flash_attention(q, k, v, *, is_causal: bool, dropout_p: float, seed: int | None = None) -> torch.Tensor:
+    """Returns ``[B, H, S, D]`` whose storage is ``[B, S, H, D]``-contiguous (a free transpose for the caller)."""
+
+    if seed is None:
+        seed = int(torch.randint(0, 2**62, (1,)).item()) if dropout_p > 0 else 0
+    return _FlashAttentionFn.apply(q, k, v, bool(is_causal), float(dropout_p), int(seed))

@@ -58,16 +58,17 @@ _rows_cache: dict[tuple, torch.Tensor] = {}
 def bf16_weight(weight: torch.Tensor) -> torch.Tensor:
     """bf16 copy of a (usually fp32) parameter, refreshed only when the parameter changes.
 
-    Entries are keyed by object identity and validated with a weak reference plus the tensor's
-    version counter and storage address, so a recycled address can never return a stale copy.
+    Entries are keyed by storage address and validated with the version counter, the shape and a
+    weak reference to the tensor object that created the entry: once that object is gone the
+    address may have been recycled, so the entry is dropped instead of trusted.
     """
 
     if weight.dtype == torch.bfloat16:
         return weight if weight.is_contiguous() else weight.contiguous()
-    key = id(weight)
+    key = weight.data_ptr()
     hit = _weight_cache.get(key)
-    version, ptr = weight._version, weight.data_ptr()
-    if hit is not None and hit[0]() is weight and hit[1] == version and hit[2] == ptr:
+    version = weight._version
+    if hit is not None and hit[0]() is not None and hit[1] == version and hit[2] == weight.shape:
         return hit[3]
     src = weight.detach()
     if not src.is_contiguous():
@@ -76,7 +77,7 @@ def bf16_weight(weight: torch.Tensor) -> torch.Tensor:
     if len(_weight_cache) > 4096:
         for k in [k for k, v in _weight_cache.items() if v[0]() is None]:
             del _weight_cache[k]
-    _weight_cache[key] = (weakref.ref(weight), version, ptr, out)
+    _weight_cache[key] = (weakref.ref(weight), version, weight.shape, out)
     return out
 
 
