@@ -718,7 +718,17 @@ PFN_cuTensorMapEncodeTiled_v12000 attn_encode_fn() {
   return fn;
 }
 
+// Driver entry points need a current context; see the note in gemm_sm100.cu.
+void attn_ensure_context_current() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 bool encode_bhsd(CUtensorMap* map, const StridedBHSD& t, int B, int H, int S, int box_rows) {
+  attn_ensure_context_current();
   auto fn = attn_encode_fn();
   if (fn == nullptr) { g_attn_last_error = "cuTensorMapEncodeTiled entry point not found"; return false; }
   if ((reinterpret_cast<uintptr_t>(t.ptr) & 15) != 0 || t.sb % 8 != 0 || t.sh % 8 != 0 || t.ss % 8 != 0) {

@@ -462,7 +462,19 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }
 
 // 2-D bf16 tensor [rows, cols] (cols contiguous), box = [box_rows, 64 cols], 128-byte swizzle.
+// The tensor-map encoder is a driver entry point and needs a current context.  Worker threads (the
+// autograd engine's, for one) may reach this code before any runtime call has bound the primary
+// context to them, so bind it once per thread.
+void ensure_context_current() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 bool encode_bf16_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  ensure_context_current();
   auto fn = encode_fn();
   if (fn == nullptr) { g_last_error = "cuTensorMapEncodeTiled entry point not found"; return false; }
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0 || rows <= 0 || cols <= 0) {
