@@ -388,3 +388,71 @@ cudaError_t launch_moe_combine_bwd(const void* dout, const void* y, const int* r
 }
 
 }  // namespace mts
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of the routing plan (declaration and contract: noalloc.h).
+// Same kernels as launch_moe_plan; the only difference is where the histogram scratch lives.
+// ---------------------------------------------------------------------------------------------------
+#include "noalloc.h"
+
+#include <cstdio>
+#include <mutex>
+
+namespace {
+
+constexpr int kNoAllocMaxRoutes = 1 << 20;
+constexpr int kNoAllocScratchInts = (kNoAllocMaxRoutes / mts::kPlanBlock) * mts::kMaxExperts;   // 65,536 ints = 256 KiB
+
+// Lives in the library's device image.  In host code this name is only a handle for
+// cudaGetSymbolAddress; it is never passed to a kernel directly.
+static __device__ __align__(256) int g_plan_scratch[kNoAllocScratchInts];
+
+constexpr int kMaxDevices = 64;
+int* g_plan_scratch_addr[kMaxDevices] = {};
+std::mutex g_plan_scratch_mutex;
+
+// Device address of the scratch array on the current device (looked up once per device).
+cudaError_t plan_scratch_for_current_device(int** out) {
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return err;
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_plan_scratch_mutex);
+  if (g_plan_scratch_addr[device] == nullptr) {
+    void* addr = nullptr;
+    err = cudaGetSymbolAddress(&addr, g_plan_scratch);
+    if (err != cudaSuccess) return err;
+    g_plan_scratch_addr[device] = static_cast<int*>(addr);
+  }
+  *out = g_plan_scratch_addr[device];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int mts_moe_plan_noalloc(const int* indices, int tokens, int top_k, int experts, int capacity_rows,
+                                    int* row_token, int* token_rows, int* tile_group, int* group_rows, int* meta,
+                                    void* cuda_stream) {
+  if (indices == nullptr || row_token == nullptr || token_rows == nullptr || tile_group == nullptr ||
+      group_rows == nullptr || meta == nullptr || tokens <= 0 || top_k <= 0 || experts <= 0 || capacity_rows <= 0 ||
+      capacity_rows % 128 != 0) {
+    std::fprintf(stderr, "mts_moe_plan_noalloc: invalid argument (null pointer, non-positive size, or capacity_rows "
+                         "not a multiple of 128)\n");
+    return -2;
+  }
+  const long long routes = static_cast<long long>(tokens) * top_k;
+  if (routes > kNoAllocMaxRoutes || experts > mts::kMaxExperts) {
+    std::fprintf(stderr, "mts_moe_plan_noalloc: %lld routes / %d experts exceed the built-in scratch "
+                         "(limit: %d routes, %d experts)\n", routes, experts, kNoAllocMaxRoutes, mts::kMaxExperts);
+    return -1;
+  }
+  int* scratch = nullptr;
+  const cudaError_t lookup = plan_scratch_for_current_device(&scratch);
+  if (lookup != cudaSuccess) {
+    std::fprintf(stderr, "mts_moe_plan_noalloc: scratch lookup failed: %s\n", cudaGetErrorString(lookup));
+    return static_cast<int>(lookup);
+  }
+  const cudaError_t err = mts::launch_moe_plan(indices, tokens, top_k, experts, capacity_rows, row_token, token_rows,
+                                               tile_group, group_rows, meta, scratch, static_cast<cudaStream_t>(cuda_stream));
+  return static_cast<int>(err);
+}
