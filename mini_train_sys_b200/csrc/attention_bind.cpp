@@ -59,14 +59,23 @@ std::vector<Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v,
 }
 
 std::vector<Tensor> flash_bwd(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
-                              const Tensor& lse, bool causal, double dropout_p, int64_t seed, const Tensor& status) {
+                              const Tensor& lse, bool causal, double dropout_p, int64_t seed, const Tensor& status,
+                              const c10::optional<Tensor>& dq_out, const c10::optional<Tensor>& dk_out,
+                              const c10::optional<Tensor>& dv_out) {
   c10::cuda::CUDAGuard guard(q.device());
   mts::AttentionArgs a = base_args(q, k, v, causal, dropout_p, seed);
   check_qkv(o, "o", q.size(0), q.size(1), q.size(2));
   check_qkv(d_o, "d_o", q.size(0), q.size(1), q.size(2));
   TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == q.size(0) * q.size(1) * q.size(2),
               "lse must be contiguous fp32 [B, H, S]");
-  Tensor dq = alloc_bhsd(q), dk = alloc_bhsd(q), dv = alloc_bhsd(q);
+  auto pick = [&](const c10::optional<Tensor>& given, const char* name) {
+    if (given.has_value() && given->defined()) {
+      check_qkv(*given, name, q.size(0), q.size(1), q.size(2));
+      return *given;
+    }
+    return alloc_bhsd(q);
+  };
+  Tensor dq = pick(dq_out, "dq"), dk = pick(dk_out, "dk"), dv = pick(dv_out, "dv");
   Tensor delta = torch::empty_like(lse);
   a.o = view_of(o); a.d_o = view_of(d_o); a.dq = view_of(dq); a.dk = view_of(dk); a.dv = view_of(dv);
   a.lse = lse.data_ptr<float>();

@@ -72,8 +72,9 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
   return {dx, dw};
 }
 
-// x: [B, Hh, S, D] view (any strides, unit inner stride) -> contiguous [B, Hh, S, D]
-Tensor rope(const Tensor& x, const Tensor& cosv, const Tensor& sinv, bool backward) {
+// x: [B, Hh, S, D] view (any strides, unit inner stride) -> contiguous [B, Hh, S, D], or into `out`
+// (same shape, any 16-byte aligned strides) when one is given.
+Tensor rope(const Tensor& x, const Tensor& cosv, const Tensor& sinv, bool backward, const c10::optional<Tensor>& out_opt) {
   check_act(x, "x");
   TORCH_CHECK(x.dim() == 4 && x.stride(3) == 1, "rope expects [B, H, S, D] with a contiguous last dimension");
   const int64_t B = x.size(0), Hh = x.size(1), S = x.size(2), D = x.size(3);
@@ -81,11 +82,20 @@ Tensor rope(const Tensor& x, const Tensor& cosv, const Tensor& sinv, bool backwa
   TORCH_CHECK(cosv.scalar_type() == x.scalar_type() && sinv.scalar_type() == x.scalar_type(), "cos/sin dtype mismatch");
   TORCH_CHECK(cosv.is_contiguous() && sinv.is_contiguous() && cosv.size(0) >= S && cosv.size(1) == D, "bad cos/sin tables");
   const int64_t vec = is_bf16(x) ? 8 : 4;
-  TORCH_CHECK(x.stride(0) % vec == 0 && x.stride(1) % vec == 0 && x.stride(2) % vec == 0 &&
-                  (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0,
-              "rope input must be 16-byte aligned in every row");
+  auto aligned = [vec](const Tensor& t) {
+    return t.stride(0) % vec == 0 && t.stride(1) % vec == 0 && t.stride(2) % vec == 0 && t.stride(3) == 1 &&
+           (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0;
+  };
+  TORCH_CHECK(aligned(x), "rope input must be 16-byte aligned in every row");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor out = torch::empty({B, Hh, S, D}, x.options());
+  Tensor out;
+  if (out_opt.has_value() && out_opt->defined()) {
+    out = *out_opt;
+    TORCH_CHECK(out.sizes() == x.sizes() && out.scalar_type() == x.scalar_type() && out.is_cuda() && aligned(out),
+                "rope output must match the input shape/dtype and be 16-byte aligned in every row");
+  } else {
+    out = torch::empty({B, Hh, S, D}, x.options());
+  }
   check_launch(mts::launch_rope(x.data_ptr(), out.data_ptr(), cosv.data_ptr(), sinv.data_ptr(), int(B), int(Hh), int(S), int(D),
                                 x.stride(0), x.stride(1), x.stride(2), out.stride(0), out.stride(1), out.stride(2), backward,
                                 is_bf16(x), cur_stream()), "rope");

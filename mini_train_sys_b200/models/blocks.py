@@ -66,10 +66,15 @@ class CausalSelfAttention(nn.Module):
         nh, hd = self.cfg.n_heads, self.cfg.head_dim
         # [B, S, 3, heads, D] -> three strided [B, heads, S, D] views of the fused projection
         fused = project(ops, self.qkv, x).view(b, s, 3, nh, hd)
-        q, k, v = (fused[:, :, j].transpose(1, 2) for j in range(3))
-        q, k = ops.rope(q, k, rope_cos, rope_sin)
         p = self.cfg.dropout if self.training else 0.0
-        ctx = ops.attention(q, k, v, is_causal=True, dropout_p=p)
+        ctx = None
+        fused_path = getattr(ops, "attention_qkv", None)   # optional backend hook: RoPE + attention in one node
+        if fused_path is not None:
+            ctx = fused_path(fused, rope_cos, rope_sin, is_causal=True, dropout_p=p)
+        if ctx is None:
+            q, k, v = (fused[:, :, j].transpose(1, 2) for j in range(3))
+            q, k = ops.rope(q, k, rope_cos, rope_sin)
+            ctx = ops.attention(q, k, v, is_causal=True, dropout_p=p)
         ctx = ctx.transpose(1, 2).contiguous().view(b, s, h)
         return self.resid_dropout(project(ops, self.out, ctx))
 

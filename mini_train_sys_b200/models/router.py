@@ -76,13 +76,18 @@ class TopKRouter(nn.Module):
     def forward(self, hidden_states: torch.Tensor, ops: OpsBackend) -> RouterOutput:
         cfg = self.cfg
         n_exp = cfg.num_experts
-        x32 = hidden_states.float()
-        if self.training and cfg.router_jitter_noise:
-            span = cfg.router_jitter_noise
-            x32 = x32 * torch.empty_like(x32).uniform_(1.0 - span, 1.0 + span)
+        jitter = self.training and cfg.router_jitter_noise
+        fused_logits = None if jitter else getattr(ops, "router_logits", None)   # optional backend hook
 
         with torch.autocast(device_type=hidden_states.device.type, enabled=False):
-            logits = F.linear(x32, self.weight.float())
+            if fused_logits is not None:
+                logits = fused_logits(hidden_states, self.weight)
+            else:
+                x32 = hidden_states.float()
+                if jitter:
+                    span = cfg.router_jitter_noise
+                    x32 = x32 * torch.empty_like(x32).uniform_(1.0 - span, 1.0 + span)
+                logits = F.linear(x32, self.weight.float())
             post = ops.router_postprocess(logits, cfg.experts_per_token, normalize=cfg.router_normalize_topk)
             weights, indices = post.expert_weights, post.expert_indices
             n_routes = indices.numel()

@@ -214,13 +214,13 @@ class _RopeFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, cos, sin):
         ctx.save_for_backward(cos, sin)
-        return ext().rope(q, cos, sin, False), ext().rope(k, cos, sin, False)
+        return ext().rope(q, cos, sin, False, None), ext().rope(k, cos, sin, False, None)
 
     @staticmethod
     def backward(ctx, dq, dk):
         cos, sin = ctx.saved_tensors
         fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()  # noqa: E731
-        return ext().rope(fix(dq), cos, sin, True), ext().rope(fix(dk), cos, sin, True), None, None
+        return ext().rope(fix(dq), cos, sin, True, None), ext().rope(fix(dk), cos, sin, True, None), None, None
 
 
 class _SwigluFn(torch.autograd.Function):
@@ -316,6 +316,58 @@ class _FusedLinearCEFn(torch.autograd.Function):
         gx = dx * g.to(dx.dtype) if dx is not None else None
         gw = (dw * g).to(ctx.w_dtype) if dw is not None else None
         return gx, gw, None
+
+
+def _split_bf16(t32: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    hi = t32.to(torch.bfloat16)
+    lo = (t32 - hi.float()).to(torch.bfloat16)
+    return hi, lo
+
+
+class _RouterLogitsFn(torch.autograd.Function):
+    """fp32 router logits ``x @ W^T`` on the tensor cores with fp32-grade accuracy.
+
+    ``x`` is bf16 (exact); the fp32 weight is split into a bf16 high and low part stacked along the
+    output dimension, so one GEMM with fp32 accumulation yields ``x W_hi^T`` and ``x W_lo^T`` whose sum
+    matches the fp32 product to about 2^-17.  The weight gradient uses the same split on the incoming
+    fp32 gradient.  (The reference runs this GEMM in fp32 through cuBLAS: minitrain/model/moe_router.py:64-73.)
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        n_exp, hidden = weight.shape
+        w_hi, w_lo = _split_bf16(weight.detach().float())
+        stacked = torch.zeros(2 * n_exp, hidden, dtype=torch.bfloat16, device=x.device)
+        stacked[:n_exp], stacked[n_exp:] = w_hi, w_lo
+        width = -(-2 * n_exp // 4) * 4
+        out = torch.empty(x.shape[0], width, dtype=torch.float32, device=x.device)
+        _gemm(x, stacked, out, x.shape[0], 2 * n_exp, hidden, ldo=width)
+        ctx.save_for_backward(x, weight, w_hi)
+        return out[:, :n_exp] + out[:, n_exp:2 * n_exp]
+
+    @staticmethod
+    def backward(ctx, g):
+        x, weight, w_hi = ctx.saved_tensors
+        n_exp, hidden = weight.shape
+        g32 = g.float()
+        g_hi, g_lo = _split_bf16(g32)
+        pad = -(-2 * n_exp // 8) * 8
+        g2 = torch.zeros(x.shape[0], pad, dtype=torch.bfloat16, device=x.device)
+        g2[:, :n_exp], g2[:, n_exp:2 * n_exp] = g_hi, g_lo
+        dx = dw = None
+        if ctx.needs_input_grad[0]:   # result is rounded to bf16 anyway: the high parts suffice
+            if n_exp % 8 == 0:
+                ga, wk = g2[:, :n_exp], w_hi
+            else:
+                kpad = -(-n_exp // 8) * 8
+                ga = torch.zeros(x.shape[0], kpad, dtype=torch.bfloat16, device=x.device)
+                ga[:, :n_exp] = g_hi
+                wk = torch.cat([w_hi, w_hi.new_zeros(kpad - n_exp, hidden)])
+            dx = gemm_nn(ga, wk, K=ga.shape[1])
+        if ctx.needs_input_grad[1]:
+            both = gemm_tn(g2, x, M=2 * n_exp)
+            dw = (both[:n_exp] + both[n_exp:2 * n_exp]).to(weight.dtype)
+        return dx, dw
 
 
 class _RouterFn(torch.autograd.Function):
@@ -477,6 +529,13 @@ class NativeOpsBackend(TorchOpsBackend):
             return _FusedLinearCEFn.apply(x, weight, targets)
         return super().fused_linear_cross_entropy(x, weight, targets)
 
+    def router_logits(self, hidden_states, weight):
+        ok = (hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16 and hidden_states.dim() == 2
+              and hidden_states.is_contiguous() and hidden_states.shape[1] % 8 == 0 and weight.shape[0] <= 64)
+        if self._count("router_logits", ok):
+            return _RouterLogitsFn.apply(hidden_states, weight)
+        return torch.nn.functional.linear(hidden_states.float(), weight.float())
+
     def router_postprocess(self, logits, top_k, *, normalize):
         check_router_args(logits, top_k)
         ok = logits.is_cuda and logits.shape[1] <= 64 and top_k <= 8
@@ -492,6 +551,15 @@ class NativeOpsBackend(TorchOpsBackend):
         if self._count("fused_moe", ok):
             return _FusedMoEFn.apply(x, gate_up_proj, down_proj, top_k_index, top_k_weights)
         return super().fused_moe(x, gate_up_proj, down_proj, top_k_index, top_k_weights)
+
+    def attention_qkv(self, fused, cos, sin, *, is_causal, dropout_p):
+        """Fused RoPE + attention on a ``[B, S, 3, H, D]`` projection; ``None`` when the inputs are not covered."""
+
+        from mini_train_sys_b200.ops import native_attention
+
+        if not self._count("attention_qkv", native_attention.qkv_supported(fused, cos, sin, dropout_p)):
+            return None
+        return native_attention.qkv_attention(fused, cos, sin, is_causal=is_causal, dropout_p=dropout_p)
 
     def attention(self, q, k, v, *, is_causal, dropout_p):
         from mini_train_sys_b200.ops import native_attention

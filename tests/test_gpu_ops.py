@@ -29,8 +29,13 @@ def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
     return float((got - want).norm() / want.norm().clamp_min(1e-12))
 
 
-def assert_close(got, want, tol, what=""):
-    err = rel_err(got, want)
+def assert_close(got, want, tol, what="", floor=0.0):
+    """Relative L2 error; ``floor`` is an absolute norm below which the expected value counts as zero."""
+
+    got, want = got.detach().float(), want.detach().float()
+    diff = float((got - want).norm())
+    scale = max(float(want.norm()), floor)
+    err = diff / max(scale, 1e-30)
     assert math.isfinite(err) and err <= tol, f"{what}: relative L2 error {err:.3e} > {tol:.1e}"
 
 
@@ -306,9 +311,9 @@ def test_tiny_model_matches_torch_backend():
         losses[name] = float(loss)
         grads[name] = {n: p.grad.float().clone() for n, p in model.named_parameters()}
     assert abs(losses["torch"] - losses["native"]) < 2e-2, losses
-    for n, g in grads["torch"].items():
-        err = rel_err(grads["native"][n], g)
-        assert err < 0.1, f"{n}: {err}"
+    errors = {n: rel_err(grads["native"][n], g) for n, g in grads["torch"].items()}
+    bad = {n: round(e, 4) for n, e in errors.items() if not e < 0.1}
+    assert not bad, f"gradient mismatch: {bad}"
 
 
 @pytest.mark.parametrize("causal", [True, False])
@@ -328,8 +333,9 @@ def test_flash_attention(causal, b, h, s):
     want = ref.attention_ref(q32, k32, v32, is_causal=causal)
     (rg,) = torch.autograd.grad(want, f32, d_o.float())
     assert_close(out, want, 2e-2, "out")
+    floor = 1e-3 * float(d_o.float().norm())   # with one key the softmax is constant and dq, dk vanish
     for j, name in enumerate("qkv"):
-        assert_close(g[:, :, j], rg[:, :, j], 3e-2, f"d{name}")
+        assert_close(g[:, :, j], rg[:, :, j], 3e-2, f"d{name}", floor=floor)
     from mini_train_sys_b200.ops.native_backend import check_kernel_status
 
     check_kernel_status()
@@ -374,3 +380,38 @@ def test_attention_capability_contract():
     assert not na.supported(ok.cpu(), ok.cpu(), ok.cpu(), is_causal=True, dropout_p=0.0)
     odd = torch.randn(1, 2, 16, 65, device=DEV, dtype=torch.bfloat16)[..., 1:]
     assert not na.supported(odd, odd, odd, is_causal=True, dropout_p=0.0)
+
+
+def test_router_logits_split_gemm(ops):
+    torch.manual_seed(15)
+    x = torch.randn(3000, 768, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (0.02 * torch.randn(8, 768, device=DEV)).requires_grad_()
+    g = torch.randn(3000, 8, device=DEV)
+    logits = ops.router_logits(x, w)
+    gx, gw = torch.autograd.grad(logits, (x, w), g)
+    x64, w64 = x.detach().double().requires_grad_(), w.detach().double().requires_grad_()
+    want = x64 @ w64.t()
+    rx, rw = torch.autograd.grad(want, (x64, w64), g.double())
+    assert logits.dtype == torch.float32
+    assert_close(logits, want, 2e-5, "logits")
+    assert_close(gw, rw, 2e-5, "dW")
+    assert_close(gx, rx, 1e-2, "dx")
+
+
+def test_qkv_attention_fused_path(ops):
+    from mini_train_sys_b200.models.rotary import rope_tables
+
+    torch.manual_seed(16)
+    b, s, h = 2, 300, 4
+    fused = torch.randn(b, s, 3, h, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    cos, sin = (t[:s].to(DEV).to(torch.bfloat16).contiguous() for t in rope_tables(64, 512, 10000.0))
+    out = ops.attention_qkv(fused, cos, sin, is_causal=True, dropout_p=0.0)
+    assert out is not None and out.shape == (b, h, s, 64)
+    d_o = torch.randn_like(out)
+    (g,) = torch.autograd.grad(out, fused, d_o)
+    f32 = fused.detach().float().requires_grad_()
+    q, k, v = (f32[:, :, j].transpose(1, 2) for j in range(3))
+    want = ref.attention_ref(ref.rope_ref(q, cos, sin), ref.rope_ref(k, cos, sin), v, is_causal=True)
+    (rg,) = torch.autograd.grad(want, f32, d_o.float())
+    assert_close(out, want, 2e-2, "out")
+    assert_close(g, rg, 3e-2, "d fused qkv")
