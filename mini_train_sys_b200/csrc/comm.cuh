@@ -1,8 +1,39 @@
-// Peer-memory collectives for sm_100a (implemented in comm.cu).
+// Peer-memory collectives for sm_100a (implemented in comm.cu): flag signalling with bounded waits,
+// pull all-gather, pull / multimem reduce-scatter, AdamW fused with the push of the updated weights,
+// and a scalar all-reduce that also produces the gradient-clipping coefficient.
 #pragma once
 
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ops.cuh"
+
 namespace mts {
+
+constexpr int kMaxPeers = 16;
+
+// One pointer per rank (peer-mapped addresses of the same symmetric allocation), passed by value.
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+
+cudaError_t launch_signal(const PeerPtrs& flag_bases, int channel, int world, int rank, unsigned epoch, cudaStream_t stream);
+cudaError_t launch_wait(const unsigned* my_flags, int channel, int world, unsigned epoch, unsigned long long timeout_ns,
+                        int* status, cudaStream_t stream);
+// `epoch == 0` skips the wait (single-rank use and tests of the copy itself).
+cudaError_t launch_allgather_pull(void* dst, const PeerPtrs& shards, long long shard_bytes, int world, const unsigned* my_flags,
+                                  int channel, unsigned epoch, unsigned long long timeout_ns, int* status, int max_ctas,
+                                  cudaStream_t stream);
+// out[i] = scale * sum_r bufs[r][slice_offset + i]; *sumsq += sum(out^2).  With `multicast_base` the sum is a
+// multimem.ld_reduce on the NVLS multicast mapping of the same buffers.
+cudaError_t launch_reduce_scatter(float* out, const PeerPtrs& bufs, const float* multicast_base, long long slice_offset,
+                                  long long n, int world, float scale, float* sumsq, const unsigned* my_flags, int channel,
+                                  unsigned epoch, unsigned long long timeout_ns, int* status, int max_ctas, cudaStream_t stream);
+cudaError_t launch_adamw_push(const AdamWArgs& args, const PeerPtrs& replicas, long long replica_elem_offset, int world,
+                              bool push_bf16, int max_ctas, cudaStream_t stream);
+cudaError_t launch_scalar_allreduce_clip(const float* local_value, const PeerPtrs& slots, const PeerPtrs& flag_bases,
+                                         const unsigned* my_flags, int channel, int world, int rank, unsigned epoch,
+                                         unsigned long long timeout_ns, float max_norm, float extra_scale, float* coef_out,
+                                         float* norm_out, int* status, cudaStream_t stream);
+
 }  // namespace mts

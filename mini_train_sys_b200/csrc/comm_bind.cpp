@@ -1,3 +1,116 @@
+// Python bindings of the peer-memory collectives.  Peer pointers arrive as integer lists (one per rank)
+// obtained from the symmetric-memory rendezvous; everything else is an ordinary CUDA tensor.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
-void bind_comm(pybind11::module_& m) { (void)m; }
+#include "comm.cuh"
+
+namespace {
+
+using torch::Tensor;
+
+cudaStream_t cur() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+mts::PeerPtrs to_ptrs(const std::vector<int64_t>& v) {
+  TORCH_CHECK(!v.empty() && v.size() <= size_t(mts::kMaxPeers), "between 1 and ", mts::kMaxPeers, " peers are supported");
+  mts::PeerPtrs out{};
+  for (size_t i = 0; i < v.size(); ++i) {
+    TORCH_CHECK(v[i] != 0 && (v[i] & 15) == 0, "peer pointers must be non-null and 16-byte aligned");
+    out.p[i] = reinterpret_cast<void*>(v[i]);
+  }
+  return out;
+}
+
+void ok(cudaError_t e, const char* what) { TORCH_CHECK(e == cudaSuccess, what, " failed: ", cudaGetErrorString(e)); }
+
+const unsigned* flags_ptr(const Tensor& flags, int64_t channel, int64_t world) {
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.is_contiguous(), "flags must be contiguous int32");
+  TORCH_CHECK(channel >= 0 && (channel + 1) * world <= flags.numel(), "flag channel out of range");
+  return reinterpret_cast<const unsigned*>(flags.data_ptr<int>());
+}
+
+void comm_signal(const std::vector<int64_t>& flag_bases, int64_t channel, int64_t rank, int64_t epoch, const Tensor& like) {
+  c10::cuda::CUDAGuard guard(like.device());
+  ok(mts::launch_signal(to_ptrs(flag_bases), int(channel), int(flag_bases.size()), int(rank), unsigned(epoch), cur()), "signal");
+}
+
+void comm_wait(const Tensor& flags, int64_t channel, int64_t world, int64_t epoch, double timeout_ms, Tensor status) {
+  c10::cuda::CUDAGuard guard(flags.device());
+  ok(mts::launch_wait(flags_ptr(flags, channel, world), int(channel), int(world), unsigned(epoch),
+                      (unsigned long long)(timeout_ms * 1e6), status.data_ptr<int>(), cur()), "wait");
+}
+
+void comm_allgather(Tensor dst, const std::vector<int64_t>& shard_ptrs, int64_t shard_bytes, const Tensor& flags, int64_t channel,
+                    int64_t epoch, double timeout_ms, Tensor status, int64_t max_ctas) {
+  const int64_t world = int64_t(shard_ptrs.size());
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && dst.numel() * dst.element_size() >= shard_bytes * world, "dst too small");
+  TORCH_CHECK(shard_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(dst.data_ptr()) & 15) == 0, "16-byte alignment required");
+  c10::cuda::CUDAGuard guard(dst.device());
+  ok(mts::launch_allgather_pull(dst.data_ptr(), to_ptrs(shard_ptrs), shard_bytes, int(world), flags_ptr(flags, channel, world),
+                                int(channel), unsigned(epoch), (unsigned long long)(timeout_ms * 1e6), status.data_ptr<int>(),
+                                int(max_ctas), cur()), "allgather");
+}
+
+void comm_reduce_scatter(Tensor out, const std::vector<int64_t>& buf_ptrs, int64_t multicast_ptr, int64_t slice_offset,
+                         double scale, const c10::optional<Tensor>& sumsq, const Tensor& flags, int64_t channel, int64_t epoch,
+                         double timeout_ms, Tensor status, int64_t max_ctas) {
+  const int64_t world = int64_t(buf_ptrs.size());
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.is_contiguous(), "out must be contiguous fp32");
+  TORCH_CHECK(out.numel() % 4 == 0 && slice_offset % 4 == 0 && (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0,
+              "reduce-scatter slices must be multiples of 4 floats and 16-byte aligned");
+  float* sq = (sumsq.has_value() && sumsq->defined()) ? sumsq->data_ptr<float>() : nullptr;
+  c10::cuda::CUDAGuard guard(out.device());
+  ok(mts::launch_reduce_scatter(out.data_ptr<float>(), to_ptrs(buf_ptrs), reinterpret_cast<const float*>(multicast_ptr),
+                                slice_offset, out.numel(), int(world), float(scale), sq, flags_ptr(flags, channel, world),
+                                int(channel), unsigned(epoch), (unsigned long long)(timeout_ms * 1e6), status.data_ptr<int>(),
+                                int(max_ctas), cur()), "reduce_scatter");
+}
+
+void comm_adamw_push(Tensor param, const Tensor& grad, Tensor exp_avg, Tensor exp_avg_sq, const std::vector<int64_t>& replica_ptrs,
+                     int64_t replica_elem_offset, bool push_bf16, double lr, double beta1, double beta2, double eps,
+                     double weight_decay, int64_t step, const c10::optional<Tensor>& grad_scale, double static_scale,
+                     int64_t max_ctas) {
+  TORCH_CHECK(param.is_cuda() && param.scalar_type() == at::kFloat && param.is_contiguous() && param.numel() % 8 == 0,
+              "param shard must be contiguous fp32 with a multiple of 8 elements");
+  TORCH_CHECK(grad.scalar_type() == at::kFloat && grad.is_contiguous() && grad.numel() == param.numel() &&
+                  exp_avg.numel() == param.numel() && exp_avg_sq.numel() == param.numel(), "state size mismatch");
+  for (const void* ptr : {param.data_ptr(), grad.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr()})
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, "adamw buffers must be 16-byte aligned");
+  TORCH_CHECK(replica_elem_offset % 8 == 0, "replica offset must be a multiple of 8 elements");
+  c10::cuda::CUDAGuard guard(param.device());
+  mts::AdamWArgs a{};
+  a.param = param.data_ptr<float>(); a.grad = grad.data_ptr<float>();
+  a.exp_avg = exp_avg.data_ptr<float>(); a.exp_avg_sq = exp_avg_sq.data_ptr<float>();
+  a.shadow_bf16 = nullptr; a.n = param.numel();
+  a.lr = float(lr); a.beta1 = float(beta1); a.beta2 = float(beta2); a.eps = float(eps); a.weight_decay = float(weight_decay);
+  a.bias_correction1 = float(1.0 - std::pow(beta1, double(step)));
+  a.bias_correction2 = float(1.0 - std::pow(beta2, double(step)));
+  a.grad_scale = (grad_scale.has_value() && grad_scale->defined()) ? grad_scale->data_ptr<float>() : nullptr;
+  a.static_grad_scale = float(static_scale);
+  ok(mts::launch_adamw_push(a, to_ptrs(replica_ptrs), replica_elem_offset, int(replica_ptrs.size()), push_bf16, int(max_ctas), cur()),
+     "adamw_push");
+}
+
+void comm_norm_clip(const Tensor& local_sumsq, const std::vector<int64_t>& slot_ptrs, const std::vector<int64_t>& flag_bases,
+                    const Tensor& flags, int64_t channel, int64_t rank, int64_t epoch, double timeout_ms, double max_norm,
+                    double extra_scale, Tensor coef, Tensor norm, Tensor status) {
+  const int64_t world = int64_t(slot_ptrs.size());
+  TORCH_CHECK(flag_bases.size() == slot_ptrs.size(), "peer lists differ in length");
+  c10::cuda::CUDAGuard guard(local_sumsq.device());
+  ok(mts::launch_scalar_allreduce_clip(local_sumsq.data_ptr<float>(), to_ptrs(slot_ptrs), to_ptrs(flag_bases),
+                                       flags_ptr(flags, channel, world), int(channel), int(world), int(rank), unsigned(epoch),
+                                       (unsigned long long)(timeout_ms * 1e6), float(max_norm), float(extra_scale),
+                                       coef.data_ptr<float>(), norm.data_ptr<float>(), status.data_ptr<int>(), cur()), "norm_clip");
+}
+
+}  // namespace
+
+void bind_comm(pybind11::module_& m) {
+  m.def("comm_signal", &comm_signal);
+  m.def("comm_wait", &comm_wait);
+  m.def("comm_allgather", &comm_allgather);
+  m.def("comm_reduce_scatter", &comm_reduce_scatter);
+  m.def("comm_adamw_push", &comm_adamw_push);
+  m.def("comm_norm_clip", &comm_norm_clip);
+}

@@ -1,0 +1,405 @@
+"""Flat-buffer data-parallel engine: sharded fp32 master weights + low-precision replicas.
+
+One engine serves both strategies of this package:
+
+* ``mode="shard"`` (FSDP): one unit per ``TransformerBlock`` plus a root unit (embedding, final norm,
+  head) - the same 13-unit split the reference gets from torch FSDP for the 12-layer model
+  (minitrain/distributed/fsdp.py:38-45, scripts/train.py:179-203).
+* ``mode="replicate"`` (DDP): units are size-bounded buckets in reverse parameter order, so the
+  first buckets complete early in backward (the reference uses torch DDP with 25 MB buckets,
+  minitrain/distributed/ddp.py:54-65).
+
+Per unit and per rank the engine holds: the rank's slice of the fp32 master weights and of both
+Adam moments, a full fp32 gradient buffer (input of the reduce-scatter) and a full low-precision
+replica that the module's parameters are views of.  A training step is then
+
+    backward      parameter hooks copy each gradient into the unit's flat buffer; when a unit is
+                  complete its reduce-scatter runs on a side stream, overlapping the rest of backward
+    optimizer     one cross-rank sum gives the global gradient norm and the clip coefficient on the
+                  device (no host synchronisation); a fused AdamW kernel updates the local slice and
+                  stores the new low-precision weights into every rank's replica, so there is no
+                  separate parameter all-gather
+
+``collectives`` decides how the cross-rank parts run: ``PeerCollectives`` (own kernels over NVLink
+peer memory) or ``TorchCollectives`` (NCCL / Gloo / single rank).  Optimizer state is always sharded.
+
+Memory note: replicas stay resident between steps (ZeRO-2-style for ``full_shard`` as well); for the
+model sizes shipped here a full bf16 replica is below 1.1 GB on a 180 GB device.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from mini_train_sys_b200.parallel.comm import PeerCollectives, SymBuffer, TorchCollectives
+from mini_train_sys_b200.runtime.config import OptimizerConfig
+
+ALIGN = 8   # parameter offsets inside a unit are multiples of 8 elements (16 bytes in bf16)
+
+
+@dataclass
+class ParamSlot:
+    name: str
+    param: nn.Parameter
+    offset: int
+    numel: int
+    shape: torch.Size
+    decay: bool
+
+
+@dataclass
+class Unit:
+    index: int
+    name: str
+    slots: list[ParamSlot]
+    total: int = 0                  # padded element count of the whole unit
+    shard_numel: int = 0
+    master: torch.Tensor = None     # fp32 [shard]
+    exp_avg: torch.Tensor = None
+    exp_avg_sq: torch.Tensor = None
+    grad_shard: torch.Tensor = None
+    grad_full: SymBuffer = None     # fp32 [total]
+    gathered: SymBuffer = None      # low precision [total]; parameters are views of this
+    low_shard: SymBuffer = None     # low precision [shard]; source of pull all-gathers
+    sumsq: torch.Tensor = None
+    pending: int = 0
+    segments: list[tuple[int, int, bool]] = field(default_factory=list)   # (lo, hi, decay) inside the local shard
+
+
+def _round_up(n: int, m: int) -> int:
+    return -(-n // m) * m
+
+
+def _partition(model: nn.Module, mode: str, per_block_units: bool, bucket_bytes: int) -> list[tuple[str, list[tuple[str, nn.Parameter]]]]:
+    named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+    frozen = [n for n, p in model.named_parameters() if not p.requires_grad]
+    if frozen:
+        raise ValueError(f"the flat engine expects every parameter to be trainable; frozen: {frozen[:3]}...")
+    if mode == "shard":
+        if not per_block_units:
+            return [("root", named)]
+        blocks: dict[str, list] = {}
+        root = []
+        for n, p in named:
+            if n.startswith("blocks."):
+                blocks.setdefault(".".join(n.split(".")[:2]), []).append((n, p))
+            else:
+                root.append((n, p))
+        return [("root", root)] + [(k, v) for k, v in blocks.items()]
+    buckets, current, size = [], [], 0
+    for n, p in reversed(named):
+        current.append((n, p))
+        size += p.numel() * 4
+        if size >= bucket_bytes:
+            buckets.append((f"bucket{len(buckets)}", current))
+            current, size = [], 0
+    if current:
+        buckets.append((f"bucket{len(buckets)}", current))
+    return buckets
+
+
+class FlatDataParallel(nn.Module):
+    def __init__(self, module: nn.Module, *, mode: str = "shard", comm: Any = None, bucket_cap_mb: int = 25,
+                 reshard_after_forward: bool = True, per_block_units: bool = True,
+                 activation_checkpointing: bool = False, collectives: Any = None) -> None:
+        super().__init__()
+        if mode not in ("shard", "replicate"):
+            raise ValueError("mode must be 'shard' or 'replicate'")
+        self.module = module
+        self.mode = mode
+        self.reshard_after_forward = reshard_after_forward
+        first = next(module.parameters())
+        self.device = first.device
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        act = getattr(module, "activation_dtype", torch.float32)
+        self.param_dtype = act if (self.device.type == "cuda" and act in (torch.bfloat16,)) else torch.float32
+
+        layout = _partition(module, mode, per_block_units, bucket_cap_mb * 2**20)
+        if collectives is None:
+            engine = getattr(comm, "engine", "auto") if comm is not None else "auto"
+            want_fused = self.device.type == "cuda" and engine in ("auto", "fused") and self.param_dtype == torch.bfloat16
+            if want_fused:
+                collectives = PeerCollectives(self.device, max_units=len(layout),
+                                              wait_timeout_ms=getattr(comm, "wait_timeout_ms", 2000),
+                                              use_multimem=getattr(comm, "use_multimem", False))
+            else:
+                collectives = TorchCollectives(self.device)
+        self.coll = collectives
+        self.step_count = 0
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.clip_coef = torch.ones(1, dtype=torch.float32, device=self.device)
+        self.grad_norm = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.units: list[Unit] = []
+        self._slot_of: dict[nn.Parameter, tuple[Unit, ParamSlot]] = {}
+        for index, (name, params) in enumerate(layout):
+            self.units.append(self._build_unit(index, name, params))
+        for unit in self.units:
+            self.coll.refresh_replicas(unit, 0)
+        if activation_checkpointing:
+            self._enable_activation_checkpointing()
+
+    # ---- construction -----------------------------------------------------------------------------
+    def _build_unit(self, index: int, name: str, params: list[tuple[str, nn.Parameter]]) -> Unit:
+        slots, offset = [], 0
+        for pname, p in params:
+            slots.append(ParamSlot(pname, p, offset, p.numel(), p.shape, p.ndim >= 2))
+            offset += _round_up(p.numel(), ALIGN)
+        unit = Unit(index, name, slots)
+        unit.total = _round_up(offset, self.world * 64)
+        unit.shard_numel = unit.total // self.world
+        dev, f32 = self.device, torch.float32
+        lo, hi = self.rank * unit.shard_numel, (self.rank + 1) * unit.shard_numel
+        flat = torch.zeros(unit.total, dtype=f32, device=dev)
+        for s in slots:
+            flat[s.offset:s.offset + s.numel].copy_(s.param.detach().reshape(-1).float())
+        unit.master = flat[lo:hi].clone()
+        del flat
+        unit.exp_avg = torch.zeros(unit.shard_numel, dtype=f32, device=dev)
+        unit.exp_avg_sq = torch.zeros(unit.shard_numel, dtype=f32, device=dev)
+        unit.grad_shard = torch.zeros(unit.shard_numel, dtype=f32, device=dev)
+        unit.grad_full = self.coll.alloc(unit.total, f32, shared=True)
+        unit.gathered = self.coll.alloc(unit.total, self.param_dtype, shared=True)
+        unit.low_shard = self.coll.alloc(unit.shard_numel, self.param_dtype, shared=True)
+        unit.sumsq = self.sumsq
+        # weight-decay segments: intersections of the parameters with the local shard
+        for s in slots:
+            a, b = max(s.offset, lo), min(s.offset + _round_up(s.numel, ALIGN), hi)
+            if a < b:
+                unit.segments.append((a - lo, b - lo, s.decay))
+        unit.segments = _merge_segments(unit.segments, unit.shard_numel)
+        for s in slots:
+            s.param.data = unit.gathered.tensor[s.offset:s.offset + s.numel].view(s.shape)
+            self._slot_of[s.param] = (unit, s)
+            s.param.register_post_accumulate_grad_hook(self._on_grad)
+        unit.pending = len(slots)
+        return unit
+
+    def _enable_activation_checkpointing(self) -> None:
+        from torch.utils.checkpoint import checkpoint
+
+        from mini_train_sys_b200.models.blocks import TransformerBlock
+
+        for m in self.module.modules():
+            if isinstance(m, TransformerBlock) and not hasattr(m, "_plain_forward"):
+                m._plain_forward = m.forward
+                m.forward = lambda *a, _f=m._plain_forward, **k: checkpoint(_f, *a, use_reentrant=False, **k)
+
+    # ---- forward / backward -------------------------------------------------------------------------
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
+    def unit_count(self) -> int:
+        return len(self.units)
+
+    @torch.no_grad()
+    def _on_grad(self, param: nn.Parameter) -> None:
+        unit, slot = self._slot_of[param]
+        dst = unit.grad_full.tensor[slot.offset:slot.offset + slot.numel].view(slot.shape)
+        dst.copy_(param.grad)
+        param.grad = None
+        unit.pending -= 1
+        if unit.pending == 0:
+            self.coll.reduce_scatter(unit, self.step_count + 1)
+
+    def _flush_incomplete_units(self) -> None:
+        """Units with parameters that received no gradient this step still have to take part."""
+
+        for unit in self.units:
+            if unit.pending > 0:
+                for s in unit.slots:
+                    if s.param.grad is not None:
+                        self._on_grad(s.param)
+                if unit.pending > 0:   # truly unused parameters contribute zeros
+                    done = len(unit.slots) - unit.pending
+                    if done == 0:
+                        unit.grad_full.tensor.zero_()
+                    unit.pending = 0
+                    self.coll.reduce_scatter(unit, self.step_count + 1)
+
+    # ---- optimizer ------------------------------------------------------------------------------------
+    def build_sharded_optimizer(self, cfg: OptimizerConfig) -> "ShardedAdamW":
+        return ShardedAdamW(self, cfg)
+
+    # ---- state dicts ------------------------------------------------------------------------------------
+    def _full_flat(self, shard: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return shard
+        full = torch.empty(shard.numel() * self.world, dtype=shard.dtype, device=shard.device)
+        dist.all_gather_into_tensor(full, shard.contiguous())
+        return full
+
+    def _mesh(self):
+        from torch.distributed.device_mesh import init_device_mesh
+
+        if not hasattr(self, "_device_mesh"):
+            self._device_mesh = init_device_mesh(self.device.type, (self.world,))
+        return self._device_mesh
+
+    def _as_sharded(self, full: torch.Tensor, cpu_offload: bool):
+        if cpu_offload and self.world == 1:
+            return full.cpu()
+        if self.world == 1:
+            return full.clone()
+        from torch.distributed.tensor import Shard, distribute_tensor
+
+        return distribute_tensor(full.contiguous(), self._mesh(), [Shard(0)])
+
+    def sharded_state_dict(self, optimizer: "ShardedAdamW", *, cpu_offload: bool = True):
+        """``(model_state, optim_state)`` keyed by plain parameter names; tensors are dim-0 sharded DTensors."""
+
+        model_state: dict[str, Any] = {}
+        opt_state: dict[str, Any] = {}
+        for unit in self.units:
+            flats = {k: self._full_flat(t) for k, t in (("p", unit.master), ("m", unit.exp_avg), ("v", unit.exp_avg_sq))}
+            for s in unit.slots:
+                pick = lambda key: flats[key][s.offset:s.offset + s.numel].view(s.shape)  # noqa: E731
+                model_state[s.name] = self._as_sharded(pick("p"), cpu_offload)
+                opt_state[s.name] = {"step": torch.tensor(float(self.step_count)),
+                                     "exp_avg": self._as_sharded(pick("m"), cpu_offload),
+                                     "exp_avg_sq": self._as_sharded(pick("v"), cpu_offload)}
+        for extra, buf in self.module.named_buffers():
+            if extra in self.module.state_dict():
+                model_state[extra] = buf
+        groups = optimizer.describe_groups() if optimizer is not None else []
+        return model_state, {"state": opt_state, "param_groups": groups}
+
+    @torch.no_grad()
+    def load_sharded_state_dict(self, model_state, optim_state, optimizer: "ShardedAdamW | None" = None) -> None:
+        def full(t):
+            t = t.full_tensor() if hasattr(t, "full_tensor") else t
+            return t.to(self.device, torch.float32).reshape(-1)
+
+        steps = []
+        for unit in self.units:
+            lo, hi = self.rank * unit.shard_numel, (self.rank + 1) * unit.shard_numel
+            for key, dst in (("p", unit.master), ("m", unit.exp_avg), ("v", unit.exp_avg_sq)):
+                flat = torch.zeros(unit.total, dtype=torch.float32, device=self.device)
+                for s in unit.slots:
+                    if key == "p":
+                        src = model_state[s.name]
+                    else:
+                        entry = optim_state.get("state", {}).get(s.name)
+                        if entry is None:
+                            continue
+                        src = entry["exp_avg" if key == "m" else "exp_avg_sq"]
+                        if key == "m" and "step" in entry:
+                            steps.append(float(entry["step"]))
+                    flat[s.offset:s.offset + s.numel].copy_(full(src))
+                dst.copy_(flat[lo:hi])
+        if steps:
+            self.step_count = int(max(steps))
+        if optimizer is not None:
+            optimizer.adopt_groups(optim_state.get("param_groups", []))
+        for unit in self.units:
+            self.coll.refresh_replicas(unit, 0)
+
+    def full_state_dict(self) -> dict[str, torch.Tensor]:
+        """Consolidated fp32 CPU weights under the plain parameter names (tied weights appear under both names)."""
+
+        out: dict[str, torch.Tensor] = {}
+        for unit in self.units:
+            flat = self._full_flat(unit.master)
+            for s in unit.slots:
+                out[s.name] = flat[s.offset:s.offset + s.numel].view(s.shape).detach().cpu().clone()
+        by_param = {id(p): n for n, p in self.module.named_parameters()}
+        for name, p in self.module.named_parameters(remove_duplicate=False):
+            if name not in out and id(p) in by_param:
+                out[name] = out[by_param[id(p)]]
+        ordered = {k: out[k] for k in self.module.state_dict().keys() if k in out}
+        return ordered
+
+    def state_dict(self, *args, **kwargs):
+        return self.module.state_dict(*args, **kwargs)
+
+
+def _merge_segments(segs: list[tuple[int, int, bool]], shard_numel: int) -> list[tuple[int, int, bool]]:
+    """Cover ``[0, shard_numel)`` with maximal runs of equal decay flag (padding joins its left neighbour)."""
+
+    if not segs:
+        return [(0, shard_numel, False)] if shard_numel else []
+    segs = sorted(segs)
+    out = [[0, segs[0][1], segs[0][2]]]
+    for lo, hi, decay in segs[1:]:
+        if decay == out[-1][2]:
+            out[-1][1] = hi
+        else:
+            out[-1][1] = lo
+            out.append([lo, hi, decay])
+    out[-1][1] = shard_numel
+    return [(a, b, d) for a, b, d in out if a < b]
+
+
+class ShardedAdamW(torch.optim.Optimizer):
+    """AdamW over the engine's flat shards; gradient clipping is folded into the update kernel."""
+
+    owns_clipping = True
+
+    def __init__(self, engine: FlatDataParallel, cfg: OptimizerConfig) -> None:
+        self.engine = engine
+        self._clip: float | None = None
+        dummy = [torch.zeros(1, device=engine.device, requires_grad=True), torch.zeros(1, device=engine.device, requires_grad=True)]
+        defaults = dict(lr=cfg.lr, betas=(cfg.beta1, cfg.beta2), eps=cfg.eps, weight_decay=cfg.weight_decay)
+        super().__init__([{"params": [dummy[0]], "weight_decay": cfg.weight_decay},
+                          {"params": [dummy[1]], "weight_decay": 0.0}], defaults)
+
+    def set_clip_norm(self, max_norm: float | None) -> None:
+        self._clip = max_norm
+
+    def last_grad_norm(self) -> torch.Tensor:
+        return self.engine.grad_norm[0]
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for unit in self.engine.units:
+            for s in unit.slots:
+                s.param.grad = None
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        eng = self.engine
+        eng._flush_incomplete_units()
+        epoch = eng.step_count + 1
+        eng.coll.norm_and_clip(eng.sumsq, self._clip, epoch, eng.clip_coef, eng.grad_norm)
+        decay_group, plain_group = self.param_groups
+        for unit in eng.units:
+            for lo, hi, decay in unit.segments:
+                g = decay_group if decay else plain_group
+                eng.coll.adamw_update(unit, (lo, hi), lr=float(g["lr"]), beta1=g["betas"][0], beta2=g["betas"][1],
+                                      eps=g["eps"], weight_decay=float(g["weight_decay"]), step=epoch, coef=eng.clip_coef)
+            if not eng.coll.fused:
+                eng.coll.refresh_replicas(unit, epoch)
+            unit.pending = len(unit.slots)
+        eng.coll.refresh_done(epoch)
+        eng.sumsq.zero_()
+        eng.step_count = epoch
+        return None
+
+    # ---- checkpoint helpers ----
+    def describe_groups(self) -> list[dict[str, Any]]:
+        names = {True: [], False: []}
+        for unit in self.engine.units:
+            for s in unit.slots:
+                names[s.decay].append(s.name)
+        out = []
+        for g, decay in zip(self.param_groups, (True, False)):
+            out.append({"lr": g["lr"], "betas": tuple(g["betas"]), "eps": g["eps"], "weight_decay": g["weight_decay"],
+                        "params": names[decay]})
+        return out
+
+    def adopt_groups(self, groups: list[dict[str, Any]]) -> None:
+        for mine, theirs in zip(self.param_groups, groups):
+            for key in ("lr", "betas", "eps", "weight_decay"):
+                if key in theirs:
+                    mine[key] = theirs[key]
+
+    def state_dict(self):
+        return {"step": self.engine.step_count, "param_groups": self.describe_groups()}
+
+    def load_state_dict(self, state):
+        self.engine.step_count = int(state.get("step", self.engine.step_count))
+        self.adopt_groups(state.get("param_groups", []))

@@ -37,7 +37,7 @@ def build_parallel_strategy(cfg: ExperimentConfig, *, resolved_precision: str | 
     if name == "single":
         from mini_train_sys_b200.parallel.single import SingleDeviceStrategy
 
-        return SingleDeviceStrategy()
+        return SingleDeviceStrategy(engine=resolve_comm_engine(cfg), comm=cfg.parallel.comm)
     engine = resolve_comm_engine(cfg)
     if name == "ddp":
         from mini_train_sys_b200.parallel.ddp import DDPStrategy

@@ -86,7 +86,7 @@ class TrainingRunner:
         started, first_step, first_tokens = session
         scalars = {k: float(v / steps) for k, v in iv.scalars.items()}
         scalars["lr"] = self.trainer.last_lr
-        scalars["grad_clip_fraction"] = iv.clipped / steps
+        scalars["grad_clip_fraction"] = scalars.get("grad_was_clipped", iv.clipped / steps)
         scalars = distributed_mean(scalars, self.device)
         images = distributed_mean_tensors({k: v / steps for k, v in iv.images.items()}, self.device)
         session_seconds = now - started

@@ -72,9 +72,17 @@ class Trainer:
             norm = torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.grad_clip_norm)
         self._record_norm(float(norm.detach()))
 
-    def _after_owned_clip(self) -> None:
-        if self.grad_clip_norm is not None and getattr(self.optimizer, "owns_clipping", False):
-            self._record_norm(float(self.optimizer.last_grad_norm()))
+    def _after_owned_clip(self) -> dict[str, torch.Tensor]:
+        """Clip statistics of an optimizer that clips on the device; nothing is read back to the host."""
+
+        if self.grad_clip_norm is None or not getattr(self.optimizer, "owns_clipping", False):
+            return {}
+        norm = self.optimizer.last_grad_norm().detach().clone()
+        self.last_grad_norm, self.last_grad_clip_coefficient, self.last_grad_was_clipped = None, 1.0, False
+        limit = float(self.grad_clip_norm)
+        return {"grad_norm": norm, "grad_clip_threshold": torch.tensor(limit),
+                "grad_clip_coefficient": (limit / (norm + 1e-6)).clamp(max=1.0),
+                "grad_was_clipped": (norm > limit).float()}
 
     # ---- the step --------------------------------------------------------------
     def train_step(self, batch: dict[str, torch.Tensor]) -> torch.Tensor:
@@ -108,7 +116,7 @@ class Trainer:
             loss.backward()
             self._clip_gradients()
             self.optimizer.step()
-        self._after_owned_clip()
+        device_clip_stats = self._after_owned_clip()
         self.optimizer.zero_grad(set_to_none=True)
 
         st = self.state
@@ -124,6 +132,7 @@ class Trainer:
                 "grad_clip_coefficient": torch.tensor(self.last_grad_clip_coefficient),
                 "grad_was_clipped": torch.tensor(float(self.last_grad_was_clipped)),
             })
+        self.last_metrics.update(device_clip_stats)
         if self.grad_scaler.is_enabled():
             self.last_metrics["grad_scale"] = torch.tensor(self.grad_scaler.get_scale())
         return loss.detach()

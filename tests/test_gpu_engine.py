@@ -1,0 +1,92 @@
+"""Flat engine and peer-memory collectives on one GPU (a world of one still runs every kernel)."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _model(ops_name="native"):
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+
+    cfg = ModelConfig(vocab_size=1000, seq_len=128, n_layers=2, n_heads=4, hidden_size=256, intermediate_size=256,
+                      ffn_type="moe", num_experts=4, experts_per_token=2, tie_word_embeddings=True)
+    torch.manual_seed(0)
+    return MiniTransformer(cfg, get_ops_backend(ops_name), activation_dtype=torch.bfloat16).to(DEV)
+
+
+def _train(engine_collectives, steps=4):
+    from mini_train_sys_b200.parallel.flat_engine import FlatDataParallel
+    from mini_train_sys_b200.runtime.config import OptimizerConfig
+    from mini_train_sys_b200.train.optim import build_optimizer
+    from mini_train_sys_b200.train.trainer import Trainer
+
+    eng = FlatDataParallel(_model(), mode="shard", collectives=engine_collectives)
+    tr = Trainer(eng, build_optimizer(eng, cfg=OptimizerConfig(lr=1e-3)), torch.device(DEV), use_fused_loss=True,
+                 precision="bf16", grad_clip_norm=1.0)
+    g = torch.Generator().manual_seed(3)
+    losses, norms = [], []
+    for _ in range(steps):
+        t = torch.randint(0, 1000, (4, 129), generator=g)
+        losses.append(float(tr.train_step({"input_ids": t[:, :-1], "targets": t[:, 1:]})))
+        norms.append(float(tr.last_metrics["grad_norm"]))
+    return eng, losses, norms
+
+
+def test_fused_engine_matches_library_collectives():
+    from mini_train_sys_b200.ops.native_backend import check_kernel_status
+    from mini_train_sys_b200.parallel.comm import PeerCollectives, TorchCollectives
+
+    dev = torch.device(DEV, 0)
+    eng_a, loss_a, norm_a = _train(PeerCollectives(dev, max_units=3))
+    eng_b, loss_b, norm_b = _train(TorchCollectives(dev))
+    assert eng_a.coll.fused and not eng_b.coll.fused
+    assert loss_a == pytest.approx(loss_b, abs=2e-2)
+    assert norm_a == pytest.approx(norm_b, rel=5e-2)
+    fa, fb = eng_a.full_state_dict(), eng_b.full_state_dict()
+    for name in fa:
+        assert torch.allclose(fa[name], fb[name], atol=2e-3), name
+    check_kernel_status()
+
+
+def test_wait_on_a_flag_nobody_sets_times_out_and_reports():
+    from mini_train_sys_b200.ops.native_backend import ext
+
+    e = ext()
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    e.comm_wait(flags, 0, 2, 5, 50.0, status)          # waits for epoch 5 from two peers; nothing ever signals
+    torch.cuda.synchronize()
+    assert int(status[0]) == 1
+    flags[:2] = 5                                       # once the epoch is there the same wait passes
+    status.zero_()
+    e.comm_wait(flags, 0, 2, 5, 50.0, status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    assert torch.ones(4, device=DEV).sum().item() == 4  # the context is still usable
+
+
+def test_collective_kernels_world_of_one():
+    from mini_train_sys_b200.ops.native_backend import ext
+
+    e = ext()
+    n = 4096
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    src = torch.randn(n, device=DEV)
+    out = torch.empty(n, device=DEV)
+    sumsq = torch.zeros(1, device=DEV)
+    e.comm_reduce_scatter(out, [src.data_ptr()], 0, 0, 0.5, sumsq, flags, 0, 0, 100.0, status, 16)
+    assert torch.allclose(out, src * 0.5)
+    assert float(sumsq) == pytest.approx(float((src * 0.5).pow(2).sum()), rel=1e-4)
+    low = src.to(torch.bfloat16)
+    full = torch.empty(n, dtype=torch.bfloat16, device=DEV)
+    e.comm_allgather(full, [low.data_ptr()], n * 2, flags, 0, 0, 100.0, status, 16)
+    assert torch.equal(full, low)
+    coef, norm = torch.zeros(1, device=DEV), torch.zeros(1, device=DEV)
+    slots = torch.zeros(64, device=DEV)
+    e.comm_norm_clip(sumsq, [slots.data_ptr()], [flags.data_ptr()], flags, 1, 0, 1, 100.0, 1.0, 1.0, coef, norm, status)
+    assert float(norm) == pytest.approx(float(sumsq.sqrt()), rel=1e-5)
+    assert float(coef) == pytest.approx(min(1.0, 1.0 / (float(norm) + 1e-6)), rel=1e-5)
+    assert int(status[0]) == 0
