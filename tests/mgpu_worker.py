@@ -1,0 +1,79 @@
+"""Worker for the multi-GPU tests: launched with torchrun, one rank per GPU, prints one PASS line per check."""
+
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+
+def main() -> None:
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+    from mini_train_sys_b200.parallel.comm import PeerCollectives, TorchCollectives
+    from mini_train_sys_b200.parallel.flat_engine import FlatDataParallel
+    from mini_train_sys_b200.runtime.config import OptimizerConfig
+    from mini_train_sys_b200.train.optim import build_optimizer
+    from mini_train_sys_b200.train.trainer import Trainer
+
+    use_mm = os.environ.get("MTS_TEST_MULTIMEM", "0") == "1"
+    coll = PeerCollectives(dev, max_units=8, wait_timeout_ms=5000, use_multimem=use_mm)
+    e = coll.ext
+
+    # ---- reduce-scatter kernel against NCCL ----
+    n = 64 * 1024 * world
+    buf = coll.alloc(n, torch.float32, shared=True)
+    torch.manual_seed(100 + rank)
+    buf.tensor.copy_(torch.randn(n, device=dev))
+    want = buf.tensor.clone()
+    dist.all_reduce(want)
+    shard = n // world
+    out = torch.empty(shard, device=dev)
+    sumsq = torch.zeros(1, device=dev)
+    e.comm_signal(coll.flags.peer_ptrs, 2, rank, 1, out)
+    e.comm_reduce_scatter(out, buf.peer_ptrs, buf.multicast_ptr, rank * shard, 1.0 / world, sumsq, coll.flags.tensor, 2, 1,
+                          5000.0, coll.status, 32)
+    torch.cuda.synchronize()
+    ref = want[rank * shard:(rank + 1) * shard] / world
+    assert torch.allclose(out, ref, atol=1e-5), float((out - ref).abs().max())
+    dist.barrier()
+    if rank == 0:
+        print(f"PASS reduce_scatter multimem={bool(buf.multicast_ptr)}", flush=True)
+
+    # ---- engine: own collectives against library collectives ----
+    cfg = ModelConfig(vocab_size=1000, seq_len=128, n_layers=2, n_heads=4, hidden_size=256, intermediate_size=512,
+                      tie_word_embeddings=True)
+
+    def run(collectives):
+        torch.manual_seed(0)
+        model = MiniTransformer(cfg, get_ops_backend("native"), activation_dtype=torch.bfloat16).to(dev)
+        eng = FlatDataParallel(model, mode="shard", collectives=collectives)
+        tr = Trainer(eng, build_optimizer(eng, cfg=OptimizerConfig(lr=1e-3)), dev, use_fused_loss=True, precision="bf16",
+                     grad_clip_norm=1.0)
+        g = torch.Generator().manual_seed(7 + rank)
+        losses = []
+        for _ in range(4):
+            t = torch.randint(0, 1000, (4, 129), generator=g)
+            losses.append(float(tr.train_step({"input_ids": t[:, :-1], "targets": t[:, 1:]})))
+        return eng.full_state_dict(), losses, float(tr.last_metrics["grad_norm"])
+
+    fa, la, na = run(PeerCollectives(dev, max_units=8, wait_timeout_ms=5000, use_multimem=use_mm))
+    fb, lb, nb = run(TorchCollectives(dev))
+    for name in fa:
+        assert torch.allclose(fa[name], fb[name], atol=2e-3), (name, float((fa[name] - fb[name]).abs().max()))
+    assert abs(na - nb) <= 5e-2 * max(nb, 1e-6), (na, nb)
+    coll.check_status()
+    dist.barrier()
+    if rank == 0:
+        print(f"PASS engine losses_fused={la} losses_lib={lb}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

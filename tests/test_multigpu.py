@@ -1,0 +1,26 @@
+"""Fused collectives and the sharded engine on 2+ GPUs (one process per GPU, launched with torchrun)."""
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _launch(n: int, extra_env=None) -> str:
+    env = {**os.environ, "MASTER_ADDR": "127.0.0.1", **(extra_env or {})}
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29733", str(ROOT / "tests" / "mgpu_worker.py")]
+    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
+    return done.stdout
+
+
+def test_peer_collectives_and_engine_on_two_gpus():
+    out = _launch(min(torch.cuda.device_count(), 2))
+    assert "PASS reduce_scatter" in out and "PASS engine" in out
