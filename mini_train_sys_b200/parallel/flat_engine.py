@@ -263,8 +263,14 @@ class FlatDataParallel(nn.Module):
                 opt_state[s.name] = {"step": torch.tensor(float(self.step_count)),
                                      "exp_avg": self._as_sharded(pick("m"), cpu_offload),
                                      "exp_avg_sq": self._as_sharded(pick("v"), cpu_offload)}
+        # tied parameters appear under every name a plain model's state dict uses
+        owner = {id(p): n for n, p in self.module.named_parameters()}
+        for alias, p in self.module.named_parameters(remove_duplicate=False):
+            if alias not in model_state and id(p) in owner:
+                model_state[alias] = model_state[owner[id(p)]]
+        persistent = set(self.module.state_dict().keys())
         for extra, buf in self.module.named_buffers():
-            if extra in self.module.state_dict():
+            if extra in persistent:
                 model_state[extra] = buf
         groups = optimizer.describe_groups() if optimizer is not None else []
         return model_state, {"state": opt_state, "param_groups": groups}
@@ -388,7 +394,9 @@ class ShardedAdamW(torch.optim.Optimizer):
         out = []
         for g, decay in zip(self.param_groups, (True, False)):
             out.append({"lr": g["lr"], "betas": tuple(g["betas"]), "eps": g["eps"], "weight_decay": g["weight_decay"],
-                        "params": names[decay]})
+                        # remaining torch.optim.AdamW group options, so the payload also loads into a stock optimizer
+                        "amsgrad": False, "maximize": False, "foreach": None, "capturable": False, "differentiable": False,
+                        "fused": None, "decoupled_weight_decay": True, "params": names[decay]})
         return out
 
     def adopt_groups(self, groups: list[dict[str, Any]]) -> None:

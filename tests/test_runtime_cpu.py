@@ -1,0 +1,196 @@
+"""Config composition, validation, batch scaling, LR schedule, precision policy, logger, monitoring (CPU only)."""
+
+import json
+import math
+from pathlib import Path
+
+import pytest
+import torch
+
+from mini_train_sys_b200.models import ModelConfig
+from mini_train_sys_b200.runtime import config as cfgmod
+from mini_train_sys_b200.runtime.logger import (JsonlLogger, balance_heatmap, build_event_logger, encode_png_rgb,
+                                                format_console_event)
+from mini_train_sys_b200.runtime.monitoring import (GpuUtilizationMonitor, distributed_gpu_utilization, distributed_mean,
+                                                    distributed_mean_tensors)
+from mini_train_sys_b200.runtime.scaling import resolve_batch_scale
+from mini_train_sys_b200.train.lr_scheduler import LearningRateScheduler, lr_scale, resolve_total_steps
+from mini_train_sys_b200.train.precision import resolve_precision_policy
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_every_shipped_run_and_model_yaml_loads():
+    models = runs = 0
+    for path in sorted((ROOT / "configs").rglob("*.yaml")):
+        payload = cfgmod.load_yaml_dict(path)      # every file, fragments included, must parse and resolve `extends`
+        if set(payload) == {"model"}:
+            ModelConfig(**payload["model"])
+            models += 1
+        elif path.parent.name == "runs" or path.name.startswith("train_") or path.name.endswith("_pretrain.yaml"):
+            payload.pop("model", None)
+            cfg = cfgmod.experiment_config_from_dict(payload)   # complete run files validate as a whole
+            assert cfg.parallel.strategy in ("single", "ddp", "fsdp")
+            runs += 1
+    assert models >= 7 and runs >= 10
+
+
+def test_extends_merges_in_order_and_detects_cycles(tmp_path):
+    (tmp_path / "base.yaml").write_text("train:\n  batch_size: 4\n  log_interval: 7\noptimizer:\n  lr: 0.1\n")
+    (tmp_path / "mid.yaml").write_text("extends: base.yaml\ntrain:\n  batch_size: 8\n")
+    (tmp_path / "top.yaml").write_text("extends: [mid.yaml]\noptimizer:\n  lr: 0.5\n")
+    merged = cfgmod.load_yaml_dict(tmp_path / "top.yaml")
+    assert merged == {"train": {"batch_size": 8, "log_interval": 7}, "optimizer": {"lr": 0.5}}
+    (tmp_path / "a.yaml").write_text("extends: b.yaml\n")
+    (tmp_path / "b.yaml").write_text("extends: a.yaml\n")
+    with pytest.raises(ValueError, match="cycle"):
+        cfgmod.load_yaml_dict(tmp_path / "a.yaml")
+
+
+@pytest.mark.parametrize("section,kwargs", [
+    (cfgmod.BackendConfig, {"ops": "jax"}), (cfgmod.ParallelConfig, {"strategy": "pp"}),
+    (cfgmod.FSDPConfig, {"sharding_strategy": "no_shard"}), (cfgmod.TrainConfig, {"max_steps": None, "epochs": None}),
+    (cfgmod.TrainConfig, {"batch_size_scaling": "linear"}), (cfgmod.CheckpointConfig, {"keep_safety": 1}),
+    (cfgmod.DataConfig, {"source": "tokens"}), (cfgmod.DataConfig, {"packing": "randomized_documents"}),
+    (cfgmod.LRSchedulerConfig, {"decay_steps": 10, "warmup_steps": 20}), (cfgmod.OptimizerConfig, {"name": "sgd"}),
+    (cfgmod.CommConfig, {"engine": "mpi"}), (cfgmod.DataConfig, {"num_workers": 0, "persistent_workers": True}),
+])
+def test_invalid_sections_are_rejected(section, kwargs):
+    with pytest.raises(ValueError):
+        section(**kwargs)
+
+
+def test_reference_backend_names_stay_valid_and_new_sections_default():
+    cfg = cfgmod.experiment_config_from_dict({"backend": {"ops": "triton"}, "parallel": {"strategy": "fsdp"}})
+    assert cfg.backend.ops == "triton" and cfg.parallel.comm.engine == "auto" and cfg.parallel.ep.capacity_factor is None
+
+
+def test_model_config_validation_and_counts():
+    with pytest.raises(ValueError):
+        ModelConfig(hidden_size=100, n_heads=12)
+    with pytest.raises(ValueError):
+        ModelConfig(ffn_type="moe", experts_per_token=9, num_experts=8)
+    payload = cfgmod.load_yaml_dict(ROOT / "configs" / "synbios_moe" / "model.yaml")["model"]
+    assert ModelConfig(**payload).param_count() == 293_494_272
+    dense = cfgmod.load_yaml_dict(ROOT / "configs" / "model_125m_dense.yaml")["model"]
+    assert ModelConfig(**dense).param_count() == 162_417_408
+
+
+def test_linear_batch_scaling():
+    train = cfgmod.TrainConfig(batch_size=24, reference_global_batch_size=96, batch_size_scaling="linear")
+    out = resolve_batch_scale(train, cfgmod.OptimizerConfig(lr=1e-3), cfgmod.LRSchedulerConfig(warmup_steps=1000, decay_steps=5000),
+                              world_size=8)
+    assert out.scale == 2.0 and out.optimizer.lr == pytest.approx(2e-3)
+    assert out.lr_scheduler.warmup_steps == 500 and out.lr_scheduler.decay_steps == 2500
+    none = resolve_batch_scale(cfgmod.TrainConfig(batch_size=24), cfgmod.OptimizerConfig(), cfgmod.LRSchedulerConfig(), world_size=8)
+    assert none.scale == 1.0 and none.global_batch_size == 192
+
+
+def test_lr_schedule_shape_and_state():
+    cfg = cfgmod.LRSchedulerConfig(schedule="cosine", warmup_steps=10, min_lr_ratio=0.1)
+    assert lr_scale(cfg, 0, 100) == pytest.approx(0.1)
+    assert lr_scale(cfg, 9, 100) == pytest.approx(1.0)
+    assert lr_scale(cfg, 10, 100) == pytest.approx(1.0)
+    assert lr_scale(cfg, 55, 100) == pytest.approx(0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * 0.5)))
+    assert lr_scale(cfg, 1000, 100) == pytest.approx(0.1)
+    assert lr_scale(cfgmod.LRSchedulerConfig(schedule="constant", warmup_steps=0), 5, 10) == 1.0
+    assert resolve_total_steps(max_steps=50, epochs=2, steps_per_epoch=10) == 20
+    with pytest.raises(ValueError):
+        resolve_total_steps(max_steps=None, epochs=None, steps_per_epoch=10)
+    opt = torch.optim.SGD([torch.zeros(1, requires_grad=True)], lr=2.0)
+    sched = LearningRateScheduler(opt, cfg, total_steps=100)
+    sched.step(9)
+    assert opt.param_groups[0]["lr"] == pytest.approx(2.0)
+    other = LearningRateScheduler(torch.optim.SGD([torch.zeros(1, requires_grad=True)], lr=2.0), cfg, total_steps=100)
+    other.load_state_dict(sched.state_dict())
+    assert other.get_last_lr() == sched.get_last_lr()
+
+
+def test_precision_policy_on_cpu():
+    pol = resolve_precision_policy("auto", torch.device("cpu"))
+    assert pol.name == "fp32" and not pol.autocast_enabled and not pol.grad_scaling_enabled
+    with pytest.raises(ValueError):
+        resolve_precision_policy("fp16", torch.device("cpu"))
+    with pytest.raises(ValueError):
+        resolve_precision_policy("fp8", torch.device("cpu"))
+
+
+def test_console_formatting_and_jsonl_sink(tmp_path):
+    line = format_console_event({"event": "train", "batch": 3, "batches_total": 10, "loss": 1.23456, "lr": 3e-4, "grad_norm": 0.5,
+                                 "tokens_per_sec": 1234.5, "progress_percent": 30.0, "eta_seconds": 3700})
+    assert line.startswith("[train] batch 3/10") and "loss 1.23456" in line and "ETA 1:01:40" in line
+    assert format_console_event({"event": "init", "run": "r", "device": "cpu", "parallel": "single", "world_size": 1, "params": 5}) \
+        == "[init] run=r device=cpu strategy=single world=1 params=5"
+    sink = JsonlLogger(tmp_path / "a" / "events.jsonl")
+    sink.log_event({"event": "x", "step": 1, "v": [1, 2]})
+    sink.close()
+    sink.close()
+    sink.log_event({"event": "ignored"})
+    assert json.loads((tmp_path / "a" / "events.jsonl").read_text().strip()) == {"event": "x", "step": 1, "v": [1, 2]}
+
+
+def test_png_encoder_and_balance_heatmap():
+    img = balance_heatmap(torch.tensor([[0.0, 0.125, 0.25], [0.125, 0.125, 0.125]]))
+    assert img.shape == (3, 2, 3) and float(img.min()) >= 0 and float(img.max()) <= 1
+    png = encode_png_rgb((img * 255).round().to(torch.uint8).permute(1, 2, 0).contiguous())
+    assert png[:8] == b"\x89PNG\r\n\x1a\n" and png[12:16] == b"IHDR" and png[-8:-4] == b"IEND"
+
+
+def test_logger_stack_respects_rank(monkeypatch, tmp_path):
+    monkeypatch.setenv("RANK", "1")
+    logger = build_event_logger(cfgmod.LoggingConfig(tensorboard=False, log_dir=str(tmp_path)), run_name="r")
+    assert type(logger).__name__ == "NullLogger"
+    monkeypatch.setenv("RANK", "0")
+    logger = build_event_logger(cfgmod.LoggingConfig(console=False, tensorboard=False, log_dir=str(tmp_path)), run_name="r")
+    logger.log_event({"event": "train", "step": 1})
+    logger.close()
+    assert len(list(tmp_path.rglob("events.jsonl"))) == 1
+
+
+class _FakeNvml:
+    class _Rates:
+        gpu, memory = 73.0, 41.0
+
+    def __init__(self):
+        self.shutdowns = 0
+
+    def nvmlInit(self):
+        pass
+
+    def nvmlDeviceGetCount(self):
+        return 2
+
+    def nvmlDeviceGetHandleByIndex(self, i):
+        return i
+
+    def nvmlDeviceGetUUID(self, h):
+        return [b"GPU-aaaa-1111", b"GPU-bbbb-2222"][h]
+
+    def nvmlDeviceGetUtilizationRates(self, h):
+        return self._Rates()
+
+    def nvmlShutdown(self):
+        self.shutdowns += 1
+
+
+def test_gpu_monitor_against_a_fake_nvml():
+    fake = _FakeNvml()
+    mon = GpuUtilizationMonitor(torch.device("cpu"), sample_interval_seconds=0.01, nvml=fake, device_uuid="GPU-BBBB-2222")
+    mon.start()
+    assert mon.available
+    import time
+
+    time.sleep(0.05)
+    stats = mon.read_interval()
+    mon.close()
+    assert stats["gpu_compute_utilization_percent_local_mean"] == 73.0 and stats["gpu_utilization_samples_local"] >= 2
+    assert fake.shutdowns == 1
+    merged = distributed_gpu_utilization(stats, torch.device("cpu"))
+    assert merged["gpu_utilization_available"] == 1 and merged["gpu_memory_controller_utilization_percent_max"] == 41.0
+    assert distributed_gpu_utilization({}, torch.device("cpu")) == {"gpu_utilization_available": 0}
+
+
+def test_single_process_reductions_are_identity():
+    assert distributed_mean({"b": 2.0, "a": 1.0}, torch.device("cpu")) == {"a": 1.0, "b": 2.0}
+    out = distributed_mean_tensors({"m": torch.arange(6.0).view(2, 3)}, torch.device("cpu"))
+    assert out == {"m": [[0.0, 1.0, 2.0], [3.0, 4.0, 5.0]]}
