@@ -117,6 +117,16 @@ __device__ __forceinline__ void store_row64(__nv_bfloat16* dst, const float (&v)
   }
 }
 
+// Optional phase trace of CTA (0, 0) of the forward kernel (build with -DMTS_ATTN_TRACE): slot 8*j+k of
+// g_attn_trace receives clock64() when the softmax warp (k = 0..5) or the MMA thread (slot 4096 + 8*j + k)
+// passes phase k of key tile j.  Compiled out by default.
+#ifdef MTS_ATTN_TRACE
+__device__ long long g_attn_trace[8192];
+#define MTS_TRACE(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) g_attn_trace[(slot)] = clock64(); } while (0)
+#else
+#define MTS_TRACE(slot) do { } while (0)
+#endif
+
 struct Params {
   __nv_bfloat16 *o, *dq, *dk, *dv;
   long long o_sb, o_sh, o_ss, dq_sb, dq_sh, dq_ss, dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
@@ -185,10 +195,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint32_t idesc_pv = make_idesc_bf16(128, 64, false, true);
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       bool ok = mbar_wait(&q_full, 0, abort_ptr);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int ik = 2 * j, iv = 2 * j + 1;
-        if (!mbar_wait(&slot_full[ik % 3], (ik / 3) & 1, abort_ptr)) break;
-        if (!mbar_wait(&s_free, (j & 1) ^ 1, abort_ptr)) break;
+      // S_j = Q K_j^T.  The softmax warps copy S into registers right away, so S_{j+1} is issued before
+      // waiting for P_j: the tensor core computes the next scores while the exponentials of tile j run.
+      auto issue_scores = [&](int j) -> bool {
+        const int ik = 2 * j;
+        if (!mbar_wait(&slot_full[ik % 3], (ik / 3) & 1, abort_ptr)) return false;
+        if (!mbar_wait(&s_free, (j & 1) ^ 1, abort_ptr)) return false;
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(sRing + (ik % 3) * TILE128);
 #pragma unroll
@@ -196,14 +208,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           umma_bf16_ss(tmem_s, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_s, kk != 0);
         umma_commit(&s_full);
         umma_commit(&slot_empty[ik % 3]);
+        return true;
+      };
+      ok = ok && issue_scores(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int iv = 2 * j + 1;
+        MTS_TRACE(4096 + 8 * j + 0);
+        if (j + 1 < n_kv && !issue_scores(j + 1)) break;
+        MTS_TRACE(4096 + 8 * j + 1);
         if (!mbar_wait(&p_ready, j & 1, abort_ptr)) break;
+        MTS_TRACE(4096 + 8 * j + 2);
         if (!mbar_wait(&slot_full[iv % 3], (iv / 3) & 1, abort_ptr)) break;
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(sRing + (iv % 3) * TILE128);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ss(tmem_pv, desc_kmajor(p_addr + (kk >> 2) * TILE128, kk & 3), desc_mnmajor(v_addr, kk), idesc_pv, kk != 0);
+          umma_bf16_ss(tmem_pv, desc_kmajor(p_addr + (kk >> 2) * TILE128, kk & 3), desc_mnmajor(v_addr, kk), idesc_pv, (j | kk) != 0);
         umma_commit(&pv_full);
+        MTS_TRACE(4096 + 8 * j + 3);
         umma_commit(&slot_empty[iv % 3]);
       }
     }
@@ -215,88 +237,115 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const float scale_log2 = p.scale * LOG2E;
     const Dropout drop = make_dropout(p.dropout_p, p.seed, uint32_t(bh), p.S);
+    // Running maximum m (log2 units, may lag the true maximum by up to kRescaleSlack), running sum l.
+    // O stays in tensor memory: every P V MMA accumulates into it, and it is only read back and rescaled when
+    // the maximum of some row of this warp moved by more than the slack (stale maxima keep exp2 arguments
+    // below 2^slack, which fp32 sums and bf16 probabilities hold without loss).
+    constexpr float kRescaleSlack = 8.f;
     float m = -CUDART_INF_F, l = 0.f;
-    float o[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait(&s_full, j & 1, abort_ptr)) { ok = false; break; }
+      if (!mbar_wait_warp(&s_full, j & 1, abort_ptr, lane)) { ok = false; break; }
+      if (warp == 2) MTS_TRACE(8 * j + 0);
       tc_fence_after_sync();
       const int k0 = j * 128;
       const bool need_mask = (p.causal && k0 + 127 > q0) || (k0 + 128 > p.S);
+      // the whole 128-column row in one TMEM round trip
+      uint32_t s0[32], s1[32], s2[32], s3[32];
+      tmem_ld_32x32(tmem_s + lane_base, s0);
+      tmem_ld_32x32(tmem_s + lane_base + 32, s1);
+      tmem_ld_32x32(tmem_s + lane_base + 64, s2);
+      tmem_ld_32x32(tmem_s + lane_base + 96, s3);
+      tmem_ld_wait();
+      epilogue_arrive(&s_free, lane);            // S is in registers: the next Q K^T may overwrite it
+      if (warp == 2) MTS_TRACE(8 * j + 1);
       float mx = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32(tmem_s + lane_base + c * 32, rr);
-        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(rr[i]);
-          if (need_mask) {
-            const int kidx = k0 + c * 32 + i;
-            if (kidx >= p.S || (p.causal && kidx > q_row)) v = -CUDART_INF_F;
+      for (int i = 0; i < 32; ++i) {
+        float v0 = __uint_as_float(s0[i]), v1 = __uint_as_float(s1[i]), v2 = __uint_as_float(s2[i]), v3 = __uint_as_float(s3[i]);
+        if (need_mask) {
+          const int kidx = k0 + i;
+          if (kidx >= p.S || (p.causal && kidx > q_row)) v0 = -CUDART_INF_F;
+          if (kidx + 32 >= p.S || (p.causal && kidx + 32 > q_row)) v1 = -CUDART_INF_F;
+          if (kidx + 64 >= p.S || (p.causal && kidx + 64 > q_row)) v2 = -CUDART_INF_F;
+          if (kidx + 96 >= p.S || (p.causal && kidx + 96 > q_row)) v3 = -CUDART_INF_F;
+          s0[i] = __float_as_uint(v0); s1[i] = __float_as_uint(v1); s2[i] = __float_as_uint(v2); s3[i] = __float_as_uint(v3);
+        }
+        mx = fmaxf(mx, fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)));
+      }
+      const float m_tile = mx * scale_log2;
+      float alpha = 1.f;
+      bool grow = false;
+      if (j == 0) {
+        m = m_tile == -CUDART_INF_F ? 0.f : m_tile;
+      } else {
+        // previous P V must be complete: its P tile is about to be overwritten and O may be rescaled
+        if (!mbar_wait_warp(&pv_full, (j - 1) & 1, abort_ptr, lane)) { ok = false; break; }
+        tc_fence_after_sync();
+        grow = m_tile > m + kRescaleSlack;
+        if (__any_sync(0xffffffffu, grow)) {
+          if (grow) { alpha = ex2(m - m_tile); m = m_tile; l *= alpha; }
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {          // rare path: narrow chunks keep the register footprint small
+            uint32_t oo[16];
+            tmem_ld_32x16(tmem_pv + lane_base + c * 16, oo);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) oo[i] = __float_as_uint(__uint_as_float(oo[i]) * alpha);
+            tmem_st_32x16(tmem_pv + lane_base + c * 16, oo);
           }
-          mx = fmaxf(mx, v);
+          tmem_st_wait();
         }
       }
-      const float m_new = fmaxf(m, mx * scale_log2);
-      const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
-      const float alpha = ex2(m - m_use);
       float rowsum = 0.f;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32(tmem_s + lane_base + c * 32, rr);
-        tmem_ld_wait();
-        float pv[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kidx = k0 + c * 32 + i;
-          float e = ex2(__uint_as_float(rr[i]) * scale_log2 - m_use);
-          if (need_mask && (kidx >= p.S || (p.causal && kidx > q_row))) e = 0.f;
-          rowsum += e;
-          pv[i] = e;
-        }
-        if (drop.thresh != 0u) {
-#pragma unroll
-          for (int w = 0; w < 8; ++w) {
-            const uint32_t bits = drop.word(uint32_t(q_row), uint32_t(k0 + c * 32 + 4 * w) >> 2);
-#pragma unroll
-            for (int t = 0; t < 4; ++t)
-              pv[4 * w + t] = ((bits >> (8 * t)) & 0xFFu) >= drop.thresh ? pv[4 * w + t] * drop.inv_keep : 0.f;
-          }
-        }
+        uint32_t (&rr)[32] = c == 0 ? s0 : (c == 1 ? s1 : (c == 2 ? s2 : s3));
         uint8_t* half = sP + (c >> 1) * TILE128;
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
+        for (int g = 0; g < 4; ++g) {            // eight probabilities at a time: exp, dropout, pack, store
+          float e[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            e[i] = ex2(__uint_as_float(rr[8 * g + i]) * scale_log2 - m);   // masked entries are -inf -> 0
+            rowsum += e[i];
+          }
+          if (drop.thresh != 0u) {
+#pragma unroll
+            for (int w = 0; w < 2; ++w) {
+              const uint32_t bits = drop.word(uint32_t(q_row), uint32_t(k0 + c * 32 + 8 * g + 4 * w) >> 2);
+#pragma unroll
+              for (int t = 0; t < 4; ++t)
+                e[4 * w + t] = ((bits >> (8 * t)) & 0xFFu) >= drop.thresh ? e[4 * w + t] * drop.inv_keep : 0.f;
+            }
+          }
           uint4 q4;
-          q4.x = pack2(pv[8 * g + 0], pv[8 * g + 1]); q4.y = pack2(pv[8 * g + 2], pv[8 * g + 3]);
-          q4.z = pack2(pv[8 * g + 4], pv[8 * g + 5]); q4.w = pack2(pv[8 * g + 6], pv[8 * g + 7]);
+          q4.x = pack2(e[0], e[1]); q4.y = pack2(e[2], e[3]); q4.z = pack2(e[4], e[5]); q4.w = pack2(e[6], e[7]);
           st_swizzled(half, r, (c & 1) * 4 + g, q4);
         }
       }
-      epilogue_arrive(&s_free, lane);            // S may be overwritten by the next Q K^T
-      l = l * alpha + rowsum;
-      m = m_new;
+      l += rowsum;
+      if (warp == 2) MTS_TRACE(8 * j + 2);
       fence_proxy_async_smem();                  // P (generic-proxy stores) -> visible to the tensor core
       epilogue_arrive(&p_ready, lane);
-      if (!mbar_wait(&pv_full, j & 1, abort_ptr)) { ok = false; break; }
+      if (warp == 2) MTS_TRACE(8 * j + 3);
+    }
+    if (ok && mbar_wait_warp(&pv_full, (n_kv - 1) & 1, abort_ptr, lane)) {
       tc_fence_after_sync();
+      float o[64];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t rr[32];
         tmem_ld_32x32(tmem_pv + lane_base + c * 32, rr);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(rr[i]);
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(rr[i]);
       }
-    }
-    if (ok && q_row < p.S) {
-      const float inv_l = l > 0.f ? 1.f / l : 0.f;
-      store_row64(p.o + (long long)b * p.o_sb + (long long)h * p.o_sh + (long long)q_row * p.o_ss, o, inv_l);
-      p.lse[((long long)bh) * p.S + q_row] = (m + log2f(l)) * LN2;
+      if (q_row < p.S) {
+        const float inv_l = l > 0.f ? 1.f / l : 0.f;
+        store_row64(p.o + (long long)b * p.o_sb + (long long)h * p.o_sh + (long long)q_row * p.o_ss, o, inv_l);
+        p.lse[((long long)bh) * p.S + q_row] = (m + log2f(l)) * LN2;
+      }
     }
   }
 
@@ -421,9 +470,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
         lse_reg[c] = qi < p.S ? lse_bh[qi] * LOG2E : 0.f;
         delta_reg[c] = qi < p.S ? delta_bh[qi] : 0.f;
       }
-      if (!mbar_wait(&st_full, i & 1, abort_ptr)) { ok = false; break; }
+      if (!mbar_wait_warp(&st_full, i & 1, abort_ptr, lane)) { ok = false; break; }
       tc_fence_after_sync();
-      if (!mbar_wait(&pds_free, (i & 1) ^ 1, abort_ptr)) { ok = false; break; }
+      if (!mbar_wait_warp(&pds_free, (i & 1) ^ 1, abort_ptr, lane)) { ok = false; break; }
       const bool need_mask = (p.causal && qbase < k0 + 127) || (qbase + 64 > p.S) || (k0 + 128 > p.S);
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
@@ -464,7 +513,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
       fence_proxy_async_smem();
       epilogue_arrive(&pds_ready, lane);
     }
-    if (ok && mbar_wait(&acc_full, 0, abort_ptr)) {
+    if (ok && mbar_wait_warp(&acc_full, 0, abort_ptr, lane)) {
       tc_fence_after_sync();
       float acc[64];
 #pragma unroll
@@ -594,9 +643,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     bool ok = true;
     for (int i = 0; i < n_iter; ++i) {
       const int kbase = i * 64;
-      if (!mbar_wait(&st_full, i & 1, abort_ptr)) { ok = false; break; }
+      if (!mbar_wait_warp(&st_full, i & 1, abort_ptr, lane)) { ok = false; break; }
       tc_fence_after_sync();
-      if (!mbar_wait(&ds_free, (i & 1) ^ 1, abort_ptr)) { ok = false; break; }
+      if (!mbar_wait_warp(&ds_free, (i & 1) ^ 1, abort_ptr, lane)) { ok = false; break; }
       const bool need_mask = (p.causal && kbase + 63 > q0) || (kbase + 64 > p.S) || (q0 + 128 > p.S);
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
@@ -639,7 +688,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       fence_proxy_async_smem();
       epilogue_arrive(&ds_ready, lane);
     }
-    if (ok && mbar_wait(&acc_full, 0, abort_ptr)) {
+    if (ok && mbar_wait_warp(&acc_full, 0, abort_ptr, lane)) {
       tc_fence_after_sync();
       float acc[64];
 #pragma unroll
@@ -819,6 +868,12 @@ cudaError_t launch_flash_bwd(const AttentionArgs& a) {
   g_launch_count += 3;
   return cudaGetLastError();
 }
+
+#ifdef MTS_ATTN_TRACE
+cudaError_t copy_attention_trace(long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(long long) * n);
+}
+#endif
 
 cudaError_t launch_dropout_keep_mask(unsigned char* keep, int BH, int S, float dropout_p, unsigned long long seed,
                                      cudaStream_t stream) {

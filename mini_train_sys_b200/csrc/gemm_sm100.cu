@@ -348,7 +348,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       const int buf = acc_it & 1;
       const uint32_t acc_ph = (acc_it >> 1) & 1;
-      if (!mbar_wait(&acc_full[buf], acc_ph, abort_ptr)) { ok = false; break; }
+      if (!mbar_wait_warp(&acc_full[buf], acc_ph, abort_ptr, lane)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * ACC_COLS;
 

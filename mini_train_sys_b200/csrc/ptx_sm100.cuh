@@ -78,7 +78,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_test(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
+    if (++spins > 8) __nanosleep(32);   // back off: a spinning waiter must not take issue slots from working warps
+    if ((spins & 0x3ff) == 0) {
       if (*abort_word != 0) return false;
       if (global_timer_ns() - t0 > kWaitDeadlineNs) {
         *abort_word = STATUS_WAIT_TIMEOUT;
@@ -87,6 +88,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
   }
   return true;
+}
+
+// Warp-wide form: lane 0 polls, the other lanes park at the warp barrier and receive the verdict.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_word, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_word) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ---- TMA ------------------------------------------------------------------------------------
@@ -212,6 +220,20 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r
       :
       : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// 32 lanes x 32 columns store (registers -> TMEM): thread i writes lane (base_lane + i), columns c..c+31.
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
 

@@ -72,6 +72,7 @@ class TopKRouter(nn.Module):
         self.weight = nn.Parameter(torch.empty(cfg.num_experts, cfg.hidden_size))
         nn.init.normal_(self.weight, mean=0.0, std=0.02)
         self.enforce_capacity = False
+        self.drop_overflow_routes = False   # expert parallelism: mark dropped routes with index -1 so they are not sent
 
     def forward(self, hidden_states: torch.Tensor, ops: OpsBackend) -> RouterOutput:
         cfg = self.cfg
@@ -104,6 +105,8 @@ class TopKRouter(nn.Module):
                     weights = torch.where(denom > 0, weights / denom.clamp_min(torch.finfo(weights.dtype).eps), weights)
                 dropped = 1.0 - keep.float().mean()
                 counts = torch.bincount(indices[keep].long(), minlength=n_exp).float()
+                if self.drop_overflow_routes:
+                    indices = torch.where(keep, indices, torch.full_like(indices, -1))
 
             load = counts / max(n_routes, 1)
             uniform = 1.0 / n_exp

@@ -50,7 +50,9 @@ class TorchCollectives:
     # grad_full: [total] fp32 -> grad_shard: [total / world] fp32, mean over ranks; returns sum of squares (tensor)
     def reduce_scatter(self, unit, epoch: int) -> None:
         shard = unit.shard_numel
-        if self.world > 1:
+        if unit.local:
+            unit.grad_shard.copy_(unit.grad_full.tensor).mul_(1.0 / self.world)
+        elif self.world > 1:
             if dist.get_backend() == "nccl":
                 dist.reduce_scatter_tensor(unit.grad_shard, unit.grad_full.tensor, op=dist.ReduceOp.SUM)
                 unit.grad_shard.mul_(1.0 / self.world)
@@ -86,7 +88,7 @@ class TorchCollectives:
         """Make the low-precision replica of ``unit`` reflect the fp32 shards of every rank."""
 
         low = unit.master.to(unit.gathered.tensor.dtype)
-        if self.world > 1:
+        if self.world > 1 and not unit.local:
             dist.all_gather_into_tensor(unit.gathered.tensor, low)
         else:
             unit.gathered.tensor.copy_(low)
@@ -145,12 +147,13 @@ class PeerCollectives:
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ready)
             channel = self.CH_UNIT0 + unit.index
-            wait_epoch = epoch if self.world > 1 else 0
-            if self.world > 1:
+            shared = self.world > 1 and not unit.local
+            if shared:
                 self.ext.comm_signal(self.flags.peer_ptrs, channel, self.rank, epoch, unit.grad_shard)
+            # rank-local units read only their own buffer (one pointer) but still take the 1 / world of the global mean
             self.ext.comm_reduce_scatter(unit.grad_shard, unit.grad_full.peer_ptrs, unit.grad_full.multicast_ptr,
-                                         self.rank * unit.shard_numel, 1.0 / self.world, unit.sumsq, self.flags.tensor,
-                                         channel, wait_epoch, self.timeout_ms, self.status, self.max_ctas)
+                                         unit.rank * unit.shard_numel, 1.0 / self.world, unit.sumsq, self.flags.tensor,
+                                         channel, epoch if shared else 0, self.timeout_ms, self.status, self.max_ctas)
 
     def norm_and_clip(self, sumsq: torch.Tensor, max_norm: float | None, epoch: int, coef: torch.Tensor,
                       norm: torch.Tensor) -> None:
@@ -163,7 +166,7 @@ class PeerCollectives:
         lo, hi = seg
         low_bf16 = unit.gathered.tensor.dtype == torch.bfloat16
         self.ext.comm_adamw_push(unit.master[lo:hi], unit.grad_shard[lo:hi], unit.exp_avg[lo:hi], unit.exp_avg_sq[lo:hi],
-                                 unit.gathered.peer_ptrs, self.rank * unit.shard_numel + lo, low_bf16, lr, beta1, beta2,
+                                 unit.gathered.peer_ptrs, unit.rank * unit.shard_numel + lo, low_bf16, lr, beta1, beta2,
                                  eps, weight_decay, step, coef, 1.0, self.max_ctas * 4)
 
     def refresh_replicas(self, unit, epoch: int) -> None:
@@ -171,6 +174,9 @@ class PeerCollectives:
 
         low = unit.low_shard
         low.tensor[:unit.shard_numel].copy_(unit.master.to(low.tensor.dtype))
+        if unit.local:
+            unit.gathered.tensor[:unit.shard_numel].copy_(low.tensor[:unit.shard_numel])
+            return
         if self.world > 1:
             torch.cuda.synchronize(self.device)
             dist.barrier(device_ids=[self.device.index])   # start-up / restore path only

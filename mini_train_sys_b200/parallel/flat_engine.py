@@ -68,6 +68,9 @@ class Unit:
     low_shard: SymBuffer = None     # low precision [shard]; source of pull all-gathers
     sumsq: torch.Tensor = None
     pending: int = 0
+    local: bool = False             # rank-local parameters (expert shards): never reduced across ranks, scaled by 1 / world
+    world: int = 1                  # number of ranks sharing this unit (1 for local units)
+    rank: int = 0
     segments: list[tuple[int, int, bool]] = field(default_factory=list)   # (lo, hi, decay) inside the local shard
 
 
@@ -75,8 +78,24 @@ def _round_up(n: int, m: int) -> int:
     return -(-n // m) * m
 
 
-def _partition(model: nn.Module, mode: str, per_block_units: bool, bucket_bytes: int) -> list[tuple[str, list[tuple[str, nn.Parameter]]]]:
-    named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+def _partition(model: nn.Module, mode: str, per_block_units: bool, bucket_bytes: int, local_names: frozenset[str] = frozenset()
+               ) -> list[tuple[str, list[tuple[str, nn.Parameter]]]]:
+    """Units as ``(name, [(param name, param)])``; names starting with ``local:`` hold rank-local parameters."""
+
+    everything = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+    named = [(n, p) for n, p in everything if n not in local_names]
+    local = [(n, p) for n, p in everything if n in local_names]
+    if local:
+        groups: dict[str, list] = {}
+        for n, p in local:
+            key = ".".join(n.split(".")[:2]) if n.startswith("blocks.") else "root"
+            groups.setdefault(f"local:{key}", []).append((n, p))
+        shared = _partition_shared(model, named, mode, per_block_units, bucket_bytes)
+        return shared + list(groups.items())
+    return _partition_shared(model, named, mode, per_block_units, bucket_bytes)
+
+
+def _partition_shared(model: nn.Module, named, mode: str, per_block_units: bool, bucket_bytes: int):
     frozen = [n for n, p in model.named_parameters() if not p.requires_grad]
     if frozen:
         raise ValueError(f"the flat engine expects every parameter to be trainable; frozen: {frozen[:3]}...")
@@ -106,7 +125,8 @@ def _partition(model: nn.Module, mode: str, per_block_units: bool, bucket_bytes:
 class FlatDataParallel(nn.Module):
     def __init__(self, module: nn.Module, *, mode: str = "shard", comm: Any = None, bucket_cap_mb: int = 25,
                  reshard_after_forward: bool = True, per_block_units: bool = True,
-                 activation_checkpointing: bool = False, collectives: Any = None) -> None:
+                 activation_checkpointing: bool = False, collectives: Any = None,
+                 local_params: list[str] | None = None) -> None:
         super().__init__()
         if mode not in ("shard", "replicate"):
             raise ValueError("mode must be 'shard' or 'replicate'")
@@ -120,7 +140,7 @@ class FlatDataParallel(nn.Module):
         act = getattr(module, "activation_dtype", torch.float32)
         self.param_dtype = act if (self.device.type == "cuda" and act in (torch.bfloat16,)) else torch.float32
 
-        layout = _partition(module, mode, per_block_units, bucket_cap_mb * 2**20)
+        layout = _partition(module, mode, per_block_units, bucket_cap_mb * 2**20, frozenset(local_params or ()))
         if collectives is None:
             engine = getattr(comm, "engine", "auto") if comm is not None else "auto"
             want_fused = self.device.type == "cuda" and engine in ("auto", "fused") and self.param_dtype == torch.bfloat16
@@ -151,10 +171,12 @@ class FlatDataParallel(nn.Module):
             slots.append(ParamSlot(pname, p, offset, p.numel(), p.shape, p.ndim >= 2))
             offset += _round_up(p.numel(), ALIGN)
         unit = Unit(index, name, slots)
-        unit.total = _round_up(offset, self.world * 64)
-        unit.shard_numel = unit.total // self.world
+        unit.local = name.startswith("local:")
+        unit.world, unit.rank = (1, 0) if unit.local else (self.world, self.rank)
+        unit.total = _round_up(offset, unit.world * 64)
+        unit.shard_numel = unit.total // unit.world
         dev, f32 = self.device, torch.float32
-        lo, hi = self.rank * unit.shard_numel, (self.rank + 1) * unit.shard_numel
+        lo, hi = unit.rank * unit.shard_numel, (unit.rank + 1) * unit.shard_numel
         flat = torch.zeros(unit.total, dtype=f32, device=dev)
         for s in slots:
             flat[s.offset:s.offset + s.numel].copy_(s.param.detach().reshape(-1).float())
@@ -163,9 +185,10 @@ class FlatDataParallel(nn.Module):
         unit.exp_avg = torch.zeros(unit.shard_numel, dtype=f32, device=dev)
         unit.exp_avg_sq = torch.zeros(unit.shard_numel, dtype=f32, device=dev)
         unit.grad_shard = torch.zeros(unit.shard_numel, dtype=f32, device=dev)
-        unit.grad_full = self.coll.alloc(unit.total, f32, shared=True)
-        unit.gathered = self.coll.alloc(unit.total, self.param_dtype, shared=True)
-        unit.low_shard = self.coll.alloc(unit.shard_numel, self.param_dtype, shared=True)
+        shared = not unit.local
+        unit.grad_full = self.coll.alloc(unit.total, f32, shared=shared)
+        unit.gathered = self.coll.alloc(unit.total, self.param_dtype, shared=shared)
+        unit.low_shard = self.coll.alloc(unit.shard_numel, self.param_dtype, shared=shared)
         unit.sumsq = self.sumsq
         # weight-decay segments: intersections of the parameters with the local shard
         for s in slots:
@@ -227,8 +250,8 @@ class FlatDataParallel(nn.Module):
         return ShardedAdamW(self, cfg)
 
     # ---- state dicts ------------------------------------------------------------------------------------
-    def _full_flat(self, shard: torch.Tensor) -> torch.Tensor:
-        if self.world == 1:
+    def _full_flat(self, shard: torch.Tensor, unit: "Unit | None" = None) -> torch.Tensor:
+        if self.world == 1 or (unit is not None and unit.local):
             return shard
         full = torch.empty(shard.numel() * self.world, dtype=shard.dtype, device=shard.device)
         dist.all_gather_into_tensor(full, shard.contiguous())
@@ -241,13 +264,15 @@ class FlatDataParallel(nn.Module):
             self._device_mesh = init_device_mesh(self.device.type, (self.world,))
         return self._device_mesh
 
-    def _as_sharded(self, full: torch.Tensor, cpu_offload: bool):
+    def _as_sharded(self, full: torch.Tensor, cpu_offload: bool, local: bool = False):
         if cpu_offload and self.world == 1:
             return full.cpu()
         if self.world == 1:
             return full.clone()
-        from torch.distributed.tensor import Shard, distribute_tensor
+        from torch.distributed.tensor import DTensor, Shard, distribute_tensor
 
+        if local:   # this rank's slice along dim 0 of a tensor that no rank holds in full (expert shards)
+            return DTensor.from_local(full.contiguous().clone(), self._mesh(), [Shard(0)], run_check=False)
         return distribute_tensor(full.contiguous(), self._mesh(), [Shard(0)])
 
     def sharded_state_dict(self, optimizer: "ShardedAdamW", *, cpu_offload: bool = True):
@@ -256,13 +281,13 @@ class FlatDataParallel(nn.Module):
         model_state: dict[str, Any] = {}
         opt_state: dict[str, Any] = {}
         for unit in self.units:
-            flats = {k: self._full_flat(t) for k, t in (("p", unit.master), ("m", unit.exp_avg), ("v", unit.exp_avg_sq))}
+            flats = {k: self._full_flat(t, unit) for k, t in (("p", unit.master), ("m", unit.exp_avg), ("v", unit.exp_avg_sq))}
             for s in unit.slots:
                 pick = lambda key: flats[key][s.offset:s.offset + s.numel].view(s.shape)  # noqa: E731
-                model_state[s.name] = self._as_sharded(pick("p"), cpu_offload)
+                model_state[s.name] = self._as_sharded(pick("p"), cpu_offload, unit.local)
                 opt_state[s.name] = {"step": torch.tensor(float(self.step_count)),
-                                     "exp_avg": self._as_sharded(pick("m"), cpu_offload),
-                                     "exp_avg_sq": self._as_sharded(pick("v"), cpu_offload)}
+                                     "exp_avg": self._as_sharded(pick("m"), cpu_offload, unit.local),
+                                     "exp_avg_sq": self._as_sharded(pick("v"), cpu_offload, unit.local)}
         # tied parameters appear under every name a plain model's state dict uses
         owner = {id(p): n for n, p in self.module.named_parameters()}
         for alias, p in self.module.named_parameters(remove_duplicate=False):
@@ -277,13 +302,16 @@ class FlatDataParallel(nn.Module):
 
     @torch.no_grad()
     def load_sharded_state_dict(self, model_state, optim_state, optimizer: "ShardedAdamW | None" = None) -> None:
-        def full(t):
+        def full(t, slot=None, local=False):
             t = t.full_tensor() if hasattr(t, "full_tensor") else t
+            if local and t.shape[0] != slot.shape[0]:   # a full [E, ...] tensor: keep this rank's experts
+                per = slot.shape[0]
+                t = t[self.rank * per:(self.rank + 1) * per]
             return t.to(self.device, torch.float32).reshape(-1)
 
         steps = []
         for unit in self.units:
-            lo, hi = self.rank * unit.shard_numel, (self.rank + 1) * unit.shard_numel
+            lo, hi = unit.rank * unit.shard_numel, (unit.rank + 1) * unit.shard_numel
             for key, dst in (("p", unit.master), ("m", unit.exp_avg), ("v", unit.exp_avg_sq)):
                 flat = torch.zeros(unit.total, dtype=torch.float32, device=self.device)
                 for s in unit.slots:
@@ -296,7 +324,7 @@ class FlatDataParallel(nn.Module):
                         src = entry["exp_avg" if key == "m" else "exp_avg_sq"]
                         if key == "m" and "step" in entry:
                             steps.append(float(entry["step"]))
-                    flat[s.offset:s.offset + s.numel].copy_(full(src))
+                    flat[s.offset:s.offset + s.numel].copy_(full(src, s, unit.local))
                 dst.copy_(flat[lo:hi])
         if steps:
             self.step_count = int(max(steps))
@@ -310,9 +338,14 @@ class FlatDataParallel(nn.Module):
 
         out: dict[str, torch.Tensor] = {}
         for unit in self.units:
-            flat = self._full_flat(unit.master)
+            flat = self._full_flat(unit.master, unit)
             for s in unit.slots:
-                out[s.name] = flat[s.offset:s.offset + s.numel].view(s.shape).detach().cpu().clone()
+                value = flat[s.offset:s.offset + s.numel].view(s.shape).detach()
+                if unit.local and self.world > 1:
+                    parts = [torch.empty_like(value) for _ in range(self.world)]
+                    dist.all_gather(parts, value.contiguous())
+                    value = torch.cat(parts, dim=0)
+                out[s.name] = value.cpu().clone()
         by_param = {id(p): n for n, p in self.module.named_parameters()}
         for name, p in self.module.named_parameters(remove_duplicate=False):
             if name not in out and id(p) in by_param:
