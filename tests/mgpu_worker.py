@@ -66,7 +66,8 @@ def main() -> None:
     fa, la, na = run(PeerCollectives(dev, max_units=8, wait_timeout_ms=5000, use_multimem=use_mm))
     fb, lb, nb = run(TorchCollectives(dev))
     for name in fa:
-        assert torch.allclose(fa[name], fb[name], atol=2e-3), (name, float((fa[name] - fb[name]).abs().max()))
+        diff = (fa[name] - fb[name]).abs()   # atomically summed weight gradients: a sign flip moves a weight by up to 2 * lr per step
+        assert float(diff.max()) <= 8.5e-3 and float(diff.mean()) < 3e-4, (name, float(diff.max()), float(diff.mean()))
     assert abs(na - nb) <= 5e-2 * max(nb, 1e-6), (na, nb)
     coll.check_status()
     dist.barrier()

@@ -45,8 +45,11 @@ def test_fused_engine_matches_library_collectives():
     assert loss_a == pytest.approx(loss_b, abs=2e-2)
     assert norm_a == pytest.approx(norm_b, rel=5e-2)
     fa, fb = eng_a.full_state_dict(), eng_b.full_state_dict()
+    # split-K weight gradients are summed with fp32 atomics, so two runs differ in rounding; an AdamW step moves a
+    # weight by at most lr, hence two runs of 4 steps at lr 1e-3 can sit 8e-3 apart where a tiny gradient flips sign
     for name in fa:
-        assert torch.allclose(fa[name], fb[name], atol=2e-3), name
+        diff = (fa[name] - fb[name]).abs()
+        assert float(diff.max()) <= 8.5e-3 and float(diff.mean()) < 3e-4, (name, float(diff.max()), float(diff.mean()))
     check_kernel_status()
 
 
