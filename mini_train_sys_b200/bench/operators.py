@@ -73,7 +73,7 @@ def build_case(kernel: str, profile: OperatorProfile, tokens: int) -> BenchCase:
         def make(d):
             from mini_train_sys_b200.models.rotary import RotaryEmbedding
 
-            rot = RotaryEmbedding(p.head_dim, s, 10000.0, dtype=_ACT).to(d)
+            rot = RotaryEmbedding(p.head_dim, s, 10000.0, cache_dtype=_ACT).to(d)
             cos, sin = rot(s)
             return {"q": _randn((b, p.heads, s, p.head_dim), d), "k": _randn((b, p.heads, s, p.head_dim), d), "cos": cos, "sin": sin}
         return BenchCase(kernel, label, make, lambda ops, a: ops.rope(a["q"], a["k"], a["cos"], a["sin"]), t,
@@ -126,7 +126,7 @@ def worker(kernel: str, profile_name: str, tokens: int, providers: list[str], *,
     case = build_case(kernel, PROFILES[profile_name], tokens)
     backends = {name: get_ops_backend(name) for name in providers}
     gate = (1e-2, 0.9999) if kernel == "fused_moe" else None
-    with torch.autocast(device.type, dtype=_ACT, enabled=device.type == "cuda"):
+    with torch.autocast(device.type, dtype=_ACT):
         rows = bench_sweep([case], backends, device, warmup=warmup, iters=iters, check=check, relative_gate=gate)
     for row in rows:
         ops = backends[row["provider"]]

@@ -1,0 +1,123 @@
+"""Benchmark harness on CPU: parity statistics, operator worker, Nsight command builder, distributed suites over Gloo."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_close_stats_streams_and_flags_violations():
+    from mini_train_sys_b200.bench.measurement import close_stats
+
+    a = torch.linspace(-1, 1, 10_000)
+    ok = close_stats(a + 1e-4, a, atol=1e-3, rtol=0.0)
+    assert ok["passed"] and ok["max_abs"] == pytest.approx(1e-4, rel=1e-2) and ok["cosine"] > 0.999999
+    b = a.clone(); b[17] += 1.0
+    bad = close_stats(b, a, atol=1e-3, rtol=0.0)
+    assert not bad["passed"] and bad["violations"] == 1
+    assert not close_stats(torch.tensor([float("nan")]), torch.tensor([0.0]), atol=1.0, rtol=0.0)["passed"]
+
+
+@pytest.mark.parametrize("kernel", ["rmsnorm", "swiglu", "rope", "attention", "cross_entropy", "fused_linear_cross_entropy", "router", "fused_moe"])
+def test_operator_cases_agree_between_library_and_oracle_back_ends(kernel):
+    from mini_train_sys_b200.bench.measurement import correctness_stats
+    from mini_train_sys_b200.bench.operators import OperatorProfile, build_case
+    from mini_train_sys_b200.models import get_ops_backend
+
+    prof = OperatorProfile("tiny", hidden=64, intermediate=96, heads=2, head_dim=32, vocab=257, seq_len=16, experts=4, top_k=2)
+    case = build_case(kernel, prof, 64)
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        stats = correctness_stats(case, get_ops_backend("torch"), get_ops_backend("reference"), torch.device("cpu"),
+                                  relative_gate=(2e-2, 0.999))
+    assert stats["passed"], stats
+
+
+def test_bench_ops_worker_cli_runs_on_cpu():
+    out = subprocess.run([sys.executable, str(ROOT / "scripts" / "bench_ops.py"), "_worker", "--kernel", "swiglu", "--profile",
+                          "project_formal", "--tokens", "512", "--providers", "torch,reference", "--warmup", "1", "--iters", "3"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    rec = json.loads(out.stdout.strip().splitlines()[-1])
+    assert rec["status"] == "ok" and {r["provider"] for r in rec["rows"]} == {"torch", "reference"}
+    ref_row = next(r for r in rec["rows"] if r["provider"] == "reference")
+    assert ref_row["correctness"]["passed"] and ref_row["full"]["p50_ms"] > 0
+
+
+def test_nsight_commands_always_leave_clocks_alone_and_stay_small():
+    from mini_train_sys_b200.bench import nsight
+
+    for name in nsight.registered():
+        line = nsight.command_for(name, "scripts/bench_ops.py", mode="full", output="x")
+        assert "--clock-control none" in line and " && ncu " in line and "-c 3" in line
+    with pytest.raises(ValueError):
+        nsight.build_command(["x.py"], mode="full", kernel_regex="k", count=50)
+    with pytest.raises(ValueError):
+        nsight.build_command(["x.py"], mode="full")
+    cmd = nsight.build_command(["x.py"], mode="launches", output="l.csv")
+    assert cmd[:3] == ["ncu", "--clock-control", "none"] and "gpu__time_duration.sum" in cmd
+
+
+def test_nsight_parsers():
+    from mini_train_sys_b200.bench import nsight
+
+    raw = '"ID","Kernel Name","gpu__time_duration.sum","dram__bytes_read.sum"\n"","","us","Mbyte"\n"0","k(int)","12.5","100"\n'
+    rows = nsight.parse_raw_csv(raw)
+    assert rows[0]["Kernel Name"] == "k(int)" and rows[0]["gpu__time_duration.sum [us]"] == "12.5"
+    assert "duration" in nsight.roofline_summary(rows)
+    listing = ('==PROF== x\n"ID","Process ID","Kernel Name","Metric Name","Metric Unit","Metric Value"\n'
+               '"0","1","a(int)","gpu__time_duration.sum","ns","3000"\n"1","1","b()","gpu__time_duration.sum","ns","1000"\n'
+               '"2","1","a(int)","gpu__time_duration.sum","ns","1000"\n')
+    shares = nsight.launch_shares(nsight.parse_launch_list(listing))
+    assert shares[0][0] == "a" and shares[0][1] == 2 and shares[0][3] == pytest.approx(0.8)
+
+
+def _rows(world, tps, batch=8, status="ok", ops="torch", dispatch=None):
+    return {"status": status, "strategy": "fsdp", "engine": "nccl", "ops": ops, "batch_size": batch, "world_size": world,
+            "tokens_per_sec": tps, "step_ms_mean": 1.0, "data_stall_fraction": 0.01, "peak_reserved_mb_max": 10.0,
+            "peak_allocated_mb_max": 5.0 + batch, "device_memory_mb": 100.0, "dispatch": dispatch}
+
+
+def test_weak_table_capacity_choice_and_gates():
+    from mini_train_sys_b200.bench import distributed as db
+
+    rows = [_rows(1, 100.0), _rows(1, 100.0), _rows(2, 190.0), _rows(2, 186.0)]
+    weak = db.weak_scaling_table(rows)
+    two = next(w for w in weak if w["world_size"] == 2)
+    assert two["efficiency_pct"] == pytest.approx(94.0)
+    gates = db.quality_gates({"rows": rows, "weak": weak}, repeats=2)
+    assert gates["passed"] and gates["min_efficiency_pct"] == pytest.approx(94.0)
+    assert not db.quality_gates({"rows": rows + [_rows(2, 0, status="failed")], "weak": weak}, repeats=2)["passed"]
+
+    cap_rows = [_rows(1, 100.0, batch=8), _rows(1, 101.0, batch=8), _rows(1, 150.0, batch=16), _rows(1, 151.0, batch=16),
+                _rows(1, 140.0, batch=32), _rows(1, 139.0, batch=32), _rows(1, 500.0, batch=64)]
+    cap = db.present_capacity(cap_rows)
+    assert cap["selected"][0]["batch_size"] == 16 and not cap["selected"][0]["selected_is_largest_tested"]
+    assert cap["selected"][0]["activation_mb_per_sample"] == pytest.approx(1.0)
+    assert any(r["batch_size"] == 64 and r["reason"] == "repeats" for r in cap["rejected"])
+
+    back = db.present_backend([_rows(1, 100.0), _rows(1, 100.0),
+                               _rows(1, 300.0, ops="native", dispatch={"attention:native": 4}),
+                               _rows(1, 300.0, ops="native", dispatch={"attention:native": 4, "attention:fallback": 1})])
+    native = next(b for b in back if b["ops"] == "native")
+    assert native["speedup_vs_torch"] == pytest.approx(3.0) and not native["valid"]
+
+
+def test_weak_suite_end_to_end_on_gloo(tmp_path):
+    cmd = [sys.executable, str(ROOT / "scripts" / "run_dist_bench.py"), "run", "--suite", "weak", "--config",
+           str(ROOT / "configs" / "bench" / "debug_moe.yaml"), "--output-dir", str(tmp_path), "--strategies", "ddp",
+           "--world-sizes", "1,2", "--ops-backends", "torch", "--engines", "nccl", "--batch-sizes", "4", "--repeats", "1",
+           "--warmup-steps", "1", "--measure-steps", "3", "--master-port", "29643", "--timeout", "600"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    summary = json.loads((tmp_path / "weak" / "summary.json").read_text())
+    assert all(r["status"] == "ok" for r in summary["rows"]), summary["rows"]
+    assert {w["world_size"] for w in summary["weak"]} == {1, 2}
+    assert (tmp_path / "weak" / "inventory.json").exists()
+    # a second invocation reuses both results (identical identity hash)
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    again = json.loads((tmp_path / "weak" / "summary.json").read_text())
+    assert all(r.get("reused") for r in again["rows"])
