@@ -141,7 +141,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t M, int64_t N, in
           int64_t epilogue, bool accumulate, bool atomic_out, const c10::optional<Tensor>& aux,
           const c10::optional<Tensor>& tile_group, const c10::optional<Tensor>& num_row_tiles,
           const c10::optional<Tensor>& group_rows, int64_t num_groups, int64_t b_group_stride_rows, int64_t out_group_stride,
-          int64_t ldo, int64_t sm_limit) {
+          int64_t ldo, int64_t sm_limit, bool pair) {
   check_rowmajor_2d(a, "a");
   check_rowmajor_2d(b, "b");
   TORCH_CHECK(is_bf16(a) && is_bf16(b), "GEMM operands must be bf16");
@@ -172,6 +172,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t M, int64_t N, in
     TORCH_CHECK(g.tile_group && g.num_row_tiles, "grouped-M needs tile_group and num_row_tiles");
     TORCH_CHECK(M % 128 == 0 && tile_group->numel() >= M / 128, "grouped-M capacity must be a multiple of 128");
     TORCH_CHECK(!a_mn, "grouped-M expects a K-major A operand");
+    TORCH_CHECK(!pair || M % 256 == 0, "grouped-M on CTA pairs needs a row capacity that is a multiple of 256");
   }
   if (mode == mts::GEMM_GROUPED_K) {
     TORCH_CHECK(g.group_rows && group_rows->numel() >= num_groups + 1, "grouped-K needs group_rows[groups + 1]");
@@ -190,6 +191,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t M, int64_t N, in
   }
   g.status = status_word(a.get_device()).data_ptr<int>();
   g.sm_limit = int(sm_limit);
+  g.pair = pair ? 1 : 0;
   g.stream = cur_stream();
   const cudaError_t gemm_err = mts::launch_gemm_sm100(g);
   TORCH_CHECK(gemm_err == cudaSuccess, "tcgen05 gemm failed: ", cudaGetErrorString(gemm_err), " (", mts::g_last_error, ")");
@@ -258,7 +260,7 @@ Tensor router_backward(const Tensor& logits, const Tensor& lse, const Tensor& id
   return out;
 }
 
-int64_t moe_capacity_rows(int64_t T, int64_t K, int64_t E) { return ((T * K + E * 127) + 127) / 128 * 128; }
+int64_t moe_capacity_rows(int64_t T, int64_t K, int64_t E) { return ((T * K + E * 255) + 255) / 256 * 256; }   // segments padded to 256 rows
 
 // returns row_token[cap], token_rows[T*K], tile_group[cap/128], group_rows[E+1], meta[4]
 std::vector<Tensor> moe_plan(const Tensor& indices, int64_t E) {

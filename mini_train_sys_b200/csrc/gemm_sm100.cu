@@ -1,9 +1,19 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a (see gemm_sm100.cuh for the interface).
 //
-// CTA = 192 threads: warp 0 issues TMA loads into a 4-stage shared-memory ring, warp 1 issues
-// tcgen05.mma (128 x 256 x 16 per instruction, fp32 accumulators in tensor memory), warps 2-5 drain
-// the accumulator (tcgen05.ld) and run the epilogue.  Two 256-column accumulators ping-pong, so
-// the epilogue of tile i overlaps the MMAs of tile i+1.  One CTA per SM, tiles assigned round-robin.
+// CTA = 320 threads: warp 0 issues TMA loads into a shared-memory ring, warp 1 issues tcgen05.mma
+// (fp32 accumulators in tensor memory), warps 2-9 drain the accumulator (tcgen05.ld, four 32-column
+// chunks in flight per warp; two warps share each 32-lane quarter and split its columns) and run the
+// epilogue.  Two 256-column accumulators ping-pong, so the epilogue of tile i overlaps the MMAs of
+// tile i+1.  One CTA per SM, tiles assigned round-robin.
+//
+// Two instantiations:
+//   single  one CTA per 128 x 256 tile (cta_group::1), 4 stages of 48 KB.
+//   pair    a cluster of two CTAs per 256 x 256 tile (cta_group::2): each CTA stages its 128 rows of A and
+//           its 128 rows of B (6 stages of 32 KB), the leader CTA issues 256 x 256 x 16 MMAs that read both
+//           shared memories and write both tensor memories, and each CTA runs the epilogue of its own 128
+//           rows.  Per FLOP this moves one third less data from L2 than the single form, which is what
+//           bounds the single form on the 768-wide contractions of the model.  No load is multicast:
+//           every TMA copy has one destination CTA and only its completion bytes go to the leader's mbarrier.
 //
 // Reference counterpart: the Triton grouped-GEMM kernels of minitrain/kernels/triton/fused_moe_kernels.py
 // (:264-437, :500-828) and the cuBLAS-backed nn.Linear layers; none of them has an sm_100 path.
@@ -12,6 +22,7 @@
 
 #include <cudaTypedefs.h>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace mts {
@@ -19,21 +30,39 @@ namespace mts {
 unsigned long long g_launch_count = 0;
 const char* g_last_error = "";
 
+#ifdef MTS_GEMM_TRACE
+// Phase trace of CTA 0 (debug builds only): clock64 stamps, 8 slots per tile, globals from slot 4000.
+__device__ long long g_gemm_trace[4096];
+#define GTRACE(slot) do { if (blockIdx.x == 0 && (slot) < 4096) g_gemm_trace[(slot)] = clock64(); } while (0)
+cudaError_t copy_gemm_trace(long long* host, int n) { return cudaMemcpyFromSymbol(host, g_gemm_trace, sizeof(long long) * n); }
+#else
+#define GTRACE(slot) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;   // producer warp, MMA warp, 8 epilogue warps
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_STAGE_BYTES = 32 * 128;   // one 32-row x 128-byte box per epilogue warp, 128-byte swizzled
 constexpr int ACC_COLS = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int MN_BLOCK_BYTES = BK * 128;  // one 64-wide MN block of an MN-major operand: BK rows of 128 B
-constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 1024;
+
+template <bool PAIR>
+struct Cfg {
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int TILE_M = PAIR ? 256 : 128;        // rows of one work item
+  static constexpr int B_ROWS = PAIR ? 128 : 256;        // rows of B staged by one CTA
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr size_t SMEM_BYTES = size_t(RING_BYTES) + EPI_WARPS * EPI_STAGE_BYTES + 1024;
+};
 
 struct KernelParams {
   int M, N, K;
@@ -52,6 +81,8 @@ struct KernelParams {
   long long out_group_stride;
   int tiles_m, tiles_n;
   int* status;
+  int tma_store;     // epilogue writes through shared memory and TMA stores / reduce-adds (else per-lane global stores)
+  int diag_no_loads; // timing diagnostic: after the ring's first fill the producer only signals, nothing is copied
 };
 
 struct Tile {
@@ -63,12 +94,15 @@ struct Tile {
   int b_k_offset;  // added to the contraction coordinate of an MN-major B (stacked experts)
   int c_row, c_col;
   long long out_offset;
+  int out_group;   // third coordinate of the output tensor map
   int row_limit, col_limit;
 };
 
+// `tiles_m` counts work items of TILE_M rows; `num_row_tiles` and `tile_group` always count 128-row tiles.
+template <int TILE_M>
 __device__ __forceinline__ int live_tiles(const KernelParams& p) {
   if (p.mode == GEMM_GROUPED_M) {
-    int rows = *p.num_row_tiles;
+    int rows = (*p.num_row_tiles + TILE_M / 128 - 1) / (TILE_M / 128);
     rows = rows < p.tiles_m ? rows : p.tiles_m;
     return rows * p.tiles_n;
   }
@@ -76,40 +110,43 @@ __device__ __forceinline__ int live_tiles(const KernelParams& p) {
   return p.tiles_m * p.tiles_n;
 }
 
+template <int TILE_M>
 __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int t) {
   Tile o;
   o.b_k_offset = 0;
   o.out_offset = 0;
+  o.out_group = 0;
   if (p.mode == GEMM_GROUPED_K) {
     const int per = p.tiles_m * p.tiles_n;
     const int g = t / per;
     const int r = t - g * per;
     const int mt = r / p.tiles_n, nt = r - mt * p.tiles_n;
     const int k0 = p.group_rows[g], k1 = p.group_rows[g + 1];
-    o.a_coord = mt * BM;
+    o.a_coord = mt * TILE_M;
     o.b_coord = nt * BN;
     o.b_coord2 = o.b_coord + 128;
     o.k_begin = k0;
     o.k_blocks = (k1 - k0 + BK - 1) / BK;
-    o.c_row = mt * BM;
+    o.c_row = mt * TILE_M;
     o.c_col = nt * BN;
     o.out_offset = (long long)g * p.out_group_stride;
+    o.out_group = p.out_group_stride > 0 ? g : 0;
     o.row_limit = p.M;
     o.col_limit = p.N;
     return o;
   }
   const int mt = t / p.tiles_n, nt = t - mt * p.tiles_n;
-  o.a_coord = mt * BM;
+  o.a_coord = mt * TILE_M;
   o.k_begin = 0;
   o.k_blocks = (p.K + BK - 1) / BK;
-  o.c_row = mt * BM;
+  o.c_row = mt * TILE_M;
   o.c_col = nt * BN;
   o.row_limit = p.M;
   o.col_limit = p.N;
   o.b_coord = nt * BN;
   o.b_coord2 = o.b_coord + 128;
   if (p.mode == GEMM_GROUPED_M) {
-    const int g = p.tile_group[mt];
+    const int g = p.tile_group[mt * (TILE_M / 128)];   // a 256-row work item needs segments padded to 256 rows
     if (p.b_mn) {
       o.b_k_offset = g * p.b_group_stride_rows;
     } else if (p.epilogue == EPI_SWIGLU) {
@@ -201,23 +238,75 @@ __device__ __forceinline__ void regs_to_float(const uint32_t (&r)[32], float (&v
 
 __device__ __forceinline__ float sigmoidf_fast(float x) { return 1.f / (1.f + __expf(-x)); }
 
+// ---- staging for TMA stores: rows of 128 bytes, 16-byte chunk j of row r lives at chunk (j ^ (r & 7)) ----
+__device__ __forceinline__ void stage_chunk(uint8_t* stage, int row, int j, uint4 q) {
+  *reinterpret_cast<uint4*>(stage + row * 128 + ((j ^ (row & 7)) << 4)) = q;
+}
+
+__device__ __forceinline__ void stage_row_bf16(uint8_t* stage, int row, int j0, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 q;
+    q.x = pack_bf16(v[8 * j + 0], v[8 * j + 1]);
+    q.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+    q.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]);
+    q.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+    stage_chunk(stage, row, j0 + j, q);
+  }
+}
+
+__device__ __forceinline__ void stage_row_f32(uint8_t* stage, int row, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint4 q;
+    q.x = __float_as_uint(v[4 * j + 0]);
+    q.y = __float_as_uint(v[4 * j + 1]);
+    q.z = __float_as_uint(v[4 * j + 2]);
+    q.w = __float_as_uint(v[4 * j + 3]);
+    stage_chunk(stage, row, j, q);
+  }
+}
+
+// Warp-collective: publish the staged box and hand it to the TMA unit; returns once the unit has read shared memory.
+__device__ __forceinline__ void flush_box(const CUtensorMap* map, const uint8_t* stage, int col, int row0, int group, bool reduce,
+                                          int lane) {
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    if (reduce) tma_reduce_add_3d(map, stage, col, row0, group);
+    else tma_store_3d(map, stage, col, row0, group);
+    tma_store_commit();
+    tma_store_wait_read<0>();
+  }
+  __syncwarp();
+}
+
 // ---- the kernel ---------------------------------------------------------------------------------
+template <bool PAIR, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                    const KernelParams p) {
+                    const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_aux, const KernelParams p) {
+  using C = Cfg<PAIR>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int STAGE_BYTES = C::STAGE_BYTES;
+  constexpr int TILE_M = C::TILE_M;
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
-  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];    // pair: only the leader's are used
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
   __shared__ __align__(8) uint64_t acc_full[2];
-  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];        // pair: only the leader's are used
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_word;
   __shared__ int loads_issued, loads_consumed;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // 0 = leader
+  const int worker = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x);
+  const int workers = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -226,7 +315,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // one arrive per epilogue warp
+      mbar_init(&acc_empty[b], PAIR ? 2 * EPI_WARPS : EPI_WARPS);  // one arrive per epilogue warp (of both CTAs)
     }
     abort_word = 0;
     loads_issued = 0;
@@ -236,107 +325,183 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     tma_prefetch_desc(&tm_b);
   }
   if (warp == 0) {
-    tmem_alloc(&tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(&tmem_slot, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything is signalled on them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abort_ptr = &abort_word;
 
-  const int total = live_tiles(p);
+  const int total = live_tiles<TILE_M>(p);
+#ifdef MTS_GEMM_TRACE
+  if (threadIdx.x == 0 && blockIdx.x == 0) { g_gemm_trace[4000] = clock64(); g_gemm_trace[4001] = (long long)global_timer_ns(); }
+#endif
 
   if (warp == 0) {
-    // ================= TMA producer =================
+    // ================= TMA producer (in a pair: each CTA loads its own halves) =================
+    // One thread; its instruction stream per k-block is kept short because the ring's refill latency rides on it.
     if (lane == 0) {
-      int it = 0;
+      int it = 0, s = 0;
+      uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-        const Tile t = decode_tile(p, tile);
-        for (int kb = 0; kb < t.k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_ptr)) { ok = false; break; }
-          uint8_t* a_dst = smem + s * STAGE_BYTES;
-          uint8_t* b_dst = a_dst + A_BYTES;
-          const int k = t.k_begin + kb * BK;
-          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          if (p.a_mn) {
-#pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(a_dst + j * MN_BLOCK_BYTES, &tm_a, &full_bar[s], t.a_coord + 64 * j, k);
+      int tj = 0;
+      const uint32_t full0 = PAIR ? map_to_cta(smem_u32(&full_bar[0]), 0) : smem_u32(&full_bar[0]);
+      const uint32_t ring0 = PAIR ? map_to_cta(smem_u32(smem), rank) : smem_u32(smem);
+      for (int tile = worker; tile < total && ok; tile += workers, ++tj) {
+        const Tile t = decode_tile<TILE_M>(p, tile);
+        const int a_coord = t.a_coord + int(rank) * 128;
+        const int b_coord = PAIR ? (B_MN ? t.b_coord + int(rank) * 128 : (rank == 0 ? t.b_coord : t.b_coord2)) : t.b_coord;
+        GTRACE(8 * tj + 6);
+        int k = t.k_begin;
+        for (int kb = 0; kb < t.k_blocks; ++kb, ++it, k += BK) {
+          if (!mbar_wait_hot(&empty_bar[s], ph ^ 1, abort_ptr)) { ok = false; break; }
+          if (p.diag_no_loads && it >= STAGES) {
+            if (rank == 0) mbar_arrive(&full_bar[s]);
+          } else if (PAIR) {
+            const uint32_t bar = full0 + s * 8;
+            const uint32_t a_sm = ring0 + s * STAGE_BYTES, b_sm = a_sm + A_BYTES;
+            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);   // both CTAs' bytes
+            if (A_MN) {
+              tma_load_2d_pair(a_sm, &tm_a, bar, a_coord, k);
+              tma_load_2d_pair(a_sm + MN_BLOCK_BYTES, &tm_a, bar, a_coord + 64, k);
+            } else {
+              tma_load_2d_pair(a_sm, &tm_a, bar, k, a_coord);
+            }
+            if (B_MN) {
+              tma_load_2d_pair(b_sm, &tm_b, bar, b_coord, k + t.b_k_offset);
+              tma_load_2d_pair(b_sm + MN_BLOCK_BYTES, &tm_b, bar, b_coord + 64, k + t.b_k_offset);
+            } else {
+              tma_load_2d_pair(b_sm, &tm_b, bar, k, b_coord);
+            }
           } else {
-            tma_load_2d(a_dst, &tm_a, &full_bar[s], k, t.a_coord);
-          }
-          if (p.b_mn) {
+            uint8_t* a_dst = smem + s * STAGE_BYTES;
+            uint8_t* b_dst = a_dst + A_BYTES;
+            mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+            if (A_MN) {
+              tma_load_2d(a_dst, &tm_a, &full_bar[s], a_coord, k);
+              tma_load_2d(a_dst + MN_BLOCK_BYTES, &tm_a, &full_bar[s], a_coord + 64, k);
+            } else {
+              tma_load_2d(a_dst, &tm_a, &full_bar[s], k, a_coord);
+            }
+            if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(b_dst + j * MN_BLOCK_BYTES, &tm_b, &full_bar[s], t.b_coord + 64 * j, k + t.b_k_offset);
-          } else {
-            tma_load_2d(b_dst, &tm_b, &full_bar[s], k, t.b_coord);
-            tma_load_2d(b_dst + 128 * 128, &tm_b, &full_bar[s], k, t.b_coord2);
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(b_dst + j * MN_BLOCK_BYTES, &tm_b, &full_bar[s], b_coord + 64 * j, k + t.b_k_offset);
+            } else {
+              tma_load_2d(b_dst, &tm_b, &full_bar[s], k, t.b_coord);
+              tma_load_2d(b_dst + 128 * 128, &tm_b, &full_bar[s], k, t.b_coord2);
+            }
           }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
       loads_issued = it;
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ================= MMA issuer =================
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn != 0, p.b_mn != 0);
-      int it = 0, acc_it = 0;
+    // ================= MMA issuer (in a pair: the leader CTA only) =================
+    // One thread feeds the tensor core: four MMAs per k-block take 4 x 128 cycles of pipe time, so everything this
+    // thread executes between them (wait, fence, descriptors, commit, loop) has to stay well below that.
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TILE_M, BN, A_MN, B_MN);
+      // descriptors differ between stages and K steps only in the 14-bit start-address field (16-byte units)
+      const uint64_t a_tmpl = A_MN ? make_smem_desc_sw128(0, MN_BLOCK_BYTES, 1024) : make_smem_desc_sw128(0, 16, 1024);
+      const uint64_t b_tmpl = B_MN ? make_smem_desc_sw128(0, MN_BLOCK_BYTES, 1024) : make_smem_desc_sw128(0, 16, 1024);
+      constexpr uint32_t a_step = (A_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4;
+      constexpr uint32_t b_step = (B_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4;
+      const uint32_t ring16 = (smem_u32(smem) & 0x3FFFF) >> 4;
+      const uint32_t empty_local = PAIR ? map_to_cta(smem_u32(&empty_bar[0]), 0) : smem_u32(&empty_bar[0]);
+      const uint32_t empty_peer = PAIR ? map_to_cta(smem_u32(&empty_bar[0]), 1) : 0u;
+      const uint32_t accfull_local = PAIR ? map_to_cta(smem_u32(&acc_full[0]), 0) : smem_u32(&acc_full[0]);
+      const uint32_t accfull_peer = PAIR ? map_to_cta(smem_u32(&acc_full[0]), 1) : 0u;
+      int it = 0, acc_it = 0, s = 0;
+      uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-        const Tile t = decode_tile(p, tile);
+      for (int tile = worker; tile < total && ok; tile += workers) {
+        const Tile t = decode_tile<TILE_M>(p, tile);
         if (t.k_blocks == 0) continue;
         const int buf = acc_it & 1;
         const uint32_t acc_ph = (acc_it >> 1) & 1;
-        if (!mbar_wait(&acc_empty[buf], acc_ph ^ 1, abort_ptr)) { ok = false; break; }
+        GTRACE(8 * acc_it + 0);
+        if (!mbar_wait_hot(&acc_empty[buf], acc_ph ^ 1, abort_ptr)) { ok = false; break; }
+        GTRACE(8 * acc_it + 1);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
+        uint32_t accumulate = 0;
         for (int kb = 0; kb < t.k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&full_bar[s], ph, abort_ptr)) { ok = false; break; }
+          if (!mbar_wait_hot(&full_bar[s], ph, abort_ptr)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t a_desc = p.a_mn ? make_smem_desc_sw128(a_addr + k * (UMMA_K * 128), MN_BLOCK_BYTES, 1024)
-                                           : make_smem_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
-            const uint64_t b_desc = p.b_mn ? make_smem_desc_sw128(b_addr + k * (UMMA_K * 128), MN_BLOCK_BYTES, 1024)
-                                           : make_smem_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
-            umma_bf16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+          const uint32_t a16 = ring16 + s * (STAGE_BYTES >> 4);
+          const uint64_t ad = a_tmpl | a16, bd = b_tmpl | (a16 + (A_BYTES >> 4));
+          if (PAIR) {
+            umma_bf16_ss_pair(d_tmem, ad, bd, idesc, accumulate);
+            umma_bf16_ss_pair(d_tmem, ad + a_step, bd + b_step, idesc, 1u);
+            umma_bf16_ss_pair(d_tmem, ad + 2 * a_step, bd + 2 * b_step, idesc, 1u);
+            umma_bf16_ss_pair(d_tmem, ad + 3 * a_step, bd + 3 * b_step, idesc, 1u);
+            umma_commit_pair(empty_local + s * 8);   // frees the stage in both CTAs once these MMAs have read it
+            umma_commit_pair(empty_peer + s * 8);
+          } else {
+            umma_bf16_ss(d_tmem, ad, bd, idesc, accumulate);
+            umma_bf16_ss(d_tmem, ad + a_step, bd + b_step, idesc, 1u);
+            umma_bf16_ss(d_tmem, ad + 2 * a_step, bd + 2 * b_step, idesc, 1u);
+            umma_bf16_ss(d_tmem, ad + 3 * a_step, bd + 3 * b_step, idesc, 1u);
+            umma_commit(&empty_bar[s]);
           }
-          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          accumulate = 1u;
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        umma_commit(&acc_full[buf]);
+        GTRACE(8 * acc_it + 2);
+        if (PAIR) {
+          umma_commit_pair(accfull_local + buf * 8);
+          umma_commit_pair(accfull_peer + buf * 8);
+        } else {
+          umma_commit(&acc_full[buf]);
+        }
         ++acc_it;
       }
       loads_consumed = it;
     }
     __syncwarp();
   } else {
-    // ================= epilogue (warps 2..5 -> TMEM lane quarters 2,3,0,1) =================
+    // ================= epilogue: warps 2..9; warp w drains TMEM lane quarter (w & 3), column half (w - 2) / 4 =======
     const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;
+    const int half_id = (warp - 2) >> 2;
+    const int row_in_tile = int(rank) * 128 + quarter * 32 + lane;
+    const uint32_t acc_empty_addr[2] = {PAIR ? map_to_cta(smem_u32(&acc_empty[0]), 0) : 0u,
+                                        PAIR ? map_to_cta(smem_u32(&acc_empty[1]), 0) : 0u};
+    uint8_t* stage = smem + C::RING_BYTES + (warp - 2) * EPI_STAGE_BYTES;
     int acc_it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-      const Tile t = decode_tile(p, tile);
+    for (int tile = worker; tile < total && ok; tile += workers) {
+      const Tile t = decode_tile<TILE_M>(p, tile);
       const int row = t.c_row + row_in_tile;
+      const int row0 = row - lane;                 // first row of this warp's 32-row box
       const bool row_ok = row < t.row_limit;
       if (t.k_blocks == 0) {
         // nothing was contracted: the product is zero
-        if (p.epilogue == EPI_STORE && !p.accumulate && !p.atomic_out && row_ok) {
+        if (p.tma_store && p.epilogue == EPI_STORE && !p.accumulate && !p.atomic_out) {
           float z[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) z[j] = 0.f;
-          for (int c = 0; c < BN / 32; ++c) {
+          if (p.out_fp32) stage_row_f32(stage, lane, z);
+          else { stage_row_bf16(stage, lane, 0, z); stage_row_bf16(stage, lane, 4, z); }
+          const int step = p.out_fp32 ? 32 : 64;
+          for (int col = t.c_col + half_id * 128; col < t.c_col + half_id * 128 + 128; col += step)
+            if (col < t.col_limit && row0 < t.row_limit) flush_box(&tm_out, stage, col, row0, t.out_group, false, lane);
+        } else if (p.epilogue == EPI_STORE && !p.accumulate && !p.atomic_out && row_ok) {
+          float z[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) z[j] = 0.f;
+          for (int c = half_id * 4; c < half_id * 4 + 4; ++c) {
             const int col = t.c_col + c * 32;
             const int valid = t.col_limit - col;
             if (valid <= 0) break;
@@ -348,17 +513,134 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       const int buf = acc_it & 1;
       const uint32_t acc_ph = (acc_it >> 1) & 1;
+      if (warp == 2 && lane == 0) GTRACE(8 * acc_it + 3);
       if (!mbar_wait_warp(&acc_full[buf], acc_ph, abort_ptr, lane)) { ok = false; break; }
+      if (warp == 2 && lane == 0) GTRACE(8 * acc_it + 4);
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + buf * ACC_COLS;
+      bool released = false;
+      // the accumulator buffer goes back to the MMA warp as soon as its values are in registers
+      auto release_acc = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(acc_empty_addr[buf]);
+          else mbar_arrive(&acc_empty[buf]);
+        }
+        released = true;
+      };
 
-      if (p.epilogue == EPI_STORE) {
+      if (p.tma_store && p.epilogue == EPI_STORE) {
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        const int c0 = half_id * 4;
+        tmem_ld_32x32(taddr + (c0 + 0) * 32, r0);
+        tmem_ld_32x32(taddr + (c0 + 1) * 32, r1);
+        tmem_ld_32x32(taddr + (c0 + 2) * 32, r2);
+        tmem_ld_32x32(taddr + (c0 + 3) * 32, r3);
+        tmem_ld_wait();
+        release_acc();
+        const bool box_rows = row0 < t.row_limit;
+        const bool reduce = p.accumulate || p.atomic_out;
+        const int col0 = t.c_col + c0 * 32;
+        float v[32];
+        if (p.out_fp32) {
+          regs_to_float(r0, v); stage_row_f32(stage, lane, v);
+          if (box_rows && col0 < t.col_limit) flush_box(&tm_out, stage, col0, row0, t.out_group, reduce, lane);
+          regs_to_float(r1, v); stage_row_f32(stage, lane, v);
+          if (box_rows && col0 + 32 < t.col_limit) flush_box(&tm_out, stage, col0 + 32, row0, t.out_group, reduce, lane);
+          regs_to_float(r2, v); stage_row_f32(stage, lane, v);
+          if (box_rows && col0 + 64 < t.col_limit) flush_box(&tm_out, stage, col0 + 64, row0, t.out_group, reduce, lane);
+          regs_to_float(r3, v); stage_row_f32(stage, lane, v);
+          if (box_rows && col0 + 96 < t.col_limit) flush_box(&tm_out, stage, col0 + 96, row0, t.out_group, reduce, lane);
+        } else {
+          regs_to_float(r0, v); stage_row_bf16(stage, lane, 0, v);
+          regs_to_float(r1, v); stage_row_bf16(stage, lane, 4, v);
+          if (box_rows && col0 < t.col_limit) flush_box(&tm_out, stage, col0, row0, t.out_group, false, lane);
+          regs_to_float(r2, v); stage_row_bf16(stage, lane, 0, v);
+          regs_to_float(r3, v); stage_row_bf16(stage, lane, 4, v);
+          if (box_rows && col0 + 64 < t.col_limit) flush_box(&tm_out, stage, col0 + 64, row0, t.out_group, false, lane);
+        }
+      } else if (p.tma_store && p.epilogue == EPI_SWIGLU) {
+        const int half = p.N / 2;
+        uint32_t rg0[32], ru0[32], rg1[32], ru1[32];
+        const int c0 = half_id * 2;
+        tmem_ld_32x32(taddr + c0 * 32, rg0);
+        tmem_ld_32x32(taddr + 128 + c0 * 32, ru0);
+        tmem_ld_32x32(taddr + (c0 + 1) * 32, rg1);
+        tmem_ld_32x32(taddr + 128 + (c0 + 1) * 32, ru1);
+        tmem_ld_wait();
+        release_acc();
+        const bool box_ok = row0 < t.row_limit && t.c_col + c0 * 32 < half;
+        const int col0 = t.c_col + c0 * 32;
+        float g0[32], g1[32], u[32];
+        regs_to_float(rg0, g0);
+        regs_to_float(rg1, g1);
+        if (p.aux != nullptr) {
+          stage_row_bf16(stage, lane, 0, g0); stage_row_bf16(stage, lane, 4, g1);
+          if (box_ok) flush_box(&tm_aux, stage, col0, row0, 0, false, lane);
+          regs_to_float(ru0, u); stage_row_bf16(stage, lane, 0, u);
+          regs_to_float(ru1, u); stage_row_bf16(stage, lane, 4, u);
+          if (box_ok) flush_box(&tm_aux, stage, half + col0, row0, 0, false, lane);
+        }
+        regs_to_float(ru0, u);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) g0[j] = g0[j] * sigmoidf_fast(g0[j]) * u[j];
+        regs_to_float(ru1, u);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) g1[j] = g1[j] * sigmoidf_fast(g1[j]) * u[j];
+        stage_row_bf16(stage, lane, 0, g0); stage_row_bf16(stage, lane, 4, g1);
+        if (box_ok) flush_box(&tm_out, stage, col0, row0, 0, false, lane);
+      } else if (p.tma_store) {  // EPI_SWIGLU_BWD
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          float v[32];
-          tmem_ld_32x32(taddr + c * 32, r);
+        for (int cc = 0; cc < 4; cc += 2) {
+          uint32_t ra[32], rb[32];
+          const int c0 = half_id * 4 + cc;
+          tmem_ld_32x32(taddr + c0 * 32, ra);
+          tmem_ld_32x32(taddr + (c0 + 1) * 32, rb);
           tmem_ld_wait();
+          if (cc == 2) release_acc();
+          const int col0 = t.c_col + c0 * 32;
+          const bool box_ok = row0 < t.row_limit && col0 < p.N;
+          float dg0[32], dg1[32], du0[32], du1[32];
+          auto grads = [&](uint32_t (&r)[32], int col, float (&dg)[32], float (&du)[32]) {
+            float d[32];
+            regs_to_float(r, d);
+            const int valid = p.N - col;
+            if (row_ok && valid > 0) {
+              const __nv_bfloat16* pre = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ld_aux;
+              load_row_bf16(pre + col, dg, valid);
+              load_row_bf16(pre + p.N + col, du, valid);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) { dg[j] = 0.f; du[j] = 0.f; }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float sg = sigmoidf_fast(dg[j]);
+              const float silu = dg[j] * sg;
+              const float dgate = d[j] * du[j] * (sg + silu * (1.f - sg));
+              du[j] = d[j] * silu;
+              dg[j] = dgate;
+            }
+          };
+          grads(ra, col0, dg0, du0);
+          grads(rb, col0 + 32, dg1, du1);
+          stage_row_bf16(stage, lane, 0, dg0); stage_row_bf16(stage, lane, 4, dg1);
+          if (box_ok) flush_box(&tm_out, stage, col0, row0, 0, false, lane);
+          stage_row_bf16(stage, lane, 0, du0); stage_row_bf16(stage, lane, 4, du1);
+          if (box_ok) flush_box(&tm_out, stage, p.N + col0, row0, 0, false, lane);
+        }
+      } else if (p.epilogue == EPI_STORE) {
+        // this warp's four chunks: one TMEM round trip
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        const int c0 = half_id * 4;
+        tmem_ld_32x32(taddr + (c0 + 0) * 32, r0);
+        tmem_ld_32x32(taddr + (c0 + 1) * 32, r1);
+        tmem_ld_32x32(taddr + (c0 + 2) * 32, r2);
+        tmem_ld_32x32(taddr + (c0 + 3) * 32, r3);
+        tmem_ld_wait();
+        auto put = [&](uint32_t (&r)[32], int c) {
+          float v[32];
           regs_to_float(r, v);
           const int col = t.c_col + c * 32;
           const int valid = t.col_limit - col;
@@ -369,16 +651,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             else
               store_row_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + t.out_offset + (long long)row * p.ldo + col, v, valid);
           }
-        }
+        };
+        put(r0, c0); put(r1, c0 + 1); put(r2, c0 + 2); put(r3, c0 + 3);
       } else if (p.epilogue == EPI_SWIGLU) {
         const int half = p.N / 2;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t rg[32], ru[32];
+        uint32_t rg0[32], ru0[32], rg1[32], ru1[32];
+        const int c0 = half_id * 2;
+        tmem_ld_32x32(taddr + c0 * 32, rg0);
+        tmem_ld_32x32(taddr + 128 + c0 * 32, ru0);
+        tmem_ld_32x32(taddr + (c0 + 1) * 32, rg1);
+        tmem_ld_32x32(taddr + 128 + (c0 + 1) * 32, ru1);
+        tmem_ld_wait();
+        auto put = [&](uint32_t (&rg)[32], uint32_t (&ru)[32], int c) {
           float g[32], u[32];
-          tmem_ld_32x32(taddr + c * 32, rg);
-          tmem_ld_32x32(taddr + 128 + c * 32, ru);
-          tmem_ld_wait();
           regs_to_float(rg, g);
           regs_to_float(ru, u);
           const int col = t.c_col + c * 32;
@@ -393,58 +678,76 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             for (int j = 0; j < 32; ++j) g[j] = g[j] * sigmoidf_fast(g[j]) * u[j];
             store_row_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo + col, g, valid);
           }
-        }
+        };
+        put(rg0, ru0, c0); put(rg1, ru1, c0 + 1);
       } else {  // EPI_SWIGLU_BWD: accumulator = d(post); aux = saved [gate | up]; out = [d gate | d up]
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          float d[32], g[32], u[32];
-          tmem_ld_32x32(taddr + c * 32, r);
+        for (int cc = 0; cc < 4; cc += 2) {
+          uint32_t ra[32], rb[32];
+          const int c0 = half_id * 4 + cc;
+          tmem_ld_32x32(taddr + c0 * 32, ra);
+          tmem_ld_32x32(taddr + (c0 + 1) * 32, rb);
           tmem_ld_wait();
-          regs_to_float(r, d);
-          const int col = t.c_col + c * 32;
-          const int valid = p.N - col;
-          if (row_ok && valid > 0) {
-            const __nv_bfloat16* pre = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ld_aux;
-            load_row_bf16(pre + col, g, valid);
-            load_row_bf16(pre + p.N + col, u, valid);
+          auto put = [&](uint32_t (&r)[32], int c) {
+            float d[32], g[32], u[32];
+            regs_to_float(r, d);
+            const int col = t.c_col + c * 32;
+            const int valid = p.N - col;
+            if (row_ok && valid > 0) {
+              const __nv_bfloat16* pre = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ld_aux;
+              load_row_bf16(pre + col, g, valid);
+              load_row_bf16(pre + p.N + col, u, valid);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float s = sigmoidf_fast(g[j]);
-              const float silu = g[j] * s;
-              const float dgate = d[j] * u[j] * (s + silu * (1.f - s));
-              u[j] = d[j] * silu;   // d up
-              g[j] = dgate;         // d gate
+              for (int j = 0; j < 32; ++j) {
+                const float s = sigmoidf_fast(g[j]);
+                const float silu = g[j] * s;
+                const float dgate = d[j] * u[j] * (s + silu * (1.f - s));
+                u[j] = d[j] * silu;   // d up
+                g[j] = dgate;         // d gate
+              }
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo;
+              store_row_bf16(o + col, g, valid);
+              store_row_bf16(o + p.N + col, u, valid);
             }
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo;
-            store_row_bf16(o + col, g, valid);
-            store_row_bf16(o + p.N + col, u, valid);
-          }
+          };
+          put(ra, c0); put(rb, c0 + 1);
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (warp == 2 && lane == 0) GTRACE(8 * acc_it + 5);
+      if (!released) release_acc();
       ++acc_it;
     }
   }
 
   // ---- teardown: every thread arrives here, also after an abort ----
+  if (p.tma_store && warp >= 2 && lane == 0) tma_store_wait<0>();   // this thread's bulk stores have been written
   tc_fence_before_sync();
   __syncthreads();
+#ifdef MTS_GEMM_TRACE
+  if (threadIdx.x == 0 && blockIdx.x == 0) { g_gemm_trace[4002] = clock64(); g_gemm_trace[4003] = (long long)global_timer_ns(); }
+#endif
   if (threadIdx.x == 0 && abort_word != 0) {
     // Loads that were issued but never consumed may still be in flight: give them a bounded
     // chance to land before shared memory is released.
-    for (int i = loads_consumed; i < loads_issued; ++i) {
-      const int s = i % STAGES;
-      const uint32_t ph = (i / STAGES) & 1;
-      for (int spin = 0; spin < (1 << 20) && !mbar_test(&full_bar[s], ph); ++spin) {
+    if (PAIR) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);   // 0.2 ms: far longer than any copy takes
+    } else {
+      for (int i = loads_consumed; i < loads_issued; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        for (int spin = 0; spin < (1 << 20) && !mbar_test(&full_bar[s], ph); ++spin) {
+        }
       }
     }
     if (p.status != nullptr) atomicMax(p.status, abort_word);
   }
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (PAIR) cluster_sync_all();   // neither CTA leaves while the other may still signal its barriers or read its tiles
+  if (warp == 0) {
+    if (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
+  }
 }
 
 // ---- host side ------------------------------------------------------------------------------------
@@ -497,6 +800,28 @@ bool encode_bf16_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t co
   return r == CUDA_SUCCESS;
 }
 
+// Output view [groups, rows, cols] (cols contiguous, row pitch `ld`, group pitch `group_stride` elements) cut into boxes of
+// 32 rows x 128 bytes with the 128-byte swizzle the epilogue stages in.  Returns false when the view cannot be described.
+bool encode_out_3d(CUtensorMap* map, const void* base, bool fp32, int64_t cols, int64_t rows, int64_t groups, int64_t ld,
+                   int64_t group_stride) {
+  ensure_context_current();
+  auto fn = encode_fn();
+  const int64_t es = fp32 ? 4 : 2;
+  if (fn == nullptr || base == nullptr || (reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * es) % 16 != 0 || cols <= 0 ||
+      rows <= 0 || groups <= 0)
+    return false;
+  if (groups > 1 && (group_stride * es) % 16 != 0) return false;
+  const int64_t gs = groups > 1 ? group_stride : rows * ld;
+  const cuuint64_t dims[3] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(groups)};
+  const cuuint64_t strides[2] = {cuuint64_t(ld * es), cuuint64_t(gs * es)};
+  const cuuint32_t box[3] = {cuuint32_t(128 / es), 32u, 1u};
+  const cuuint32_t elem[3] = {1u, 1u, 1u};
+  const CUresult r = fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),
+                        dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -525,7 +850,28 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
   p.b_group_stride_rows = int(a.b_group_stride_rows);
   p.out_group_stride = a.out_group_stride;
   p.status = a.status;
-  p.tiles_m = int((a.M + BM - 1) / BM);
+  const bool pair = a.pair != 0;
+  // epilogue through shared memory + TMA when every output view can be described by a tensor map
+  CUtensorMap tm_out, tm_aux;
+  static const int env_tma_store = [] { const char* e = getenv("MTS_GEMM_TMA_STORE"); return e ? atoi(e) : 1; }();
+  {
+    const int64_t out_cols = a.epilogue == EPI_SWIGLU ? a.N / 2 : (a.epilogue == EPI_SWIGLU_BWD ? 2 * a.N : a.N);
+    const int64_t groups = (a.mode == GEMM_GROUPED_K && a.out_group_stride > 0) ? a.num_groups : 1;
+    // TMA stores clip at 16-byte granularity: the view is widened to the next 16-byte boundary when the row pitch has the
+    // room (those pad columns then receive exact zeros), otherwise the per-lane store path is used.
+    const int64_t per16 = a.out_fp32 ? 4 : 8;
+    int64_t map_cols = (out_cols + per16 - 1) / per16 * per16;
+    bool ok = env_tma_store != 0 && (map_cols == out_cols || (map_cols <= a.ldo && a.epilogue == EPI_STORE && !a.accumulate && !a.atomic_out));
+    ok = ok && encode_out_3d(&tm_out, a.out, a.out_fp32 != 0, map_cols, a.M, groups, a.ldo, a.out_group_stride);
+    if (ok && a.epilogue == EPI_SWIGLU && a.aux != nullptr) ok = encode_out_3d(&tm_aux, a.aux, false, a.N, a.M, 1, a.ld_aux, 0);
+    else if (ok) tm_aux = tm_out;
+    if (!ok) { tm_out = tm_a; tm_aux = tm_a; }
+    p.tma_store = ok ? 1 : 0;
+  }
+  static const int env_noload = [] { const char* e = getenv("MTS_GEMM_DIAG_NOLOAD"); return e ? atoi(e) : 0; }();
+  p.diag_no_loads = env_noload;
+  const int tile_m = pair ? 256 : 128;
+  p.tiles_m = int((a.M + tile_m - 1) / tile_m);
   p.tiles_n = int((a.N + BN - 1) / BN);
   g_last_error = "inconsistent epilogue arguments";
   if (a.epilogue == EPI_SWIGLU && (a.N % 256 != 0 || a.mode != GEMM_GROUPED_M || a.b_mn_major)) return cudaErrorInvalidValue;
@@ -536,20 +882,48 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
   long long total = (long long)p.tiles_m * p.tiles_n;
   if (a.mode == GEMM_GROUPED_K) total *= a.num_groups;
   if (total <= 0) return cudaSuccess;
-  int ctas = sm_count();
-  if (a.sm_limit > 0 && a.sm_limit < ctas) ctas = a.sm_limit;
-  if (total < ctas) ctas = int(total);
+  int workers = pair ? sm_count() / 2 : sm_count();
+  if (a.sm_limit > 0 && a.sm_limit < workers * (pair ? 2 : 1)) workers = pair ? (a.sm_limit / 2 > 0 ? a.sm_limit / 2 : 1) : a.sm_limit;
+  if (total < workers) workers = int(total);
 
+  using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const KernelParams);
+  static const KernelFn kernels[2][2][2] = {
+      {{gemm_tcgen05_kernel<false, false, false>, gemm_tcgen05_kernel<false, false, true>},
+       {gemm_tcgen05_kernel<false, true, false>, gemm_tcgen05_kernel<false, true, true>}},
+      {{gemm_tcgen05_kernel<true, false, false>, gemm_tcgen05_kernel<true, false, true>},
+       {gemm_tcgen05_kernel<true, true, false>, gemm_tcgen05_kernel<true, true, true>}}};
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES));
-    if (e != cudaSuccess) return e;
+    for (int i = 0; i < 8; ++i) {
+      const bool pr = (i >> 2) & 1;
+      cudaError_t e = cudaFuncSetAttribute(kernels[pr][(i >> 1) & 1][i & 1], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           int(pr ? Cfg<true>::SMEM_BYTES : Cfg<false>::SMEM_BYTES));
+      if (e != cudaSuccess) return e;
+    }
     attr_set = true;
   }
+  const KernelFn kernel = kernels[pair ? 1 : 0][a.a_mn_major ? 1 : 0][a.b_mn_major ? 1 : 0];
   (void)cudaGetLastError();   // do not attribute an earlier sticky error to this launch
-  gemm_tcgen05_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, a.stream>>>(tm_a, tm_b, p);
+  cudaError_t launch_err;
+  if (pair) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(workers) * 2u);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
+    cfg.stream = a.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    launch_err = cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_out, tm_aux, p);
+  } else {
+    kernel<<<workers, NUM_THREADS, Cfg<false>::SMEM_BYTES, a.stream>>>(tm_a, tm_b, tm_out, tm_aux, p);
+    launch_err = cudaGetLastError();
+  }
   ++g_launch_count;
-  const cudaError_t launch_err = cudaGetLastError();
   if (launch_err != cudaSuccess) g_last_error = "kernel launch failed";
   return launch_err;
 }

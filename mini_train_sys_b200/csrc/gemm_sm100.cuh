@@ -15,7 +15,9 @@
 //                  groups add into the same output, which is how split-K wgrad is expressed.
 //
 // Epilogues:
-//   EPI_STORE       D -> out (bf16 or fp32; optional accumulate; optional fp32 atomic add)
+//   EPI_STORE       D -> out (bf16 or fp32; optional accumulate; optional fp32 atomic add).  When N is not a multiple of
+//                   16 bytes' worth of elements and the row pitch has room, the columns between N and that boundary
+//                   are overwritten with zeros (the store goes through TMA, which clips at 16-byte granularity).
 //   EPI_SWIGLU      the 256 accumulator columns are [128 gate | 128 up] of one expert:
 //                   out = silu(gate) * up (bf16, [M, N/2]); aux (optional) receives gate/up (bf16, [M, N])
 //   EPI_SWIGLU_BWD  accumulator = d(post) ; aux holds the saved gate/up; out = [d gate | d up] (bf16, [M, 2*N])
@@ -61,6 +63,7 @@ struct GemmArgs {
   int64_t b_group_stride_rows = 0;   // GROUPED_M: rows of stacked B per group
   int64_t out_group_stride = 0;      // GROUPED_K: elements between consecutive group outputs (0 with atomic_out)
 
+  int pair = 0;                      // 1: two-CTA clusters on 256 x 256 tiles (GROUPED_M then needs 256-row aligned segments)
   int* status = nullptr;             // device int: receives a KernelStatus on failure
   int sm_limit = 0;                  // cap on CTAs (0 = all SMs)
   cudaStream_t stream = nullptr;

@@ -4,7 +4,7 @@
 // Reference counterparts: minitrain/kernels/triton/router.py:61-259 (router),
 // fused_moe_kernels.py:25-234 (histogram / prefix-sum / scatter) and :451-498 (weighted gather-sum).
 // The plan here replaces the sort + associative scan by per-block counting: deterministic, token order
-// is preserved inside every expert, and each expert segment is padded to a multiple of 128 rows so
+// is preserved inside every expert, and each expert segment is padded to a multiple of 256 rows so
 // that GEMM tiles never straddle two experts and padding rows contribute exact zeros.
 #include "ops.cuh"
 
@@ -138,6 +138,10 @@ plan_count_kernel(const int* __restrict__ indices, int n_routes, int E, int* __r
   if (threadIdx.x < E) block_counts[blockIdx.x * E + threadIdx.x] = hist[threadIdx.x];
 }
 
+// Expert segments start on multiples of this many rows: two 128-row tiles, so that a 256-row work item of the
+// two-CTA GEMM never straddles two experts.
+constexpr int kSegmentPad = 256;
+
 // Pass 2 (one CTA): exclusive scan over CTAs for every expert, padded expert offsets, tile -> expert map.
 __global__ void __launch_bounds__(kMaxExperts)
 plan_scan_kernel(int* __restrict__ block_counts, int n_blocks, int E, int capacity_rows, int* __restrict__ group_rows,
@@ -159,12 +163,12 @@ plan_scan_kernel(int* __restrict__ block_counts, int n_blocks, int E, int capaci
     int row = 0;
     for (int g = 0; g < E; ++g) {
       starts[g] = row;
-      row += (totals[g] + 127) / 128 * 128;
+      row += (totals[g] + kSegmentPad - 1) / kSegmentPad * kSegmentPad;
     }
     starts[E] = row;
     meta[0] = row / 128;
     meta[1] = row;
-    meta[2] = row > capacity_rows ? 1 : 0;   // overflow flag (cannot happen when capacity = T*K + E*127 rounded up)
+    meta[2] = row > capacity_rows ? 1 : 0;   // overflow flag (cannot happen when capacity = T*K + E*(kSegmentPad-1) rounded up)
   }
   __syncthreads();
   for (int q = threadIdx.x; q <= E; q += blockDim.x) group_rows[q] = starts[q];

@@ -149,7 +149,8 @@ def test_gemm_nt(nb, m, n, k):
     nb._gemm(a, b, out, m, n, k, ldo=n_pad)
     want = a.float() @ b.float().t()
     assert_close(out[:, :n], want, 1e-2, f"nt {m}x{n}x{k}")
-    assert bool((out[:, n:] == 7.0).all()), "columns beyond N were written"
+    pad = out[:, n:]     # inside the row pitch up to the next 16-byte boundary: left alone or zeroed, never garbage
+    assert bool(((pad == 7.0) | (pad == 0.0)).all()), "columns beyond N hold garbage"
     nb.check_kernel_status()
 
 
@@ -235,7 +236,7 @@ def test_moe_plan(nb, mode):
     rt, tr, tg, gr, mt = (t.cpu() for t in (row_token, token_rows, tile_group, group_rows, meta))
     counts = torch.bincount(idx.flatten().long().cpu(), minlength=experts)
     assert int(mt[2]) == 0
-    padded = (counts + 127) // 128 * 128
+    padded = (counts + 255) // 256 * 256     # two 128-row tiles: a 256-row work item of the paired GEMM stays inside one expert
     assert gr.tolist() == [0, *padded.cumsum(0).tolist()]
     assert int(mt[1]) == int(padded.sum()) and int(mt[0]) == int(padded.sum()) // 128
     flat = idx.flatten().cpu()
