@@ -191,42 +191,53 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-      const uint32_t idesc_pv = make_idesc_bf16(128, 64, false, true);
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, 64, false, true);
+      // Descriptors are built once: a 16-wide contraction step adds 2 (32 B) to a K-major descriptor and 128 (2048 B) to
+      // an MN-major one; ring slots and the two halves of P lie TILE128 bytes (1024 descriptor units) apart.
+      const uint64_t qd = desc_kmajor(smem_u32(sQ), 0), pd = desc_kmajor(smem_u32(sP), 0);
+      const uint64_t ring_k = desc_kmajor(smem_u32(sRing), 0), ring_m = desc_mnmajor(smem_u32(sRing), 0);
+      constexpr uint64_t kSlot = TILE128 >> 4;
       bool ok = mbar_wait(&q_full, 0, abort_ptr);
       // S_j = Q K_j^T.  The softmax warps copy S into registers right away, so S_{j+1} is issued before
       // waiting for P_j: the tensor core computes the next scores while the exponentials of tile j run.
       auto issue_scores = [&](int j) -> bool {
-        const int ik = 2 * j;
-        if (!mbar_wait(&slot_full[ik % 3], (ik / 3) & 1, abort_ptr)) return false;
-        if (!mbar_wait(&s_free, (j & 1) ^ 1, abort_ptr)) return false;
+        const int slot = (2 * j) % 3;
+        if (!mbar_wait_hot(&slot_full[slot], ((2 * j) / 3) & 1, abort_ptr)) return false;
+        if (!mbar_wait_hot(&s_free, (j & 1) ^ 1, abort_ptr)) return false;
         tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(sRing + (ik % 3) * TILE128);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          umma_bf16_ss(tmem_s, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_s, kk != 0);
+        const uint64_t kd = ring_k + slot * kSlot;
+        umma_bf16_ss(tmem_s, qd, kd, idesc_s, 0u);
+        umma_bf16_ss(tmem_s, qd + 2, kd + 2, idesc_s, 1u);
+        umma_bf16_ss(tmem_s, qd + 4, kd + 4, idesc_s, 1u);
+        umma_bf16_ss(tmem_s, qd + 6, kd + 6, idesc_s, 1u);
         umma_commit(&s_full);
-        umma_commit(&slot_empty[ik % 3]);
+        umma_commit(&slot_empty[slot]);
         return true;
       };
       ok = ok && issue_scores(0);
       for (int j = 0; j < n_kv && ok; ++j) {
         const int iv = 2 * j + 1;
+        const int slot = iv % 3;
         MTS_TRACE(4096 + 8 * j + 0);
         if (j + 1 < n_kv && !issue_scores(j + 1)) break;
         MTS_TRACE(4096 + 8 * j + 1);
-        if (!mbar_wait(&p_ready, j & 1, abort_ptr)) break;
+        if (!mbar_wait_hot(&p_ready, j & 1, abort_ptr)) break;
         MTS_TRACE(4096 + 8 * j + 2);
-        if (!mbar_wait(&slot_full[iv % 3], (iv / 3) & 1, abort_ptr)) break;
+        if (!mbar_wait_hot(&slot_full[slot], (iv / 3) & 1, abort_ptr)) break;
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(sRing + (iv % 3) * TILE128);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ss(tmem_pv, desc_kmajor(p_addr + (kk >> 2) * TILE128, kk & 3), desc_mnmajor(v_addr, kk), idesc_pv, (j | kk) != 0);
+        const uint64_t vm = ring_m + slot * kSlot;
+        umma_bf16_ss(tmem_pv, pd, vm, idesc_pv, j != 0 ? 1u : 0u);
+        umma_bf16_ss(tmem_pv, pd + 2, vm + 128, idesc_pv, 1u);
+        umma_bf16_ss(tmem_pv, pd + 4, vm + 256, idesc_pv, 1u);
+        umma_bf16_ss(tmem_pv, pd + 6, vm + 384, idesc_pv, 1u);
+        umma_bf16_ss(tmem_pv, pd + kSlot, vm + 512, idesc_pv, 1u);
+        umma_bf16_ss(tmem_pv, pd + kSlot + 2, vm + 640, idesc_pv, 1u);
+        umma_bf16_ss(tmem_pv, pd + kSlot + 4, vm + 768, idesc_pv, 1u);
+        umma_bf16_ss(tmem_pv, pd + kSlot + 6, vm + 896, idesc_pv, 1u);
         umma_commit(&pv_full);
         MTS_TRACE(4096 + 8 * j + 3);
-        umma_commit(&slot_empty[iv % 3]);
+        umma_commit(&slot_empty[slot]);
       }
     }
     __syncwarp();
@@ -362,7 +373,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // =====================================================================================================
 // backward, sweep 1: dK / dV.  CTA = 128 keys; streams 64-query tiles.
 // =====================================================================================================
-constexpr int BWD_KV_SMEM = 2 * TILE128 /*K,V*/ + 4 * TILE64 /*Q,dO x 2 stages*/ + 2 * TILE128 /*P^T, dS^T*/ + 1024;
+constexpr int BWD_KV_SMEM = 2 * TILE128 /*K,V*/ + 4 * TILE64 /*Q,dO x 2 stages*/ + 2 * TILE128 /*P^T, dS^T*/ + 2048 /*lse, delta*/ + 1024;
 
 __global__ void __launch_bounds__(THREADS, 2)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_constant__ CUtensorMap tm_k,
@@ -375,6 +386,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
   uint8_t* sDO = smem + 2 * TILE128 + 2 * TILE64;   // 2 stages x 8 KB
   uint8_t* sP = smem + 2 * TILE128 + 4 * TILE64;    // [128 keys x 64 q]
   uint8_t* sDS = sP + TILE128;
+  uint8_t* sStats = sDS + TILE128;                  // 4 warps x 512 B
 
   __shared__ __align__(8) uint64_t kv_full, qd_full[2], qd_empty[2], st_full, st_free, pds_ready, pds_free, acc_full;
   __shared__ uint32_t tmem_slot;
@@ -420,31 +432,58 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);   // [128 keys x 64 q], both K-major
-      const uint32_t idesc_acc = make_idesc_bf16(128, 64, false, true);   // B = [q rows x 64 d] read MN-major
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
+      constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);   // [128 keys x 64 q], both K-major
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, 64, false, true);   // B = [q rows x 64 d] read MN-major
+      // This one thread feeds the tensor core, so its instruction stream is kept short: every descriptor is built once;
+      // a 16-wide contraction step adds 2 (32 B) to a K-major descriptor and 128 (2048 B) to an MN-major one, and the
+      // second Q / dO stage lies TILE64 bytes (512 descriptor units) after the first.
+      const uint64_t kd = desc_kmajor(smem_u32(sK), 0), vd = desc_kmajor(smem_u32(sV), 0);
+      const uint64_t pd = desc_kmajor(smem_u32(sP), 0), dsd = desc_kmajor(smem_u32(sDS), 0);
+      const uint64_t qk0 = desc_kmajor(smem_u32(sQ), 0), dok0 = desc_kmajor(smem_u32(sDO), 0);
+      const uint64_t qm0 = desc_mnmajor(smem_u32(sQ), 0), dom0 = desc_mnmajor(smem_u32(sDO), 0);
+      constexpr uint64_t kStage = TILE64 >> 4;
+      // S^T_i = K Q_i^T and dP^T_i = V dO_i^T.  The compute warps copy both to registers early in their iteration, so the
+      // scores of tile i+1 are issued before waiting for P^T_i / dS^T_i and run while tile i is being processed.
+      auto issue_scores = [&](int i) -> bool {
+        const int s = i & 1;
+        if (!mbar_wait_hot(&qd_full[s], (i >> 1) & 1, abort_ptr)) return false;
+        if (!mbar_wait_hot(&st_free, (i & 1) ^ 1, abort_ptr)) return false;
+        tc_fence_after_sync();
+        const uint64_t q = qk0 + s * kStage, d_o = dok0 + s * kStage;
+        umma_bf16_ss(t_st, kd, q, idesc_st, 0u);
+        umma_bf16_ss(t_st, kd + 2, q + 2, idesc_st, 1u);
+        umma_bf16_ss(t_st, kd + 4, q + 4, idesc_st, 1u);
+        umma_bf16_ss(t_st, kd + 6, q + 6, idesc_st, 1u);
+        umma_bf16_ss(t_dp, vd, d_o, idesc_st, 0u);
+        umma_bf16_ss(t_dp, vd + 2, d_o + 2, idesc_st, 1u);
+        umma_bf16_ss(t_dp, vd + 4, d_o + 4, idesc_st, 1u);
+        umma_bf16_ss(t_dp, vd + 6, d_o + 6, idesc_st, 1u);
+        umma_commit(&st_full);
+        return true;
+      };
       bool ok = mbar_wait(&kv_full, 0, abort_ptr);
+      ok = ok && (n_iter <= 0 || issue_scores(0));
       for (int i = 0; i < n_iter && ok; ++i) {
         const int s = i & 1;
-        if (!mbar_wait(&qd_full[s], (i >> 1) & 1, abort_ptr)) break;
-        if (!mbar_wait(&st_free, (i & 1) ^ 1, abort_ptr)) break;
+        MTS_TRACE(4096 + 8 * i + 0);
+        if (i + 1 < n_iter && !issue_scores(i + 1)) break;
+        MTS_TRACE(4096 + 8 * i + 1);
+        if (!mbar_wait_hot(&pds_ready, i & 1, abort_ptr)) break;
+        MTS_TRACE(4096 + 8 * i + 2);
         tc_fence_after_sync();
-        const uint32_t q_addr = smem_u32(sQ + s * TILE64), do_addr = smem_u32(sDO + s * TILE64);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(t_st, desc_kmajor(k_addr, kk), desc_kmajor(q_addr, kk), idesc_st, kk != 0);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(t_dp, desc_kmajor(v_addr, kk), desc_kmajor(do_addr, kk), idesc_st, kk != 0);
-        umma_commit(&st_full);
-        if (!mbar_wait(&pds_ready, i & 1, abort_ptr)) break;
-        tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16_ss(t_dv, desc_kmajor(p_addr, kk), desc_mnmajor(do_addr, kk), idesc_acc, (i | kk) != 0);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16_ss(t_dk, desc_kmajor(ds_addr, kk), desc_mnmajor(q_addr, kk), idesc_acc, (i | kk) != 0);
+        const uint64_t qm = qm0 + s * kStage, dom = dom0 + s * kStage;
+        const uint32_t acc = i != 0 ? 1u : 0u;
+        umma_bf16_ss(t_dv, pd, dom, idesc_acc, acc);
+        umma_bf16_ss(t_dv, pd + 2, dom + 128, idesc_acc, 1u);
+        umma_bf16_ss(t_dv, pd + 4, dom + 256, idesc_acc, 1u);
+        umma_bf16_ss(t_dv, pd + 6, dom + 384, idesc_acc, 1u);
+        umma_bf16_ss(t_dk, dsd, qm, idesc_acc, acc);
+        umma_bf16_ss(t_dk, dsd + 2, qm + 128, idesc_acc, 1u);
+        umma_bf16_ss(t_dk, dsd + 4, qm + 256, idesc_acc, 1u);
+        umma_bf16_ss(t_dk, dsd + 6, qm + 384, idesc_acc, 1u);
         umma_commit(&qd_empty[s]);
         umma_commit(&pds_free);
+        MTS_TRACE(4096 + 8 * i + 3);
       }
       umma_commit(&acc_full);
     }
@@ -458,21 +497,33 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
     const Dropout drop = make_dropout(p.dropout_p, p.seed, uint32_t(bh), p.S);
     const float* lse_bh = p.lse + (long long)bh * p.S;
     const float* delta_bh = p.delta + (long long)bh * p.S;
+    const uint32_t keep_shift = uint32_t(key & 3) * 8u;
+    float* stats = reinterpret_cast<float*>(sStats) + (warp - 2) * 128;   // [lse 32 | delta 32] x 2 halves, this warp's own
+    float pre[4];
+    auto fetch_stats = [&](int qb0) {
+      const int qa = qb0 + lane, qb = qb0 + 32 + lane;
+      pre[0] = qa < p.S ? lse_bh[qa] * LOG2E : 0.f;
+      pre[1] = qa < p.S ? delta_bh[qa] : 0.f;
+      pre[2] = qb < p.S ? lse_bh[qb] * LOG2E : 0.f;
+      pre[3] = qb < p.S ? delta_bh[qb] : 0.f;
+    };
+    if (n_iter > 0) fetch_stats(first_q * 64);
     bool ok = true;
     for (int i = 0; i < n_iter; ++i) {
       const int qbase = (first_q + i) * 64;
-      // lse / delta of the 64 queries of this tile live in registers, two per lane, and are
-      // broadcast with shuffles (no shared staging, so no CTA-level barrier inside the loop)
-      float lse_reg[2], delta_reg[2];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int qi = qbase + c * 32 + lane;
-        lse_reg[c] = qi < p.S ? lse_bh[qi] * LOG2E : 0.f;
-        delta_reg[c] = qi < p.S ? delta_bh[qi] : 0.f;
-      }
+      // lse / delta of the 64 queries of this tile: staged in a 512-byte area private to the warp and read back as
+      // float4 broadcasts (every lane reads the same address), 16 loads per 32 queries instead of 64 shuffles.  The
+      // values were fetched from global memory one iteration ahead, so their latency is not on this path.
+      stats[lane] = pre[0];
+      stats[32 + lane] = pre[1];
+      stats[64 + lane] = pre[2];
+      stats[96 + lane] = pre[3];
+      if (i + 1 < n_iter) fetch_stats(qbase + 64);
+      __syncwarp();
+      if (warp == 2) MTS_TRACE(8 * i + 0);
       if (!mbar_wait_warp(&st_full, i & 1, abort_ptr, lane)) { ok = false; break; }
+      if (warp == 2) MTS_TRACE(8 * i + 1);
       tc_fence_after_sync();
-      if (!mbar_wait_warp(&pds_free, (i & 1) ^ 1, abort_ptr, lane)) { ok = false; break; }
       const bool need_mask = (p.causal && qbase < k0 + 127) || (qbase + 64 > p.S) || (k0 + 128 > p.S);
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
@@ -480,36 +531,77 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
         tmem_ld_32x32(t_st + lane_base + c * 32, rs);
         tmem_ld_32x32(t_dp + lane_base + c * 32, rd);
         tmem_ld_wait();
-        float pv[32], ds[32];
+        if (warp == 2) MTS_TRACE(8 * i + 2 + 3 * c);
+        // both halves are in registers: the MMA warp may start the scores of the next query tile
+        if (c == 1) epilogue_arrive(&st_free, lane);
+        const float4* lse4 = reinterpret_cast<const float4*>(stats + c * 64);
+        const float4* del4 = reinterpret_cast<const float4*>(stats + c * 64 + 32);
+        // The loops below are written one operation at a time over all 32 columns: with two compute warps per
+        // scheduler the latency of each exp2 / multiply has to be covered by independent work of the same warp.
+        float e[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int qi = qbase + c * 32 + j;
-          const float lse_q = __shfl_sync(0xffffffffu, lse_reg[c], j);
-          const float delta_q = __shfl_sync(0xffffffffu, delta_reg[c], j);
-          float e = ex2(__uint_as_float(rs[j]) * scale_log2 - lse_q);
-          if (need_mask && (qi >= p.S || key >= p.S || (p.causal && key > qi))) e = 0.f;
-          float dp = __uint_as_float(rd[j]);
-          float pd = e;
-          if (drop.thresh != 0u) {
-            const bool kept = drop.keep(uint32_t(qi), uint32_t(key));
-            pd = kept ? e * drop.inv_keep : 0.f;
-            dp = kept ? dp * drop.inv_keep : 0.f;
-          }
-          pv[j] = pd;
-          ds[j] = e * (dp - delta_q) * p.scale;
+        for (int g = 0; g < 8; ++g) {
+          const float4 l4 = lse4[g];
+          e[4 * g + 0] = ex2(fmaf(__uint_as_float(rs[4 * g + 0]), scale_log2, -l4.x));
+          e[4 * g + 1] = ex2(fmaf(__uint_as_float(rs[4 * g + 1]), scale_log2, -l4.y));
+          e[4 * g + 2] = ex2(fmaf(__uint_as_float(rs[4 * g + 2]), scale_log2, -l4.z));
+          e[4 * g + 3] = ex2(fmaf(__uint_as_float(rs[4 * g + 3]), scale_log2, -l4.w));
         }
+        if (need_mask) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int qi = qbase + c * 32 + j;
+            if (qi >= p.S || key >= p.S || (p.causal && key > qi)) e[j] = 0.f;
+          }
+        }
+        uint32_t pa[16], pb[16];
+        if (drop.thresh != 0u) {
+          // Keep bits: one hashed word covers four consecutive keys of one query, i.e. the four lanes of a quad.
+          // Each lane hashes the words of 8 of the 32 queries and the quad exchanges them by shuffle.
+          uint32_t words[8];
+#pragma unroll
+          for (int t = 0; t < 8; ++t)
+            words[t] = drop.word(uint32_t(qbase + c * 32 + 4 * t + (lane & 3)), uint32_t(key) >> 2);
+          const int quad = lane & 28;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const float4 d4 = del4[g];
+            const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pv[4], ds[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const uint32_t w = __shfl_sync(0xffffffffu, words[g], quad | u);
+              const bool kept = ((w >> keep_shift) & 0xFFu) >= drop.thresh;
+              pv[u] = kept ? e[4 * g + u] : 0.f;                                    // 1 / keep: applied to dV at the end
+              const float dp = kept ? __uint_as_float(rd[4 * g + u]) * drop.inv_keep : 0.f;
+              ds[u] = e[4 * g + u] * (dp - dl[u]);                                   // softmax scale: applied to dK at the end
+            }
+            pa[2 * g] = pack2(pv[0], pv[1]); pa[2 * g + 1] = pack2(pv[2], pv[3]);
+            pb[2 * g] = pack2(ds[0], ds[1]); pb[2 * g + 1] = pack2(ds[2], ds[3]);
+          }
+        } else {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const float4 d4 = del4[g];
+            const float ds0 = e[4 * g + 0] * (__uint_as_float(rd[4 * g + 0]) - d4.x);
+            const float ds1 = e[4 * g + 1] * (__uint_as_float(rd[4 * g + 1]) - d4.y);
+            const float ds2 = e[4 * g + 2] * (__uint_as_float(rd[4 * g + 2]) - d4.z);
+            const float ds3 = e[4 * g + 3] * (__uint_as_float(rd[4 * g + 3]) - d4.w);
+            pa[2 * g] = pack2(e[4 * g + 0], e[4 * g + 1]); pa[2 * g + 1] = pack2(e[4 * g + 2], e[4 * g + 3]);
+            pb[2 * g] = pack2(ds0, ds1); pb[2 * g + 1] = pack2(ds2, ds3);
+          }
+        }
+        if (warp == 2) MTS_TRACE(8 * i + 3 + 3 * c);
+        // the previous tile's dV / dK MMAs must have read P^T / dS^T before they are overwritten
+        if (c == 0 && !mbar_wait_warp(&pds_free, (i & 1) ^ 1, abort_ptr, lane)) { ok = false; break; }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          uint4 a, d4;
-          a.x = pack2(pv[8 * g + 0], pv[8 * g + 1]); a.y = pack2(pv[8 * g + 2], pv[8 * g + 3]);
-          a.z = pack2(pv[8 * g + 4], pv[8 * g + 5]); a.w = pack2(pv[8 * g + 6], pv[8 * g + 7]);
-          d4.x = pack2(ds[8 * g + 0], ds[8 * g + 1]); d4.y = pack2(ds[8 * g + 2], ds[8 * g + 3]);
-          d4.z = pack2(ds[8 * g + 4], ds[8 * g + 5]); d4.w = pack2(ds[8 * g + 6], ds[8 * g + 7]);
-          st_swizzled(sP, r, c * 4 + g, a);
-          st_swizzled(sDS, r, c * 4 + g, d4);
+          st_swizzled(sP, r, c * 4 + g, make_uint4(pa[4 * g], pa[4 * g + 1], pa[4 * g + 2], pa[4 * g + 3]));
+          st_swizzled(sDS, r, c * 4 + g, make_uint4(pb[4 * g], pb[4 * g + 1], pb[4 * g + 2], pb[4 * g + 3]));
         }
+        if (warp == 2) MTS_TRACE(8 * i + 4 + 3 * c);
       }
-      epilogue_arrive(&st_free, lane);
+      if (!ok) break;
       fence_proxy_async_smem();
       epilogue_arrive(&pds_ready, lane);
     }
@@ -524,7 +616,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
       }
-      if (key < p.S) store_row64(p.dv + (long long)b * p.dv_sb + (long long)h * p.dv_sh + (long long)key * p.dv_ss, acc, 1.f);
+      if (key < p.S) store_row64(p.dv + (long long)b * p.dv_sb + (long long)h * p.dv_sh + (long long)key * p.dv_ss, acc,
+                                 drop.thresh != 0u ? drop.inv_keep : 1.f);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t rr[32];
@@ -533,7 +626,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
       }
-      if (key < p.S) store_row64(p.dk + (long long)b * p.dk_sb + (long long)h * p.dk_sh + (long long)key * p.dk_ss, acc, 1.f);
+      if (key < p.S) store_row64(p.dk + (long long)b * p.dk_sb + (long long)h * p.dk_sh + (long long)key * p.dk_ss, acc, p.scale);
     }
   }
 
@@ -605,28 +698,47 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
-      const uint32_t idesc_dq = make_idesc_bf16(128, 64, false, true);
-      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO), ds_addr = smem_u32(sDS);
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, false, true);
+      // descriptors built once (see the dK / dV sweep for the arithmetic on them)
+      const uint64_t qd = desc_kmajor(smem_u32(sQ), 0), dod = desc_kmajor(smem_u32(sDO), 0), dsd = desc_kmajor(smem_u32(sDS), 0);
+      const uint64_t kk0 = desc_kmajor(smem_u32(sK), 0), vk0 = desc_kmajor(smem_u32(sV), 0), km0 = desc_mnmajor(smem_u32(sK), 0);
+      constexpr uint64_t kStage = TILE64 >> 4;
+      auto issue_scores = [&](int i) -> bool {
+        const int s = i & 1;
+        if (!mbar_wait_hot(&kv_full[s], (i >> 1) & 1, abort_ptr)) return false;
+        if (!mbar_wait_hot(&st_free, (i & 1) ^ 1, abort_ptr)) return false;
+        tc_fence_after_sync();
+        const uint64_t k = kk0 + s * kStage, v = vk0 + s * kStage;
+        umma_bf16_ss(t_s, qd, k, idesc_s, 0u);
+        umma_bf16_ss(t_s, qd + 2, k + 2, idesc_s, 1u);
+        umma_bf16_ss(t_s, qd + 4, k + 4, idesc_s, 1u);
+        umma_bf16_ss(t_s, qd + 6, k + 6, idesc_s, 1u);
+        umma_bf16_ss(t_dp, dod, v, idesc_s, 0u);
+        umma_bf16_ss(t_dp, dod + 2, v + 2, idesc_s, 1u);
+        umma_bf16_ss(t_dp, dod + 4, v + 4, idesc_s, 1u);
+        umma_bf16_ss(t_dp, dod + 6, v + 6, idesc_s, 1u);
+        umma_commit(&st_full);
+        return true;
+      };
       bool ok = mbar_wait(&qd_full, 0, abort_ptr);
+      ok = ok && (n_iter <= 0 || issue_scores(0));
       for (int i = 0; i < n_iter && ok; ++i) {
         const int s = i & 1;
-        if (!mbar_wait(&kv_full[s], (i >> 1) & 1, abort_ptr)) break;
-        if (!mbar_wait(&st_free, (i & 1) ^ 1, abort_ptr)) break;
+        MTS_TRACE(6144 + 8 * i + 0);
+        if (i + 1 < n_iter && !issue_scores(i + 1)) break;   // next scores run while dS of this tile is being formed
+        MTS_TRACE(6144 + 8 * i + 1);
+        if (!mbar_wait_hot(&ds_ready, i & 1, abort_ptr)) break;
+        MTS_TRACE(6144 + 8 * i + 2);
         tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(sK + s * TILE64), v_addr = smem_u32(sV + s * TILE64);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(t_s, desc_kmajor(q_addr, kk), desc_kmajor(k_addr, kk), idesc_s, kk != 0);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) umma_bf16_ss(t_dp, desc_kmajor(do_addr, kk), desc_kmajor(v_addr, kk), idesc_s, kk != 0);
-        umma_commit(&st_full);
-        if (!mbar_wait(&ds_ready, i & 1, abort_ptr)) break;
-        tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16_ss(t_dq, desc_kmajor(ds_addr, kk), desc_mnmajor(k_addr, kk), idesc_dq, (i | kk) != 0);
+        const uint64_t km = km0 + s * kStage;
+        umma_bf16_ss(t_dq, dsd, km, idesc_dq, i != 0 ? 1u : 0u);
+        umma_bf16_ss(t_dq, dsd + 2, km + 128, idesc_dq, 1u);
+        umma_bf16_ss(t_dq, dsd + 4, km + 256, idesc_dq, 1u);
+        umma_bf16_ss(t_dq, dsd + 6, km + 384, idesc_dq, 1u);
         umma_commit(&kv_empty[s]);
         umma_commit(&ds_free);
+        MTS_TRACE(6144 + 8 * i + 3);
       }
       umma_commit(&acc_full);
     }
@@ -643,9 +755,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     bool ok = true;
     for (int i = 0; i < n_iter; ++i) {
       const int kbase = i * 64;
+      if (warp == 2) MTS_TRACE(2048 + 8 * i + 0);
       if (!mbar_wait_warp(&st_full, i & 1, abort_ptr, lane)) { ok = false; break; }
+      if (warp == 2) MTS_TRACE(2048 + 8 * i + 1);
       tc_fence_after_sync();
-      if (!mbar_wait_warp(&ds_free, (i & 1) ^ 1, abort_ptr, lane)) { ok = false; break; }
       const bool need_mask = (p.causal && kbase + 63 > q0) || (kbase + 64 > p.S) || (q0 + 128 > p.S);
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
@@ -653,6 +766,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tmem_ld_32x32(t_s + lane_base + c * 32, rs);
         tmem_ld_32x32(t_dp + lane_base + c * 32, rd);
         tmem_ld_wait();
+        if (warp == 2) MTS_TRACE(2048 + 8 * i + 2 + 3 * c);
+        if (c == 1) epilogue_arrive(&st_free, lane);   // S / dP are in registers: the next scores may be issued
         float ds[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -669,22 +784,24 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             for (int t = 0; t < 4; ++t) {
               const bool kept = ((bits >> (8 * t)) & 0xFFu) >= drop.thresh;
               const float dp = kept ? __uint_as_float(rd[4 * w + t]) * drop.inv_keep : 0.f;
-              ds[4 * w + t] = ds[4 * w + t] * (dp - delta) * p.scale;
+              ds[4 * w + t] = ds[4 * w + t] * (dp - delta);
             }
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) ds[j] = ds[j] * (__uint_as_float(rd[j]) - delta) * p.scale;
+          for (int j = 0; j < 32; ++j) ds[j] = ds[j] * (__uint_as_float(rd[j]) - delta);   // softmax scale: applied to dQ at the end
         }
+        uint32_t pk[16];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 d4;
-          d4.x = pack2(ds[8 * g + 0], ds[8 * g + 1]); d4.y = pack2(ds[8 * g + 2], ds[8 * g + 3]);
-          d4.z = pack2(ds[8 * g + 4], ds[8 * g + 5]); d4.w = pack2(ds[8 * g + 6], ds[8 * g + 7]);
-          st_swizzled(sDS, r, c * 4 + g, d4);
-        }
+        for (int j = 0; j < 16; ++j) pk[j] = pack2(ds[2 * j], ds[2 * j + 1]);
+        if (warp == 2) MTS_TRACE(2048 + 8 * i + 3 + 3 * c);
+        // the previous tile's dQ MMAs must have read dS before it is overwritten
+        if (c == 0 && !mbar_wait_warp(&ds_free, (i & 1) ^ 1, abort_ptr, lane)) { ok = false; break; }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) st_swizzled(sDS, r, c * 4 + g, make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]));
+        if (warp == 2) MTS_TRACE(2048 + 8 * i + 4 + 3 * c);
       }
-      epilogue_arrive(&st_free, lane);
+      if (!ok) break;
       fence_proxy_async_smem();
       epilogue_arrive(&ds_ready, lane);
     }
@@ -699,7 +816,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
       }
-      if (q_row < p.S) store_row64(p.dq + (long long)b * p.dq_sb + (long long)h * p.dq_sh + (long long)q_row * p.dq_ss, acc, 1.f);
+      if (q_row < p.S) store_row64(p.dq + (long long)b * p.dq_sb + (long long)h * p.dq_sh + (long long)q_row * p.dq_ss, acc, p.scale);
     }
   }
 
