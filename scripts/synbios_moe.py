@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""SynBioS experiment workflow.
+
+    prepare                generate profiles / biographies and tokenise them into training shards
+    token-statistics       length, vocabulary and first-token statistics of a generated dataset
+    cache-probes           build the memory-mapped probe cache (format 2)
+    validate-probe-cache   structural + lineage checks of a cache
+    evaluate               teacher-forced attribute recall of a trained model (model.pt)
+    cloze-evaluate         progressive greedy cloze generation of attribute values
+    summarize-cloze        merge cloze reports into one table
+    probe                  train one P / Q probe (resumable)
+    validate-probe         re-evaluate a trained probe from its saved weights
+    probe-pipeline         schedule all probe jobs over the available devices, then validate them
+    summarize-probes       collect probe results into a table
+    analyze                router analyses: NMI(attribute, expert), expert load, route Jaccard
+    report-formal-study    probe table + cloze table + router report of one study directory
+    audit-synbios-repository   lineage audit of dataset / cache / pipeline directories
+
+Evaluation and probing always build the model with the library (``torch``) operator back end in fp32 and load only the
+exported ``model.pt`` (reference: scripts/synbios_moe.py:141-168), independent of how training was sharded.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+from experiments.synbios_moe.pretraining.dataset import ATTRIBUTES, VARIANTS  # noqa: E402
+
+
+# ---------------------------------------------------------------------------------------------------------
+# shared helpers
+# ---------------------------------------------------------------------------------------------------------
+
+def load_backbone(model_config: str, checkpoint: str, device: str, *, codec_vocab: int | None = None):
+    import torch
+
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+    from mini_train_sys_b200.runtime.config import load_yaml_dict
+
+    payload = load_yaml_dict(model_config)
+    cfg = ModelConfig(**payload.get("model", payload))
+    if codec_vocab is not None and codec_vocab > cfg.vocab_size:
+        raise ValueError(f"the codec has {codec_vocab} tokens but the model only {cfg.vocab_size}")
+    model = MiniTransformer(cfg, get_ops_backend("torch"), activation_dtype=torch.float32)
+    state = torch.load(checkpoint, map_location="cpu", weights_only=False)
+    state = state.get("model", state) if isinstance(state, dict) else state
+    model.load_state_dict(state)
+    return model.to(device)
+
+
+class EventSink:
+    """``events.jsonl`` under ``--log-dir`` (the scheduler's heartbeat source) plus optional console lines."""
+
+    def __init__(self, log_dir: str | None, quiet: bool) -> None:
+        self.quiet = quiet
+        self.handle = None
+        if log_dir:
+            Path(log_dir).mkdir(parents=True, exist_ok=True)
+            self.handle = open(Path(log_dir) / "events.jsonl", "a", buffering=1)
+
+    def __call__(self, event: dict) -> None:
+        event = {"time": time.time(), **event}
+        if self.handle:
+            self.handle.write(json.dumps(event, default=str) + "\n")
+        if not self.quiet:
+            print(json.dumps(event, default=str), flush=True)
+
+
+def _codec(args):
+    from experiments.synbios_moe.codec import get_codec
+
+    return get_codec(args.codec)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# handlers
+# ---------------------------------------------------------------------------------------------------------
+
+def cmd_prepare(args) -> int:
+    from experiments.synbios_moe.pretraining.dataset import write_dataset
+    from mini_train_sys_b200.data.documents import CleaningConfig
+    from mini_train_sys_b200.data.preprocess import prepare_token_shards
+
+    sink = EventSink(args.log_dir, args.quiet)
+    out = write_dataset(args.output, num_people=args.num_people, variant=args.variant, seed=args.seed)
+    sink({"event": "dataset_written", "path": str(out)})
+    if args.codec == "gpt2":
+        from mini_train_sys_b200.data.tokenizer import TiktokenTokenizer
+
+        tokenizer = TiktokenTokenizer("gpt2")
+    else:
+        from experiments.synbios_moe.codec import ShardTokenizer, get_codec
+
+        tokenizer = ShardTokenizer(get_codec(args.codec))
+    # one biography per line; nothing is filtered (min_chars=1) and everything trains (validation_fraction=0): the held-out
+    # half of the PEOPLE is a probe split, not a language-model validation split
+    shards = prepare_token_shards([out / "biographies.txt"], output_dir=out / "tokens", tokenizer=tokenizer,
+                                  cleaning=CleaningConfig(min_chars=1, exact_dedup=False), validation_fraction=0.0,
+                                  max_shard_tokens=args.max_shard_tokens)
+    sink({"event": "shards_written", "path": str(shards)})
+    return 0
+
+
+def cmd_token_statistics(args) -> int:
+    from experiments.synbios_moe.artifact_io import read_jsonl, write_json
+    from experiments.synbios_moe.pretraining.token_statistics import dataset_token_statistics
+
+    root = Path(args.data)
+    stats = dataset_token_statistics(_codec(args), read_jsonl(root / "biographies.jsonl"), read_jsonl(root / "profiles.jsonl"))
+    write_json(args.output, stats)
+    print(json.dumps({k: v for k, v in stats.items() if k != "attributes"}))
+    return 0
+
+
+def cmd_cache_probes(args) -> int:
+    from experiments.synbios_moe.probes.dataset import build_probe_cache
+
+    path = build_probe_cache(args.data, args.output, codec_name=args.codec, force=args.force, require_coverage=args.require_coverage)
+    print(json.dumps({"probe_cache": str(path)}))
+    return 0
+
+
+def cmd_validate_probe_cache(args) -> int:
+    from experiments.synbios_moe.probes.dataset import validate_probe_cache
+
+    verdict = validate_probe_cache(args.probe_cache, args.data)
+    print(json.dumps(verdict))
+    return 0 if verdict["ok"] else 1
+
+
+def cmd_evaluate(args) -> int:
+    from experiments.synbios_moe.artifact_io import read_jsonl, write_json
+    from experiments.synbios_moe.pretraining.attribute_recall import evaluate_attribute_recall
+
+    codec = _codec(args)
+    model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
+    report = evaluate_attribute_recall(model, codec, read_jsonl(Path(args.data) / "biographies.jsonl"), device=args.device,
+                                       batch_size=args.batch_size, max_items=args.max_items)
+    write_json(args.output, report)
+    print(json.dumps(report["overall"]))
+    return 0
+
+
+def cmd_cloze(args) -> int:
+    from experiments.synbios_moe.artifact_io import read_jsonl, write_json
+    from experiments.synbios_moe.pretraining.cloze import evaluate_cloze
+
+    codec = _codec(args)
+    model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
+    report = evaluate_cloze(model, codec, read_jsonl(Path(args.data) / "biographies.jsonl"), device=args.device,
+                            batch_size=args.batch_size, max_items=args.max_items)
+    write_json(args.output, report)
+    print(json.dumps({"overall_exact_match": report["overall_exact_match"], "items": report["items"]}))
+    return 0
+
+
+def cmd_summarize_cloze(args) -> int:
+    from experiments.synbios_moe.artifact_io import read_json, write_csv
+    from experiments.synbios_moe.pretraining.cloze import summarize_cloze
+
+    rows = summarize_cloze({Path(p).stem: read_json(p) for p in args.reports})
+    write_csv(args.output, rows, ["run", "attribute", "exact_match", "first_token", "token_accuracy", "items"])
+    print(json.dumps({"rows": len(rows), "output": args.output}))
+    return 0
+
+
+def cmd_probe(args) -> int:
+    from experiments.synbios_moe.artifact_io import sha256_file
+    from experiments.synbios_moe.probes.model import save_probe_result, train_probe
+
+    sink = EventSink(args.log_dir, args.quiet)
+    codec = _codec(args)
+    model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
+    cache = args.probe_cache or str(Path(args.data) / "probe_cache")
+    identity = {"checkpoint_sha256": args.checkpoint_model_sha256 or sha256_file(args.checkpoint), "codec": args.codec}
+    result = train_probe(model, cache, kind=args.kind, attribute=args.attribute, target=args.target, steps=args.steps, device=args.device,
+                         rank=args.rank, batch_size=args.batch_size, evaluation_batch_size=args.evaluation_batch_size, seed=args.seed,
+                         recovery_checkpoint=args.recovery_checkpoint, checkpoint_interval_steps=args.checkpoint_interval_steps,
+                         resume=args.resume_probe, evaluate_train=args.evaluate_train, skip_final_validation=args.skip_final_validation,
+                         identity=identity, on_event=sink, max_eval_items=args.max_eval_items)
+    out = Path(args.output)
+    save_probe_result(result, out, out.with_suffix(".pt"))
+    sink({"event": "probe_done", "output": str(out), "validation": result.get("validation", {}).get("accuracy")})
+    return 0
+
+
+def cmd_validate_probe(args) -> int:
+    from experiments.synbios_moe.artifact_io import write_json
+    from experiments.synbios_moe.probes.model import validate_saved_probe
+
+    codec = _codec(args)
+    model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
+    verdict = validate_saved_probe(model, args.probe_cache, args.probe_state, device=args.device, max_items=args.max_eval_items)
+    write_json(args.output, verdict)
+    if not args.quiet:
+        print(json.dumps(verdict["validation"]))
+    return 0
+
+
+def cmd_probe_pipeline(args) -> int:
+    """Stages ``smoke`` -> ``pilot`` -> ``formal`` of ``configs/synbios_moe/probe_pipeline.yaml``: a stage needs the marker of
+    the stage it ``requires``; an optional cloze gate refuses to probe a model that has not memorised the biographies."""
+
+    import yaml
+
+    from experiments.synbios_moe.artifact_io import read_jsonl, write_json
+    from experiments.synbios_moe.probes.commands import all_training_jobs, validation_job
+    from experiments.synbios_moe.probes.pipeline import pipeline_identity, run_pipeline
+    from experiments.synbios_moe.probes.results import summarize_probe_results
+
+    settings = yaml.safe_load(Path(args.config).read_text()) if args.config else {}
+    stage = settings.get("stages", {}).get(args.stage, {})
+    runtime = settings.get("runtime", {})
+    steps = args.steps or stage.get("steps", {"smoke": 20, "pilot": 2000, "formal": 30000}[args.stage])
+    root = Path(args.output)
+    root.mkdir(parents=True, exist_ok=True)
+    required = stage.get("requires")
+    if required and not args.skip_requirements and not (root.parent / required / "STAGE_OK").is_file():
+        print(json.dumps({"error": f"stage {args.stage!r} requires a finished {required!r} stage at {root.parent / required}"}))
+        return 3
+    gate = settings.get("gate")
+    if gate and not args.skip_gate:
+        from experiments.synbios_moe.pretraining.cloze import evaluate_cloze
+
+        codec = _codec(args)
+        model = load_backbone(args.model_config, args.checkpoint, args.device.split(",")[0], codec_vocab=codec.vocab_size)
+        rows = read_jsonl(Path(args.data) / "biographies.jsonl")
+        report = evaluate_cloze(model, codec, rows, device=args.device, batch_size=int(gate.get("batch_size", 128)),
+                                max_items=int(gate.get("sample_biographies", 12)))
+        verdict = {"exact_match": report["overall_exact_match"], "threshold": gate.get("threshold", 0.9), "items": report["items"]}
+        verdict["passed"] = verdict["exact_match"] >= verdict["threshold"]
+        write_json(root / "gate.json", verdict)
+        del model
+        if not verdict["passed"]:
+            print(json.dumps({"error": "cloze gate failed", **verdict}))
+            return 3
+    ranks = {"p": args.p_rank, "q": args.q_rank}
+    batches = runtime.get("training_batch_sizes", {})
+    devices = args.devices.split(",")
+    hyper = {"stage": args.stage, "steps": steps, "ranks": ranks, "batches": batches, "seed": args.seed, "codec": args.codec,
+             "tasks": stage.get("tasks", "all")}
+    identity = pipeline_identity(checkpoint=args.checkpoint, probe_cache=args.probe_cache, model_config=args.model_config, settings=hyper)
+    extra = ("--max-eval-items", str(args.max_eval_items)) if args.max_eval_items else ()
+    training = all_training_jobs(root, kinds=tuple(args.kinds.split(",")), tasks=stage.get("tasks", "all"), data=args.data,
+                                 probe_cache=args.probe_cache, model_config=args.model_config, checkpoint=args.checkpoint, steps=steps,
+                                 ranks=ranks, batch_sizes=batches, evaluation_batch_sizes=runtime.get("validation_batch_sizes", {}),
+                                 evaluate_train=bool(runtime.get("evaluate_train", False)), seed=args.seed,
+                                 checkpoint_interval_steps=args.checkpoint_interval_steps or runtime.get("checkpoint_interval_steps"),
+                                 codec=args.codec, extra=extra)
+    if args.attributes:
+        keep = set(args.attributes.split(","))
+        training = [j for j in training if j.metadata["attribute"] in keep]
+    validation = [validation_job(root, j, data=args.data, probe_cache=args.probe_cache, model_config=args.model_config,
+                                 checkpoint=args.checkpoint, codec=args.codec) for j in training]
+    heartbeat = args.heartbeat_seconds or float(runtime.get("heartbeat_seconds", 30))
+    summary = run_pipeline(root, training, validation, devices=devices, identity=identity, heartbeat_seconds=heartbeat,
+                           on_heartbeat=None if args.quiet else (lambda name, ev: print(json.dumps({"job": name, "last_event": ev}), flush=True)))
+    summary["results"] = summarize_probe_results(root)["mean_accuracy"]
+    if summary["ok"]:
+        (root / "STAGE_OK").write_text(identity + "\n")
+    print(json.dumps(summary, default=str))
+    return 0 if summary["ok"] else 1
+
+
+def cmd_summarize_probes(args) -> int:
+    from experiments.synbios_moe.artifact_io import write_csv
+    from experiments.synbios_moe.probes.results import summarize_probe_results
+
+    summary = summarize_probe_results(args.root)
+    if args.output:
+        write_csv(args.output, summary["rows"])
+    print(json.dumps({k: v for k, v in summary.items() if k != "rows"}))
+    return 0
+
+
+def cmd_analyze(args) -> int:
+    from experiments.synbios_moe.artifact_io import read_jsonl, write_json
+    from experiments.synbios_moe.mechanisms.token_routes import collect_token_routes, route_report
+
+    codec = _codec(args)
+    model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
+    if not model.cfg.is_moe:
+        print(json.dumps({"error": "router analyses need an MoE model"}))
+        return 2
+    collected = collect_token_routes(model, codec, read_jsonl(Path(args.data) / "biographies.jsonl"), device=args.device,
+                                     max_items=args.max_items or 256)
+    report = route_report(collected, model.cfg.num_experts)
+    write_json(args.output, {str(k): v for k, v in report.items()})
+    print(json.dumps({str(k): v["nmi_attribute_expert"] for k, v in report.items()}))
+    return 0
+
+
+def cmd_report(args) -> int:
+    from experiments.synbios_moe.artifact_io import read_json, write_json
+    from experiments.synbios_moe.probes.results import summarize_probe_results
+
+    root = Path(args.root)
+    report = {"probes": summarize_probe_results(root / "probes") if (root / "probes" / "training").is_dir() else None}
+    for name in ("cloze", "recall", "routes", "token_statistics"):
+        path = root / f"{name}.json"
+        report[name] = read_json(path) if path.is_file() else None
+    write_json(args.output, report)
+    print(json.dumps({k: v is not None for k, v in report.items()}))
+    return 0
+
+
+def cmd_audit(args) -> int:
+    from experiments.synbios_moe.audit import audit_study
+
+    verdict = audit_study(data_root=args.data, probe_cache=args.probe_cache, pipeline_root=args.pipeline)
+    print(json.dumps(verdict, indent=1))
+    return 0 if verdict["ok"] else 1
+
+
+# ---------------------------------------------------------------------------------------------------------
+# argument tree
+# ---------------------------------------------------------------------------------------------------------
+
+def build_parser() -> argparse.ArgumentParser:
+    import torch
+
+    default_device = "cuda" if torch.cuda.is_available() else "cpu"
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="command", required=True)
+
+    def common(p, *, model=True, monitoring=True):
+        p.add_argument("--codec", choices=("gpt2", "bytes"), default="gpt2")
+        if model:
+            p.add_argument("--model-config", required=True)
+            p.add_argument("--checkpoint", required=True, help="exported model.pt")
+            p.add_argument("--device", default=default_device)
+        if monitoring:
+            p.add_argument("--log-dir")
+            p.add_argument("--quiet", action="store_true")
+
+    p = sub.add_parser("prepare"); common(p, model=False)
+    p.add_argument("--output", required=True); p.add_argument("--variant", default="single", choices=VARIANTS)
+    p.add_argument("--num-people", type=int, default=100_000); p.add_argument("--seed", type=int, default=1337)
+    p.add_argument("--max-shard-tokens", type=int, default=10_000_000); p.set_defaults(func=cmd_prepare)
+
+    p = sub.add_parser("token-statistics"); common(p, model=False, monitoring=False)
+    p.add_argument("--data", required=True); p.add_argument("--output", required=True); p.set_defaults(func=cmd_token_statistics)
+
+    p = sub.add_parser("cache-probes"); common(p, model=False, monitoring=False)
+    p.add_argument("--data", required=True); p.add_argument("--output", required=True); p.add_argument("--force", action="store_true")
+    p.add_argument("--require-coverage", action="store_true"); p.set_defaults(func=cmd_cache_probes)
+
+    p = sub.add_parser("validate-probe-cache"); p.add_argument("--probe-cache", required=True); p.add_argument("--data")
+    p.set_defaults(func=cmd_validate_probe_cache)
+
+    for name, fn in (("evaluate", cmd_evaluate), ("cloze-evaluate", cmd_cloze), ("analyze", cmd_analyze)):
+        p = sub.add_parser(name); common(p)
+        p.add_argument("--data", required=True); p.add_argument("--output", required=True)
+        p.add_argument("--batch-size", type=int, default=32); p.add_argument("--max-items", type=int); p.set_defaults(func=fn)
+
+    p = sub.add_parser("summarize-cloze"); p.add_argument("reports", nargs="+"); p.add_argument("--output", required=True)
+    p.set_defaults(func=cmd_summarize_cloze)
+
+    p = sub.add_parser("probe"); common(p)
+    p.add_argument("--data", required=True); p.add_argument("--probe-cache"); p.add_argument("--output", required=True)
+    p.add_argument("--attribute", choices=ATTRIBUTES, required=True); p.add_argument("--target", choices=("first", "whole"), default="first")
+    p.add_argument("--kind", choices=("p", "q"), required=True); p.add_argument("--rank", type=int)
+    p.add_argument("--checkpoint-model-sha256", help=argparse.SUPPRESS)
+    p.add_argument("--batch-size", type=int); p.add_argument("--evaluation-batch-size", type=int)
+    p.add_argument("--steps", type=int, default=30_000); p.add_argument("--seed", type=int, default=1337)
+    p.add_argument("--recovery-checkpoint"); p.add_argument("--checkpoint-interval-steps", type=int)
+    p.add_argument("--resume-probe", action=argparse.BooleanOptionalAction, default=True)
+    p.add_argument("--evaluate-train", action="store_true"); p.add_argument("--skip-final-validation", action="store_true")
+    p.add_argument("--max-eval-items", type=int); p.set_defaults(func=cmd_probe)
+
+    p = sub.add_parser("validate-probe"); common(p)
+    p.add_argument("--probe-cache", required=True); p.add_argument("--probe-state", required=True); p.add_argument("--output", required=True)
+    p.add_argument("--max-eval-items", type=int); p.set_defaults(func=cmd_validate_probe)
+
+    p = sub.add_parser("probe-pipeline"); common(p)
+    p.add_argument("--data", required=True); p.add_argument("--probe-cache", required=True); p.add_argument("--output", required=True)
+    p.add_argument("--stage", choices=("smoke", "pilot", "formal"), required=True); p.add_argument("--config")
+    p.add_argument("--devices", default=default_device); p.add_argument("--kinds", default="p,q"); p.add_argument("--attributes")
+    p.add_argument("--steps", type=int); p.add_argument("--seed", type=int, default=1337)
+    p.add_argument("--checkpoint-interval-steps", type=int); p.add_argument("--heartbeat-seconds", type=float)
+    p.add_argument("--p-rank", type=int); p.add_argument("--q-rank", type=int)
+    p.add_argument("--skip-gate", action="store_true"); p.add_argument("--skip-requirements", action="store_true")
+    p.add_argument("--max-eval-items", type=int); p.set_defaults(func=cmd_probe_pipeline)
+
+    p = sub.add_parser("summarize-probes"); p.add_argument("root"); p.add_argument("--output"); p.set_defaults(func=cmd_summarize_probes)
+    p = sub.add_parser("report-formal-study"); p.add_argument("root"); p.add_argument("--output", required=True); p.set_defaults(func=cmd_report)
+    p = sub.add_parser("audit-synbios-repository"); p.add_argument("--data"); p.add_argument("--probe-cache"); p.add_argument("--pipeline")
+    p.set_defaults(func=cmd_audit)
+    return ap
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    return int(args.func(args) or 0)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,215 @@
+"""SynBioS layer end to end on CPU with the byte codec and a tiny MoE model."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+CLI = [sys.executable, str(ROOT / "scripts" / "synbios_moe.py")]
+
+
+@pytest.fixture(scope="module")
+def study(tmp_path_factory):
+    """dataset (multi2+permute, 24 people) -> shards -> probe cache -> randomly initialised model.pt"""
+
+    root = tmp_path_factory.mktemp("synbios")
+    data = root / "data"
+    run = lambda *a: subprocess.run([*CLI, *a], capture_output=True, text=True, timeout=600)   # noqa: E731
+    out = run("prepare", "--output", str(data), "--variant", "multi2+permute", "--num-people", "24", "--codec", "bytes", "--quiet")
+    assert out.returncode == 0, out.stderr[-2000:]
+    out = run("cache-probes", "--data", str(data), "--output", str(root / "cache"), "--codec", "bytes")
+    assert out.returncode == 0, out.stderr[-2000:]
+    cfg = {"model": {"vocab_size": 257, "seq_len": 512, "n_layers": 2, "n_heads": 2, "hidden_size": 32, "intermediate_size": 32,
+                     "ffn_type": "moe", "num_experts": 4, "experts_per_token": 2, "dropout": 0.0}}
+    (root / "model.yaml").write_text(json.dumps(cfg))      # JSON is YAML
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+
+    torch.manual_seed(0)
+    model = MiniTransformer(ModelConfig(**cfg["model"]), get_ops_backend("torch"), activation_dtype=torch.float32)
+    torch.save(model.state_dict(), root / "model.pt")
+    return {"root": root, "data": data, "cache": root / "cache", "model_config": root / "model.yaml", "checkpoint": root / "model.pt", "run": run}
+
+
+def test_profiles_are_identical_across_variants_and_spans_are_exact(tmp_path):
+    from experiments.synbios_moe.pretraining.dataset import ATTRIBUTES, VARIANTS, entries_per_person, write_dataset
+
+    a = write_dataset(tmp_path / "a", num_people=30, variant="single", seed=7)
+    b = write_dataset(tmp_path / "b", num_people=30, variant="multi5+permute", seed=7)
+    assert (a / "profiles.jsonl").read_bytes() == (b / "profiles.jsonl").read_bytes()
+    profiles = {json.loads(l)["person_id"]: json.loads(l) for l in (b / "profiles.jsonl").read_text().splitlines()}
+    bios = [json.loads(l) for l in (b / "biographies.jsonl").read_text().splitlines()]
+    assert len(bios) == 30 * 5 and entries_per_person("single+permute5") == 5 and len(VARIANTS) == 9
+    orders = set()
+    for bio in bios:
+        for attribute in ATTRIBUTES:
+            lo, hi = bio["attribute_spans"][attribute]
+            assert bio["text"][lo:hi] == profiles[bio["person_id"]][attribute]
+        orders.add(tuple(sorted(ATTRIBUTES, key=lambda x: bio["attribute_spans"][x][0])))
+        assert bio["text"].count(profiles[bio["person_id"]]["full_name"]) == 1     # the name appears once, in the first sentence
+    assert len(orders) > 5                                                            # sentences really are permuted
+    assert {p["split"] for p in profiles.values()} == {"train", "validation"}
+    # regenerating gives byte-identical files
+    c = write_dataset(tmp_path / "c", num_people=30, variant="multi5+permute", seed=7)
+    assert (b / "biographies.jsonl").read_bytes() == (c / "biographies.jsonl").read_bytes()
+
+
+def test_prepare_writes_shards_and_manifest(study):
+    manifest = json.loads((study["data"] / "tokens" / "manifest.json").read_text())
+    assert manifest["vocab_size"] == 257 and (study["data"] / "tokens" / "train" / "shard_00000.bin").is_file()
+    assert json.loads((study["data"] / "manifest.json").read_text())["num_biographies"] == 48
+
+
+def test_probe_cache_layout_and_validation(study):
+    from experiments.synbios_moe.probes.dataset import CachedProbeDataset, validate_probe_cache
+
+    cache = study["cache"]
+    verdict = validate_probe_cache(cache, study["data"])
+    assert verdict["ok"], verdict
+    assert np.load(cache / "profile_labels.npy").shape == (24, 11)
+    assert np.load(cache / "p_positions.npy").shape == (48, 6)
+    ds = CachedProbeDataset(cache, kind="p", attribute="university", target="whole", split="train")
+    item = ds[0]
+    assert item.positions.shape == (6,) and (np.diff(item.positions) > 0).all() and item.input_ids[0] == 256
+    q = CachedProbeDataset(cache, kind="q", attribute="birth_date", target="first", split="validation")
+    assert q[0].positions.tolist() == [q[0].input_ids.shape[0] - 1] and set(q.class_names) <= {
+        "January", "February", "March", "April", "May", "June", "July", "August", "September", "October", "November", "December"}
+    # the byte before every P position ends right before the value: decode and compare
+    from experiments.synbios_moe.codec import ByteCodec
+    bios = [json.loads(l) for l in (study["data"] / "biographies.jsonl").read_text().splitlines()]
+    ids = np.memmap(cache / "p_tokens.bin", dtype="<i4", mode="r")
+    off = np.load(cache / "p_offsets.npy"); pos = np.load(cache / "p_positions.npy")
+    text0 = ByteCodec().decode(ids[off[0]:off[1]].tolist())
+    assert text0 == bios[0]["text"]
+    starts = sorted(v[0] for v in bios[0]["attribute_spans"].values())
+    assert pos[0].tolist() == starts            # byte codec: position p (EOS at 0) is the token that ends at character p
+    # tampering is detected
+    (cache / "q_offsets.npy").write_bytes((cache / "q_offsets.npy").read_bytes()[:-8] + b"\0" * 8)
+    assert not validate_probe_cache(cache)["ok"]
+
+
+def test_recall_cloze_and_router_reports(study):
+    run = study["run"]
+    common = ["--data", str(study["data"]), "--model-config", str(study["model_config"]), "--checkpoint", str(study["checkpoint"]),
+              "--codec", "bytes", "--device", "cpu", "--max-items", "6"]
+    out = run("evaluate", *common, "--output", str(study["root"] / "recall.json"))
+    assert out.returncode == 0, out.stderr[-2000:]
+    recall = json.loads((study["root"] / "recall.json").read_text())
+    assert recall["overall"]["values"] == 36 and 0.0 <= recall["overall"]["token_accuracy"] <= 1.0
+    out = run("cloze-evaluate", *common, "--output", str(study["root"] / "cloze.json"), "--batch-size", "4")
+    assert out.returncode == 0, out.stderr[-2000:]
+    cloze = json.loads((study["root"] / "cloze.json").read_text())
+    assert cloze["items"] == 36 and set(cloze["per_attribute"]) == {"birth_date", "birth_city", "university", "major", "company", "company_city"}
+    out = run("analyze", *common, "--output", str(study["root"] / "routes.json"))
+    assert out.returncode == 0, out.stderr[-2000:]
+    routes = json.loads((study["root"] / "routes.json").read_text())
+    assert set(routes) == {"0", "1"} and 0.0 <= routes["0"]["nmi_attribute_expert"] <= 1.0
+    assert abs(sum(routes["0"]["value_token_load"]) - 1.0) < 1e-6 and routes["0"]["jaccard_same_fact"] is not None
+
+
+def test_cloze_of_a_memorising_model_is_exact():
+    """A 'model' that already knows the text must score 100 %: checks prompt / answer alignment and the decode loop."""
+
+    from experiments.synbios_moe.codec import ByteCodec
+    from experiments.synbios_moe.pretraining.cloze import evaluate_cloze
+    from experiments.synbios_moe.pretraining.dataset import generate_profiles, render_biography
+
+    codec = ByteCodec()
+    profiles = generate_profiles(3, 5)
+    rows = []
+    for p in profiles:
+        bio = render_biography(p, variant="single", sample=0, seed=5)
+        rows.append({"person_id": p.person_id, "text": bio.text, "attribute_spans": bio.attribute_spans})
+    texts = [[codec.eos, *codec.encode(r["text"])] for r in rows]
+
+    class Oracle(torch.nn.Module):
+        class cfg:  # noqa: N801
+            seq_len = 4096
+
+        def hidden_states(self, ids):
+            out = torch.zeros(ids.shape[0], ids.shape[1], 257)
+            for b in range(ids.shape[0]):
+                for t in range(ids.shape[1]):
+                    prefix = ids[b, :t + 1].tolist()
+                    for full in texts:
+                        if full[:t + 1] == prefix and len(full) > t + 1:
+                            out[b, t, full[t + 1]] = 1.0
+                            break
+            return out
+
+        def lm_head(self, h):
+            return h
+
+        def forward(self, ids):
+            return self.hidden_states(ids)
+
+    report = evaluate_cloze(Oracle(), codec, rows, batch_size=5)
+    assert report["overall_exact_match"] == 1.0 and report["items"] == 18
+    from experiments.synbios_moe.pretraining.attribute_recall import evaluate_attribute_recall
+
+    recall = evaluate_attribute_recall(Oracle(), codec, rows)
+    assert recall["overall"]["token_accuracy"] == 1.0 and recall["company"]["whole_value_accuracy"] == 1.0
+
+
+def test_probe_training_resumes_with_identical_result(study, tmp_path):
+    from experiments.synbios_moe.probes.model import train_probe
+    from scripts.synbios_moe import load_backbone
+
+    def backbone():
+        return load_backbone(str(study["model_config"]), str(study["checkpoint"]), "cpu")
+
+    kw = dict(kind="q", attribute="company_city", target="whole", steps=6, batch_size=4, seed=3, max_eval_items=8)
+    full = train_probe(backbone(), study["cache"], **kw)
+    rec = tmp_path / "rec.pt"
+
+    class Stop(Exception):
+        pass
+
+    def interrupt(event):
+        if event["event"] == "probe_train" and event["step"] == 6:
+            raise AssertionError("should not get here in the interrupted run")
+
+    # run 3 steps (checkpoint every 3), then "crash": emulate by asking for steps=6 but stopping via a short first run
+    first = train_probe(backbone(), study["cache"], **{**kw}, recovery_checkpoint=rec, checkpoint_interval_steps=3,
+                        on_event=lambda e: (_ for _ in ()).throw(Stop()) if e["event"] == "probe_train" and e.get("step") == 10 else None)
+    assert rec.is_file()                                 # written at step 3
+    resumed = train_probe(backbone(), study["cache"], **kw, recovery_checkpoint=rec, checkpoint_interval_steps=3)
+    # the recovery file holds step 3: the resumed run replays steps 4..6 with the same batches and lr
+    for k, v in full["probe_state"].items():
+        assert torch.allclose(v.float(), resumed["probe_state"][k].float(), atol=1e-6), k
+    assert first["final_loss"] == pytest.approx(full["final_loss"])
+    with pytest.raises(ValueError):
+        train_probe(backbone(), study["cache"], **{**kw, "seed": 4}, recovery_checkpoint=rec)      # another job's checkpoint
+
+
+def test_probe_pipeline_schedules_validates_and_skips_fresh_jobs(study, tmp_path):
+    run = study["run"]
+    args = ["probe-pipeline", "--data", str(study["data"]), "--probe-cache", str(study["cache"]), "--model-config", str(study["model_config"]),
+            "--checkpoint", str(study["checkpoint"]), "--codec", "bytes", "--device", "cpu", "--devices", "cpu,cpu", "--stage", "smoke",
+            "--steps", "3", "--attributes", "major", "--output", str(tmp_path / "pipe"), "--heartbeat-seconds", "1", "--max-eval-items", "8",
+            "--quiet"]
+    out = run(*args)
+    assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-1500:])
+    summary = json.loads(out.stdout.strip().splitlines()[-1])
+    assert summary["ok"] and set(summary["training"]) == {"p-major-first", "p-major-whole", "q-major-first", "q-major-whole"}
+    state = json.loads((tmp_path / "pipe" / "pipeline.json").read_text())
+    assert all(j["status"] == "done" for j in state["jobs"].values()) and len(state["jobs"]) == 8
+    assert (tmp_path / "pipe" / "training" / "p-major-whole.pt").is_file() and (tmp_path / "pipe" / "validation" / "q-major-first.json").is_file()
+    again = json.loads(run(*args).stdout.strip().splitlines()[-1])
+    assert set(again["training"].values()) == {"skipped"} and set(again["validation"].values()) == {"skipped"}
+    out = run("summarize-probes", str(tmp_path / "pipe"), "--output", str(tmp_path / "table.csv"))
+    assert out.returncode == 0 and json.loads(out.stdout.strip().splitlines()[-1])["jobs"] == 4
+    audit = run("audit-synbios-repository", "--data", str(study["data"]), "--pipeline", str(tmp_path / "pipe"))
+    assert audit.returncode == 0, audit.stdout
+
+
+def test_nmi_extremes():
+    from experiments.synbios_moe.mechanisms.routing import normalized_mutual_information
+
+    labels = torch.tensor([0, 0, 1, 1, 2, 2, -1])
+    assert normalized_mutual_information(labels, torch.tensor([0, 0, 1, 1, 2, 2, 3]), 4) == pytest.approx(1.0)
+    assert normalized_mutual_information(torch.tensor([0, 1, 0, 1]), torch.tensor([0, 0, 1, 1]), 2) == pytest.approx(0.0, abs=1e-9)
