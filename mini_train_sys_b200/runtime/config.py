@@ -89,11 +89,14 @@ class CommConfig:
     wait_timeout_ms: int = 2000
     prefetch_units: int = 1
     use_multimem: bool = False
+    health_check: bool = False            # host-side heartbeats through the process-group store, checked before every step
+    health_max_age_seconds: float = 300.0
 
     def __post_init__(self) -> None:
         _require(self.engine in ("auto", "fused", "nccl"), "parallel.comm.engine must be auto, fused, or nccl")
         _require(self.wait_timeout_ms > 0, "parallel.comm.wait_timeout_ms must be positive")
         _require(self.prefetch_units >= 0, "parallel.comm.prefetch_units must be non-negative")
+        _require(self.health_max_age_seconds > 0, "parallel.comm.health_max_age_seconds must be positive")
 
 
 @dataclass(frozen=True)

@@ -16,6 +16,7 @@ from typing import Any
 
 import torch
 
+from mini_train_sys_b200.runtime.health import PeerLostError, RankHealth
 from mini_train_sys_b200.models.config import ModelConfig
 from mini_train_sys_b200.parallel.strategy import ParallelStrategy
 from mini_train_sys_b200.runtime.config import ExperimentConfig
@@ -167,6 +168,8 @@ class TrainingRunner:
         last_saved = resume_path
         epochs_limit = self.cfg.train.epochs
 
+        comm = self.cfg.parallel.comm
+        health = RankHealth() if (comm.health_check and self.world_size > 1) else None
         while not done and (epochs_limit is None or epoch < epochs_limit):
             epoch += 1
             sampler = getattr(self.dataloader, "sampler", None)
@@ -179,7 +182,17 @@ class TrainingRunner:
                 t_wait = time.perf_counter()
                 batch = next(stream)
                 iv.data_wait += time.perf_counter() - t_wait
+                if health is not None:
+                    # on the host, with nothing of this rank in flight: a peer that left or fell silent ends the run here
+                    # instead of in a device-side wait or a collective timeout
+                    try:
+                        health.check(max_age_seconds=comm.health_max_age_seconds)
+                    except PeerLostError as exc:
+                        self.logger.log_event({"event": "peer_lost", "step": st.step, "detail": str(exc)})
+                        raise SystemExit(3) from exc
                 loss = self.trainer.train_step(batch)
+                if health is not None:
+                    health.beat(st.step)
                 iv.add(iv.scalars, {"loss": loss})
                 iv.add(iv.scalars, self.trainer.last_metrics)
                 iv.add(iv.images, self.trainer.last_visualizations)
