@@ -30,7 +30,7 @@ def test_every_shipped_run_and_model_yaml_loads():
         elif path.parent.name == "runs" or path.name.startswith("train_") or path.name.endswith("_pretrain.yaml"):
             payload.pop("model", None)
             cfg = cfgmod.experiment_config_from_dict(payload)   # complete run files validate as a whole
-            assert cfg.parallel.strategy in ("single", "ddp", "fsdp")
+            assert cfg.parallel.strategy in ("single", "ddp", "fsdp", "ep")
             runs += 1
     assert models >= 7 and runs >= 10
 
