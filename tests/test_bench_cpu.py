@@ -121,3 +121,34 @@ def test_weak_suite_end_to_end_on_gloo(tmp_path):
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
     again = json.loads((tmp_path / "weak" / "summary.json").read_text())
     assert all(r.get("reused") for r in again["rows"])
+
+
+def test_evidence_tooling_roundtrip(tmp_path):
+    """Catalogue, audit and manifest of a small results tree; the manifest check notices a changed file."""
+
+    tree = tmp_path / "results"
+    raw = tree / "distributed" / "weak" / "raw"
+    raw.mkdir(parents=True)
+    rows = []
+    for world, tps in ((1, 100.0), (2, 190.0)):
+        row = {**_rows(world, tps), "name": f"r{world}", "identity": f"id{world}", "timing": "cuda events per step, max over ranks",
+               "warmup_steps": 3}
+        (raw / f"r{world}.json").write_text(json.dumps(row))
+        rows.append(row)
+    from mini_train_sys_b200.bench.distributed import weak_scaling_table
+
+    (tree / "distributed" / "weak" / "summary.json").write_text(json.dumps({"suite": "weak", "rows": rows, "weak": weak_scaling_table(rows),
+                                                                           "quality_gates": {"passed": True}}))
+    (tree / "bench.json").write_text(json.dumps({"metric": "tokens/sec", "value": 1.0, "n_gpus": 1}))
+    run = lambda *a: subprocess.run([sys.executable, *a], capture_output=True, text=True, timeout=300)   # noqa: E731
+    out = run(str(ROOT / "scripts" / "build_results_catalog.py"), str(tree))
+    assert out.returncode == 0 and json.loads(out.stdout)["kinds"] == {"distributed/weak": 1, "bench": 1, "json": 2}, out.stdout + out.stderr
+    assert run(str(ROOT / "scripts" / "audit_results_export.py"), str(tree)).returncode == 0
+    assert run(str(ROOT / "scripts" / "build_results_manifest.py"), str(tree)).returncode == 0
+    assert run(str(ROOT / "scripts" / "build_results_manifest.py"), str(tree), "--check").returncode == 0
+    (tree / "bench.json").write_text("{}")
+    bad = run(str(ROOT / "scripts" / "build_results_manifest.py"), str(tree), "--check")
+    assert bad.returncode == 1 and "bench.json" in bad.stdout
+    rows[1]["identity"] = "tampered"
+    (tree / "distributed" / "weak" / "summary.json").write_text(json.dumps({"suite": "weak", "rows": rows, "weak": weak_scaling_table(rows)}))
+    assert run(str(ROOT / "scripts" / "audit_results_export.py"), str(tree)).returncode == 1
