@@ -308,7 +308,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tmem_st_wait();
         }
       }
-      float rowsum = 0.f;
+      float rowsum[8];                          // eight independent partial sums: one accumulator would chain 128 dependent adds
+#pragma unroll
+      for (int i = 0; i < 8; ++i) rowsum[i] = 0.f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t (&rr)[32] = c == 0 ? s0 : (c == 1 ? s1 : (c == 2 ? s2 : s3));
@@ -318,8 +320,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           float e[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            e[i] = ex2(__uint_as_float(rr[8 * g + i]) * scale_log2 - m);   // masked entries are -inf -> 0
-            rowsum += e[i];
+            e[i] = ex2(fmaf(__uint_as_float(rr[8 * g + i]), scale_log2, -m));   // masked entries are -inf -> 0
+            rowsum[i] += e[i];
           }
           if (drop.thresh != 0u) {
 #pragma unroll
@@ -335,7 +337,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           st_swizzled(half, r, (c & 1) * 4 + g, q4);
         }
       }
-      l += rowsum;
+      l += ((rowsum[0] + rowsum[1]) + (rowsum[2] + rowsum[3])) + ((rowsum[4] + rowsum[5]) + (rowsum[6] + rowsum[7]));
       if (warp == 2) MTS_TRACE(8 * j + 2);
       fence_proxy_async_smem();                  // P (generic-proxy stores) -> visible to the tensor core
       epilogue_arrive(&p_ready, lane);

@@ -121,6 +121,21 @@ std::vector<Tensor> swiglu_bwd(const Tensor& dy, const Tensor& g, const Tensor& 
   return {dg, du};
 }
 
+// out = residual + dropout(y); with an undefined residual: out = dropout(y) (this is also the backward of the y branch)
+Tensor dropout_add(const Tensor& y, const c10::optional<Tensor>& residual, double p, int64_t seed) {
+  check_act(y, "y");
+  TORCH_CHECK(y.is_contiguous() && y.numel() % 8 == 0, "dropout_add needs a contiguous tensor with numel % 8 == 0");
+  const bool has_res = residual.has_value() && residual->defined();
+  if (has_res)
+    TORCH_CHECK(residual->is_contiguous() && residual->sizes() == y.sizes() && residual->scalar_type() == y.scalar_type(),
+                "residual must match y");
+  c10::cuda::CUDAGuard guard(y.device());
+  Tensor out = torch::empty_like(y);
+  check_launch(mts::launch_dropout_add(y.data_ptr(), has_res ? residual->data_ptr() : nullptr, out.data_ptr(), y.numel(), float(p),
+                                       static_cast<unsigned long long>(seed), is_bf16(y), cur_stream()), "dropout_add");
+  return out;
+}
+
 Tensor cast_bf16(const Tensor& src) {
   TORCH_CHECK(src.is_cuda() && src.scalar_type() == at::kFloat && src.is_contiguous(), "cast_bf16 expects contiguous fp32");
   c10::cuda::CUDAGuard guard(src.device());
@@ -368,6 +383,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope", &rope);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("dropout_add", &dropout_add);
   m.def("cast_bf16", &cast_bf16);
   m.def("cast_bf16_into", &cast_bf16_into);
   m.def("gemm", &gemm);

@@ -291,4 +291,120 @@ cudaError_t launch_scalar_allreduce_clip(const float* local_value, const PeerPtr
   return cudaGetLastError();
 }
 
+
+// ---- expert-parallel exchange: rows pushed to the rank that owns their expert, results pulled back ---------------------
+//
+// Receive layout on every rank: `world` regions of `cap_rows` rows; region s belongs to source rank s, which fills slots
+// 0 .. count_s - 1 in its own route order and posts count_s.  A route is (token, destination rank, slot, expert local to
+// the destination).  One warp moves one row with 16-byte accesses; the destination pointer is the peer mapping of the
+// receiver's buffer, so the dispatch IS the all-to-all: no staging buffer, no library call.
+namespace {
+
+__global__ void __launch_bounds__(256)
+ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ route_token, const int* __restrict__ route_dest,
+                    const int* __restrict__ route_slot, const int* __restrict__ route_expert, const float* __restrict__ route_scale,
+                    int n_routes, int H, PeerPtrs recv_rows, PeerPtrs recv_expert, int src_rank, int cap_rows) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+  const int vec_per_row = H / 8;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n_routes; r += warps_per_grid) {
+    const int dest = route_dest[r];
+    if (dest < 0) continue;
+    const long long dst_row = (long long)src_rank * cap_rows + route_slot[r];
+    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)route_token[r] * H);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(recv_rows.p[dest]) + dst_row * H);
+    const float scale = route_scale != nullptr ? route_scale[r] : 1.f;
+    for (int v = lane; v < vec_per_row; v += 32) {
+      uint4 q = src[v];
+      if (route_scale != nullptr) {
+        uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&w[k]);
+          h = __floats2bfloat162_rn(__low2float(h) * scale, __high2float(h) * scale);
+          w[k] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        q = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      dst[v] = q;
+    }
+    if (lane == 0 && route_expert != nullptr) static_cast<int*>(recv_expert.p[dest])[dst_row] = route_expert[r];
+  }
+}
+
+// out[t] = sum_k weight[t, k] * rows_of(dest(t, k))[me * cap + slot(t, k)], read through the peers' mappings.  `saved`
+// (optional, [T * K, H]) keeps the pulled rows for the backward pass of the weights.
+__global__ void __launch_bounds__(256)
+ep_pull_combine_kernel(__nv_bfloat16* __restrict__ out, const int* __restrict__ token_dest, const int* __restrict__ token_slot,
+                       const float* __restrict__ weight, int T, int K, int H, PeerPtrs rows, int my_rank, int cap_rows,
+                       __nv_bfloat16* __restrict__ saved) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+  const int vec_per_row = H / 8;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps_per_grid) {
+    for (int v = lane; v < vec_per_row; v += 32) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int k = 0; k < K; ++k) {
+        const int dest = token_dest[t * K + k];
+        uint4 q = make_uint4(0u, 0u, 0u, 0u);
+        if (dest >= 0) {
+          const long long row = (long long)my_rank * cap_rows + token_slot[t * K + k];
+          q = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(rows.p[dest]) + row * H)[v];
+        }
+        if (saved != nullptr) reinterpret_cast<uint4*>(saved + ((long long)t * K + k) * H)[v] = q;
+        const float w = weight != nullptr ? weight[t * K + k] : 1.f;
+        const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&ww[j]);
+          acc[2 * j] += w * __low2float(h);
+          acc[2 * j + 1] += w * __high2float(h);
+        }
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        o[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      reinterpret_cast<uint4*>(out + (long long)t * H)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+__global__ void ep_post_counts_kernel(const int* __restrict__ counts, PeerPtrs recv_counts, int world, int src_rank) {
+  const int d = threadIdx.x;
+  if (d < world) static_cast<int*>(recv_counts.p[d])[src_rank] = counts[d];
+}
+
+}  // namespace
+
+cudaError_t launch_ep_push_rows(const void* x, const int* route_token, const int* route_dest, const int* route_slot,
+                                const int* route_expert, const float* route_scale, int n_routes, int H, const PeerPtrs& recv_rows,
+                                const PeerPtrs& recv_expert, const int* counts, const PeerPtrs& recv_counts, int world, int src_rank,
+                                int cap_rows, int max_ctas, cudaStream_t stream) {
+  if (H % 8 != 0) return cudaErrorInvalidValue;
+  if (counts != nullptr) ep_post_counts_kernel<<<1, 32, 0, stream>>>(counts, recv_counts, world, src_rank);
+  if (n_routes > 0) {
+    int grid = (n_routes + 7) / 8;
+    if (grid > max_ctas) grid = max_ctas;
+    ep_push_rows_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), route_token, route_dest, route_slot,
+                                                 route_expert, route_scale, n_routes, H, recv_rows, recv_expert, src_rank, cap_rows);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_pull_combine(void* out, const int* token_dest, const int* token_slot, const float* weight, int T, int K, int H,
+                                   const PeerPtrs& rows, int my_rank, int cap_rows, void* saved, int max_ctas, cudaStream_t stream) {
+  if (H % 8 != 0) return cudaErrorInvalidValue;
+  if (T <= 0) return cudaSuccess;
+  int grid = (T + 7) / 8;
+  if (grid > max_ctas) grid = max_ctas;
+  ep_pull_combine_kernel<<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(out), token_dest, token_slot, weight, T, K, H, rows,
+                                                  my_rank, cap_rows, static_cast<__nv_bfloat16*>(saved));
+  return cudaGetLastError();
+}
+
 }  // namespace mts

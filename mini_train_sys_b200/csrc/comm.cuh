@@ -36,4 +36,13 @@ cudaError_t launch_scalar_allreduce_clip(const float* local_value, const PeerPtr
                                          unsigned long long timeout_ns, float max_norm, float extra_scale, float* coef_out,
                                          float* norm_out, int* status, cudaStream_t stream);
 
+// Expert-parallel exchange over peer memory (see comm.cu): rows are stored straight into the owning rank's receive regions, results
+// are read back through the peers' mappings and combined.  `counts` (optional, [world]) is posted to every peer's `recv_counts[src]`.
+cudaError_t launch_ep_push_rows(const void* x, const int* route_token, const int* route_dest, const int* route_slot,
+                                const int* route_expert, const float* route_scale, int n_routes, int H, const PeerPtrs& recv_rows,
+                                const PeerPtrs& recv_expert, const int* counts, const PeerPtrs& recv_counts, int world, int src_rank,
+                                int cap_rows, int max_ctas, cudaStream_t stream);
+cudaError_t launch_ep_pull_combine(void* out, const int* token_dest, const int* token_slot, const float* weight, int T, int K, int H,
+                                   const PeerPtrs& rows, int my_rank, int cap_rows, void* saved, int max_ctas, cudaStream_t stream);
+
 }  // namespace mts

@@ -104,9 +104,66 @@ void comm_norm_clip(const Tensor& local_sumsq, const std::vector<int64_t>& slot_
                                        coef.data_ptr<float>(), norm.data_ptr<float>(), status.data_ptr<int>(), cur()), "norm_clip");
 }
 
+
+// rows of `x` (bf16 [T, H]) go to the receive regions of the ranks that own their experts; see comm.cu for the layout
+void ep_push_rows(const Tensor& x, const Tensor& route_token, const Tensor& route_dest, const Tensor& route_slot,
+                  const c10::optional<Tensor>& route_expert, const c10::optional<Tensor>& route_scale,
+                  const std::vector<int64_t>& recv_rows, const std::vector<int64_t>& recv_expert, const c10::optional<Tensor>& counts,
+                  const std::vector<int64_t>& recv_counts, int64_t src_rank, int64_t cap_rows, int64_t max_ctas) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous() && x.size(1) % 8 == 0,
+              "x must be a contiguous bf16 matrix with a multiple of 8 columns");
+  auto ints = [](const Tensor& t, const char* n) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), n, " must be contiguous int32");
+    return t.data_ptr<int>();
+  };
+  const int64_t n = route_token.numel();
+  TORCH_CHECK(route_dest.numel() == n && route_slot.numel() == n, "route arrays disagree");
+  const int* expert = nullptr;
+  if (route_expert.has_value() && route_expert->defined()) { TORCH_CHECK(route_expert->numel() == n, "route_expert size"); expert = ints(*route_expert, "route_expert"); }
+  const float* scale = nullptr;
+  if (route_scale.has_value() && route_scale->defined()) {
+    TORCH_CHECK(route_scale->is_cuda() && route_scale->scalar_type() == at::kFloat && route_scale->is_contiguous() && route_scale->numel() == n,
+                "route_scale must be contiguous fp32, one per route");
+    scale = route_scale->data_ptr<float>();
+  }
+  const int* cnt = nullptr;
+  if (counts.has_value() && counts->defined()) { TORCH_CHECK(counts->numel() >= int64_t(recv_rows.size()), "counts size"); cnt = ints(*counts, "counts"); }
+  c10::cuda::CUDAGuard guard(x.device());
+  ok(mts::launch_ep_push_rows(x.data_ptr(), ints(route_token, "route_token"), ints(route_dest, "route_dest"), ints(route_slot, "route_slot"),
+                              expert, scale, int(n), int(x.size(1)), to_ptrs(recv_rows), expert ? to_ptrs(recv_expert) : mts::PeerPtrs{},
+                              cnt, cnt ? to_ptrs(recv_counts) : mts::PeerPtrs{}, int(recv_rows.size()), int(src_rank), int(cap_rows),
+                              int(max_ctas), cur()), "ep_push_rows");
+}
+
+void ep_pull_combine(Tensor out, const Tensor& token_dest, const Tensor& token_slot, const c10::optional<Tensor>& weight,
+                     const std::vector<int64_t>& rows, int64_t my_rank, int64_t cap_rows, const c10::optional<Tensor>& saved, int64_t max_ctas) {
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.is_contiguous() && out.size(1) % 8 == 0,
+              "out must be a contiguous bf16 matrix with a multiple of 8 columns");
+  TORCH_CHECK(token_dest.is_cuda() && token_dest.scalar_type() == at::kInt && token_dest.is_contiguous() && token_dest.dim() == 2 &&
+                  token_dest.size(0) == out.size(0) && token_slot.sizes() == token_dest.sizes() && token_slot.scalar_type() == at::kInt &&
+                  token_slot.is_contiguous(), "token_dest / token_slot must be contiguous int32 [T, K]");
+  const float* w = nullptr;
+  if (weight.has_value() && weight->defined()) {
+    TORCH_CHECK(weight->is_cuda() && weight->scalar_type() == at::kFloat && weight->is_contiguous() && weight->sizes() == token_dest.sizes(),
+                "weight must be contiguous fp32 [T, K]");
+    w = weight->data_ptr<float>();
+  }
+  void* keep = nullptr;
+  if (saved.has_value() && saved->defined()) {
+    TORCH_CHECK(saved->scalar_type() == at::kBFloat16 && saved->is_contiguous() && saved->numel() == token_dest.numel() * out.size(1), "saved size");
+    keep = saved->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(out.device());
+  ok(mts::launch_ep_pull_combine(out.data_ptr(), token_dest.data_ptr<int>(), token_slot.data_ptr<int>(), w, int(out.size(0)),
+                                 int(token_dest.size(1)), int(out.size(1)), to_ptrs(rows), int(my_rank), int(cap_rows), keep, int(max_ctas),
+                                 cur()), "ep_pull_combine");
+}
+
 }  // namespace
 
 void bind_comm(pybind11::module_& m) {
+  m.def("ep_push_rows", &ep_push_rows);
+  m.def("ep_pull_combine", &ep_pull_combine);
   m.def("comm_signal", &comm_signal);
   m.def("comm_wait", &comm_wait);
   m.def("comm_allgather", &comm_allgather);

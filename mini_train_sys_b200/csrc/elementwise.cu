@@ -184,6 +184,93 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const floa
   }
 }
 
+// bf16 fast path of the backward pass.  The generic kernel above keeps x, dy, w and the dw partial sums as fp32 registers
+// (about 150 per thread, one CTA per SM); here x and dy stay packed (4 registers per 8 values) and w is re-read through
+// L1, which fits three CTAs per SM and lets enough loads be in flight to approach the copy bandwidth.
+__device__ __forceinline__ void unpack8(const uint4& q, float (&v)[8]) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+    v[2 * i] = __low2float(h);
+    v[2 * i + 1] = __high2float(h);
+  }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(kNormWarps * 32, 3)
+rmsnorm_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                        const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, long long rows, int H) {
+  extern __shared__ float red[];   // [kNormWarps][H]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nvec = H / 8;
+  float acc[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  for (long long row = (long long)blockIdx.x * kNormWarps + warp; row < rows; row += (long long)gridDim.x * kNormWarps) {
+    uint4 xp[VPL], dp[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        xp[i] = *reinterpret_cast<const uint4*>(x + row * H + v * 8);
+        dp[i] = *reinterpret_cast<const uint4*>(dy + row * H + v * 8);
+      }
+    }
+    const float inv = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float xs[8], ds[8], wv[8];
+        unpack8(xp[i], xs);
+        unpack8(dp[i], ds);
+        Vec8<float>::load(w + v * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc[i][j] += ds[j] * xs[j] * inv;
+          dot += ds[j] * wv[j] * xs[j];
+        }
+      }
+    }
+    dot = warp_sum(dot);
+    const float coef = dot / float(H) * inv * inv;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float xs[8], ds[8], wv[8], o[8];
+        unpack8(xp[i], xs);
+        unpack8(dp[i], ds);
+        Vec8<float>::load(w + v * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = inv * (ds[j] * wv[j] - xs[j] * coef);
+        Vec8<__nv_bfloat16>::store(dx + row * H + v * 8, o);
+      }
+    }
+  }
+  if (dw == nullptr) return;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) red[warp * H + v * 8 + j] = acc[i][j];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < kNormWarps; ++wi) s += red[wi * H + c];
+    atomicAdd(dw + c, s);
+  }
+}
+
 // ---------------- RoPE (half-split pairs (d, d + D/2)) ----------------
 // in : [B, Hh, S, D] view with arbitrary strides (innermost contiguous); out: contiguous [B, Hh, S, D].
 // sign = +1 forward, -1 backward (inverse rotation applied to the incoming gradient).
@@ -215,6 +302,35 @@ __global__ void rope_kernel(const T* __restrict__ in, T* __restrict__ out, const
     }
     Vec8<T>::store(dst + v * 8, olo);
     Vec8<T>::store(dst + D / 2 + v * 8, ohi);
+  }
+}
+
+// ---------------- residual + dropout(y) ----------------
+// out = residual + keep(i) * y / (1 - p); backward of y: dy_in = keep(i) * dy / (1 - p) (the residual branch passes dy through).
+// keep(i) is a stateless function of (seed, element index): byte (i & 3) of a hashed word per 4 elements is compared with
+// round(p * 256), so the mask is never stored and the two passes agree by construction.
+__device__ __forceinline__ uint32_t mix32(uint32_t h) {
+  h ^= h >> 16; h *= 0x85ebca6bu; h ^= h >> 13; h *= 0xc2b2ae35u; h ^= h >> 16;
+  return h;
+}
+
+template <typename T, bool WITH_RESIDUAL>
+__global__ void dropout_add_kernel(const T* __restrict__ y, const T* __restrict__ res, T* __restrict__ out, long long nvec,
+                                   uint32_t thresh, float inv_keep, uint32_t seed_lo, uint32_t seed_hi) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float a[8], r[8];
+    Vec8<T>::load(y + i * 8, a);
+    if (WITH_RESIDUAL) Vec8<T>::load(res + i * 8, r);
+    const uint32_t lo = uint32_t(i), hi = uint32_t(i >> 32);
+    const uint32_t w0 = mix32((lo * 2u) * 0x9E3779B1u ^ seed_lo ^ mix32(hi + seed_hi));
+    const uint32_t w1 = mix32((lo * 2u + 1u) * 0x9E3779B1u ^ seed_lo ^ mix32(hi + seed_hi));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t byte = ((j < 4 ? w0 : w1) >> ((j & 3) * 8)) & 0xFFu;
+      const float kept = byte >= thresh ? a[j] * inv_keep : 0.f;
+      a[j] = WITH_RESIDUAL ? r[j] + kept : kept;
+    }
+    Vec8<T>::store(out + i * 8, a);
   }
 }
 
@@ -298,8 +414,23 @@ cudaError_t launch_rmsnorm_fwd(const void* x, const float* w, void* y, float* rs
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, void* dx, float* dw,
                                long long rows, int H, bool bf16, cudaStream_t stream) {
   if (H % 8 != 0 || H > 32 * kMaxVecPerLane * 8) return cudaErrorInvalidValue;
-  const int grid = grid_for(rows, kNormWarps, 4);
   const size_t smem = dw != nullptr ? sizeof(float) * kNormWarps * H : 0;
+  if (bf16) {
+    const int vpl = (H / 8 + 31) / 32;
+    const int grid3 = grid_for(rows, kNormWarps, 3);
+    auto* dyp = static_cast<const __nv_bfloat16*>(dy);
+    auto* xp = static_cast<const __nv_bfloat16*>(x);
+    auto* dxp = static_cast<__nv_bfloat16*>(dx);
+    switch (vpl) {
+      case 1: rmsnorm_bwd_bf16_kernel<1><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, dxp, dw, rows, H); break;
+      case 2: rmsnorm_bwd_bf16_kernel<2><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, dxp, dw, rows, H); break;
+      case 3: rmsnorm_bwd_bf16_kernel<3><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, dxp, dw, rows, H); break;
+      default: rmsnorm_bwd_bf16_kernel<4><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, dxp, dw, rows, H); break;
+    }
+    ++g_launch_count;
+    return cudaGetLastError();
+  }
+  const int grid = grid_for(rows, kNormWarps, 4);
   MTS_DISPATCH_FLOAT(bf16, rmsnorm_bwd_kernel<T><<<grid, kNormWarps * 32, smem, stream>>>(
       static_cast<const T*>(dy), static_cast<const T*>(x), w, rstd, static_cast<T*>(dx), dw, rows, H);)
   ++g_launch_count;
@@ -336,6 +467,24 @@ cudaError_t launch_swiglu_bwd(const void* dy, const void* g, const void* u, void
   MTS_DISPATCH_FLOAT(bf16, swiglu_bwd_kernel<T><<<grid, 256, 0, stream>>>(
       static_cast<const T*>(dy), static_cast<const T*>(g), static_cast<const T*>(u), static_cast<T*>(dg),
       static_cast<T*>(du), n / 8);)
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dropout_add(const void* y, const void* residual, void* out, long long n, float p, unsigned long long seed,
+                               bool bf16, cudaStream_t stream) {
+  if (n % 8 != 0 || p < 0.f || p >= 1.f) return cudaErrorInvalidValue;
+  const int grid = grid_for(n / 8, 256, 16);
+  const uint32_t thresh = uint32_t(p * 256.f + 0.5f);
+  const float inv_keep = 1.f / (1.f - float(thresh) * (1.f / 256.f));
+  const uint32_t lo = uint32_t(seed), hi = uint32_t(seed >> 32);
+  if (residual != nullptr) {
+    MTS_DISPATCH_FLOAT(bf16, dropout_add_kernel<T, true><<<grid, 256, 0, stream>>>(
+        static_cast<const T*>(y), static_cast<const T*>(residual), static_cast<T*>(out), n / 8, thresh, inv_keep, lo, hi);)
+  } else {
+    MTS_DISPATCH_FLOAT(bf16, dropout_add_kernel<T, false><<<grid, 256, 0, stream>>>(
+        static_cast<const T*>(y), nullptr, static_cast<T*>(out), n / 8, thresh, inv_keep, lo, hi);)
+  }
   ++g_launch_count;
   return cudaGetLastError();
 }

@@ -21,6 +21,9 @@ cudaError_t launch_rope(const void* in, void* out, const void* cosp, const void*
 cudaError_t launch_swiglu_fwd(const void* g, const void* u, void* out, long long n, bool bf16, cudaStream_t stream);
 cudaError_t launch_swiglu_bwd(const void* dy, const void* g, const void* u, void* dg, void* du, long long n, bool bf16,
                               cudaStream_t stream);
+// out = residual + dropout(y) (residual may be null: out = dropout(y)); keep pattern = f(seed, element index), p quantised to 1/256.
+cudaError_t launch_dropout_add(const void* y, const void* residual, void* out, long long n, float p, unsigned long long seed,
+                               bool bf16, cudaStream_t stream);
 cudaError_t launch_cast_f32_to_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
 
 // ---- cross_entropy.cu ----

@@ -36,6 +36,18 @@ def project(ops: OpsBackend, layer: nn.Linear, x: torch.Tensor) -> torch.Tensor:
     return layer(x) if fn is None else fn(x, layer.weight)
 
 
+def add_dropped(ops: OpsBackend, drop: nn.Dropout, y: torch.Tensor, residual: torch.Tensor | None) -> torch.Tensor:
+    """``residual + dropout(y)``; one fused pass when the backend offers ``dropout_add``, and plain ``dropout(y)`` when the
+    caller keeps the residual sum to itself (``residual is None``)."""
+
+    if residual is None:
+        return drop(y)
+    fused = getattr(ops, "dropout_add", None)
+    if fused is not None and y.is_cuda:
+        return fused(y, residual, drop.p if drop.training else 0.0)
+    return residual + drop(y)
+
+
 def _scaled_std(cfg: ModelConfig) -> float:
     return 0.02 / math.sqrt(2 * cfg.n_layers)
 
@@ -61,7 +73,8 @@ class CausalSelfAttention(nn.Module):
         nn.init.normal_(self.qkv.weight, mean=0.0, std=0.02)
         nn.init.normal_(self.out.weight, mean=0.0, std=_scaled_std(cfg))
 
-    def forward(self, x: torch.Tensor, ops: OpsBackend, rope_cos: torch.Tensor, rope_sin: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ops: OpsBackend, rope_cos: torch.Tensor, rope_sin: torch.Tensor,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
         b, s, h = x.shape
         nh, hd = self.cfg.n_heads, self.cfg.head_dim
         # [B, S, 3, heads, D] -> three strided [B, heads, S, D] views of the fused projection
@@ -76,7 +89,7 @@ class CausalSelfAttention(nn.Module):
             q, k = ops.rope(q, k, rope_cos, rope_sin)
             ctx = ops.attention(q, k, v, is_causal=True, dropout_p=p)
         ctx = ctx.transpose(1, 2).contiguous().view(b, s, h)
-        return self.resid_dropout(project(ops, self.out, ctx))
+        return add_dropped(ops, self.resid_dropout, project(ops, self.out, ctx), residual)
 
 
 class DenseFeedForward(nn.Module):
@@ -91,9 +104,9 @@ class DenseFeedForward(nn.Module):
         nn.init.normal_(self.up.weight, mean=0.0, std=0.02)
         nn.init.normal_(self.down.weight, mean=0.0, std=_scaled_std(cfg))
 
-    def forward(self, x: torch.Tensor, ops: OpsBackend) -> FeedForwardOutput:
+    def forward(self, x: torch.Tensor, ops: OpsBackend, residual: torch.Tensor | None = None) -> FeedForwardOutput:
         act = ops.swiglu(project(ops, self.gate, x), project(ops, self.up, x))
-        return FeedForwardOutput(self.dropout(project(ops, self.down, act)))
+        return FeedForwardOutput(add_dropped(ops, self.dropout, project(ops, self.down, act), residual))
 
 
 class MoEFeedForward(nn.Module):
@@ -112,7 +125,7 @@ class MoEFeedForward(nn.Module):
         # Set by the expert-parallel strategy: callable(x, indices, weights, module) -> y
         self.expert_dispatch = None
 
-    def forward(self, x: torch.Tensor, ops: OpsBackend) -> FeedForwardOutput:
+    def forward(self, x: torch.Tensor, ops: OpsBackend, residual: torch.Tensor | None = None) -> FeedForwardOutput:
         tokens = x.reshape(-1, x.shape[-1])
         route = self.router(tokens, ops)
         if self.expert_dispatch is not None:
@@ -121,7 +134,7 @@ class MoEFeedForward(nn.Module):
             mixed = ops.fused_moe(tokens, self.gate_up_proj, self.down_proj,
                                   route.expert_indices, route.expert_weights)
         return FeedForwardOutput(
-            hidden_states=self.dropout(mixed.view(x.shape)),
+            hidden_states=add_dropped(ops, self.dropout, mixed.view(x.shape), residual),
             router_aux_loss=route.auxiliary_loss,
             router_z_loss=route.z_loss,
             router_metrics=route.metrics,
@@ -147,10 +160,8 @@ class TransformerBlock(nn.Module):
     mlp = property(lambda self: self.ffn)
 
     def forward(self, x: torch.Tensor, ops: OpsBackend, rope_cos: torch.Tensor, rope_sin: torch.Tensor) -> FeedForwardOutput:
-        x = x + self.attn(self.attn_norm(x, ops), ops, rope_cos, rope_sin)
-        ff = self.ffn(self.ffn_norm(x, ops), ops)
-        ff.hidden_states = x + ff.hidden_states
-        return ff
+        x = self.attn(self.attn_norm(x, ops), ops, rope_cos, rope_sin, residual=x)
+        return self.ffn(self.ffn_norm(x, ops), ops, residual=x)      # hidden_states already include the residual
 
 
 SwiGLUMLP = DenseFeedForward

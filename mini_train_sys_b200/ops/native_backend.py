@@ -144,10 +144,22 @@ def gemm_tn(a_km: torch.Tensor, b_kn: torch.Tensor, out: torch.Tensor | None = N
     if out is None:
         out = (torch.zeros if splits > 1 else torch.empty)(M, N, dtype=torch.float32, device=a_km.device)
         accumulate = False
+    elif splits > 1 and not accumulate:
+        out.zero_()              # the splits add into the output
     atomic = splits > 1
     _gemm(a_km, b_kn, out, M, N, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=rows, num_groups=splits,
           accumulate=accumulate and not atomic, atomic_out=atomic, out_group_stride=0)
     return out
+
+
+def grad_sink(param: torch.Tensor):
+    """``(fp32 destination, done callback)`` when a sharding engine wants this parameter's gradient written in place.
+
+    The engine attaches ``_mts_grad_sink`` to parameters that are used once per step; a backward function that honours it writes
+    the fp32 gradient there, calls ``done(param)`` and returns no gradient for the parameter, which saves the bf16 round trip
+    (fp32 -> parameter dtype -> fp32 copy in the accumulate hook) and two passes over every weight-sized tensor."""
+
+    return getattr(param, "_mts_grad_sink", None)
 
 
 def _gemm_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -189,7 +201,12 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm_nn(dy2, w16, K=dy2.shape[1]).view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm_tn(dy2, x2, M=n_out).to(weight.dtype)
+            sink = grad_sink(weight)
+            if sink is not None:
+                gemm_tn(dy2, x2, out=sink[0], M=n_out)      # fp32, straight into the engine's flat gradient buffer
+                sink[1](weight)
+            else:
+                dw = gemm_tn(dy2, x2, M=n_out).to(weight.dtype)
         return dx, dw
 
 
@@ -322,6 +339,33 @@ class _FusedLinearCEFn(torch.autograd.Function):
         gx = dx * g.to(dx.dtype) if dx is not None else None
         gw = (dw * g).to(ctx.w_dtype) if dw is not None else None
         return gx, gw, None
+
+
+_dropout_calls = 0
+
+
+def _next_dropout_seed() -> int:
+    """Seed of the next fused dropout: a function of ``torch.initial_seed()`` and a call counter (no device sync, and two
+    runs that seed torch identically and make the same calls get the same masks)."""
+
+    global _dropout_calls
+    _dropout_calls += 1
+    return (torch.initial_seed() * 0x9E3779B97F4A7C15 + _dropout_calls * 0xD1B54A32D192ED03) & 0x7FFFFFFFFFFFFFFF
+
+
+class _DropoutAddFn(torch.autograd.Function):
+    """``residual + dropout(y)`` in one pass; the keep pattern is recomputed (not stored) in backward."""
+
+    @staticmethod
+    def forward(ctx, y, residual, p, seed):
+        ctx.p, ctx.seed = p, seed
+        return ext().dropout_add(y.contiguous(), residual.contiguous(), p, seed)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        gy = ext().dropout_add(g, None, ctx.p, ctx.seed) if ctx.needs_input_grad[0] else None
+        return gy, (g if ctx.needs_input_grad[1] else None), None, None
 
 
 def _split_bf16(t32: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -459,15 +503,25 @@ class _FusedMoEFn(torch.autograd.Function):
             dx = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
             e.moe_combine(dxs, token_rows, None, dx, k)
         if ctx.needs_input_grad[1]:
-            dgu = torch.empty(n_exp, two_i, hidden, dtype=torch.float32, device=dev)
+            sink = grad_sink(gate_up_proj)
+            dgu = sink[0] if sink is not None else torch.empty(n_exp, two_i, hidden, dtype=torch.float32, device=dev)
             _gemm(d_pre, xs, dgu, two_i, hidden, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=group_rows,
                   num_groups=n_exp, out_group_stride=two_i * hidden, ldo=hidden)
-            dgu = dgu.to(gate_up_proj.dtype)
+            if sink is not None:
+                sink[1](gate_up_proj)
+                dgu = None
+            else:
+                dgu = dgu.to(gate_up_proj.dtype)
         if ctx.needs_input_grad[2]:
-            ddn = torch.empty(n_exp, hidden, inter, dtype=torch.float32, device=dev)
+            sink = grad_sink(down_proj)
+            ddn = sink[0] if sink is not None else torch.empty(n_exp, hidden, inter, dtype=torch.float32, device=dev)
             _gemm(dys, post, ddn, hidden, inter, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=group_rows,
                   num_groups=n_exp, out_group_stride=hidden * inter, ldo=inter)
-            ddn = ddn.to(down_proj.dtype)
+            if sink is not None:
+                sink[1](down_proj)
+                ddn = None
+            else:
+                ddn = ddn.to(down_proj.dtype)
         dw = dwts.view(tokens, k).to(ctx.w_dtype) if ctx.needs_input_grad[4] else None
         return dx, dgu, ddn, None, dw
 
@@ -522,6 +576,17 @@ class NativeOpsBackend(TorchOpsBackend):
         if self._count("swiglu", ok):
             return _SwigluFn.apply(gate, up)
         return super().swiglu(gate, up)
+
+    def dropout_add(self, y, residual, p: float):
+        """``residual + dropout(y, p)`` (optional hook outside the 8-op protocol; the blocks use it when present)."""
+
+        ok = (_native_act(y, residual) and y.dtype == residual.dtype and y.shape == residual.shape and y.numel() % 8 == 0
+              and 0.0 <= p < 1.0)
+        if self._count("dropout_add", ok):
+            if p == 0.0:
+                return residual + y
+            return _DropoutAddFn.apply(y, residual, float(p), _next_dropout_seed())
+        return residual + torch.nn.functional.dropout(y, p, training=p > 0.0)
 
     def cross_entropy(self, logits, targets):
         ok = _native_act(logits) and logits.dim() == 2 and targets.is_cuda and targets.dtype == torch.long

@@ -200,8 +200,26 @@ class FlatDataParallel(nn.Module):
             s.param.data = unit.gathered.tensor[s.offset:s.offset + s.numel].view(s.shape)
             self._slot_of[s.param] = (unit, s)
             s.param.register_post_accumulate_grad_hook(self._on_grad)
+            if self._sink_ok(s):
+                dst = unit.grad_full.tensor[s.offset:s.offset + s.numel].view(s.shape)
+                s.param._mts_grad_sink = (dst, self._on_sunk_grad)
         unit.pending = len(slots)
         return unit
+
+    def _sink_ok(self, slot) -> bool:
+        """Parameters whose backward may write the fp32 gradient in place: matrices used once per step by an operator that
+        knows the protocol (linear layers and expert stacks inside the blocks; never tied or embedding weights)."""
+
+        name = slot.name
+        if not (self.coll.fused and slot.param.dim() >= 2 and ".blocks." in f".{name}"):
+            return False
+        return name.endswith(("qkv.weight", "out.weight", "gate.weight", "up.weight", "down.weight", "gate_up_proj", "down_proj"))
+
+    def _on_sunk_grad(self, param: nn.Parameter) -> None:
+        unit, _ = self._slot_of[param]
+        unit.pending -= 1
+        if unit.pending == 0:
+            self.coll.reduce_scatter(unit, self.step_count + 1)
 
     def _enable_activation_checkpointing(self) -> None:
         from torch.utils.checkpoint import checkpoint

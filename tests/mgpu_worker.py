@@ -71,7 +71,42 @@ def main() -> None:
     assert abs(na - nb) <= 5e-2 * max(nb, 1e-6), (na, nb)
     coll.check_status()
     dist.barrier()
+
+    # ---- expert-parallel layer: own peer-memory exchange against the all_to_all_single path ----
+    from mini_train_sys_b200.models.blocks import MoEFeedForward
+    from mini_train_sys_b200.parallel import ep as ep_mod
+
+    moe_cfg = ModelConfig(vocab_size=1000, seq_len=128, n_layers=1, n_heads=4, hidden_size=256, intermediate_size=256, ffn_type="moe",
+                          num_experts=2 * world, experts_per_token=2, dropout=0.0)
+    ops = get_ops_backend("native")
+    results = {}
+    for mode in ("library", "peer"):
+        torch.manual_seed(5)
+        layer = MoEFeedForward(moe_cfg).to(dev)
+
+        class Holder(torch.nn.Module):
+            def __init__(self, ffn):
+                super().__init__()
+                self.ffn = ffn
+        holder = Holder(layer)
+        ep_mod.shard_experts(holder, rank, world, ep_mod.ExchangeHolder(timeout_ms=5000) if mode == "peer" else None)
+        torch.manual_seed(50 + rank)
+        x = torch.randn(4 * 128, 256, device=dev, dtype=torch.bfloat16).requires_grad_()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = layer(x.view(4, 128, 256), ops).hidden_states
+        g = torch.randn_like(out)
+        out.backward(g)
+        results[mode] = (out.detach().float(), x.grad.float().clone(), layer.gate_up_proj.grad.float().clone(),
+                         layer.down_proj.grad.float().clone(), layer.router.weight.grad.float().clone())
+    names = ("out", "dx", "d_gate_up", "d_down", "d_router")
+    for name, a, b in zip(names, results["peer"], results["library"]):
+        err = float((a - b).abs().max()) / max(float(b.abs().max()), 1e-6)
+        assert err < 3e-2, (name, err)
+    torch.cuda.synchronize()
+    assert int(e.status_tensor(dev.index)[0]) == 0
+    dist.barrier()
     if rank == 0:
+        print("PASS expert_parallel peer exchange == library exchange", flush=True)
         print(f"PASS engine losses_fused={la} losses_lib={lb}", flush=True)
     dist.destroy_process_group()
 

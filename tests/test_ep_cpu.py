@@ -93,3 +93,26 @@ def test_router_drops_overflow_and_reports_it():
     assert float(out.expert_weights[out.expert_indices < 0].abs().sum()) == 0.0
     kept_per_expert = torch.bincount(out.expert_indices[out.expert_indices >= 0].long(), minlength=4)
     assert int(kept_per_expert.max()) <= expert_capacity(cfg, 64)
+
+
+def test_route_layout_slots_are_dense_per_destination_and_overflow_is_dropped():
+    import torch
+
+    from mini_train_sys_b200.parallel.ep import _route_layout
+
+    torch.manual_seed(0)
+    world, n_local, t, k = 4, 2, 50, 2
+    idx = torch.randint(0, world * n_local, (t, k))
+    idx[3, 1] = -1
+    dest, slot, local_e, counts, over = _route_layout(idx, n_local, world, cap=1000)
+    flat = idx.reshape(-1)
+    assert int(over) == 0 and dest[7] == -1 and counts.sum() == t * k - 1
+    for d in range(world):
+        mine = (dest == d).nonzero().flatten()
+        assert slot[mine].tolist() == list(range(len(mine)))            # route order is kept inside a destination
+        assert (flat[mine] // n_local == d).all() and (local_e[mine] == flat[mine] % n_local).all()
+        assert int(counts[d]) == len(mine)
+    # a region of 5 rows: everything past slot 4 is dropped and counted
+    dest2, slot2, _, counts2, over2 = _route_layout(idx, n_local, world, cap=5)
+    assert int(over2) == int((counts - 5).clamp(min=0).sum()) and int(slot2.max()) <= 4 and (counts2 <= 5).all()
+    assert int((dest2 >= 0).sum()) == int(counts2.sum())

@@ -93,3 +93,37 @@ def test_collective_kernels_world_of_one():
     assert float(norm) == pytest.approx(float(sumsq.sqrt()), rel=1e-5)
     assert float(coef) == pytest.approx(min(1.0, 1.0 / (float(norm) + 1e-6)), rel=1e-5)
     assert int(status[0]) == 0
+
+
+def test_expert_exchange_kernels_with_one_rank_match_the_local_layer():
+    """World of one: every route goes to 'the owner' through the push / pull kernels; results must equal the plain layer."""
+
+    from mini_train_sys_b200.models import ModelConfig, get_ops_backend
+    from mini_train_sys_b200.models.blocks import MoEFeedForward
+    from mini_train_sys_b200.ops.native_backend import check_kernel_status
+    from mini_train_sys_b200.parallel import ep as ep_mod
+
+    cfg = ModelConfig(vocab_size=1000, seq_len=128, n_layers=1, n_heads=4, hidden_size=256, intermediate_size=256, ffn_type="moe",
+                      num_experts=4, experts_per_token=2, dropout=0.0)
+    ops = get_ops_backend("native")
+    got = {}
+    for mode in ("plain", "peer"):
+        torch.manual_seed(5)
+        layer = MoEFeedForward(cfg).to(DEV)
+        if mode == "peer":
+            class Holder(torch.nn.Module):
+                def __init__(self, ffn):
+                    super().__init__()
+                    self.ffn = ffn
+            ep_mod.shard_experts(Holder(layer), 0, 1, ep_mod.ExchangeHolder())
+        torch.manual_seed(6)
+        x = torch.randn(3, 128, 256, device=DEV, dtype=torch.bfloat16).requires_grad_()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = layer(x, ops).hidden_states
+        g = torch.randn_like(out)
+        out.backward(g)
+        got[mode] = [t.float().clone() for t in (out.detach(), x.grad, layer.gate_up_proj.grad, layer.down_proj.grad, layer.router.weight.grad)]
+    for name, a, b in zip(("out", "dx", "d_gate_up", "d_down", "d_router"), got["peer"], got["plain"]):
+        err = float((a - b).abs().max()) / max(float(b.abs().max()), 1e-6)
+        assert err < 3e-2, (name, err)
+    check_kernel_status()

@@ -417,3 +417,25 @@ def test_qkv_attention_fused_path(ops):
     (rg,) = torch.autograd.grad(want, f32, d_o.float())
     assert_close(out, want, 2e-2, "out")
     assert_close(g, rg, 3e-2, "d fused qkv")
+
+
+def test_dropout_add_masks_agree_between_passes(ops):
+    torch.manual_seed(21)
+    y = torch.randn(4096, 768, device=DEV, dtype=torch.bfloat16).requires_grad_()
+    res = torch.randn_like(y).requires_grad_()
+    p = 0.1
+    out = ops.dropout_add(y, res, p)
+    g = torch.randn_like(out)
+    out.backward(g)
+    kept = (out.detach().float() - res.detach().float()).abs() > 0          # y is never exactly zero
+    rate = 1.0 - kept.float().mean().item()
+    p_eff = round(p * 256) / 256
+    assert abs(rate - p_eff) < 2e-3, rate
+    scale = 1.0 / (1.0 - p_eff)
+    want = torch.where(kept, y.detach().float() * scale, torch.zeros_like(y, dtype=torch.float32)) + res.detach().float()
+    assert_close(out, want, 1e-2, "dropout_add forward")
+    assert_close(y.grad, torch.where(kept, g.float() * scale, torch.zeros_like(g, dtype=torch.float32)), 1e-2, "dropout_add dy")
+    assert torch.equal(res.grad, g)
+    out2 = ops.dropout_add(y.detach(), res.detach(), p)                      # a new call draws a new mask
+    assert not torch.equal(out2, out.detach())
+    assert torch.equal(ops.dropout_add(y.detach(), res.detach(), 0.0), res.detach() + y.detach())

@@ -23,4 +23,4 @@ def _launch(n: int, extra_env=None) -> str:
 
 def test_peer_collectives_and_engine_on_two_gpus():
     out = _launch(min(torch.cuda.device_count(), 2))
-    assert "PASS reduce_scatter" in out and "PASS engine" in out
+    assert "PASS reduce_scatter" in out and "PASS engine" in out and "PASS expert_parallel" in out
