@@ -270,20 +270,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tmem_ld_wait();
       epilogue_arrive(&s_free, lane);            // S is in registers: the next Q K^T may overwrite it
       if (warp == 2) MTS_TRACE(8 * j + 1);
-      float mx = -CUDART_INF_F;
+      if (need_mask) {       // one uniform branch around the loop (diagonal and ragged tiles only)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kidx = k0 + i;
+          if (kidx >= p.S || (p.causal && kidx > q_row)) s0[i] = __float_as_uint(-CUDART_INF_F);
+          if (kidx + 32 >= p.S || (p.causal && kidx + 32 > q_row)) s1[i] = __float_as_uint(-CUDART_INF_F);
+          if (kidx + 64 >= p.S || (p.causal && kidx + 64 > q_row)) s2[i] = __float_as_uint(-CUDART_INF_F);
+          if (kidx + 96 >= p.S || (p.causal && kidx + 96 > q_row)) s3[i] = __float_as_uint(-CUDART_INF_F);
+        }
+      }
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};   // four independent max chains
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        float v0 = __uint_as_float(s0[i]), v1 = __uint_as_float(s1[i]), v2 = __uint_as_float(s2[i]), v3 = __uint_as_float(s3[i]);
-        if (need_mask) {
-          const int kidx = k0 + i;
-          if (kidx >= p.S || (p.causal && kidx > q_row)) v0 = -CUDART_INF_F;
-          if (kidx + 32 >= p.S || (p.causal && kidx + 32 > q_row)) v1 = -CUDART_INF_F;
-          if (kidx + 64 >= p.S || (p.causal && kidx + 64 > q_row)) v2 = -CUDART_INF_F;
-          if (kidx + 96 >= p.S || (p.causal && kidx + 96 > q_row)) v3 = -CUDART_INF_F;
-          s0[i] = __float_as_uint(v0); s1[i] = __float_as_uint(v1); s2[i] = __float_as_uint(v2); s3[i] = __float_as_uint(v3);
-        }
-        mx = fmaxf(mx, fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)));
+        mx4[0] = fmaxf(mx4[0], __uint_as_float(s0[i]));
+        mx4[1] = fmaxf(mx4[1], __uint_as_float(s1[i]));
+        mx4[2] = fmaxf(mx4[2], __uint_as_float(s2[i]));
+        mx4[3] = fmaxf(mx4[3], __uint_as_float(s3[i]));
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_tile = mx * scale_log2;
       float alpha = 1.f;
       bool grow = false;
@@ -772,11 +777,13 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (c == 1) epilogue_arrive(&st_free, lane);   // S / dP are in registers: the next scores may be issued
         float ds[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int kidx = kbase + c * 32 + j;
-          float e = ex2(__uint_as_float(rs[j]) * scale_log2 - lse2);
-          if (need_mask && (kidx >= p.S || q_row >= p.S || (p.causal && kidx > q_row))) e = 0.f;
-          ds[j] = e;   // probability; turned into dS below once the keep bits are known
+        for (int j = 0; j < 32; ++j) ds[j] = ex2(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2));   // probabilities first
+        if (need_mask) {      // one uniform branch around the whole loop: per-element branches would serialise the exponentials
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int kidx = kbase + c * 32 + j;
+            if (kidx >= p.S || q_row >= p.S || (p.causal && kidx > q_row)) ds[j] = 0.f;
+          }
         }
         if (drop.thresh != 0u) {
 #pragma unroll

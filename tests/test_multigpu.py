@@ -24,3 +24,13 @@ def _launch(n: int, extra_env=None) -> str:
 def test_peer_collectives_and_engine_on_two_gpus():
     out = _launch(min(torch.cuda.device_count(), 2))
     assert "PASS reduce_scatter" in out and "PASS engine" in out and "PASS expert_parallel" in out
+
+
+def test_a_rank_that_leaves_between_steps_is_noticed_on_the_host():
+    n = min(torch.cuda.device_count(), 4)
+    env = {**os.environ, "MASTER_ADDR": "127.0.0.1", "NCCL_NVLS_ENABLE": "0", "TORCH_NCCL_ASYNC_ERROR_HANDLING": "0"}
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29741", str(ROOT / "tests" / "mgpu_exit_worker.py")]
+    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    out = done.stdout + done.stderr
+    assert out.count("PASS survivor") == n - 1 and "LEFT rank" in out and "FAIL" not in out, out[-3000:]
