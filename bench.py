@@ -238,17 +238,25 @@ def main() -> None:
     total_ms, clocks, n_launch, last_loss = timed(step_device, "device")
     e2e_ms, clocks_e2e, _, last_loss_e2e = timed(step_e2e, "e2e")
 
+    headline = Path(args.model_config).resolve() == (ROOT / "configs" / "synbios_moe" / "model.yaml").resolve()
+    if headline:
+        model_label = "synbios_moe 293.49M top-2 MoE (12L, d768, 8 experts, vocab 50257, dropout 0.1, tied)"
+    else:
+        mc = cfg.model
+        model_label = (f"{Path(args.model_config).stem} ({mc.get('n_layers')}L, d{mc.get('hidden_size')}, ffn {mc.get('ffn_type', 'dense')}, "
+                       f"vocab {mc.get('vocab_size')}, seq {mc.get('seq_len')})")
     tokens_per_step = batch * seq_len * world
     value = tokens_per_step * steps / (total_ms / 1e3)
     e2e_value = tokens_per_step * steps / (e2e_ms / 1e3)
     peak_mb = torch.cuda.max_memory_allocated(device) / 2**20
     record = {
-        "metric": "tokens/sec, 293M MoE FSDP (weak scaling, max over ranks)", "value": round(value, 1),
+        "metric": "tokens/sec, 293M MoE FSDP (weak scaling, max over ranks)" if headline else
+                  f"tokens/sec, {Path(args.model_config).stem} {strategy_name} (weak scaling, max over ranks)", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": round(total_ms / steps, 3), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": round(value / PUBLISHED_TOKENS_PER_SEC, 3), "dtype": "bf16",
+        "vs_baseline": round(value / PUBLISHED_TOKENS_PER_SEC, 3) if headline else None, "dtype": "bf16",
         "data": "synthetic uniform-random tokens, random-init weights", "impl": args.impl,
-        "config": {"model": "synbios_moe 293.49M top-2 MoE (12L, d768, 8 experts, vocab 50257, dropout 0.1, tied)",
+        "config": {"model": model_label,
                    "global_batch": batch * world, "local_batch": batch, "seq_len": seq_len,
                    "parallelism": f"{strategy_name}{world}", "ops": getattr(ops, "name", "?"),
                    "comm_engine": getattr(strategy, "resolved_engine", lambda: "n/a")(),

@@ -240,6 +240,8 @@ class FlatDataParallel(nn.Module):
 
     @torch.no_grad()
     def _on_grad(self, param: nn.Parameter) -> None:
+        if param.grad is None:
+            return      # the operator wrote this gradient through the parameter's sink and already reported it
         unit, slot = self._slot_of[param]
         dst = unit.grad_full.tensor[slot.offset:slot.offset + slot.numel].view(slot.shape)
         dst.copy_(param.grad)

@@ -421,8 +421,9 @@ def test_qkv_attention_fused_path(ops):
 
 def test_dropout_add_masks_agree_between_passes(ops):
     torch.manual_seed(21)
-    y = torch.randn(4096, 768, device=DEV, dtype=torch.bfloat16).requires_grad_()
-    res = torch.randn_like(y).requires_grad_()
+    # |y| in [1, 2) and |res| < 1: a kept element always changes the sum visibly in bf16, so the mask can be read off the output
+    y = ((1 + torch.rand(4096, 768, device=DEV)) * torch.where(torch.rand(4096, 768, device=DEV) < 0.5, -1.0, 1.0)).to(torch.bfloat16).requires_grad_()
+    res = (torch.rand(4096, 768, device=DEV) * 1.8 - 0.9).to(torch.bfloat16).requires_grad_()
     p = 0.1
     out = ops.dropout_add(y, res, p)
     g = torch.randn_like(out)
