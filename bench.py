@@ -28,7 +28,7 @@ import time
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
-PUBLISHED_TOKENS_PER_SEC = 352_544.0   # reference CUDA backend, 4x RTX 4090, local batch 96
+PUBLISHED_TOKENS_PER_SEC = 352_544.0   # published by the reference: CUDA backend, 4x RTX 4090, local batch 96 (README.md:70 of the reference)
 
 
 def parse_args() -> argparse.Namespace:
