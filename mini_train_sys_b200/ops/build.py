@@ -10,10 +10,14 @@ extension is an error there, so that a silent library fallback cannot happen
 
 from __future__ import annotations
 
+import hashlib
 import importlib.util
+import json
 import os
+import shlex
 import shutil
 import sys
+from dataclasses import dataclass
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parents[1]
@@ -24,6 +28,42 @@ EXT_PATH = PKG_DIR / f"{EXT_NAME}.so"
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+
+# Build profiles (``MTS_BUILD_PROFILE``); the reference's counterpart selects head dimensions and dtypes to instantiate
+# (minitrain/kernels/cuda_ext/build.py:57-71), here a profile only adds diagnostics to the one set of kernels.
+PROFILES = {
+    "release": [],
+    "trace-gemm": ["-DMTS_GEMM_TRACE"],          # clock64 phase stamps of CTA 0 in the GEMM
+    "trace-attention": ["-DMTS_ATTN_TRACE"],     # the same for the attention kernels
+}
+
+
+@dataclass(frozen=True)
+class BuildConfig:
+    """What determines the binary: profile, extra flags, and the content of every source file."""
+
+    profile: str = "release"
+    extra_nvcc_flags: tuple[str, ...] = ()
+    verbose: bool = False
+
+    @classmethod
+    def from_env(cls, env=os.environ) -> "BuildConfig":
+        profile = env.get("MTS_BUILD_PROFILE", "release")
+        if profile not in PROFILES:
+            raise ValueError(f"MTS_BUILD_PROFILE={profile!r}: expected one of {sorted(PROFILES)}")
+        extra = tuple(shlex.split(env.get("MTS_EXTRA_NVCC_FLAGS", "")))
+        return cls(profile, extra, env.get("MTS_BUILD_VERBOSE", "0") == "1")
+
+    def nvcc_flags(self) -> list[str]:
+        return [*NVCC_FLAGS, *PROFILES[self.profile], *self.extra_nvcc_flags]
+
+    def cache_key(self) -> str:
+        digest = hashlib.sha256(json.dumps([self.profile, list(self.extra_nvcc_flags), NVCC_FLAGS]).encode())
+        for path in sorted(CSRC.iterdir()):
+            if path.suffix in (".cu", ".cpp", ".cuh", ".h"):
+                digest.update(path.name.encode())
+                digest.update(path.read_bytes())
+        return digest.hexdigest()[:16]
 
 
 def sources() -> list[str]:
@@ -37,8 +77,14 @@ def _stale() -> bool:
     return any(p.stat().st_mtime > built for p in CSRC.iterdir() if p.suffix in (".cu", ".cpp", ".cuh", ".h"))
 
 
-def build_extension(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not _stale():
+KEY_PATH = PKG_DIR / "_build" / "cache_key.txt"
+
+
+def build_extension(force: bool = False, verbose: bool = False, config: BuildConfig | None = None) -> Path:
+    config = config or BuildConfig.from_env()
+    key = config.cache_key()
+    same_key = KEY_PATH.is_file() and KEY_PATH.read_text().strip() == key
+    if not force and EXT_PATH.exists() and (same_key or (not KEY_PATH.is_file() and not _stale())):
         return EXT_PATH
     from torch.utils import cpp_extension
 
@@ -46,9 +92,10 @@ def build_extension(force: bool = False, verbose: bool = False) -> Path:
     os.environ.setdefault("MAX_JOBS", str(os.cpu_count() or 4))
     BUILD_DIR.mkdir(exist_ok=True)
     cpp_extension.load(name=EXT_NAME, sources=sources(), extra_cflags=["-O3", "-std=c++17"],
-                       extra_cuda_cflags=NVCC_FLAGS, extra_include_paths=[str(CSRC)], extra_ldflags=["-lcuda"],
-                       build_directory=str(BUILD_DIR), verbose=verbose, is_python_module=False)
+                       extra_cuda_cflags=config.nvcc_flags(), extra_include_paths=[str(CSRC)], extra_ldflags=["-lcuda"],
+                       build_directory=str(BUILD_DIR), verbose=verbose or config.verbose, is_python_module=False)
     shutil.copy2(BUILD_DIR / f"{EXT_NAME}.so", EXT_PATH)
+    KEY_PATH.write_text(key + "\n")
     return EXT_PATH
 
 

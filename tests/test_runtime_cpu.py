@@ -194,3 +194,15 @@ def test_single_process_reductions_are_identity():
     assert distributed_mean({"b": 2.0, "a": 1.0}, torch.device("cpu")) == {"a": 1.0, "b": 2.0}
     out = distributed_mean_tensors({"m": torch.arange(6.0).view(2, 3)}, torch.device("cpu"))
     assert out == {"m": [[0.0, 1.0, 2.0], [3.0, 4.0, 5.0]]}
+
+
+def test_build_config_profiles_and_cache_key():
+    from mini_train_sys_b200.ops.build import NVCC_FLAGS, BuildConfig
+
+    assert "arch=compute_100a,code=sm_100a" in NVCC_FLAGS and "-lineinfo" in NVCC_FLAGS
+    release = BuildConfig.from_env({})
+    traced = BuildConfig.from_env({"MTS_BUILD_PROFILE": "trace-attention", "MTS_EXTRA_NVCC_FLAGS": "-DFOO=1"})
+    assert release.profile == "release" and "-DMTS_ATTN_TRACE" in traced.nvcc_flags() and "-DFOO=1" in traced.nvcc_flags()
+    assert release.cache_key() != traced.cache_key() and release.cache_key() == BuildConfig().cache_key()
+    with pytest.raises(ValueError):
+        BuildConfig.from_env({"MTS_BUILD_PROFILE": "nope"})
