@@ -50,7 +50,7 @@ register_nsight_kernel("flash_fwd", "flash_fwd_kernel", _case("attention", 24576
 register_nsight_kernel("flash_bwd_dkdv", "flash_bwd_dkdv_kernel", _case("attention", 24576))
 register_nsight_kernel("flash_bwd_dq", "flash_bwd_dq_kernel", _case("attention", 24576))
 register_nsight_kernel("rmsnorm_fwd", "rmsnorm_fwd_kernel", _case("rmsnorm", 57344))
-register_nsight_kernel("rmsnorm_bwd", "rmsnorm_bwd_kernel", _case("rmsnorm", 57344))
+register_nsight_kernel("rmsnorm_bwd", "rmsnorm_bwd", _case("rmsnorm", 57344))
 register_nsight_kernel("rope", "rope_kernel", _case("rope", 57344))
 register_nsight_kernel("swiglu_fwd", "swiglu_fwd_kernel", _case("swiglu", 57344))
 register_nsight_kernel("swiglu_bwd", "swiglu_bwd_kernel", _case("swiglu", 57344))

@@ -162,6 +162,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int q0 = q_tile * 128;
   const int n_kv = p.causal ? min((p.S + 127) / 128, q_tile + 1) : (p.S + 127) / 128;
+  if (warp == 0) MTS_TRACE(8000);
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
@@ -176,6 +177,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_s = tmem_slot, tmem_pv = tmem_slot + 128;
   volatile int* abort_ptr = &abort_word;
+  if (warp == 0) MTS_TRACE(8001);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -364,6 +366,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         store_row64(p.o + (long long)b * p.o_sb + (long long)h * p.o_sh + (long long)q_row * p.o_ss, o, inv_l);
         p.lse[((long long)bh) * p.S + q_row] = (m + log2f(l)) * LN2;
       }
+      if (warp == 2) MTS_TRACE(8002);
     }
   }
 
@@ -374,6 +377,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (p.status != nullptr) atomicMax(p.status, abort_word);
   }
   __syncthreads();
+  if (warp == 0) MTS_TRACE(8003);
   if (warp == 0) tmem_dealloc(tmem_slot, 256);
 }
 
