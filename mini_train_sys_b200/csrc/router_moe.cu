@@ -106,13 +106,16 @@ router_backward_kernel(const float* __restrict__ logits, const float* __restrict
     if (normalize) {
       float s = 0.f;
       for (int k = 0; k < K; ++k) {
-        s += p[indices[(long long)t * K + k]];
+        const int e = indices[(long long)t * K + k];
+        if (e < 0) continue;                       // dropped route: no weight, no gradient
+        s += p[e];
         inner += g_weights[(long long)t * K + k] * weights[(long long)t * K + k];
       }
       denom = fmaxf(s, 1.1920929e-07f);
     }
     for (int k = 0; k < K; ++k) {
       const int e = indices[(long long)t * K + k];
+      if (e < 0) continue;
       const float g = g_weights[(long long)t * K + k];
       dp[e] += normalize ? (g - inner) / denom : g;
     }
@@ -133,7 +136,10 @@ plan_count_kernel(const int* __restrict__ indices, int n_routes, int E, int* __r
   if (threadIdx.x < E) hist[threadIdx.x] = 0;
   __syncthreads();
   const int i = blockIdx.x * kPlanBlock + threadIdx.x;
-  if (i < n_routes) atomicAdd(&hist[indices[i]], 1);
+  if (i < n_routes) {
+    const int e = indices[i];
+    if (e >= 0 && e < E) atomicAdd(&hist[e], 1);   // negative ids mark dropped routes / empty slots
+  }
   __syncthreads();
   if (threadIdx.x < E) block_counts[blockIdx.x * E + threadIdx.x] = hist[threadIdx.x];
 }
@@ -190,7 +196,8 @@ plan_place_kernel(const int* __restrict__ indices, int n_routes, int K, int E, c
   __shared__ int warp_hist[kPlanBlock / 32][kMaxExperts];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int i = blockIdx.x * kPlanBlock + threadIdx.x;
-  const int e = i < n_routes ? indices[i] : -1;
+  int e = i < n_routes ? indices[i] : -1;
+  if (e >= E) e = -1;
   for (int q = lane; q < E; q += 32) warp_hist[warp][q] = 0;
   __syncwarp();
   // rank inside the warp among lanes with the same expert
@@ -208,6 +215,8 @@ plan_place_kernel(const int* __restrict__ indices, int n_routes, int K, int E, c
     } else {
       token_rows[i] = -1;
     }
+  } else if (i < n_routes) {
+    token_rows[i] = -1;      // a dropped route has no row: the combine kernels skip it
   }
 }
 

@@ -440,3 +440,26 @@ def test_dropout_add_masks_agree_between_passes(ops):
     out2 = ops.dropout_add(y.detach(), res.detach(), p)                      # a new call draws a new mask
     assert not torch.equal(out2, out.detach())
     assert torch.equal(ops.dropout_add(y.detach(), res.detach(), 0.0), res.detach() + y.detach())
+
+
+def test_moe_plan_and_fused_moe_skip_dropped_routes(nb, ops):
+    """Expert id -1 marks a dropped route (capacity overflow, empty exchange slot): it gets no row and contributes nothing."""
+
+    torch.manual_seed(12)
+    tokens, experts, k, hidden, inter = 3000, 8, 2, 256, 256
+    idx, w = _skewed_routes(tokens, experts, k, "uniform")
+    drop = torch.rand(tokens, k, device=DEV) < 0.3
+    dropped = torch.where(drop, torch.full_like(idx, -1), idx)
+    row_token, token_rows, tile_group, group_rows, meta = nb.ext().moe_plan(dropped.contiguous(), experts)
+    tr = token_rows.view(tokens, k)
+    assert bool((tr[drop] == -1).all()) and bool((tr[~drop] >= 0).all())
+    counts = torch.bincount(idx[~drop].long(), minlength=experts)
+    assert int(meta[1]) == int(((counts + 255) // 256 * 256).sum())
+    x = torch.randn(tokens, hidden, device=DEV, dtype=torch.bfloat16)
+    gu = (torch.randn(experts, 2 * inter, hidden, device=DEV) * 0.05).requires_grad_()
+    dn = (torch.randn(experts, hidden, inter, device=DEV) * 0.05).requires_grad_()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        got = ops.fused_moe(x, gu, dn, dropped, w)
+        want = ops.fused_moe(x, gu, dn, idx, torch.where(drop, torch.zeros_like(w), w))
+    assert_close(got, want, 2e-2, "fused_moe with dropped routes")
+    nb.check_kernel_status()
