@@ -336,7 +336,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               const uint32_t bits = drop.word(uint32_t(q_row), uint32_t(k0 + c * 32 + 8 * g + 4 * w) >> 2);
 #pragma unroll
               for (int t = 0; t < 4; ++t)
-                e[4 * w + t] = ((bits >> (8 * t)) & 0xFFu) >= drop.thresh ? e[4 * w + t] * drop.inv_keep : 0.f;
+                e[4 * w + t] = ((bits >> (8 * t)) & 0xFFu) >= drop.thresh ? e[4 * w + t] : 0.f;   // 1 / keep: applied to O at the end
             }
           }
           uint4 q4;
@@ -362,7 +362,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(rr[i]);
       }
       if (q_row < p.S) {
-        const float inv_l = l > 0.f ? 1.f / l : 0.f;
+        const float inv_l = l > 0.f ? (drop.thresh != 0u ? drop.inv_keep : 1.f) / l : 0.f;
         store_row64(p.o + (long long)b * p.o_sb + (long long)h * p.o_sh + (long long)q_row * p.o_ss, o, inv_l);
         p.lse[((long long)bh) * p.S + q_row] = (m + log2f(l)) * LN2;
       }
