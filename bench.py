@@ -178,6 +178,10 @@ def main() -> None:
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is missing: install the reference first"}))
         return
+    if args.impl == "reference" and args.strategy not in (None, "single", "ddp", "fsdp"):
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": f"the reference has no {args.strategy!r} strategy (single, ddp, fsdp only)"}))
+        return
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29517")
 
