@@ -93,8 +93,8 @@ def _two_rank_worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-def test_two_gloo_ranks_match_single_process_on_the_global_batch(tmp_path):
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gloo_ranks_match_single_process_on_the_global_batch(tmp_path, world):
     port = 29640 + os.getpid() % 200
     mp.spawn(_two_rank_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     got = torch.load(tmp_path / "result.pt", weights_only=False)
@@ -104,4 +104,6 @@ def test_two_gloo_ranks_match_single_process_on_the_global_batch(tmp_path):
     for b in batches(3, batch=4 * world):
         tr.train_step(b)
     for name, p in model.state_dict().items():
-        assert torch.allclose(got["full"][name], p, atol=2e-5), name
+        # Adam divides by sqrt(v): where a gradient is tiny, a different summation order over ranks moves single elements
+        diff = (got["full"][name] - p).abs()
+        assert float(diff.max()) < 1e-4 and float(diff.mean()) < 1e-6, (name, float(diff.max()), float(diff.mean()))
