@@ -54,8 +54,8 @@ def _worker(rank, world, port, out_dir):
         strat.teardown()
 
 
-def test_expert_parallel_matches_single_process(tmp_path):
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_matches_single_process(tmp_path, world):
     mp.spawn(_worker, args=(world, 29900 + os.getpid() % 90, str(tmp_path)), nprocs=world, join=True)
     got = torch.load(tmp_path / "ep.pt")
     model = _model()
@@ -65,7 +65,8 @@ def test_expert_parallel_matches_single_process(tmp_path):
     want = model.state_dict()
     assert got["blocks.0.ffn.gate_up_proj"].shape == want["blocks.0.ffn.gate_up_proj"].shape
     for name, p in want.items():
-        assert torch.allclose(got[name], p, atol=3e-5), (name, float((got[name] - p).abs().max()))
+        diff = (got[name] - p).abs()
+        assert float(diff.max()) < 1e-4 and float(diff.mean()) < 2e-6, (name, float(diff.max()), float(diff.mean()))
 
 
 def test_capacity_mask_admits_highest_weights_first():
