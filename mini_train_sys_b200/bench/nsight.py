@@ -56,7 +56,7 @@ register_nsight_kernel("swiglu_fwd", "swiglu_fwd_kernel", _case("swiglu", 57344)
 register_nsight_kernel("swiglu_bwd", "swiglu_bwd_kernel", _case("swiglu", 57344))
 register_nsight_kernel("ce_forward", "ce_forward_kernel", _case("cross_entropy", 8192))
 register_nsight_kernel("ce_backward", "ce_backward_kernel", _case("cross_entropy", 8192))
-register_nsight_kernel("router_fwd", "router_fwd_kernel", _case("router", 262144))
+register_nsight_kernel("router_fwd", "router_forward_kernel", _case("router", 262144))
 register_nsight_kernel("moe_gather", "moe_gather_kernel", _case("fused_moe", 24576))
 register_nsight_kernel("moe_combine", "moe_combine_kernel", _case("fused_moe", 24576))
 
