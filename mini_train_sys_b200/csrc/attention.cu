@@ -92,29 +92,6 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// bf16 pair without the conversion unit: add half an ulp and keep the upper halves (round half up; differs from
-// round-to-nearest-even only on exact ties).  For finite non-negative inputs such as probabilities.
-__device__ __forceinline__ uint32_t pack2_alu(float lo, float hi) {
-  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
-}
-// Two fp32 operations per instruction (packed f32x2 forms of sm_100): halves the FMA-pipe instruction count of the softmax loops.
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)),
-      "l"(*reinterpret_cast<uint64_t*>(&c)));
-  return *reinterpret_cast<float2*>(&d);
-}
-__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
-  return *reinterpret_cast<float2*>(&d);
-}
-#ifdef MTS_ATTN_ALU_PACK
-#define PACK_P pack2_alu
-#else
-#define PACK_P pack2
-#endif
-
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int kstep) {   // kstep: 16 contraction elements
   return make_smem_desc_sw128(tile_addr + kstep * 32, 16, 1024);
 }
@@ -348,22 +325,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
         for (int g = 0; g < 4; ++g) {            // eight probabilities at a time: exp, dropout, pack, store
           float e[8];
-#ifdef MTS_ATTN_F32X2
-#pragma unroll
-          for (int i = 0; i < 8; i += 2) {
-            const float2 a2 = ffma2(make_float2(__uint_as_float(rr[8 * g + i]), __uint_as_float(rr[8 * g + i + 1])),
-                                    make_float2(scale_log2, scale_log2), make_float2(-m, -m));
-            e[i] = ex2(a2.x); e[i + 1] = ex2(a2.y);                               // masked entries are -inf -> 0
-            const float2 r2 = fadd2(make_float2(rowsum[i], rowsum[i + 1]), make_float2(e[i], e[i + 1]));
-            rowsum[i] = r2.x; rowsum[i + 1] = r2.y;
-          }
-#else
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             e[i] = ex2(fmaf(__uint_as_float(rr[8 * g + i]), scale_log2, -m));   // masked entries are -inf -> 0
             rowsum[i] += e[i];
           }
-#endif
           if (drop.thresh != 0u) {
 #pragma unroll
             for (int w = 0; w < 2; ++w) {
@@ -374,7 +340,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
           }
           uint4 q4;
-          q4.x = PACK_P(e[0], e[1]); q4.y = PACK_P(e[2], e[3]); q4.z = PACK_P(e[4], e[5]); q4.w = PACK_P(e[6], e[7]);
+          q4.x = pack2(e[0], e[1]); q4.y = pack2(e[2], e[3]); q4.z = pack2(e[4], e[5]); q4.w = pack2(e[6], e[7]);
           st_swizzled(half, r, (c & 1) * 4 + g, q4);
         }
       }
