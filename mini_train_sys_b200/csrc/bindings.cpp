@@ -57,8 +57,14 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
   return {y, rstd};
 }
 
-std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, bool need_dw) {
+// dres (optional): gradient of the residual branch with the shape of x; the result is dx + dres.
+std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, bool need_dw,
+                                const c10::optional<Tensor>& dres) {
   check_act(x, "x");
+  const bool fuse_res = dres.has_value() && dres->defined() && is_bf16(x);
+  if (dres.has_value() && dres->defined())
+    TORCH_CHECK(dres->scalar_type() == x.scalar_type() && dres->is_contiguous() && dres->numel() == x.numel() && dres->is_cuda(),
+                "dres must match x");
   TORCH_CHECK(dy.scalar_type() == x.scalar_type() && dy.is_contiguous() && x.is_contiguous(), "dy/x mismatch");
   const int64_t H = x.size(-1);
   TORCH_CHECK(H % 8 == 0 && H <= 1024, "rmsnorm backward supports hidden sizes up to 1024 (multiple of 8)");
@@ -66,9 +72,11 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
   c10::cuda::CUDAGuard guard(x.device());
   Tensor dx = torch::empty_like(x);
   Tensor dw = need_dw ? torch::zeros({H}, x.options().dtype(torch::kFloat)) : Tensor();
-  check_launch(mts::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr(),
+  check_launch(mts::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr<float>(), rstd.data_ptr<float>(),
+                                       fuse_res ? dres->data_ptr() : nullptr, dx.data_ptr(),
                                        need_dw ? dw.data_ptr<float>() : nullptr, rows, int(H), is_bf16(x), cur_stream()),
                "rmsnorm_bwd");
+  if (dres.has_value() && dres->defined() && !fuse_res) dx.add_(*dres);
   return {dx, dw};
 }
 
@@ -379,7 +387,8 @@ void bind_comm(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("need_dw"),
+        py::arg("dres") = py::none());
   m.def("rope", &rope);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);

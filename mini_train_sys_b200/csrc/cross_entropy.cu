@@ -22,6 +22,14 @@ template <typename T> __device__ __forceinline__ T from_f(float v);
 template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
 
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct MaxSum {
   float m, s;
   __device__ __forceinline__ void push(float z) {
@@ -31,6 +39,26 @@ struct MaxSum {
     } else {
       s += __expf(z - m);
     }
+  }
+  // N values at once: one maximum, at most one rescale of the running sum, then N independent exponentials in two
+  // chains.  The element-at-a-time form carries (m, s) through a branch per element and is bound by that chain.
+  template <int N>
+  __device__ __forceinline__ void push_vec(const float (&z)[N]) {
+    float vm = z[0];
+#pragma unroll
+    for (int j = 1; j < N; ++j) vm = fmaxf(vm, z[j]);
+    if (vm > m) {
+      s *= ex2f((m - vm) * kLog2e);      // m = -inf: the factor is 0 and s is 0
+      m = vm;
+    }
+    const float mb = m == -CUDART_INF_F ? 0.f : -m * kLog2e;
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int j = 0; j < N; j += 2) {
+      a += ex2f(fmaf(z[j], kLog2e, mb));
+      b += ex2f(fmaf(z[j + 1], kLog2e, mb));
+    }
+    s += a + b;
   }
   __device__ __forceinline__ void merge(const MaxSum& o) {
     const float nm = fmaxf(m, o.m);
@@ -65,7 +93,33 @@ ce_forward_kernel(const T* __restrict__ logits, long long ld, const long long* _
   const long long r = blockIdx.x;
   const T* row = logits + r * ld;
   MaxSum acc{-CUDART_INF_F, 0.f};
-  for_each_column<T>(row, vocab, [&](int, float z) { acc.push(z); });
+  {
+    constexpr int per = 16 / sizeof(T);
+    int head = int(((16 - (reinterpret_cast<uintptr_t>(row) & 15)) & 15) / sizeof(T));
+    if (head > vocab) head = vocab;
+    for (int c = threadIdx.x; c < head; c += blockDim.x) acc.push(to_f<T>(row[c]));
+    const int nvec = (vocab - head) / per;
+    const uint4* body = reinterpret_cast<const uint4*>(row + head);
+    int v = threadIdx.x;
+    for (; v + int(blockDim.x) < nvec; v += 2 * blockDim.x) {      // two 16-byte loads in flight per thread
+      const uint4 q0 = body[v], q1 = body[v + blockDim.x];
+      float z[2 * per];
+      const T* e0 = reinterpret_cast<const T*>(&q0);
+      const T* e1 = reinterpret_cast<const T*>(&q1);
+#pragma unroll
+      for (int j = 0; j < per; ++j) { z[j] = to_f<T>(e0[j]); z[per + j] = to_f<T>(e1[j]); }
+      acc.push_vec(z);
+    }
+    for (; v < nvec; v += blockDim.x) {
+      const uint4 q = body[v];
+      const T* e = reinterpret_cast<const T*>(&q);
+      float z[per];
+#pragma unroll
+      for (int j = 0; j < per; ++j) z[j] = to_f<T>(e[j]);
+      acc.push_vec(z);
+    }
+    for (int c = head + nvec * per + threadIdx.x; c < vocab; c += blockDim.x) acc.push(to_f<T>(row[c]));
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     MaxSum other{__shfl_xor_sync(0xffffffffu, acc.m, o), __shfl_xor_sync(0xffffffffu, acc.s, o)};
@@ -104,19 +158,26 @@ ce_backward_kernel(T* __restrict__ logits, long long ld, const long long* __rest
   constexpr int per = 16 / sizeof(T);
   int head = int(((16 - (reinterpret_cast<uintptr_t>(row) & 15)) & 15) / sizeof(T));
   if (head > vocab) head = vocab;
+  const float lse2 = -lse * kLog2e;
   auto grad = [&](int c, float z) -> float {
-    float g = live ? __expf(z - lse) : 0.f;
+    float g = live ? ex2f(fmaf(z, kLog2e, lse2)) : 0.f;
     if (c == t) g -= 1.f;
     return g * scale;
   };
   for (int c = threadIdx.x; c < head; c += blockDim.x) row[c] = from_f<T>(grad(c, to_f<T>(row[c])));
   const int nvec = (vocab - head) / per;
   uint4* body = reinterpret_cast<uint4*>(row + head);
+  const int t_vec = live && t >= head ? int((t - head) / per) : -1;     // the one vector that holds the target column
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
     uint4 q = body[v];
     T* e = reinterpret_cast<T*>(&q);
+    if (v == t_vec) {
 #pragma unroll
-    for (int j = 0; j < per; ++j) e[j] = from_f<T>(grad(head + v * per + j, to_f<T>(e[j])));
+      for (int j = 0; j < per; ++j) e[j] = from_f<T>(grad(head + v * per + j, to_f<T>(e[j])));
+    } else {
+#pragma unroll
+      for (int j = 0; j < per; ++j) e[j] = from_f<T>((live ? ex2f(fmaf(to_f<T>(e[j]), kLog2e, lse2)) : 0.f) * scale);
+    }
     body[v] = q;
   }
   for (int c = head + nvec * per + threadIdx.x; c < vocab; c += blockDim.x) row[c] = from_f<T>(grad(c, to_f<T>(row[c])));

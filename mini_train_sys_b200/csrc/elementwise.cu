@@ -200,7 +200,10 @@ __device__ __forceinline__ void unpack8(const uint4& q, float (&v)[8]) {
 template <int VPL>
 __global__ void __launch_bounds__(kNormWarps * 32, 3)
 rmsnorm_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
-                        const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, long long rows, int H) {
+                        const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                        float* __restrict__ dw, long long rows, int H) {
+  // dres (optional): gradient that reached x through the residual branch; added here so that the sum of the two
+  // paths costs no pass of its own.
   extern __shared__ float red[];   // [kNormWarps][H]
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -249,6 +252,12 @@ rmsnorm_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
         Vec8<float>::load(w + v * 8, wv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = inv * (ds[j] * wv[j] - xs[j] * coef);
+        if (dres != nullptr) {
+          float rs[8];
+          unpack8(*reinterpret_cast<const uint4*>(dres + row * H + v * 8), rs);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += rs[j];
+        }
         Vec8<__nv_bfloat16>::store(dx + row * H + v * 8, o);
       }
     }
@@ -411,9 +420,10 @@ cudaError_t launch_rmsnorm_fwd(const void* x, const float* w, void* y, float* rs
   return cudaGetLastError();
 }
 
-cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, void* dx, float* dw,
-                               long long rows, int H, bool bf16, cudaStream_t stream) {
+cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres, void* dx,
+                               float* dw, long long rows, int H, bool bf16, cudaStream_t stream) {
   if (H % 8 != 0 || H > 32 * kMaxVecPerLane * 8) return cudaErrorInvalidValue;
+  if (dres != nullptr && !bf16) return cudaErrorInvalidValue;      // the fused residual sum exists for bf16 only
   const size_t smem = dw != nullptr ? sizeof(float) * kNormWarps * H : 0;
   if (bf16) {
     const int vpl = (H / 8 + 31) / 32;
@@ -421,11 +431,12 @@ cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, co
     auto* dyp = static_cast<const __nv_bfloat16*>(dy);
     auto* xp = static_cast<const __nv_bfloat16*>(x);
     auto* dxp = static_cast<__nv_bfloat16*>(dx);
+    auto* drp = static_cast<const __nv_bfloat16*>(dres);
     switch (vpl) {
-      case 1: rmsnorm_bwd_bf16_kernel<1><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, dxp, dw, rows, H); break;
-      case 2: rmsnorm_bwd_bf16_kernel<2><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, dxp, dw, rows, H); break;
-      case 3: rmsnorm_bwd_bf16_kernel<3><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, dxp, dw, rows, H); break;
-      default: rmsnorm_bwd_bf16_kernel<4><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, dxp, dw, rows, H); break;
+      case 1: rmsnorm_bwd_bf16_kernel<1><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, drp, dxp, dw, rows, H); break;
+      case 2: rmsnorm_bwd_bf16_kernel<2><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, drp, dxp, dw, rows, H); break;
+      case 3: rmsnorm_bwd_bf16_kernel<3><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, drp, dxp, dw, rows, H); break;
+      default: rmsnorm_bwd_bf16_kernel<4><<<grid3, kNormWarps * 32, smem, stream>>>(dyp, xp, w, rstd, drp, dxp, dw, rows, H); break;
     }
     ++g_launch_count;
     return cudaGetLastError();

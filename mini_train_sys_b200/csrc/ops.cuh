@@ -13,8 +13,8 @@ int device_sm_count();
 // ---- elementwise.cu ----
 cudaError_t launch_rmsnorm_fwd(const void* x, const float* w, void* y, float* rstd, long long rows, int H, float eps,
                                bool bf16, cudaStream_t stream);
-cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, void* dx, float* dw,
-                               long long rows, int H, bool bf16, cudaStream_t stream);
+cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres, void* dx,
+                               float* dw, long long rows, int H, bool bf16, cudaStream_t stream);
 cudaError_t launch_rope(const void* in, void* out, const void* cosp, const void* sinp, int B, int Hh, int S, int D,
                         long long sb, long long sh, long long ss, long long osb, long long osh, long long oss,
                         bool backward, bool bf16, cudaStream_t stream);

@@ -61,6 +61,15 @@ class RMSNorm(nn.Module):
     def forward(self, x: torch.Tensor, ops: OpsBackend) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps)
 
+    def with_residual(self, x: torch.Tensor, ops: OpsBackend) -> tuple[torch.Tensor, torch.Tensor]:
+        """``(norm(x), x)`` for a pre-norm block.  A backend that offers ``rmsnorm_residual`` returns its own handle on x,
+        through which the residual branch's gradient comes back into the norm's backward kernel."""
+
+        fused = getattr(ops, "rmsnorm_residual", None)
+        if fused is not None and x.is_cuda:
+            return fused(x, self.weight, self.eps)
+        return ops.rmsnorm(x, self.weight, self.eps), x
+
 
 class CausalSelfAttention(nn.Module):
     def __init__(self, cfg: ModelConfig) -> None:
@@ -160,8 +169,10 @@ class TransformerBlock(nn.Module):
     mlp = property(lambda self: self.ffn)
 
     def forward(self, x: torch.Tensor, ops: OpsBackend, rope_cos: torch.Tensor, rope_sin: torch.Tensor) -> FeedForwardOutput:
-        x = self.attn(self.attn_norm(x, ops), ops, rope_cos, rope_sin, residual=x)
-        return self.ffn(self.ffn_norm(x, ops), ops, residual=x)      # hidden_states already include the residual
+        h, res = self.attn_norm.with_residual(x, ops)
+        x = self.attn(h, ops, rope_cos, rope_sin, residual=res)
+        h, res = self.ffn_norm.with_residual(x, ops)
+        return self.ffn(h, ops, residual=res)      # hidden_states already include the residual
 
 
 SwiGLUMLP = DenseFeedForward

@@ -231,6 +231,32 @@ class _RMSNormFn(torch.autograd.Function):
         return dx, (dw.to(ctx.w_dtype) if dw is not None and dw.numel() else None), None
 
 
+class _RMSNormResidualFn(torch.autograd.Function):
+    """``(rmsnorm(x), x)``: the second output is x itself, handed to the residual branch.  Autograd then delivers the
+    gradient of that branch to this backward, where the kernel adds it to the gradient of the norm, instead of summing
+    the two paths in a pass of its own."""
+
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        xc = x if x.is_contiguous() else x.contiguous()
+        w32 = weight if weight.dtype == torch.float32 else weight.float()
+        y, rstd = ext().rmsnorm_fwd(xc, w32.contiguous(), eps)
+        ctx.save_for_backward(xc, w32, rstd)
+        ctx.w_dtype = weight.dtype
+        return y, xc          # an input returned as an output: autograd gives it a node of its own
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        x, w32, rstd = ctx.saved_tensors
+        if dy is None:
+            return dres, None, None
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        if dres is not None and not dres.is_contiguous():
+            dres = dres.contiguous()
+        dx, dw = ext().rmsnorm_bwd(dyc, x, w32, rstd, ctx.needs_input_grad[1], dres)
+        return dx, (dw.to(ctx.w_dtype) if dw is not None and dw.numel() else None), None
+
+
 class _RopeFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, cos, sin):
@@ -559,6 +585,16 @@ class NativeOpsBackend(TorchOpsBackend):
         if self._count("rmsnorm", ok):
             return _RMSNormFn.apply(x, weight, eps)
         return super().rmsnorm(x, weight, eps)
+
+    def rmsnorm_residual(self, x, weight, eps):
+        """``(rmsnorm(x), x)`` for a pre-norm block: the backward sums the norm's and the residual's gradient in one kernel."""
+
+        ok = _native_act(x) and weight.is_cuda and x.shape[-1] % 8 == 0 and x.shape[-1] <= 1024
+        if self._count("rmsnorm", ok):
+            if torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad):
+                return _RMSNormResidualFn.apply(x, weight, eps)
+            return _RMSNormFn.apply(x, weight, eps), x
+        return super().rmsnorm(x, weight, eps), x
 
     def rope(self, q, k, cos, sin):
         def aligned(t):

@@ -60,6 +60,30 @@ def test_rmsnorm(ops, dtype, rows, hidden):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rmsnorm_residual_sums_both_gradient_paths_in_the_kernel(ops, dtype):
+    torch.manual_seed(3)
+    rows, hidden = 777, 768
+    x = torch.randn(rows, hidden, device=DEV, dtype=dtype, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV)).requires_grad_()
+    dy = torch.randn(rows, hidden, device=DEV, dtype=dtype)
+    dres = torch.randn(rows, hidden, device=DEV, dtype=dtype)
+    y, res = ops.rmsnorm_residual(x, w, 1e-5)
+    assert res.data_ptr() == x.data_ptr()
+    gx, gw = torch.autograd.grad((y, res), (x, w), (dy, dres))
+    x64 = x.detach().double().requires_grad_()
+    w64 = w.detach().double().requires_grad_()
+    y64 = x64 * torch.rsqrt(x64.pow(2).mean(-1, keepdim=True) + 1e-5) * w64
+    rx, rw = torch.autograd.grad((y64, x64 * 1.0), (x64, w64), (dy.double(), dres.double()))
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    assert_close(gx, rx, tol, "dx")
+    assert_close(gw, rw, 5e-3 if dtype == torch.bfloat16 else 1e-4, "dw")
+    # only the residual branch used: the gradient passes through unchanged
+    y2, res2 = ops.rmsnorm_residual(x, w, 1e-5)
+    (gx2,) = torch.autograd.grad(res2, x, dres, allow_unused=True)
+    assert torch.equal(gx2, dres)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_rope_strided(ops, dtype):
     from mini_train_sys_b200.models.rotary import rope_tables
 
