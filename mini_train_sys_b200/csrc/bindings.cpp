@@ -182,7 +182,9 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t M, int64_t N, in
   g.out = out.data_ptr(); g.ldo = ldo; g.out_fp32 = out.scalar_type() == at::kFloat;
   g.accumulate = accumulate; g.atomic_out = atomic_out;
   if (aux.has_value() && aux->defined()) {
-    TORCH_CHECK(is_bf16(*aux) && aux->dim() == 2 && aux->stride(1) == 1, "aux must be a row-major bf16 matrix");
+    // storage for the saved pre-activations; the kernels lay it out in 32-row blocks of their own
+    TORCH_CHECK(is_bf16(*aux) && aux->dim() == 2 && aux->is_contiguous() && aux->size(0) % 32 == 0 && aux->size(1) % 8 == 0,
+                "aux must be a contiguous bf16 matrix with a multiple of 32 rows and of 8 columns");
     g.aux = aux->data_ptr(); g.ld_aux = aux->stride(0);
   }
   auto int_ptr = [](const c10::optional<Tensor>& t) -> const int* {

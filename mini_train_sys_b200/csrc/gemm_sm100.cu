@@ -212,31 +212,19 @@ __device__ __forceinline__ void store_row_f32(float* dst, float (&v)[32], int va
   }
 }
 
-__device__ __forceinline__ void load_row_bf16(const __nv_bfloat16* src, float (&v)[32], int valid_cols) {
-  if (valid_cols >= 32 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint4 q = reinterpret_cast<const uint4*>(src)[j];
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
-        v[8 * j + 2 * i] = __low2float(h);
-        v[8 * j + 2 * i + 1] = __high2float(h);
-      }
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = j < valid_cols ? __bfloat162float(src[j]) : 0.f;
-  }
-}
-
 __device__ __forceinline__ void regs_to_float(const uint32_t (&r)[32], float (&v)[32]) {
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
 }
 
-__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.f / (1.f + __expf(-x)); }
+// sigmoid(x) = 0.5 tanh(x / 2) + 0.5: one MUFU instruction and two FMA-pipe ones.  The form 1 / (1 + exp(-x)) costs an
+// exponential, a full-precision division (about ten instructions) and made the SwiGLU epilogues, not the MMA, the bound
+// of the expert GEMMs.  tanh.approx is good to about 2^-11, inside the bf16 rounding of everything these epilogues store.
+__device__ __forceinline__ float sigmoidf_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(0.5f, t, 0.5f);
+}
 
 // ---- staging for TMA stores: rows of 128 bytes, 16-byte chunk j of row r lives at chunk (j ^ (r & 7)) ----
 __device__ __forceinline__ void stage_chunk(uint8_t* stage, int row, int j, uint4 q) {
@@ -267,7 +255,15 @@ __device__ __forceinline__ void stage_row_f32(uint8_t* stage, int row, const flo
   }
 }
 
-// Warp-collective: publish the staged box and hand it to the TMA unit; returns once the unit has read shared memory.
+// Warp-collective: the staging box may be rewritten once the TMA unit has read what the previous flush handed over.
+// Waiting here, right before the next write, instead of right after the flush lets the math of the next box run while
+// the unit drains the last one.
+__device__ __forceinline__ void stage_acquire(int lane) {
+  if (lane == 0) tma_store_wait_read<0>();
+  __syncwarp();
+}
+
+// Warp-collective: publish the staged box and hand it to the TMA unit.  The box belongs to the unit until stage_acquire.
 __device__ __forceinline__ void flush_box(const CUtensorMap* map, const uint8_t* stage, int col, int row0, int group, bool reduce,
                                           int lane) {
   fence_proxy_async_smem();
@@ -276,9 +272,45 @@ __device__ __forceinline__ void flush_box(const CUtensorMap* map, const uint8_t*
     if (reduce) tma_reduce_add_3d(map, stage, col, row0, group);
     else tma_store_3d(map, stage, col, row0, group);
     tma_store_commit();
-    tma_store_wait_read<0>();
   }
-  __syncwarp();
+}
+
+// The SwiGLU pre-activations saved by the forward epilogue are read by nothing but the backward epilogue, so they live in a
+// layout of their own: [rows / 32][ld / 8][32 rows][8 values].  The 16 bytes that lane r (row r of a 32-row block) owns of
+// column chunk q sit between those of lanes r - 1 and r + 1, so every per-row access of a warp is one 512-byte transaction
+// (row-major, the same access touched 32 lines and ran at an eighth of the L1 rate, which bounded the whole GEMM).
+__device__ __forceinline__ long long aux_chunk(long long row, int col, long long ld) {     // element offset; col % 8 == 0
+  return (((row >> 5) * (ld >> 3) + (col >> 3)) * 32 + (row & 31)) * 8;
+}
+
+__device__ __forceinline__ void aux_store32(__nv_bfloat16* aux, long long row, int col, long long ld, const float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 q;
+    q.x = pack_bf16(v[8 * j + 0], v[8 * j + 1]); q.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+    q.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]); q.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+    *reinterpret_cast<uint4*>(aux + aux_chunk(row, col + 8 * j, ld)) = q;
+  }
+}
+
+// 32 saved gate values and 32 saved up values of one row, as packed bf16 (four 16-byte loads each).
+__device__ __forceinline__ void aux_load32(const __nv_bfloat16* aux, long long row, int gate_col, int up_col, long long ld,
+                                           uint4 (&pg)[4], uint4 (&pu)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    pg[j] = __ldg(reinterpret_cast<const uint4*>(aux + aux_chunk(row, gate_col + 8 * j, ld)));
+    pu[j] = __ldg(reinterpret_cast<const uint4*>(aux + aux_chunk(row, up_col + 8 * j, ld)));
+  }
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* ptr) { asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr)); }
+
+template <int OFF>
+__device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&v)[32]) {
+  v[OFF + 0] = __uint_as_float(q.x << 16); v[OFF + 1] = __uint_as_float(q.x & 0xFFFF0000u);
+  v[OFF + 2] = __uint_as_float(q.y << 16); v[OFF + 3] = __uint_as_float(q.y & 0xFFFF0000u);
+  v[OFF + 4] = __uint_as_float(q.z << 16); v[OFF + 5] = __uint_as_float(q.z & 0xFFFF0000u);
+  v[OFF + 6] = __uint_as_float(q.w << 16); v[OFF + 7] = __uint_as_float(q.w & 0xFFFF0000u);
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
@@ -479,6 +511,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const uint32_t acc_empty_addr[2] = {PAIR ? map_to_cta(smem_u32(&acc_empty[0]), 0) : 0u,
                                         PAIR ? map_to_cta(smem_u32(&acc_empty[1]), 0) : 0u};
     uint8_t* stage = smem + C::RING_BYTES + (warp - 2) * EPI_STAGE_BYTES;
+    const bool aux_vec = p.aux != nullptr && (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0 && (p.ld_aux & 7) == 0 && (p.N & 7) == 0;
     int acc_it = 0;
     bool ok = true;
     for (int tile = worker; tile < total && ok; tile += workers) {
@@ -492,6 +525,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           float z[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) z[j] = 0.f;
+          stage_acquire(lane);
           if (p.out_fp32) stage_row_f32(stage, lane, z);
           else { stage_row_bf16(stage, lane, 0, z); stage_row_bf16(stage, lane, 4, z); }
           const int step = p.out_fp32 ? 32 : 64;
@@ -510,6 +544,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
         }
         continue;
+      }
+      // SwiGLU backward reads the saved [gate | up] values of its rows, 32 columns at a time.  The first chunk is fetched
+      // into registers before the accumulator is awaited, so that its latency hides behind the MMA; the lines of the
+      // other chunks are pulled into L2 meanwhile, and each is loaded one chunk ahead of its use.
+      uint4 cg[4], cu[4];
+      bool swb_fast = false;
+      if (p.tma_store && p.epilogue == EPI_SWIGLU_BWD) {
+        const int colw = t.c_col + half_id * 128;
+        const __nv_bfloat16* pre = reinterpret_cast<const __nv_bfloat16*>(p.aux);
+        swb_fast = row0 < t.row_limit && aux_vec && colw + 128 <= p.N;
+        if (swb_fast) {
+          aux_load32(pre, row, colw, p.N + colw, p.ld_aux, cg, cu);
+          // this warp's 128 gate columns are one contiguous 8 KB run of the blocked layout, and so are its up columns:
+          // 64 lines each, two per lane
+          const char* g_run = reinterpret_cast<const char*>(pre + aux_chunk(row0, colw, p.ld_aux));
+          const char* u_run = reinterpret_cast<const char*>(pre + aux_chunk(row0, p.N + colw, p.ld_aux));
+          prefetch_l2(g_run + 128 * lane); prefetch_l2(g_run + 128 * (lane + 32));
+          prefetch_l2(u_run + 128 * lane); prefetch_l2(u_run + 128 * (lane + 32));
+        }
       }
       const int buf = acc_it & 1;
       const uint32_t acc_ph = (acc_it >> 1) & 1;
@@ -544,18 +597,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int col0 = t.c_col + c0 * 32;
         float v[32];
         if (p.out_fp32) {
-          regs_to_float(r0, v); stage_row_f32(stage, lane, v);
+          stage_acquire(lane); regs_to_float(r0, v); stage_row_f32(stage, lane, v);
           if (box_rows && col0 < t.col_limit) flush_box(&tm_out, stage, col0, row0, t.out_group, reduce, lane);
-          regs_to_float(r1, v); stage_row_f32(stage, lane, v);
+          stage_acquire(lane); regs_to_float(r1, v); stage_row_f32(stage, lane, v);
           if (box_rows && col0 + 32 < t.col_limit) flush_box(&tm_out, stage, col0 + 32, row0, t.out_group, reduce, lane);
-          regs_to_float(r2, v); stage_row_f32(stage, lane, v);
+          stage_acquire(lane); regs_to_float(r2, v); stage_row_f32(stage, lane, v);
           if (box_rows && col0 + 64 < t.col_limit) flush_box(&tm_out, stage, col0 + 64, row0, t.out_group, reduce, lane);
-          regs_to_float(r3, v); stage_row_f32(stage, lane, v);
+          stage_acquire(lane); regs_to_float(r3, v); stage_row_f32(stage, lane, v);
           if (box_rows && col0 + 96 < t.col_limit) flush_box(&tm_out, stage, col0 + 96, row0, t.out_group, reduce, lane);
         } else {
+          stage_acquire(lane);
           regs_to_float(r0, v); stage_row_bf16(stage, lane, 0, v);
           regs_to_float(r1, v); stage_row_bf16(stage, lane, 4, v);
           if (box_rows && col0 < t.col_limit) flush_box(&tm_out, stage, col0, row0, t.out_group, false, lane);
+          stage_acquire(lane);
           regs_to_float(r2, v); stage_row_bf16(stage, lane, 0, v);
           regs_to_float(r3, v); stage_row_bf16(stage, lane, 4, v);
           if (box_rows && col0 + 64 < t.col_limit) flush_box(&tm_out, stage, col0 + 64, row0, t.out_group, false, lane);
@@ -575,12 +630,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         float g0[32], g1[32], u[32];
         regs_to_float(rg0, g0);
         regs_to_float(rg1, g1);
-        if (p.aux != nullptr) {
-          stage_row_bf16(stage, lane, 0, g0); stage_row_bf16(stage, lane, 4, g1);
-          if (box_ok) flush_box(&tm_aux, stage, col0, row0, 0, false, lane);
-          regs_to_float(ru0, u); stage_row_bf16(stage, lane, 0, u);
-          regs_to_float(ru1, u); stage_row_bf16(stage, lane, 4, u);
-          if (box_ok) flush_box(&tm_aux, stage, half + col0, row0, 0, false, lane);
+        if (p.aux != nullptr && box_ok) {          // whole 32-row blocks: rows past the segment's end are padding of the buffer
+          __nv_bfloat16* pre = reinterpret_cast<__nv_bfloat16*>(p.aux);
+          aux_store32(pre, row, col0, p.ld_aux, g0);
+          aux_store32(pre, row, col0 + 32, p.ld_aux, g1);
+          regs_to_float(ru0, u); aux_store32(pre, row, half + col0, p.ld_aux, u);
+          regs_to_float(ru1, u); aux_store32(pre, row, half + col0 + 32, p.ld_aux, u);
         }
         regs_to_float(ru0, u);
 #pragma unroll
@@ -588,47 +643,64 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         regs_to_float(ru1, u);
 #pragma unroll
         for (int j = 0; j < 32; ++j) g1[j] = g1[j] * sigmoidf_fast(g1[j]) * u[j];
+        stage_acquire(lane);
         stage_row_bf16(stage, lane, 0, g0); stage_row_bf16(stage, lane, 4, g1);
         if (box_ok) flush_box(&tm_out, stage, col0, row0, 0, false, lane);
       } else if (p.tma_store) {  // EPI_SWIGLU_BWD
-#pragma unroll 1
-        for (int cc = 0; cc < 4; cc += 2) {
-          uint32_t ra[32], rb[32];
-          const int c0 = half_id * 4 + cc;
-          tmem_ld_32x32(taddr + c0 * 32, ra);
-          tmem_ld_32x32(taddr + (c0 + 1) * 32, rb);
+        // Four 32-column chunks; registers hold one chunk at a time (accumulator, saved gate / up, results), the packed
+        // d(up) of an even chunk, which waits for its own box, and the packed saved values of the next chunk.
+        const __nv_bfloat16* pre = reinterpret_cast<const __nv_bfloat16*>(p.aux);
+        uint4 keep[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = half_id * 4 + k;
+          const int col = t.c_col + c * 32;
+          uint32_t r[32];
+          float g[32], u[32];
+          tmem_ld_32x32(taddr + c * 32, r);
           tmem_ld_wait();
-          if (cc == 2) release_acc();
-          const int col0 = t.c_col + c0 * 32;
-          const bool box_ok = row0 < t.row_limit && col0 < p.N;
-          float dg0[32], dg1[32], du0[32], du1[32];
-          auto grads = [&](uint32_t (&r)[32], int col, float (&dg)[32], float (&du)[32]) {
-            float d[32];
-            regs_to_float(r, d);
-            const int valid = p.N - col;
-            if (row_ok && valid > 0) {
-              const __nv_bfloat16* pre = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ld_aux;
-              load_row_bf16(pre + col, dg, valid);
-              load_row_bf16(pre + p.N + col, du, valid);
-            } else {
+          if (k == 3) release_acc();
+          if (swb_fast) {
+            unpack_bf16x8<0>(cg[0], g); unpack_bf16x8<8>(cg[1], g); unpack_bf16x8<16>(cg[2], g); unpack_bf16x8<24>(cg[3], g);
+            unpack_bf16x8<0>(cu[0], u); unpack_bf16x8<8>(cu[1], u); unpack_bf16x8<16>(cu[2], u); unpack_bf16x8<24>(cu[3], u);
+            if (k < 3) aux_load32(pre, row, col + 32, p.N + col + 32, p.ld_aux, cg, cu);   // in flight during the math below
+          } else if (row0 < t.row_limit && aux_vec && col < p.N) {      // tiles that reach past N: chunk by chunk
+            uint4 tg[4], tu[4];
+            aux_load32(pre, row, col, p.N + col, p.ld_aux, tg, tu);
+            unpack_bf16x8<0>(tg[0], g); unpack_bf16x8<8>(tg[1], g); unpack_bf16x8<16>(tg[2], g); unpack_bf16x8<24>(tg[3], g);
+            unpack_bf16x8<0>(tu[0], u); unpack_bf16x8<8>(tu[1], u); unpack_bf16x8<16>(tu[2], u); unpack_bf16x8<24>(tu[3], u);
+          } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) { dg[j] = 0.f; du[j] = 0.f; }
-            }
+            for (int j = 0; j < 32; ++j) { g[j] = 0.f; u[j] = 0.f; }
+          }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float sg = sigmoidf_fast(dg[j]);
-              const float silu = dg[j] * sg;
-              const float dgate = d[j] * du[j] * (sg + silu * (1.f - sg));
-              du[j] = d[j] * silu;
-              dg[j] = dgate;
+          for (int j = 0; j < 32; ++j) {             // g <- d gate, u <- d up
+            const float d = __uint_as_float(r[j]);
+            const float sg = sigmoidf_fast(g[j]);
+            const float silu = g[j] * sg;
+            const float dgate = d * u[j] * (sg + silu * (1.f - sg));
+            u[j] = d * silu;
+            g[j] = dgate;
+          }
+          if ((k & 1) == 0) {
+            stage_acquire(lane);
+            stage_row_bf16(stage, lane, 0, g);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              keep[j].x = pack_bf16(u[8 * j + 0], u[8 * j + 1]); keep[j].y = pack_bf16(u[8 * j + 2], u[8 * j + 3]);
+              keep[j].z = pack_bf16(u[8 * j + 4], u[8 * j + 5]); keep[j].w = pack_bf16(u[8 * j + 6], u[8 * j + 7]);
             }
-          };
-          grads(ra, col0, dg0, du0);
-          grads(rb, col0 + 32, dg1, du1);
-          stage_row_bf16(stage, lane, 0, dg0); stage_row_bf16(stage, lane, 4, dg1);
-          if (box_ok) flush_box(&tm_out, stage, col0, row0, 0, false, lane);
-          stage_row_bf16(stage, lane, 0, du0); stage_row_bf16(stage, lane, 4, du1);
-          if (box_ok) flush_box(&tm_out, stage, p.N + col0, row0, 0, false, lane);
+          } else {
+            const int col0 = col - 32;
+            const bool box_ok = row0 < t.row_limit && col0 < p.N;
+            stage_row_bf16(stage, lane, 4, g);
+            if (box_ok) flush_box(&tm_out, stage, col0, row0, 0, false, lane);
+            stage_acquire(lane);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) stage_chunk(stage, lane, j, keep[j]);
+            stage_row_bf16(stage, lane, 4, u);
+            if (box_ok) flush_box(&tm_out, stage, p.N + col0, row0, 0, false, lane);
+          }
         }
       } else if (p.epilogue == EPI_STORE) {
         // this warp's four chunks: one TMEM round trip
@@ -669,10 +741,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const int col = t.c_col + c * 32;
           const int valid = half - col;
           if (row_ok && valid > 0) {
-            if (p.aux != nullptr) {
-              __nv_bfloat16* pre = reinterpret_cast<__nv_bfloat16*>(p.aux) + (long long)row * p.ld_aux;
-              store_row_bf16(pre + col, g, valid);
-              store_row_bf16(pre + half + col, u, valid);
+            if (p.aux != nullptr) {                 // N % 256 == 0 for this epilogue: chunks are whole
+              __nv_bfloat16* pre = reinterpret_cast<__nv_bfloat16*>(p.aux);
+              aux_store32(pre, row, col, p.ld_aux, g);
+              aux_store32(pre, row, half + col, p.ld_aux, u);
             }
 #pragma unroll
             for (int j = 0; j < 32; ++j) g[j] = g[j] * sigmoidf_fast(g[j]) * u[j];
@@ -694,9 +766,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             const int col = t.c_col + c * 32;
             const int valid = p.N - col;
             if (row_ok && valid > 0) {
-              const __nv_bfloat16* pre = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ld_aux;
-              load_row_bf16(pre + col, g, valid);
-              load_row_bf16(pre + p.N + col, u, valid);
+              uint4 tg[4], tu[4];
+              aux_load32(reinterpret_cast<const __nv_bfloat16*>(p.aux), row, col, p.N + col, p.ld_aux, tg, tu);
+              unpack_bf16x8<0>(tg[0], g); unpack_bf16x8<8>(tg[1], g); unpack_bf16x8<16>(tg[2], g); unpack_bf16x8<24>(tg[3], g);
+              unpack_bf16x8<0>(tu[0], u); unpack_bf16x8<8>(tu[1], u); unpack_bf16x8<16>(tu[2], u); unpack_bf16x8<24>(tu[3], u);
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
                 const float s = sigmoidf_fast(g[j]);
@@ -863,8 +936,7 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
     int64_t map_cols = (out_cols + per16 - 1) / per16 * per16;
     bool ok = env_tma_store != 0 && (map_cols == out_cols || (map_cols <= a.ldo && a.epilogue == EPI_STORE && !a.accumulate && !a.atomic_out));
     ok = ok && encode_out_3d(&tm_out, a.out, a.out_fp32 != 0, map_cols, a.M, groups, a.ldo, a.out_group_stride);
-    if (ok && a.epilogue == EPI_SWIGLU && a.aux != nullptr) ok = encode_out_3d(&tm_aux, a.aux, false, a.N, a.M, 1, a.ld_aux, 0);
-    else if (ok) tm_aux = tm_out;
+    if (ok) tm_aux = tm_out;     // spare map slot: the saved pre-activations are written with plain coalesced stores
     if (!ok) { tm_out = tm_a; tm_aux = tm_a; }
     p.tma_store = ok ? 1 : 0;
   }
@@ -875,7 +947,9 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
   p.tiles_n = int((a.N + BN - 1) / BN);
   g_last_error = "inconsistent epilogue arguments";
   if (a.epilogue == EPI_SWIGLU && (a.N % 256 != 0 || a.mode != GEMM_GROUPED_M || a.b_mn_major)) return cudaErrorInvalidValue;
-  if (a.epilogue == EPI_SWIGLU_BWD && a.aux == nullptr) return cudaErrorInvalidValue;
+  if (a.epilogue == EPI_SWIGLU_BWD && (a.aux == nullptr || a.N % 32 != 0)) return cudaErrorInvalidValue;
+  // saved pre-activations: blocked layout of 32-row x 8-value chunks (see aux_chunk), addressed with 16-byte accesses
+  if (a.aux != nullptr && ((reinterpret_cast<uintptr_t>(a.aux) & 15) != 0 || a.ld_aux % 8 != 0)) return cudaErrorInvalidValue;
   if (a.atomic_out && !a.out_fp32) return cudaErrorInvalidValue;
   g_last_error = "";
 
