@@ -262,10 +262,12 @@ std::vector<Tensor> router_forward(const Tensor& logits, int64_t K, bool normali
   c10::cuda::CUDAGuard guard(logits.device());
   auto f32 = logits.options();
   Tensor w = torch::empty({T, K}, f32), idx = torch::empty({T, K}, f32.dtype(torch::kInt32));
-  Tensor lse = torch::empty({T}, f32), sums = torch::zeros({E + 2}, f32);
+  // sums: [E] probability mass, sum lse^2, sum entropy, [E] routes per expert; balance: 5 load-balance figures + [E] load fractions
+  Tensor lse = torch::empty({T}, f32), sums = torch::zeros({2 * E + 2}, f32), balance = torch::empty({5 + E}, f32);
   check_launch(mts::launch_router_forward(logits.data_ptr<float>(), int(T), int(E), int(K), normalize, w.data_ptr<float>(),
-                                          idx.data_ptr<int>(), lse.data_ptr<float>(), sums.data_ptr<float>(), cur_stream()), "router_forward");
-  return {w, idx, lse, sums};
+                                          idx.data_ptr<int>(), lse.data_ptr<float>(), sums.data_ptr<float>(),
+                                          balance.data_ptr<float>(), cur_stream()), "router_forward");
+  return {w, idx, lse, sums, balance};
 }
 
 Tensor router_backward(const Tensor& logits, const Tensor& lse, const Tensor& idx, const Tensor& w,

@@ -42,7 +42,7 @@ cudaError_t launch_count_valid_targets(const long long* targets, long long n, fl
 // Softmax over E experts, top-k (k <= 8) with optional renormalisation, and the batch statistics.
 // sums[0..E) += per-expert probability sums, sums[E] += sum(lse^2), sums[E+1] += sum(entropy).
 cudaError_t launch_router_forward(const float* logits, int T, int E, int K, bool normalize, float* weights, int* indices,
-                                  float* row_lse, float* sums, cudaStream_t stream);
+                                  float* row_lse, float* sums, float* balance, cudaStream_t stream);
 cudaError_t launch_router_backward(const float* logits, const float* row_lse, const int* indices, const float* weights,
                                    const float* g_weights, const float* g_mean_prob, const float* g_zloss, int T, int E,
                                    int K, bool normalize, float* g_logits, cudaStream_t stream);

@@ -28,8 +28,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 __global__ void __launch_bounds__(256)
 router_forward_kernel(const float* __restrict__ logits, int T, int E, int K, int normalize, float* __restrict__ weights,
                       int* __restrict__ indices, float* __restrict__ row_lse, float* __restrict__ sums) {
-  extern __shared__ float block_sums[];   // [E + 2]
-  for (int i = threadIdx.x; i < E + 2; i += blockDim.x) block_sums[i] = 0.f;
+  // sums: [0, E) probability mass per expert, [E] sum of lse^2, [E + 1] sum of entropies, [E + 2, 2E + 2) routes per expert
+  extern __shared__ float block_sums[];   // [2E + 2]
+  for (int i = threadIdx.x; i < 2 * E + 2; i += blockDim.x) block_sums[i] = 0.f;
   __syncthreads();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   float p[kMaxExperts];
@@ -68,6 +69,7 @@ router_forward_kernel(const float* __restrict__ logits, int T, int E, int K, int
     for (int k = 0; k < K; ++k) {
       weights[(long long)t * K + k] = chosen_w[k] * inv;
       indices[(long long)t * K + k] = chosen_i[k];
+      atomicAdd(&block_sums[E + 2 + chosen_i[k]], 1.f);
     }
   }
   // CTA-level reduction of the statistics, then one atomic per value per CTA
@@ -82,7 +84,41 @@ router_forward_kernel(const float* __restrict__ logits, int T, int E, int K, int
     atomicAdd(&block_sums[E + 1], h);
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < E + 2; i += blockDim.x) atomicAdd(sums + i, block_sums[i]);
+  for (int i = threadIdx.x; i < 2 * E + 2; i += blockDim.x) atomicAdd(sums + i, block_sums[i]);
+}
+
+// Load-balance figures of one routing decision from the per-expert route counts, one warp:
+// out = [max count, min count, coefficient of variation of the load, max load / mean load, experts without a route,
+//        load fraction of every expert ...].  (The framework-op form of the same numbers is a dozen launches and, through
+// the histogram's size query, a host synchronisation per layer.)
+__global__ void router_balance_kernel(const float* __restrict__ counts, int E, float n_routes, float* __restrict__ out) {
+  const int lane = threadIdx.x;
+  float mx = -CUDART_INF_F, mn = CUDART_INF_F, sum = 0.f, sq = 0.f, dead = 0.f;
+  const float inv_routes = 1.f / fmaxf(n_routes, 1.f);
+  for (int e = lane; e < E; e += 32) {
+    const float c = counts[e];
+    const float load = c * inv_routes;
+    mx = fmaxf(mx, c); mn = fminf(mn, c);
+    sum += load; sq += load * load;
+    dead += c == 0.f ? 1.f : 0.f;
+    out[5 + e] = load;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    dead += __shfl_xor_sync(0xffffffffu, dead, o);
+  }
+  if (lane == 0) {
+    const float mean = sum / float(E);
+    const float var = fmaxf(sq / float(E) - mean * mean, 0.f);
+    out[0] = mx; out[1] = mn;
+    out[2] = sqrtf(var) * float(E);            // std / (1 / E)
+    out[3] = mx * inv_routes * float(E);       // max load / (1 / E)
+    out[4] = dead;
+  }
 }
 
 // ---------------- router backward ----------------
@@ -332,11 +368,15 @@ int capped_grid(long long items, int per_block) {
 }  // namespace
 
 cudaError_t launch_router_forward(const float* logits, int T, int E, int K, bool normalize, float* weights, int* indices,
-                                  float* row_lse, float* sums, cudaStream_t stream) {
+                                  float* row_lse, float* sums, float* balance, cudaStream_t stream) {
   if (E > kMaxExperts || K > kMaxTopK || K > E || T <= 0) return cudaErrorInvalidValue;
-  router_forward_kernel<<<(T + 255) / 256, 256, sizeof(float) * (E + 2), stream>>>(logits, T, E, K, normalize ? 1 : 0,
-                                                                                   weights, indices, row_lse, sums);
+  router_forward_kernel<<<(T + 255) / 256, 256, sizeof(float) * (2 * E + 2), stream>>>(logits, T, E, K, normalize ? 1 : 0,
+                                                                                       weights, indices, row_lse, sums);
   ++g_launch_count;
+  if (balance != nullptr) {
+    router_balance_kernel<<<1, 32, 0, stream>>>(sums + E + 2, E, float(T) * float(K), balance);
+    ++g_launch_count;
+  }
   return cudaGetLastError();
 }
 

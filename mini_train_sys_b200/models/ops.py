@@ -26,6 +26,9 @@ class RouterPostprocessOutput:
     probability_per_expert: torch.Tensor  # [E] mean full-softmax probability, differentiable
     z_loss: torch.Tensor                  # scalar mean(lse^2), differentiable
     entropy: torch.Tensor                 # scalar, detached
+    # Optional, from backends whose routing kernel counts as it goes (no gradient):
+    expert_counts: torch.Tensor | None = None   # [E] fp32 routes per expert
+    balance_stats: torch.Tensor | None = None   # [5 + E] fp32: max count, min count, load cv, max / mean load, dead experts, load fractions
 
 
 @runtime_checkable

@@ -92,9 +92,14 @@ class TopKRouter(nn.Module):
             post = ops.router_postprocess(logits, cfg.experts_per_token, normalize=cfg.router_normalize_topk)
             weights, indices = post.expert_weights, post.expert_indices
             n_routes = indices.numel()
-            counts = torch.bincount(indices.reshape(-1).long(), minlength=n_exp).float()
+            # Routes per expert: from the routing kernel when it counts as it goes (torch.bincount asks the device for its
+            # output size, which stalls the launch queue once per layer), else a histogram.
+            counts = getattr(post, "expert_counts", None)
+            balance = getattr(post, "balance_stats", None)
+            if counts is None:
+                counts = torch.bincount(indices.reshape(-1).long(), minlength=n_exp).float()
             # Assignment fractions carry no gradient; the probability mean does.
-            aux = n_exp * torch.sum((counts / n_routes) * post.probability_per_expert)
+            aux = torch.dot(counts, post.probability_per_expert) * (n_exp / n_routes)
 
             dropped = weights.new_zeros(())
             if self.enforce_capacity and cfg.expert_capacity_factor is not None:
@@ -105,25 +110,35 @@ class TopKRouter(nn.Module):
                     weights = torch.where(denom > 0, weights / denom.clamp_min(torch.finfo(weights.dtype).eps), weights)
                 dropped = 1.0 - keep.float().mean()
                 counts = torch.bincount(indices[keep].long(), minlength=n_exp).float()
+                balance = None                       # the kernel's figures describe the routing before the capacity limit
                 if self.drop_overflow_routes:
                     indices = torch.where(keep, indices, torch.full_like(indices, -1))
 
-            load = counts / max(n_routes, 1)
-            uniform = 1.0 / n_exp
             log_e = math.log(n_exp) if n_exp > 1 else 1.0
             metrics = {
                 "moe/router_entropy": post.entropy,
                 "moe/router_entropy_normalized": (post.entropy / log_e).detach(),
                 "moe/dropped_route_fraction": dropped.detach(),
-                "moe/max_expert_load": counts.max().detach(),
-                "moe/min_expert_load": counts.min().detach(),
-                "moe/expert_load_cv": (load.std(unbiased=False) / uniform).detach(),
-                "moe/max_to_mean_load": (load.max() / uniform).detach(),
-                "moe/dead_expert_count": (counts == 0).sum().detach(),
-                # per-expert vectors: stacked over layers into [layer, expert] heatmaps by the logger
-                "moe/expert_load_fraction": load.detach(),
-                "moe/expert_probability": post.probability_per_expert.detach(),
             }
+            if balance is not None:                  # slices of one small tensor: no launches
+                metrics.update({
+                    "moe/max_expert_load": balance[0], "moe/min_expert_load": balance[1], "moe/expert_load_cv": balance[2],
+                    "moe/max_to_mean_load": balance[3], "moe/dead_expert_count": balance[4],
+                    "moe/expert_load_fraction": balance[5:],
+                })
+            else:
+                load = counts / max(n_routes, 1)
+                uniform = 1.0 / n_exp
+                metrics.update({
+                    "moe/max_expert_load": counts.max().detach(),
+                    "moe/min_expert_load": counts.min().detach(),
+                    "moe/expert_load_cv": (load.std(unbiased=False) / uniform).detach(),
+                    "moe/max_to_mean_load": (load.max() / uniform).detach(),
+                    "moe/dead_expert_count": (counts == 0).sum().detach(),
+                    "moe/expert_load_fraction": load.detach(),
+                })
+            # per-expert vectors are stacked over layers into [layer, expert] heatmaps by the logger
+            metrics["moe/expert_probability"] = post.probability_per_expert.detach()
         return RouterOutput(
             expert_indices=indices.to(torch.int32),
             expert_weights=weights.to(hidden_states.dtype),

@@ -450,16 +450,17 @@ class _RouterFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, top_k, normalize):
         lg = logits.contiguous()
-        w, idx, lse, sums = ext().router_forward(lg, top_k, normalize)
+        w, idx, lse, sums, balance = ext().router_forward(lg, top_k, normalize)
         tokens, experts = lg.shape
         ctx.save_for_backward(lg, lse, idx, w)
         ctx.normalize = normalize
-        ctx.mark_non_differentiable(idx)
-        inv = 1.0 / tokens
-        return w, idx, sums[:experts] * inv, sums[experts] * inv, sums[experts + 1] * inv
+        counts = sums[experts + 2:]
+        ctx.mark_non_differentiable(idx, counts, balance)
+        scaled = sums[:experts + 2] * (1.0 / tokens)          # mean probability per expert, mean lse^2, mean entropy
+        return w, idx, scaled[:experts], scaled[experts], scaled[experts + 1], counts, balance
 
     @staticmethod
-    def backward(ctx, g_w, _g_idx, g_mp, g_z, _g_ent):
+    def backward(ctx, g_w, _g_idx, g_mp, g_z, _g_ent, _g_counts, _g_balance):
         lg, lse, idx, w = ctx.saved_tensors
         opt = lambda t: None if t is None else t.float().contiguous()  # noqa: E731
         gz = None if g_z is None else g_z.float().reshape(1).contiguous()
@@ -647,8 +648,8 @@ class NativeOpsBackend(TorchOpsBackend):
         check_router_args(logits, top_k)
         ok = logits.is_cuda and logits.shape[1] <= 64 and top_k <= 8
         if self._count("router_postprocess", ok):
-            w, idx, mean_prob, z, ent = _RouterFn.apply(logits, top_k, normalize)
-            return RouterPostprocessOutput(w, idx, mean_prob, z, ent.detach())
+            w, idx, mean_prob, z, ent, counts, balance = _RouterFn.apply(logits, top_k, normalize)
+            return RouterPostprocessOutput(w, idx, mean_prob, z, ent.detach(), expert_counts=counts, balance_stats=balance)
         return super().router_postprocess(logits, top_k, normalize=normalize)
 
     def fused_moe(self, x, gate_up_proj, down_proj, top_k_index, top_k_weights):

@@ -147,6 +147,14 @@ def test_router(ops, tokens, experts, k, normalize):
     assert_close(out.probability_per_expert, want.probability_per_expert, 1e-5, "mean prob")
     assert abs(float(out.z_loss) - float(want.z_loss)) < 1e-4 * max(1.0, float(want.z_loss))
     assert abs(float(out.entropy) - float(want.entropy)) < 1e-4
+    # route counts and load-balance figures come from the routing kernels themselves
+    counts = torch.bincount(out.expert_indices.reshape(-1).long(), minlength=experts).float()
+    assert torch.equal(out.expert_counts, counts)
+    load = counts / (tokens * k)
+    want_stats = torch.stack([counts.max(), counts.min(), load.std(unbiased=False) * experts, load.max() * experts,
+                              (counts == 0).sum().float()])
+    assert_close(out.balance_stats[:5], want_stats, 1e-5, "balance figures")
+    assert_close(out.balance_stats[5:], load, 1e-6, "load fractions")
     # combined gradient through all three differentiable outputs
     gw = torch.randn_like(out.expert_weights)
     gp = torch.randn(experts, device=DEV)
