@@ -26,13 +26,14 @@ class NsightKernel:
     name: str            # registry key, e.g. "gemm"
     regex: str           # kernel-name regex handed to ncu -k
     case: tuple[str, ...]  # arguments of the operator-bench worker that launches it on a small case
+    skip: int = 0        # matching launches to pass over before the capture (ncu -s)
 
 
 _REGISTRY: dict[str, NsightKernel] = {}
 
 
-def register_nsight_kernel(name: str, regex: str, case: Iterable[str]) -> None:
-    _REGISTRY[name] = NsightKernel(name, regex, tuple(case))
+def register_nsight_kernel(name: str, regex: str, case: Iterable[str], skip: int = 0) -> None:
+    _REGISTRY[name] = NsightKernel(name, regex, tuple(case), skip)
 
 
 def registered() -> dict[str, NsightKernel]:
@@ -46,6 +47,10 @@ def _case(kernel: str, tokens: int, profile: str = "project_formal") -> tuple[st
 
 # small cases: a few hundred MB on the device, inputs larger than L2 where the op is bandwidth bound
 register_nsight_kernel("gemm", "gemm_tcgen05_kernel", _case("linear", 24576))
+# the fused MoE operator launches its GEMMs in a fixed order: up projection with the SwiGLU epilogue, down projection,
+# then (backward) the down-projection dgrad with the SwiGLU-derivative epilogue
+register_nsight_kernel("gemm_swiglu", "gemm_tcgen05_kernel", _case("fused_moe", 24576))
+register_nsight_kernel("gemm_swiglu_bwd", "gemm_tcgen05_kernel", _case("fused_moe", 24576), skip=2)
 register_nsight_kernel("flash_fwd", "flash_fwd_kernel", _case("attention", 24576))
 register_nsight_kernel("flash_bwd_dkdv", "flash_bwd_dkdv_kernel", _case("attention", 24576))
 register_nsight_kernel("flash_bwd_dq", "flash_bwd_dq_kernel", _case("attention", 24576))
@@ -102,7 +107,7 @@ def command_for(name: str, script: str | Path, *, mode: str = "full", output: st
     k = _REGISTRY[name]
     target = [str(script), *k.case]
     plain = " ".join(shlex.quote(c) for c in ["python", *target])
-    cap = " ".join(shlex.quote(c) for c in build_command(target, mode=mode, kernel_regex=k.regex, output=output))
+    cap = " ".join(shlex.quote(c) for c in build_command(target, mode=mode, kernel_regex=k.regex, skip=k.skip, output=output))
     return f"{plain} > /dev/null && {cap}"
 
 
