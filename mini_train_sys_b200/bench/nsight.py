@@ -47,10 +47,11 @@ def _case(kernel: str, tokens: int, profile: str = "project_formal") -> tuple[st
 
 # small cases: a few hundred MB on the device, inputs larger than L2 where the op is bandwidth bound
 register_nsight_kernel("gemm", "gemm_tcgen05_kernel", _case("linear", 24576))
-# the fused MoE operator launches its GEMMs in a fixed order: up projection with the SwiGLU epilogue, down projection,
-# then (backward) the down-projection dgrad with the SwiGLU-derivative epilogue
+# the fused MoE worker launches its GEMMs in a fixed order: seven forward passes (up projection with the SwiGLU epilogue,
+# down projection) while it times the forward, then forward + backward, whose first GEMM is the down-projection dgrad
+# with the SwiGLU-derivative epilogue: launch 14 of the kernel
 register_nsight_kernel("gemm_swiglu", "gemm_tcgen05_kernel", _case("fused_moe", 24576))
-register_nsight_kernel("gemm_swiglu_bwd", "gemm_tcgen05_kernel", _case("fused_moe", 24576), skip=2)
+register_nsight_kernel("gemm_swiglu_bwd", "gemm_tcgen05_kernel", _case("fused_moe", 24576), skip=14)
 register_nsight_kernel("flash_fwd", "flash_fwd_kernel", _case("attention", 24576))
 register_nsight_kernel("flash_bwd_dkdv", "flash_bwd_dkdv_kernel", _case("attention", 24576))
 register_nsight_kernel("flash_bwd_dq", "flash_bwd_dq_kernel", _case("attention", 24576))
