@@ -117,6 +117,32 @@ __device__ __forceinline__ void store_row64(__nv_bfloat16* dst, const float (&v)
   }
 }
 
+// The same store for a gradient of rotated q / k rows: v is d(rotated row) at position `pos`; what is written is the gradient of
+// the row before the half-split rotation, lo' = lo cos + hi sin, hi' = hi cos - lo sin (fp32, one rounding).
+__device__ __forceinline__ void store_row64_unrotated(__nv_bfloat16* dst, const float (&v)[64], float mul,
+                                                      const __nv_bfloat16* cos_row, const __nv_bfloat16* sin_row) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 cq = reinterpret_cast<const uint4*>(cos_row)[j], sq = reinterpret_cast<const uint4*>(sin_row)[j];
+    const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w}, sw[4] = {sq.x, sq.y, sq.z, sq.w};
+    float lo[8], hi[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t cbits = (i & 1) ? (cw[i >> 1] & 0xFFFF0000u) : (cw[i >> 1] << 16);
+      const uint32_t sbits = (i & 1) ? (sw[i >> 1] & 0xFFFF0000u) : (sw[i >> 1] << 16);
+      const float c = __uint_as_float(cbits) * mul, sn = __uint_as_float(sbits) * mul;
+      const float a = v[8 * j + i], b = v[32 + 8 * j + i];
+      lo[i] = a * c + b * sn;
+      hi[i] = b * c - a * sn;
+    }
+    uint4 q;
+    q.x = pack2(lo[0], lo[1]); q.y = pack2(lo[2], lo[3]); q.z = pack2(lo[4], lo[5]); q.w = pack2(lo[6], lo[7]);
+    reinterpret_cast<uint4*>(dst)[j] = q;
+    q.x = pack2(hi[0], hi[1]); q.y = pack2(hi[2], hi[3]); q.z = pack2(hi[4], hi[5]); q.w = pack2(hi[6], hi[7]);
+    reinterpret_cast<uint4*>(dst)[4 + j] = q;
+  }
+}
+
 // Optional phase trace of CTA (0, 0) of the forward kernel (build with -DMTS_ATTN_TRACE): slot 8*j+k of
 // g_attn_trace receives clock64() when the softmax warp (k = 0..5) or the MMA thread (slot 4096 + 8*j + k)
 // passes phase k of key tile j.  Compiled out by default.
@@ -136,6 +162,7 @@ struct Params {
   float scale, dropout_p;
   unsigned long long seed;
   int* status;
+  const __nv_bfloat16 *rope_cos, *rope_sin;   // backward: un-rotate dQ / dK while storing them (nullptr = store as is)
 };
 
 // =====================================================================================================
@@ -637,7 +664,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
       }
-      if (key < p.S) store_row64(p.dk + (long long)b * p.dk_sb + (long long)h * p.dk_sh + (long long)key * p.dk_ss, acc, p.scale);
+      if (key < p.S) {
+        __nv_bfloat16* dst = p.dk + (long long)b * p.dk_sb + (long long)h * p.dk_sh + (long long)key * p.dk_ss;
+        if (p.rope_cos != nullptr) store_row64_unrotated(dst, acc, p.scale, p.rope_cos + (long long)key * 64, p.rope_sin + (long long)key * 64);
+        else store_row64(dst, acc, p.scale);
+      }
     }
   }
 
@@ -829,7 +860,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
       }
-      if (q_row < p.S) store_row64(p.dq + (long long)b * p.dq_sb + (long long)h * p.dq_sh + (long long)q_row * p.dq_ss, acc, p.scale);
+      if (q_row < p.S) {
+        __nv_bfloat16* dst = p.dq + (long long)b * p.dq_sb + (long long)h * p.dq_sh + (long long)q_row * p.dq_ss;
+        if (p.rope_cos != nullptr) store_row64_unrotated(dst, acc, p.scale, p.rope_cos + (long long)q_row * 64, p.rope_sin + (long long)q_row * 64);
+        else store_row64(dst, acc, p.scale);
+      }
     }
   }
 
@@ -940,6 +975,8 @@ Params make_params(const AttentionArgs& a) {
   p.lse = a.lse; p.delta = a.delta;
   p.B = a.B; p.H = a.H; p.S = a.S; p.causal = a.causal;
   p.scale = a.scale; p.dropout_p = a.dropout_p; p.seed = a.seed; p.status = a.status;
+  p.rope_cos = static_cast<const __nv_bfloat16*>(a.rope_cos);
+  p.rope_sin = static_cast<const __nv_bfloat16*>(a.rope_sin);
   return p;
 }
 

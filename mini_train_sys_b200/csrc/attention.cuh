@@ -30,6 +30,10 @@ struct AttentionArgs {
   unsigned long long seed;
   int* status;
   cudaStream_t stream;
+  // Backward only, optional: bf16 RoPE tables [>= S, 64] (two identical halves).  When set, dQ and dK are rotated back
+  // (the gradient of the half-split rotation applied to q and k before the forward) in the epilogues that write them.
+  const void* rope_cos = nullptr;
+  const void* rope_sin = nullptr;
 };
 
 constexpr int kAttnHeadDim = 64;

@@ -61,9 +61,19 @@ std::vector<Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v,
 std::vector<Tensor> flash_bwd(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
                               const Tensor& lse, bool causal, double dropout_p, int64_t seed, const Tensor& status,
                               const c10::optional<Tensor>& dq_out, const c10::optional<Tensor>& dk_out,
-                              const c10::optional<Tensor>& dv_out) {
+                              const c10::optional<Tensor>& dv_out, const c10::optional<Tensor>& rope_cos,
+                              const c10::optional<Tensor>& rope_sin) {
   c10::cuda::CUDAGuard guard(q.device());
   mts::AttentionArgs a = base_args(q, k, v, causal, dropout_p, seed);
+  if (rope_cos.has_value() && rope_cos->defined()) {
+    // q and k were rotated before the forward: dQ / dK come back un-rotated from the kernels that produce them
+    TORCH_CHECK(rope_sin.has_value() && rope_sin->defined(), "rope_cos needs rope_sin");
+    for (const Tensor* t : {&*rope_cos, &*rope_sin})
+      TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kBFloat16 && t->dim() == 2 && t->is_contiguous() &&
+                  t->size(0) >= q.size(2) && t->size(1) == 64, "rope tables must be contiguous bf16 [>= S, 64]");
+    a.rope_cos = rope_cos->data_ptr();
+    a.rope_sin = rope_sin->data_ptr();
+  }
   check_qkv(o, "o", q.size(0), q.size(1), q.size(2));
   check_qkv(d_o, "d_o", q.size(0), q.size(1), q.size(2));
   TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == q.size(0) * q.size(1) * q.size(2),
@@ -99,6 +109,10 @@ Tensor dropout_keep_mask(int64_t BH, int64_t S, double dropout_p, int64_t seed, 
 
 void bind_attention(pybind11::module_& m) {
   m.def("flash_fwd", &flash_fwd);
-  m.def("flash_bwd", &flash_bwd);
+  m.def("flash_bwd", &flash_bwd, pybind11::arg("d_o"), pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("o"),
+        pybind11::arg("lse"), pybind11::arg("causal"), pybind11::arg("dropout_p"), pybind11::arg("seed"), pybind11::arg("status"),
+        pybind11::arg("dq_out") = pybind11::none(), pybind11::arg("dk_out") = pybind11::none(),
+        pybind11::arg("dv_out") = pybind11::none(), pybind11::arg("rope_cos") = pybind11::none(),
+        pybind11::arg("rope_sin") = pybind11::none());
   m.def("dropout_keep_mask", &dropout_keep_mask);
 }

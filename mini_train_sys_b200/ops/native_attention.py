@@ -83,9 +83,9 @@ class _QKVAttentionFn(torch.autograd.Function):
     """RoPE + causal attention on a fused ``[B, S, 3, H, D]`` projection, in one autograd node.
 
     Forward rotates the q / k views into contiguous buffers and runs the attention kernel on them and on the
-    strided v view.  Backward lets the attention kernel write dV straight into slot 2 of one fused gradient
-    buffer and un-rotates dQ / dK into slots 0 and 1, so the three view gradients never exist as separate
-    zero-filled tensors that autograd would have to add up.
+    strided v view.  Backward lets the attention kernels write dV straight into slot 2 of one fused gradient
+    buffer and dQ / dK, rotated back in the epilogues that produce them, into slots 0 and 1, so the three view
+    gradients never exist as separate zero-filled tensors that autograd would have to add up.
     """
 
     @staticmethod
@@ -115,9 +115,8 @@ class _QKVAttentionFn(torch.autograd.Function):
         dq_slot, dk_slot, dv_slot = (d_fused[:, :, j].transpose(1, 2) for j in range(3))
         v = fused[:, :, 2].transpose(1, 2)
         status = e.status_tensor(fused.device.index or 0)
-        dq, dk, _ = e.flash_bwd(d_o, qr, kr, v, o, lse, is_causal, dropout_p, seed, status, None, None, dv_slot)
-        e.rope(dq, cos, sin, True, dq_slot)
-        e.rope(dk, cos, sin, True, dk_slot)
+        # the kernels that produce dQ and dK rotate them back while storing, straight into slots 0 and 1
+        e.flash_bwd(d_o, qr, kr, v, o, lse, is_causal, dropout_p, seed, status, dq_slot, dk_slot, dv_slot, cos, sin)
         return d_fused, None, None, None, None, None
 
 
@@ -128,6 +127,8 @@ def qkv_supported(fused: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, dro
     if d != HEAD_DIM or not fused.is_contiguous() or b * h == 0 or s == 0 or b * h > 65535 or s > 65535:
         return False
     if cos.dtype != fused.dtype or not (cos.is_contiguous() and sin.is_contiguous()) or cos.shape[0] < s:
+        return False
+    if cos.dim() != 2 or cos.shape[1] != HEAD_DIM or sin.shape != cos.shape:
         return False
     return 0.0 <= float(dropout_p) < 1.0
 
