@@ -412,6 +412,15 @@ class _RouterLogitsFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight):
         n_exp, hidden = weight.shape
+        if weight.dtype == torch.bfloat16:
+            # a bf16 replica of the parameter (sharded engines): it is its own high part and the low part is zero
+            w_hi = weight.detach()
+            w_hi = w_hi if w_hi.is_contiguous() else w_hi.contiguous()
+            width = -(-n_exp // 4) * 4
+            out = torch.empty(x.shape[0], width, dtype=torch.float32, device=x.device)
+            _gemm(x, w_hi, out, x.shape[0], n_exp, hidden, ldo=width)
+            ctx.save_for_backward(x, weight, w_hi)
+            return out if width == n_exp else out[:, :n_exp].contiguous()
         w_hi, w_lo = _split_bf16(weight.detach().float())
         stacked = torch.zeros(2 * n_exp, hidden, dtype=torch.bfloat16, device=x.device)
         stacked[:n_exp], stacked[n_exp:] = w_hi, w_lo
