@@ -185,20 +185,29 @@ plan_count_kernel(const int* __restrict__ indices, int n_routes, int E, int* __r
 constexpr int kSegmentPad = 256;
 
 // Pass 2 (one CTA): exclusive scan over CTAs for every expert, padded expert offsets, tile -> expert map.
-__global__ void __launch_bounds__(kMaxExperts)
+constexpr int kScanThreads = 1024;
+__global__ void __launch_bounds__(kScanThreads)
 plan_scan_kernel(int* __restrict__ block_counts, int n_blocks, int E, int capacity_rows, int* __restrict__ group_rows,
                  int* __restrict__ tile_group, int* __restrict__ meta) {
   __shared__ int totals[kMaxExperts];
   __shared__ int starts[kMaxExperts + 1];
-  const int e = threadIdx.x;
-  if (e < E) {
+  // one warp per expert, 32 CTAs' counts per step: a shuffle scan instead of a chain of n_blocks dependent loads
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += n_warps) {
     int run = 0;
-    for (int b = 0; b < n_blocks; ++b) {
-      const int c = block_counts[b * E + e];
-      block_counts[b * E + e] = run;     // becomes the CTA's offset inside the expert
-      run += c;
+    for (int base = 0; base < n_blocks; base += 32) {
+      const int b = base + lane;
+      const int c = b < n_blocks ? block_counts[b * E + e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (b < n_blocks) block_counts[b * E + e] = run + incl - c;     // becomes the CTA's offset inside the expert
+      run += __shfl_sync(0xffffffffu, incl, 31);
     }
-    totals[e] = run;
+    if (lane == 0) totals[e] = run;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -402,7 +411,7 @@ cudaError_t launch_moe_plan(const int* indices, int T, int K, int E, int capacit
   const int blocks = (routes + kPlanBlock - 1) / kPlanBlock;
   fill_int_kernel<<<capped_grid(capacity_rows, 256), 256, 0, stream>>>(row_token, -1, capacity_rows);
   plan_count_kernel<<<blocks, kPlanBlock, 0, stream>>>(indices, routes, E, workspace);
-  plan_scan_kernel<<<1, kMaxExperts, 0, stream>>>(workspace, blocks, E, capacity_rows, group_rows, tile_group, meta);
+  plan_scan_kernel<<<1, kScanThreads, 0, stream>>>(workspace, blocks, E, capacity_rows, group_rows, tile_group, meta);
   plan_place_kernel<<<blocks, kPlanBlock, 0, stream>>>(indices, routes, K, E, workspace, group_rows, capacity_rows,
                                                       row_token, token_rows);
   g_launch_count += 4;
