@@ -58,8 +58,9 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
 }
 
 // dres (optional): gradient of the residual branch with the shape of x; the result is dx + dres.
+// dw_out (optional): fp32 [H] destination of the weight gradient (a slot of a flat gradient buffer); it is overwritten.
 std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, bool need_dw,
-                                const c10::optional<Tensor>& dres) {
+                                const c10::optional<Tensor>& dres, const c10::optional<Tensor>& dw_out) {
   check_act(x, "x");
   const bool fuse_res = dres.has_value() && dres->defined() && is_bf16(x);
   if (dres.has_value() && dres->defined())
@@ -71,7 +72,15 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
   const int64_t rows = x.numel() / H;
   c10::cuda::CUDAGuard guard(x.device());
   Tensor dx = torch::empty_like(x);
-  Tensor dw = need_dw ? torch::zeros({H}, x.options().dtype(torch::kFloat)) : Tensor();
+  Tensor dw;
+  if (need_dw && dw_out.has_value() && dw_out->defined()) {
+    TORCH_CHECK(dw_out->is_cuda() && dw_out->scalar_type() == at::kFloat && dw_out->is_contiguous() && dw_out->numel() == H,
+                "dw_out must be a contiguous fp32 CUDA tensor of H elements");
+    dw = *dw_out;
+    dw.zero_();
+  } else if (need_dw) {
+    dw = torch::zeros({H}, x.options().dtype(torch::kFloat));
+  }
   check_launch(mts::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr<float>(), rstd.data_ptr<float>(),
                                        fuse_res ? dres->data_ptr() : nullptr, dx.data_ptr(),
                                        need_dw ? dw.data_ptr<float>() : nullptr, rows, int(H), is_bf16(x), cur_stream()),
@@ -392,7 +401,7 @@ void bind_comm(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("need_dw"),
-        py::arg("dres") = py::none());
+        py::arg("dres") = py::none(), py::arg("dw_out") = py::none());
   m.def("rope", &rope);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);

@@ -219,16 +219,26 @@ class _RMSNormFn(torch.autograd.Function):
         xc = x if x.is_contiguous() else x.contiguous()
         w32 = weight if weight.dtype == torch.float32 else weight.float()
         y, rstd = ext().rmsnorm_fwd(xc, w32.contiguous(), eps)
-        ctx.save_for_backward(xc, w32, rstd)
-        ctx.w_dtype = weight.dtype
+        ctx.save_for_backward(xc, w32, rstd, weight)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w32, rstd = ctx.saved_tensors
+        x, w32, rstd, weight = ctx.saved_tensors
         dyc = dy if dy.is_contiguous() else dy.contiguous()
-        dx, dw = ext().rmsnorm_bwd(dyc, x, w32, rstd, ctx.needs_input_grad[1])
-        return dx, (dw.to(ctx.w_dtype) if dw is not None and dw.numel() else None), None
+        return (*_rmsnorm_backward(dyc, x, w32, rstd, weight, ctx.needs_input_grad[1], None), None)
+
+
+def _rmsnorm_backward(dy, x, w32, rstd, weight, need_dw, dres):
+    """``(dx, dw)``; the weight gradient goes straight into the engine's flat fp32 buffer when the parameter has a sink."""
+
+    sink = grad_sink(weight) if need_dw else None
+    if sink is not None and sink[0].is_contiguous():
+        dx, _ = ext().rmsnorm_bwd(dy, x, w32, rstd, True, dres, sink[0])
+        sink[1](weight)
+        return dx, None
+    dx, dw = ext().rmsnorm_bwd(dy, x, w32, rstd, need_dw, dres)
+    return dx, (dw.to(weight.dtype) if dw is not None and dw.numel() else None)
 
 
 class _RMSNormResidualFn(torch.autograd.Function):
@@ -241,20 +251,18 @@ class _RMSNormResidualFn(torch.autograd.Function):
         xc = x if x.is_contiguous() else x.contiguous()
         w32 = weight if weight.dtype == torch.float32 else weight.float()
         y, rstd = ext().rmsnorm_fwd(xc, w32.contiguous(), eps)
-        ctx.save_for_backward(xc, w32, rstd)
-        ctx.w_dtype = weight.dtype
+        ctx.save_for_backward(xc, w32, rstd, weight)
         return y, xc          # an input returned as an output: autograd gives it a node of its own
 
     @staticmethod
     def backward(ctx, dy, dres):
-        x, w32, rstd = ctx.saved_tensors
+        x, w32, rstd, weight = ctx.saved_tensors
         if dy is None:
             return dres, None, None
         dyc = dy if dy.is_contiguous() else dy.contiguous()
         if dres is not None and not dres.is_contiguous():
             dres = dres.contiguous()
-        dx, dw = ext().rmsnorm_bwd(dyc, x, w32, rstd, ctx.needs_input_grad[1], dres)
-        return dx, (dw.to(ctx.w_dtype) if dw is not None and dw.numel() else None), None
+        return (*_rmsnorm_backward(dyc, x, w32, rstd, weight, ctx.needs_input_grad[1], dres), None)
 
 
 class _RopeFn(torch.autograd.Function):

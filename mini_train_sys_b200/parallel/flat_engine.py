@@ -211,8 +211,10 @@ class FlatDataParallel(nn.Module):
         knows the protocol (linear layers and expert stacks inside the blocks; never tied or embedding weights)."""
 
         name = slot.name
-        if not (self.coll.fused and slot.param.dim() >= 2 and ".blocks." in f".{name}"):
+        if not (self.coll.fused and ".blocks." in f".{name}"):
             return False
+        if slot.param.dim() == 1:      # the two norm weights of a block: RMSNorm backward accumulates dw in fp32 anyway
+            return name.endswith(("attn_norm.weight", "ffn_norm.weight"))
         return name.endswith(("qkv.weight", "out.weight", "gate.weight", "up.weight", "down.weight", "gate_up_proj", "down_proj"))
 
     def _on_sunk_grad(self, param: nn.Parameter) -> None:
