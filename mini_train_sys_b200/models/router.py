@@ -42,6 +42,15 @@ def expert_capacity(cfg: ModelConfig, tokens: int) -> int | None:
     return max(cfg.expert_min_capacity, math.ceil(cfg.expert_capacity_factor * even))
 
 
+def route_histogram(indices: torch.Tensor, bins: int, weights: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 counts (or weight sums) per bin without a device-to-host round trip: ``torch.bincount`` reads the maximum index
+    back to size its output, which stalls the launch queue; ``scatter_add_`` into a tensor of known size does not."""
+
+    flat = indices.reshape(-1).long()
+    src = torch.ones_like(flat, dtype=torch.float32) if weights is None else weights.reshape(-1).float()
+    return torch.zeros(bins, dtype=torch.float32, device=flat.device).scatter_add_(0, flat, src)
+
+
 def capacity_keep_mask(expert_indices: torch.Tensor, expert_weights: torch.Tensor, num_experts: int,
                        capacity: int | None) -> torch.Tensor:
     """Boolean ``[T, K]`` mask of routes that fit within ``capacity`` rows per expert.
@@ -57,7 +66,7 @@ def capacity_keep_mask(expert_indices: torch.Tensor, expert_weights: torch.Tenso
     # One composite key sorts by expert first, then by descending weight.
     order = torch.argsort(flat_w, descending=True, stable=True)
     order = order[torch.argsort(flat_e[order], stable=True)]
-    counts = torch.bincount(flat_e, minlength=num_experts)
+    counts = route_histogram(flat_e, num_experts).long()
     starts = torch.cumsum(counts, 0) - counts
     rank = torch.arange(order.numel(), device=order.device) - starts[flat_e[order]]
     keep = torch.empty_like(flat_e, dtype=torch.bool)
@@ -92,12 +101,12 @@ class TopKRouter(nn.Module):
             post = ops.router_postprocess(logits, cfg.experts_per_token, normalize=cfg.router_normalize_topk)
             weights, indices = post.expert_weights, post.expert_indices
             n_routes = indices.numel()
-            # Routes per expert: from the routing kernel when it counts as it goes (torch.bincount asks the device for its
-            # output size, which stalls the launch queue once per layer), else a histogram.
+            # Routes per expert: from the routing kernel when it counts as it goes, else a histogram that needs no
+            # device-to-host round trip.
             counts = getattr(post, "expert_counts", None)
             balance = getattr(post, "balance_stats", None)
             if counts is None:
-                counts = torch.bincount(indices.reshape(-1).long(), minlength=n_exp).float()
+                counts = route_histogram(indices, n_exp)
             # Assignment fractions carry no gradient; the probability mean does.
             aux = torch.dot(counts, post.probability_per_expert) * (n_exp / n_routes)
 
@@ -109,7 +118,7 @@ class TopKRouter(nn.Module):
                     denom = weights.sum(-1, keepdim=True)
                     weights = torch.where(denom > 0, weights / denom.clamp_min(torch.finfo(weights.dtype).eps), weights)
                 dropped = 1.0 - keep.float().mean()
-                counts = torch.bincount(indices[keep].long(), minlength=n_exp).float()
+                counts = route_histogram(indices, n_exp, keep)
                 balance = None                       # the kernel's figures describe the routing before the capacity limit
                 if self.drop_overflow_routes:
                     indices = torch.where(keep, indices, torch.full_like(indices, -1))

@@ -182,7 +182,7 @@ def _route_layout(expert_indices: torch.Tensor, n_local: int, world: int, cap: i
     kept = flat >= 0
     dest = torch.where(kept, flat // n_local, torch.full_like(flat, world))
     order = torch.argsort(dest, stable=True)
-    counts = torch.bincount(dest, minlength=world + 1)[:world]
+    counts = torch.zeros(world + 1, dtype=torch.long, device=flat.device).scatter_add_(0, dest, torch.ones_like(dest))[:world]
     starts = torch.cumsum(counts, 0) - counts
     ds = dest[order]
     slot_sorted = torch.arange(flat.numel(), device=flat.device) - torch.cat([starts, starts.new_zeros(1)])[ds]
