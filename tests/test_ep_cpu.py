@@ -117,3 +117,12 @@ def test_route_layout_slots_are_dense_per_destination_and_overflow_is_dropped():
     dest2, slot2, _, counts2, over2 = _route_layout(idx, n_local, world, cap=5)
     assert int(over2) == int((counts - 5).clamp(min=0).sum()) and int(slot2.max()) <= 4 and (counts2 <= 5).all()
     assert int((dest2 >= 0).sum()) == int(counts2.sum())
+
+
+def test_route_histogram_matches_bincount_with_and_without_weights():
+    from mini_train_sys_b200.models.router import route_histogram
+
+    idx = torch.randint(0, 7, (40, 3))
+    assert torch.equal(route_histogram(idx, 9), torch.bincount(idx.reshape(-1), minlength=9).float())
+    keep = torch.rand(40, 3) > 0.3
+    assert torch.equal(route_histogram(idx, 9, keep), torch.bincount(idx[keep], minlength=9).float())
