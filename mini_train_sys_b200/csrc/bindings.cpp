@@ -41,6 +41,48 @@ Tensor& status_word(int device) {
   return words[device];
 }
 
+// ---------------- router projection (skinny GEMM) ----------------
+void check_router_operands(const Tensor& x, const Tensor& w) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(), "x must be contiguous bf16 [T, H]");
+  TORCH_CHECK(w.is_cuda() && w.dim() == 2 && w.is_contiguous() && w.size(1) == x.size(1) &&
+                  (w.scalar_type() == at::kFloat || w.scalar_type() == at::kBFloat16), "w must be contiguous fp32 or bf16 [E, H]");
+  TORCH_CHECK(mts::router_logits_supported(int(w.size(0)), int(w.size(1))), "router projection: E must be 4, 8 or 16 and H a multiple of 8");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(w.data_ptr()) & 15) == 0,
+              "router projection operands must be 16-byte aligned");
+}
+
+bool router_logits_ok(int64_t experts, int64_t hidden) { return mts::router_logits_supported(int(experts), int(hidden)); }
+
+Tensor router_logits_fwd(const Tensor& x, const Tensor& w) {
+  check_router_operands(x, w);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({x.size(0), w.size(0)}, x.options().dtype(torch::kFloat));
+  check_launch(mts::launch_router_logits_fwd(x.data_ptr(), w.data_ptr(), is_bf16(w), out.data_ptr<float>(), int(x.size(0)),
+                                             int(w.size(0)), int(w.size(1)), cur_stream()), "router_logits_fwd");
+  return out;
+}
+
+// g: fp32 [T, E] gradient of the logits.  Returns (dx bf16 [T, H] or undefined, dw fp32 [E, H] or undefined).
+std::vector<Tensor> router_logits_bwd(const Tensor& g, const Tensor& x, const Tensor& w, bool need_dx, bool need_dw) {
+  check_router_operands(x, w);
+  TORCH_CHECK(g.is_cuda() && g.scalar_type() == at::kFloat && g.is_contiguous() && g.dim() == 2 && g.size(0) == x.size(0) &&
+                  g.size(1) == w.size(0), "g must be contiguous fp32 [T, E]");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx, dw;
+  const int T = int(x.size(0)), E = int(w.size(0)), H = int(w.size(1));
+  if (need_dx) {
+    dx = torch::empty_like(x);
+    check_launch(mts::launch_router_logits_dx(g.data_ptr<float>(), w.data_ptr(), is_bf16(w), dx.data_ptr(), T, E, H, cur_stream()),
+                 "router_logits_dx");
+  }
+  if (need_dw) {
+    dw = torch::zeros({w.size(0), w.size(1)}, x.options().dtype(torch::kFloat));
+    check_launch(mts::launch_router_logits_dw(g.data_ptr<float>(), x.data_ptr(), dw.data_ptr<float>(), T, E, H, cur_stream()),
+                 "router_logits_dw");
+  }
+  return {dx, dw};
+}
+
 // ---------------- memory-bound ops ----------------
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
   check_act(x, "x");
@@ -173,7 +215,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t M, int64_t N, in
           int64_t epilogue, bool accumulate, bool atomic_out, const c10::optional<Tensor>& aux,
           const c10::optional<Tensor>& tile_group, const c10::optional<Tensor>& num_row_tiles,
           const c10::optional<Tensor>& group_rows, int64_t num_groups, int64_t b_group_stride_rows, int64_t out_group_stride,
-          int64_t ldo, int64_t sm_limit, bool pair) {
+          int64_t ldo, int64_t sm_limit, bool pair, int64_t k_splits) {
   check_rowmajor_2d(a, "a");
   check_rowmajor_2d(b, "b");
   TORCH_CHECK(is_bf16(a) && is_bf16(b), "GEMM operands must be bf16");
@@ -212,11 +254,14 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t M, int64_t N, in
     TORCH_CHECK(g.group_rows && group_rows->numel() >= num_groups + 1, "grouped-K needs group_rows[groups + 1]");
     TORCH_CHECK(a_mn && b_mn, "grouped-K expects MN-major operands");
   }
+  TORCH_CHECK(k_splits >= 1 && k_splits <= 64, "k_splits out of range");
+  TORCH_CHECK(k_splits == 1 || (mode == mts::GEMM_GROUPED_K && atomic_out), "k_splits needs grouped-K with atomic_out");
+  g.k_splits = int(k_splits);
   g.num_groups = int(num_groups); g.b_group_stride_rows = b_group_stride_rows; g.out_group_stride = out_group_stride;
   // extents that the epilogue may touch must lie inside `out`
   const int64_t out_rows = (mode == mts::GEMM_GROUPED_K) ? M : M;
   const int64_t out_cols = epilogue == mts::EPI_SWIGLU ? N / 2 : (epilogue == mts::EPI_SWIGLU_BWD ? 2 * N : N);
-  const int64_t groups_out = (mode == mts::GEMM_GROUPED_K && !atomic_out && out_group_stride > 0) ? num_groups : 1;
+  const int64_t groups_out = (mode == mts::GEMM_GROUPED_K && out_group_stride > 0) ? num_groups : 1;
   TORCH_CHECK(ldo >= out_cols, "output leading dimension too small");
   TORCH_CHECK((groups_out - 1) * out_group_stride + (out_rows - 1) * ldo + out_cols <= out.numel(), "output buffer too small");
   if (g.aux) {
@@ -412,6 +457,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_forward", &ce_forward);
   m.def("ce_backward", &ce_backward);
   m.def("count_valid", &count_valid);
+  m.def("router_logits_ok", &router_logits_ok);
+  m.def("router_logits_fwd", &router_logits_fwd);
+  m.def("router_logits_bwd", &router_logits_bwd);
   m.def("router_forward", &router_forward);
   m.def("router_backward", &router_backward);
   m.def("moe_capacity_rows", &moe_capacity_rows);

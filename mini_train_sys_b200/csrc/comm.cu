@@ -74,16 +74,26 @@ __global__ void wait_kernel(const uint32_t* my_flags, int channel, int world, ui
   block_wait_peers(my_flags + channel * world, world, epoch, timeout_ns, status);
 }
 
+// The copy kernels use CTAs of 128 threads with few registers: that is what fits on an SM beside a persistent GEMM CTA
+// (320 threads x 168 registers and nearly all shared memory), so that a gather or a reduction on the side stream makes
+// progress while the compute stream runs GEMMs instead of waiting for a whole SM to drain.
+constexpr int kCopyThreads = 128;
+
 // ---- all-gather (pull) ----
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(kCopyThreads)
 allgather_pull_kernel(uint4* __restrict__ dst, PeerPtrs shards, long long shard_vec, int world, const uint32_t* my_flags,
                       int channel, uint32_t epoch, unsigned long long timeout_ns, int* status) {
   if (epoch != 0 && !block_wait_peers(my_flags + channel * world, world, epoch, timeout_ns, status)) return;
-  const long long total = shard_vec * world;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int peer = int(i / shard_vec);
-    const long long off = i - (long long)peer * shard_vec;
-    dst[i] = static_cast<const uint4*>(shards.p[peer])[off];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int peer = 0; peer < world; ++peer) {
+    const uint4* __restrict__ src = static_cast<const uint4*>(shards.p[peer]);
+    uint4* __restrict__ out = dst + (long long)peer * shard_vec;
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < shard_vec; i += 4 * stride) {      // four independent 16-byte loads in flight per thread
+      const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+      out[i] = a; out[i + stride] = b; out[i + 2 * stride] = c; out[i + 3 * stride] = d;
+    }
+    for (; i < shard_vec; i += stride) out[i] = src[i];
   }
 }
 
@@ -101,13 +111,28 @@ __device__ __forceinline__ void block_add_to(float v, float* out) {
   }
 }
 
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(kCopyThreads)
 reduce_scatter_pull_kernel(float4* __restrict__ out, PeerPtrs bufs, long long slice_vec_offset, long long n_vec, int world,
                            float scale, float* __restrict__ sumsq, const uint32_t* my_flags, int channel, uint32_t epoch,
                            unsigned long long timeout_ns, int* status) {
   if (epoch != 0 && !block_wait_peers(my_flags + channel * world, world, epoch, timeout_ns, status)) return;
   float sq = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + stride < n_vec; i += 2 * stride) {                 // two positions x `world` peers of loads in flight
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    for (int p = 0; p < world; ++p) {
+      const float4* src = static_cast<const float4*>(bufs.p[p]) + slice_vec_offset;
+      const float4 u = src[i], v = src[i + stride];
+      a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+      b.x += v.x; b.y += v.y; b.z += v.z; b.w += v.w;
+    }
+    a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+    b.x *= scale; b.y *= scale; b.z *= scale; b.w *= scale;
+    out[i] = a; out[i + stride] = b;
+    sq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+  }
+  for (; i < n_vec; i += stride) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < world; ++p) {
       const float4 v = static_cast<const float4*>(bufs.p[p])[slice_vec_offset + i];
@@ -121,7 +146,7 @@ reduce_scatter_pull_kernel(float4* __restrict__ out, PeerPtrs bufs, long long sl
 }
 
 // Same contract; the sum over ranks is done by the switch (NVLS) on a multicast address.
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(kCopyThreads)
 reduce_scatter_multimem_kernel(float4* __restrict__ out, const float* __restrict__ mc_base, long long slice_vec_offset,
                                long long n_vec, int world, float scale, float* __restrict__ sumsq, const uint32_t* my_flags,
                                int channel, uint32_t epoch, unsigned long long timeout_ns, int* status) {
@@ -142,54 +167,91 @@ reduce_scatter_multimem_kernel(float4* __restrict__ out, const float* __restrict
 }
 
 // ---- AdamW on the local fp32 shard + push of the new low-precision weights to every replica ----
+// Eight consecutive elements: update p, m, v in place and store the new weights into `world` replicas.
+__device__ __forceinline__ void adamw_update8(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                                              float* __restrict__ v, long long i, void* const* replicas, long long replica_elem_offset,
+                                              int world, int push_bf16, float lr, float b1, float b2, float eps, float wd, float step,
+                                              float inv_sqrt_bc2, float gs) {
+  float pp[8], gg[8], mm[8], vv[8];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float4 a = reinterpret_cast<const float4*>(p)[2 * i + h], b = reinterpret_cast<const float4*>(g)[2 * i + h];
+    const float4 c = reinterpret_cast<const float4*>(m)[2 * i + h], d = reinterpret_cast<const float4*>(v)[2 * i + h];
+    pp[4 * h] = a.x; pp[4 * h + 1] = a.y; pp[4 * h + 2] = a.z; pp[4 * h + 3] = a.w;
+    gg[4 * h] = b.x; gg[4 * h + 1] = b.y; gg[4 * h + 2] = b.z; gg[4 * h + 3] = b.w;
+    mm[4 * h] = c.x; mm[4 * h + 1] = c.y; mm[4 * h + 2] = c.z; mm[4 * h + 3] = c.w;
+    vv[4 * h] = d.x; vv[4 * h + 1] = d.y; vv[4 * h + 2] = d.z; vv[4 * h + 3] = d.w;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float grad = gg[j] * gs;
+    mm[j] = b1 * mm[j] + (1.f - b1) * grad;
+    vv[j] = b2 * vv[j] + (1.f - b2) * grad * grad;
+    pp[j] = pp[j] * (1.f - lr * wd) - step * mm[j] / (sqrtf(vv[j]) * inv_sqrt_bc2 + eps);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    reinterpret_cast<float4*>(p)[2 * i + h] = make_float4(pp[4 * h], pp[4 * h + 1], pp[4 * h + 2], pp[4 * h + 3]);
+    reinterpret_cast<float4*>(m)[2 * i + h] = make_float4(mm[4 * h], mm[4 * h + 1], mm[4 * h + 2], mm[4 * h + 3]);
+    reinterpret_cast<float4*>(v)[2 * i + h] = make_float4(vv[4 * h], vv[4 * h + 1], vv[4 * h + 2], vv[4 * h + 3]);
+  }
+  if (push_bf16) {
+    uint4 packed;
+    uint32_t* w = &packed.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(pp[2 * j], pp[2 * j + 1]);
+      w[j] = *reinterpret_cast<uint32_t*>(&h2);
+    }
+    for (int r = 0; r < world; ++r)
+      reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(replicas[r]) + replica_elem_offset)[i] = packed;
+  } else {
+    for (int r = 0; r < world; ++r) {
+      float4* dst = reinterpret_cast<float4*>(static_cast<float*>(replicas[r]) + replica_elem_offset);
+      dst[2 * i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+      dst[2 * i + 1] = make_float4(pp[4], pp[5], pp[6], pp[7]);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 adamw_push_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                   long long n, PeerPtrs replicas, long long replica_elem_offset, int world, int push_bf16, float lr, float b1,
-                  float b2, float eps, float wd, float bc1, float bc2, const float* __restrict__ gscale_ptr, float static_scale) {
+                  float b2, float eps, float wd, float bc1, float bc2, const float* __restrict__ gscale_ptr, float static_scale,
+                  const int* __restrict__ status) {
+  // A wait that ran out earlier in this step left stale gradients behind: the whole update is skipped, so that weights and both
+  // moments stay exactly as they were (weight decay and the momentum term would otherwise still move them).
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
   const float gs = (gscale_ptr != nullptr ? *gscale_ptr : 1.f) * static_scale;
   const float step = lr / bc1;
   const float inv_sqrt_bc2 = rsqrtf(bc2);
   const long long nvec = n / 8;   // the caller guarantees n % 8 == 0 and 32-byte aligned shards
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-    float pp[8], gg[8], mm[8], vv[8];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const float4 a = reinterpret_cast<const float4*>(p)[2 * i + h], b = reinterpret_cast<const float4*>(g)[2 * i + h];
-      const float4 c = reinterpret_cast<const float4*>(m)[2 * i + h], d = reinterpret_cast<const float4*>(v)[2 * i + h];
-      pp[4 * h] = a.x; pp[4 * h + 1] = a.y; pp[4 * h + 2] = a.z; pp[4 * h + 3] = a.w;
-      gg[4 * h] = b.x; gg[4 * h + 1] = b.y; gg[4 * h + 2] = b.z; gg[4 * h + 3] = b.w;
-      mm[4 * h] = c.x; mm[4 * h + 1] = c.y; mm[4 * h + 2] = c.z; mm[4 * h + 3] = c.w;
-      vv[4 * h] = d.x; vv[4 * h + 1] = d.y; vv[4 * h + 2] = d.z; vv[4 * h + 3] = d.w;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x)
+    adamw_update8(p, g, m, v, i, replicas.p, replica_elem_offset, world, push_bf16, lr, b1, b2, eps, wd, step, inv_sqrt_bc2, gs);
+}
+
+// The same update over a table of segments in ONE launch: the segments of every unit of the model (a dozen units, two
+// weight-decay groups) would otherwise be fifty launches of a few microseconds of work each.  Work is cut into chunks of
+// kAdamChunk elements; a CTA finds the segment of a chunk by bisection over the chunk prefix stored in the table.
+__global__ void __launch_bounds__(256)
+adamw_push_table_kernel(const AdamWSegment* __restrict__ segs, int n_segs, long long total_chunks, float lr0, float lr1, float wd0,
+                        float wd1, float b1, float b2, float eps, float bc1, float bc2, const float* __restrict__ gscale_ptr,
+                        float static_scale, const int* __restrict__ status) {
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
+  const float gs = (gscale_ptr != nullptr ? *gscale_ptr : 1.f) * static_scale;
+  const float inv_sqrt_bc2 = rsqrtf(bc2);
+  for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    int lo = 0, hi = n_segs - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (segs[mid].chunk_begin <= chunk) lo = mid; else hi = mid - 1;
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float grad = gg[j] * gs;
-      mm[j] = b1 * mm[j] + (1.f - b1) * grad;
-      vv[j] = b2 * vv[j] + (1.f - b2) * grad * grad;
-      pp[j] = pp[j] * (1.f - lr * wd) - step * mm[j] / (sqrtf(vv[j]) * inv_sqrt_bc2 + eps);
-    }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      reinterpret_cast<float4*>(p)[2 * i + h] = make_float4(pp[4 * h], pp[4 * h + 1], pp[4 * h + 2], pp[4 * h + 3]);
-      reinterpret_cast<float4*>(m)[2 * i + h] = make_float4(mm[4 * h], mm[4 * h + 1], mm[4 * h + 2], mm[4 * h + 3]);
-      reinterpret_cast<float4*>(v)[2 * i + h] = make_float4(vv[4 * h], vv[4 * h + 1], vv[4 * h + 2], vv[4 * h + 3]);
-    }
-    if (push_bf16) {
-      uint4 packed;
-      uint32_t* w = &packed.x;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(pp[2 * j], pp[2 * j + 1]);
-        w[j] = *reinterpret_cast<uint32_t*>(&h2);
-      }
-      for (int r = 0; r < world; ++r)
-        reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(replicas.p[r]) + replica_elem_offset)[i] = packed;
-    } else {
-      for (int r = 0; r < world; ++r) {
-        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(replicas.p[r]) + replica_elem_offset);
-        dst[2 * i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
-        dst[2 * i + 1] = make_float4(pp[4], pp[5], pp[6], pp[7]);
-      }
+    const AdamWSegment& sg = segs[lo];
+    const long long i = (chunk - sg.chunk_begin) * (kAdamChunk / 8) + threadIdx.x;
+    if (i * 8 < sg.n) {
+      const float lr = sg.group == 0 ? lr0 : lr1, wd = sg.group == 0 ? wd0 : wd1;
+      adamw_update8(sg.p, sg.g, sg.m, sg.v, i, sg.replicas, sg.replica_offset, sg.world, sg.push_bf16, lr, b1, b2, eps, wd,
+                    lr / bc1, inv_sqrt_bc2, gs);
     }
   }
 }
@@ -248,7 +310,7 @@ cudaError_t launch_allgather_pull(void* dst, const PeerPtrs& shards, long long s
                                   cudaStream_t stream) {
   if (world > kMaxPeers || shard_bytes % 16 != 0) return cudaErrorInvalidValue;
   const long long vec = shard_bytes / 16;
-  allgather_pull_kernel<<<copy_grid(vec * world, 512, max_ctas), 512, 0, stream>>>(
+  allgather_pull_kernel<<<copy_grid(vec, kCopyThreads * 4, max_ctas), kCopyThreads, 0, stream>>>(
       static_cast<uint4*>(dst), shards, vec, world, my_flags, channel, epoch, timeout_ns, status);
   ++g_launch_count;
   return cudaGetLastError();
@@ -258,24 +320,35 @@ cudaError_t launch_reduce_scatter(float* out, const PeerPtrs& bufs, const float*
                                   long long n, int world, float scale, float* sumsq, const unsigned* my_flags, int channel,
                                   unsigned epoch, unsigned long long timeout_ns, int* status, int max_ctas, cudaStream_t stream) {
   if (world > kMaxPeers || n % 4 != 0 || slice_offset % 4 != 0) return cudaErrorInvalidValue;
-  const int grid = copy_grid(n / 4, 512, max_ctas);
+  const int grid = copy_grid(n / 4, kCopyThreads * 2, max_ctas);
   if (multicast_base != nullptr)
-    reduce_scatter_multimem_kernel<<<grid, 512, 0, stream>>>(reinterpret_cast<float4*>(out), multicast_base, slice_offset / 4,
+    reduce_scatter_multimem_kernel<<<grid, kCopyThreads, 0, stream>>>(reinterpret_cast<float4*>(out), multicast_base, slice_offset / 4,
                                                              n / 4, world, scale, sumsq, my_flags, channel, epoch, timeout_ns, status);
   else
-    reduce_scatter_pull_kernel<<<grid, 512, 0, stream>>>(reinterpret_cast<float4*>(out), bufs, slice_offset / 4, n / 4, world,
+    reduce_scatter_pull_kernel<<<grid, kCopyThreads, 0, stream>>>(reinterpret_cast<float4*>(out), bufs, slice_offset / 4, n / 4, world,
                                                          scale, sumsq, my_flags, channel, epoch, timeout_ns, status);
   ++g_launch_count;
   return cudaGetLastError();
 }
 
 cudaError_t launch_adamw_push(const AdamWArgs& a, const PeerPtrs& replicas, long long replica_elem_offset, int world,
-                              bool push_bf16, int max_ctas, cudaStream_t stream) {
+                              bool push_bf16, int max_ctas, const int* status, cudaStream_t stream) {
   if (world > kMaxPeers || a.n % 8 != 0) return cudaErrorInvalidValue;
   if (a.n == 0) return cudaSuccess;
   adamw_push_kernel<<<copy_grid(a.n / 8, 256, max_ctas), 256, 0, stream>>>(
       a.param, a.grad, a.exp_avg, a.exp_avg_sq, a.n, replicas, replica_elem_offset, world, push_bf16 ? 1 : 0, a.lr, a.beta1,
-      a.beta2, a.eps, a.weight_decay, a.bias_correction1, a.bias_correction2, a.grad_scale, a.static_grad_scale);
+      a.beta2, a.eps, a.weight_decay, a.bias_correction1, a.bias_correction2, a.grad_scale, a.static_grad_scale, status);
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_adamw_push_table(const AdamWSegment* segs, int n_segs, long long total_chunks, float lr0, float lr1, float wd0,
+                                    float wd1, float beta1, float beta2, float eps, float bc1, float bc2, const float* grad_scale,
+                                    float static_scale, const int* status, int max_ctas, cudaStream_t stream) {
+  if (n_segs <= 0 || total_chunks <= 0) return cudaSuccess;
+  const int grid = int(total_chunks < max_ctas ? total_chunks : max_ctas);
+  adamw_push_table_kernel<<<grid, 256, 0, stream>>>(segs, n_segs, total_chunks, lr0, lr1, wd0, wd1, beta1, beta2, eps, bc1, bc2,
+                                                    grad_scale, static_scale, status);
   ++g_launch_count;
   return cudaGetLastError();
 }

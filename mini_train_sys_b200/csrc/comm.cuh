@@ -29,8 +29,25 @@ cudaError_t launch_allgather_pull(void* dst, const PeerPtrs& shards, long long s
 cudaError_t launch_reduce_scatter(float* out, const PeerPtrs& bufs, const float* multicast_base, long long slice_offset,
                                   long long n, int world, float scale, float* sumsq, const unsigned* my_flags, int channel,
                                   unsigned epoch, unsigned long long timeout_ns, int* status, int max_ctas, cudaStream_t stream);
+// `status` (optional): the device's status word; when it is non-zero at launch the kernel changes nothing.
 cudaError_t launch_adamw_push(const AdamWArgs& args, const PeerPtrs& replicas, long long replica_elem_offset, int world,
-                              bool push_bf16, int max_ctas, cudaStream_t stream);
+                              bool push_bf16, int max_ctas, const int* status, cudaStream_t stream);
+// One row of the table behind launch_adamw_push_table: a run of a unit's local shard with one weight-decay group.
+constexpr int kAdamChunk = 2048;   // elements per CTA pass (256 threads x 8)
+struct AdamWSegment {
+  float* p; const float* g; float* m; float* v;   // start of the run in the fp32 shard buffers
+  long long n;                // elements, a multiple of 8
+  long long chunk_begin;      // number of chunks in all earlier rows
+  long long replica_offset;   // element offset of the run inside every replica
+  void* replicas[kMaxPeers];  // low-precision destinations (the rank's own shard buffer, or every peer's replica)
+  int world;                  // how many of them
+  int group;                  // 0: decayed parameters (lr0, wd0), 1: the rest (lr1, wd1)
+  int push_bf16;
+  int reserved;
+};
+cudaError_t launch_adamw_push_table(const AdamWSegment* segs, int n_segs, long long total_chunks, float lr0, float lr1, float wd0,
+                                    float wd1, float beta1, float beta2, float eps, float bc1, float bc2, const float* grad_scale,
+                                    float static_scale, const int* status, int max_ctas, cudaStream_t stream);
 cudaError_t launch_scalar_allreduce_clip(const float* local_value, const PeerPtrs& slots, const PeerPtrs& flag_bases,
                                          const unsigned* my_flags, int channel, int world, int rank, unsigned epoch,
                                          unsigned long long timeout_ns, float max_norm, float extra_scale, float* coef_out,

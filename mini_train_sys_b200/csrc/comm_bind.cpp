@@ -1,6 +1,9 @@
 // Python bindings of the peer-memory collectives.  Peer pointers arrive as integer lists (one per rank)
 // obtained from the symmetric-memory rendezvous; everything else is an ordinary CUDA tensor.
 #include <ATen/cuda/CUDAContext.h>
+#include <cmath>
+#include <cstring>
+#include <tuple>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
@@ -70,7 +73,7 @@ void comm_reduce_scatter(Tensor out, const std::vector<int64_t>& buf_ptrs, int64
 void comm_adamw_push(Tensor param, const Tensor& grad, Tensor exp_avg, Tensor exp_avg_sq, const std::vector<int64_t>& replica_ptrs,
                      int64_t replica_elem_offset, bool push_bf16, double lr, double beta1, double beta2, double eps,
                      double weight_decay, int64_t step, const c10::optional<Tensor>& grad_scale, double static_scale,
-                     int64_t max_ctas) {
+                     int64_t max_ctas, const c10::optional<Tensor>& status) {
   TORCH_CHECK(param.is_cuda() && param.scalar_type() == at::kFloat && param.is_contiguous() && param.numel() % 8 == 0,
               "param shard must be contiguous fp32 with a multiple of 8 elements");
   TORCH_CHECK(grad.scalar_type() == at::kFloat && grad.is_contiguous() && grad.numel() == param.numel() &&
@@ -88,8 +91,51 @@ void comm_adamw_push(Tensor param, const Tensor& grad, Tensor exp_avg, Tensor ex
   a.bias_correction2 = float(1.0 - std::pow(beta2, double(step)));
   a.grad_scale = (grad_scale.has_value() && grad_scale->defined()) ? grad_scale->data_ptr<float>() : nullptr;
   a.static_grad_scale = float(static_scale);
-  ok(mts::launch_adamw_push(a, to_ptrs(replica_ptrs), replica_elem_offset, int(replica_ptrs.size()), push_bf16, int(max_ctas), cur()),
-     "adamw_push");
+  const int* status_ptr = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+  ok(mts::launch_adamw_push(a, to_ptrs(replica_ptrs), replica_elem_offset, int(replica_ptrs.size()), push_bf16, int(max_ctas),
+                            status_ptr, cur()), "adamw_push");
+}
+
+// rows: [p, g, m, v, n, replica_offset, group, push_bf16, replica pointers...] (addresses as integers).  Returns the table as a
+// device byte tensor and the total number of chunks.
+std::tuple<Tensor, int64_t> comm_adamw_table(const std::vector<std::vector<int64_t>>& rows, const Tensor& like) {
+  std::vector<mts::AdamWSegment> host(rows.size());
+  int64_t chunks = 0;
+  for (size_t i = 0; i < rows.size(); ++i) {
+    const auto& r = rows[i];
+    TORCH_CHECK(r.size() >= 9 && r.size() <= 8 + size_t(mts::kMaxPeers), "adamw table row: 8 fields + 1..16 replica pointers");
+    mts::AdamWSegment sg{};
+    sg.p = reinterpret_cast<float*>(r[0]); sg.g = reinterpret_cast<const float*>(r[1]);
+    sg.m = reinterpret_cast<float*>(r[2]); sg.v = reinterpret_cast<float*>(r[3]);
+    sg.n = r[4]; sg.replica_offset = r[5]; sg.group = int(r[6]); sg.push_bf16 = int(r[7]);
+    TORCH_CHECK(sg.n > 0 && sg.n % 8 == 0 && sg.replica_offset % 8 == 0, "adamw table: runs must be multiples of 8 elements");
+    for (int64_t a : {r[0], r[1], r[2], r[3]}) TORCH_CHECK(a != 0 && (a & 15) == 0, "adamw table: 16-byte aligned buffers");
+    sg.world = int(r.size() - 8);
+    for (int k = 0; k < sg.world; ++k) {
+      TORCH_CHECK(r[8 + k] != 0 && (r[8 + k] & 15) == 0, "adamw table: replica pointers must be 16-byte aligned");
+      sg.replicas[k] = reinterpret_cast<void*>(r[8 + k]);
+    }
+    sg.chunk_begin = chunks;
+    chunks += (sg.n + mts::kAdamChunk - 1) / mts::kAdamChunk;
+    host[i] = sg;
+  }
+  Tensor cpu = torch::empty({int64_t(host.size() * sizeof(mts::AdamWSegment))}, torch::dtype(torch::kUInt8));
+  std::memcpy(cpu.data_ptr(), host.data(), host.size() * sizeof(mts::AdamWSegment));
+  return {cpu.to(like.device()), chunks};
+}
+
+void comm_adamw_push_table(const Tensor& table, int64_t n_segs, int64_t total_chunks, double lr0, double lr1, double wd0, double wd1,
+                           double beta1, double beta2, double eps, int64_t step, const c10::optional<Tensor>& grad_scale,
+                           double static_scale, const c10::optional<Tensor>& status, int64_t max_ctas) {
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kByte && table.is_contiguous() &&
+                  table.numel() == n_segs * int64_t(sizeof(mts::AdamWSegment)), "adamw table has the wrong size");
+  c10::cuda::CUDAGuard guard(table.device());
+  const float* gs = (grad_scale.has_value() && grad_scale->defined()) ? grad_scale->data_ptr<float>() : nullptr;
+  const int* st = (status.has_value() && status->defined()) ? status->data_ptr<int>() : nullptr;
+  ok(mts::launch_adamw_push_table(reinterpret_cast<const mts::AdamWSegment*>(table.data_ptr()), int(n_segs), total_chunks, float(lr0),
+                                  float(lr1), float(wd0), float(wd1), float(beta1), float(beta2), float(eps),
+                                  float(1.0 - std::pow(beta1, double(step))), float(1.0 - std::pow(beta2, double(step))), gs,
+                                  float(static_scale), st, int(max_ctas), cur()), "adamw_push_table");
 }
 
 void comm_norm_clip(const Tensor& local_sumsq, const std::vector<int64_t>& slot_ptrs, const std::vector<int64_t>& flag_bases,
@@ -169,5 +215,7 @@ void bind_comm(pybind11::module_& m) {
   m.def("comm_allgather", &comm_allgather);
   m.def("comm_reduce_scatter", &comm_reduce_scatter);
   m.def("comm_adamw_push", &comm_adamw_push);
+  m.def("comm_adamw_table", &comm_adamw_table);
+  m.def("comm_adamw_push_table", &comm_adamw_push_table);
   m.def("comm_norm_clip", &comm_norm_clip);
 }

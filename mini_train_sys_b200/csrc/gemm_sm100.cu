@@ -23,11 +23,12 @@
 #include <cudaTypedefs.h>
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 
 namespace mts {
 
-unsigned long long g_launch_count = 0;
+std::atomic<unsigned long long> g_launch_count{0};
 const char* g_last_error = "";
 
 #ifdef MTS_GEMM_TRACE
@@ -77,6 +78,7 @@ struct KernelParams {
   const int* num_row_tiles;
   const int* group_rows;
   int num_groups;
+  int k_splits;      // GROUPED_K: every group's row range is cut into this many parts, each a work item that adds into the group's output
   int b_group_stride_rows;
   long long out_group_stride;
   int tiles_m, tiles_n;
@@ -106,7 +108,7 @@ __device__ __forceinline__ int live_tiles(const KernelParams& p) {
     rows = rows < p.tiles_m ? rows : p.tiles_m;
     return rows * p.tiles_n;
   }
-  if (p.mode == GEMM_GROUPED_K) return p.num_groups * p.tiles_m * p.tiles_n;
+  if (p.mode == GEMM_GROUPED_K) return p.num_groups * p.k_splits * p.tiles_m * p.tiles_n;
   return p.tiles_m * p.tiles_n;
 }
 
@@ -118,10 +120,18 @@ __device__ __forceinline__ Tile decode_tile(const KernelParams& p, int t) {
   o.out_group = 0;
   if (p.mode == GEMM_GROUPED_K) {
     const int per = p.tiles_m * p.tiles_n;
-    const int g = t / per;
-    const int r = t - g * per;
+    const int part = t / per;                       // (group, split), splits of one group adjacent
+    const int r = t - part * per;
     const int mt = r / p.tiles_n, nt = r - mt * p.tiles_n;
-    const int k0 = p.group_rows[g], k1 = p.group_rows[g + 1];
+    const int g = part / p.k_splits, sp = part - g * p.k_splits;
+    int k0 = p.group_rows[g], k1 = p.group_rows[g + 1];
+    if (p.k_splits > 1) {                           // equal parts, whole k-blocks each; the last ones may be empty
+      const int blocks = (k1 - k0 + BK - 1) / BK;
+      const int per_split = (blocks + p.k_splits - 1) / p.k_splits;
+      const int lo = k0 + sp * per_split * BK, hi = lo + per_split * BK;
+      k0 = lo < k1 ? lo : k1;
+      k1 = hi < k1 ? hi : k1;
+    }
     o.a_coord = mt * TILE_M;
     o.b_coord = nt * BN;
     o.b_coord2 = o.b_coord + 128;
@@ -895,14 +905,17 @@ bool encode_out_3d(CUtensorMap* map, const void* base, bool fp32, int64_t cols, 
   return r == CUDA_SUCCESS;
 }
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
+int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev >= 0 && dev < 64 ? dev : 0;
+}
+
+int sm_count() {       // per device: a process may drive several
+  static int n[64] = {};
+  const int dev = current_device();
+  if (n[dev] == 0) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+  return n[dev];
 }
 
 }  // namespace
@@ -920,6 +933,7 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
   p.aux = a.aux; p.ld_aux = a.ld_aux;
   p.tile_group = a.tile_group; p.num_row_tiles = a.num_row_tiles; p.group_rows = a.group_rows;
   p.num_groups = a.num_groups;
+  p.k_splits = a.k_splits > 1 ? a.k_splits : 1;
   p.b_group_stride_rows = int(a.b_group_stride_rows);
   p.out_group_stride = a.out_group_stride;
   p.status = a.status;
@@ -951,10 +965,11 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
   // saved pre-activations: blocked layout of 32-row x 8-value chunks (see aux_chunk), addressed with 16-byte accesses
   if (a.aux != nullptr && ((reinterpret_cast<uintptr_t>(a.aux) & 15) != 0 || a.ld_aux % 8 != 0)) return cudaErrorInvalidValue;
   if (a.atomic_out && !a.out_fp32) return cudaErrorInvalidValue;
+  if (p.k_splits > 1 && (a.mode != GEMM_GROUPED_K || !a.atomic_out)) return cudaErrorInvalidValue;   // parts add into one output
   g_last_error = "";
 
   long long total = (long long)p.tiles_m * p.tiles_n;
-  if (a.mode == GEMM_GROUPED_K) total *= a.num_groups;
+  if (a.mode == GEMM_GROUPED_K) total *= (long long)a.num_groups * p.k_splits;
   if (total <= 0) return cudaSuccess;
   int workers = pair ? sm_count() / 2 : sm_count();
   if (a.sm_limit > 0 && a.sm_limit < workers * (pair ? 2 : 1)) workers = pair ? (a.sm_limit / 2 > 0 ? a.sm_limit / 2 : 1) : a.sm_limit;
@@ -966,7 +981,8 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
        {gemm_tcgen05_kernel<false, true, false>, gemm_tcgen05_kernel<false, true, true>}},
       {{gemm_tcgen05_kernel<true, false, false>, gemm_tcgen05_kernel<true, false, true>},
        {gemm_tcgen05_kernel<true, true, false>, gemm_tcgen05_kernel<true, true, true>}}};
-  static bool attr_set = false;
+  static bool attr_set_on[64] = {};          // cudaFuncSetAttribute applies to the current device only
+  bool& attr_set = attr_set_on[current_device()];
   if (!attr_set) {
     for (int i = 0; i < 8; ++i) {
       const bool pr = (i >> 2) & 1;

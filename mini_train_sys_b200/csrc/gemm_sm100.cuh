@@ -12,7 +12,8 @@
 //                  128-row tile comes from `tile_group`; B is the experts' weights stacked along rows.
 //   GEMM_GROUPED_K one output per group; the contraction runs over that group's row range
 //                  [group_rows[g], group_rows[g+1]) of A and B (both MN-major).  With `atomic_out` all
-//                  groups add into the same output, which is how split-K wgrad is expressed.
+//                  groups add into the same output, which is how split-K wgrad is expressed; with `k_splits` > 1
+//                  every group's range is cut further and the parts add into that group's output (pre-zeroed).
 //
 // Epilogues:
 //   EPI_STORE       D -> out (bf16 or fp32; optional accumulate; optional fp32 atomic add).  When N is not a multiple of
@@ -25,6 +26,8 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <atomic>
 
 namespace mts {
 
@@ -60,6 +63,7 @@ struct GemmArgs {
   const int* num_row_tiles = nullptr;  // GROUPED_M: device scalar, number of live 128-row tiles
   const int* group_rows = nullptr;   // GROUPED_K: [groups + 1] row offsets (multiples of 64)
   int num_groups = 1;
+  int k_splits = 1;                  // GROUPED_K with atomic_out: cut every group's rows into this many work items (load balance)
   int64_t b_group_stride_rows = 0;   // GROUPED_M: rows of stacked B per group
   int64_t out_group_stride = 0;      // GROUPED_K: elements between consecutive group outputs (0 with atomic_out)
 
@@ -73,7 +77,7 @@ struct GemmArgs {
 cudaError_t launch_gemm_sm100(const GemmArgs& args);
 
 // Number of kernels launched through this library since load (the benchmark reports it).
-extern unsigned long long g_launch_count;
+extern std::atomic<unsigned long long> g_launch_count;
 // Human-readable reason of the most recent launch_gemm_sm100 failure ("" when none).
 extern const char* g_last_error;
 

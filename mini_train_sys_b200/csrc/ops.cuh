@@ -5,9 +5,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace mts {
 
-extern unsigned long long g_launch_count;
+extern std::atomic<unsigned long long> g_launch_count;
 int device_sm_count();
 
 // ---- elementwise.cu ----
@@ -67,6 +69,14 @@ cudaError_t launch_moe_combine(const void* y, const int* token_rows, const void*
 cudaError_t launch_moe_combine_bwd(const void* dout, const void* y, const int* row_token, const int* token_rows,
                                    const void* weights, void* dys, float* dweights, int T, int K, int H,
                                    int capacity_rows, const int* meta, cudaStream_t stream);
+
+// ---- skinny_gemm.cu: router projection x[T, H] (bf16) x W[E, H] (fp32 or bf16), E in {4, 8, 16}, fp32 arithmetic ----
+bool router_logits_supported(int E, int H);
+cudaError_t launch_router_logits_fwd(const void* x, const void* w, bool w_bf16, float* out, int T, int E, int H, cudaStream_t stream);
+// dx[T, H] (bf16) = g[T, E] W
+cudaError_t launch_router_logits_dx(const float* g, const void* w, bool w_bf16, void* dx, int T, int E, int H, cudaStream_t stream);
+// dw[E, H] (fp32, zeroed by the caller) += g^T x
+cudaError_t launch_router_logits_dw(const float* g, const void* x, float* dw, int T, int E, int H, cudaStream_t stream);
 
 // ---- optim.cu ----
 struct AdamWArgs {

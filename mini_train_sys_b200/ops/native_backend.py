@@ -85,12 +85,12 @@ def bf16_weight(weight: torch.Tensor) -> torch.Tensor:
 
 def _gemm(a, b, out, M, N, K, *, a_mn=False, b_mn=False, mode=GEMM_DENSE, epilogue=EPI_STORE, accumulate=False,
           atomic_out=False, aux=None, tile_group=None, num_row_tiles=None, group_rows=None, num_groups=1,
-          b_group_stride_rows=0, out_group_stride=0, ldo=None, sm_limit=0, pair=None) -> None:
+          b_group_stride_rows=0, out_group_stride=0, ldo=None, sm_limit=0, pair=None, k_splits=1) -> None:
     if pair is None:
         pair = GEMM_PAIR
     ext().gemm(a, b, out, M, N, K, a_mn, b_mn, mode, epilogue, accumulate, atomic_out, aux, tile_group, num_row_tiles,
                group_rows, num_groups, b_group_stride_rows, out_group_stride, out.stride(-2) if ldo is None else ldo,
-               sm_limit, bool(pair))
+               sm_limit, bool(pair), k_splits)
 
 
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, out_dtype=torch.bfloat16
@@ -150,6 +150,29 @@ def gemm_tn(a_km: torch.Tensor, b_kn: torch.Tensor, out: torch.Tensor | None = N
     _gemm(a_km, b_kn, out, M, N, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=rows, num_groups=splits,
           accumulate=accumulate and not atomic, atomic_out=atomic, out_group_stride=0)
     return out
+
+
+def expert_wgrad_splits(rows: int, groups: int, m: int, n: int, device: torch.device) -> int:
+    """How many parts to cut every expert's rows into for a grouped weight-gradient GEMM.
+
+    One expert's gradient is only ``ceil(m / 256) * ceil(n / 256)`` tiles (12 for a 768 x 1024 down projection), so eight
+    experts fill 96 of the 74 CTA pairs' second wave and leave the machine two thirds idle for half of the kernel.  Cutting
+    the contraction gives more, shorter work items that add into the (pre-zeroed) output with TMA reduce-adds; the count is
+    the one that wastes the least of the last wave while every part keeps at least 1,024 rows."""
+
+    pairs = max(torch.cuda.get_device_properties(device).multi_processor_count // 2, 1) if GEMM_PAIR else \
+        torch.cuda.get_device_properties(device).multi_processor_count
+    tiles = groups * -(-m // (256 if GEMM_PAIR else 128)) * -(-n // 256)
+    per_group = max(rows // max(groups, 1), 1)
+    best, best_eff = 1, 0.0
+    for s in range(1, 9):
+        if s > 1 and per_group // s < 1024:
+            break
+        items = tiles * s
+        eff = items / (-(-items // pairs) * pairs)
+        if eff > best_eff + 0.02:
+            best, best_eff = s, eff
+    return best
 
 
 def grad_sink(param: torch.Tensor):
@@ -427,7 +450,7 @@ class _RouterLogitsFn(torch.autograd.Function):
             width = -(-n_exp // 4) * 4
             out = torch.empty(x.shape[0], width, dtype=torch.float32, device=x.device)
             _gemm(x, w_hi, out, x.shape[0], n_exp, hidden, ldo=width)
-            ctx.save_for_backward(x, weight, w_hi)
+            ctx.save_for_backward(x, weight, None)
             return out if width == n_exp else out[:, :n_exp].contiguous()
         w_hi, w_lo = _split_bf16(weight.detach().float())
         stacked = torch.zeros(2 * n_exp, hidden, dtype=torch.bfloat16, device=x.device)
@@ -441,6 +464,8 @@ class _RouterLogitsFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         x, weight, w_hi = ctx.saved_tensors
+        if w_hi is None:     # bf16 replica: read it through the parameter, whose storage may have moved since forward
+            w_hi = weight.detach() if weight.is_contiguous() else weight.detach().contiguous()
         n_exp, hidden = weight.shape
         g32 = g.float()
         g_hi, g_lo = _split_bf16(g32)
@@ -461,6 +486,28 @@ class _RouterLogitsFn(torch.autograd.Function):
             both = gemm_tn(g2, x, M=2 * n_exp)
             dw = (both[:n_exp] + both[n_exp:2 * n_exp]).to(weight.dtype)
         return dx, dw
+
+
+class _RouterProjectionFn(torch.autograd.Function):
+    """fp32 router logits by the skinny-GEMM kernels: ``x`` (bf16) is read once per pass, arithmetic is fp32 FMA.
+
+    Replaces three launches of the 256-wide tcgen05 GEMM per layer (32-38 us each for 0.6 GFLOP) by kernels that take
+    the time of reading ``x``.  The weight may be the fp32 parameter or a bf16 replica of it (sharded engines)."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        w = weight.detach()
+        w = w if w.is_contiguous() else w.contiguous()
+        ctx.save_for_backward(x, weight)
+        return ext().router_logits_fwd(x, w)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, weight = ctx.saved_tensors       # the parameter itself: its storage may have moved since forward (staged units)
+        w = weight.detach()
+        w = w if w.is_contiguous() else w.contiguous()
+        dx, dw = ext().router_logits_bwd(g.float().contiguous(), x, w, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        return dx, (dw.to(weight.dtype) if dw is not None else None)
 
 
 class _RouterFn(torch.autograd.Function):
@@ -549,8 +596,11 @@ class _FusedMoEFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             sink = grad_sink(gate_up_proj)
             dgu = sink[0] if sink is not None else torch.empty(n_exp, two_i, hidden, dtype=torch.float32, device=dev)
+            splits = expert_wgrad_splits(cap, n_exp, two_i, hidden, dev)
+            if splits > 1:
+                dgu.zero_()
             _gemm(d_pre, xs, dgu, two_i, hidden, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=group_rows,
-                  num_groups=n_exp, out_group_stride=two_i * hidden, ldo=hidden)
+                  num_groups=n_exp, out_group_stride=two_i * hidden, ldo=hidden, k_splits=splits, atomic_out=splits > 1)
             if sink is not None:
                 sink[1](gate_up_proj)
                 dgu = None
@@ -559,8 +609,11 @@ class _FusedMoEFn(torch.autograd.Function):
         if ctx.needs_input_grad[2]:
             sink = grad_sink(down_proj)
             ddn = sink[0] if sink is not None else torch.empty(n_exp, hidden, inter, dtype=torch.float32, device=dev)
+            splits = expert_wgrad_splits(cap, n_exp, hidden, inter, dev)
+            if splits > 1:
+                ddn.zero_()
             _gemm(dys, post, ddn, hidden, inter, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=group_rows,
-                  num_groups=n_exp, out_group_stride=hidden * inter, ldo=inter)
+                  num_groups=n_exp, out_group_stride=hidden * inter, ldo=inter, k_splits=splits, atomic_out=splits > 1)
             if sink is not None:
                 sink[1](down_proj)
                 ddn = None
@@ -658,6 +711,8 @@ class NativeOpsBackend(TorchOpsBackend):
         ok = (hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16 and hidden_states.dim() == 2
               and hidden_states.is_contiguous() and hidden_states.shape[1] % 8 == 0 and weight.shape[0] <= 64)
         if self._count("router_logits", ok):
+            if ext().router_logits_ok(weight.shape[0], weight.shape[1]) and weight.dtype in (torch.float32, torch.bfloat16):
+                return _RouterProjectionFn.apply(hidden_states, weight)
             return _RouterLogitsFn.apply(hidden_states, weight)
         return torch.nn.functional.linear(hidden_states.float(), weight.float())
 

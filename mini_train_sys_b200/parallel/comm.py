@@ -9,7 +9,8 @@ pointers (optionally ``multimem`` on the NVLS multicast mapping).  No NCCL call 
 ``TorchCollectives`` implements the same five operations with ``torch.distributed`` (NCCL or Gloo) or,
 for a world of one, with local copies; it is the CPU-testable twin and the baseline engine.
 
-Both expose: ``alloc``, ``reduce_scatter``, ``norm_and_clip``, ``adamw_update`` and ``refresh_done``.
+Both expose: ``alloc``, ``reduce_scatter``, ``norm_and_clip``, ``adamw_update``, ``refresh_done`` and the
+public ``all_reduce_``.
 """
 
 from __future__ import annotations
@@ -93,7 +94,31 @@ class TorchCollectives:
         else:
             unit.gathered.tensor.copy_(low)
 
+    def refresh_shard(self, unit) -> None:
+        """``full_shard``: only the rank's own low-precision shard is kept; rebuild it from the fp32 master."""
+
+        unit.low_shard.tensor[:unit.shard_numel].copy_(unit.master.to(unit.low_shard.tensor.dtype))
+
+    def gather_unit(self, unit, dst: torch.Tensor) -> None:
+        """All-gather the low-precision shards of ``unit`` into ``dst`` (``[unit.total]``)."""
+
+        mine = unit.low_shard.tensor[:unit.shard_numel]
+        if self.world > 1 and not unit.local:
+            dist.all_gather_into_tensor(dst[:unit.total], mine.contiguous())
+        else:
+            dst[:unit.total].copy_(mine)
+
     def refresh_done(self, epoch: int) -> None:
+        pass
+
+    def all_reduce_(self, tensor: torch.Tensor) -> torch.Tensor:
+        """In-place sum over ranks through the library (identity for a single rank)."""
+
+        if self.world > 1:
+            dist.all_reduce(tensor, op=dist.ReduceOp.SUM)
+        return tensor
+
+    def check_status(self) -> None:
         pass
 
     def close(self) -> None:
@@ -106,10 +131,12 @@ class PeerCollectives:
     fused = True
     CH_NORM = 0
     CH_PARAMS = 1
-    CH_UNIT0 = 2      # one "gradients complete" channel per unit from here on
+    CH_ALLREDUCE = 2  # the public all-reduce
+    CH_UNIT0 = 3      # one "gradients complete" channel per unit from here on
+    ALLREDUCE_ONE_SHOT_BYTES = 256 * 1024
 
     def __init__(self, device: torch.device, *, max_units: int, wait_timeout_ms: float = 2000.0,
-                 use_multimem: bool = False, max_ctas: int = 64) -> None:
+                 use_multimem: bool = False, max_ctas: int = 296) -> None:
         from mini_train_sys_b200.ops.native_backend import ext
 
         self.ext = ext()
@@ -124,6 +151,11 @@ class PeerCollectives:
         self.flags = self.alloc(channels * self.world, torch.int32, shared=True)
         self.slots = self.alloc(4 * max(self.world, 4), torch.float32, shared=True)
         self.comm_stream = torch.cuda.Stream(device)
+        self._ar_stage: SymBuffer | None = None     # all-reduce staging: two halves used alternately
+        self._ar_part: SymBuffer | None = None      # this rank's reduced slice, read by every peer
+        self._ar_result: torch.Tensor | None = None
+        self._ar_calls = 0
+        self.allreduce_capacity = 16 * 2**20        # fp32 elements per pass (64 MiB); larger tensors go in passes
 
     def alloc(self, numel: int, dtype: torch.dtype, *, shared: bool = False) -> SymBuffer:
         numel = -(-numel // 64) * 64
@@ -164,10 +196,36 @@ class PeerCollectives:
 
     def adamw_update(self, unit, seg, *, lr, beta1, beta2, eps, weight_decay, step, coef) -> None:
         lo, hi = seg
-        low_bf16 = unit.gathered.tensor.dtype == torch.bfloat16
+        if getattr(unit, "staged", False):      # full_shard: the new weights go into the rank's own shard only
+            dests, offset, low = [unit.low_shard.tensor.data_ptr()], lo, unit.low_shard.tensor
+        else:
+            dests, offset, low = unit.gathered.peer_ptrs, unit.rank * unit.shard_numel + lo, unit.gathered.tensor
         self.ext.comm_adamw_push(unit.master[lo:hi], unit.grad_shard[lo:hi], unit.exp_avg[lo:hi], unit.exp_avg_sq[lo:hi],
-                                 unit.gathered.peer_ptrs, unit.rank * unit.shard_numel + lo, low_bf16, lr, beta1, beta2,
-                                 eps, weight_decay, step, coef, 1.0, self.max_ctas * 4)
+                                 dests, offset, low.dtype == torch.bfloat16, lr, beta1, beta2,
+                                 eps, weight_decay, step, coef, 1.0, self.max_ctas * 4, self.status)
+
+    def adamw_update_table(self, table, n_rows: int, chunks: int, *, lr, weight_decay, betas, eps, step, coef) -> None:
+        """Every segment of every unit in one launch (the table comes from ``ext.comm_adamw_table``)."""
+
+        self.ext.comm_adamw_push_table(table, n_rows, chunks, lr[0], lr[1], weight_decay[0], weight_decay[1], betas[0], betas[1],
+                                       eps, step, coef, 1.0, self.status, self.max_ctas * 4)
+
+    def refresh_shard(self, unit) -> None:
+        """``full_shard`` start-up / restore: rebuild the own low-precision shard, then let every rank finish before any gathers."""
+
+        unit.low_shard.tensor[:unit.shard_numel].copy_(unit.master.to(unit.low_shard.tensor.dtype))
+        if self.world > 1 and not unit.local:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(device_ids=[self.device.index])
+
+    def gather_unit(self, unit, dst: torch.Tensor) -> None:
+        """Pull every owner's shard of ``unit`` into ``dst`` on the current stream.  No flag wait is needed: the shards were
+        completed before ``refresh_done`` of the last step returned on every rank, and they are next written after the
+        global-norm exchange of this step, which every rank enters only after its last gather."""
+
+        low = unit.low_shard
+        self.ext.comm_allgather(dst, low.peer_ptrs, unit.shard_numel * low.tensor.element_size(), self.flags.tensor,
+                                self.CH_PARAMS, 0, self.timeout_ms, self.status, self.max_ctas)
 
     def refresh_replicas(self, unit, epoch: int) -> None:
         """Pull all-gather of the low-precision shards (used at start-up and after a checkpoint load)."""
@@ -193,6 +251,71 @@ class PeerCollectives:
             return
         self.ext.comm_signal(self.flags.peer_ptrs, self.CH_PARAMS, self.rank, epoch, self.flags.tensor)
         self.ext.comm_wait(self.flags.tensor, self.CH_PARAMS, self.world, epoch, self.timeout_ms, self.status)
+
+    # -- public all-reduce ----------------------------------------------------------------------------------------
+    def _allreduce_buffers(self) -> None:
+        if self._ar_stage is None:
+            cap = self.allreduce_capacity
+            self._ar_stage = self.alloc(2 * cap, torch.float32, shared=True)
+            self._ar_part = self.alloc(cap // self.world + 64, torch.float32, shared=True)
+            self._ar_result = torch.empty(cap, dtype=torch.float32, device=self.device)
+
+    @torch.no_grad()
+    def all_reduce_(self, tensor: torch.Tensor) -> torch.Tensor:
+        """In-place sum of ``tensor`` over all ranks with the peer-memory kernels (no library collective).
+
+        Every rank must call this with the same shape, in the same order, on its current stream.  Small inputs take one
+        pass (stage, signal, every rank sums all peers' copies); larger ones take two (each rank sums its slice of all
+        peers' copies, then gathers the reduced slices).  With ``use_multimem`` the sums are done inside the switch.
+        Sums are formed in fp32 in rank order, so every rank obtains bit-identical results."""
+
+        if self.world == 1 or tensor.numel() == 0:
+            return tensor
+        if not tensor.is_cuda:
+            raise ValueError("PeerCollectives.all_reduce_ needs a CUDA tensor")
+        self._allreduce_buffers()
+        flat = tensor.reshape(-1) if tensor.is_contiguous() else tensor.contiguous().view(-1)
+        work = flat if flat.dtype == torch.float32 else flat.float()
+        cap = self.allreduce_capacity
+        for lo in range(0, work.numel(), cap):
+            self._allreduce_pass(work[lo:lo + cap])
+        if work is not flat:
+            flat.copy_(work)
+        if flat.data_ptr() != tensor.data_ptr():
+            tensor.copy_(flat.view(tensor.shape))
+        return tensor
+
+    def _allreduce_pass(self, part: torch.Tensor) -> None:
+        n = part.numel()
+        quantum = 4 * self.world
+        padded = -(-n // quantum) * quantum
+        self._ar_calls += 1
+        call = self._ar_calls
+        half = (call & 1) * self.allreduce_capacity
+        stage = self._ar_stage.tensor[half:half + padded]
+        stage[:n].copy_(part)
+        if padded > n:
+            stage[n:].zero_()
+        stage_ptrs = [p + half * 4 for p in self._ar_stage.peer_ptrs]
+        mc = self._ar_stage.multicast_ptr + half * 4 if self._ar_stage.multicast_ptr else 0
+        ch = self.CH_ALLREDUCE
+        self.ext.comm_signal(self.flags.peer_ptrs, ch, self.rank, 2 * call - 1, stage)            # my copy is staged
+        if padded * 4 <= self.ALLREDUCE_ONE_SHOT_BYTES:
+            out = self._ar_result[:padded]
+            self.ext.comm_reduce_scatter(out, stage_ptrs, mc, 0, 1.0, None, self.flags.tensor, ch, 2 * call - 1,
+                                         self.timeout_ms, self.status, self.max_ctas)
+            # Alternating halves make the next call's staging safe: a peer signals call c + 1 only after its reads of call c.
+            self.ext.comm_signal(self.flags.peer_ptrs, ch, self.rank, 2 * call, stage)
+        else:
+            per = padded // self.world
+            mine = self._ar_part.tensor[:per]
+            self.ext.comm_reduce_scatter(mine, stage_ptrs, mc, self.rank * per, 1.0, None, self.flags.tensor, ch, 2 * call - 1,
+                                         self.timeout_ms, self.status, self.max_ctas)
+            self.ext.comm_signal(self.flags.peer_ptrs, ch, self.rank, 2 * call, stage)             # my slice is reduced
+            out = self._ar_result[:padded]
+            self.ext.comm_allgather(out, self._ar_part.peer_ptrs, per * 4, self.flags.tensor, ch, 2 * call, self.timeout_ms,
+                                    self.status, self.max_ctas)
+        part.copy_(out[:n])
 
     def check_status(self) -> None:
         word = int(self.status[0].item())

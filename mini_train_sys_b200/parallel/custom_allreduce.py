@@ -1,8 +1,11 @@
 """Public all-reduce entry point.
 
-On CUDA with the fused engine available this runs the own peer-memory all-reduce
-(parallel/comm); otherwise it falls back to ``torch.distributed.all_reduce``.  The
-reference's counterpart is a clone + NCCL call (minitrain/distributed/custom_allreduce.py:5-14).
+``allreduce_sum(tensor, comm=engine_collectives)`` returns the sum of ``tensor`` over all ranks.  With a
+``PeerCollectives`` object (the fused engine's, or one built for the purpose) and a CUDA tensor the sum is
+formed by the peer-memory kernels of ``csrc/comm.cu`` (one pass for small tensors, reduce-scatter plus
+all-gather for large ones, ``multimem`` reductions when enabled); otherwise it is ``torch.distributed.all_reduce``
+(NCCL or Gloo), and the identity without a process group.  The input is never modified.
+The reference's counterpart is a clone plus the NCCL call (minitrain/distributed/custom_allreduce.py:5-14).
 """
 
 from __future__ import annotations
@@ -13,9 +16,11 @@ import torch.distributed as dist
 
 def allreduce_sum(tensor: torch.Tensor, *, comm=None) -> torch.Tensor:
     out = tensor.clone()
-    if comm is not None and tensor.is_cuda:
+    if comm is not None and tensor.is_cuda and getattr(comm, "fused", False):
         return comm.all_reduce_(out)
-    if dist.is_available() and dist.is_initialized():
+    if comm is not None and hasattr(comm, "all_reduce_") and not getattr(comm, "fused", False):
+        return comm.all_reduce_(out)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(out, op=dist.ReduceOp.SUM)
     return out
 

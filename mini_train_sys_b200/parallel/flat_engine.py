@@ -10,21 +10,29 @@ One engine serves both strategies of this package:
   minitrain/distributed/ddp.py:54-65).
 
 Per unit and per rank the engine holds: the rank's slice of the fp32 master weights and of both
-Adam moments, a full fp32 gradient buffer (input of the reduce-scatter) and a full low-precision
-replica that the module's parameters are views of.  A training step is then
+Adam moments, a full fp32 gradient buffer (input of the reduce-scatter) and the low-precision
+weights the module's parameters are views of.  Where those low-precision weights live depends on
+the sharding strategy:
 
-    backward      parameter hooks copy each gradient into the unit's flat buffer; when a unit is
-                  complete its reduce-scatter runs on a side stream, overlapping the rest of backward
+* ``shard_grad_op`` / DDP (``reshard_after_forward=False``): a full replica per rank stays resident; the fused AdamW
+  kernel stores the new weights into every rank's replica, so there is no separate parameter all-gather.
+* ``full_shard`` (``reshard_after_forward=True``, more than one rank): only the rank's own low-precision shard is
+  resident (parameter memory ~ 1 / world).  A unit is gathered from the owners' shards over peer memory into one of two
+  staging slots one unit ahead of its use - block i + 1 while block i runs in forward, block i - 1 in backward (the
+  analogue of torch FSDP's forward / ``BACKWARD_PRE`` prefetch, minitrain/distributed/fsdp.py:128-153) - and the
+  parameters are re-pointed at the slot.  The root unit (embedding, final norm, head) has a staging buffer of its own
+  that is gathered at the start of every step.  Gradient buffers stay full-size per unit in both modes.
+
+A training step is then
+
+    backward      parameter hooks copy each gradient into the unit's flat buffer (or the operator writes it there);
+                  when a unit is complete its reduce-scatter runs on a side stream, overlapping the rest of backward
     optimizer     one cross-rank sum gives the global gradient norm and the clip coefficient on the
-                  device (no host synchronisation); a fused AdamW kernel updates the local slice and
-                  stores the new low-precision weights into every rank's replica, so there is no
-                  separate parameter all-gather
+                  device (no host synchronisation); ONE fused AdamW launch walks a table of all shard segments,
+                  updates the fp32 state and stores the new low-precision weights (into the replicas or the shard)
 
 ``collectives`` decides how the cross-rank parts run: ``PeerCollectives`` (own kernels over NVLink
 peer memory) or ``TorchCollectives`` (NCCL / Gloo / single rank).  Optimizer state is always sharded.
-
-Memory note: replicas stay resident between steps (ZeRO-2-style for ``full_shard`` as well); for the
-model sizes shipped here a full bf16 replica is below 1.1 GB on a 180 GB device.
 """
 
 from __future__ import annotations
@@ -72,6 +80,8 @@ class Unit:
     world: int = 1                  # number of ranks sharing this unit (1 for local units)
     rank: int = 0
     segments: list[tuple[int, int, bool]] = field(default_factory=list)   # (lo, hi, decay) inside the local shard
+    staged: bool = False            # parameters live in a staging slot only while the unit is in use (full_shard)
+    reported: set = field(default_factory=set)   # offsets of the slots whose gradient arrived this step
 
 
 def _round_up(n: int, m: int) -> int:
@@ -126,7 +136,7 @@ class FlatDataParallel(nn.Module):
     def __init__(self, module: nn.Module, *, mode: str = "shard", comm: Any = None, bucket_cap_mb: int = 25,
                  reshard_after_forward: bool = True, per_block_units: bool = True,
                  activation_checkpointing: bool = False, collectives: Any = None,
-                 local_params: list[str] | None = None) -> None:
+                 local_params: list[str] | None = None, stage_single_rank: bool = False) -> None:
         super().__init__()
         if mode not in ("shard", "replicate"):
             raise ValueError("mode must be 'shard' or 'replicate'")
@@ -146,12 +156,18 @@ class FlatDataParallel(nn.Module):
             want_fused = self.device.type == "cuda" and engine in ("auto", "fused") and self.param_dtype == torch.bfloat16
             if want_fused:
                 collectives = PeerCollectives(self.device, max_units=len(layout),
-                                              wait_timeout_ms=getattr(comm, "wait_timeout_ms", 2000),
+                                              wait_timeout_ms=getattr(comm, "wait_timeout_ms", 20000),
                                               use_multimem=getattr(comm, "use_multimem", False))
             else:
                 collectives = TorchCollectives(self.device)
         self.coll = collectives
-        self.step_count = 0
+        self.step_count = 0      # optimizer steps taken (restored from checkpoints; feeds the bias corrections)
+        self.comm_epoch = 0      # sequence number of the peer flags: only ever grows, never restored, so that a flag left
+                                 # by a later step can not satisfy a wait after an older checkpoint is loaded
+        # full_shard: only the own low-precision shard is resident; units are gathered into staging slots around their use
+        self.staged = (mode == "shard" and reshard_after_forward and per_block_units
+                       and (self.world > 1 or stage_single_rank))
+        self.prefetch = int(getattr(comm, "prefetch_units", 1)) > 0
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.clip_coef = torch.ones(1, dtype=torch.float32, device=self.device)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -159,8 +175,10 @@ class FlatDataParallel(nn.Module):
         self._slot_of: dict[nn.Parameter, tuple[Unit, ParamSlot]] = {}
         for index, (name, params) in enumerate(layout):
             self.units.append(self._build_unit(index, name, params))
+        self._adamw_table = None
+        self._setup_staging()
         for unit in self.units:
-            self.coll.refresh_replicas(unit, 0)
+            self._refresh_unit(unit)
         if activation_checkpointing:
             self._enable_activation_checkpointing()
 
@@ -186,8 +204,9 @@ class FlatDataParallel(nn.Module):
         unit.exp_avg_sq = torch.zeros(unit.shard_numel, dtype=f32, device=dev)
         unit.grad_shard = torch.zeros(unit.shard_numel, dtype=f32, device=dev)
         shared = not unit.local
+        unit.staged = self.staged and not unit.local
         unit.grad_full = self.coll.alloc(unit.total, f32, shared=shared)
-        unit.gathered = self.coll.alloc(unit.total, self.param_dtype, shared=shared)
+        unit.gathered = None if unit.staged else self.coll.alloc(unit.total, self.param_dtype, shared=shared)
         unit.low_shard = self.coll.alloc(unit.shard_numel, self.param_dtype, shared=shared)
         unit.sumsq = self.sumsq
         # weight-decay segments: intersections of the parameters with the local shard
@@ -197,7 +216,8 @@ class FlatDataParallel(nn.Module):
                 unit.segments.append((a - lo, b - lo, s.decay))
         unit.segments = _merge_segments(unit.segments, unit.shard_numel)
         for s in slots:
-            s.param.data = unit.gathered.tensor[s.offset:s.offset + s.numel].view(s.shape)
+            if not unit.staged:
+                s.param.data = unit.gathered.tensor[s.offset:s.offset + s.numel].view(s.shape)
             self._slot_of[s.param] = (unit, s)
             s.param.register_post_accumulate_grad_hook(self._on_grad)
             if self._sink_ok(s):
@@ -217,11 +237,17 @@ class FlatDataParallel(nn.Module):
             return name.endswith(("attn_norm.weight", "ffn_norm.weight"))
         return name.endswith(("qkv.weight", "out.weight", "gate.weight", "up.weight", "down.weight", "gate_up_proj", "down_proj"))
 
-    def _on_sunk_grad(self, param: nn.Parameter) -> None:
-        unit, _ = self._slot_of[param]
+    def _arrived(self, unit: Unit, slot: ParamSlot) -> None:
+        if slot.offset in unit.reported:
+            raise RuntimeError(f"parameter {slot.name!r} received a second gradient before optimizer.step(): the flat engine "
+                               "supports one backward pass per step (no gradient accumulation)")
+        unit.reported.add(slot.offset)
         unit.pending -= 1
         if unit.pending == 0:
-            self.coll.reduce_scatter(unit, self.step_count + 1)
+            self.coll.reduce_scatter(unit, self.comm_epoch + 1)
+
+    def _on_sunk_grad(self, param: nn.Parameter) -> None:
+        self._arrived(*self._slot_of[param])
 
     def _enable_activation_checkpointing(self) -> None:
         from torch.utils.checkpoint import checkpoint
@@ -235,6 +261,8 @@ class FlatDataParallel(nn.Module):
 
     # ---- forward / backward -------------------------------------------------------------------------
     def forward(self, *args, **kwargs):
+        if self.staged:
+            self._begin_step()
         return self.module(*args, **kwargs)
 
     def unit_count(self) -> int:
@@ -248,24 +276,163 @@ class FlatDataParallel(nn.Module):
         dst = unit.grad_full.tensor[slot.offset:slot.offset + slot.numel].view(slot.shape)
         dst.copy_(param.grad)
         param.grad = None
-        unit.pending -= 1
-        if unit.pending == 0:
-            self.coll.reduce_scatter(unit, self.step_count + 1)
+        self._arrived(unit, slot)
 
     def _flush_incomplete_units(self) -> None:
-        """Units with parameters that received no gradient this step still have to take part."""
+        """Units with parameters that received no gradient this step still have to take part: the ranges of exactly those
+        parameters (padding included) are zeroed, so that last step's values are not reduced and applied again."""
 
         for unit in self.units:
             if unit.pending > 0:
                 for s in unit.slots:
                     if s.param.grad is not None:
                         self._on_grad(s.param)
-                if unit.pending > 0:   # truly unused parameters contribute zeros
-                    done = len(unit.slots) - unit.pending
-                    if done == 0:
-                        unit.grad_full.tensor.zero_()
+                if unit.pending > 0:
+                    for s in unit.slots:
+                        if s.offset not in unit.reported:
+                            unit.grad_full.tensor[s.offset:s.offset + _round_up(s.numel, ALIGN)].zero_()
                     unit.pending = 0
-                    self.coll.reduce_scatter(unit, self.step_count + 1)
+                    self.coll.reduce_scatter(unit, self.comm_epoch + 1)
+
+    # ---- staging of sharded parameters (full_shard) --------------------------------------------------------------
+    def _setup_staging(self) -> None:
+        self._block_units: dict[int, Unit] = {}
+        self._root_unit: Unit | None = None
+        self._slots: list[torch.Tensor] = []
+        self._slot_unit: list[int | None] = []
+        self._slot_event: list[Any] = []
+        self._root_stage: torch.Tensor | None = None
+        self._root_fresh = False
+        if not self.staged:
+            return
+        blocks = [u for u in self.units if u.staged and u.name != "root"]
+        for u in self.units:
+            if u.staged and u.name == "root":
+                self._root_unit = u
+                self._root_stage = torch.zeros(u.total, dtype=self.param_dtype, device=self.device)
+                self._point(u, self._root_stage)
+        if blocks:
+            widest = max(u.total for u in blocks)
+            self._slots = [torch.zeros(widest, dtype=self.param_dtype, device=self.device) for _ in range(2)]
+            self._slot_unit = [None, None]
+            self._slot_event = [None, None]
+        order = {u.index: i for i, u in enumerate(blocks)}
+        self._block_order = blocks
+        for u in blocks:
+            module = self.module.get_submodule(u.name)
+            pos = order[u.index]
+            nxt = blocks[pos + 1] if pos + 1 < len(blocks) else None
+            prv = blocks[pos - 1] if pos > 0 else None
+            module.register_forward_pre_hook(lambda _m, _a, u=u, nxt=nxt: self._use(u, nxt))
+            module.register_forward_hook(lambda _m, _a, out, u=u, prv=prv: self._watch_output(out, u, prv))
+
+    def _watch_output(self, out, unit: Unit, prefetch: Unit | None) -> None:
+        """Backward of a block starts when the gradient of its hidden-state output arrives: a hook on that tensor brings the
+        unit's weights back before any of the block's backward nodes runs (the block returns a record, not a tensor, so
+        module-level backward hooks do not apply).  Every other backward node of the block that touches a weight depends,
+        directly or through the routed weights, on this gradient."""
+
+        hidden = getattr(out, "hidden_states", None)
+        if hidden is None:
+            hidden = out[0] if isinstance(out, (tuple, list)) else out
+        if isinstance(hidden, torch.Tensor) and hidden.requires_grad:
+            hidden.register_hook(lambda _g, u=unit, p=prefetch: self._use(u, p))
+
+    def _point(self, unit: Unit, buffer: torch.Tensor) -> None:
+        for s in unit.slots:
+            s.param.data = buffer[s.offset:s.offset + s.numel].view(s.shape)
+
+    def _gather_into(self, unit: Unit, dst: torch.Tensor):
+        """All-gather of ``unit``'s low-precision shards into ``dst`` on the communication stream; returns the event that marks
+        its end.  Every kernel already queued on the compute stream finishes first (it may still read the slot's old content)."""
+
+        stream = getattr(self.coll, "comm_stream", None)
+        if stream is None:      # CPU / library twin: gather in line
+            self.coll.gather_unit(unit, dst)
+            return None
+        before = torch.cuda.Event()
+        before.record()
+        with torch.cuda.stream(stream):
+            stream.wait_event(before)
+            self.coll.gather_unit(unit, dst)
+            done = torch.cuda.Event()
+            done.record()
+        return done
+
+    def _use(self, unit: Unit, prefetch: Unit | None) -> None:
+        """Called right before ``unit``'s block runs (forward, recomputation or backward): make its weights resident, then start
+        gathering the unit that runs next into the other slot."""
+
+        slot = self._slot_unit.index(unit.index) if unit.index in self._slot_unit else None
+        if slot is None:
+            slot = self._free_slot(keep=None)
+            self._slot_event[slot] = self._gather_into(unit, self._slots[slot][:unit.total])
+            self._slot_unit[slot] = unit.index
+        if self._slot_event[slot] is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._slot_event[slot])
+            self._slot_event[slot] = None
+        self._point(unit, self._slots[slot])
+        if self.prefetch and prefetch is not None and prefetch.index not in self._slot_unit:
+            other = self._free_slot(keep=slot)
+            self._slot_event[other] = self._gather_into(prefetch, self._slots[other][:prefetch.total])
+            self._slot_unit[other] = prefetch.index
+
+    def _free_slot(self, keep: int | None) -> int:
+        for i, held in enumerate(self._slot_unit):
+            if held is None and i != keep:
+                return i
+        return 1 - keep if keep is not None else 0
+
+    def _begin_step(self) -> None:
+        """Start of a forward pass in staged mode: the root unit (needed first and last) and the first block."""
+
+        if self._root_unit is not None and not self._root_fresh:
+            ev = self._gather_into(self._root_unit, self._root_stage)
+            if ev is not None:
+                torch.cuda.current_stream(self.device).wait_event(ev)
+            self._root_fresh = True
+        if self._block_order and self._block_order[0].index not in self._slot_unit:
+            first = self._block_order[0]
+            slot = self._free_slot(keep=None)
+            self._slot_event[slot] = self._gather_into(first, self._slots[slot][:first.total])
+            self._slot_unit[slot] = first.index
+
+    def _after_update(self) -> None:
+        """The shards changed: nothing that sits in a staging buffer is current any more."""
+
+        if self.staged:
+            self._slot_unit = [None] * len(self._slot_unit)
+            self._slot_event = [None] * len(self._slot_event)
+            self._root_fresh = False
+
+    def _refresh_unit(self, unit: Unit) -> None:
+        """Start-up and checkpoint restore: rebuild the low-precision weights of ``unit`` from the fp32 shards."""
+
+        if unit.staged:
+            self.coll.refresh_shard(unit)
+            self._after_update()
+        else:
+            self.coll.refresh_replicas(unit, 0)
+
+    def parameter_bytes(self) -> dict[str, int]:
+        """Bytes this rank holds for parameters: ``resident`` stays allocated between steps (fp32 master, both moments and the
+        low-precision weights), ``staging`` is the fixed pool that units pass through under ``full_shard``."""
+
+        low = torch.empty(0, dtype=self.param_dtype).element_size()
+        resident = staging = 0
+        for u in self.units:
+            resident += 3 * 4 * u.shard_numel + low * u.shard_numel
+            if u.gathered is not None:
+                resident += low * u.total
+        staging += sum(t.numel() * low for t in self._slots)
+        if self._root_stage is not None:
+            staging += self._root_stage.numel() * low
+        return {"resident": resident, "staging": staging}
+
+    def check_status(self) -> None:
+        """Raise if a device-side wait of this engine's collectives ran out (synchronises the device)."""
+
+        self.coll.check_status()
 
     # ---- optimizer ------------------------------------------------------------------------------------
     def build_sharded_optimizer(self, cfg: OptimizerConfig) -> "ShardedAdamW":
@@ -353,7 +520,7 @@ class FlatDataParallel(nn.Module):
         if optimizer is not None:
             optimizer.adopt_groups(optim_state.get("param_groups", []))
         for unit in self.units:
-            self.coll.refresh_replicas(unit, 0)
+            self._refresh_unit(unit)
 
     def full_state_dict(self) -> dict[str, torch.Tensor]:
         """Consolidated fp32 CPU weights under the plain parameter names (tied weights appear under both names)."""
@@ -420,24 +587,56 @@ class ShardedAdamW(torch.optim.Optimizer):
             for s in unit.slots:
                 s.param.grad = None
 
+    def _segment_table(self):
+        """Device table of every (unit, weight-decay run) of the local shards, built once: the update is one launch."""
+
+        eng = self.engine
+        if eng._adamw_table is None:
+            rows = []
+            low_bf16 = eng.param_dtype == torch.bfloat16
+            for unit in eng.units:
+                for lo, hi, decay in unit.segments:
+                    if unit.staged:
+                        dests, offset = [unit.low_shard.tensor.data_ptr()], lo
+                    else:
+                        dests, offset = list(unit.gathered.peer_ptrs), unit.rank * unit.shard_numel + lo
+                    rows.append([unit.master[lo:hi].data_ptr(), unit.grad_shard[lo:hi].data_ptr(), unit.exp_avg[lo:hi].data_ptr(),
+                                 unit.exp_avg_sq[lo:hi].data_ptr(), hi - lo, offset, 0 if decay else 1, int(low_bf16), *dests])
+            table, chunks = eng.coll.ext.comm_adamw_table(rows, eng.sumsq)
+            eng._adamw_table = (table, len(rows), int(chunks))
+        return eng._adamw_table
+
     @torch.no_grad()
     def step(self, closure=None):
         eng = self.engine
         eng._flush_incomplete_units()
-        epoch = eng.step_count + 1
+        epoch = eng.comm_epoch + 1
+        step = eng.step_count + 1
         eng.coll.norm_and_clip(eng.sumsq, self._clip, epoch, eng.clip_coef, eng.grad_norm)
         decay_group, plain_group = self.param_groups
-        for unit in eng.units:
-            for lo, hi, decay in unit.segments:
-                g = decay_group if decay else plain_group
-                eng.coll.adamw_update(unit, (lo, hi), lr=float(g["lr"]), beta1=g["betas"][0], beta2=g["betas"][1],
-                                      eps=g["eps"], weight_decay=float(g["weight_decay"]), step=epoch, coef=eng.clip_coef)
-            if not eng.coll.fused:
-                eng.coll.refresh_replicas(unit, epoch)
-            unit.pending = len(unit.slots)
+        if eng.coll.fused and decay_group["betas"] == plain_group["betas"] and decay_group["eps"] == plain_group["eps"]:
+            table, n_rows, chunks = self._segment_table()
+            eng.coll.adamw_update_table(table, n_rows, chunks, lr=(float(decay_group["lr"]), float(plain_group["lr"])),
+                                        weight_decay=(float(decay_group["weight_decay"]), float(plain_group["weight_decay"])),
+                                        betas=decay_group["betas"], eps=decay_group["eps"], step=step, coef=eng.clip_coef)
+            for unit in eng.units:
+                unit.pending = len(unit.slots)
+                unit.reported.clear()
+        else:
+            for unit in eng.units:
+                for lo, hi, decay in unit.segments:
+                    g = decay_group if decay else plain_group
+                    eng.coll.adamw_update(unit, (lo, hi), lr=float(g["lr"]), beta1=g["betas"][0], beta2=g["betas"][1],
+                                          eps=g["eps"], weight_decay=float(g["weight_decay"]), step=step, coef=eng.clip_coef)
+                if not eng.coll.fused:
+                    eng._refresh_unit(unit)
+                unit.pending = len(unit.slots)
+                unit.reported.clear()
         eng.coll.refresh_done(epoch)
+        eng._after_update()
         eng.sumsq.zero_()
-        eng.step_count = epoch
+        eng.comm_epoch = epoch
+        eng.step_count = step
         return None
 
     # ---- checkpoint helpers ----

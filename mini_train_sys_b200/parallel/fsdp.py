@@ -4,10 +4,12 @@
   (minitrain/distributed/fsdp.py:25-160): one unit per ``TransformerBlock`` plus the root,
   bf16 parameters / fp32 reduction, backward prefetch, optional CPU offload and
   non-reentrant activation checkpointing.  This is the measured baseline.
-* engine ``fused`` shards flat fp32 master weights per unit in peer-mapped memory, gathers
-  bf16 parameters with the own all-gather kernel one unit ahead of use, and reduces
-  gradients with the own reduce-scatter kernel fused with the sharded AdamW update
-  (parallel/flat_engine.py).
+* engine ``fused`` (parallel/flat_engine.py) shards flat fp32 master weights and Adam state per unit and reduces
+  gradients with the own reduce-scatter kernel, whose result feeds a sharded AdamW kernel.  ``full_shard`` keeps only
+  the rank's bf16 shard resident and pulls each unit from the owners' shards over peer memory into a two-slot staging
+  buffer one unit ahead of its use (forward and backward); ``shard_grad_op`` keeps a bf16 replica per rank that the
+  AdamW kernel refreshes on every rank by peer stores, so no gather runs during the step.  Options the fused engine
+  does not implement (CPU offload, ``no_shard`` / ``hybrid_shard``, fp16 loss scaling) are refused, not ignored.
 """
 
 from __future__ import annotations
@@ -97,6 +99,16 @@ class FSDPStrategy(ProcessGroupMixin):
         if self.resolved_engine() == "fused":
             from mini_train_sys_b200.parallel.flat_engine import FlatDataParallel
 
+            unsupported = []
+            if self.cpu_offload:
+                unsupported.append("cpu_offload")
+            if self.sharding_strategy not in ("full_shard", "shard_grad_op"):
+                unsupported.append(f"sharding_strategy={self.sharding_strategy}")
+            if self.precision == "fp16":
+                unsupported.append("precision=fp16 (loss scaling)")
+            if unsupported:
+                raise ValueError("parallel.comm.engine=fused does not implement: " + ", ".join(unsupported)
+                                 + "; select parallel.comm.engine=nccl for these options")
             return FlatDataParallel(
                 model, mode="shard", comm=self.comm, reshard_after_forward=self.sharding_strategy == "full_shard",
                 per_block_units=self.auto_wrap_policy_name == "transformer_block",

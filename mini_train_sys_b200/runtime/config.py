@@ -82,11 +82,14 @@ class CommConfig:
     ``engine``: ``fused`` = own peer-memory kernels (all-gather, reduce-scatter/all-reduce
     fused with the AdamW update, expert all-to-all); ``nccl`` = stock torch DDP/FSDP (the
     baseline); ``auto`` = fused on CUDA with >1 rank and peer access, else nccl/gloo.
-    ``wait_timeout_ms`` bounds every device-side wait on a peer flag.
+    ``wait_timeout_ms`` bounds every device-side wait on a peer flag; a wait that runs out sets the device's
+    status word, the optimizer kernel then leaves the weights untouched and the runner raises at its next
+    log or checkpoint boundary.  The default leaves room for a peer that logs, checkpoints or collects garbage.
+    ``prefetch_units``: under ``full_shard``, how many units ahead of the running one are gathered (0 or 1).
     """
 
     engine: str = "auto"
-    wait_timeout_ms: int = 2000
+    wait_timeout_ms: int = 20000
     prefetch_units: int = 1
     use_multimem: bool = False
     health_check: bool = False            # host-side heartbeats through the process-group store, checked before every step
@@ -95,7 +98,7 @@ class CommConfig:
     def __post_init__(self) -> None:
         _require(self.engine in ("auto", "fused", "nccl"), "parallel.comm.engine must be auto, fused, or nccl")
         _require(self.wait_timeout_ms > 0, "parallel.comm.wait_timeout_ms must be positive")
-        _require(self.prefetch_units >= 0, "parallel.comm.prefetch_units must be non-negative")
+        _require(self.prefetch_units in (0, 1), "parallel.comm.prefetch_units must be 0 or 1")
         _require(self.health_max_age_seconds > 0, "parallel.comm.health_max_age_seconds must be positive")
 
 

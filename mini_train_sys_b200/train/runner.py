@@ -123,7 +123,25 @@ class TrainingRunner:
         self.logger.log_event(event)
 
     # ---- checkpoints -------------------------------------------------------------
+    def _check_device_status(self) -> None:
+        """Raise when a kernel of this process gave up on a bounded wait (a peer that stalled or left): gradients of that
+        step were incomplete, the optimizer kernel skipped the update, and going on - or saving - would hide it.  Called where
+        the device is synchronised anyway: at every log boundary and before every checkpoint."""
+
+        if self.device.type != "cuda":
+            return
+        import sys
+
+        if "_mts_b200_ext" in sys.modules:      # only when the native extension is in use
+            from mini_train_sys_b200.ops.native_backend import check_kernel_status
+
+            check_kernel_status(self.device)
+        checker = getattr(self.trainer.model, "check_status", None)
+        if callable(checker):
+            checker()
+
     def _save(self, *, epoch: int, force_model_export: bool = False) -> Path:
+        self._check_device_status()
         ck, st = self.cfg.checkpoint, self.trainer.state
         target = checkpoint_path(ck.directory, self.cfg.run.name, epoch=epoch, step=st.step)
         every = ck.export_model_every_epochs
@@ -202,6 +220,7 @@ class TrainingRunner:
                         or batch_index == n_batches or hit_limit):
                     if on_cuda:
                         torch.cuda.synchronize(self.device)
+                        self._check_device_status()
                     self._emit_train_event(iv, epoch=epoch, batch_index=batch_index, batches_in_epoch=n_batches,
                                            total_steps=total_steps, tokens_goal=tokens_goal, session=session)
                     iv = self._new_interval()

@@ -7,24 +7,25 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _model(ops_name="native"):
+def _model(ops_name="native", layers=2):
     from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
 
-    cfg = ModelConfig(vocab_size=1000, seq_len=128, n_layers=2, n_heads=4, hidden_size=256, intermediate_size=256,
+    cfg = ModelConfig(vocab_size=1000, seq_len=128, n_layers=layers, n_heads=4, hidden_size=256, intermediate_size=256,
                       ffn_type="moe", num_experts=4, experts_per_token=2, tie_word_embeddings=True)
     torch.manual_seed(0)
     return MiniTransformer(cfg, get_ops_backend(ops_name), activation_dtype=torch.bfloat16).to(DEV)
 
 
-def _train(engine_collectives, steps=4):
+def _train(engine_collectives, steps=4, layers=2, **engine_kwargs):
     from mini_train_sys_b200.parallel.flat_engine import FlatDataParallel
     from mini_train_sys_b200.runtime.config import OptimizerConfig
     from mini_train_sys_b200.train.optim import build_optimizer
     from mini_train_sys_b200.train.trainer import Trainer
 
-    eng = FlatDataParallel(_model(), mode="shard", collectives=engine_collectives)
-    tr = Trainer(eng, build_optimizer(eng, cfg=OptimizerConfig(lr=1e-3)), torch.device(DEV), use_fused_loss=True,
-                 precision="bf16", grad_clip_norm=1.0)
+    eng = FlatDataParallel(_model(layers=layers), mode="shard", collectives=engine_collectives, **engine_kwargs)
+    opt = build_optimizer(eng, cfg=OptimizerConfig(lr=1e-3))
+    tr = Trainer(eng, opt, torch.device(DEV), use_fused_loss=True, precision="bf16", grad_clip_norm=1.0)
+    eng._test_optimizer, eng._test_trainer = opt, tr
     g = torch.Generator().manual_seed(3)
     losses, norms = [], []
     for _ in range(steps):
@@ -51,6 +52,54 @@ def test_fused_engine_matches_library_collectives():
         diff = (fa[name] - fb[name]).abs()
         assert float(diff.max()) <= 8.5e-3 and float(diff.mean()) < 3e-4, (name, float(diff.max()), float(diff.mean()))
     check_kernel_status()
+
+
+def test_staged_parameters_match_resident_replicas():
+    """full_shard residency with a world of one: five blocks pass through two staging slots in forward and backward; the
+    gathers, the re-pointed parameters and the shard-only AdamW push must reproduce the run that keeps a full replica."""
+
+    from mini_train_sys_b200.ops.native_backend import check_kernel_status
+    from mini_train_sys_b200.parallel.comm import PeerCollectives
+
+    dev = torch.device(DEV, 0)
+    eng_a, loss_a, norm_a = _train(PeerCollectives(dev, max_units=6), layers=5, stage_single_rank=True)
+    eng_b, loss_b, norm_b = _train(PeerCollectives(dev, max_units=6), layers=5)
+    assert eng_a.staged and not eng_b.staged and all(u.gathered is None for u in eng_a.units)
+    assert loss_a == pytest.approx(loss_b, abs=2e-2)
+    assert norm_a == pytest.approx(norm_b, rel=5e-2)
+    assert loss_a[0] == pytest.approx(loss_b[0], abs=1e-4)          # before any update the two runs compute the same thing
+    sizes = eng_a.parameter_bytes()
+    assert sizes["resident"] == sum(14 * u.shard_numel for u in eng_a.units) and sizes["staging"] > 0
+    check_kernel_status()
+
+
+def test_a_wait_that_runs_out_blocks_the_update_and_is_reported():
+    """A peer flag that never arrives: the wait gives up, the status word is set, the AdamW launch of that step leaves the
+    weights and both moments bit-identical, and the engine's status check raises.  The word is cleared afterwards."""
+
+    from mini_train_sys_b200.ops.native_backend import ext
+    from mini_train_sys_b200.parallel.comm import PeerCollectives
+
+    dev = torch.device(DEV, 0)
+    eng, _, _ = _train(PeerCollectives(dev, max_units=3), steps=1)
+    opt = eng._test_optimizer
+    tr = eng._test_trainer
+    before = [(u.master.clone(), u.exp_avg.clone(), u.exp_avg_sq.clone()) for u in eng.units]
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+    ext().comm_wait(flags, 0, 2, 9, 20.0, eng.coll.status)      # waits 20 ms for two peers nobody plays
+    t = torch.randint(0, 1000, (4, 129))
+    tr.train_step({"input_ids": t[:, :-1], "targets": t[:, 1:]})
+    torch.cuda.synchronize()
+    for u, (p, m, v) in zip(eng.units, before):
+        assert torch.equal(u.master, p) and torch.equal(u.exp_avg, m) and torch.equal(u.exp_avg_sq, v)
+    with pytest.raises(RuntimeError, match="status 1"):
+        eng.check_status()
+    eng.coll.status.zero_()
+    tr.train_step({"input_ids": t[:, :-1], "targets": t[:, 1:]})
+    torch.cuda.synchronize()
+    assert not torch.equal(eng.units[0].master, before[0][0])
+    eng.check_status()
+    del opt
 
 
 def test_wait_on_a_flag_nobody_sets_times_out_and_reports():

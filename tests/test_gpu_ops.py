@@ -288,7 +288,7 @@ def test_moe_plan(nb, mode):
 
 
 @pytest.mark.parametrize("mode", ["uniform", "one_expert", "empty"])
-@pytest.mark.parametrize("tokens,hidden,inter,experts", [(1000, 128, 128, 4), (2048, 768, 1024, 8)])
+@pytest.mark.parametrize("tokens,hidden,inter,experts", [(1000, 128, 128, 4), (2048, 768, 1024, 8), (12288, 768, 1024, 8)])
 def test_fused_moe(ops, mode, tokens, hidden, inter, experts):
     torch.manual_seed(11)
     k = 2
@@ -309,6 +309,32 @@ def test_fused_moe(ops, mode, tokens, hidden, inter, experts):
     assert_close(gdn, rdn, 3e-2, "d down")
     assert_close(gw, rw, 3e-2, "d route weights")
     assert ops.dispatch["fused_moe:native"] > 0
+
+
+@pytest.mark.parametrize("splits", [2, 3, 5])
+def test_grouped_k_gemm_with_split_groups(nb, splits):
+    """Per-expert weight gradients with every expert's rows cut into parts that add into the expert's output."""
+
+    torch.manual_seed(21)
+    groups, m, n = 4, 768, 512
+    sizes = [1280, 256, 0, 2048]                 # rows per group (multiples of 256, one of them empty)
+    bounds = torch.tensor([0, *torch.tensor(sizes).cumsum(0).tolist()], dtype=torch.int32, device=DEV)
+    rows = int(bounds[-1])
+    a = torch.randn(rows, m, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(rows, n, device=DEV, dtype=torch.bfloat16)
+    canary = 7.0
+    buf = torch.full((groups * m * n + 2 * 1024,), canary, device=DEV)
+    out = buf[1024:1024 + groups * m * n].view(groups, m, n)
+    out.zero_()
+    nb._gemm(a, b, out, m, n, 0, a_mn=True, b_mn=True, mode=nb.GEMM_GROUPED_K, group_rows=bounds, num_groups=groups,
+             out_group_stride=m * n, ldo=n, k_splits=splits, atomic_out=True)
+    torch.cuda.synchronize()
+    assert bool((buf[:1024] == canary).all()) and bool((buf[-1024:] == canary).all()), "wrote outside the output"
+    for gi in range(groups):
+        lo, hi = int(bounds[gi]), int(bounds[gi + 1])
+        want = a[lo:hi].float().t() @ b[lo:hi].float()
+        assert_close(out[gi], want, 5e-3, f"group {gi}", floor=1e-3)
+    nb.check_kernel_status()
 
 
 def test_adamw_matches_torch(nb):
@@ -417,11 +443,14 @@ def test_attention_capability_contract():
 
 
 @pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
-def test_router_logits_split_gemm(ops, w_dtype):
+@pytest.mark.parametrize("tokens,experts,hidden", [(3000, 8, 768), (777, 4, 256), (1025, 16, 384), (513, 6, 768)])
+def test_router_logits_split_gemm(ops, w_dtype, tokens, experts, hidden):
+    """Router projection: the skinny fp32 kernels for 4 / 8 / 16 experts, the split-bf16 tensor-core GEMM otherwise."""
+
     torch.manual_seed(15)
-    x = torch.randn(3000, 768, device=DEV, dtype=torch.bfloat16, requires_grad=True)
-    w = (0.02 * torch.randn(8, 768, device=DEV)).to(w_dtype).requires_grad_()
-    g = torch.randn(3000, 8, device=DEV)
+    x = torch.randn(tokens, hidden, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (0.02 * torch.randn(experts, hidden, device=DEV)).to(w_dtype).requires_grad_()
+    g = torch.randn(tokens, experts, device=DEV)
     logits = ops.router_logits(x, w)
     gx, gw = torch.autograd.grad(logits, (x, w), g)
     x64, w64 = x.detach().double().requires_grad_(), w.detach().double().requires_grad_()
