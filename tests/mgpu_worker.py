@@ -36,8 +36,9 @@ def main() -> None:
     shard = n // world
     out = torch.empty(shard, device=dev)
     sumsq = torch.zeros(1, device=dev)
-    e.comm_signal(coll.flags.peer_ptrs, 2, rank, 1, out)
-    e.comm_reduce_scatter(out, buf.peer_ptrs, buf.multicast_ptr, rank * shard, 1.0 / world, sumsq, coll.flags.tensor, 2, 1,
+    ch = coll.CH_UNIT0
+    e.comm_signal(coll.flags.peer_ptrs, ch, rank, 1, out)
+    e.comm_reduce_scatter(out, buf.peer_ptrs, buf.multicast_ptr, rank * shard, 1.0 / world, sumsq, coll.flags.tensor, ch, 1,
                           5000.0, coll.status, 32)
     torch.cuda.synchronize()
     ref = want[rank * shard:(rank + 1) * shard] / world
@@ -46,31 +47,71 @@ def main() -> None:
     if rank == 0:
         print(f"PASS reduce_scatter multimem={bool(buf.multicast_ptr)}", flush=True)
 
-    # ---- engine: own collectives against library collectives ----
-    cfg = ModelConfig(vocab_size=1000, seq_len=128, n_layers=2, n_heads=4, hidden_size=256, intermediate_size=512,
+    # ---- public all-reduce (one pass for small tensors, reduce-scatter + all-gather for large) against NCCL ----
+    from mini_train_sys_b200.parallel.custom_allreduce import allreduce_sum
+
+    for numel, dtype in ((1000, torch.float32), (65536 + 3, torch.float32), (3_000_001, torch.float32), (40_000, torch.bfloat16)):
+        torch.manual_seed(200 + rank)
+        src = torch.randn(numel, device=dev).to(dtype)
+        keep = src.clone()
+        want = src.float().clone()
+        dist.all_reduce(want)
+        for _ in range(3):          # back-to-back calls reuse the staging halves
+            got = allreduce_sum(src, comm=coll)
+        torch.cuda.synchronize()
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        assert torch.equal(src, keep), "the input was modified"
+        assert torch.allclose(got.float(), want, atol=tol * max(1.0, float(want.abs().max()))), (numel, float((got.float() - want).abs().max()))
+    coll.check_status()
+    dist.barrier()
+    if rank == 0:
+        print(f"PASS all_reduce multimem={bool(coll._ar_stage.multicast_ptr)}", flush=True)
+
+    # ---- engine: own collectives against library collectives; full_shard (staged) and shard_grad_op (resident) ----
+    cfg = ModelConfig(vocab_size=1000, seq_len=128, n_layers=4, n_heads=4, hidden_size=256, intermediate_size=512,
                       tie_word_embeddings=True)
 
-    def run(collectives):
+    def run(collectives, steps=4, **kwargs):
         torch.manual_seed(0)
         model = MiniTransformer(cfg, get_ops_backend("native"), activation_dtype=torch.bfloat16).to(dev)
-        eng = FlatDataParallel(model, mode="shard", collectives=collectives)
+        eng = FlatDataParallel(model, mode="shard", collectives=collectives, **kwargs)
         tr = Trainer(eng, build_optimizer(eng, cfg=OptimizerConfig(lr=1e-3)), dev, use_fused_loss=True, precision="bf16",
                      grad_clip_norm=1.0)
         g = torch.Generator().manual_seed(7 + rank)
         losses = []
-        for _ in range(4):
+        for _ in range(steps):
             t = torch.randint(0, 1000, (4, 129), generator=g)
             losses.append(float(tr.train_step({"input_ids": t[:, :-1], "targets": t[:, 1:]})))
-        return eng.full_state_dict(), losses, float(tr.last_metrics["grad_norm"])
+        return eng, eng.full_state_dict(), losses, float(tr.last_metrics["grad_norm"])
 
-    fa, la, na = run(PeerCollectives(dev, max_units=8, wait_timeout_ms=5000, use_multimem=use_mm))
-    fb, lb, nb = run(TorchCollectives(dev))
-    for name in fa:
-        diff = (fa[name] - fb[name]).abs()   # atomically summed weight gradients: a sign flip moves a weight by up to 2 * lr per step
-        assert float(diff.max()) <= 8.5e-3 and float(diff.mean()) < 3e-4, (name, float(diff.max()), float(diff.mean()))
-    assert abs(na - nb) <= 5e-2 * max(nb, 1e-6), (na, nb)
+    def peer():
+        return PeerCollectives(dev, max_units=8, wait_timeout_ms=5000, use_multimem=use_mm)
+
+    ea, fa, la, na = run(peer())                                   # full_shard: parameters staged
+    ec, fc, lc, nc = run(peer(), reshard_after_forward=False)      # shard_grad_op: resident replica
+    eb, fb, lb, nb = run(TorchCollectives(dev))
+    assert ea.staged and not ec.staged and eb.staged
+    for other in (fa, fc):
+        for name in other:
+            diff = (other[name] - fb[name]).abs()   # atomically summed weight gradients: a sign flip moves a weight by up to 2 * lr per step
+            assert float(diff.max()) <= 8.5e-3 and float(diff.mean()) < 3e-4, (name, float(diff.max()), float(diff.mean()))
+    assert abs(na - nb) <= 5e-2 * max(nb, 1e-6) and abs(nc - nb) <= 5e-2 * max(nb, 1e-6), (na, nc, nb)
+    # parameter residency: full_shard keeps 1 / world of every unit (fp32 master, two moments, bf16 shard = 14 bytes per element)
+    total = sum(u.total for u in ea.units)
+    assert ea.parameter_bytes()["resident"] == 14 * total // world, (ea.parameter_bytes(), total)
+    assert ec.parameter_bytes()["resident"] == 14 * total // world + 2 * total
     coll.check_status()
     dist.barrier()
+    del ea, ec, eb
+
+    # ---- 50 steps: the loss curve of the fused full_shard engine follows the library engine ----
+    _, _, long_a, _ = run(peer(), steps=50)
+    _, _, long_b, _ = run(TorchCollectives(dev), steps=50)
+    worst = max(abs(a - b) for a, b in zip(long_a, long_b))
+    assert worst < 5e-2, (worst, long_a[0], long_a[-1])     # uniform-random tokens: the loss itself stays near ln(vocab)
+    dist.barrier()
+    if rank == 0:
+        print(f"PASS fifty_steps worst_loss_gap={worst:.4f} first={long_a[0]:.3f} last={long_a[-1]:.3f}", flush=True)
 
     # ---- expert-parallel layer: own peer-memory exchange against the all_to_all_single path ----
     from mini_train_sys_b200.models.blocks import MoEFeedForward

@@ -21,9 +21,19 @@ def _launch(n: int, extra_env=None) -> str:
     return done.stdout
 
 
-def test_peer_collectives_and_engine_on_two_gpus():
-    out = _launch(min(torch.cuda.device_count(), 2))
-    assert "PASS reduce_scatter" in out and "PASS engine" in out and "PASS expert_parallel" in out
+@pytest.mark.parametrize("multimem", [False, True])
+@pytest.mark.parametrize("ranks", [2, 4, 8])
+def test_peer_collectives_and_engine(ranks, multimem):
+    """Reduce-scatter, all-reduce, the sharded engine (full_shard and shard_grad_op) and the expert exchange against their
+    library twins, on as many GPUs as the box has; ``multimem`` repeats it with the switch-side reductions."""
+
+    if torch.cuda.device_count() < ranks:
+        pytest.skip(f"needs {ranks} GPUs")
+    out = _launch(ranks, {"MTS_TEST_MULTIMEM": "1" if multimem else "0"})
+    for marker in ("PASS reduce_scatter", "PASS all_reduce", "PASS engine", "PASS fifty_steps", "PASS expert_parallel"):
+        assert marker in out, out[-2000:]
+    if multimem:
+        assert "PASS reduce_scatter multimem=True" in out, "the multicast mapping was not used"
 
 
 def test_a_rank_that_leaves_between_steps_is_noticed_on_the_host():
