@@ -42,6 +42,13 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--strategy", default=None, help="single | ddp | fsdp | ep (default: fsdp when gpus > 1)")
     ap.add_argument("--engine", default="auto", help="parallel.comm.engine for the own arm")
     ap.add_argument("--model-config", default=str(ROOT / "configs" / "synbios_moe" / "model.yaml"))
+    ap.add_argument("--sharding", default="full_shard", choices=["full_shard", "shard_grad_op"],
+                    help="parallel.fsdp.sharding_strategy (own arm, fused engine: staged parameters vs resident replica)")
+    ap.add_argument("--multimem", action="store_true", help="parallel.comm.use_multimem: gradient sums inside the switch (NVLS)")
+    ap.add_argument("--capacity-factor", type=float, default=None, help="parallel.ep.capacity_factor (strategy ep); default: no limit")
+    ap.add_argument("--seq-len", type=int, default=None, help="override the model's sequence length")
+    ap.add_argument("--comm-timing", action="store_true",
+                    help="own arm: report, per step, how long the compute stream waited in each communication phase")
     return ap.parse_args()
 
 
@@ -106,6 +113,8 @@ def run_payload(args, strategy: str) -> dict:
     import yaml
 
     model = yaml.safe_load(Path(args.model_config).read_text())["model"]
+    if getattr(args, "seq_len", None):
+        model["seq_len"] = int(args.seq_len)
     return {
         "run": {"name": "bench", "seed": 1337},
         "backend": {"ops": args.ops if args.impl == "own" else "torch"},
@@ -146,7 +155,10 @@ def assemble(args, strategy_name: str):
         from mini_train_sys_b200.train.precision import resolve_precision_policy
         from mini_train_sys_b200.train.trainer import Trainer
         from mini_train_sys_b200.utils.seed import seed_everything
-        payload["parallel"]["comm"] = {"engine": args.engine}
+        payload["parallel"]["comm"] = {"engine": args.engine, "use_multimem": bool(getattr(args, "multimem", False))}
+        payload["parallel"]["fsdp"] = {"sharding_strategy": getattr(args, "sharding", "full_shard")}
+        if getattr(args, "capacity_factor", None) is not None:
+            payload["parallel"]["ep"] = {"capacity_factor": float(args.capacity_factor)}
 
         def launches() -> int:
             from mini_train_sys_b200.ops.build import load_extension
@@ -239,8 +251,17 @@ def main() -> None:
     def step_e2e(i: int):
         return trainer.train_step(host_batches[i]).item()
 
-    total_ms, clocks, n_launch, last_loss = timed(step_device, "device")
+    # The end-to-end pass runs first: whatever still warms up after the warm-up steps (allocator growth, lazily built buffers
+    # of a wrapped engine) falls into its warm-up, and the device-resident pass that follows is steady-state for both arms.
     e2e_ms, clocks_e2e, _, last_loss_e2e = timed(step_e2e, "e2e")
+    engine_timing = getattr(trainer.model, "enable_timing", None) if args.comm_timing else None
+    if engine_timing is not None:
+        for i in range(warmup):          # the timed region below starts right after these
+            step_device(i)
+        sync_all()
+        engine_timing(True)
+    total_ms, clocks, n_launch, last_loss = timed(step_device, "device")
+    comm_ms = trainer.model.timing_summary(steps + warmup) if engine_timing is not None else None
 
     headline = Path(args.model_config).resolve() == (ROOT / "configs" / "synbios_moe" / "model.yaml").resolve()
     if headline:
@@ -274,6 +295,18 @@ def main() -> None:
     }
     if hasattr(ops, "dispatch_summary"):
         record["dispatch"] = ops.dispatch_summary()
+    if comm_ms is not None:
+        record["comm_wait_ms_per_step"] = comm_ms        # this rank's compute-stream stalls, events also cover the warm-up steps
+    if args.impl == "own":
+        record["config"]["sharding"] = args.sharding if strategy_name == "fsdp" else None
+        record["config"]["multimem"] = bool(args.multimem)
+        dropped = trainer.last_metrics.get("moe/dropped_route_fraction")
+        if dropped is not None:
+            record["dropped_route_fraction"] = round(float(dropped), 5)
+            record["config"]["capacity_factor"] = args.capacity_factor
+        sizes = getattr(trainer.model, "parameter_bytes", None)
+        if callable(sizes):
+            record["parameter_bytes"] = sizes()
     if args.impl == "own":
         from mini_train_sys_b200.ops.native_backend import check_kernel_status
 

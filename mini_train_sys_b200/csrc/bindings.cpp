@@ -41,6 +41,41 @@ Tensor& status_word(int device) {
   return words[device];
 }
 
+// ---------------- embedding ----------------
+void check_embedding(const Tensor& ids, int64_t H) {
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids must be contiguous int64 on the device");
+  TORCH_CHECK(H % 8 == 0, "embedding width must be a multiple of 8");
+}
+
+Tensor embedding_fwd(const Tensor& ids, const Tensor& w) {
+  TORCH_CHECK(w.is_cuda() && w.dim() == 2 && w.is_contiguous() && (w.scalar_type() == at::kFloat || is_bf16(w)),
+              "embedding weight must be contiguous fp32 or bf16 [V, H]");
+  check_embedding(ids, w.size(1));
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(w.data_ptr()) & 15) == 0, "embedding weight must be 16-byte aligned");
+  c10::cuda::CUDAGuard guard(w.device());
+  auto shape = ids.sizes().vec();
+  shape.push_back(w.size(1));
+  Tensor out = torch::empty(shape, w.options().dtype(torch::kBFloat16));
+  check_launch(mts::launch_embedding_fwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), w.data_ptr(), is_bf16(w),
+                                         out.data_ptr(), ids.numel(), int(w.size(0)), int(w.size(1)),
+                                         status_word(w.get_device()).data_ptr<int>(), cur_stream()), "embedding_fwd");
+  return out;
+}
+
+// dw (fp32 [V, H], contiguous) += scatter of dout's rows; the caller decides whether dw starts at zero.
+void embedding_bwd(const Tensor& ids, const Tensor& dout, Tensor dw) {
+  TORCH_CHECK(dw.is_cuda() && dw.dim() == 2 && dw.is_contiguous() && dw.scalar_type() == at::kFloat, "dw must be contiguous fp32 [V, H]");
+  check_embedding(ids, dw.size(1));
+  TORCH_CHECK(dout.is_cuda() && is_bf16(dout) && dout.is_contiguous() && dout.numel() == ids.numel() * dw.size(1),
+              "dout must be contiguous bf16 with one row per id");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(dw.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(dout.data_ptr()) & 15) == 0,
+              "embedding gradient buffers must be 16-byte aligned");
+  c10::cuda::CUDAGuard guard(dw.device());
+  check_launch(mts::launch_embedding_bwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), dout.data_ptr(),
+                                         dw.data_ptr<float>(), ids.numel(), int(dw.size(0)), int(dw.size(1)),
+                                         status_word(dw.get_device()).data_ptr<int>(), cur_stream()), "embedding_bwd");
+}
+
 // ---------------- router projection (skinny GEMM) ----------------
 void check_router_operands(const Tensor& x, const Tensor& w) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(), "x must be contiguous bf16 [T, H]");
@@ -70,15 +105,29 @@ std::vector<Tensor> router_logits_bwd(const Tensor& g, const Tensor& x, const Te
   c10::cuda::CUDAGuard guard(x.device());
   Tensor dx, dw;
   const int T = int(x.size(0)), E = int(w.size(0)), H = int(w.size(1));
-  if (need_dx) {
+  if (need_dx && T > 0) {
     dx = torch::empty_like(x);
     check_launch(mts::launch_router_logits_dx(g.data_ptr<float>(), w.data_ptr(), is_bf16(w), dx.data_ptr(), T, E, H, cur_stream()),
                  "router_logits_dx");
   }
   if (need_dw) {
-    dw = torch::zeros({w.size(0), w.size(1)}, x.options().dtype(torch::kFloat));
-    check_launch(mts::launch_router_logits_dw(g.data_ptr<float>(), x.data_ptr(), dw.data_ptr<float>(), T, E, H, cur_stream()),
-                 "router_logits_dw");
+    dw = torch::empty({w.size(0), w.size(1)}, x.options().dtype(torch::kFloat));
+    if (T == 0) {
+      dw.zero_();
+    } else {
+      int passes = 0, gx = 0;
+      long long floats = 0;
+      mts::router_logits_dw_plan(E, H, &passes, &gx, &floats);
+      Tensor partial = torch::empty({floats}, dw.options());
+      // one counter array per device, zeroed once: the kernel resets what it used (launches on one stream are ordered)
+      static std::vector<Tensor> counters(64);
+      Tensor& arrivals = counters[x.get_device()];
+      if (!arrivals.defined()) arrivals = torch::zeros({64}, x.options().dtype(torch::kInt));
+      TORCH_CHECK(passes <= 64, "router projection: too many column passes");
+      check_launch(mts::launch_router_logits_dw(g.data_ptr<float>(), x.data_ptr(), dw.data_ptr<float>(), partial.data_ptr<float>(),
+                                                reinterpret_cast<unsigned*>(arrivals.data_ptr<int>()), T, E, H, cur_stream()),
+                   "router_logits_dw");
+    }
   }
   return {dx, dw};
 }
@@ -457,6 +506,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_forward", &ce_forward);
   m.def("ce_backward", &ce_backward);
   m.def("count_valid", &count_valid);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
   m.def("router_logits_ok", &router_logits_ok);
   m.def("router_logits_fwd", &router_logits_fwd);
   m.def("router_logits_bwd", &router_logits_bwd);

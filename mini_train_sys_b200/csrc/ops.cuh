@@ -70,13 +70,23 @@ cudaError_t launch_moe_combine_bwd(const void* dout, const void* y, const int* r
                                    const void* weights, void* dys, float* dweights, int T, int K, int H,
                                    int capacity_rows, const int* meta, cudaStream_t stream);
 
+// ---- embedding.cu: out[t] = W[ids[t]] (bf16 out; W fp32 or bf16) and dW[ids[t]] += dout[t] (fp32 reductions) ----
+// Ids outside [0, V) are skipped and raise STATUS_BAD_ARGUMENT in `status` (may be null).
+cudaError_t launch_embedding_fwd(const long long* ids, const void* w, bool w_bf16, void* out, long long T, int V, int H, int* status,
+                                 cudaStream_t stream);
+cudaError_t launch_embedding_bwd(const long long* ids, const void* dout, float* dw, long long T, int V, int H, int* status,
+                                 cudaStream_t stream);
+
 // ---- skinny_gemm.cu: router projection x[T, H] (bf16) x W[E, H] (fp32 or bf16), E in {4, 8, 16}, fp32 arithmetic ----
 bool router_logits_supported(int E, int H);
 cudaError_t launch_router_logits_fwd(const void* x, const void* w, bool w_bf16, float* out, int T, int E, int H, cudaStream_t stream);
 // dx[T, H] (bf16) = g[T, E] W
 cudaError_t launch_router_logits_dx(const float* g, const void* w, bool w_bf16, void* dx, int T, int E, int H, cudaStream_t stream);
-// dw[E, H] (fp32, zeroed by the caller) += g^T x
-cudaError_t launch_router_logits_dw(const float* g, const void* x, float* dw, int T, int E, int H, cudaStream_t stream);
+// dw[E, H] (fp32) = g^T x.  `partial` (floats, size from router_logits_dw_plan) and `arrivals` (one zeroed counter per column pass;
+// the kernel leaves them zeroed) are scratch; launches that share them must not overlap.
+void router_logits_dw_plan(int E, int H, int* passes, int* ctas_per_pass, long long* partial_floats);
+cudaError_t launch_router_logits_dw(const float* g, const void* x, float* dw, float* partial, unsigned* arrivals, int T, int E, int H,
+                                    cudaStream_t stream);
 
 // ---- optim.cu ----
 struct AdamWArgs {

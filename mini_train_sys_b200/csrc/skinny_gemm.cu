@@ -10,7 +10,8 @@
 //   forward   per (row, pass) the lane's E partial sums are reduced over the warp with a halving exchange and added to a
 //             warp-private accumulator in shared memory (fixed order: deterministic)
 //   dx        out[row][cols] = sum_e g[row][e] * W[e][cols]
-//   dW        acc[e][cols] += g[row][e] * x[row][cols] over the warp's rows, then one atomic per element per CTA
+//   dW        acc[e][cols] += g[row][e] * x[row][cols] over the warp's rows; CTA partials meet in global memory and the last
+//             CTA of a column pass adds them up in a fixed order (deterministic, no per-element atomics)
 #include "ops.cuh"
 
 #include <cuda_bf16.h>
@@ -195,11 +196,15 @@ router_logits_dx_kernel(const float* __restrict__ g, const void* __restrict__ w,
   }
 }
 
-// dW[E, H] (fp32, pre-zeroed) += g^T x.  blockIdx.y = column pass; every warp accumulates its rows in registers (four rows
-// in flight per step), the CTA adds its eight warps up in shared memory and issues one atomic per element.
+// dW[E, H] (fp32) = g^T x.  blockIdx.y = column pass; every warp accumulates its rows in registers (four rows in flight per
+// step) and the CTA adds its eight warps up in shared memory.  The CTAs of a pass then meet in global memory: each writes its
+// partial [E x SPAN] block, and the last one to arrive (a counter per pass) adds all of them up in a fixed order and writes
+// the result, so the gradient is deterministic and nothing serialises on same-address atomics (one atomic per CTA instead of
+// one per element: with 100 CTAs per pass the per-element version spent most of its 60 us queueing in L2).
 template <int E, int COLS>
 __global__ void __launch_bounds__(256)
-router_logits_dw_kernel(const float* __restrict__ g, const __nv_bfloat16* __restrict__ x, float* __restrict__ dw, int T, int H) {
+router_logits_dw_kernel(const float* __restrict__ g, const __nv_bfloat16* __restrict__ x, float* __restrict__ dw,
+                        float* __restrict__ partial, unsigned* __restrict__ arrivals, int T, int H) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int warp_in_grid = blockIdx.x * 8 + warp;
@@ -235,18 +240,42 @@ router_logits_dw_kernel(const float* __restrict__ g, const __nv_bfloat16* __rest
     }
   }
   __shared__ float part[E * SPAN];
+  __shared__ int is_last;
   for (int i = threadIdx.x; i < E * SPAN; i += blockDim.x) part[i] = 0.f;
   __syncthreads();
+  for (int w = 0; w < 8; ++w) {        // warps take turns: a fixed order of additions
+    if (warp == w) {
 #pragma unroll
-  for (int e = 0; e < E; ++e)
+      for (int e = 0; e < E; ++e)
 #pragma unroll
-    for (int c = 0; c < COLS; ++c) atomicAdd(&part[e * SPAN + lane * COLS + c], acc[e][c]);
+        for (int c = 0; c < COLS; ++c) part[e * SPAN + lane * COLS + c] += acc[e][c];
+    }
+    __syncthreads();
+  }
+  float* mine = partial + ((long long)blockIdx.y * gridDim.x + blockIdx.x) * (E * SPAN);
+  for (int i = threadIdx.x; i < E * SPAN; i += blockDim.x) mine[i] = part[i];
+  __threadfence();
   __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(arrivals + blockIdx.y, 1u) == gridDim.x - 1 ? 1 : 0;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const float* base = partial + (long long)blockIdx.y * gridDim.x * (E * SPAN);
   for (int i = threadIdx.x; i < E * SPAN; i += blockDim.x) {
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    int b = 0;
+    for (; b + 3 < int(gridDim.x); b += 4) {
+      s0 += __ldcg(base + (long long)b * (E * SPAN) + i);
+      s1 += __ldcg(base + (long long)(b + 1) * (E * SPAN) + i);
+      s2 += __ldcg(base + (long long)(b + 2) * (E * SPAN) + i);
+      s3 += __ldcg(base + (long long)(b + 3) * (E * SPAN) + i);
+    }
+    for (; b < int(gridDim.x); ++b) s0 += __ldcg(base + (long long)b * (E * SPAN) + i);
     const int e = i / SPAN, c = i - e * SPAN;
     const int gc = blockIdx.y * SPAN + c;
-    if (gc < H && part[i] != 0.f) atomicAdd(dw + (long long)e * H + gc, part[i]);
+    if (gc < H) dw[(long long)e * H + gc] = (s0 + s1) + (s2 + s3);
   }
+  if (threadIdx.x == 0) arrivals[blockIdx.y] = 0;     // ready for the next launch on this stream
 }
 
 template <int E, int COLS>
@@ -266,11 +295,11 @@ cudaError_t run_dx(const float* g, const void* w, bool w_bf16, void* dx, int T, 
 }
 
 template <int E, int COLS>
-cudaError_t run_dw(const float* g, const void* x, float* dw, int T, int H, cudaStream_t stream) {
+cudaError_t run_dw(const float* g, const void* x, float* dw, float* partial, unsigned* arrivals, int gx, int T, int H,
+                   cudaStream_t stream) {
   const int passes = (H + 32 * COLS - 1) / (32 * COLS);
-  int gx = device_sm_count() * 2 / passes;
-  if (gx < 1) gx = 1;
-  router_logits_dw_kernel<E, COLS><<<dim3(gx, passes), 256, 0, stream>>>(g, static_cast<const __nv_bfloat16*>(x), dw, T, H);
+  router_logits_dw_kernel<E, COLS><<<dim3(gx, passes), 256, 0, stream>>>(g, static_cast<const __nv_bfloat16*>(x), dw, partial,
+                                                                      arrivals, T, H);
   return cudaGetLastError();
 }
 
@@ -296,13 +325,26 @@ cudaError_t launch_router_logits_dx(const float* g, const void* w, bool w_bf16, 
   return run_dx<16, 4>(g, w, w_bf16, dx, T, H, stream);
 }
 
-cudaError_t launch_router_logits_dw(const float* g, const void* x, float* dw, int T, int E, int H, cudaStream_t stream) {
-  if (!router_logits_supported(E, H)) return cudaErrorInvalidValue;
-  if (T <= 0) return cudaSuccess;
+// Scratch of the weight-gradient kernel: `ctas_per_pass` partial blocks per column pass and one arrival counter per pass.
+void router_logits_dw_plan(int E, int H, int* passes, int* ctas_per_pass, long long* partial_floats) {
+  const int span = E == 16 ? 128 : 256;
+  *passes = (H + span - 1) / span;
+  int gx = device_sm_count() * 2 / *passes;
+  if (gx < 1) gx = 1;
+  *ctas_per_pass = gx;
+  *partial_floats = (long long)*passes * gx * E * span;
+}
+
+cudaError_t launch_router_logits_dw(const float* g, const void* x, float* dw, float* partial, unsigned* arrivals, int T, int E, int H,
+                                    cudaStream_t stream) {
+  if (!router_logits_supported(E, H) || T <= 0) return cudaErrorInvalidValue;
+  int passes = 0, gx = 0;
+  long long floats = 0;
+  router_logits_dw_plan(E, H, &passes, &gx, &floats);
   ++g_launch_count;
-  if (E == 4) return run_dw<4, 8>(g, x, dw, T, H, stream);
-  if (E == 8) return run_dw<8, 8>(g, x, dw, T, H, stream);
-  return run_dw<16, 4>(g, x, dw, T, H, stream);
+  if (E == 4) return run_dw<4, 8>(g, x, dw, partial, arrivals, gx, T, H, stream);
+  if (E == 8) return run_dw<8, 8>(g, x, dw, partial, arrivals, gx, T, H, stream);
+  return run_dw<16, 4>(g, x, dw, partial, arrivals, gx, T, H, stream);
 }
 
 }  // namespace mts

@@ -60,7 +60,12 @@ class MiniTransformer(nn.Module):
         embeddings with the same shape; probes train it against a frozen backbone.
         """
 
-        h = self.embed(input_ids)
+        h = None
+        own_embedding = getattr(self.ops, "embedding", None)
+        if own_embedding is not None and embedding_delta is None and self.activation_dtype == torch.bfloat16:
+            h = own_embedding(input_ids, self.embed.weight)      # None when the backend does not cover these inputs
+        if h is None:
+            h = self.embed(input_ids)
         if embedding_delta is not None:
             if embedding_delta.shape != h.shape:
                 raise ValueError("embedding_delta must match embedded input shape")

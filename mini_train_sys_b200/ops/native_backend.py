@@ -176,13 +176,19 @@ def expert_wgrad_splits(rows: int, groups: int, m: int, n: int, device: torch.de
 
 
 def grad_sink(param: torch.Tensor):
-    """``(fp32 destination, done callback)`` when a sharding engine wants this parameter's gradient written in place.
+    """``(fp32 destination, done callback, accumulate)`` when a sharding engine wants this parameter's gradient written in place.
 
-    The engine attaches ``_mts_grad_sink`` to parameters that are used once per step; a backward function that honours it writes
-    the fp32 gradient there, calls ``done(param)`` and returns no gradient for the parameter, which saves the bf16 round trip
-    (fp32 -> parameter dtype -> fp32 copy in the accumulate hook) and two passes over every weight-sized tensor."""
+    The engine attaches ``_mts_grad_sink`` to parameters; a backward function that honours it writes the fp32 gradient there,
+    calls ``done(param)`` and returns no gradient for the parameter, which saves the bf16 round trip (fp32 -> parameter
+    dtype -> fp32 copy in the accumulate hook) and two passes over every weight-sized tensor.  ``accumulate`` is False for
+    parameters used once per step (the writer overwrites the destination) and True for parameters with several uses, such
+    as a tied embedding / output matrix: every writer ADDS to the destination, which the engine zeroes after each step."""
 
     return getattr(param, "_mts_grad_sink", None)
+
+
+def _sink_accumulates(sink) -> bool:
+    return len(sink) > 2 and bool(sink[2])
 
 
 def _gemm_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -226,7 +232,8 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             sink = grad_sink(weight)
             if sink is not None:
-                gemm_tn(dy2, x2, out=sink[0], M=n_out)      # fp32, straight into the engine's flat gradient buffer
+                # fp32, straight into the engine's flat gradient buffer
+                gemm_tn(dy2, x2, out=sink[0], M=n_out, accumulate=_sink_accumulates(sink))
                 sink[1](weight)
             else:
                 dw = gemm_tn(dy2, x2, M=n_out).to(weight.dtype)
@@ -386,16 +393,53 @@ class _FusedLinearCEFn(torch.autograd.Function):
                     one_group[n] = torch.tensor([0, n], dtype=torch.int32, device=dev)
                 _gemm(z, xs, dw, vocab, hidden, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=one_group[n],
                       num_groups=1, accumulate=True, ldo=hidden)
-        ctx.save_for_backward(dx, dw)
+        ctx.save_for_backward(dx, dw, weight)
         ctx.w_dtype = weight.dtype
         return stats[0] / stats[1]
 
     @staticmethod
     def backward(ctx, g):
-        dx, dw = ctx.saved_tensors
+        dx, dw, weight = ctx.saved_tensors
         gx = dx * g.to(dx.dtype) if dx is not None else None
-        gw = (dw * g).to(ctx.w_dtype) if dw is not None else None
+        gw = None
+        if dw is not None:
+            sink = grad_sink(weight)
+            if sink is not None:       # scale straight into the engine's fp32 buffer: no weight-sized temporaries, no dtype round trip
+                if _sink_accumulates(sink):
+                    sink[0].addcmul_(dw, g.to(dw.dtype))
+                else:
+                    torch.mul(dw, g.to(dw.dtype), out=sink[0])
+                sink[1](weight)
+            else:
+                gw = (dw * g).to(ctx.w_dtype)
         return gx, gw, None
+
+
+class _EmbeddingFn(torch.autograd.Function):
+    """Token embedding by the own gather kernel; the gradient is scattered in fp32 (into the engine's buffer when there is one)."""
+
+    @staticmethod
+    def forward(ctx, ids, weight):
+        w = weight.detach()
+        w = w if w.is_contiguous() else w.contiguous()
+        idc = ids if ids.is_contiguous() else ids.contiguous()
+        ctx.save_for_backward(idc, weight)
+        return ext().embedding_fwd(idc, w)
+
+    @staticmethod
+    def backward(ctx, dout):
+        ids, weight = ctx.saved_tensors
+        go = dout if dout.is_contiguous() else dout.contiguous()
+        sink = grad_sink(weight)
+        if sink is not None:
+            if not _sink_accumulates(sink):
+                sink[0].zero_()
+            ext().embedding_bwd(ids, go, sink[0])
+            sink[1](weight)
+            return None, None
+        dw = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+        ext().embedding_bwd(ids, go, dw)
+        return None, dw.to(weight.dtype)
 
 
 _dropout_calls = 0
@@ -643,6 +687,16 @@ class NativeOpsBackend(TorchOpsBackend):
 
     def dispatch_summary(self) -> dict[str, int]:
         return dict(self.dispatch)
+
+    # -- embedding (optional hook outside the 8-op protocol; the model uses it when present) -----
+    def embedding(self, input_ids, weight):
+        """bf16 rows of ``weight`` for every id, or ``None`` when the inputs are not covered (the caller falls back)."""
+
+        ok = (input_ids.is_cuda and input_ids.dtype == torch.long and weight.is_cuda and weight.dim() == 2
+              and weight.shape[1] % 8 == 0 and weight.dtype in (torch.float32, torch.bfloat16))
+        if not self._count("embedding", ok):
+            return None
+        return _EmbeddingFn.apply(input_ids, weight)
 
     # -- projections ------------------------------------------------------------------------
     def linear(self, x, weight):

@@ -58,6 +58,8 @@ class ParamSlot:
     numel: int
     shape: torch.Size
     decay: bool
+    late: bool = False     # several uses per step (embedding, tied head): writers ADD into the flat buffer, which is zeroed after
+                           # every step, and the slot counts as arrived when the optimizer step begins
 
 
 @dataclass
@@ -168,6 +170,7 @@ class FlatDataParallel(nn.Module):
         self.staged = (mode == "shard" and reshard_after_forward and per_block_units
                        and (self.world > 1 or stage_single_rank))
         self.prefetch = int(getattr(comm, "prefetch_units", 1)) > 0
+        self._timing: dict[str, list] | None = None   # phase -> [(start event, end event)] while enable_timing() is on
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.clip_coef = torch.ones(1, dtype=torch.float32, device=self.device)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -222,15 +225,27 @@ class FlatDataParallel(nn.Module):
             s.param.register_post_accumulate_grad_hook(self._on_grad)
             if self._sink_ok(s):
                 dst = unit.grad_full.tensor[s.offset:s.offset + s.numel].view(s.shape)
-                s.param._mts_grad_sink = (dst, self._on_sunk_grad)
+                s.param._mts_grad_sink = (dst, self._on_sunk_grad, False)
+            elif self._late_sink_ok(s):
+                s.late = True
+                dst = unit.grad_full.tensor[s.offset:s.offset + s.numel].view(s.shape)
+                s.param._mts_grad_sink = (dst, lambda _p: None, True)
         unit.pending = len(slots)
         return unit
+
+    def _late_sink_ok(self, slot) -> bool:
+        """The embedding matrix (which is also the output matrix when the two are tied): its gradient is complete only after
+        the very last operator of backward, so nothing is lost by closing its unit when the optimizer step begins."""
+
+        return self.coll.fused and slot.param.dim() == 2 and slot.name == "embed.weight"
 
     def _sink_ok(self, slot) -> bool:
         """Parameters whose backward may write the fp32 gradient in place: matrices used once per step by an operator that
         knows the protocol (linear layers and expert stacks inside the blocks; never tied or embedding weights)."""
 
         name = slot.name
+        if self.coll.fused and name == "lm_head.weight" and slot.param.dim() == 2:
+            return True        # an output matrix of its own (not tied to the embedding): one use, by the loss
         if not (self.coll.fused and ".blocks." in f".{name}"):
             return False
         if slot.param.dim() == 1:      # the two norm weights of a block: RMSNorm backward accumulates dw in fp32 anyway
@@ -274,6 +289,10 @@ class FlatDataParallel(nn.Module):
             return      # the operator wrote this gradient through the parameter's sink and already reported it
         unit, slot = self._slot_of[param]
         dst = unit.grad_full.tensor[slot.offset:slot.offset + slot.numel].view(slot.shape)
+        if slot.late:      # contributions that came through autograd join the ones written in place
+            dst.add_(param.grad)
+            param.grad = None
+            return
         dst.copy_(param.grad)
         param.grad = None
         self._arrived(unit, slot)
@@ -289,7 +308,7 @@ class FlatDataParallel(nn.Module):
                         self._on_grad(s.param)
                 if unit.pending > 0:
                     for s in unit.slots:
-                        if s.offset not in unit.reported:
+                        if s.offset not in unit.reported and not s.late:
                             unit.grad_full.tensor[s.offset:s.offset + _round_up(s.numel, ALIGN)].zero_()
                     unit.pending = 0
                     self.coll.reduce_scatter(unit, self.comm_epoch + 1)
@@ -369,7 +388,8 @@ class FlatDataParallel(nn.Module):
             self._slot_event[slot] = self._gather_into(unit, self._slots[slot][:unit.total])
             self._slot_unit[slot] = unit.index
         if self._slot_event[slot] is not None:
-            torch.cuda.current_stream(self.device).wait_event(self._slot_event[slot])
+            with self._timed("gather_wait"):       # exposed part of the parameter gather: zero when the prefetch was in time
+                torch.cuda.current_stream(self.device).wait_event(self._slot_event[slot])
             self._slot_event[slot] = None
         self._point(unit, self._slots[slot])
         if self.prefetch and prefetch is not None and prefetch.index not in self._slot_unit:
@@ -389,7 +409,8 @@ class FlatDataParallel(nn.Module):
         if self._root_unit is not None and not self._root_fresh:
             ev = self._gather_into(self._root_unit, self._root_stage)
             if ev is not None:
-                torch.cuda.current_stream(self.device).wait_event(ev)
+                with self._timed("gather_wait"):
+                    torch.cuda.current_stream(self.device).wait_event(ev)
             self._root_fresh = True
         if self._block_order and self._block_order[0].index not in self._slot_unit:
             first = self._block_order[0]
@@ -428,6 +449,41 @@ class FlatDataParallel(nn.Module):
         if self._root_stage is not None:
             staging += self._root_stage.numel() * low
         return {"resident": resident, "staging": staging}
+
+    # ---- where a step waits for communication (CUDA events on the compute stream) ----------------------------------
+    def enable_timing(self, on: bool = True) -> None:
+        self._timing = {} if on else None
+
+    def _timed(self, phase: str):
+        """Context manager: brackets what the compute stream does inside with two events (no-op unless timing is on)."""
+
+        engine = self
+
+        class _Span:
+            def __enter__(self_inner):
+                if engine._timing is not None and engine.device.type == "cuda":
+                    self_inner.a = torch.cuda.Event(enable_timing=True)
+                    self_inner.a.record()
+                return self_inner
+
+            def __exit__(self_inner, *exc):
+                if engine._timing is not None and engine.device.type == "cuda":
+                    b = torch.cuda.Event(enable_timing=True)
+                    b.record()
+                    engine._timing.setdefault(phase, []).append((self_inner.a, b))
+                return False
+
+        return _Span()
+
+    def timing_summary(self, steps: int) -> dict[str, float]:
+        """Milliseconds per step the compute stream spent in each bracketed phase since timing was enabled (synchronises)."""
+
+        if not self._timing:
+            return {}
+        torch.cuda.synchronize(self.device)
+        out = {k: round(sum(a.elapsed_time(b) for a, b in v) / max(steps, 1), 4) for k, v in self._timing.items()}
+        self._timing = {}
+        return out
 
     def check_status(self) -> None:
         """Raise if a device-side wait of this engine's collectives ran out (synchronises the device)."""
@@ -612,13 +668,19 @@ class ShardedAdamW(torch.optim.Optimizer):
         eng._flush_incomplete_units()
         epoch = eng.comm_epoch + 1
         step = eng.step_count + 1
-        eng.coll.norm_and_clip(eng.sumsq, self._clip, epoch, eng.clip_coef, eng.grad_norm)
+        stream = getattr(eng.coll, "comm_stream", None)
+        if stream is not None:
+            with eng._timed("reduce_scatter_tail"):     # what is left of the gradient reductions once backward has finished
+                torch.cuda.current_stream(eng.device).wait_stream(stream)
+        with eng._timed("norm_and_clip"):
+            eng.coll.norm_and_clip(eng.sumsq, self._clip, epoch, eng.clip_coef, eng.grad_norm)
         decay_group, plain_group = self.param_groups
         if eng.coll.fused and decay_group["betas"] == plain_group["betas"] and decay_group["eps"] == plain_group["eps"]:
             table, n_rows, chunks = self._segment_table()
-            eng.coll.adamw_update_table(table, n_rows, chunks, lr=(float(decay_group["lr"]), float(plain_group["lr"])),
-                                        weight_decay=(float(decay_group["weight_decay"]), float(plain_group["weight_decay"])),
-                                        betas=decay_group["betas"], eps=decay_group["eps"], step=step, coef=eng.clip_coef)
+            with eng._timed("adamw"):
+                eng.coll.adamw_update_table(table, n_rows, chunks, lr=(float(decay_group["lr"]), float(plain_group["lr"])),
+                                            weight_decay=(float(decay_group["weight_decay"]), float(plain_group["weight_decay"])),
+                                            betas=decay_group["betas"], eps=decay_group["eps"], step=step, coef=eng.clip_coef)
             for unit in eng.units:
                 unit.pending = len(unit.slots)
                 unit.reported.clear()
@@ -632,7 +694,12 @@ class ShardedAdamW(torch.optim.Optimizer):
                     eng._refresh_unit(unit)
                 unit.pending = len(unit.slots)
                 unit.reported.clear()
-        eng.coll.refresh_done(epoch)
+        for unit in eng.units:          # multi-use parameters accumulate in place: start the next step from zero
+            for s in unit.slots:
+                if s.late:
+                    unit.grad_full.tensor[s.offset:s.offset + s.numel].zero_()
+        with eng._timed("refresh_done"):
+            eng.coll.refresh_done(epoch)
         eng._after_update()
         eng.sumsq.zero_()
         eng.comm_epoch = epoch

@@ -525,3 +525,39 @@ def test_moe_plan_and_fused_moe_skip_dropped_routes(nb, ops):
         want = ops.fused_moe(x, gu, dn, idx, torch.where(drop, torch.zeros_like(w), w))
     assert_close(got, want, 2e-2, "fused_moe with dropped routes")
     nb.check_kernel_status()
+
+
+@pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
+def test_embedding_gather_and_scatter_add(ops, w_dtype):
+    torch.manual_seed(31)
+    vocab, hidden = 1003, 264
+    w = torch.randn(vocab, hidden, device=DEV).to(w_dtype).requires_grad_()
+    ids = torch.randint(0, vocab, (7, 129), device=DEV)
+    ids[0, :40] = 5                                        # many tokens on one row: the reductions must not lose updates
+    out = ops.embedding(ids, w)
+    assert out.dtype == torch.bfloat16 and out.shape == (7, 129, hidden)
+    assert torch.equal(out, w.detach().to(torch.bfloat16)[ids])
+    g = torch.randn_like(out)
+    (gw,) = torch.autograd.grad(out, w, g)
+    want = torch.zeros(vocab, hidden, device=DEV, dtype=torch.float64)
+    want.index_add_(0, ids.reshape(-1), g.reshape(-1, hidden).double())
+    assert_close(gw, want, 1e-6 if w_dtype == torch.float32 else 5e-3, "dW")
+    # the engine protocol: gradients ADDED into a flat fp32 buffer that already holds another contribution
+    sink = torch.ones(vocab, hidden, device=DEV)
+    calls = []
+    w._mts_grad_sink = (sink, calls.append, True)
+    out2 = ops.embedding(ids, w)
+    assert torch.autograd.grad(out2, w, g, allow_unused=True)[0] is None and len(calls) == 1
+    assert_close(sink, want + 1.0, 1e-6, "sink")
+
+
+def test_embedding_refuses_ids_outside_the_vocabulary_without_touching_memory(nb, ops):
+    w = torch.randn(64, 128, device=DEV)
+    ids = torch.tensor([[1, 70, -3, 2]], device=DEV)
+    out = ops.embedding(ids, w)
+    torch.cuda.synchronize()
+    assert torch.equal(out[0, 1], torch.zeros(128, device=DEV, dtype=torch.bfloat16)) and float(out[0, 0].float().abs().sum()) > 0
+    with pytest.raises(RuntimeError, match="status 2"):
+        nb.check_kernel_status()
+    nb.ext().status_tensor(0).zero_()
+    nb.check_kernel_status()
