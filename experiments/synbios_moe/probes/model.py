@@ -118,18 +118,23 @@ def train_probe(backbone, cache_dir: str | Path, *, kind: str, attribute: str, t
                 rank: int | None = None, batch_size: int | None = None, evaluation_batch_size: int | None = None, seed: int = 1337,
                 recovery_checkpoint: str | Path | None = None, checkpoint_interval_steps: int | None = None, resume: bool = True,
                 evaluate_train: bool = False, skip_final_validation: bool = False, identity: dict | None = None,
-                on_event: Callable[[dict], None] | None = None, max_eval_items: int | None = None) -> dict:
+                on_event: Callable[[dict], None] | None = None, max_eval_items: int | None = None,
+                train_set=None, valid_set=None, return_probe: bool = False) -> dict:
     """Train one probe; returns the result record (also what ``training/<job>.json`` holds).
 
     ``identity`` is stored in the recovery checkpoint and must match on resume (a checkpoint of another backbone,
-    task or hyper-parameter set is refused rather than silently continued).
+    task or hyper-parameter set is refused rather than silently continued).  ``train_set`` / ``valid_set`` replace the
+    cached task's examples with a derived dataset (same item type, ``class_names`` and ``eos``): the interventions that
+    rebuild probe inputs train through this entry; with ``return_probe`` the trained module is returned under ``"probe"``.
     """
 
     rank = DEFAULT_RANK[kind] if rank is None else rank
     batch_size = DEFAULT_BATCH[kind] if batch_size is None else batch_size
     evaluation_batch_size = evaluation_batch_size or batch_size
-    train_set = CachedProbeDataset(cache_dir, kind=kind, attribute=attribute, target=target, split="train")
-    valid_set = CachedProbeDataset(cache_dir, kind=kind, attribute=attribute, target=target, split="validation")
+    if train_set is None:
+        train_set = CachedProbeDataset(cache_dir, kind=kind, attribute=attribute, target=target, split="train")
+    if valid_set is None:
+        valid_set = CachedProbeDataset(cache_dir, kind=kind, attribute=attribute, target=target, split="validation")
     if len(train_set) == 0:
         raise ValueError("the training split of this probe task is empty")
     torch.manual_seed(seed)
@@ -140,6 +145,7 @@ def train_probe(backbone, cache_dir: str | Path, *, kind: str, attribute: str, t
     identity = {"kind": kind, "attribute": attribute, "target": target, "rank": rank, "batch_size": batch_size, "steps": steps,
                 "seed": seed, **(identity or {})}
     step, losses = 0, []
+    resumed_from = None
     recovery = Path(recovery_checkpoint) if recovery_checkpoint else None
     if recovery is not None and resume and recovery.is_file():
         saved = torch.load(recovery, map_location="cpu", weights_only=False)
@@ -150,7 +156,7 @@ def train_probe(backbone, cache_dir: str | Path, *, kind: str, attribute: str, t
         torch.set_rng_state(saved["torch_rng"])
         if saved.get("cuda_rng") is not None and torch.cuda.is_available():
             torch.cuda.set_rng_state_all(saved["cuda_rng"])
-        step = int(saved["step"])
+        step = resumed_from = int(saved["step"])
         if on_event:
             on_event({"event": "probe_resume", "step": step, "path": str(recovery)})
 
@@ -182,7 +188,8 @@ def train_probe(backbone, cache_dir: str | Path, *, kind: str, attribute: str, t
             on_event({"event": "probe_train", "step": step, "steps": steps, "loss": losses[-1], "lr": optimizer.param_groups[0]["lr"]})
         if checkpoint_interval_steps and step % checkpoint_interval_steps == 0 and step < steps:
             save_recovery()
-    result = {"identity": identity, "steps": step, "final_loss": losses[-1] if losses else None, "train_examples": n,
+    result = {"identity": identity, "steps": step, "resumed_from_step": resumed_from, "final_loss": losses[-1] if losses else None,
+              "train_examples": n,
               "validation_examples": len(valid_set), "classes": len(train_set.class_names), "seconds": time.time() - started,
               "trainable_parameters": sum(p.numel() for p in params)}
     if not skip_final_validation:
@@ -190,18 +197,41 @@ def train_probe(backbone, cache_dir: str | Path, *, kind: str, attribute: str, t
     if evaluate_train:
         result["train"] = evaluate(probe, train_set, batch_size=evaluation_batch_size, device=device, max_items=max_eval_items)
     result["probe_state"] = probe.trainable_state()
+    if return_probe:
+        result["probe"] = probe
     return result
 
 
 def save_probe_result(result: dict, json_path: str | Path, state_path: str | Path) -> None:
     """``training/<job>.pt`` (trainable weights) first, then ``training/<job>.json``: the marker is written last."""
 
+    result.pop("probe", None)
     state = result.pop("probe_state")
     _atomic_torch_save({"version": CHECKPOINT_VERSION, "identity": result["identity"], "probe": state}, Path(state_path))
     tmp = Path(json_path).with_suffix(".json.tmp")
     Path(json_path).parent.mkdir(parents=True, exist_ok=True)
     tmp.write_text(json.dumps(result, indent=1, default=str))
     os.replace(tmp, json_path)
+
+
+def load_saved_probe(backbone, state_path: str | Path, num_classes: int, *, expect: dict | None = None, device="cpu") -> AttributeProbe:
+    """Rebuild a trained probe from ``training/<job>.pt``; ``expect`` lists identity fields that must match (kind, attribute,
+    target, ...), so that a head of another task is refused instead of silently evaluated."""
+
+    saved = torch.load(state_path, map_location="cpu", weights_only=False)
+    ident = saved.get("identity")
+    if saved.get("version") != CHECKPOINT_VERSION or not isinstance(ident, dict):
+        raise ValueError(f"{state_path} is not a probe result of this format")
+    for key, want in (expect or {}).items():
+        if ident.get(key) != want:
+            raise ValueError(f"{state_path}: {key} is {ident.get(key)!r}, expected {want!r}")
+    probe = AttributeProbe(backbone, num_classes, rank=int(ident["rank"]), kind=ident["kind"])
+    merged = {**probe.state_dict(), **saved["probe"]}
+    missing = [k for k in probe.trainable_state() if k not in saved["probe"]]
+    if missing:
+        raise ValueError(f"{state_path} lacks trainable tensors: {missing[:3]}")
+    probe.load_state_dict(merged)
+    return probe.to(device)
 
 
 def validate_saved_probe(backbone, cache_dir: str | Path, state_path: str | Path, *, device="cpu", batch_size: int = 200,

@@ -1,0 +1,128 @@
+#!/usr/bin/env python
+"""Run a walkthrough unattended and keep a per-cell record of what happened.
+
+Accepts a Jupyter notebook (``.ipynb``: its code cells are executed in order in one namespace; no Jupyter packages are
+needed, the file is plain JSON) or a Python walkthrough (``.py``: cut into cells at ``# %%`` markers, or run as a single
+cell when it has none, with ``__name__ == "__main__"``).  For every cell the runner stores source, captured output, the
+traceback of an exception and the wall time in ``<output>.json``; optionally an executed copy of the notebook with the
+outputs filled in.  The exit code is non-zero when any cell raised, which is what makes the walkthroughs usable as server
+acceptance tests (reference: scripts/run_server_notebook.py:1-125, which drives nbclient).
+
+    python scripts/run_server_notebook.py examples/training_walkthrough.py --output runs/walkthrough.json
+"""
+
+from __future__ import annotations
+
+import argparse
+import contextlib
+import io
+import json
+import sys
+import time
+import traceback
+from pathlib import Path
+
+
+def load_cells(path: Path) -> list[str]:
+    if path.suffix == ".ipynb":
+        notebook = json.loads(path.read_text(encoding="utf-8"))
+        cells = []
+        for cell in notebook.get("cells", []):
+            if cell.get("cell_type") == "code":
+                src = cell.get("source", "")
+                cells.append("".join(src) if isinstance(src, list) else str(src))
+        return cells
+    text = path.read_text(encoding="utf-8")
+    if "\n# %%" not in "\n" + text:
+        return [text]
+    cells, current = [], []
+    for line in text.splitlines(keepends=True):
+        if line.startswith("# %%") and current:
+            cells.append("".join(current))
+            current = []
+        current.append(line)
+    if current:
+        cells.append("".join(current))
+    return cells
+
+
+def _strip_magics(source: str) -> str:
+    """IPython line magics and shell escapes are not Python: comment them out so that the rest of the cell still runs."""
+
+    return "".join(("# " + line) if line.lstrip().startswith(("%", "!")) else line for line in source.splitlines(keepends=True))
+
+
+def run_cells(cells: list[str], *, filename: str, keep_going: bool = False, echo: bool = False) -> list[dict]:
+    namespace: dict = {"__name__": "__main__", "__file__": filename}
+    records = []
+    for index, source in enumerate(cells):
+        out, err = io.StringIO(), io.StringIO()
+        started = time.perf_counter()
+        record = {"cell": index, "source": source, "status": "ok", "error": None}
+        try:
+            code = compile(_strip_magics(source), f"{filename}#cell{index}", "exec")
+            with contextlib.redirect_stdout(out), contextlib.redirect_stderr(err):
+                exec(code, namespace)      # noqa: S102 - executing the user's own walkthrough is the purpose of this tool
+        except SystemExit as exc:          # a walkthrough that ends with sys.exit(main())
+            if exc.code not in (None, 0):
+                record.update(status="error", error=f"SystemExit({exc.code!r})")
+        except BaseException:              # noqa: BLE001 - the record is the product; the cell's failure must not kill the runner
+            record.update(status="error", error=traceback.format_exc())
+        record.update(stdout=out.getvalue(), stderr=err.getvalue(), seconds=round(time.perf_counter() - started, 3))
+        records.append(record)
+        if echo:
+            print(f"[cell {index}] {record['status']} in {record['seconds']} s", flush=True)
+        if record["status"] == "error" and not keep_going:
+            break
+    return records
+
+
+def write_executed_notebook(source: Path, records: list[dict], destination: Path) -> None:
+    notebook = json.loads(source.read_text(encoding="utf-8"))
+    by_index = {r["cell"]: r for r in records}
+    code_index = 0
+    for cell in notebook.get("cells", []):
+        if cell.get("cell_type") != "code":
+            continue
+        rec = by_index.get(code_index)
+        code_index += 1
+        if rec is None:
+            continue
+        outputs = []
+        if rec["stdout"]:
+            outputs.append({"output_type": "stream", "name": "stdout", "text": rec["stdout"]})
+        if rec["error"]:
+            outputs.append({"output_type": "error", "ename": "Exception", "evalue": rec["error"].strip().splitlines()[-1],
+                            "traceback": rec["error"].splitlines()})
+        cell["outputs"], cell["execution_count"] = outputs, rec["cell"] + 1
+    destination.parent.mkdir(parents=True, exist_ok=True)
+    destination.write_text(json.dumps(notebook, indent=1), encoding="utf-8")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("walkthrough", type=Path)
+    ap.add_argument("--output", type=Path, help="JSON record (default: <walkthrough>.run.json)")
+    ap.add_argument("--executed-notebook", type=Path, help="for .ipynb inputs: write a copy with the outputs filled in")
+    ap.add_argument("--keep-going", action="store_true", help="run the remaining cells after a failure")
+    ap.add_argument("--quiet", action="store_true")
+    args = ap.parse_args(argv)
+    path = args.walkthrough.resolve()
+    cells = load_cells(path)
+    records = run_cells(cells, filename=str(path), keep_going=args.keep_going, echo=not args.quiet)
+    failed = [r["cell"] for r in records if r["status"] == "error"]
+    report = {"walkthrough": str(path), "cells": len(cells), "executed": len(records), "failed_cells": failed,
+              "seconds": round(sum(r["seconds"] for r in records), 3), "records": records}
+    output = args.output or path.with_suffix(".run.json")
+    output.parent.mkdir(parents=True, exist_ok=True)
+    output.write_text(json.dumps(report, indent=1), encoding="utf-8")
+    if args.executed_notebook and path.suffix == ".ipynb":
+        write_executed_notebook(path, records, args.executed_notebook)
+    if failed and not args.quiet:
+        print(records[failed[0]]["error"], file=sys.stderr)
+    print(json.dumps({k: report[k] for k in ("cells", "executed", "failed_cells", "seconds")}))
+    return 1 if failed else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -15,6 +15,14 @@
     analyze                router analyses: NMI(attribute, expert), expert load, route Jaccard
     report-formal-study    probe table + cloze table + router report of one study directory
     audit-synbios-repository   lineage audit of dataset / cache / pipeline directories
+    oracle-first-token     insert the true first token into the Q inputs and re-read the unchanged Q-whole heads
+    ground-truth-first-whole   train one P-whole probe on prefixes extended by the true first token (resumable)
+    ground-truth-first-report  table of a ground-truth-first run against the original P probes
+    company-relation       exposure-position curve fits of the paired attributes (company / company city)
+    probe-batch-benchmark  step time and peak memory of probe steps per batch size, on the longest examples
+    summarize-probe-batch-benchmarks   merge benchmark runs of several devices into one recommendation
+    compare-formal-studies single vs multi5+permute probe studies: tidy table, headline means, Markdown
+    diagnostic-report      oracle and routing evidence of both conditions side by side
 
 Evaluation and probing always build the model with the library (``torch``) operator back end in fp32 and load only the
 exported ``model.pt`` (reference: scripts/synbios_moe.py:141-168), independent of how training was sharded.
@@ -319,6 +327,118 @@ def cmd_audit(args) -> int:
     return 0 if verdict["ok"] else 1
 
 
+def cmd_oracle_first_token(args) -> int:
+    from experiments.synbios_moe.mechanisms.oracle_first_token import oracle_first_token_validation
+
+    codec = _codec(args)
+    sink = EventSink(args.log_dir, args.quiet)
+    model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
+    attributes = tuple(args.attributes.split(",")) if args.attributes else None
+    kwargs = {"attributes": attributes} if attributes else {}
+    summary = oracle_first_token_validation(model, data_root=args.data, cache_root=args.probe_cache, probe_dir=args.probe_dir,
+                                            output_dir=args.output, device=args.device, batch_size=args.batch_size,
+                                            max_examples=args.max_examples,
+                                            progress=lambda name, done: sink({"event": "oracle_progress", "attribute": name, "done": done}),
+                                            **kwargs)
+    print(json.dumps(summary["overall"]))
+    return 0
+
+
+def cmd_ground_truth_first_whole(args) -> int:
+    from experiments.synbios_moe.artifact_io import write_json
+    from experiments.synbios_moe.mechanisms.first_token_intervention import train_ground_truth_first_whole_probe
+    from experiments.synbios_moe.probes.model import _atomic_torch_save, CHECKPOINT_VERSION
+
+    codec = _codec(args)
+    sink = EventSink(args.log_dir, args.quiet)
+    model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
+    result = train_ground_truth_first_whole_probe(
+        model, cache_root=args.probe_cache, probe_dir=args.probe_dir, attribute=args.attribute, codec=codec, device=args.device,
+        batch_size=args.batch_size, evaluation_batch_size=args.evaluation_batch_size, steps=args.steps, seed=args.seed,
+        recovery_checkpoint=args.recovery_checkpoint, checkpoint_interval_steps=args.checkpoint_interval_steps,
+        resume=args.resume_probe, max_validation_examples=args.max_validation_examples, on_event=sink)
+    out = Path(args.output)
+    state = result.pop("probe_state")
+    _atomic_torch_save({"version": CHECKPOINT_VERSION, "identity": result["identity"], "probe": state}, out.with_suffix(".pt"))
+    write_json(out, result)          # the marker is written last
+    print(json.dumps({"attribute": args.attribute, "accuracy_by_position": result["whole_accuracy_validation_by_source_position"]}))
+    return 0
+
+
+def cmd_ground_truth_first_report(args) -> int:
+    from experiments.synbios_moe.mechanisms.intervention_report import summarize_ground_truth_first_whole
+
+    summary = summarize_ground_truth_first_whole(args.run_dir, args.probe_dir, args.output)
+    print(json.dumps({k: summary[k] for k in ("attributes_reported", "attributes_missing", "mean_gain_points")}))
+    return 0
+
+
+def cmd_company_relation(args) -> int:
+    from experiments.synbios_moe.mechanisms.company_relation import fit_company_pair, load_position_curves
+
+    summary = fit_company_pair(load_position_curves(args.input_csv, condition=args.condition), args.output)
+    print(json.dumps({k: summary[k] for k in ("pair_mean_gain", "unpaired_max_gain")}))
+    return 0
+
+
+def cmd_probe_batch_benchmark(args) -> int:
+    from experiments.synbios_moe.artifact_io import write_json
+    from experiments.synbios_moe.probes.batch_benchmark import benchmark_probe_batches, parse_batch_sizes
+    from experiments.synbios_moe.probes.dataset import CachedProbeDataset
+    from experiments.synbios_moe.probes.model import DEFAULT_RANK
+
+    codec = _codec(args)
+    sink = EventSink(args.log_dir, args.quiet)
+    model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
+    runs = []
+    for kind in args.kinds.split(","):
+        split = "train" if args.mode == "training" else "validation"
+        data = CachedProbeDataset(args.probe_cache, kind=kind, attribute=args.attribute, target=args.target, split=split)
+        if args.ground_truth_first:
+            if kind != "p":
+                continue
+            from experiments.synbios_moe.mechanisms.first_token_intervention import prepare_ground_truth_first_whole_data
+
+            prepared = prepare_ground_truth_first_whole_data(cache_root=args.probe_cache, probe_dir=args.probe_dir,
+                                                             attribute=args.attribute, codec=codec)
+            data = prepared.train_data if args.mode == "training" else prepared.validation_data
+        sizes = parse_batch_sizes(args.p_batch_sizes if kind == "p" else args.q_batch_sizes)
+        sizes = tuple(s for s in sizes if s <= len(data)) or (min(len(data), sizes[0]),)
+        runs.append(benchmark_probe_batches(
+            model, data, kind=kind, num_classes=len(data.class_names), rank=args.rank or DEFAULT_RANK[kind], batch_sizes=sizes,
+            device=args.device, mode=args.mode, warmup_steps=args.warmup_steps, measure_steps=args.measure_steps,
+            memory_limit_percent=args.memory_limit_percent, on_result=lambda rec, k=kind: sink({"event": "probe_batch", "kind": k, **rec})))
+    write_json(args.output, {"attribute": args.attribute, "target": args.target, "ground_truth_first": bool(args.ground_truth_first),
+                             "benchmarks": runs})
+    print(json.dumps({r["kind"]: r["recommended_capacity_batch_size"] for r in runs}))
+    return 0
+
+
+def cmd_summarize_probe_batch_benchmarks(args) -> int:
+    from experiments.synbios_moe.artifact_io import write_json
+    from experiments.synbios_moe.probes.batch_benchmark import summarize_probe_benchmarks
+
+    summary = summarize_probe_benchmarks(args.results)
+    write_json(args.output, summary)
+    print(json.dumps({k: v["recommended_batch_size"] for k, v in summary["recommendations"].items()}))
+    return 0
+
+
+def cmd_compare_formal_studies(args) -> int:
+    from experiments.synbios_moe.probes.comparison_report import build_formal_report_artifacts
+
+    out = build_formal_report_artifacts(args.single, args.multi, args.output, single_cache=args.single_cache, multi_cache=args.multi_cache)
+    print(json.dumps(out["headline"]["delta_multi_minus_single"]))
+    return 0
+
+
+def cmd_diagnostic_report(args) -> int:
+    from experiments.synbios_moe.mechanisms.comparison_report import build_diagnostic_report_artifacts
+
+    print(json.dumps(build_diagnostic_report_artifacts({"single": args.single, "multi5_permute": args.multi}, args.output)))
+    return 0
+
+
 # ---------------------------------------------------------------------------------------------------------
 # argument tree
 # ---------------------------------------------------------------------------------------------------------
@@ -393,6 +513,44 @@ def build_parser() -> argparse.ArgumentParser:
     p = sub.add_parser("report-formal-study"); p.add_argument("root"); p.add_argument("--output", required=True); p.set_defaults(func=cmd_report)
     p = sub.add_parser("audit-synbios-repository"); p.add_argument("--data"); p.add_argument("--probe-cache"); p.add_argument("--pipeline")
     p.set_defaults(func=cmd_audit)
+
+    p = sub.add_parser("oracle-first-token"); common(p)
+    p.add_argument("--data", required=True); p.add_argument("--probe-cache", required=True); p.add_argument("--probe-dir", required=True)
+    p.add_argument("--output", required=True); p.add_argument("--attributes"); p.add_argument("--batch-size", type=int, default=256)
+    p.add_argument("--max-examples", type=int); p.set_defaults(func=cmd_oracle_first_token)
+
+    p = sub.add_parser("ground-truth-first-whole"); common(p)
+    p.add_argument("--probe-cache", required=True); p.add_argument("--probe-dir", required=True); p.add_argument("--output", required=True)
+    p.add_argument("--attribute", required=True); p.add_argument("--steps", type=int, default=3000); p.add_argument("--seed", type=int, default=1337)
+    p.add_argument("--batch-size", type=int, default=50); p.add_argument("--evaluation-batch-size", type=int, default=256)
+    p.add_argument("--recovery-checkpoint"); p.add_argument("--checkpoint-interval-steps", type=int)
+    p.add_argument("--resume-probe", action=argparse.BooleanOptionalAction, default=True)
+    p.add_argument("--max-validation-examples", type=int); p.set_defaults(func=cmd_ground_truth_first_whole)
+
+    p = sub.add_parser("ground-truth-first-report"); p.add_argument("--run-dir", required=True); p.add_argument("--probe-dir", required=True)
+    p.add_argument("--output"); p.set_defaults(func=cmd_ground_truth_first_report)
+
+    p = sub.add_parser("company-relation"); p.add_argument("--input-csv", required=True); p.add_argument("--output", required=True)
+    p.add_argument("--condition", default="multi5_permute"); p.set_defaults(func=cmd_company_relation)
+
+    p = sub.add_parser("probe-batch-benchmark"); common(p)
+    p.add_argument("--probe-cache", required=True); p.add_argument("--output", required=True); p.add_argument("--probe-dir")
+    p.add_argument("--attribute", default="university"); p.add_argument("--target", choices=("first", "whole"), default="whole")
+    p.add_argument("--kinds", default="p,q"); p.add_argument("--mode", choices=("training", "validation"), default="training")
+    p.add_argument("--p-batch-sizes", default="25,50,100,200"); p.add_argument("--q-batch-sizes", default="100,200,400,800")
+    p.add_argument("--rank", type=int); p.add_argument("--warmup-steps", type=int, default=3); p.add_argument("--measure-steps", type=int, default=10)
+    p.add_argument("--memory-limit-percent", type=float, default=92.0); p.add_argument("--ground-truth-first", action="store_true")
+    p.set_defaults(func=cmd_probe_batch_benchmark)
+
+    p = sub.add_parser("summarize-probe-batch-benchmarks"); p.add_argument("results", nargs="+"); p.add_argument("--output", required=True)
+    p.set_defaults(func=cmd_summarize_probe_batch_benchmarks)
+
+    p = sub.add_parser("compare-formal-studies"); p.add_argument("--single", required=True); p.add_argument("--multi", required=True)
+    p.add_argument("--single-cache", required=True); p.add_argument("--multi-cache", required=True); p.add_argument("--output", required=True)
+    p.set_defaults(func=cmd_compare_formal_studies)
+
+    p = sub.add_parser("diagnostic-report"); p.add_argument("--single", required=True); p.add_argument("--multi", required=True)
+    p.add_argument("--output", required=True); p.set_defaults(func=cmd_diagnostic_report)
     return ap
 
 

@@ -92,3 +92,58 @@ def test_prepare_data_cli_and_training_on_shards(tmp_path):
     run([str(ROOT / "scripts" / "train.py"), "--config", "run.yaml", "--model-config", str(ROOT / "configs" / "model_debug_dense.yaml"),
          "--device", "cpu"], tmp_path)
     assert len([e for e in events(tmp_path) if e["event"] == "train"]) == 3
+
+
+def test_walkthrough_runner_records_cells_and_fails_on_errors(tmp_path):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    runner = [sys.executable, str(root / "scripts" / "run_server_notebook.py")]
+    good = tmp_path / "good.py"
+    good.write_text("# %% first\nx = 2\nprint('x is', x)\n# %% second\nassert x == 2\nprint('done')\n")
+    done = subprocess.run([*runner, str(good), "--output", str(tmp_path / "good.json"), "--quiet"], capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr
+    rec = json.loads((tmp_path / "good.json").read_text())
+    assert rec["cells"] == 2 and rec["failed_cells"] == [] and rec["records"][0]["stdout"] == "x is 2\n"
+    notebook = {"cells": [{"cell_type": "markdown", "source": ["# title"]},
+                          {"cell_type": "code", "source": ["%matplotlib inline\n", "y = 1\n"], "outputs": []},
+                          {"cell_type": "code", "source": "raise ValueError('boom')", "outputs": []},
+                          {"cell_type": "code", "source": "print('never reached')", "outputs": []}], "metadata": {}, "nbformat": 4}
+    bad = tmp_path / "bad.ipynb"
+    bad.write_text(json.dumps(notebook))
+    done = subprocess.run([*runner, str(bad), "--output", str(tmp_path / "bad.json"), "--executed-notebook", str(tmp_path / "bad.out.ipynb"),
+                           "--quiet"], capture_output=True, text=True)
+    assert done.returncode == 1
+    rec = json.loads((tmp_path / "bad.json").read_text())
+    assert rec["executed"] == 2 and rec["failed_cells"] == [1] and "ValueError: boom" in rec["records"][1]["error"]
+    executed = json.loads((tmp_path / "bad.out.ipynb").read_text())
+    assert executed["cells"][2]["outputs"][0]["output_type"] == "error"
+
+
+def test_ground_truth_first_audit_lists_every_violation(tmp_path):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    rec = {"protocol": "ground_truth_first_whole_rank_matched_v1", "ground_truth_first_token": True, "backbone_parameters_updated": False,
+           "target": "whole", "identity": {"kind": "p", "rank": 2, "steps": 20}, "reference_rank": 2, "steps": 20, "final_loss": 1.5,
+           "resumed_from_step": 10, "whole_accuracy_validation_by_source_position": [0.5] * 6,
+           "whole_correct_validation_by_source_position": [2] * 6, "whole_total_validation_by_source_position": [4] * 6,
+           "first_token_text": {"32": " "}}
+    path = tmp_path / "p_university.json"
+    path.write_text(json.dumps(rec))
+    path.with_suffix(".pt").write_bytes(b"x")
+    cmd = [sys.executable, str(root / "scripts" / "audit_ground_truth_first_probe.py"), str(path), "--expect-resumed-from", "10"]
+    done = subprocess.run(cmd, capture_output=True, text=True)
+    assert done.returncode == 0 and json.loads(done.stdout)["ok"], done.stdout + done.stderr
+    rec.update(backbone_parameters_updated=True, resumed_from_step=None)
+    rec["whole_total_validation_by_source_position"] = [4, 4, 4, 4, 4, 9]
+    path.write_text(json.dumps(rec))
+    done = subprocess.run(cmd, capture_output=True, text=True)
+    errors = json.loads(done.stdout)["errors"]
+    assert done.returncode == 1 and len(errors) >= 3 and any("frozen" in e for e in errors) and any("resumed" in e for e in errors)

@@ -1,0 +1,229 @@
+"""SynBioS interventions and reports on CPU: byte codec, tiny MoE model, a handful of probe steps."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+CLI = [sys.executable, str(ROOT / "scripts" / "synbios_moe.py")]
+MODEL = {"vocab_size": 257, "seq_len": 512, "n_layers": 2, "n_heads": 2, "hidden_size": 32, "intermediate_size": 32,
+         "ffn_type": "moe", "num_experts": 4, "experts_per_token": 2, "dropout": 0.0}
+
+
+def run(*args, timeout=900):
+    done = subprocess.run([*CLI, *args], capture_output=True, text=True, timeout=timeout)
+    assert done.returncode == 0, done.stdout[-1500:] + done.stderr[-2500:]
+    return done.stdout
+
+
+@pytest.fixture(scope="module")
+def studies(tmp_path_factory):
+    """Two matched studies (single, multi5+permute) of the same 20 people, each with the probe heads the mechanisms need."""
+
+    root = tmp_path_factory.mktemp("mechanisms")
+    (root / "model.yaml").write_text(json.dumps({"model": MODEL}))
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+
+    torch.manual_seed(0)
+    model = MiniTransformer(ModelConfig(**MODEL), get_ops_backend("torch"), activation_dtype=torch.float32)
+    torch.save(model.state_dict(), root / "model.pt")
+    out = {"root": root, "model_config": str(root / "model.yaml"), "checkpoint": str(root / "model.pt")}
+    base = ["--model-config", out["model_config"], "--checkpoint", out["checkpoint"], "--codec", "bytes", "--device", "cpu", "--quiet"]
+    for condition, variant in (("single", "single"), ("multi5_permute", "multi5+permute")):
+        data, cache, probes = root / condition / "data", root / condition / "cache", root / condition / "probes"
+        run("prepare", "--output", str(data), "--variant", variant, "--num-people", "20", "--codec", "bytes", "--quiet")
+        run("cache-probes", "--data", str(data), "--output", str(cache), "--codec", "bytes")
+        for kind, attribute, target in (("q", "university", "first"), ("q", "university", "whole"), ("p", "university", "first"),
+                                        ("p", "university", "whole")):
+            run("probe", *base, "--data", str(data), "--probe-cache", str(cache), "--kind", kind, "--attribute", attribute,
+                "--target", target, "--steps", "3", "--batch-size", "4", "--evaluate-train",
+                "--output", str(probes / "training" / f"{kind}-{attribute}-{target}.json"))
+        out[condition] = {"data": data, "cache": cache, "probes": probes}
+    out["base"] = base
+    return out
+
+
+def test_insertion_and_summary_arithmetic():
+    from experiments.synbios_moe.mechanisms.oracle_first_token import insert_oracle_first_token, summarize_oracle_rows
+
+    assert insert_oracle_first_token([256, 10, 11, 256], 32, 256) == [256, 10, 11, 32, 256]
+    with pytest.raises(ValueError):
+        insert_oracle_first_token([256, 10, 11], 32, 256)
+    rows = [{"whole_before_correct": b, "whole_after_correct": a} for b, a in ((0, 1), (0, 0), (0, 1), (1, 1), (1, 0))]
+    s = summarize_oracle_rows(rows)
+    assert s["examples"] == 5 and s["baseline_errors"] == 3 and s["recovered_errors"] == 2 and s["harmed_correct"] == 1
+    assert s["recovery_rate"] == pytest.approx(2 / 3) and s["harm_rate"] == 0.5 and s["accuracy_delta"] == pytest.approx(0.2)
+    assert summarize_oracle_rows([])["accuracy_before"] == 0.0
+
+
+def test_oracle_first_token_runs_on_unchanged_heads(studies):
+    s = studies["multi5_permute"]
+    out = studies["root"] / "oracle"
+    run("oracle-first-token", *studies["base"], "--data", str(s["data"]), "--probe-cache", str(s["cache"]), "--probe-dir", str(s["probes"]),
+        "--output", str(out), "--attributes", "university", "--batch-size", "7")
+    summary = json.loads((out / "summary.json").read_text())
+    assert summary["protocol"] == "q_whole_oracle_first_token_v1" and summary["parameters_updated"] is False
+    held_out = int((np.load(s["cache"] / "profile_splits.npy") == 1).sum())
+    assert summary["overall"]["examples"] == held_out == summary["attributes"][0]["examples"]
+    records = (out / "records.csv").read_text().splitlines()
+    assert len(records) == held_out + 1 and "whole_after_correct" in records[0]
+
+
+def test_ground_truth_first_inputs_and_training(studies, tmp_path):
+    from experiments.synbios_moe.codec import get_codec
+    from experiments.synbios_moe.mechanisms.first_token_intervention import (GroundTruthFirstWholeDataset, build_ground_truth_first_input,
+                                                                             first_token_text, prepare_ground_truth_first_whole_data)
+    from experiments.synbios_moe.probes.dataset import CachedProbeDataset, ProbeItem
+
+    codec = get_codec("bytes")
+    assert first_token_text("32", codec) == (32, " ")
+    for bad in ("x", "256", "65"):          # not an id, the EOS, no leading space
+        with pytest.raises(ValueError):
+            first_token_text(bad, codec)
+    item = ProbeItem(np.arange(20), np.asarray([2, 5, 8, 11, 14, 17]), 3)
+    rebuilt = build_ground_truth_first_input(item, 1, 99)
+    assert rebuilt.input_ids.tolist() == [0, 1, 2, 3, 4, 5, 99] and rebuilt.positions.tolist() == [6] and rebuilt.label == 3
+    s = studies["multi5_permute"]
+    prepared = prepare_ground_truth_first_whole_data(cache_root=s["cache"], probe_dir=s["probes"], attribute="university", codec=codec)
+    whole = CachedProbeDataset(s["cache"], kind="p", attribute="university", target="whole", split="train")
+    data = prepared.train_data
+    assert isinstance(data, GroundTruthFirstWholeDataset) and len(data) == 6 * len(whole) and prepared.rank == 2
+    sample = data[7]                                         # source 1, position 1
+    src = whole[1]
+    assert sample.label == src.label and sample.input_ids[-1] == 32
+    assert sample.input_ids[:-1].tolist() == src.input_ids[: src.positions[1] + 1].tolist()
+    assert max(len(i.input_ids) for i in data.longest(3)) == max(len(data[i].input_ids) for i in range(len(data)))
+    with pytest.raises(ValueError):
+        prepare_ground_truth_first_whole_data(cache_root=s["cache"], probe_dir=s["probes"], attribute="birth_date", codec=codec)
+    # the CLI trains it (resumable) and the report joins it with the original P probes
+    out = tmp_path / "gtf"
+    run("ground-truth-first-whole", *studies["base"], "--probe-cache", str(s["cache"]), "--probe-dir", str(s["probes"]),
+        "--attribute", "university", "--steps", "3", "--batch-size", "4", "--output", str(out / "university.json"))
+    rec = json.loads((out / "university.json").read_text())
+    assert rec["protocol"] == "ground_truth_first_whole_rank_matched_v1" and len(rec["whole_accuracy_validation_by_source_position"]) == 6
+    assert sum(rec["whole_total_validation_by_source_position"]) == 6 * len(prepared.validation_data.whole_data)
+    assert (out / "university.pt").is_file()
+    run("ground-truth-first-report", "--run-dir", str(out), "--probe-dir", str(s["probes"]), "--output", str(out / "report"))
+    summary = json.loads((out / "report" / "summary.json").read_text())
+    assert summary["attributes_reported"] == ["university"] and "major" in summary["attributes_missing"]
+    assert "| university |" in (out / "report" / "report.md").read_text()
+
+
+def test_exposure_curve_fit_recovers_known_parameters(tmp_path):
+    from experiments.synbios_moe.mechanisms.company_relation import fit_company_pair, fit_exposure_curve, load_position_curves, paired_exposure
+    from experiments.synbios_moe.pretraining.dataset import WHOLE_ATTRIBUTES
+
+    x = paired_exposure()
+    assert x.tolist() == pytest.approx([0.0, 1 / 3, 0.6, 0.8, 14 / 15, 1.0])
+    fit = fit_exposure_curve(0.2 + 0.7 * x, x)
+    assert fit["baseline"] == pytest.approx(0.2) and fit["gain"] == pytest.approx(0.7) and fit["rmse"] < 1e-12
+    assert fit["saturation"] == pytest.approx(0.9) and fit["leave_one_out_rmse"] < 1e-10
+    rows = ["condition,split,kind,target,attribute,position,accuracy"]
+    for attribute in WHOLE_ATTRIBUTES:
+        gain = 0.6 if attribute in ("company", "company_city") else 0.05
+        rows += [f"multi5_permute,person_held_out_validation,p,whole,{attribute},{k},{0.1 + gain * x[k]}" for k in range(6)]
+        rows += [f"single,person_held_out_validation,p,whole,{attribute},{k},0.0" for k in range(6)]
+    (tmp_path / "tidy.csv").write_text("\n".join(rows) + "\n")
+    summary = fit_company_pair(load_position_curves(tmp_path / "tidy.csv", condition="multi5_permute"), tmp_path / "out")
+    assert summary["pair_mean_gain"] == pytest.approx(0.6) and summary["unpaired_max_gain"] == pytest.approx(0.05)
+    assert (tmp_path / "out" / "company_relation_metrics.csv").read_text().count("\n") == 6
+    with pytest.raises(ValueError):
+        load_position_curves(tmp_path / "tidy.csv", condition="nothing")
+
+
+def test_probe_batch_benchmark_and_merge(studies, tmp_path):
+    s = studies["multi5_permute"]
+    a, b = tmp_path / "gpu0.json", tmp_path / "gpu1.json"
+    for out in (a, b):
+        run("probe-batch-benchmark", *studies["base"], "--probe-cache", str(s["cache"]), "--attribute", "university", "--target", "whole",
+            "--p-batch-sizes", "2,4", "--q-batch-sizes", "2,4", "--warmup-steps", "1", "--measure-steps", "2", "--output", str(out))
+    rec = json.loads(a.read_text())
+    assert [r["kind"] for r in rec["benchmarks"]] == ["p", "q"]
+    for bench in rec["benchmarks"]:
+        assert [r["batch_size"] for r in bench["results"]] == [2, 4] and all(r["status"] == "completed" for r in bench["results"])
+        assert bench["recommended_capacity_batch_size"] in (2, 4)
+    run("summarize-probe-batch-benchmarks", str(a), str(b), "--output", str(tmp_path / "merged.json"))
+    merged = json.loads((tmp_path / "merged.json").read_text())
+    assert merged["recommendations"]["p_training"]["replicas"] == 2 and merged["recommendations"]["q_training"]["recommended_batch_size"] in (2, 4)
+    from experiments.synbios_moe.probes.batch_benchmark import parse_batch_sizes
+
+    assert parse_batch_sizes("8, 2,8,4") == (2, 4, 8)
+    with pytest.raises(ValueError):
+        parse_batch_sizes("4,0")
+
+
+def test_formal_comparison_requires_matched_complete_studies(studies, tmp_path):
+    from experiments.synbios_moe.probes import comparison_report as cr
+
+    # a complete study: every one of the 22 heads present (copies of the trained ones with the identity rewritten)
+    def complete(condition):
+        src = studies[condition]["probes"]
+        dst = tmp_path / condition
+        (dst / "training").mkdir(parents=True)
+        from experiments.synbios_moe.probes.dataset import probe_tasks
+
+        jobs = {}
+        for kind in ("p", "q"):
+            template = json.loads((src / "training" / f"{kind}-university-whole.json").read_text())
+            for t in probe_tasks():
+                rec = json.loads(json.dumps(template))
+                rec["identity"].update({"kind": kind, "attribute": t.attribute, "target": t.target})
+                name = f"{kind}-{t.attribute}-{t.target}"
+                (dst / "training" / f"{name}.json").write_text(json.dumps(rec))
+                jobs[name] = {"status": "done", "phase": "training"}
+        (dst / "pipeline.json").write_text(json.dumps({"identity": "x", "jobs": jobs}))
+        return dst
+
+    single, multi = complete("single"), complete("multi5_permute")
+    out = tmp_path / "report"
+    run("compare-formal-studies", "--single", str(single), "--multi", str(multi), "--single-cache", str(studies["single"]["cache"]),
+        "--multi-cache", str(studies["multi5_permute"]["cache"]), "--output", str(out))
+    head = json.loads((out / "headline_metrics.json").read_text())
+    assert set(head) == {"single", "multi5_permute", "delta_multi_minus_single", "published_q_reference_macro_means"}
+    assert len(head["single"]) == 6
+    tidy = (out / "probe_metrics_tidy.csv").read_text().splitlines()
+    # 2 conditions x (11 P heads x 6 + 11 Q heads x 1) positions x 2 splits (validation and train recall)
+    assert len(tidy) - 1 == 2 * (11 * 6 + 11) * 2
+    # swapped conditions, different people and different hyper-parameters are all refused
+    a = cr.load_formal_run("single", single, studies["single"]["cache"])
+    b = cr.load_formal_run("multi5_permute", multi, studies["multi5_permute"]["cache"])
+    cr.validate_matched_runs(a, b)
+    with pytest.raises(ValueError, match="variant"):
+        cr.validate_matched_runs(cr.load_formal_run("single", multi, studies["multi5_permute"]["cache"]), b)
+    rec = json.loads((multi / "training" / "q-major-whole.json").read_text())
+    rec["identity"]["steps"] = 99
+    (multi / "training" / "q-major-whole.json").write_text(json.dumps(rec))
+    with pytest.raises(ValueError, match="steps differs"):
+        cr.validate_matched_runs(a, cr.load_formal_run("multi5_permute", multi, studies["multi5_permute"]["cache"]))
+    (multi / "training" / "q-major-whole.json").unlink()
+    with pytest.raises(ValueError, match="no training result"):
+        cr.load_formal_run("multi5_permute", multi, studies["multi5_permute"]["cache"])
+
+
+def test_diagnostic_report_checks_its_inputs(studies, tmp_path):
+    roots = {}
+    for condition in ("single", "multi5_permute"):
+        s = studies[condition]
+        out = tmp_path / condition
+        run("oracle-first-token", *studies["base"], "--data", str(s["data"]), "--probe-cache", str(s["cache"]), "--probe-dir", str(s["probes"]),
+            "--output", str(out / "oracle"), "--attributes", "university")
+        run("analyze", *studies["base"], "--data", str(s["data"]), "--output", str(out / "routes.json"), "--max-items", "8")
+        roots[condition] = out
+    summary = json.loads(run("diagnostic-report", "--single", str(roots["single"]), "--multi", str(roots["multi5_permute"]),
+                             "--output", str(tmp_path / "diag")))
+    assert summary["route_layers"] == 2 and set(summary["oracle_overall"]) == {"single", "multi5_permute"}
+    assert "nmi_attribute_expert_delta" in (tmp_path / "diag" / "routes_by_layer.csv").read_text().splitlines()[0]
+    # an edited summary (overall row no longer the mean of its attribute rows) is refused
+    path = roots["single"] / "oracle" / "summary.json"
+    rec = json.loads(path.read_text())
+    rec["overall"]["examples"] += 1
+    path.write_text(json.dumps(rec))
+    from experiments.synbios_moe.mechanisms.comparison_report import load_diagnostic_evidence
+
+    with pytest.raises(ValueError, match="cover"):
+        load_diagnostic_evidence(roots)
