@@ -42,7 +42,7 @@ def main() -> int:
             "run": {"name": "walkthrough", "seed": 7}, "backend": {"ops": "torch"}, "parallel": {"strategy": "single"},
             "train": {"batch_size": 4, "max_steps": 2, "epochs": 50, "precision": "fp32", "log_interval": 1, "use_fused_loss": True},
             "optimizer": {"lr": 1e-3}, "lr_scheduler": {"schedule": "constant", "warmup_steps": 0},
-            "data": {"source": "token_shards", "path": str(data / "tokens"), "num_workers": 0, "persistent_workers": False,
+            "data": {"source": "token_shards", "path": str(data / "token_shards"), "num_workers": 0, "persistent_workers": False,
                      "pin_memory": False, "packing": "contiguous"},
             "checkpoint": {"directory": str(work / "ckpt"), "every_epochs": 1, "save_final": True, "export_model": True, "keep_last": 3},
             "logging": {"console": False, "jsonl": True, "tensorboard": False, "log_dir": str(work / "runs")}}))

@@ -107,11 +107,11 @@ def cmd_prepare(args) -> int:
         from experiments.synbios_moe.codec import ShardTokenizer, get_codec
 
         tokenizer = ShardTokenizer(get_codec(args.codec))
-    # one biography per line; nothing is filtered (min_chars=1) and everything trains (validation_fraction=0): the held-out
-    # half of the PEOPLE is a probe split, not a language-model validation split
-    shards = prepare_token_shards([out / "biographies.txt"], output_dir=out / "tokens", tokenizer=tokenizer,
+    # one document per biography (each starts with the boundary token); nothing is filtered (min_chars=1) and everything
+    # trains (validation_fraction=0): the held-out half of the PEOPLE is a probe split, not a language-model validation split
+    shards = prepare_token_shards([out / "biographies.jsonl"], output_dir=out / "token_shards", tokenizer=tokenizer,
                                   cleaning=CleaningConfig(min_chars=1, exact_dedup=False), validation_fraction=0.0,
-                                  max_shard_tokens=args.max_shard_tokens)
+                                  max_shard_tokens=args.max_shard_tokens, split_seed=args.seed)
     sink({"event": "shards_written", "path": str(shards)})
     return 0
 
@@ -320,8 +320,19 @@ def cmd_report(args) -> int:
 
 
 def cmd_audit(args) -> int:
-    from experiments.synbios_moe.audit import audit_study
+    from experiments.synbios_moe.audit import audit_study, build_study_audit
 
+    if args.single_data or args.multi_data:     # both conditions of the comparison: lineage files + summary under --output
+        spec = {"single": {"data": args.single_data, "probe_cache": args.single_cache, "pipeline": args.single_pipeline, "model": args.single_model},
+                "multi5_permute": {"data": args.multi_data, "probe_cache": args.multi_cache, "pipeline": args.multi_pipeline,
+                                   "model": args.multi_model}}
+        try:
+            summary = build_study_audit(spec, args.output or "audit")
+        except (ValueError, OSError, KeyError) as exc:
+            print(json.dumps({"status": "failed", "error": str(exc)}))
+            return 1
+        print(json.dumps({"status": summary["status"], "checks": len(summary["checks"])}))
+        return 0
     verdict = audit_study(data_root=args.data, probe_cache=args.probe_cache, pipeline_root=args.pipeline)
     print(json.dumps(verdict, indent=1))
     return 0 if verdict["ok"] else 1
@@ -512,7 +523,10 @@ def build_parser() -> argparse.ArgumentParser:
     p = sub.add_parser("summarize-probes"); p.add_argument("root"); p.add_argument("--output"); p.set_defaults(func=cmd_summarize_probes)
     p = sub.add_parser("report-formal-study"); p.add_argument("root"); p.add_argument("--output", required=True); p.set_defaults(func=cmd_report)
     p = sub.add_parser("audit-synbios-repository"); p.add_argument("--data"); p.add_argument("--probe-cache"); p.add_argument("--pipeline")
-    p.set_defaults(func=cmd_audit)
+    for side in ("single", "multi"):
+        for what in ("data", "cache", "pipeline", "model"):
+            p.add_argument(f"--{side}-{what}")
+    p.add_argument("--output"); p.set_defaults(func=cmd_audit)
 
     p = sub.add_parser("oracle-first-token"); common(p)
     p.add_argument("--data", required=True); p.add_argument("--probe-cache", required=True); p.add_argument("--probe-dir", required=True)

@@ -59,8 +59,8 @@ def test_profiles_are_identical_across_variants_and_spans_are_exact(tmp_path):
 
 
 def test_prepare_writes_shards_and_manifest(study):
-    manifest = json.loads((study["data"] / "tokens" / "manifest.json").read_text())
-    assert manifest["vocab_size"] == 257 and (study["data"] / "tokens" / "train" / "shard_00000.bin").is_file()
+    manifest = json.loads((study["data"] / "token_shards" / "manifest.json").read_text())
+    assert manifest["vocab_size"] == 257 and (study["data"] / "token_shards" / "train" / "shard_00000.bin").is_file()
     assert json.loads((study["data"] / "manifest.json").read_text())["num_biographies"] == 48
 
 

@@ -227,3 +227,28 @@ def test_diagnostic_report_checks_its_inputs(studies, tmp_path):
 
     with pytest.raises(ValueError, match="cover"):
         load_diagnostic_evidence(roots)
+
+
+def test_two_condition_audit_writes_lineage_and_notices_tampering(studies, tmp_path):
+    args = []
+    for side, condition in (("single", "single"), ("multi", "multi5_permute")):
+        s = studies[condition]
+        args += [f"--{side}-data", str(s["data"]), f"--{side}-cache", str(s["cache"]), f"--{side}-model", studies["checkpoint"]]
+    out = json.loads(run("audit-synbios-repository", *args, "--output", str(tmp_path / "audit")))
+    assert out["status"] == "passed" and out["checks"] >= 6
+    lineage = json.loads((tmp_path / "audit" / "dataset_lineage.json").read_text())
+    for condition in ("single", "multi5_permute"):
+        rec = lineage[condition]
+        assert rec["token_shards"]["documents"] == rec["source_dataset"]["biographies"]          # one document per biography
+        assert rec["probe_cache"]["parent_manifest_sha256"] == rec["source_dataset"]["manifest_sha256"]
+        assert (studies[condition]["data"] / "lineage.json").is_file() and (studies[condition]["cache"] / "lineage.json").is_file()
+    assert lineage["single"]["source_dataset"]["profiles_sha256"] == lineage["multi5_permute"]["source_dataset"]["profiles_sha256"]
+    # a shard that changed after the manifest was written is found
+    shard = studies["single"]["data"] / "token_shards" / "train" / "shard_00000.bin"
+    original = shard.read_bytes()
+    try:
+        shard.write_bytes(original[:-2] + b"\x01\x00")
+        done = subprocess.run([*CLI, "audit-synbios-repository", *args, "--output", str(tmp_path / "audit2")], capture_output=True, text=True)
+        assert done.returncode == 1 and "shard_00000.bin differs" in done.stdout
+    finally:
+        shard.write_bytes(original)
