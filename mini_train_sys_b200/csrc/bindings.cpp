@@ -6,9 +6,22 @@
 #include <torch/extension.h>
 
 #include "attention.cuh"
+#include "debug_bounds.cuh"
 #include "comm.cuh"
 #include "gemm_sm100.cuh"
 #include "ops.cuh"
+
+namespace mts {
+namespace dbg {
+namespace {
+std::vector<Collector>& collectors() {
+  static std::vector<Collector> list;      // built on first use: registration happens during static initialisation
+  return list;
+}
+}  // namespace
+void register_bounds_collector(Collector fn) { collectors().push_back(fn); }
+}  // namespace dbg
+}  // namespace mts
 
 namespace {
 
@@ -414,7 +427,7 @@ void moe_gather(const Tensor& x, const Tensor& row_token, Tensor xs, const Tenso
   TORCH_CHECK(xs.size(0) >= row_token.numel(), "sorted buffer smaller than the plan capacity");
   c10::cuda::CUDAGuard guard(x.device());
   check_launch(mts::launch_moe_gather(x.data_ptr(), row_token.data_ptr<int>(), xs.data_ptr(), int(row_token.numel()), int(x.size(1)),
-                                      meta.data_ptr<int>(), cur_stream()), "moe_gather");
+                                      meta.data_ptr<int>(), int(x.size(0)), cur_stream()), "moe_gather");
 }
 
 void moe_combine(const Tensor& y, const Tensor& token_rows, const c10::optional<Tensor>& weights, Tensor out, int64_t K) {
@@ -427,7 +440,7 @@ void moe_combine(const Tensor& y, const Tensor& token_rows, const c10::optional<
   TORCH_CHECK(token_rows.numel() == out.size(0) * K, "token_rows must have T*K entries");
   c10::cuda::CUDAGuard guard(y.device());
   check_launch(mts::launch_moe_combine(y.data_ptr(), token_rows.data_ptr<int>(), w, out.data_ptr(), int(out.size(0)), int(K),
-                                       int(out.size(1)), cur_stream()), "moe_combine");
+                                       int(out.size(1)), int(y.size(0)), cur_stream()), "moe_combine");
 }
 
 void moe_combine_bwd(const Tensor& dout, const Tensor& y, const Tensor& row_token, const Tensor& token_rows, const Tensor& weights,
@@ -483,6 +496,27 @@ void clip_coef(const Tensor& sumsq_in, double max_norm, double extra, Tensor coe
                                      norm_out.data_ptr<float>(), cur_stream()), "clip_coef");
 }
 
+// Out-of-range indices recorded by a bounds-checking build since the last reset: rows of
+// (kernel id, block, thread, index, limit).  Always empty in a release build.  Synchronises the device.
+std::vector<std::vector<int64_t>> debug_bounds_report(bool reset) {
+  std::vector<std::vector<int64_t>> rows;
+  cudaDeviceSynchronize();
+  for (auto fn : mts::dbg::collectors()) {
+    mts::dbg::BoundsRecord buf[mts::dbg::kRingSize];
+    const int n = fn(buf, mts::dbg::kRingSize, reset);
+    for (int i = 0; i < n; ++i) rows.push_back({buf[i].kernel, buf[i].block, buf[i].thread, buf[i].index, buf[i].limit});
+  }
+  return rows;
+}
+
+bool debug_bounds_enabled() {
+#ifdef MTS_DEBUG_BOUNDS
+  return true;
+#else
+  return false;
+#endif
+}
+
 int64_t launch_count() { return int64_t(mts::g_launch_count); }
 
 Tensor status_tensor(int64_t device) { return status_word(int(device)); }
@@ -522,6 +556,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sumsq", &sumsq);
   m.def("clip_coef", &clip_coef);
   m.def("launch_count", &launch_count);
+  m.def("debug_bounds_report", &debug_bounds_report, py::arg("reset") = true);
+  m.def("debug_bounds_enabled", &debug_bounds_enabled);
   m.def("status_tensor", &status_tensor);
   bind_attention(m);
   bind_comm(m);

@@ -17,6 +17,7 @@
 // The reference has no counterpart: it calls torch DDP / FSDP (NCCL) for all of this
 // (minitrain/distributed/ddp.py:54-65, fsdp.py:128-153).
 #include "comm.cuh"
+#include "debug_bounds.cuh"
 #include "ops.cuh"
 #include "ptx_sm100.cuh"
 
@@ -383,6 +384,7 @@ ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__
   for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n_routes; r += warps_per_grid) {
     const int dest = route_dest[r];
     if (dest < 0) continue;
+    if (!MTS_IN_BOUNDS(dbg::KERNEL_EP_PUSH, dest, kMaxPeers) || !MTS_IN_BOUNDS(dbg::KERNEL_EP_PUSH, route_slot[r], cap_rows)) continue;
     const long long dst_row = (long long)src_rank * cap_rows + route_slot[r];
     const uint4* src = reinterpret_cast<const uint4*>(x + (long long)route_token[r] * H);
     uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(recv_rows.p[dest]) + dst_row * H);
@@ -422,7 +424,8 @@ ep_pull_combine_kernel(__nv_bfloat16* __restrict__ out, const int* __restrict__ 
       for (int k = 0; k < K; ++k) {
         const int dest = token_dest[t * K + k];
         uint4 q = make_uint4(0u, 0u, 0u, 0u);
-        if (dest >= 0) {
+        if (dest >= 0 && MTS_IN_BOUNDS(dbg::KERNEL_EP_PULL, dest, kMaxPeers) &&
+            MTS_IN_BOUNDS(dbg::KERNEL_EP_PULL, token_slot[t * K + k], cap_rows)) {
           const long long row = (long long)my_rank * cap_rows + token_slot[t * K + k];
           q = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(rows.p[dest]) + row * H)[v];
         }

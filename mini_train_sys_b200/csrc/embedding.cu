@@ -7,6 +7,7 @@
 // An id outside [0, V) cannot be made to index memory: the row is skipped (forward writes zeros) and the status word is
 // raised to STATUS_BAD_ARGUMENT, which the host reads at its next status check.
 // The reference uses nn.Embedding, i.e. the library gather and `embedding_dense_backward` (minitrain/model/transformer.py:30,76).
+#include "debug_bounds.cuh"
 #include "ops.cuh"
 #include "ptx_sm100.cuh"
 
@@ -25,7 +26,10 @@ embedding_fwd_kernel(const long long* __restrict__ ids, const void* __restrict__
   for (long long t = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
     const long long id = ids[t];
     const bool ok = id >= 0 && id < V;
-    if (!ok && lane == 0 && status != nullptr) atomicMax(status, STATUS_BAD_ARGUMENT);
+    if (!ok && lane == 0) {
+      if (status != nullptr) atomicMax(status, STATUS_BAD_ARGUMENT);
+      (void)MTS_IN_BOUNDS(dbg::KERNEL_EMBEDDING_FWD, id, V);      // bounds-checking builds also record which id it was
+    }
     uint4* dst = reinterpret_cast<uint4*>(out + t * H);
     for (int v = lane; v < vecs; v += 32) {
       uint4 q = make_uint4(0u, 0u, 0u, 0u);
@@ -59,7 +63,10 @@ embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __r
   for (long long t = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
     const long long id = ids[t];
     if (id < 0 || id >= V) {
-      if (lane == 0 && status != nullptr) atomicMax(status, STATUS_BAD_ARGUMENT);
+      if (lane == 0) {
+        if (status != nullptr) atomicMax(status, STATUS_BAD_ARGUMENT);
+        (void)MTS_IN_BOUNDS(dbg::KERNEL_EMBEDDING_BWD, id, V);
+      }
       continue;
     }
     const uint4* src = reinterpret_cast<const uint4*>(dout + t * H);

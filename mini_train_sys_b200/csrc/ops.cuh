@@ -60,11 +60,12 @@ size_t moe_plan_workspace_ints(int T, int K, int E);
 
 // x_sorted[r] = x[row_token[r]] (zeros for padding); only rows below meta[1] are written, plus zero fill
 // up to `capacity_rows` when `zero_tail` is set.
+// `tokens` = rows of x (the extent source indices are checked against in bounds-checking builds).
 cudaError_t launch_moe_gather(const void* x, const int* row_token, void* x_sorted, int capacity_rows, int H,
-                              const int* meta, cudaStream_t stream);
+                              const int* meta, int tokens, cudaStream_t stream);
 // out[t] = sum_k w[t,k] * y[token_rows[t,k]]   (w may be null -> unweighted sum)
 cudaError_t launch_moe_combine(const void* y, const int* token_rows, const void* weights, void* out, int T, int K, int H,
-                               cudaStream_t stream);
+                               int y_rows, cudaStream_t stream);
 // Backward of combine: dys[r] = w * dout[token] ; dweights[t,k] = <dout[t], y[row]> (fp32)
 cudaError_t launch_moe_combine_bwd(const void* dout, const void* y, const int* row_token, const int* token_rows,
                                    const void* weights, void* dys, float* dweights, int T, int K, int H,

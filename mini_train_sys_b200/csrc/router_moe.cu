@@ -7,6 +7,7 @@
 // is preserved inside every expert, and each expert segment is padded to a multiple of 256 rows so
 // that GEMM tiles never straddle two experts and padding rows contribute exact zeros.
 #include "ops.cuh"
+#include "debug_bounds.cuh"
 
 #include <cuda_bf16.h>
 #include <math_constants.h>
@@ -294,13 +295,13 @@ __device__ __forceinline__ uint4 float_to_bf16x8(const float (&v)[8]) {
 // One warp per sorted row.
 __global__ void __launch_bounds__(256)
 moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_token, __nv_bfloat16* __restrict__ xs,
-                  int H, const int* __restrict__ meta) {
+                  int H, const int* __restrict__ meta, int tokens) {
   const int live_rows = meta[1];
   const int lane = threadIdx.x & 31;
   for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < live_rows; row += gridDim.x * 8) {
     const int tok = row_token[row];
     uint4* dst = reinterpret_cast<uint4*>(xs + (long long)row * H);
-    if (tok >= 0) {
+    if (tok >= 0 && MTS_IN_BOUNDS(dbg::KERNEL_MOE_GATHER, tok, tokens)) {
       const uint4* src = reinterpret_cast<const uint4*>(x + (long long)tok * H);
       for (int v = lane; v < H / 8; v += 32) dst[v] = src[v];
     } else {
@@ -312,14 +313,14 @@ moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ r
 // One warp per token: out[t] = sum_k w[t,k] * y[row(t,k)].
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ token_rows,
-                   const __nv_bfloat16* __restrict__ weights, __nv_bfloat16* __restrict__ out, int T, int K, int H) {
+                   const __nv_bfloat16* __restrict__ weights, __nv_bfloat16* __restrict__ out, int T, int K, int H, int y_rows) {
   const int lane = threadIdx.x & 31;
   for (int t = blockIdx.x * 8 + (threadIdx.x >> 5); t < T; t += gridDim.x * 8) {
     for (int v = lane; v < H / 8; v += 32) {
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int k = 0; k < K; ++k) {
         const int row = token_rows[(long long)t * K + k];
-        if (row < 0) continue;
+        if (row < 0 || !MTS_IN_BOUNDS(dbg::KERNEL_MOE_COMBINE, row, y_rows)) continue;
         const float w = weights != nullptr ? __bfloat162float(weights[(long long)t * K + k]) : 1.f;
         float val[8];
         bf16x8_to_float(reinterpret_cast<const uint4*>(y + (long long)row * H)[v], val);
@@ -336,13 +337,13 @@ __global__ void __launch_bounds__(256)
 moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ y,
                        const int* __restrict__ row_token, const int* __restrict__ token_rows,
                        const __nv_bfloat16* __restrict__ weights, __nv_bfloat16* __restrict__ dys,
-                       float* __restrict__ dweights, int K, int H, const int* __restrict__ meta) {
+                       float* __restrict__ dweights, int K, int H, const int* __restrict__ meta, int tokens) {
   const int live_rows = meta[1];
   const int lane = threadIdx.x & 31;
   for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < live_rows; row += gridDim.x * 8) {
     const int tok = row_token[row];
     uint4* dst = reinterpret_cast<uint4*>(dys + (long long)row * H);
-    if (tok < 0) {
+    if (tok < 0 || !MTS_IN_BOUNDS(dbg::KERNEL_MOE_COMBINE_BWD, tok, tokens)) {
       for (int v = lane; v < H / 8; v += 32) dst[v] = make_uint4(0, 0, 0, 0);
       continue;
     }
@@ -419,20 +420,20 @@ cudaError_t launch_moe_plan(const int* indices, int T, int K, int E, int capacit
 }
 
 cudaError_t launch_moe_gather(const void* x, const int* row_token, void* x_sorted, int capacity_rows, int H,
-                              const int* meta, cudaStream_t stream) {
+                              const int* meta, int tokens, cudaStream_t stream) {
   if (H % 8 != 0) return cudaErrorInvalidValue;
   moe_gather_kernel<<<capped_grid(capacity_rows, 8), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), row_token, static_cast<__nv_bfloat16*>(x_sorted), H, meta);
+      static_cast<const __nv_bfloat16*>(x), row_token, static_cast<__nv_bfloat16*>(x_sorted), H, meta, tokens);
   ++g_launch_count;
   return cudaGetLastError();
 }
 
 cudaError_t launch_moe_combine(const void* y, const int* token_rows, const void* weights, void* out, int T, int K, int H,
-                               cudaStream_t stream) {
+                               int y_rows, cudaStream_t stream) {
   if (H % 8 != 0) return cudaErrorInvalidValue;
   moe_combine_kernel<<<capped_grid(T, 8), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), token_rows,
                                                             static_cast<const __nv_bfloat16*>(weights),
-                                                            static_cast<__nv_bfloat16*>(out), T, K, H);
+                                                            static_cast<__nv_bfloat16*>(out), T, K, H, y_rows);
   ++g_launch_count;
   return cudaGetLastError();
 }
@@ -441,10 +442,9 @@ cudaError_t launch_moe_combine_bwd(const void* dout, const void* y, const int* r
                                    const void* weights, void* dys, float* dweights, int T, int K, int H,
                                    int capacity_rows, const int* meta, cudaStream_t stream) {
   if (H % 8 != 0) return cudaErrorInvalidValue;
-  (void)T;
   moe_combine_bwd_kernel<<<capped_grid(capacity_rows, 8), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(y), row_token, token_rows,
-      static_cast<const __nv_bfloat16*>(weights), static_cast<__nv_bfloat16*>(dys), dweights, K, H, meta);
+      static_cast<const __nv_bfloat16*>(weights), static_cast<__nv_bfloat16*>(dys), dweights, K, H, meta, T);
   ++g_launch_count;
   return cudaGetLastError();
 }

@@ -35,6 +35,9 @@ PROFILES = {
     "release": [],
     "trace-gemm": ["-DMTS_GEMM_TRACE"],          # clock64 phase stamps of CTA 0 in the GEMM
     "trace-attention": ["-DMTS_ATTN_TRACE"],     # the same for the attention kernels
+    # data-dependent indices (token ids, routing tables, peer slots) are range-checked; violations are recorded in a ring
+    # that ``ext.debug_bounds_report()`` returns, the access is skipped and nothing traps (see csrc/debug_bounds.cuh)
+    "debug-bounds": ["-DMTS_DEBUG_BOUNDS"],
 }
 
 

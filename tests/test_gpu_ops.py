@@ -561,3 +561,104 @@ def test_embedding_refuses_ids_outside_the_vocabulary_without_touching_memory(nb
         nb.check_kernel_status()
     nb.ext().status_tensor(0).zero_()
     nb.check_kernel_status()
+
+
+# ---- determinism and out-of-bounds guards (what a memory checker would otherwise report) -------------------------------
+
+def _twice(fn):
+    a = fn()
+    torch.cuda.synchronize()
+    b = fn()
+    torch.cuda.synchronize()
+    a, b = (a if isinstance(a, (tuple, list)) else (a,)), (b if isinstance(b, (tuple, list)) else (b,))
+    for i, (x, y) in enumerate(zip(a, b)):
+        assert torch.equal(x, y), f"output {i} differs between two identical launches"
+
+
+def test_kernels_documented_as_deterministic_repeat_bit_for_bit(nb, ops):
+    """Attention (forward and both backward sweeps), RMSNorm, the router, its projection and the routing plan have no
+    atomics on their result paths: two launches on the same inputs must agree exactly."""
+
+    from mini_train_sys_b200.ops import native_attention
+
+    torch.manual_seed(41)
+    e = nb.ext()
+    x = torch.randn(4096, 768, device=DEV, dtype=torch.bfloat16)
+    w = torch.rand(768, device=DEV) + 0.5
+    _twice(lambda: e.rmsnorm_fwd(x, w, 1e-5))
+    y, rstd = e.rmsnorm_fwd(x, w, 1e-5)
+    dy = torch.randn_like(x)
+    _twice(lambda: e.rmsnorm_bwd(dy, x, w, rstd, False, None)[0])
+    wr = 0.02 * torch.randn(8, 768, device=DEV)
+    _twice(lambda: e.router_logits_fwd(x, wr))
+    g = torch.randn(4096, 8, device=DEV)
+    _twice(lambda: tuple(e.router_logits_bwd(g, x, wr, True, True)))
+    logits = torch.randn(4096, 8, device=DEV)
+    _twice(lambda: tuple(e.router_forward(logits, 2, True)[:3]))
+    idx = torch.randint(0, 8, (4096, 2), device=DEV, dtype=torch.int32)
+    _twice(lambda: tuple(e.moe_plan(idx, 8)))
+    q, k, v = (torch.randn(2, 4, 300, 64, device=DEV, dtype=torch.bfloat16).requires_grad_() for _ in range(3))
+    go = torch.randn(2, 4, 300, 64, device=DEV, dtype=torch.bfloat16)
+
+    def attention():
+        out = native_attention.flash_attention(q, k, v, is_causal=True, dropout_p=0.0)
+        return (out.detach(), *torch.autograd.grad(out, (q, k, v), go))
+
+    _twice(attention)
+    nb.check_kernel_status()
+
+
+def test_outputs_stay_inside_their_buffers(nb):
+    """Canary rows around the outputs of the kernels that compute their own addresses (gathers, scatters, tile stores with
+    tails): anything written outside the requested extent shows up as a changed canary."""
+
+    torch.manual_seed(42)
+    e = nb.ext()
+    canary = -123.0
+
+    def framed(rows, cols, dtype):
+        buf = torch.full((rows + 16, cols), canary, device=DEV, dtype=dtype)
+        return buf, buf[8:8 + rows]
+
+    def intact(buf, rows):
+        return bool((buf[:8] == canary).all()) and bool((buf[8 + rows:] == canary).all())
+
+    # GEMM with ragged M / N: 300 x 200 output inside a wider allocation, pitch 208
+    a = torch.randn(300, 136, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(200, 136, device=DEV, dtype=torch.bfloat16)
+    buf, out = framed(300, 208, torch.bfloat16)
+    nb._gemm(a, b, out, 300, 200, 136, ldo=208)
+    torch.cuda.synchronize()
+    assert intact(buf, 300) and bool((out[:, 200:] == canary).all() | (out[:, 200:] == 0).all())
+    assert_close(out[:, :200], a.float() @ b.float().t(), 5e-3, "gemm inside a frame")
+    # expert permutation: gather into a framed buffer, then the weighted combine back
+    tokens, k, experts, hidden = 777, 2, 8, 256
+    idx = torch.randint(0, experts, (tokens, k), device=DEV, dtype=torch.int32)
+    row_token, token_rows, tile_group, group_rows, meta = e.moe_plan(idx, experts)
+    cap = row_token.numel()
+    x = torch.randn(tokens, hidden, device=DEV, dtype=torch.bfloat16)
+    buf, xs = framed(cap, hidden, torch.bfloat16)
+    e.moe_gather(x, row_token, xs, meta)
+    torch.cuda.synchronize()
+    assert intact(buf, cap)
+    live = row_token >= 0
+    assert torch.equal(xs[live], x[row_token[live].long()])
+    wts = torch.rand(tokens, k, device=DEV).to(torch.bfloat16)
+    buf, mixed = framed(tokens, hidden, torch.bfloat16)
+    e.moe_combine(xs, token_rows, wts, mixed, k)
+    torch.cuda.synchronize()
+    assert intact(buf, tokens)
+    # embedding scatter-add into a framed fp32 table
+    ids = torch.randint(0, 100, (5, 33), device=DEV)
+    dout = torch.randn(5, 33, hidden, device=DEV, dtype=torch.bfloat16)
+    buf, table = framed(100, hidden, torch.float32)
+    table.zero_()
+    e.embedding_bwd(ids, dout, table)
+    torch.cuda.synchronize()
+    assert intact(buf, 100)
+    nb.check_kernel_status()
+
+
+def test_release_build_reports_no_bounds_records(nb):
+    e = nb.ext()
+    assert e.debug_bounds_enabled() is False and e.debug_bounds_report() == []

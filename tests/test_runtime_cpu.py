@@ -206,3 +206,26 @@ def test_build_config_profiles_and_cache_key():
     assert release.cache_key() != traced.cache_key() and release.cache_key() == BuildConfig().cache_key()
     with pytest.raises(ValueError):
         BuildConfig.from_env({"MTS_BUILD_PROFILE": "nope"})
+
+
+def test_bounds_checking_profile_compiles_the_kernels_that_use_it(tmp_path):
+    """The ``debug-bounds`` build profile: every source that uses the checked accessor must still compile with it on."""
+
+    import shutil
+    import subprocess
+
+    from mini_train_sys_b200.ops.build import CSRC, PROFILES, BuildConfig
+
+    assert "-DMTS_DEBUG_BOUNDS" in PROFILES["debug-bounds"]
+    assert "-DMTS_DEBUG_BOUNDS" in BuildConfig(profile="debug-bounds").nvcc_flags()
+    assert BuildConfig(profile="debug-bounds").cache_key() != BuildConfig().cache_key()
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not shutil.which(nvcc):
+        pytest.skip("nvcc not available")
+    users = [p for p in sorted(CSRC.glob("*.cu")) if "MTS_IN_BOUNDS" in p.read_text()]
+    assert {p.name for p in users} >= {"embedding.cu", "router_moe.cu", "comm.cu"}
+    for src in users[:2]:     # two translation units are enough to catch a broken header; each takes a few seconds
+        done = subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "--expt-relaxed-constexpr",
+                               "-DMTS_DEBUG_BOUNDS", "-I", str(CSRC), "-c", str(src), "-o", str(tmp_path / (src.stem + ".o"))],
+                              capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
