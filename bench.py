@@ -47,6 +47,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--multimem", action="store_true", help="parallel.comm.use_multimem: gradient sums inside the switch (NVLS)")
     ap.add_argument("--capacity-factor", type=float, default=None, help="parallel.ep.capacity_factor (strategy ep); default: no limit")
     ap.add_argument("--seq-len", type=int, default=None, help="override the model's sequence length")
+    ap.add_argument("--cuda-graph", action=argparse.BooleanOptionalAction, default=True,
+                    help="own arm: replay the device part of every step from one CUDA graph (train.cuda_graph); ignored where the "
+                         "trainer cannot replay (expert parallelism, library engines) and with --comm-timing")
     ap.add_argument("--comm-timing", action="store_true",
                     help="own arm: report, per step, how long the compute stream waited in each communication phase")
     return ap.parse_args()
@@ -179,6 +182,9 @@ def assemble(args, strategy_name: str):
     scheduler = LearningRateScheduler(optimizer, cfg.lr_scheduler, total_steps=100000)
     trainer = Trainer(model, optimizer, device=device, use_fused_loss=True, precision=precision.name,
                       grad_clip_norm=cfg.train.grad_clip_norm, check_finite=True, lr_scheduler=scheduler)
+    want_graph = args.impl == "own" and getattr(args, "cuda_graph", False) and not getattr(args, "comm_timing", False)
+    if want_graph and trainer._graph_unsupported_reason() is None:
+        trainer.cuda_graph = True
     return cfg, trainer, strategy, device, ops, launches
 
 
@@ -222,7 +228,7 @@ def main() -> None:
         sync_all()
         sampler = ClockSampler(device.index)
         sampler.start()
-        count0 = launches()
+        count0 = launches() + int(getattr(trainer, "kernel_launches_replayed", 0))
         t_host = time.perf_counter()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -237,7 +243,8 @@ def main() -> None:
         worst = torch.tensor([ms], dtype=torch.float64, device=device)
         if dist.is_initialized():
             dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-        return float(worst.item()), clocks, launches() - count0, float(last)
+        count1 = launches() + int(getattr(trainer, "kernel_launches_replayed", 0))
+        return float(worst.item()), clocks, count1 - count0, float(last)
 
     # (1) device-resident inputs
     dev_batches = [{k: v.to(device) for k, v in b.items()} for b in host_batches]
@@ -250,6 +257,13 @@ def main() -> None:
 
     def step_e2e(i: int):
         return trainer.train_step(host_batches[i]).item()
+
+    if getattr(trainer, "cuda_graph", False):
+        # set-up, not warm-up: the trainer runs its first steps eagerly and captures the step graph on the next one; do that
+        # here so that neither the warm-up nor the timed region of either pass contains the capture
+        for i in range(trainer.graph_warmup_steps + 1):
+            trainer.train_step(dev_batches[i % len(dev_batches)])
+        sync_all()
 
     # The end-to-end pass runs first: whatever still warms up after the warm-up steps (allocator growth, lazily built buffers
     # of a wrapped engine) falls into its warm-up, and the device-resident pass that follows is steady-state for both arms.
@@ -300,6 +314,7 @@ def main() -> None:
     if args.impl == "own":
         record["config"]["sharding"] = args.sharding if strategy_name == "fsdp" else None
         record["config"]["multimem"] = bool(args.multimem)
+        record["config"]["cuda_graph"] = bool(getattr(trainer, "_graph", None) is not None)
         dropped = trainer.last_metrics.get("moe/dropped_route_fraction")
         if dropped is not None:
             record["dropped_route_fraction"] = round(float(dropped), 5)

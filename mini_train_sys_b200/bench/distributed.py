@@ -120,7 +120,8 @@ def worker(config: str, model_config: str | None, *, strategy: str, ops: str, en
     optimizer = build_optimizer(model, cfg=cfg.optimizer)
     scheduler = LearningRateScheduler(optimizer, cfg.lr_scheduler, total_steps=10**6)
     trainer = Trainer(model, optimizer, device=device, use_fused_loss=cfg.train.use_fused_loss, precision=precision.name,
-                      grad_clip_norm=cfg.train.grad_clip_norm, check_finite=cfg.train.check_finite, lr_scheduler=scheduler)
+                      grad_clip_norm=cfg.train.grad_clip_norm, check_finite=cfg.train.check_finite, lr_scheduler=scheduler,
+                          cuda_graph=cfg.train.cuda_graph)
 
     stream = iter(loader)
 

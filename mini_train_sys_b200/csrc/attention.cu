@@ -161,6 +161,7 @@ struct Params {
   int B, H, S, causal;
   float scale, dropout_p;
   unsigned long long seed;
+  const StepContext* ctx;   // seed is salted with ctx->salt (0 outside graph replay)
   int* status;
   const __nv_bfloat16 *rope_cos, *rope_sin;   // backward: un-rotate dQ / dK while storing them (nullptr = store as is)
 };
@@ -276,7 +277,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int q_row = q0 + r;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const float scale_log2 = p.scale * LOG2E;
-    const Dropout drop = make_dropout(p.dropout_p, p.seed, uint32_t(bh), p.S);
+    const Dropout drop = make_dropout(p.dropout_p, p.seed + p.ctx->salt * kSaltMultiplier, uint32_t(bh), p.S);
     // Running maximum m (log2 units, may lag the true maximum by up to kRescaleSlack), running sum l.
     // O stays in tensor memory: every P V MMA accumulates into it, and it is only read back and rescaled when
     // the maximum of some row of this warp moved by more than the slack (stale maxima keep exp2 arguments
@@ -532,7 +533,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
     const int key = k0 + r;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const float scale_log2 = p.scale * LOG2E;
-    const Dropout drop = make_dropout(p.dropout_p, p.seed, uint32_t(bh), p.S);
+    const Dropout drop = make_dropout(p.dropout_p, p.seed + p.ctx->salt * kSaltMultiplier, uint32_t(bh), p.S);
     const float* lse_bh = p.lse + (long long)bh * p.S;
     const float* delta_bh = p.delta + (long long)bh * p.S;
     const uint32_t keep_shift = uint32_t(key & 3) * 8u;
@@ -791,7 +792,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int q_row = q0 + r;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const float scale_log2 = p.scale * LOG2E;
-    const Dropout drop = make_dropout(p.dropout_p, p.seed, uint32_t(bh), p.S);
+    const Dropout drop = make_dropout(p.dropout_p, p.seed + p.ctx->salt * kSaltMultiplier, uint32_t(bh), p.S);
     const float lse2 = q_row < p.S ? p.lse[(long long)bh * p.S + q_row] * LOG2E : 0.f;
     const float delta = q_row < p.S ? p.delta[(long long)bh * p.S + q_row] : 0.f;
     bool ok = true;
@@ -974,7 +975,8 @@ Params make_params(const AttentionArgs& a) {
   p.dv = static_cast<__nv_bfloat16*>(a.dv.ptr); p.dv_sb = a.dv.sb; p.dv_sh = a.dv.sh; p.dv_ss = a.dv.ss;
   p.lse = a.lse; p.delta = a.delta;
   p.B = a.B; p.H = a.H; p.S = a.S; p.causal = a.causal;
-  p.scale = a.scale; p.dropout_p = a.dropout_p; p.seed = a.seed; p.status = a.status;
+  p.scale = a.scale; p.dropout_p = a.dropout_p; p.seed = a.seed; p.ctx = step_context(); p.status = a.status;
+  if (p.ctx == nullptr) { g_attn_last_error = "step context allocation failed"; }
   p.rope_cos = static_cast<const __nv_bfloat16*>(a.rope_cos);
   p.rope_sin = static_cast<const __nv_bfloat16*>(a.rope_sin);
   return p;

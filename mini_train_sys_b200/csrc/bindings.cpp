@@ -517,6 +517,22 @@ bool debug_bounds_enabled() {
 #endif
 }
 
+// The per-device StepContext block as an int32 tensor (a view of device memory owned by the extension; see ops.cuh for the
+// layout: salt lo/hi, epoch_delta, dynamic_adam, then lr0, lr1, bias corrections as float bits).
+Tensor step_context_tensor(int64_t device) {
+  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+  mts::StepContext* ctx = mts::step_context();
+  TORCH_CHECK(ctx != nullptr, "could not allocate the step context");
+  return torch::from_blob(ctx, {int64_t(sizeof(mts::StepContext) / 4)}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+}
+
+void set_step_context(int64_t device, int64_t salt, int64_t epoch_delta, bool dynamic_adam, double lr0, double lr1, double bc1, double bc2) {
+  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+  check_launch(mts::launch_set_step_context(static_cast<unsigned long long>(salt), static_cast<unsigned int>(epoch_delta),
+                                            dynamic_adam ? 1u : 0u, float(lr0), float(lr1), float(bc1), float(bc2), cur_stream()),
+               "set_step_context");
+}
+
 int64_t launch_count() { return int64_t(mts::g_launch_count); }
 
 Tensor status_tensor(int64_t device) { return status_word(int(device)); }
@@ -556,6 +572,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sumsq", &sumsq);
   m.def("clip_coef", &clip_coef);
   m.def("launch_count", &launch_count);
+  m.def("step_context_tensor", &step_context_tensor);
+  m.def("set_step_context", &set_step_context);
   m.def("debug_bounds_report", &debug_bounds_report, py::arg("reset") = true);
   m.def("debug_bounds_enabled", &debug_bounds_enabled);
   m.def("status_tensor", &status_tensor);

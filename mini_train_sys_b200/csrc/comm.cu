@@ -37,6 +37,12 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
+// Sequence number of this launch: the by-value number plus the per-step offset of graph replay (0 otherwise); 0 stays 0
+// ("do not wait").
+__device__ __forceinline__ uint32_t live_epoch(uint32_t epoch, const StepContext* ctx) {
+  return epoch == 0u ? 0u : epoch + ctx->epoch_delta;
+}
+
 // true when *flag reached `epoch` before the deadline
 __device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch, unsigned long long timeout_ns) {
   if (int32_t(ld_acquire_sys(flag) - epoch) >= 0) return true;
@@ -62,7 +68,8 @@ __device__ __forceinline__ bool block_wait_peers(const uint32_t* my_flags, int w
   return failed == 0;
 }
 
-__global__ void signal_kernel(PeerPtrs flag_bases, int channel, int world, int rank, uint32_t epoch) {
+__global__ void signal_kernel(PeerPtrs flag_bases, int channel, int world, int rank, uint32_t epoch, const StepContext* ctx) {
+  epoch = live_epoch(epoch, ctx);
   const int peer = threadIdx.x;
   if (peer < world) {
     __threadfence_system();
@@ -71,7 +78,8 @@ __global__ void signal_kernel(PeerPtrs flag_bases, int channel, int world, int r
 }
 
 __global__ void wait_kernel(const uint32_t* my_flags, int channel, int world, uint32_t epoch, unsigned long long timeout_ns,
-                            int* status) {
+                            int* status, const StepContext* ctx) {
+  epoch = live_epoch(epoch, ctx);
   block_wait_peers(my_flags + channel * world, world, epoch, timeout_ns, status);
 }
 
@@ -83,7 +91,8 @@ constexpr int kCopyThreads = 128;
 // ---- all-gather (pull) ----
 __global__ void __launch_bounds__(kCopyThreads)
 allgather_pull_kernel(uint4* __restrict__ dst, PeerPtrs shards, long long shard_vec, int world, const uint32_t* my_flags,
-                      int channel, uint32_t epoch, unsigned long long timeout_ns, int* status) {
+                      int channel, uint32_t epoch, unsigned long long timeout_ns, int* status, const StepContext* ctx) {
+  epoch = live_epoch(epoch, ctx);
   if (epoch != 0 && !block_wait_peers(my_flags + channel * world, world, epoch, timeout_ns, status)) return;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (int peer = 0; peer < world; ++peer) {
@@ -115,7 +124,8 @@ __device__ __forceinline__ void block_add_to(float v, float* out) {
 __global__ void __launch_bounds__(kCopyThreads)
 reduce_scatter_pull_kernel(float4* __restrict__ out, PeerPtrs bufs, long long slice_vec_offset, long long n_vec, int world,
                            float scale, float* __restrict__ sumsq, const uint32_t* my_flags, int channel, uint32_t epoch,
-                           unsigned long long timeout_ns, int* status) {
+                           unsigned long long timeout_ns, int* status, const StepContext* ctx) {
+  epoch = live_epoch(epoch, ctx);
   if (epoch != 0 && !block_wait_peers(my_flags + channel * world, world, epoch, timeout_ns, status)) return;
   float sq = 0.f;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -150,7 +160,8 @@ reduce_scatter_pull_kernel(float4* __restrict__ out, PeerPtrs bufs, long long sl
 __global__ void __launch_bounds__(kCopyThreads)
 reduce_scatter_multimem_kernel(float4* __restrict__ out, const float* __restrict__ mc_base, long long slice_vec_offset,
                                long long n_vec, int world, float scale, float* __restrict__ sumsq, const uint32_t* my_flags,
-                               int channel, uint32_t epoch, unsigned long long timeout_ns, int* status) {
+                               int channel, uint32_t epoch, unsigned long long timeout_ns, int* status, const StepContext* ctx) {
+  epoch = live_epoch(epoch, ctx);
   if (epoch != 0 && !block_wait_peers(my_flags + channel * world, world, epoch, timeout_ns, status)) return;
   float sq = 0.f;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
@@ -237,8 +248,11 @@ adamw_push_kernel(float* __restrict__ p, const float* __restrict__ g, float* __r
 __global__ void __launch_bounds__(256)
 adamw_push_table_kernel(const AdamWSegment* __restrict__ segs, int n_segs, long long total_chunks, float lr0, float lr1, float wd0,
                         float wd1, float b1, float b2, float eps, float bc1, float bc2, const float* __restrict__ gscale_ptr,
-                        float static_scale, const int* __restrict__ status) {
+                        float static_scale, const int* __restrict__ status, const StepContext* __restrict__ ctx) {
   if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
+  if (ctx->dynamic_adam != 0u) {     // graph replay: this step's learning rates and bias corrections come from device memory
+    lr0 = ctx->lr0; lr1 = ctx->lr1; bc1 = ctx->bias_correction1; bc2 = ctx->bias_correction2;
+  }
   const float gs = (gscale_ptr != nullptr ? *gscale_ptr : 1.f) * static_scale;
   const float inv_sqrt_bc2 = rsqrtf(bc2);
   for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
@@ -261,7 +275,9 @@ adamw_push_table_kernel(const AdamWSegment* __restrict__ segs, int n_segs, long 
 __global__ void scalar_allreduce_clip_kernel(const float* __restrict__ local_value, PeerPtrs slots, PeerPtrs flag_bases,
                                              const uint32_t* my_flags, int channel, int world, int rank, uint32_t epoch,
                                              unsigned long long timeout_ns, float max_norm, float extra_scale,
-                                             float* __restrict__ coef_out, float* __restrict__ norm_out, int* status) {
+                                             float* __restrict__ coef_out, float* __restrict__ norm_out, int* status,
+                                             const StepContext* ctx) {
+  epoch = live_epoch(epoch, ctx);
   const int peer = threadIdx.x;
   if (peer < world) {
     // slot layout at every rank: [parity][world] so that consecutive steps never reuse a slot that is still being read
@@ -293,7 +309,7 @@ int copy_grid(long long items, int threads, int max_ctas) {
 
 cudaError_t launch_signal(const PeerPtrs& flag_bases, int channel, int world, int rank, unsigned epoch, cudaStream_t stream) {
   if (world > kMaxPeers) return cudaErrorInvalidValue;
-  signal_kernel<<<1, 32, 0, stream>>>(flag_bases, channel, world, rank, epoch);
+  signal_kernel<<<1, 32, 0, stream>>>(flag_bases, channel, world, rank, epoch, step_context());
   ++g_launch_count;
   return cudaGetLastError();
 }
@@ -301,7 +317,7 @@ cudaError_t launch_signal(const PeerPtrs& flag_bases, int channel, int world, in
 cudaError_t launch_wait(const unsigned* my_flags, int channel, int world, unsigned epoch, unsigned long long timeout_ns,
                         int* status, cudaStream_t stream) {
   if (world > kMaxPeers) return cudaErrorInvalidValue;
-  wait_kernel<<<1, 32, 0, stream>>>(my_flags, channel, world, epoch, timeout_ns, status);
+  wait_kernel<<<1, 32, 0, stream>>>(my_flags, channel, world, epoch, timeout_ns, status, step_context());
   ++g_launch_count;
   return cudaGetLastError();
 }
@@ -312,7 +328,7 @@ cudaError_t launch_allgather_pull(void* dst, const PeerPtrs& shards, long long s
   if (world > kMaxPeers || shard_bytes % 16 != 0) return cudaErrorInvalidValue;
   const long long vec = shard_bytes / 16;
   allgather_pull_kernel<<<copy_grid(vec, kCopyThreads * 4, max_ctas), kCopyThreads, 0, stream>>>(
-      static_cast<uint4*>(dst), shards, vec, world, my_flags, channel, epoch, timeout_ns, status);
+      static_cast<uint4*>(dst), shards, vec, world, my_flags, channel, epoch, timeout_ns, status, step_context());
   ++g_launch_count;
   return cudaGetLastError();
 }
@@ -324,10 +340,10 @@ cudaError_t launch_reduce_scatter(float* out, const PeerPtrs& bufs, const float*
   const int grid = copy_grid(n / 4, kCopyThreads * 2, max_ctas);
   if (multicast_base != nullptr)
     reduce_scatter_multimem_kernel<<<grid, kCopyThreads, 0, stream>>>(reinterpret_cast<float4*>(out), multicast_base, slice_offset / 4,
-                                                             n / 4, world, scale, sumsq, my_flags, channel, epoch, timeout_ns, status);
+                                                             n / 4, world, scale, sumsq, my_flags, channel, epoch, timeout_ns, status, step_context());
   else
     reduce_scatter_pull_kernel<<<grid, kCopyThreads, 0, stream>>>(reinterpret_cast<float4*>(out), bufs, slice_offset / 4, n / 4, world,
-                                                         scale, sumsq, my_flags, channel, epoch, timeout_ns, status);
+                                                         scale, sumsq, my_flags, channel, epoch, timeout_ns, status, step_context());
   ++g_launch_count;
   return cudaGetLastError();
 }
@@ -349,7 +365,7 @@ cudaError_t launch_adamw_push_table(const AdamWSegment* segs, int n_segs, long l
   if (n_segs <= 0 || total_chunks <= 0) return cudaSuccess;
   const int grid = int(total_chunks < max_ctas ? total_chunks : max_ctas);
   adamw_push_table_kernel<<<grid, 256, 0, stream>>>(segs, n_segs, total_chunks, lr0, lr1, wd0, wd1, beta1, beta2, eps, bc1, bc2,
-                                                    grad_scale, static_scale, status);
+                                                    grad_scale, static_scale, status, step_context());
   ++g_launch_count;
   return cudaGetLastError();
 }
@@ -360,7 +376,7 @@ cudaError_t launch_scalar_allreduce_clip(const float* local_value, const PeerPtr
                                          float* norm_out, int* status, cudaStream_t stream) {
   if (world > kMaxPeers) return cudaErrorInvalidValue;
   scalar_allreduce_clip_kernel<<<1, 32, 0, stream>>>(local_value, slots, flag_bases, my_flags, channel, world, rank, epoch,
-                                                     timeout_ns, max_norm, extra_scale, coef_out, norm_out, status);
+                                                     timeout_ns, max_norm, extra_scale, coef_out, norm_out, status, step_context());
   ++g_launch_count;
   return cudaGetLastError();
 }

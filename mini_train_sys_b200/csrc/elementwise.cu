@@ -6,6 +6,8 @@
 // swiglu.py:75-157 (Triton, architecture-neutral).
 #include "ops.cuh"
 
+#include <mutex>
+
 #include <cuda_bf16.h>
 
 namespace mts {
@@ -325,7 +327,9 @@ __device__ __forceinline__ uint32_t mix32(uint32_t h) {
 
 template <typename T, bool WITH_RESIDUAL>
 __global__ void dropout_add_kernel(const T* __restrict__ y, const T* __restrict__ res, T* __restrict__ out, long long nvec,
-                                   uint32_t thresh, float inv_keep, uint32_t seed_lo, uint32_t seed_hi) {
+                                   uint32_t thresh, float inv_keep, unsigned long long seed, const StepContext* __restrict__ ctx) {
+  const unsigned long long salted = seed + ctx->salt * kSaltMultiplier;     // salt is 0 outside graph replay
+  const uint32_t seed_lo = uint32_t(salted), seed_hi = uint32_t(salted >> 32);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
     float a[8], r[8];
     Vec8<T>::load(y + i * 8, a);
@@ -397,13 +401,44 @@ int grid_for(long long work_items, int block, int per_sm) {
 }  // namespace
 
 int device_sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  static int n[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev = dev >= 0 && dev < 64 ? dev : 0;
+  if (n[dev] == 0) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+  return n[dev];
+}
+
+namespace {
+__global__ void set_step_context_kernel(StepContext* ctx, unsigned long long salt, unsigned int epoch_delta, unsigned int dynamic_adam,
+                                        float lr0, float lr1, float bc1, float bc2) {
+  ctx->salt = salt; ctx->epoch_delta = epoch_delta; ctx->dynamic_adam = dynamic_adam;
+  ctx->lr0 = lr0; ctx->lr1 = lr1; ctx->bias_correction1 = bc1; ctx->bias_correction2 = bc2;
+}
+}  // namespace
+
+cudaError_t launch_set_step_context(unsigned long long salt, unsigned int epoch_delta, unsigned int dynamic_adam, float lr0, float lr1,
+                                    float bias_correction1, float bias_correction2, cudaStream_t stream) {
+  StepContext* ctx = step_context();
+  if (ctx == nullptr) return cudaErrorMemoryAllocation;
+  set_step_context_kernel<<<1, 1, 0, stream>>>(ctx, salt, epoch_delta, dynamic_adam, lr0, lr1, bias_correction1, bias_correction2);
+  return cudaGetLastError();
+}
+
+StepContext* step_context() {
+  static StepContext* blocks[64] = {};
+  static std::mutex guard;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev = dev >= 0 && dev < 64 ? dev : 0;
+  std::lock_guard<std::mutex> lock(guard);
+  if (blocks[dev] == nullptr) {
+    // first use happens in the warm-up steps, before any stream capture: allocation and memset are not capturable
+    if (cudaMalloc(&blocks[dev], sizeof(StepContext)) != cudaSuccess) return nullptr;
+    cudaMemset(blocks[dev], 0, sizeof(StepContext));
+    cudaDeviceSynchronize();
   }
-  return n;
+  return blocks[dev];
 }
 
 #define MTS_DISPATCH_FLOAT(is_bf16, ...)            \
@@ -488,13 +523,14 @@ cudaError_t launch_dropout_add(const void* y, const void* residual, void* out, l
   const int grid = grid_for(n / 8, 256, 16);
   const uint32_t thresh = uint32_t(p * 256.f + 0.5f);
   const float inv_keep = 1.f / (1.f - float(thresh) * (1.f / 256.f));
-  const uint32_t lo = uint32_t(seed), hi = uint32_t(seed >> 32);
+  const StepContext* ctx = step_context();
+  if (ctx == nullptr) return cudaErrorMemoryAllocation;
   if (residual != nullptr) {
     MTS_DISPATCH_FLOAT(bf16, dropout_add_kernel<T, true><<<grid, 256, 0, stream>>>(
-        static_cast<const T*>(y), static_cast<const T*>(residual), static_cast<T*>(out), n / 8, thresh, inv_keep, lo, hi);)
+        static_cast<const T*>(y), static_cast<const T*>(residual), static_cast<T*>(out), n / 8, thresh, inv_keep, seed, ctx);)
   } else {
     MTS_DISPATCH_FLOAT(bf16, dropout_add_kernel<T, false><<<grid, 256, 0, stream>>>(
-        static_cast<const T*>(y), nullptr, static_cast<T*>(out), n / 8, thresh, inv_keep, lo, hi);)
+        static_cast<const T*>(y), nullptr, static_cast<T*>(out), n / 8, thresh, inv_keep, seed, ctx);)
   }
   ++g_launch_count;
   return cudaGetLastError();

@@ -12,6 +12,24 @@ namespace mts {
 extern std::atomic<unsigned long long> g_launch_count;
 int device_sm_count();
 
+// Values that change with every optimizer step but must not be baked into kernel arguments, so that a whole step can be
+// replayed from a CUDA graph: kernels read them from this per-device block, the host rewrites it before each replay.
+// All zeros (the state outside graph replay) reproduces the by-value behaviour exactly.
+struct StepContext {
+  unsigned long long salt;      // mixed into every dropout seed (fused dropout + residual, attention dropout)
+  unsigned int epoch_delta;     // added to the sequence number of every peer-flag signal / wait
+  unsigned int dynamic_adam;    // 1: the table-driven AdamW takes the four values below instead of its arguments
+  float lr0, lr1, bias_correction1, bias_correction2;
+  unsigned int reserved[8];
+};
+constexpr unsigned long long kSaltMultiplier = 0x9E3779B97F4A7C15ull;
+// Device pointer of the calling thread's current device; allocated (zero-filled) on first use, never freed.
+StepContext* step_context();
+// Rewrite the block on `stream` (a one-thread kernel: the values travel as launch arguments, so consecutive steps never race
+// on a host staging buffer).
+cudaError_t launch_set_step_context(unsigned long long salt, unsigned int epoch_delta, unsigned int dynamic_adam, float lr0, float lr1,
+                                    float bias_correction1, float bias_correction2, cudaStream_t stream);
+
 // ---- elementwise.cu ----
 cudaError_t launch_rmsnorm_fwd(const void* x, const float* w, void* y, float* rstd, long long rows, int H, float eps,
                                bool bf16, cudaStream_t stream);

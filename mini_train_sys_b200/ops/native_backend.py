@@ -376,7 +376,6 @@ class _FusedLinearCEFn(torch.autograd.Function):
         logits = torch.empty(chunk, vp, dtype=torch.bfloat16, device=dev)
         dx = torch.empty_like(xc) if need_dx else None
         dw = torch.zeros(vocab, hidden, dtype=torch.float32, device=dev) if need_dw else None
-        one_group: dict[int, torch.Tensor] = {}
         for lo in range(0, rows, chunk):
             n = min(chunk, rows - lo)
             xs, ts, ls = xc[lo:lo + n], tg[lo:lo + n], lse[lo:lo + n]
@@ -389,9 +388,10 @@ class _FusedLinearCEFn(torch.autograd.Function):
             if need_dx:
                 _gemm(z, w16, dx[lo:lo + n], n, hidden, vp, b_mn=True, ldo=hidden)
             if need_dw:
-                if n not in one_group:
-                    one_group[n] = torch.tensor([0, n], dtype=torch.int32, device=dev)
-                _gemm(z, xs, dw, vocab, hidden, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=one_group[n],
+                key = ("one_group", n, dev.index)       # cached across calls: no host-to-device copy in steady state
+                if key not in _rows_cache:
+                    _rows_cache[key] = torch.tensor([0, n], dtype=torch.int32, device=dev)
+                _gemm(z, xs, dw, vocab, hidden, 0, a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=_rows_cache[key],
                       num_groups=1, accumulate=True, ldo=hidden)
         ctx.save_for_backward(dx, dw, weight)
         ctx.w_dtype = weight.dtype

@@ -179,6 +179,7 @@ class TrainConfig:
     check_finite: bool = True
     reference_global_batch_size: int | None = None
     batch_size_scaling: str = "none"
+    cuda_graph: bool = False       # replay the device part of a step from one CUDA graph (fused sharding engine, fixed batch shape)
 
     def __post_init__(self) -> None:
         _require(self.batch_size > 0 and self.log_interval > 0,

@@ -112,7 +112,8 @@ def main(argv=None) -> None:
         scheduler = LearningRateScheduler(optimizer, scale.lr_scheduler, total_steps=total_steps)
         trainer = Trainer(model, optimizer, device=device, use_fused_loss=cfg.train.use_fused_loss,
                           precision=precision.name, grad_clip_norm=cfg.train.grad_clip_norm,
-                          check_finite=cfg.train.check_finite, lr_scheduler=scheduler)
+                          check_finite=cfg.train.check_finite, lr_scheduler=scheduler,
+                          cuda_graph=cfg.train.cuda_graph)
 
         resume = args.resume if args.resume is not None else cfg.checkpoint.resume_from
         resume_path = None

@@ -176,3 +176,82 @@ def test_expert_exchange_kernels_with_one_rank_match_the_local_layer():
         err = float((a - b).abs().max()) / max(float(b.abs().max()), 1e-6)
         assert err < 3e-2, (name, err)
     check_kernel_status()
+
+
+def _run_steps(cuda_graph: bool, steps: int, dropout: float = 0.0, same_batch: bool = False, layers: int = 3, **engine_kwargs):
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+    from mini_train_sys_b200.parallel.comm import PeerCollectives
+    from mini_train_sys_b200.parallel.flat_engine import FlatDataParallel
+    from mini_train_sys_b200.runtime.config import LRSchedulerConfig, OptimizerConfig
+    from mini_train_sys_b200.train.lr_scheduler import LearningRateScheduler
+    from mini_train_sys_b200.train.optim import build_optimizer
+    from mini_train_sys_b200.train.trainer import Trainer
+
+    cfg = ModelConfig(vocab_size=1000, seq_len=128, n_layers=layers, n_heads=4, hidden_size=256, intermediate_size=256, ffn_type="moe",
+                      num_experts=4, experts_per_token=2, tie_word_embeddings=True, dropout=dropout)
+    torch.manual_seed(0)
+    model = MiniTransformer(cfg, get_ops_backend("native"), activation_dtype=torch.bfloat16).to(DEV)
+    eng = FlatDataParallel(model, mode="shard", collectives=PeerCollectives(torch.device(DEV, 0), max_units=layers + 1), **engine_kwargs)
+    opt = build_optimizer(eng, cfg=OptimizerConfig(lr=2e-3))
+    sched = LearningRateScheduler(opt, LRSchedulerConfig(schedule="cosine", warmup_steps=4, min_lr_ratio=0.1), total_steps=20)
+    tr = Trainer(eng, opt, torch.device(DEV), use_fused_loss=True, precision="bf16", grad_clip_norm=1.0, lr_scheduler=sched,
+                 cuda_graph=cuda_graph, graph_warmup_steps=3)
+    g = torch.Generator().manual_seed(9)
+    first = torch.randint(0, 1000, (4, 129), generator=g)
+    losses, lrs = [], []
+    for _ in range(steps):
+        t = first if same_batch else torch.randint(0, 1000, (4, 129), generator=g)
+        losses.append(float(tr.train_step({"input_ids": t[:, :-1], "targets": t[:, 1:]})))
+        lrs.append(tr.last_lr)
+    torch.cuda.synchronize()
+    eng.check_status()
+    return eng, tr, losses, lrs
+
+
+@pytest.mark.parametrize("staged", [False, True])
+def test_replayed_step_graph_follows_the_eager_run(staged):
+    """Three eager steps, then the captured step is replayed: new batches, the warm-up / cosine learning rate, the AdamW bias
+    corrections and the flag sequence numbers all have to advance although nothing about them is baked into the graph."""
+
+    from mini_train_sys_b200.ops.native_backend import ext
+
+    kwargs = {"stage_single_rank": True} if staged else {}
+    try:
+        eng_g, tr_g, loss_g, lr_g = _run_steps(True, 9, **kwargs)
+        assert tr_g._graph is not None and eng_g.step_count == 9 and eng_g.comm_epoch == 9
+    finally:
+        ext().set_step_context(0, 0, 0, False, 0.0, 0.0, 1.0, 1.0)       # neutral again for whatever runs next
+        torch.cuda.synchronize()
+    eng_e, tr_e, loss_e, lr_e = _run_steps(False, 9, **kwargs)
+    assert lr_g == pytest.approx(lr_e) and len(set(lr_g)) > 5
+    assert loss_g == pytest.approx(loss_e, abs=3e-2)
+    assert loss_g[:3] == pytest.approx(loss_e[:3], abs=2e-3)             # the eager warm-up steps are the same code (atomics aside)
+    fa, fb = eng_g.full_state_dict(), eng_e.full_state_dict()
+    for name in fa:
+        diff = (fa[name] - fb[name]).abs()
+        assert float(diff.max()) <= 2e-2 and float(diff.mean()) < 6e-4, (name, float(diff.max()), float(diff.mean()))
+
+
+def test_replays_draw_fresh_dropout_masks():
+    from mini_train_sys_b200.ops.native_backend import ext
+
+    try:
+        _, _, losses, _ = _run_steps(True, 7, dropout=0.3, same_batch=True)
+    finally:
+        ext().set_step_context(0, 0, 0, False, 0.0, 0.0, 1.0, 1.0)
+        torch.cuda.synchronize()
+    replayed = losses[3:]
+    # the same batch every step: with one baked mask the loss would fall monotonically; fresh masks make it jitter by more
+    # than the optimisation moves it, and in any case no two replays may agree to the last digit
+    assert len(set(replayed)) == len(replayed)
+
+
+def test_graph_mode_refuses_what_it_cannot_replay():
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+    from mini_train_sys_b200.train.optim import build_optimizer
+    from mini_train_sys_b200.train.trainer import Trainer
+
+    cfg = ModelConfig(vocab_size=512, seq_len=64, n_layers=1, n_heads=2, hidden_size=128, intermediate_size=128)
+    model = MiniTransformer(cfg, get_ops_backend("native"), activation_dtype=torch.bfloat16).to(DEV)
+    with pytest.raises(ValueError, match="fused sharding engine"):
+        Trainer(model, build_optimizer(model), torch.device(DEV), precision="bf16", cuda_graph=True)

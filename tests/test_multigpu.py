@@ -30,7 +30,7 @@ def test_peer_collectives_and_engine(ranks, multimem):
     if torch.cuda.device_count() < ranks:
         pytest.skip(f"needs {ranks} GPUs")
     out = _launch(ranks, {"MTS_TEST_MULTIMEM": "1" if multimem else "0"})
-    for marker in ("PASS reduce_scatter", "PASS all_reduce", "PASS engine", "PASS fifty_steps", "PASS expert_parallel"):
+    for marker in ("PASS reduce_scatter", "PASS all_reduce", "PASS engine", "PASS graph_replay", "PASS fifty_steps", "PASS expert_parallel"):
         assert marker in out, out[-2000:]
     if multimem:
         assert "PASS reduce_scatter multimem=True" in out, "the multicast mapping was not used"
