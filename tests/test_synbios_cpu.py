@@ -213,3 +213,72 @@ def test_nmi_extremes():
     labels = torch.tensor([0, 0, 1, 1, 2, 2, -1])
     assert normalized_mutual_information(labels, torch.tensor([0, 0, 1, 1, 2, 2, 3]), 4) == pytest.approx(1.0)
     assert normalized_mutual_information(torch.tensor([0, 1, 0, 1]), torch.tensor([0, 0, 1, 1]), 2) == pytest.approx(0.0, abs=1e-9)
+
+
+class _ToyBpe:
+    """Greedy longest-match tokens over UTF-8 bytes: multi-byte tokens, some with a leading space, like a byte-level BPE."""
+
+    name = "toy"
+
+    def __init__(self) -> None:
+        pieces = [" was born", " born", " in", " the", " uni", "vers", "ity", "An", "na", " Zür", "ich", "é", " ", "on ", "19", "90"]
+        self.table = [p.encode("utf-8") for p in pieces]
+        self.eos = 256 + len(self.table)
+        self.vocab_size = self.eos + 1
+
+    def encode(self, text: str) -> list[int]:
+        data, out, i = text.encode("utf-8"), [], 0
+        while i < len(data):
+            best = max((k for k, piece in enumerate(self.table) if data.startswith(piece, i)), key=lambda k: len(self.table[k]), default=None)
+            if best is None:
+                out.append(data[i]); i += 1
+            else:
+                out.append(256 + best); i += len(self.table[best])
+        return out
+
+    def token_num_bytes(self, token: int) -> int:
+        return 0 if token == self.eos else (1 if token < 256 else len(self.table[token - 256]))
+
+    def decode(self, tokens) -> str:
+        return b"".join(bytes([t]) if t < 256 else self.table[t - 256] for t in tokens if t != self.eos).decode("utf-8", errors="replace")
+
+
+def test_character_spans_map_to_token_positions_with_multi_byte_tokens():
+    """The span arithmetic behind every probe position: character offsets (code points) against token boundaries (bytes)."""
+
+    from experiments.synbios_moe.codec import positions_before_chars, token_span_of_chars
+
+    codec = _ToyBpe()
+    text = "Anna Rée was born in Zürich on 1990."
+    ids = codec.encode(text)
+    assert codec.decode(ids) == text and any(codec.token_num_bytes(t) > 2 for t in ids)
+    starts = [text.index("Zürich"), text.index("1990"), 0]
+    tokens, positions = positions_before_chars(codec, text, starts)
+    assert tokens[0] == codec.eos and tokens[1:] == ids
+    for start, pos in zip(starts, positions):
+        # the tokens up to and including position `pos` spell exactly the text before the value (position 0 is the EOS)
+        prefix = codec.decode(tokens[1:pos + 1])
+        assert text.startswith(prefix) and len(prefix) <= start
+        # ... and the next token already reaches into the value: the read-out sits right before it
+        longer = codec.decode(tokens[1:pos + 2])
+        assert len(longer) > start or pos + 1 == len(tokens)
+    # " Zür" carries the leading space: the value's first token starts before the value's first character
+    z = text.index("Zürich")
+    toks, lo, hi = token_span_of_chars(codec, text, z, z + len("Zürich"))
+    assert "Zürich" in codec.decode(toks[lo:hi]) and codec.decode(toks[lo:hi]).strip() == "Zürich"
+    toks, lo, hi = token_span_of_chars(codec, text, text.index("é"), text.index("é") + 1)
+    assert codec.decode(toks[lo:hi]) == "é"                      # a two-byte character that is one token
+
+
+def test_gpt2_alignment_when_the_vocabulary_is_available():
+    from experiments.synbios_moe.codec import get_codec, positions_before_chars
+
+    try:
+        codec = get_codec("gpt2")
+    except Exception as exc:       # no network / no cached BPE tables on this machine
+        pytest.skip(f"GPT-2 tables unavailable: {type(exc).__name__}")
+    text = "Anya Briar Forger was born on October 2, 1996. She spent her early years in Princeton, NJ."
+    start = text.index("Princeton")
+    tokens, (pos,) = positions_before_chars(codec, text, [start])
+    assert codec.decode(tokens[1:pos + 1]) == text[:start].rstrip(" ") or codec.decode(tokens[1:pos + 1]) == text[:start]
+    assert codec.decode(tokens[pos + 1:pos + 2]).strip().startswith("Pr")
