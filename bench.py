@@ -39,6 +39,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--local-batch", type=int, default=96)
     ap.add_argument("--ops", default="native")
+    ap.add_argument("--ref-ops", default="torch", choices=["torch", "triton", "cuda"],
+                    help="backend.ops of the reference arm (its documented oracle is torch; triton / cuda are its own kernels)")
     ap.add_argument("--strategy", default=None, help="single | ddp | fsdp | ep (default: fsdp when gpus > 1)")
     ap.add_argument("--engine", default="auto", help="parallel.comm.engine for the own arm")
     ap.add_argument("--model-config", default=str(ROOT / "configs" / "synbios_moe" / "model.yaml"))
@@ -120,7 +122,7 @@ def run_payload(args, strategy: str) -> dict:
         model["seq_len"] = int(args.seq_len)
     return {
         "run": {"name": "bench", "seed": 1337},
-        "backend": {"ops": args.ops if args.impl == "own" else "torch"},
+        "backend": {"ops": args.ops if args.impl == "own" else args.ref_ops},
         "parallel": {"strategy": strategy, "process_group_backend": "nccl" if strategy != "single" else "auto"},
         "optimizer": {"name": "adamw", "lr": 1e-3, "weight_decay": 0.1, "beta1": 0.9, "beta2": 0.95, "eps": 1e-6},
         "lr_scheduler": {"schedule": "cosine", "warmup_steps": 1000, "min_lr_ratio": 0.1},
@@ -207,7 +209,20 @@ def main() -> None:
     import torch.distributed as dist
 
     strategy_name = args.strategy or ("fsdp" if world > 1 else "single")
-    cfg, trainer, strategy, device, ops, launches = assemble(args, strategy_name)
+    if args.impl == "reference" and args.ref_ops != "torch":
+        # the reference's own kernels are compiled on first use; a backend that cannot be built here is reported, not replaced
+        try:
+            cfg, trainer, strategy, device, ops, launches = assemble(args, strategy_name)
+            probe = torch.randint(0, int(cfg.model["vocab_size"]), (2, int(cfg.model["seq_len"]) + 1))
+            trainer.train_step({"input_ids": probe[:, :-1], "targets": probe[:, 1:]})
+            torch.cuda.synchronize(device)
+        except Exception as exc:  # noqa: BLE001 - any build or launch error of the foreign backend ends the arm
+            if rank == 0:
+                why = f"{type(exc).__name__}: {exc}".splitlines()[0][:300]
+                print(json.dumps({"impl": "reference", "ref_ops": args.ref_ops, "unavailable": f"reference ops backend {args.ref_ops!r} did not run here: {why}"}))
+            return
+    else:
+        cfg, trainer, strategy, device, ops, launches = assemble(args, strategy_name)
     seq_len, vocab = int(cfg.model["seq_len"]), int(cfg.model["vocab_size"])
     steps, warmup, batch = args.steps, max(args.warmup, 0), args.local_batch
 
@@ -311,6 +326,8 @@ def main() -> None:
         record["dispatch"] = ops.dispatch_summary()
     if comm_ms is not None:
         record["comm_wait_ms_per_step"] = comm_ms        # this rank's compute-stream stalls, events also cover the warm-up steps
+    if args.impl == "reference":
+        record["config"]["ref_ops"] = args.ref_ops
     if args.impl == "own":
         record["config"]["sharding"] = args.sharding if strategy_name == "fsdp" else None
         record["config"]["multimem"] = bool(args.multimem)

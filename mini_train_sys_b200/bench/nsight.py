@@ -63,6 +63,11 @@ register_nsight_kernel("swiglu_bwd", "swiglu_bwd_kernel", _case("swiglu", 57344)
 register_nsight_kernel("ce_forward", "ce_forward_kernel", _case("cross_entropy", 8192))
 register_nsight_kernel("ce_backward", "ce_backward_kernel", _case("cross_entropy", 8192))
 register_nsight_kernel("router_fwd", "router_forward_kernel", _case("router", 262144))
+register_nsight_kernel("router_logits_fwd", "router_logits_fwd_kernel", _case("router_logits", 98304))
+register_nsight_kernel("router_logits_dx", "router_logits_dx_kernel", _case("router_logits", 98304))
+register_nsight_kernel("router_logits_dw", "router_logits_dw_kernel", _case("router_logits", 98304))
+register_nsight_kernel("embedding_fwd", "embedding_fwd_kernel", _case("embedding", 98304))
+register_nsight_kernel("embedding_bwd", "embedding_bwd_kernel", _case("embedding", 98304))
 register_nsight_kernel("moe_gather", "moe_gather_kernel", _case("fused_moe", 24576))
 register_nsight_kernel("moe_combine", "moe_combine_kernel", _case("fused_moe", 24576))
 

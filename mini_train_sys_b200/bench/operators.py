@@ -43,8 +43,8 @@ PROFILES = {
     "mixtral_7b": OperatorProfile("mixtral_7b", 4096, 14336, 32, 128, 32000, 2048, token_sizes=(2048, 8192, 16384)),
 }
 
-DENSE_KERNELS = ("rmsnorm", "rope", "swiglu", "attention", "cross_entropy", "fused_linear_cross_entropy", "linear")
-MOE_KERNELS = ("router", "fused_moe")
+DENSE_KERNELS = ("embedding", "rmsnorm", "rope", "swiglu", "attention", "cross_entropy", "fused_linear_cross_entropy", "linear")
+MOE_KERNELS = ("router", "router_logits", "fused_moe")
 ROUTER_TOKEN_SIZES = (1024, 4096, 16384, 65536, 262144, 524288)
 
 _ACT = torch.bfloat16
@@ -100,6 +100,19 @@ def build_case(kernel: str, profile: OperatorProfile, tokens: int) -> BenchCase:
             return torch.nn.functional.linear(a["x"], a["w"].to(a["x"].dtype))
         return BenchCase(kernel, label, lambda d: {"x": _randn((t, h), d), "w": _randn((3 * h, h), d, dtype=torch.float32, scale=0.02)},
                          run, t, flops=2.0 * t * h * 3 * h, atol=5e-2, rtol=8e-2, meta=meta)
+    if kernel == "embedding":
+        def run(ops, a):
+            out = ops.embedding(a["ids"], a["w"]) if hasattr(ops, "embedding") else None
+            return out if out is not None else torch.nn.functional.embedding(a["ids"], a["w"]).to(_ACT)
+        return BenchCase(kernel, label, lambda d: {"ids": torch.randint(0, v, (t,), device=d), "w": _randn((v, h), d, dtype=torch.float32, scale=0.02)},
+                         run, t, bytes_moved=t * h * (4 + 2), atol=1e-2, rtol=1e-2, meta=meta)
+    if kernel == "router_logits":
+        def run(ops, a):
+            if hasattr(ops, "router_logits"):
+                return ops.router_logits(a["x"], a["w"])
+            return torch.nn.functional.linear(a["x"].float(), a["w"].float())
+        return BenchCase(kernel, label, lambda d: {"x": _randn((t, h), d), "w": _randn((p.experts, h), d, dtype=torch.float32, scale=0.02)},
+                         run, t, bytes_moved=t * h * 2 + t * p.experts * 4, atol=2e-2, rtol=2e-2, meta=meta)
     if kernel == "router":
         return BenchCase(kernel, label, lambda d: {"logits": _randn((t, p.experts), d, dtype=torch.float32)},
                          lambda ops, a: ops.router_postprocess(a["logits"], p.top_k, normalize=True), t,

@@ -1,7 +1,9 @@
 // FlashAttention forward / backward for sm_100a (head_dim 64, bf16); interface in attention.cuh.
 //
-// Every CTA has 192 threads: warp 0 drives TMA, warp 1 issues tcgen05.mma, warps 2-5 (one thread per
-// tile row) do the softmax arithmetic on accumulators read from tensor memory.  Probability / dS
+// Every CTA has 320 threads: warp 0 drives TMA, warp 1 issues tcgen05.mma, warps 2-9 do the softmax arithmetic on
+// accumulators read from tensor memory, two threads per tile row: warps w and w + 4 share 32 rows and split the
+// tile's columns between them, so every scheduler has four compute warps (two CTAs per SM) to hide the exp2 / TMEM
+// latencies behind.  Probability / dS
 // tiles that feed a second MMA are written to shared memory in the 128-byte swizzled K-major layout
 // the UMMA descriptors expect.  Shared memory and TMEM budgets are sized for two CTAs per SM so one
 // CTA's exponentials overlap the other's MMAs.
@@ -33,7 +35,7 @@ namespace {
 constexpr int D = kAttnHeadDim;
 constexpr int TILE128 = 128 * D * 2;   // bytes of a [128 x 64] bf16 tile
 constexpr int TILE64 = 64 * D * 2;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;   // TMA warp, MMA warp, 2 x 4 compute warps (two threads per accumulator row)
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -180,9 +182,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint8_t* sRing = smem + TILE128;
   uint8_t* sP = smem + 4 * TILE128;
 
-  __shared__ __align__(8) uint64_t q_full, slot_full[3], slot_empty[3], s_full, s_free, p_ready, pv_full;
+  __shared__ __align__(8) uint64_t q_full, slot_full[3], slot_empty[3], s_full, s_free, p_ready, pv_full, pair_bar[4];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_word;
+  __shared__ float pair_val[2][2][128];   // [tile parity][column half][row]: what the two threads of a row tell each other
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_q_tiles = (p.S + 127) / 128;
@@ -195,7 +198,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
     for (int i = 0; i < 3; ++i) { mbar_init(&slot_full[i], 1); mbar_init(&slot_empty[i], 1); }
-    mbar_init(&s_full, 1); mbar_init(&s_free, 4); mbar_init(&p_ready, 4); mbar_init(&pv_full, 1);
+    mbar_init(&s_full, 1); mbar_init(&s_free, 8); mbar_init(&p_ready, 8); mbar_init(&pv_full, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
     abort_word = 0;
     mbar_fence_init();
   }
@@ -272,13 +276,28 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     __syncwarp();
   } else {
-    const int quarter = warp & 3;
+    const int quarter = warp & 3;             // the 32 tensor-memory lanes (tile rows) this warp may read
+    const int half = (warp - 2) >> 2;         // key columns 64 * half .. + 63 of every tile; output columns 32 * half .. + 31
     const int r = quarter * 32 + lane;
     const int q_row = q0 + r;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const float scale_log2 = p.scale * LOG2E;
     const Dropout drop = make_dropout(p.dropout_p, p.seed + p.ctx->salt * kSaltMultiplier, uint32_t(bh), p.S);
-    // Running maximum m (log2 units, may lag the true maximum by up to kRescaleSlack), running sum l.
+    uint8_t* const p_half = sP + half * TILE128;
+    // The two threads of a row exchange one float per tile (their half-row maximum) and one at the end (their half-row sum)
+    // through shared memory; an mbarrier with two arrivals (one per warp) orders the exchange and inherits the bounded wait.
+    int pair_phase = 0;
+    auto exchange = [&](float mine, int parity, float& other) -> bool {
+      pair_val[parity][half][r] = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pair_bar[quarter]);
+      if (!mbar_wait_warp(&pair_bar[quarter], pair_phase & 1, abort_ptr, lane)) return false;
+      ++pair_phase;
+      __syncwarp();                             // lane 0 observed the phase: order the other lanes' reads behind it
+      other = pair_val[parity][half ^ 1][r];
+      return true;
+    };
+    // Running maximum m (log2 units, may lag the true maximum by up to kRescaleSlack), running sum l of this thread's columns.
     // O stays in tensor memory: every P V MMA accumulates into it, and it is only read back and rescaled when
     // the maximum of some row of this warp moved by more than the slack (stale maxima keep exp2 arguments
     // below 2^slack, which fp32 sums and bf16 probabilities hold without loss).
@@ -289,14 +308,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!mbar_wait_warp(&s_full, j & 1, abort_ptr, lane)) { ok = false; break; }
       if (warp == 2) MTS_TRACE(8 * j + 0);
       tc_fence_after_sync();
-      const int k0 = j * 128;
-      const bool need_mask = (p.causal && k0 + 127 > q0) || (k0 + 128 > p.S);
-      // the whole 128-column row in one TMEM round trip
-      uint32_t s0[32], s1[32], s2[32], s3[32];
-      tmem_ld_32x32(tmem_s + lane_base, s0);
-      tmem_ld_32x32(tmem_s + lane_base + 32, s1);
-      tmem_ld_32x32(tmem_s + lane_base + 64, s2);
-      tmem_ld_32x32(tmem_s + lane_base + 96, s3);
+      const int k0 = j * 128 + half * 64;
+      const bool need_mask = (p.causal && k0 + 63 > q0) || (k0 + 64 > p.S);
+      uint32_t s0[32], s1[32];
+      tmem_ld_32x32(tmem_s + lane_base + half * 64, s0);
+      tmem_ld_32x32(tmem_s + lane_base + half * 64 + 32, s1);
       tmem_ld_wait();
       epilogue_arrive(&s_free, lane);            // S is in registers: the next Q K^T may overwrite it
       if (warp == 2) MTS_TRACE(8 * j + 1);
@@ -306,19 +322,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const int kidx = k0 + i;
           if (kidx >= p.S || (p.causal && kidx > q_row)) s0[i] = __float_as_uint(-CUDART_INF_F);
           if (kidx + 32 >= p.S || (p.causal && kidx + 32 > q_row)) s1[i] = __float_as_uint(-CUDART_INF_F);
-          if (kidx + 64 >= p.S || (p.causal && kidx + 64 > q_row)) s2[i] = __float_as_uint(-CUDART_INF_F);
-          if (kidx + 96 >= p.S || (p.causal && kidx + 96 > q_row)) s3[i] = __float_as_uint(-CUDART_INF_F);
         }
       }
       float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};   // four independent max chains
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
+      for (int i = 0; i < 16; ++i) {
         mx4[0] = fmaxf(mx4[0], __uint_as_float(s0[i]));
-        mx4[1] = fmaxf(mx4[1], __uint_as_float(s1[i]));
-        mx4[2] = fmaxf(mx4[2], __uint_as_float(s2[i]));
-        mx4[3] = fmaxf(mx4[3], __uint_as_float(s3[i]));
+        mx4[1] = fmaxf(mx4[1], __uint_as_float(s0[16 + i]));
+        mx4[2] = fmaxf(mx4[2], __uint_as_float(s1[i]));
+        mx4[3] = fmaxf(mx4[3], __uint_as_float(s1[16 + i]));
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), mx_other;
+      if (!exchange(mx, j & 1, mx_other)) { ok = false; break; }
+      mx = fmaxf(mx, mx_other);
       const float m_tile = mx * scale_log2;
       float alpha = 1.f;
       bool grow = false;
@@ -328,11 +344,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // previous P V must be complete: its P tile is about to be overwritten and O may be rescaled
         if (!mbar_wait_warp(&pv_full, (j - 1) & 1, abort_ptr, lane)) { ok = false; break; }
         tc_fence_after_sync();
-        grow = m_tile > m + kRescaleSlack;
+        grow = m_tile > m + kRescaleSlack;        // the same decision in both threads of a row: m and m_tile are shared
         if (__any_sync(0xffffffffu, grow)) {
           if (grow) { alpha = ex2(m - m_tile); m = m_tile; l *= alpha; }
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {          // rare path: narrow chunks keep the register footprint small
+          for (int c = 2 * half; c < 2 * half + 2; ++c) {   // rare path: this thread's 32 of the 64 output columns
             uint32_t oo[16];
             tmem_ld_32x16(tmem_pv + lane_base + c * 16, oo);
             tmem_ld_wait();
@@ -343,13 +359,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tmem_st_wait();
         }
       }
-      float rowsum[8];                          // eight independent partial sums: one accumulator would chain 128 dependent adds
+      float rowsum[8];                          // eight independent partial sums: one accumulator would chain 64 dependent adds
 #pragma unroll
       for (int i = 0; i < 8; ++i) rowsum[i] = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t (&rr)[32] = c == 0 ? s0 : (c == 1 ? s1 : (c == 2 ? s2 : s3));
-        uint8_t* half = sP + (c >> 1) * TILE128;
+      for (int c = 0; c < 2; ++c) {
+        uint32_t (&rr)[32] = c == 0 ? s0 : s1;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {            // eight probabilities at a time: exp, dropout, pack, store
           float e[8];
@@ -369,7 +384,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
           uint4 q4;
           q4.x = pack2(e[0], e[1]); q4.y = pack2(e[2], e[3]); q4.z = pack2(e[4], e[5]); q4.w = pack2(e[6], e[7]);
-          st_swizzled(half, r, (c & 1) * 4 + g, q4);
+          st_swizzled(p_half, r, c * 4 + g, q4);
         }
       }
       l += ((rowsum[0] + rowsum[1]) + (rowsum[2] + rowsum[3])) + ((rowsum[4] + rowsum[5]) + (rowsum[6] + rowsum[7]));
@@ -378,21 +393,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       epilogue_arrive(&p_ready, lane);
       if (warp == 2) MTS_TRACE(8 * j + 3);
     }
+    float l_other = 0.f;
+    ok = ok && exchange(l, n_kv & 1, l_other);
     if (ok && mbar_wait_warp(&pv_full, (n_kv - 1) & 1, abort_ptr, lane)) {
       tc_fence_after_sync();
-      float o[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32(tmem_pv + lane_base + c * 32, rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = __uint_as_float(rr[i]);
-      }
+      l += l_other;
+      uint32_t rr[32];
+      tmem_ld_32x32(tmem_pv + lane_base + half * 32, rr);
+      tmem_ld_wait();
       if (q_row < p.S) {
         const float inv_l = l > 0.f ? (drop.thresh != 0u ? drop.inv_keep : 1.f) / l : 0.f;
-        store_row64(p.o + (long long)b * p.o_sb + (long long)h * p.o_sh + (long long)q_row * p.o_ss, o, inv_l);
-        p.lse[((long long)bh) * p.S + q_row] = (m + log2f(l)) * LN2;
+        __nv_bfloat16* dst = p.o + (long long)b * p.o_sb + (long long)h * p.o_sh + (long long)q_row * p.o_ss + half * 32;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          uint4 q;
+          q.x = pack2(__uint_as_float(rr[8 * jj + 0]) * inv_l, __uint_as_float(rr[8 * jj + 1]) * inv_l);
+          q.y = pack2(__uint_as_float(rr[8 * jj + 2]) * inv_l, __uint_as_float(rr[8 * jj + 3]) * inv_l);
+          q.z = pack2(__uint_as_float(rr[8 * jj + 4]) * inv_l, __uint_as_float(rr[8 * jj + 5]) * inv_l);
+          q.w = pack2(__uint_as_float(rr[8 * jj + 6]) * inv_l, __uint_as_float(rr[8 * jj + 7]) * inv_l);
+          reinterpret_cast<uint4*>(dst)[jj] = q;
+        }
+        if (half == 0) p.lse[((long long)bh) * p.S + q_row] = (m + log2f(l)) * LN2;
       }
       if (warp == 2) MTS_TRACE(8002);
     }
@@ -425,7 +446,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
   uint8_t* sDO = smem + 2 * TILE128 + 2 * TILE64;   // 2 stages x 8 KB
   uint8_t* sP = smem + 2 * TILE128 + 4 * TILE64;    // [128 keys x 64 q]
   uint8_t* sDS = sP + TILE128;
-  uint8_t* sStats = sDS + TILE128;                  // 4 warps x 512 B
+  uint8_t* sStats = sDS + TILE128;                  // 8 warps x 256 B
 
   __shared__ __align__(8) uint64_t kv_full, qd_full[2], qd_empty[2], st_full, st_free, pds_ready, pds_free, acc_full;
   __shared__ uint32_t tmem_slot;
@@ -444,7 +465,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
   if (threadIdx.x == 0) {
     mbar_init(&kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&qd_full[i], 1); mbar_init(&qd_empty[i], 1); }
-    mbar_init(&st_full, 1); mbar_init(&st_free, 4); mbar_init(&pds_ready, 4); mbar_init(&pds_free, 1); mbar_init(&acc_full, 1);
+    mbar_init(&st_full, 1); mbar_init(&st_free, 8); mbar_init(&pds_ready, 8); mbar_init(&pds_free, 1); mbar_init(&acc_full, 1);
     abort_word = 0;
     mbar_fence_init();
   }
@@ -529,6 +550,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
     __syncwarp();
   } else {
     const int quarter = warp & 3;
+    const int c = (warp - 2) >> 2;               // this thread's 32 of the tile's 64 query columns
     const int r = quarter * 32 + lane;           // key row inside the tile
     const int key = k0 + r;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
@@ -537,26 +559,22 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
     const float* lse_bh = p.lse + (long long)bh * p.S;
     const float* delta_bh = p.delta + (long long)bh * p.S;
     const uint32_t keep_shift = uint32_t(key & 3) * 8u;
-    float* stats = reinterpret_cast<float*>(sStats) + (warp - 2) * 128;   // [lse 32 | delta 32] x 2 halves, this warp's own
-    float pre[4];
+    float* stats = reinterpret_cast<float*>(sStats) + (warp - 2) * 64;   // [lse 32 | delta 32] of this warp's query columns
+    float pre[2];
     auto fetch_stats = [&](int qb0) {
-      const int qa = qb0 + lane, qb = qb0 + 32 + lane;
+      const int qa = qb0 + c * 32 + lane;
       pre[0] = qa < p.S ? lse_bh[qa] * LOG2E : 0.f;
       pre[1] = qa < p.S ? delta_bh[qa] : 0.f;
-      pre[2] = qb < p.S ? lse_bh[qb] * LOG2E : 0.f;
-      pre[3] = qb < p.S ? delta_bh[qb] : 0.f;
     };
     if (n_iter > 0) fetch_stats(first_q * 64);
     bool ok = true;
     for (int i = 0; i < n_iter; ++i) {
       const int qbase = (first_q + i) * 64;
-      // lse / delta of the 64 queries of this tile: staged in a 512-byte area private to the warp and read back as
+      // lse / delta of this warp's 32 queries of the tile: staged in a 256-byte area private to the warp and read back as
       // float4 broadcasts (every lane reads the same address), 16 loads per 32 queries instead of 64 shuffles.  The
       // values were fetched from global memory one iteration ahead, so their latency is not on this path.
       stats[lane] = pre[0];
       stats[32 + lane] = pre[1];
-      stats[64 + lane] = pre[2];
-      stats[96 + lane] = pre[3];
       if (i + 1 < n_iter) fetch_stats(qbase + 64);
       __syncwarp();
       if (warp == 2) MTS_TRACE(8 * i + 0);
@@ -564,19 +582,18 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
       if (warp == 2) MTS_TRACE(8 * i + 1);
       tc_fence_after_sync();
       const bool need_mask = (p.causal && qbase < k0 + 127) || (qbase + 64 > p.S) || (k0 + 128 > p.S);
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      {
         uint32_t rs[32], rd[32];
         tmem_ld_32x32(t_st + lane_base + c * 32, rs);
         tmem_ld_32x32(t_dp + lane_base + c * 32, rd);
         tmem_ld_wait();
-        if (warp == 2) MTS_TRACE(8 * i + 2 + 3 * c);
-        // both halves are in registers: the MMA warp may start the scores of the next query tile
-        if (c == 1) epilogue_arrive(&st_free, lane);
-        const float4* lse4 = reinterpret_cast<const float4*>(stats + c * 64);
-        const float4* del4 = reinterpret_cast<const float4*>(stats + c * 64 + 32);
-        // The loops below are written one operation at a time over all 32 columns: with two compute warps per
-        // scheduler the latency of each exp2 / multiply has to be covered by independent work of the same warp.
+        if (warp == 2) MTS_TRACE(8 * i + 2);
+        // this warp's columns are in registers: once all eight warps say so the MMA warp starts the next query tile's scores
+        epilogue_arrive(&st_free, lane);
+        const float4* lse4 = reinterpret_cast<const float4*>(stats);
+        const float4* del4 = reinterpret_cast<const float4*>(stats + 32);
+        // The loops below are written one operation at a time over all 32 columns so that the latency of each
+        // exp2 / multiply is covered by independent work of the same warp.
         float e[32];
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
@@ -630,42 +647,36 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
             pb[2 * g] = pack2(ds0, ds1); pb[2 * g + 1] = pack2(ds2, ds3);
           }
         }
-        if (warp == 2) MTS_TRACE(8 * i + 3 + 3 * c);
+        if (warp == 2) MTS_TRACE(8 * i + 3);
         // the previous tile's dV / dK MMAs must have read P^T / dS^T before they are overwritten
-        if (c == 0 && !mbar_wait_warp(&pds_free, (i & 1) ^ 1, abort_ptr, lane)) { ok = false; break; }
+        if (!mbar_wait_warp(&pds_free, (i & 1) ^ 1, abort_ptr, lane)) { ok = false; break; }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           st_swizzled(sP, r, c * 4 + g, make_uint4(pa[4 * g], pa[4 * g + 1], pa[4 * g + 2], pa[4 * g + 3]));
           st_swizzled(sDS, r, c * 4 + g, make_uint4(pb[4 * g], pb[4 * g + 1], pb[4 * g + 2], pb[4 * g + 3]));
         }
-        if (warp == 2) MTS_TRACE(8 * i + 4 + 3 * c);
+        if (warp == 2) MTS_TRACE(8 * i + 4);
       }
-      if (!ok) break;
       fence_proxy_async_smem();
       epilogue_arrive(&pds_ready, lane);
     }
     if (ok && mbar_wait_warp(&acc_full, 0, abort_ptr, lane)) {
       tc_fence_after_sync();
+      // the two threads of a key row share the write-out: one takes dV, the other dK
       float acc[64];
+      const uint32_t t_src = c == 0 ? t_dv : t_dk;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t rr[32];
-        tmem_ld_32x32(t_dv + lane_base + c * 32, rr);
+        tmem_ld_32x32(t_src + lane_base + cc * 32, rr);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
+        for (int j = 0; j < 32; ++j) acc[cc * 32 + j] = __uint_as_float(rr[j]);
       }
-      if (key < p.S) store_row64(p.dv + (long long)b * p.dv_sb + (long long)h * p.dv_sh + (long long)key * p.dv_ss, acc,
-                                 drop.thresh != 0u ? drop.inv_keep : 1.f);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32(t_dk + lane_base + c * 32, rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
-      }
-      if (key < p.S) {
+      if (key < p.S && c == 0) {
+        store_row64(p.dv + (long long)b * p.dv_sb + (long long)h * p.dv_sh + (long long)key * p.dv_ss, acc,
+                    drop.thresh != 0u ? drop.inv_keep : 1.f);
+      } else if (key < p.S) {
         __nv_bfloat16* dst = p.dk + (long long)b * p.dk_sb + (long long)h * p.dk_sh + (long long)key * p.dk_ss;
         if (p.rope_cos != nullptr) store_row64_unrotated(dst, acc, p.scale, p.rope_cos + (long long)key * 64, p.rope_sin + (long long)key * 64);
         else store_row64(dst, acc, p.scale);
@@ -714,7 +725,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   if (threadIdx.x == 0) {
     mbar_init(&qd_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    mbar_init(&st_full, 1); mbar_init(&st_free, 4); mbar_init(&ds_ready, 4); mbar_init(&ds_free, 1); mbar_init(&acc_full, 1);
+    mbar_init(&st_full, 1); mbar_init(&st_free, 8); mbar_init(&ds_ready, 8); mbar_init(&ds_free, 1); mbar_init(&acc_full, 1);
     abort_word = 0;
     mbar_fence_init();
   }
@@ -788,6 +799,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     __syncwarp();
   } else {
     const int quarter = warp & 3;
+    const int c = (warp - 2) >> 2;               // this thread's 32 of the tile's 64 key columns
     const int r = quarter * 32 + lane;
     const int q_row = q0 + r;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
@@ -803,14 +815,13 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (warp == 2) MTS_TRACE(2048 + 8 * i + 1);
       tc_fence_after_sync();
       const bool need_mask = (p.causal && kbase + 63 > q0) || (kbase + 64 > p.S) || (q0 + 128 > p.S);
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      {
         uint32_t rs[32], rd[32];
         tmem_ld_32x32(t_s + lane_base + c * 32, rs);
         tmem_ld_32x32(t_dp + lane_base + c * 32, rd);
         tmem_ld_wait();
-        if (warp == 2) MTS_TRACE(2048 + 8 * i + 2 + 3 * c);
-        if (c == 1) epilogue_arrive(&st_free, lane);   // S / dP are in registers: the next scores may be issued
+        if (warp == 2) MTS_TRACE(2048 + 8 * i + 2);
+        epilogue_arrive(&st_free, lane);   // S / dP are in registers: the next scores may be issued once all eight warps say so
         float ds[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) ds[j] = ex2(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2));   // probabilities first
@@ -839,32 +850,52 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) pk[j] = pack2(ds[2 * j], ds[2 * j + 1]);
-        if (warp == 2) MTS_TRACE(2048 + 8 * i + 3 + 3 * c);
+        if (warp == 2) MTS_TRACE(2048 + 8 * i + 3);
         // the previous tile's dQ MMAs must have read dS before it is overwritten
-        if (c == 0 && !mbar_wait_warp(&ds_free, (i & 1) ^ 1, abort_ptr, lane)) { ok = false; break; }
+        if (!mbar_wait_warp(&ds_free, (i & 1) ^ 1, abort_ptr, lane)) { ok = false; break; }
 #pragma unroll
         for (int g = 0; g < 4; ++g) st_swizzled(sDS, r, c * 4 + g, make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]));
-        if (warp == 2) MTS_TRACE(2048 + 8 * i + 4 + 3 * c);
+        if (warp == 2) MTS_TRACE(2048 + 8 * i + 4);
       }
-      if (!ok) break;
       fence_proxy_async_smem();
       epilogue_arrive(&ds_ready, lane);
     }
     if (ok && mbar_wait_warp(&acc_full, 0, abort_ptr, lane)) {
       tc_fence_after_sync();
-      float acc[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32(t_dq + lane_base + c * 32, rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(rr[j]);
-      }
+      // write-out shared by the two threads of a query row: output columns 16 c .. + 15 and 32 + 16 c .. + 15, the pairs the
+      // rotary un-rotation couples
+      uint32_t lo[16], hi[16];
+      tmem_ld_32x16(t_dq + lane_base + 16 * c, lo);
+      tmem_ld_32x16(t_dq + lane_base + 32 + 16 * c, hi);
+      tmem_ld_wait();
       if (q_row < p.S) {
         __nv_bfloat16* dst = p.dq + (long long)b * p.dq_sb + (long long)h * p.dq_sh + (long long)q_row * p.dq_ss;
-        if (p.rope_cos != nullptr) store_row64_unrotated(dst, acc, p.scale, p.rope_cos + (long long)q_row * 64, p.rope_sin + (long long)q_row * 64);
-        else store_row64(dst, acc, p.scale);
+        const bool rot = p.rope_cos != nullptr;
+        const __nv_bfloat16* cos_row = rot ? p.rope_cos + (long long)q_row * 64 : nullptr;
+        const __nv_bfloat16* sin_row = rot ? p.rope_sin + (long long)q_row * 64 : nullptr;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float a8[8], b8[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { a8[i] = __uint_as_float(lo[8 * j + i]) * p.scale; b8[i] = __uint_as_float(hi[8 * j + i]) * p.scale; }
+          if (rot) {      // gradient of the row before the half-split rotation: lo' = lo cos + hi sin, hi' = hi cos - lo sin
+            const uint4 cq = reinterpret_cast<const uint4*>(cos_row)[2 * c + j], sq = reinterpret_cast<const uint4*>(sin_row)[2 * c + j];
+            const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w}, sw[4] = {sq.x, sq.y, sq.z, sq.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float cs = __uint_as_float((i & 1) ? (cw[i >> 1] & 0xFFFF0000u) : (cw[i >> 1] << 16));
+              const float sn = __uint_as_float((i & 1) ? (sw[i >> 1] & 0xFFFF0000u) : (sw[i >> 1] << 16));
+              const float x = a8[i], y = b8[i];
+              a8[i] = x * cs + y * sn;
+              b8[i] = y * cs - x * sn;
+            }
+          }
+          uint4 q;
+          q.x = pack2(a8[0], a8[1]); q.y = pack2(a8[2], a8[3]); q.z = pack2(a8[4], a8[5]); q.w = pack2(a8[6], a8[7]);
+          reinterpret_cast<uint4*>(dst)[2 * c + j] = q;
+          q.x = pack2(b8[0], b8[1]); q.y = pack2(b8[2], b8[3]); q.z = pack2(b8[4], b8[5]); q.w = pack2(b8[6], b8[7]);
+          reinterpret_cast<uint4*>(dst)[4 + 2 * c + j] = q;
+        }
       }
     }
   }

@@ -277,7 +277,9 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t M, int64_t N, in
           int64_t epilogue, bool accumulate, bool atomic_out, const c10::optional<Tensor>& aux,
           const c10::optional<Tensor>& tile_group, const c10::optional<Tensor>& num_row_tiles,
           const c10::optional<Tensor>& group_rows, int64_t num_groups, int64_t b_group_stride_rows, int64_t out_group_stride,
-          int64_t ldo, int64_t sm_limit, bool pair, int64_t k_splits) {
+          int64_t ldo, int64_t sm_limit, bool pair, int64_t k_splits, const c10::optional<Tensor>& gather_a,
+          const c10::optional<Tensor>& gather_b, const c10::optional<Tensor>& row_scale, const c10::optional<Tensor>& row_slot,
+          const c10::optional<Tensor>& row_grad) {
   check_rowmajor_2d(a, "a");
   check_rowmajor_2d(b, "b");
   TORCH_CHECK(is_bf16(a) && is_bf16(b), "GEMM operands must be bf16");
@@ -329,6 +331,26 @@ void gemm(const Tensor& a, const Tensor& b, Tensor out, int64_t M, int64_t N, in
   if (g.aux) {
     const int64_t aux_cols = epilogue == mts::EPI_SWIGLU ? N : 2 * N;
     TORCH_CHECK(aux->size(0) >= M && aux->size(1) >= aux_cols, "aux buffer too small");
+  }
+  g.gather_a = int_ptr(gather_a); g.gather_b = int_ptr(gather_b);
+  if (g.gather_a != nullptr) {
+    const int64_t need = (mode == mts::GEMM_GROUPED_M) ? M : 0;      // grouped-K: one entry per contraction row of the padded layout
+    TORCH_CHECK(gather_a->numel() >= need && gather_a->numel() % 4 == 0 && (reinterpret_cast<uintptr_t>(g.gather_a) & 15) == 0,
+                "gather_a must cover the padded rows, in multiples of 4, 16-byte aligned");
+  }
+  if (g.gather_b != nullptr)
+    TORCH_CHECK(gather_b->numel() % 4 == 0 && (reinterpret_cast<uintptr_t>(g.gather_b) & 15) == 0, "gather_b must be 16-byte aligned");
+  if (row_scale.has_value() && row_scale->defined()) {
+    TORCH_CHECK(row_scale->is_cuda() && row_scale->scalar_type() == at::kFloat && row_scale->is_contiguous() && row_scale->numel() >= M,
+                "row_scale must be contiguous fp32 with one entry per output row");
+    g.row_scale = row_scale->data_ptr<float>();
+  }
+  if (row_slot.has_value() && row_slot->defined()) {
+    TORCH_CHECK(row_grad.has_value() && row_grad->defined() && row_grad->is_cuda() && row_grad->scalar_type() == at::kFloat &&
+                    row_grad->is_contiguous(), "row_slot needs a contiguous fp32 row_grad");
+    TORCH_CHECK(row_slot->numel() >= M, "row_slot must have one entry per output row");
+    g.row_slot = int_ptr(row_slot);
+    g.row_grad = row_grad->data_ptr<float>();
   }
   g.status = status_word(a.get_device()).data_ptr<int>();
   g.sm_limit = int(sm_limit);
@@ -428,6 +450,20 @@ void moe_gather(const Tensor& x, const Tensor& row_token, Tensor xs, const Tenso
   c10::cuda::CUDAGuard guard(x.device());
   check_launch(mts::launch_moe_gather(x.data_ptr(), row_token.data_ptr<int>(), xs.data_ptr(), int(row_token.numel()), int(x.size(1)),
                                       meta.data_ptr<int>(), int(x.size(0)), cur_stream()), "moe_gather");
+}
+
+std::vector<Tensor> moe_row_meta(const Tensor& row_token, const Tensor& token_rows, const Tensor& weights, int64_t K) {
+  TORCH_CHECK(row_token.is_cuda() && row_token.scalar_type() == at::kInt && row_token.is_contiguous(), "row_token must be contiguous int32");
+  TORCH_CHECK(token_rows.is_cuda() && token_rows.scalar_type() == at::kInt && token_rows.is_contiguous() && K > 0 &&
+                  token_rows.numel() % K == 0, "token_rows must be contiguous int32 [T * K]");
+  TORCH_CHECK(is_bf16(weights) && weights.is_contiguous() && weights.numel() == token_rows.numel(), "weights must be contiguous bf16 [T * K]");
+  c10::cuda::CUDAGuard guard(row_token.device());
+  Tensor row_weight = torch::empty({row_token.numel()}, row_token.options().dtype(torch::kFloat));
+  Tensor row_slot = torch::empty({row_token.numel()}, row_token.options());
+  check_launch(mts::launch_moe_row_meta(row_token.data_ptr<int>(), token_rows.data_ptr<int>(), weights.data_ptr(), row_weight.data_ptr<float>(),
+                                        row_slot.data_ptr<int>(), int(row_token.numel()), int(K), int(token_rows.numel() / K), cur_stream()),
+               "moe_row_meta");
+  return {row_weight, row_slot};
 }
 
 void moe_combine(const Tensor& y, const Tensor& token_rows, const c10::optional<Tensor>& weights, Tensor out, int64_t K) {
@@ -566,6 +602,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_capacity_rows", &moe_capacity_rows);
   m.def("moe_plan", &moe_plan);
   m.def("moe_gather", &moe_gather);
+  m.def("moe_row_meta", &moe_row_meta);
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_bwd", &moe_combine_bwd);
   m.def("adamw_step", &adamw_step);

@@ -83,6 +83,12 @@ struct KernelParams {
   long long out_group_stride;
   int tiles_m, tiles_n;
   int* status;
+  const int* gather_a;   // pair kernels only: row r of A (K-major, grouped-M) or contraction row k of A (MN-major, grouped-K) is row
+  const int* gather_b;   // gather[r] of the tensor behind the map (negative: a zero row); same for B (MN-major, grouped-K)
+  int gather_a_rows, gather_b_rows;   // extents of those tensors: the index used for "no row"
+  const float* row_scale;   // SwiGLU epilogues: weight of every output row (route weight; 0 on padding rows) or null
+  const int* row_slot;      // SwiGLU backward: where the row's weight gradient goes (index into row_grad; negative: nowhere)
+  float* row_grad;          // SwiGLU backward: += sum_i acc[r, i] * silu(gate) * up, the gradient of row_scale
   int tma_store;     // epilogue writes through shared memory and TMA stores / reduce-adds (else per-lane global stores)
   int diag_no_loads; // timing diagnostic: after the ring's first fill the producer only signals, nothing is copied
 };
@@ -389,8 +395,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   if (warp == 0) {
     // ================= TMA producer (in a pair: each CTA loads its own halves) =================
-    // One thread; its instruction stream per k-block is kept short because the ring's refill latency rides on it.
-    if (lane == 0) {
+    // One thread; its instruction stream per k-block is kept short because the ring's refill latency rides on it.  With a
+    // gathered operand all 32 lanes take part: every lane fetches four rows per k-block with one tile::gather4 copy, lane 0
+    // still posts the byte count and loads the other operand.
+    const bool gathers = PAIR && (p.gather_a != nullptr || p.gather_b != nullptr);
+    if (lane == 0 || gathers) {
       int it = 0, s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -403,25 +412,63 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int b_coord = PAIR ? (B_MN ? t.b_coord + int(rank) * 128 : (rank == 0 ? t.b_coord : t.b_coord2)) : t.b_coord;
         GTRACE(8 * tj + 6);
         int k = t.k_begin;
+        // K-major gathered A (grouped-M): the same 128 rows for every k-block of the tile, four per lane
+        int4 rows_a = make_int4(0, 0, 0, 0);
+        if (gathers && !A_MN && p.gather_a != nullptr) {
+          rows_a = *reinterpret_cast<const int4*>(p.gather_a + a_coord + 4 * lane);
+          rows_a.x = rows_a.x < 0 ? p.gather_a_rows : rows_a.x; rows_a.y = rows_a.y < 0 ? p.gather_a_rows : rows_a.y;
+          rows_a.z = rows_a.z < 0 ? p.gather_a_rows : rows_a.z; rows_a.w = rows_a.w < 0 ? p.gather_a_rows : rows_a.w;
+        }
+        // MN-major gathered operands (grouped-K): four contraction rows per lane and k-block, fetched one k-block ahead
+        const int sub = lane & 15, blk = lane >> 4;      // rows 4 * sub .. + 3 of 64-column block blk
+        int4 next_a = make_int4(0, 0, 0, 0), next_b = make_int4(0, 0, 0, 0);
+        if (gathers && A_MN && p.gather_a != nullptr && t.k_blocks > 0) next_a = *reinterpret_cast<const int4*>(p.gather_a + k + 4 * sub);
+        if (gathers && B_MN && p.gather_b != nullptr && t.k_blocks > 0) next_b = *reinterpret_cast<const int4*>(p.gather_b + k + 4 * sub);
         for (int kb = 0; kb < t.k_blocks; ++kb, ++it, k += BK) {
+          int4 cur_a = next_a, cur_b = next_b;
+          if (gathers && kb + 1 < t.k_blocks) {
+            if (A_MN && p.gather_a != nullptr) next_a = *reinterpret_cast<const int4*>(p.gather_a + k + BK + 4 * sub);
+            if (B_MN && p.gather_b != nullptr) next_b = *reinterpret_cast<const int4*>(p.gather_b + k + BK + 4 * sub);
+          }
           if (!mbar_wait_hot(&empty_bar[s], ph ^ 1, abort_ptr)) { ok = false; break; }
           if (p.diag_no_loads && it >= STAGES) {
-            if (rank == 0) mbar_arrive(&full_bar[s]);
+            if (rank == 0 && lane == 0) mbar_arrive(&full_bar[s]);
           } else if (PAIR) {
             const uint32_t bar = full0 + s * 8;
             const uint32_t a_sm = ring0 + s * STAGE_BYTES, b_sm = a_sm + A_BYTES;
-            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);   // both CTAs' bytes
-            if (A_MN) {
-              tma_load_2d_pair(a_sm, &tm_a, bar, a_coord, k);
-              tma_load_2d_pair(a_sm + MN_BLOCK_BYTES, &tm_a, bar, a_coord + 64, k);
-            } else {
-              tma_load_2d_pair(a_sm, &tm_a, bar, k, a_coord);
+            const bool ga = gathers && p.gather_a != nullptr, gb = gathers && p.gather_b != nullptr;
+            if (lane == 0) {
+              if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);   // both CTAs' bytes
+              if (!ga) {
+                if (A_MN) {
+                  tma_load_2d_pair(a_sm, &tm_a, bar, a_coord, k);
+                  tma_load_2d_pair(a_sm + MN_BLOCK_BYTES, &tm_a, bar, a_coord + 64, k);
+                } else {
+                  tma_load_2d_pair(a_sm, &tm_a, bar, k, a_coord);
+                }
+              }
+              if (!gb) {
+                if (B_MN) {
+                  tma_load_2d_pair(b_sm, &tm_b, bar, b_coord, k + t.b_k_offset);
+                  tma_load_2d_pair(b_sm + MN_BLOCK_BYTES, &tm_b, bar, b_coord + 64, k + t.b_k_offset);
+                } else {
+                  tma_load_2d_pair(b_sm, &tm_b, bar, k, b_coord);
+                }
+              }
             }
-            if (B_MN) {
-              tma_load_2d_pair(b_sm, &tm_b, bar, b_coord, k + t.b_k_offset);
-              tma_load_2d_pair(b_sm + MN_BLOCK_BYTES, &tm_b, bar, b_coord + 64, k + t.b_k_offset);
-            } else {
-              tma_load_2d_pair(b_sm, &tm_b, bar, k, b_coord);
+            if (ga) {
+              if (A_MN) {
+                const int none = p.gather_a_rows;
+                tma_gather4_pair(a_sm + blk * MN_BLOCK_BYTES + sub * 512, &tm_a, bar, a_coord + 64 * blk, cur_a.x < 0 ? none : cur_a.x,
+                                 cur_a.y < 0 ? none : cur_a.y, cur_a.z < 0 ? none : cur_a.z, cur_a.w < 0 ? none : cur_a.w);
+              } else {
+                tma_gather4_pair(a_sm + lane * 512, &tm_a, bar, k, rows_a.x, rows_a.y, rows_a.z, rows_a.w);
+              }
+            }
+            if (gb) {     // MN-major only (checked on the host)
+              const int none = p.gather_b_rows;
+              tma_gather4_pair(b_sm + blk * MN_BLOCK_BYTES + sub * 512, &tm_b, bar, b_coord + 64 * blk, cur_b.x < 0 ? none : cur_b.x,
+                               cur_b.y < 0 ? none : cur_b.y, cur_b.z < 0 ? none : cur_b.z, cur_b.w < 0 ? none : cur_b.w);
             }
           } else {
             uint8_t* a_dst = smem + s * STAGE_BYTES;
@@ -445,7 +492,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
-      loads_issued = it;
+      if (lane == 0) loads_issued = it;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -529,6 +576,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const int row = t.c_row + row_in_tile;
       const int row0 = row - lane;                 // first row of this warp's 32-row box
       const bool row_ok = row < t.row_limit;
+      // SwiGLU epilogues of the routed experts: this row's route weight (0 on padding rows) and, in backward, where the
+      // gradient of that weight is accumulated
+      const float wrow = (p.row_scale != nullptr && p.epilogue != EPI_STORE && row_ok) ? __ldg(p.row_scale + row) : 1.f;
+      float wgrad_part = 0.f;
       if (t.k_blocks == 0) {
         // nothing was contracted: the product is zero
         if (p.tma_store && p.epilogue == EPI_STORE && !p.accumulate && !p.atomic_out) {
@@ -649,10 +700,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
         regs_to_float(ru0, u);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) g0[j] = g0[j] * sigmoidf_fast(g0[j]) * u[j];
+        for (int j = 0; j < 32; ++j) g0[j] = g0[j] * sigmoidf_fast(g0[j]) * (u[j] * wrow);
         regs_to_float(ru1, u);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) g1[j] = g1[j] * sigmoidf_fast(g1[j]) * u[j];
+        for (int j = 0; j < 32; ++j) g1[j] = g1[j] * sigmoidf_fast(g1[j]) * (u[j] * wrow);
         stage_acquire(lane);
         stage_row_bf16(stage, lane, 0, g0); stage_row_bf16(stage, lane, 4, g1);
         if (box_ok) flush_box(&tm_out, stage, col0, row0, 0, false, lane);
@@ -685,9 +736,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) {             // g <- d gate, u <- d up
-            const float d = __uint_as_float(r[j]);
+            const float acc = __uint_as_float(r[j]);
+            const float d = acc * wrow;
             const float sg = sigmoidf_fast(g[j]);
             const float silu = g[j] * sg;
+            wgrad_part = fmaf(acc, silu * u[j], wgrad_part);
             const float dgate = d * u[j] * (sg + silu * (1.f - sg));
             u[j] = d * silu;
             g[j] = dgate;
@@ -757,7 +810,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               aux_store32(pre, row, half + col, p.ld_aux, u);
             }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) g[j] = g[j] * sigmoidf_fast(g[j]) * u[j];
+            for (int j = 0; j < 32; ++j) g[j] = g[j] * sigmoidf_fast(g[j]) * (u[j] * wrow);
             store_row_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo + col, g, valid);
           }
         };
@@ -784,8 +837,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               for (int j = 0; j < 32; ++j) {
                 const float s = sigmoidf_fast(g[j]);
                 const float silu = g[j] * s;
-                const float dgate = d[j] * u[j] * (s + silu * (1.f - s));
-                u[j] = d[j] * silu;   // d up
+                if (j < valid) wgrad_part = fmaf(d[j], silu * u[j], wgrad_part);
+                const float dd = d[j] * wrow;
+                const float dgate = dd * u[j] * (s + silu * (1.f - s));
+                u[j] = dd * silu;     // d up
                 g[j] = dgate;         // d gate
               }
               __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo;
@@ -795,6 +850,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           };
           put(ra, c0); put(rb, c0 + 1);
         }
+      }
+      if (p.epilogue == EPI_SWIGLU_BWD && p.row_grad != nullptr && p.row_slot != nullptr && row_ok) {
+        const int slot = __ldg(p.row_slot + row);
+        if (slot >= 0) atomicAdd(p.row_grad + slot, wgrad_part);     // eight partial sums per row (column halves x N tiles)
       }
       if (warp == 2 && lane == 0) GTRACE(8 * acc_it + 5);
       if (!released) release_acc();
@@ -922,8 +981,15 @@ int sm_count() {       // per device: a process may drive several
 
 cudaError_t launch_gemm_sm100(const GemmArgs& a) {
   CUtensorMap tm_a, tm_b;
-  if (!encode_bf16_2d(&tm_a, a.a, a.a_rows, a.a_cols, a.lda, a.a_mn_major ? 64 : 128)) return cudaErrorInvalidValue;
-  if (!encode_bf16_2d(&tm_b, a.b, a.b_rows, a.b_cols, a.ldb, a.b_mn_major ? 64 : 128)) return cudaErrorInvalidValue;
+  // a gathered operand is fetched four rows at a time by index (tile::gather4): its map describes boxes of one row
+  g_last_error = "gathered operands need the paired kernel; B (and A in grouped-K) must be MN-major, A K-major only in grouped-M";
+  if ((a.gather_a != nullptr || a.gather_b != nullptr) && !a.pair) return cudaErrorInvalidValue;
+  if (a.gather_b != nullptr && !(a.b_mn_major && a.mode == GEMM_GROUPED_K)) return cudaErrorInvalidValue;
+  if (a.gather_a != nullptr && !((a.a_mn_major && a.mode == GEMM_GROUPED_K) || (!a.a_mn_major && a.mode == GEMM_GROUPED_M)))
+    return cudaErrorInvalidValue;
+  g_last_error = "";
+  if (!encode_bf16_2d(&tm_a, a.a, a.a_rows, a.a_cols, a.lda, a.gather_a != nullptr ? 1 : (a.a_mn_major ? 64 : 128))) return cudaErrorInvalidValue;
+  if (!encode_bf16_2d(&tm_b, a.b, a.b_rows, a.b_cols, a.ldb, a.gather_b != nullptr ? 1 : (a.b_mn_major ? 64 : 128))) return cudaErrorInvalidValue;
 
   KernelParams p{};
   p.M = int(a.M); p.N = int(a.N); p.K = int(a.K);
@@ -937,6 +1003,9 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
   p.b_group_stride_rows = int(a.b_group_stride_rows);
   p.out_group_stride = a.out_group_stride;
   p.status = a.status;
+  p.gather_a = a.gather_a; p.gather_b = a.gather_b;
+  p.gather_a_rows = int(a.a_rows); p.gather_b_rows = int(a.b_rows);
+  p.row_scale = a.row_scale; p.row_slot = a.row_slot; p.row_grad = a.row_grad;
   const bool pair = a.pair != 0;
   // epilogue through shared memory + TMA when every output view can be described by a tensor map
   CUtensorMap tm_out, tm_aux;

@@ -67,6 +67,18 @@ struct GemmArgs {
   int64_t b_group_stride_rows = 0;   // GROUPED_M: rows of stacked B per group
   int64_t out_group_stride = 0;      // GROUPED_K: elements between consecutive group outputs (0 with atomic_out)
 
+  // Operands gathered by row index (paired kernel only).  `gather_a`: grouped-M with a K-major A - output row r reads row
+  // gather_a[r] of the tensor `a`; grouped-K with an MN-major A - contraction row k reads row gather_a[k].  `gather_b`: grouped-K,
+  // MN-major B, same meaning.  A negative index is a row of zeros.  Index arrays have one entry per row of the padded layout.
+  const int* gather_a = nullptr;
+  const int* gather_b = nullptr;
+  // SwiGLU epilogues: optional weight per output row.  EPI_SWIGLU: out = weight * silu(gate) * up.  EPI_SWIGLU_BWD: the
+  // accumulator is the gradient of that weighted output, so d(gate, up) use weight * accumulator, and the gradient of the
+  // weight, sum_i acc * silu(gate) * up, is added to row_grad[row_slot[row]] (rows with a negative slot add nothing).
+  const float* row_scale = nullptr;
+  const int* row_slot = nullptr;
+  float* row_grad = nullptr;
+
   int pair = 0;                      // 1: two-CTA clusters on 256 x 256 tiles (GROUPED_M then needs 256-row aligned segments)
   int* status = nullptr;             // device int: receives a KernelStatus on failure
   int sm_limit = 0;                  // cap on CTAs (0 = all SMs)

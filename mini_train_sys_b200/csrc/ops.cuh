@@ -81,6 +81,9 @@ size_t moe_plan_workspace_ints(int T, int K, int E);
 // `tokens` = rows of x (the extent source indices are checked against in bounds-checking builds).
 cudaError_t launch_moe_gather(const void* x, const int* row_token, void* x_sorted, int capacity_rows, int H,
                               const int* meta, int tokens, cudaStream_t stream);
+// row_slot[r] = route (t * K + k) carried by sorted row r or -1; row_weight[r] = weights[route] (bf16 in, fp32 out) or 0
+cudaError_t launch_moe_row_meta(const int* row_token, const int* token_rows, const void* weights, float* row_weight, int* row_slot,
+                                int rows, int K, int tokens, cudaStream_t stream);
 // out[t] = sum_k w[t,k] * y[token_rows[t,k]]   (w may be null -> unweighted sum)
 cudaError_t launch_moe_combine(const void* y, const int* token_rows, const void* weights, void* out, int T, int K, int H,
                                int y_rows, cudaStream_t stream);

@@ -260,6 +260,19 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_cluster_addr, cons
       : "memory");
 }
 
+// Four rows of a 2-D tensor, chosen by index, into four consecutive 128-byte rows of this CTA's shared memory
+// (tile::gather4; the tensor map's box is {columns, 1 row}).  Completion bytes are counted on an mbarrier of either CTA of the
+// pair.  One destination CTA: this is not a multicast.  Rows outside the tensor read the fill value (zero).
+__device__ __forceinline__ void tma_gather4_pair(uint32_t dst_cluster_addr, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
+                                                 int r0, int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%3, %4, %5, "
+      "%6, %7}], [%2];"
+      :
+      : "r"(dst_cluster_addr), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
+
 // Tensor-memory allocation for a CTA pair: one warp of EACH CTA executes these, with the same shared-memory slot offset.
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)

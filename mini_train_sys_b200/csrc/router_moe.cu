@@ -368,6 +368,23 @@ moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat
   }
 }
 
+// Per sorted row: the route it carries (t * K + k, or -1 on a padding row) and that route's weight (0 on padding rows).
+// The grouped expert GEMMs read both in their SwiGLU epilogues.
+__global__ void __launch_bounds__(256)
+moe_row_meta_kernel(const int* __restrict__ row_token, const int* __restrict__ token_rows, const __nv_bfloat16* __restrict__ weights,
+                    float* __restrict__ row_weight, int* __restrict__ row_slot, int rows, int K, int tokens) {
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < rows; row += gridDim.x * blockDim.x) {
+    const int tok = row_token[row];
+    int slot = -1;
+    if (tok >= 0 && tok < tokens) {
+      for (int k = 0; k < K; ++k)
+        if (token_rows[(long long)tok * K + k] == row) slot = tok * K + k;
+    }
+    row_slot[row] = slot;
+    row_weight[row] = slot >= 0 ? __bfloat162float(weights[slot]) : 0.f;
+  }
+}
+
 int capped_grid(long long items, int per_block) {
   long long b = (items + per_block - 1) / per_block;
   const long long cap = (long long)device_sm_count() * 16;
@@ -424,6 +441,15 @@ cudaError_t launch_moe_gather(const void* x, const int* row_token, void* x_sorte
   if (H % 8 != 0) return cudaErrorInvalidValue;
   moe_gather_kernel<<<capped_grid(capacity_rows, 8), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), row_token, static_cast<__nv_bfloat16*>(x_sorted), H, meta, tokens);
+  ++g_launch_count;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_row_meta(const int* row_token, const int* token_rows, const void* weights, float* row_weight, int* row_slot,
+                                int rows, int K, int tokens, cudaStream_t stream) {
+  if (rows <= 0) return cudaSuccess;
+  moe_row_meta_kernel<<<capped_grid(rows, 256), 256, 0, stream>>>(row_token, token_rows, static_cast<const __nv_bfloat16*>(weights),
+                                                                  row_weight, row_slot, rows, K, tokens);
   ++g_launch_count;
   return cudaGetLastError();
 }

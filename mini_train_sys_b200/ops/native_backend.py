@@ -85,12 +85,13 @@ def bf16_weight(weight: torch.Tensor) -> torch.Tensor:
 
 def _gemm(a, b, out, M, N, K, *, a_mn=False, b_mn=False, mode=GEMM_DENSE, epilogue=EPI_STORE, accumulate=False,
           atomic_out=False, aux=None, tile_group=None, num_row_tiles=None, group_rows=None, num_groups=1,
-          b_group_stride_rows=0, out_group_stride=0, ldo=None, sm_limit=0, pair=None, k_splits=1) -> None:
+          b_group_stride_rows=0, out_group_stride=0, ldo=None, sm_limit=0, pair=None, k_splits=1, gather_a=None, gather_b=None,
+          row_scale=None, row_slot=None, row_grad=None) -> None:
     if pair is None:
         pair = GEMM_PAIR
     ext().gemm(a, b, out, M, N, K, a_mn, b_mn, mode, epilogue, accumulate, atomic_out, aux, tile_group, num_row_tiles,
                group_rows, num_groups, b_group_stride_rows, out_group_stride, out.stride(-2) if ldo is None else ldo,
-               sm_limit, bool(pair), k_splits)
+               sm_limit, bool(pair), k_splits, gather_a, gather_b, row_scale, row_slot, row_grad)
 
 
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, out_dtype=torch.bfloat16
@@ -575,6 +576,106 @@ class _RouterFn(torch.autograd.Function):
         return ext().router_backward(lg, lse, idx, w, opt(g_w), opt(g_mp), gz, ctx.normalize), None, None
 
 
+# MTS_MOE_GATHER=1: the grouped GEMMs fetch the rows of the routed experts by index (TMA tile::gather4) instead of reading
+# an expert-sorted copy, and fold the route weight into their SwiGLU epilogues.  Off by default: a gather4 copy moves four
+# 128-byte rows per instruction against 16 KB for a tiled copy, and at the 293M model's shapes the gathered GEMMs ran 1.6x to
+# 2.8x slower than the tiled ones (764 vs 298 us for the up projection), which costs far more than the copy kernels it removes.
+MOE_GATHER = os.environ.get("MTS_MOE_GATHER", "0") == "1"
+
+
+class _GatheredMoEFn(torch.autograd.Function):
+    """Routed SwiGLU experts without an expert-sorted copy of the activations.
+
+    forward    up projection: A rows gathered from ``x`` by the routing plan inside the GEMM; the epilogue applies SwiGLU AND the
+               route weight (``post = w * silu(gate) * up``), so the down projection yields weighted rows and the combine is a
+               plain sum over a token's routes
+    backward   d(post) = dout[token] W_down with A gathered from ``dout``; the epilogue scales by the route weight, applies the
+               SwiGLU derivative and accumulates the route-weight gradient ``<d(post), silu(gate) * up>`` per row; both weight
+               gradients gather their activation operand (``dout`` rows, ``x`` rows) the same way
+    Neither the sorted activations, the sorted output gradients nor the expert outputs are kept for backward."""
+
+    @staticmethod
+    def forward(ctx, x, gate_up_proj, down_proj, top_k_index, top_k_weights):
+        e = ext()
+        n_exp, two_i, hidden = gate_up_proj.shape
+        inter = two_i // 2
+        tokens, k = top_k_index.shape
+        xc = x if x.is_contiguous() else x.contiguous()
+        idx = top_k_index.to(torch.int32).contiguous()
+        w16 = top_k_weights.to(torch.bfloat16).contiguous()
+        gu16 = bf16_weight(gate_up_proj).view(n_exp * two_i, hidden)
+        dn16 = bf16_weight(down_proj).view(n_exp * hidden, inter)
+        row_token, token_rows, tile_group, group_rows, meta = e.moe_plan(idx, n_exp)
+        row_weight, row_slot = e.moe_row_meta(row_token, token_rows, w16.view(-1), k)
+        cap = row_token.numel()
+        dev = x.device
+        post = torch.empty(cap, inter, dtype=torch.bfloat16, device=dev)
+        pre = torch.empty(cap, two_i, dtype=torch.bfloat16, device=dev)
+        tiles = meta[0:1]
+        _gemm(xc, gu16, post, cap, two_i, hidden, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU, aux=pre, tile_group=tile_group,
+              num_row_tiles=tiles, b_group_stride_rows=two_i, ldo=inter, gather_a=row_token, row_scale=row_weight, pair=True)
+        y = torch.empty(cap, hidden, dtype=torch.bfloat16, device=dev)
+        _gemm(post, dn16, y, cap, hidden, inter, mode=GEMM_GROUPED_M, tile_group=tile_group, num_row_tiles=tiles,
+              b_group_stride_rows=hidden, ldo=hidden, pair=True)
+        out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
+        e.moe_combine(y, token_rows, None, out, k)            # rows are already weighted
+        ctx.save_for_backward(xc, pre, post, row_token, token_rows, tile_group, group_rows, meta, row_weight, row_slot,
+                              gate_up_proj, down_proj)
+        ctx.dims = (n_exp, inter, hidden, tokens, k)
+        ctx.w_dtype = top_k_weights.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        e = ext()
+        (xc, pre, post, row_token, token_rows, tile_group, group_rows, meta, row_weight, row_slot, gate_up_proj,
+         down_proj) = ctx.saved_tensors
+        n_exp, inter, hidden, tokens, k = ctx.dims
+        two_i = 2 * inter
+        cap = row_token.numel()
+        dev = dout.device
+        gu16 = bf16_weight(gate_up_proj).view(n_exp * two_i, hidden)
+        dn16 = bf16_weight(down_proj).view(n_exp * hidden, inter)
+        tiles = meta[0:1]
+        go = dout if dout.is_contiguous() else dout.contiguous()
+        dwts = torch.zeros(tokens * k, dtype=torch.float32, device=dev)
+        d_pre = torch.empty(cap, two_i, dtype=torch.bfloat16, device=dev)
+        _gemm(go, dn16, d_pre, cap, inter, hidden, b_mn=True, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU_BWD, aux=pre,
+              tile_group=tile_group, num_row_tiles=tiles, b_group_stride_rows=hidden, ldo=two_i, gather_a=row_token,
+              row_scale=row_weight, row_slot=row_slot, row_grad=dwts, pair=True)
+        dx = dgu = ddn = None
+        if ctx.needs_input_grad[0]:
+            dxs = torch.empty(cap, hidden, dtype=torch.bfloat16, device=dev)
+            _gemm(d_pre, gu16, dxs, cap, hidden, two_i, b_mn=True, mode=GEMM_GROUPED_M, tile_group=tile_group,
+                  num_row_tiles=tiles, b_group_stride_rows=two_i, ldo=hidden, pair=True)
+            dx = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
+            e.moe_combine(dxs, token_rows, None, dx, k)
+        for which, param in ((1, gate_up_proj), (2, down_proj)):
+            if not ctx.needs_input_grad[which]:
+                continue
+            rows_out, cols_out = (two_i, hidden) if which == 1 else (hidden, inter)
+            sink = grad_sink(param)
+            grad = sink[0] if sink is not None else torch.empty(n_exp, rows_out, cols_out, dtype=torch.float32, device=dev)
+            splits = expert_wgrad_splits(cap, n_exp, rows_out, cols_out, dev)
+            adds = splits > 1 or (sink is not None and _sink_accumulates(sink))
+            if splits > 1 and not (sink is not None and _sink_accumulates(sink)):
+                grad.zero_()
+            common = dict(a_mn=True, b_mn=True, mode=GEMM_GROUPED_K, group_rows=group_rows, num_groups=n_exp,
+                          out_group_stride=rows_out * cols_out, ldo=cols_out, k_splits=splits, atomic_out=adds, pair=True)
+            if which == 1:      # d W_up[e] = sum_r d_pre[r]^T x[token(r)]
+                _gemm(d_pre, xc, grad, two_i, hidden, 0, gather_b=row_token, **common)
+            else:               # d W_down[e] = sum_r dout[token(r)]^T post[r]   (post carries the route weight)
+                _gemm(go, post, grad, hidden, inter, 0, gather_a=row_token, **common)
+            if sink is not None:
+                sink[1](param)
+            elif which == 1:
+                dgu = grad.to(param.dtype)
+            else:
+                ddn = grad.to(param.dtype)
+        dw = dwts.view(tokens, k).to(ctx.w_dtype) if ctx.needs_input_grad[4] else None
+        return dx, dgu, ddn, None, dw
+
+
 class _FusedMoEFn(torch.autograd.Function):
     """Routed SwiGLU experts as four grouped tcgen05 GEMMs around an expert-sorted, 128-row padded layout."""
 
@@ -783,7 +884,8 @@ class NativeOpsBackend(TorchOpsBackend):
         ok = (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and hidden % 8 == 0 and two_i % 256 == 0
               and n_exp <= 64 and gate_up_proj.is_cuda)
         if self._count("fused_moe", ok):
-            return _FusedMoEFn.apply(x, gate_up_proj, down_proj, top_k_index, top_k_weights)
+            fn = _GatheredMoEFn if (MOE_GATHER and GEMM_PAIR and hidden % 64 == 0 and (two_i // 2) % 64 == 0) else _FusedMoEFn
+            return fn.apply(x, gate_up_proj, down_proj, top_k_index, top_k_weights)
         return super().fused_moe(x, gate_up_proj, down_proj, top_k_index, top_k_weights)
 
     def attention_qkv(self, fused, cos, sin, *, is_causal, dropout_p):

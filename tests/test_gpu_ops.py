@@ -287,9 +287,13 @@ def test_moe_plan(nb, mode):
         assert bool((seg[1:] >= seg[:-1]).all())
 
 
+@pytest.mark.parametrize("gathered", [True, False])
 @pytest.mark.parametrize("mode", ["uniform", "one_expert", "empty"])
 @pytest.mark.parametrize("tokens,hidden,inter,experts", [(1000, 128, 128, 4), (2048, 768, 1024, 8), (12288, 768, 1024, 8)])
-def test_fused_moe(ops, mode, tokens, hidden, inter, experts):
+def test_fused_moe(nb, ops, monkeypatch, mode, tokens, hidden, inter, experts, gathered):
+    """Both forms of the routed experts: activations gathered by index inside the grouped GEMMs, and through a sorted copy."""
+
+    monkeypatch.setattr(nb, "MOE_GATHER", gathered)
     torch.manual_seed(11)
     k = 2
     x = torch.randn(tokens, hidden, device=DEV, dtype=torch.bfloat16, requires_grad=True)

@@ -75,3 +75,53 @@ def test_noalloc_plan_rejects_oversized_requests():
     assert fn(p, 16, 2, 65, 128, p, p, p, p, p, 0) == -1            # more than 64 experts
     assert fn(p, 16, 2, 8, 100, p, p, p, p, p, 0) == -2             # capacity not a multiple of 128
     assert fn(None, 16, 2, 8, 128, p, p, p, p, p, 0) == -2
+
+
+def test_noalloc_plan_flags_an_undersized_capacity_and_stays_inside_it():
+    """A capacity below the padded row count raises the overflow word; nothing is written past the caller's buffers."""
+
+    fn = _load_symbol()
+    torch.manual_seed(3)
+    tokens, top_k, experts = 2000, 2, 8
+    idx = torch.rand(tokens, experts, device="cuda").topk(top_k, -1).indices.to(torch.int32).contiguous()
+    capacity = 1024                                       # 4000 routes cannot fit
+    guard = 256
+    i32 = dict(dtype=torch.int32, device="cuda")
+    row_token = torch.full((capacity + guard,), -7, **i32)
+    tile_group = torch.full((capacity // 128 + guard,), -7, **i32)
+    token_rows = torch.full((tokens * top_k + guard,), -7, **i32)
+    group_rows = torch.empty(experts + 1, **i32)
+    meta = torch.zeros(4, **i32)
+    rc = fn(idx.data_ptr(), tokens, top_k, experts, capacity, row_token.data_ptr(), token_rows.data_ptr(), tile_group.data_ptr(),
+            group_rows.data_ptr(), meta.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(meta[2]) == 1
+    assert bool((row_token[capacity:] == -7).all()) and bool((tile_group[capacity // 128:] == -7).all())
+    assert bool((token_rows[tokens * top_k:] == -7).all())
+    placed = token_rows[:tokens * top_k]
+    assert int(placed.max()) < capacity and bool((placed[placed >= 0] < capacity).all())
+    assert bool((placed == -1).any())                     # the routes that did not fit have no row
+
+
+def test_noalloc_plan_treats_negative_indices_as_dropped_routes():
+    from mini_train_sys_b200.ops.native_backend import ext
+
+    fn = _load_symbol()
+    torch.manual_seed(4)
+    tokens, top_k, experts = 1500, 2, 8
+    idx = torch.rand(tokens, experts, device="cuda").topk(top_k, -1).indices.to(torch.int32)
+    drop = torch.rand(tokens, top_k, device="cuda") < 0.3
+    idx = torch.where(drop, torch.full_like(idx, -1), idx).contiguous()
+    capacity = int(ext().moe_capacity_rows(tokens, top_k, experts))
+    rc, got = _call(fn, idx, experts, capacity)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(got["meta"][2]) == 0
+    rows = got["token_rows"].view(tokens, top_k)
+    assert bool((rows[drop] == -1).all()) and bool((rows[~drop] >= 0).all())
+    kept = rows[~drop].long()
+    assert kept.unique().numel() == kept.numel()          # every kept route has a row of its own
+    starts = got["group_rows"].long()
+    expert_of_row = torch.bucketize(kept, starts[1:], right=True)
+    assert torch.equal(expert_of_row, idx[~drop].long())  # and it lies in its expert's segment
+    tok = torch.arange(tokens, device="cuda").view(-1, 1).expand(-1, top_k)[~drop]
+    assert torch.equal(got["row_token"][kept].long(), tok)
