@@ -171,34 +171,42 @@ struct Params {
 // =====================================================================================================
 // forward
 // =====================================================================================================
-constexpr int FWD_SMEM = TILE128 /*Q*/ + 3 * TILE128 /*K,V ring*/ + 2 * TILE128 /*P*/ + 1024;
+constexpr int FWD_SMEM = TILE128 /*Q*/ + TILE128 /*K*/ + 2 * TILE128 /*V x 2*/ + 2 * TILE128 /*P*/ + 1024;
 
+// Persistent: the grid is two CTAs per SM and every CTA walks the work items (query tile, batch * head) it owns, heaviest
+// query tiles first.  Barriers and tensor memory are set up once; the loader runs ahead into the next item (its Q as soon
+// as the last Q K^T of the current item has been issued, its K / V as their buffers free up) and the MMA warp computes the
+// next item's first scores while the softmax warps write the current item's output, so the latency of an item's first
+// loads and the write-out of its last rows are no longer paid once per 128 query rows.  O is double-buffered in tensor
+// memory (columns 128..191 and 192..255) so that the next item's first P V does not wait for that write-out.
 __global__ void __launch_bounds__(THREADS, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sRing = smem + TILE128;
+  uint8_t* sK = smem + TILE128;          // one K tile: it is free again as soon as its Q K^T has run, a whole softmax before the next is needed
+  uint8_t* sV = smem + 2 * TILE128;      // two V tiles: a V tile is held until its P V has run, at the end of its key tile
   uint8_t* sP = smem + 4 * TILE128;
 
-  __shared__ __align__(8) uint64_t q_full, slot_full[3], slot_empty[3], s_full, s_free, p_ready, pv_full, pair_bar[4];
+  __shared__ __align__(8) uint64_t q_full, q_free, k_full, k_empty, v_full[2], v_empty[2], s_full, s_free, p_ready, pv_full, o_free[2], pair_bar[4];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_word;
-  __shared__ float pair_val[2][2][128];   // [tile parity][column half][row]: what the two threads of a row tell each other
+  __shared__ float pair_val[2][2][128];   // [exchange parity][column half][row]: what the two threads of a row tell each other
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_q_tiles = (p.S + 127) / 128;
-  const int q_tile = n_q_tiles - 1 - int(blockIdx.x);      // heavy (late) causal tiles are scheduled first
-  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
-  const int q0 = q_tile * 128;
-  const int n_kv = p.causal ? min((p.S + 127) / 128, q_tile + 1) : (p.S + 127) / 128;
+  const int n_k_tiles = n_q_tiles;
+  const int BH = p.B * p.H;
+  const int total = n_q_tiles * BH;
   if (warp == 0) MTS_TRACE(8000);
 
   if (threadIdx.x == 0) {
-    mbar_init(&q_full, 1);
-    for (int i = 0; i < 3; ++i) { mbar_init(&slot_full[i], 1); mbar_init(&slot_empty[i], 1); }
+    mbar_init(&q_full, 1); mbar_init(&q_free, 1);
+    mbar_init(&k_full, 1); mbar_init(&k_empty, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
     mbar_init(&s_full, 1); mbar_init(&s_free, 8); mbar_init(&p_ready, 8); mbar_init(&pv_full, 1);
+    mbar_init(&o_free[0], 8); mbar_init(&o_free[1], 8);
     for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
     abort_word = 0;
     mbar_fence_init();
@@ -207,19 +215,30 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_s = tmem_slot, tmem_pv = tmem_slot + 128;
+  const uint32_t tmem_s = tmem_slot, tmem_o = tmem_slot + 128;
   volatile int* abort_ptr = &abort_word;
   if (warp == 0) MTS_TRACE(8001);
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(&q_full, TILE128);
-      tma_load_4d(sQ, &tm_q, &q_full, 0, q0, h, b);
-      for (int i = 0; i < 2 * n_kv; ++i) {
-        const int slot = i % 3;
-        if (!mbar_wait(&slot_empty[slot], ((i / 3) & 1) ^ 1, abort_ptr)) break;
-        mbar_expect_tx(&slot_full[slot], TILE128);
-        tma_load_4d(sRing + slot * TILE128, (i & 1) ? &tm_v : &tm_k, &slot_full[slot], 0, (i >> 1) * 128, h, b);
+      int kt = 0;            // key tiles loaded so far, over all items (K and V counted alike)
+      int n = 0;             // items started by this CTA
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++n) {
+        const int q_tile = n_q_tiles - 1 - item / BH, bh = item % BH, b = bh / p.H, h = bh % p.H;
+        const int n_kv = p.causal ? min(n_k_tiles, q_tile + 1) : n_k_tiles;
+        if (n > 0 && !mbar_wait(&q_free, (n - 1) & 1, abort_ptr)) break;      // the previous item's Q K^T are all issued and done
+        mbar_expect_tx(&q_full, TILE128);
+        tma_load_4d(sQ, &tm_q, &q_full, 0, q_tile * 128, h, b);
+        for (int j = 0; j < n_kv; ++j, ++kt) {
+          if (!mbar_wait(&k_empty, (kt & 1) ^ 1, abort_ptr)) { ok = false; break; }
+          mbar_expect_tx(&k_full, TILE128);
+          tma_load_4d(sK, &tm_k, &k_full, 0, j * 128, h, b);
+          const int vs = kt & 1;
+          if (!mbar_wait(&v_empty[vs], ((kt >> 1) & 1) ^ 1, abort_ptr)) { ok = false; break; }
+          mbar_expect_tx(&v_full[vs], TILE128);
+          tma_load_4d(sV + vs * TILE128, &tm_v, &v_full[vs], 0, j * 128, h, b);
+        }
       }
     }
     __syncwarp();
@@ -228,50 +247,60 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, 64, false, true);
       // Descriptors are built once: a 16-wide contraction step adds 2 (32 B) to a K-major descriptor and 128 (2048 B) to
-      // an MN-major one; ring slots and the two halves of P lie TILE128 bytes (1024 descriptor units) apart.
+      // an MN-major one; the two V tiles and the two halves of P lie TILE128 bytes (1024 descriptor units) apart.
       const uint64_t qd = desc_kmajor(smem_u32(sQ), 0), pd = desc_kmajor(smem_u32(sP), 0);
-      const uint64_t ring_k = desc_kmajor(smem_u32(sRing), 0), ring_m = desc_mnmajor(smem_u32(sRing), 0);
+      const uint64_t kd = desc_kmajor(smem_u32(sK), 0), v_m = desc_mnmajor(smem_u32(sV), 0);
       constexpr uint64_t kSlot = TILE128 >> 4;
-      bool ok = mbar_wait(&q_full, 0, abort_ptr);
-      // S_j = Q K_j^T.  The softmax warps copy S into registers right away, so S_{j+1} is issued before
-      // waiting for P_j: the tensor core computes the next scores while the exponentials of tile j run.
-      auto issue_scores = [&](int j) -> bool {
-        const int slot = (2 * j) % 3;
-        if (!mbar_wait_hot(&slot_full[slot], ((2 * j) / 3) & 1, abort_ptr)) return false;
-        if (!mbar_wait_hot(&s_free, (j & 1) ^ 1, abort_ptr)) return false;
-        tc_fence_after_sync();
-        const uint64_t kd = ring_k + slot * kSlot;
-        umma_bf16_ss(tmem_s, qd, kd, idesc_s, 0u);
-        umma_bf16_ss(tmem_s, qd + 2, kd + 2, idesc_s, 1u);
-        umma_bf16_ss(tmem_s, qd + 4, kd + 4, idesc_s, 1u);
-        umma_bf16_ss(tmem_s, qd + 6, kd + 6, idesc_s, 1u);
-        umma_commit(&s_full);
-        umma_commit(&slot_empty[slot]);
-        return true;
-      };
-      ok = ok && issue_scores(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int iv = 2 * j + 1;
-        const int slot = iv % 3;
-        MTS_TRACE(4096 + 8 * j + 0);
-        if (j + 1 < n_kv && !issue_scores(j + 1)) break;
-        MTS_TRACE(4096 + 8 * j + 1);
-        if (!mbar_wait_hot(&p_ready, j & 1, abort_ptr)) break;
-        MTS_TRACE(4096 + 8 * j + 2);
-        if (!mbar_wait_hot(&slot_full[slot], (iv / 3) & 1, abort_ptr)) break;
-        tc_fence_after_sync();
-        const uint64_t vm = ring_m + slot * kSlot;
-        umma_bf16_ss(tmem_pv, pd, vm, idesc_pv, j != 0 ? 1u : 0u);
-        umma_bf16_ss(tmem_pv, pd + 2, vm + 128, idesc_pv, 1u);
-        umma_bf16_ss(tmem_pv, pd + 4, vm + 256, idesc_pv, 1u);
-        umma_bf16_ss(tmem_pv, pd + 6, vm + 384, idesc_pv, 1u);
-        umma_bf16_ss(tmem_pv, pd + kSlot, vm + 512, idesc_pv, 1u);
-        umma_bf16_ss(tmem_pv, pd + kSlot + 2, vm + 640, idesc_pv, 1u);
-        umma_bf16_ss(tmem_pv, pd + kSlot + 4, vm + 768, idesc_pv, 1u);
-        umma_bf16_ss(tmem_pv, pd + kSlot + 6, vm + 896, idesc_pv, 1u);
-        umma_commit(&pv_full);
-        MTS_TRACE(4096 + 8 * j + 3);
-        umma_commit(&slot_empty[slot]);
+      int tiles = 0;         // key tiles whose scores have been issued, over all items (parity of s_full / s_free)
+      int pvs = 0;           // key tiles whose P V has been issued (parity of p_ready / pv_full)
+      int n = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++n) {
+        const int q_tile = n_q_tiles - 1 - item / BH;
+        const int n_kv = p.causal ? min(n_k_tiles, q_tile + 1) : n_k_tiles;
+        const uint32_t tmem_pv = tmem_o + 64u * uint32_t(n & 1);
+        // S_j = Q K_j^T.  The softmax warps copy S into registers right away, so S_{j+1} is issued before
+        // waiting for P_j: the tensor core computes the next scores while the exponentials of tile j run.
+        auto issue_scores = [&](int j) -> bool {
+          if (!mbar_wait_hot(&k_full, tiles & 1, abort_ptr)) return false;
+          if (!mbar_wait_hot(&s_free, (tiles & 1) ^ 1, abort_ptr)) return false;
+          tc_fence_after_sync();
+          umma_bf16_ss(tmem_s, qd, kd, idesc_s, 0u);
+          umma_bf16_ss(tmem_s, qd + 2, kd + 2, idesc_s, 1u);
+          umma_bf16_ss(tmem_s, qd + 4, kd + 4, idesc_s, 1u);
+          umma_bf16_ss(tmem_s, qd + 6, kd + 6, idesc_s, 1u);
+          umma_commit(&s_full);
+          umma_commit(&k_empty);
+          if (j == n_kv - 1) umma_commit(&q_free);       // Q may be replaced by the next item's
+          ++tiles;
+          return true;
+        };
+        if (!mbar_wait(&q_full, n & 1, abort_ptr)) break;
+        if (!issue_scores(0)) break;
+        for (int j = 0; j < n_kv; ++j, ++pvs) {
+          const int vs = pvs & 1;
+          if (n == 0) MTS_TRACE(4096 + 8 * j + 0);
+          if (j + 1 < n_kv && !issue_scores(j + 1)) { ok = false; break; }
+          if (n == 0) MTS_TRACE(4096 + 8 * j + 1);
+          if (!mbar_wait_hot(&p_ready, pvs & 1, abort_ptr)) { ok = false; break; }
+          if (n == 0) MTS_TRACE(4096 + 8 * j + 2);
+          // the write-out of the item that used this O buffer two items ago has read it
+          if (j == 0 && n >= 2 && !mbar_wait_hot(&o_free[n & 1], ((n >> 1) - 1) & 1, abort_ptr)) { ok = false; break; }
+          if (!mbar_wait_hot(&v_full[vs], (pvs >> 1) & 1, abort_ptr)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t vm = v_m + vs * kSlot;
+          umma_bf16_ss(tmem_pv, pd, vm, idesc_pv, j != 0 ? 1u : 0u);
+          umma_bf16_ss(tmem_pv, pd + 2, vm + 128, idesc_pv, 1u);
+          umma_bf16_ss(tmem_pv, pd + 4, vm + 256, idesc_pv, 1u);
+          umma_bf16_ss(tmem_pv, pd + 6, vm + 384, idesc_pv, 1u);
+          umma_bf16_ss(tmem_pv, pd + kSlot, vm + 512, idesc_pv, 1u);
+          umma_bf16_ss(tmem_pv, pd + kSlot + 2, vm + 640, idesc_pv, 1u);
+          umma_bf16_ss(tmem_pv, pd + kSlot + 4, vm + 768, idesc_pv, 1u);
+          umma_bf16_ss(tmem_pv, pd + kSlot + 6, vm + 896, idesc_pv, 1u);
+          umma_commit(&pv_full);
+          if (n == 0) MTS_TRACE(4096 + 8 * j + 3);
+          umma_commit(&v_empty[vs]);
+        }
       }
     }
     __syncwarp();
@@ -279,19 +308,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int quarter = warp & 3;             // the 32 tensor-memory lanes (tile rows) this warp may read
     const int half = (warp - 2) >> 2;         // key columns 64 * half .. + 63 of every tile; output columns 32 * half .. + 31
     const int r = quarter * 32 + lane;
-    const int q_row = q0 + r;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const float scale_log2 = p.scale * LOG2E;
-    const Dropout drop = make_dropout(p.dropout_p, p.seed + p.ctx->salt * kSaltMultiplier, uint32_t(bh), p.S);
     uint8_t* const p_half = sP + half * TILE128;
-    // The two threads of a row exchange one float per tile (their half-row maximum) and one at the end (their half-row sum)
+    // The two threads of a row exchange one float per tile (their half-row maximum) and one per item (their half-row sum)
     // through shared memory; an mbarrier with two arrivals (one per warp) orders the exchange and inherits the bounded wait.
     int pair_phase = 0;
-    auto exchange = [&](float mine, int parity, float& other) -> bool {
+    auto exchange = [&](float mine, float& other) -> bool {
+      const int parity = pair_phase & 1;
       pair_val[parity][half][r] = mine;
       __syncwarp();
       if (lane == 0) mbar_arrive(&pair_bar[quarter]);
-      if (!mbar_wait_warp(&pair_bar[quarter], pair_phase & 1, abort_ptr, lane)) return false;
+      if (!mbar_wait_warp(&pair_bar[quarter], parity, abort_ptr, lane)) return false;
       ++pair_phase;
       __syncwarp();                             // lane 0 observed the phase: order the other lanes' reads behind it
       other = pair_val[parity][half ^ 1][r];
@@ -302,105 +330,119 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // the maximum of some row of this warp moved by more than the slack (stale maxima keep exp2 arguments
     // below 2^slack, which fp32 sums and bf16 probabilities hold without loss).
     constexpr float kRescaleSlack = 8.f;
-    float m = -CUDART_INF_F, l = 0.f;
+    int tiles = 0;           // key tiles processed, over all items: parity of s_full / pv_full
+    int n = 0;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait_warp(&s_full, j & 1, abort_ptr, lane)) { ok = false; break; }
-      if (warp == 2) MTS_TRACE(8 * j + 0);
-      tc_fence_after_sync();
-      const int k0 = j * 128 + half * 64;
-      const bool need_mask = (p.causal && k0 + 63 > q0) || (k0 + 64 > p.S);
-      uint32_t s0[32], s1[32];
-      tmem_ld_32x32(tmem_s + lane_base + half * 64, s0);
-      tmem_ld_32x32(tmem_s + lane_base + half * 64 + 32, s1);
-      tmem_ld_wait();
-      epilogue_arrive(&s_free, lane);            // S is in registers: the next Q K^T may overwrite it
-      if (warp == 2) MTS_TRACE(8 * j + 1);
-      if (need_mask) {       // one uniform branch around the loop (diagonal and ragged tiles only)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kidx = k0 + i;
-          if (kidx >= p.S || (p.causal && kidx > q_row)) s0[i] = __float_as_uint(-CUDART_INF_F);
-          if (kidx + 32 >= p.S || (p.causal && kidx + 32 > q_row)) s1[i] = __float_as_uint(-CUDART_INF_F);
-        }
-      }
-      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};   // four independent max chains
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        mx4[0] = fmaxf(mx4[0], __uint_as_float(s0[i]));
-        mx4[1] = fmaxf(mx4[1], __uint_as_float(s0[16 + i]));
-        mx4[2] = fmaxf(mx4[2], __uint_as_float(s1[i]));
-        mx4[3] = fmaxf(mx4[3], __uint_as_float(s1[16 + i]));
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), mx_other;
-      if (!exchange(mx, j & 1, mx_other)) { ok = false; break; }
-      mx = fmaxf(mx, mx_other);
-      const float m_tile = mx * scale_log2;
-      float alpha = 1.f;
-      bool grow = false;
-      if (j == 0) {
-        m = m_tile == -CUDART_INF_F ? 0.f : m_tile;
-      } else {
-        // previous P V must be complete: its P tile is about to be overwritten and O may be rescaled
-        if (!mbar_wait_warp(&pv_full, (j - 1) & 1, abort_ptr, lane)) { ok = false; break; }
+    for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++n) {
+      const int q_tile = n_q_tiles - 1 - item / BH, bh = item % BH, b = bh / p.H, h = bh % p.H;
+      const int n_kv = p.causal ? min(n_k_tiles, q_tile + 1) : n_k_tiles;
+      const int q0 = q_tile * 128, q_row = q0 + r;
+      const uint32_t tmem_pv = tmem_o + 64u * uint32_t(n & 1);
+      const Dropout drop = make_dropout(p.dropout_p, p.seed + p.ctx->salt * kSaltMultiplier, uint32_t(bh), p.S);
+      float m = -CUDART_INF_F, l = 0.f;
+      for (int j = 0; j < n_kv; ++j, ++tiles) {
+        if (!mbar_wait_warp(&s_full, tiles & 1, abort_ptr, lane)) { ok = false; break; }
+        if (warp == 2 && n == 0) MTS_TRACE(8 * j + 0);
         tc_fence_after_sync();
-        grow = m_tile > m + kRescaleSlack;        // the same decision in both threads of a row: m and m_tile are shared
-        if (__any_sync(0xffffffffu, grow)) {
-          if (grow) { alpha = ex2(m - m_tile); m = m_tile; l *= alpha; }
+        const int k0 = j * 128 + half * 64;
+        const bool need_mask = (p.causal && k0 + 63 > q0) || (k0 + 64 > p.S);
+        uint32_t s0[32], s1[32];
+        tmem_ld_32x32(tmem_s + lane_base + half * 64, s0);
+        tmem_ld_32x32(tmem_s + lane_base + half * 64 + 32, s1);
+        tmem_ld_wait();
+        epilogue_arrive(&s_free, lane);            // S is in registers: the next Q K^T may overwrite it
+        if (warp == 2 && n == 0) MTS_TRACE(8 * j + 1);
+        if (need_mask) {       // one uniform branch around the loop (diagonal and ragged tiles only)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kidx = k0 + i;
+            if (kidx >= p.S || (p.causal && kidx > q_row)) s0[i] = __float_as_uint(-CUDART_INF_F);
+            if (kidx + 32 >= p.S || (p.causal && kidx + 32 > q_row)) s1[i] = __float_as_uint(-CUDART_INF_F);
+          }
+        }
+        float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};   // four independent max chains
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          mx4[0] = fmaxf(mx4[0], __uint_as_float(s0[i]));
+          mx4[1] = fmaxf(mx4[1], __uint_as_float(s0[16 + i]));
+          mx4[2] = fmaxf(mx4[2], __uint_as_float(s1[i]));
+          mx4[3] = fmaxf(mx4[3], __uint_as_float(s1[16 + i]));
+        }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])), mx_other;
+        if (!exchange(mx, mx_other)) { ok = false; break; }
+        mx = fmaxf(mx, mx_other);
+        if (warp == 2 && n == 0) MTS_TRACE(8 * j + 4);
+        const float m_tile = mx * scale_log2;
+        float alpha = 1.f;
+        bool grow = false;
+        if (j == 0) {
+          // the last P V of the previous item was awaited before its write-out: P is free, and this item's O buffer is
+          // handed over by the MMA warp (it waits for the write-out that last read it)
+          m = m_tile == -CUDART_INF_F ? 0.f : m_tile;
+        } else {
+          // previous P V must be complete: its P tile is about to be overwritten and O may be rescaled
+          if (!mbar_wait_warp(&pv_full, (tiles - 1) & 1, abort_ptr, lane)) { ok = false; break; }
+          tc_fence_after_sync();
+          if (warp == 2 && n == 0) MTS_TRACE(8 * j + 5);
+          grow = m_tile > m + kRescaleSlack;        // the same decision in both threads of a row: m and m_tile are shared
+          if (__any_sync(0xffffffffu, grow)) {
+            if (grow) { alpha = ex2(m - m_tile); m = m_tile; l *= alpha; }
 #pragma unroll 1
-          for (int c = 2 * half; c < 2 * half + 2; ++c) {   // rare path: this thread's 32 of the 64 output columns
-            uint32_t oo[16];
-            tmem_ld_32x16(tmem_pv + lane_base + c * 16, oo);
-            tmem_ld_wait();
+            for (int c = 2 * half; c < 2 * half + 2; ++c) {   // rare path: this thread's 32 of the 64 output columns
+              uint32_t oo[16];
+              tmem_ld_32x16(tmem_pv + lane_base + c * 16, oo);
+              tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) oo[i] = __float_as_uint(__uint_as_float(oo[i]) * alpha);
-            tmem_st_32x16(tmem_pv + lane_base + c * 16, oo);
-          }
-          tmem_st_wait();
-        }
-      }
-      float rowsum[8];                          // eight independent partial sums: one accumulator would chain 64 dependent adds
-#pragma unroll
-      for (int i = 0; i < 8; ++i) rowsum[i] = 0.f;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t (&rr)[32] = c == 0 ? s0 : s1;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {            // eight probabilities at a time: exp, dropout, pack, store
-          float e[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            e[i] = ex2(fmaf(__uint_as_float(rr[8 * g + i]), scale_log2, -m));   // masked entries are -inf -> 0
-            rowsum[i] += e[i];
-          }
-          if (drop.thresh != 0u) {
-#pragma unroll
-            for (int w = 0; w < 2; ++w) {
-              const uint32_t bits = drop.word(uint32_t(q_row), uint32_t(k0 + c * 32 + 8 * g + 4 * w) >> 2);
-#pragma unroll
-              for (int t = 0; t < 4; ++t)
-                e[4 * w + t] = ((bits >> (8 * t)) & 0xFFu) >= drop.thresh ? e[4 * w + t] : 0.f;   // 1 / keep: applied to O at the end
+              for (int i = 0; i < 16; ++i) oo[i] = __float_as_uint(__uint_as_float(oo[i]) * alpha);
+              tmem_st_32x16(tmem_pv + lane_base + c * 16, oo);
             }
+            tmem_st_wait();
           }
-          uint4 q4;
-          q4.x = pack2(e[0], e[1]); q4.y = pack2(e[2], e[3]); q4.z = pack2(e[4], e[5]); q4.w = pack2(e[6], e[7]);
-          st_swizzled(p_half, r, c * 4 + g, q4);
         }
+        float rowsum[8];                          // eight independent partial sums: one accumulator would chain 64 dependent adds
+#pragma unroll
+        for (int i = 0; i < 8; ++i) rowsum[i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t (&rr)[32] = c == 0 ? s0 : s1;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {            // eight probabilities at a time: exp, dropout, pack, store
+            float e[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              e[i] = ex2(fmaf(__uint_as_float(rr[8 * g + i]), scale_log2, -m));   // masked entries are -inf -> 0
+              rowsum[i] += e[i];
+            }
+            if (drop.thresh != 0u) {
+#pragma unroll
+              for (int w = 0; w < 2; ++w) {
+                const uint32_t bits = drop.word(uint32_t(q_row), uint32_t(k0 + c * 32 + 8 * g + 4 * w) >> 2);
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+                  e[4 * w + t] = ((bits >> (8 * t)) & 0xFFu) >= drop.thresh ? e[4 * w + t] : 0.f;   // 1 / keep: applied to O at the end
+              }
+            }
+            uint4 q4;
+            q4.x = pack2(e[0], e[1]); q4.y = pack2(e[2], e[3]); q4.z = pack2(e[4], e[5]); q4.w = pack2(e[6], e[7]);
+            st_swizzled(p_half, r, c * 4 + g, q4);
+          }
+        }
+        l += ((rowsum[0] + rowsum[1]) + (rowsum[2] + rowsum[3])) + ((rowsum[4] + rowsum[5]) + (rowsum[6] + rowsum[7]));
+        if (warp == 2 && n == 0) MTS_TRACE(8 * j + 2);
+        fence_proxy_async_smem();                  // P (generic-proxy stores) -> visible to the tensor core
+        epilogue_arrive(&p_ready, lane);
+        if (warp == 2 && n == 0) MTS_TRACE(8 * j + 3);
       }
-      l += ((rowsum[0] + rowsum[1]) + (rowsum[2] + rowsum[3])) + ((rowsum[4] + rowsum[5]) + (rowsum[6] + rowsum[7]));
-      if (warp == 2) MTS_TRACE(8 * j + 2);
-      fence_proxy_async_smem();                  // P (generic-proxy stores) -> visible to the tensor core
-      epilogue_arrive(&p_ready, lane);
-      if (warp == 2) MTS_TRACE(8 * j + 3);
-    }
-    float l_other = 0.f;
-    ok = ok && exchange(l, n_kv & 1, l_other);
-    if (ok && mbar_wait_warp(&pv_full, (n_kv - 1) & 1, abort_ptr, lane)) {
+      if (!ok) break;
+      float l_other = 0.f;
+      if (!exchange(l, l_other)) { ok = false; break; }
+      if (!mbar_wait_warp(&pv_full, (tiles - 1) & 1, abort_ptr, lane)) { ok = false; break; }
       tc_fence_after_sync();
       l += l_other;
       uint32_t rr[32];
       tmem_ld_32x32(tmem_pv + lane_base + half * 32, rr);
       tmem_ld_wait();
+      epilogue_arrive(&o_free[n & 1], lane);       // O is in registers: the buffer may take the item after the next
       if (q_row < p.S) {
         const float inv_l = l > 0.f ? (drop.thresh != 0u ? drop.inv_keep : 1.f) / l : 0.f;
         __nv_bfloat16* dst = p.o + (long long)b * p.o_sb + (long long)h * p.o_sh + (long long)q_row * p.o_ss + half * 32;
@@ -1033,7 +1075,8 @@ cudaError_t launch_flash_fwd(const AttentionArgs& a) {
     if (e != cudaSuccess) return e;
     once = true;
   }
-  const dim3 grid((a.S + 127) / 128, a.B * a.H);
+  const long long items = (long long)((a.S + 127) / 128) * a.B * a.H;
+  const int grid = int(items < 2LL * device_sm_count() ? items : 2LL * device_sm_count());     // two resident CTAs per SM
   (void)cudaGetLastError();
   flash_fwd_kernel<<<grid, THREADS, FWD_SMEM, a.stream>>>(tq, tk, tv, make_params(a));
   ++g_launch_count;

@@ -44,5 +44,8 @@ cudaError_t launch_flash_bwd(const AttentionArgs& a);
 cudaError_t launch_dropout_keep_mask(unsigned char* keep, int BH, int S, float dropout_p, unsigned long long seed,
                                      cudaStream_t stream);
 extern const char* g_attn_last_error;
+#ifdef MTS_ATTN_TRACE
+cudaError_t copy_attention_trace(long long* host, int n);   // clock64 phase stamps of CTA 0 (trace-attention build profile)
+#endif
 
 }  // namespace mts

@@ -545,6 +545,15 @@ std::vector<std::vector<int64_t>> debug_bounds_report(bool reset) {
   return rows;
 }
 
+#ifdef MTS_ATTN_TRACE
+// clock64 phase stamps of the first work item of CTA 0 (trace-attention build profile only)
+Tensor attention_trace() {
+  Tensor out = torch::zeros({8192}, torch::dtype(torch::kInt64));
+  check_launch(mts::copy_attention_trace(reinterpret_cast<long long*>(out.data_ptr<int64_t>()), 8192), "attention trace");
+  return out;
+}
+#endif
+
 bool debug_bounds_enabled() {
 #ifdef MTS_DEBUG_BOUNDS
   return true;
@@ -612,6 +621,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("step_context_tensor", &step_context_tensor);
   m.def("set_step_context", &set_step_context);
   m.def("debug_bounds_report", &debug_bounds_report, py::arg("reset") = true);
+  #ifdef MTS_ATTN_TRACE
+  m.def("attention_trace", &attention_trace);
+#endif
   m.def("debug_bounds_enabled", &debug_bounds_enabled);
   m.def("status_tensor", &status_tensor);
   bind_attention(m);

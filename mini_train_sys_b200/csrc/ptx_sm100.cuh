@@ -57,14 +57,19 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One poll of a phase.  try_wait parks the thread in hardware until the phase completes or a time limit passes; the limit is
+// given explicitly (suspend-time hint, nanoseconds) because the default is short enough that a CTA's idle roles (a loader or
+// an MMA issuer waiting for the arithmetic warps) otherwise spend a quarter of their scheduler's issue slots on polling.
+constexpr uint32_t kTryWaitHintNs = 20000;
+
 __device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kTryWaitHintNs)
       : "memory");
   return done;
 }

@@ -61,7 +61,7 @@ class BuildConfig:
         return [*NVCC_FLAGS, *PROFILES[self.profile], *self.extra_nvcc_flags]
 
     def cache_key(self) -> str:
-        digest = hashlib.sha256(json.dumps([self.profile, list(self.extra_nvcc_flags), NVCC_FLAGS]).encode())
+        digest = hashlib.sha256(json.dumps([self.profile, list(self.extra_nvcc_flags), NVCC_FLAGS, "host-defines"]).encode())
         for path in sorted(CSRC.iterdir()):
             if path.suffix in (".cu", ".cpp", ".cuh", ".h"):
                 digest.update(path.name.encode())
@@ -94,7 +94,8 @@ def build_extension(force: bool = False, verbose: bool = False, config: BuildCon
     os.environ["TORCH_CUDA_ARCH_LIST"] = "10.0a"   # keeps torch from appending its own arch list
     os.environ.setdefault("MAX_JOBS", str(os.cpu_count() or 4))
     BUILD_DIR.mkdir(exist_ok=True)
-    cpp_extension.load(name=EXT_NAME, sources=sources(), extra_cflags=["-O3", "-std=c++17"],
+    # the profile's defines go to the host compiler too: the bindings expose what a diagnostic profile adds
+    cpp_extension.load(name=EXT_NAME, sources=sources(), extra_cflags=["-O3", "-std=c++17", *PROFILES[config.profile]],
                        extra_cuda_cflags=config.nvcc_flags(), extra_include_paths=[str(CSRC)], extra_ldflags=["-lcuda"],
                        build_directory=str(BUILD_DIR), verbose=verbose or config.verbose, is_python_module=False)
     shutil.copy2(BUILD_DIR / f"{EXT_NAME}.so", EXT_PATH)
