@@ -168,13 +168,31 @@ struct Params {
   const __nv_bfloat16 *rope_cos, *rope_sin;   // backward: un-rotate dQ / dK while storing them (nullptr = store as is)
 };
 
+// Work order of the persistent kernels.  A (batch, head) with T tiles along the CTA's own axis is cut into ceil(T / 2) pairs
+// (tile T-1-i, tile i): under a causal mask a pair costs the same whatever i is, so handing pair g to CTA g % grid balances the
+// CTAs without a queue, and CTAs that run at the same time work on the same or neighbouring (batch, head): the K / V (or Q /
+// dO) tiles they stream are read from DRAM once and found in L2 by the others.  Slot `seq` of a CTA is the first (seq even) or
+// second (seq odd) tile of its (seq / 2)-th pair; the middle tile of an odd T is a pair of one.
+struct WorkItem { int tile, bh; bool valid, done; };
+__device__ __forceinline__ WorkItem work_item(int seq, int T, int BH) {
+  const int per_bh = (T + 1) >> 1;
+  const long long pair = (long long)blockIdx.x + (long long)(seq >> 1) * gridDim.x;
+  WorkItem w;
+  w.done = pair >= (long long)per_bh * BH;
+  w.bh = int(pair / per_bh);
+  const int i = int(pair % per_bh);
+  w.tile = (seq & 1) ? i : T - 1 - i;
+  w.valid = !((seq & 1) && i == T - 1 - i);
+  return w;
+}
+
 // =====================================================================================================
 // forward
 // =====================================================================================================
 constexpr int FWD_SMEM = TILE128 /*Q*/ + TILE128 /*K*/ + 2 * TILE128 /*V x 2*/ + 2 * TILE128 /*P*/ + 1024;
 
-// Persistent: the grid is two CTAs per SM and every CTA walks the work items (query tile, batch * head) it owns, heaviest
-// query tiles first.  Barriers and tensor memory are set up once; the loader runs ahead into the next item (its Q as soon
+// Persistent: the grid is two CTAs per SM and every CTA walks the work items (query tile, batch * head) it owns, in the
+// order work_item() gives.  Barriers and tensor memory are set up once; the loader runs ahead into the next item (its Q as soon
 // as the last Q K^T of the current item has been issued, its K / V as their buffers free up) and the MMA warp computes the
 // next item's first scores while the softmax warps write the current item's output, so the latency of an item's first
 // loads and the write-out of its last rows are no longer paid once per 128 query rows.  O is double-buffered in tensor
@@ -198,7 +216,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int n_q_tiles = (p.S + 127) / 128;
   const int n_k_tiles = n_q_tiles;
   const int BH = p.B * p.H;
-  const int total = n_q_tiles * BH;
   if (warp == 0) MTS_TRACE(8000);
 
   if (threadIdx.x == 0) {
@@ -224,10 +241,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       int kt = 0;            // key tiles loaded so far, over all items (K and V counted alike)
       int n = 0;             // items started by this CTA
       bool ok = true;
-      for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++n) {
-        const int q_tile = n_q_tiles - 1 - item / BH, bh = item % BH, b = bh / p.H, h = bh % p.H;
+      for (int seq = 0; ok; ++seq) {
+        const WorkItem w = work_item(seq, n_q_tiles, BH);
+        if (w.done) break;
+        if (!w.valid) continue;
+        const int q_tile = w.tile, bh = w.bh, b = bh / p.H, h = bh % p.H;
         const int n_kv = p.causal ? min(n_k_tiles, q_tile + 1) : n_k_tiles;
+        if (n < 20) MTS_TRACE(7800 + 8 * n + 0);
         if (n > 0 && !mbar_wait(&q_free, (n - 1) & 1, abort_ptr)) break;      // the previous item's Q K^T are all issued and done
+        if (n < 20) MTS_TRACE(7800 + 8 * n + 1);
         mbar_expect_tx(&q_full, TILE128);
         tma_load_4d(sQ, &tm_q, &q_full, 0, q_tile * 128, h, b);
         for (int j = 0; j < n_kv; ++j, ++kt) {
@@ -239,6 +261,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           mbar_expect_tx(&v_full[vs], TILE128);
           tma_load_4d(sV + vs * TILE128, &tm_v, &v_full[vs], 0, j * 128, h, b);
         }
+        ++n;
       }
     }
     __syncwarp();
@@ -255,8 +278,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       int pvs = 0;           // key tiles whose P V has been issued (parity of p_ready / pv_full)
       int n = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++n) {
-        const int q_tile = n_q_tiles - 1 - item / BH;
+      for (int seq = 0; ok; ++seq) {
+        const WorkItem w = work_item(seq, n_q_tiles, BH);
+        if (w.done) break;
+        if (!w.valid) continue;
+        const int q_tile = w.tile;
         const int n_kv = p.causal ? min(n_k_tiles, q_tile + 1) : n_k_tiles;
         const uint32_t tmem_pv = tmem_o + 64u * uint32_t(n & 1);
         // S_j = Q K_j^T.  The softmax warps copy S into registers right away, so S_{j+1} is issued before
@@ -275,8 +301,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ++tiles;
           return true;
         };
+        if (n < 20) MTS_TRACE(7600 + 8 * n + 0);
         if (!mbar_wait(&q_full, n & 1, abort_ptr)) break;
+        if (n < 20) MTS_TRACE(7600 + 8 * n + 1);
         if (!issue_scores(0)) break;
+        if (n < 20) MTS_TRACE(7600 + 8 * n + 2);
         for (int j = 0; j < n_kv; ++j, ++pvs) {
           const int vs = pvs & 1;
           if (n == 0) MTS_TRACE(4096 + 8 * j + 0);
@@ -301,6 +330,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (n == 0) MTS_TRACE(4096 + 8 * j + 3);
           umma_commit(&v_empty[vs]);
         }
+        ++n;
       }
     }
     __syncwarp();
@@ -333,16 +363,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     int tiles = 0;           // key tiles processed, over all items: parity of s_full / pv_full
     int n = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++n) {
-      const int q_tile = n_q_tiles - 1 - item / BH, bh = item % BH, b = bh / p.H, h = bh % p.H;
+    for (int seq = 0; ok; ++seq) {
+      const WorkItem w = work_item(seq, n_q_tiles, BH);
+      if (w.done) break;
+      if (!w.valid) continue;
+      const int q_tile = w.tile, bh = w.bh, b = bh / p.H, h = bh % p.H;
       const int n_kv = p.causal ? min(n_k_tiles, q_tile + 1) : n_k_tiles;
       const int q0 = q_tile * 128, q_row = q0 + r;
       const uint32_t tmem_pv = tmem_o + 64u * uint32_t(n & 1);
       const Dropout drop = make_dropout(p.dropout_p, p.seed + p.ctx->salt * kSaltMultiplier, uint32_t(bh), p.S);
       float m = -CUDART_INF_F, l = 0.f;
+      if (warp == 2 && n < 60) MTS_TRACE(7000 + 8 * n + 0);
       for (int j = 0; j < n_kv; ++j, ++tiles) {
         if (!mbar_wait_warp(&s_full, tiles & 1, abort_ptr, lane)) { ok = false; break; }
         if (warp == 2 && n == 0) MTS_TRACE(8 * j + 0);
+        if (warp == 2 && n < 60 && j == 0) MTS_TRACE(7000 + 8 * n + 1);
         tc_fence_after_sync();
         const int k0 = j * 128 + half * 64;
         const bool need_mask = (p.causal && k0 + 63 > q0) || (k0 + 64 > p.S);
@@ -352,12 +387,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tmem_ld_wait();
         epilogue_arrive(&s_free, lane);            // S is in registers: the next Q K^T may overwrite it
         if (warp == 2 && n == 0) MTS_TRACE(8 * j + 1);
-        if (need_mask) {       // one uniform branch around the loop (diagonal and ragged tiles only)
+        if (need_mask) {       // one uniform branch around the loop (diagonal and ragged tiles only); selects inside, no branches
+          const int last = min(p.S - 1, p.causal ? q_row : 0x7fffffff) - k0;    // last column of this thread's 64 that is kept
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int kidx = k0 + i;
-            if (kidx >= p.S || (p.causal && kidx > q_row)) s0[i] = __float_as_uint(-CUDART_INF_F);
-            if (kidx + 32 >= p.S || (p.causal && kidx + 32 > q_row)) s1[i] = __float_as_uint(-CUDART_INF_F);
+            s0[i] = i > last ? __float_as_uint(-CUDART_INF_F) : s0[i];
+            s1[i] = i + 32 > last ? __float_as_uint(-CUDART_INF_F) : s1[i];
           }
         }
         float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};   // four independent max chains
@@ -434,15 +469,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (warp == 2 && n == 0) MTS_TRACE(8 * j + 3);
       }
       if (!ok) break;
+      if (warp == 2 && n < 60) MTS_TRACE(7000 + 8 * n + 2);
       float l_other = 0.f;
       if (!exchange(l, l_other)) { ok = false; break; }
       if (!mbar_wait_warp(&pv_full, (tiles - 1) & 1, abort_ptr, lane)) { ok = false; break; }
       tc_fence_after_sync();
+      if (warp == 2 && n < 60) MTS_TRACE(7000 + 8 * n + 3);
       l += l_other;
       uint32_t rr[32];
       tmem_ld_32x32(tmem_pv + lane_base + half * 32, rr);
       tmem_ld_wait();
       epilogue_arrive(&o_free[n & 1], lane);       // O is in registers: the buffer may take the item after the next
+      if (warp == 2 && n < 60) MTS_TRACE(7000 + 8 * n + 4);
       if (q_row < p.S) {
         const float inv_l = l > 0.f ? (drop.thresh != 0u ? drop.inv_keep : 1.f) / l : 0.f;
         __nv_bfloat16* dst = p.o + (long long)b * p.o_sb + (long long)h * p.o_sh + (long long)q_row * p.o_ss + half * 32;
@@ -457,7 +495,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         if (half == 0) p.lse[((long long)bh) * p.S + q_row] = (m + log2f(l)) * LN2;
       }
-      if (warp == 2) MTS_TRACE(8002);
+      if (warp == 2 && n < 60) MTS_TRACE(7000 + 8 * n + 5);
+      ++n;
     }
   }
 
@@ -645,12 +684,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
           e[4 * g + 2] = ex2(fmaf(__uint_as_float(rs[4 * g + 2]), scale_log2, -l4.z));
           e[4 * g + 3] = ex2(fmaf(__uint_as_float(rs[4 * g + 3]), scale_log2, -l4.w));
         }
-        if (need_mask) {
+        if (need_mask) {       // selects on two per-thread bounds, no per-element branches
+          const int col0 = qbase + c * 32;
+          const int first = p.causal ? key - col0 : -0x7fffffff;   // queries before the key are masked
+          const int end = key < p.S ? p.S - col0 : 0;              // queries past the sequence; a key past it masks its whole row
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int qi = qbase + c * 32 + j;
-            if (qi >= p.S || key >= p.S || (p.causal && key > qi)) e[j] = 0.f;
-          }
+          for (int j = 0; j < 32; ++j) e[j] = (j < first || j >= end) ? 0.f : e[j];
         }
         uint32_t pa[16], pb[16];
         if (drop.thresh != 0u) {
@@ -867,12 +906,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         float ds[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) ds[j] = ex2(fmaf(__uint_as_float(rs[j]), scale_log2, -lse2));   // probabilities first
-        if (need_mask) {      // one uniform branch around the whole loop: per-element branches would serialise the exponentials
+        if (need_mask) {      // one uniform branch around the whole loop; selects on one per-thread bound inside
+          const int last = q_row < p.S ? min(p.S - 1, p.causal ? q_row : 0x7fffffff) - (kbase + c * 32) : -1;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int kidx = kbase + c * 32 + j;
-            if (kidx >= p.S || q_row >= p.S || (p.causal && kidx > q_row)) ds[j] = 0.f;
-          }
+          for (int j = 0; j < 32; ++j) ds[j] = j > last ? 0.f : ds[j];
         }
         if (drop.thresh != 0u) {
 #pragma unroll
@@ -1075,8 +1112,8 @@ cudaError_t launch_flash_fwd(const AttentionArgs& a) {
     if (e != cudaSuccess) return e;
     once = true;
   }
-  const long long items = (long long)((a.S + 127) / 128) * a.B * a.H;
-  const int grid = int(items < 2LL * device_sm_count() ? items : 2LL * device_sm_count());     // two resident CTAs per SM
+  const long long pairs = (long long)(((a.S + 127) / 128 + 1) / 2) * a.B * a.H;      // see work_item()
+  const int grid = int(pairs < 2LL * device_sm_count() ? pairs : 2LL * device_sm_count());     // two resident CTAs per SM
   (void)cudaGetLastError();
   flash_fwd_kernel<<<grid, THREADS, FWD_SMEM, a.stream>>>(tq, tk, tv, make_params(a));
   ++g_launch_count;
