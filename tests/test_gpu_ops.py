@@ -405,11 +405,57 @@ def test_flash_attention(causal, b, h, s):
     check_kernel_status()
 
 
-def test_flash_attention_dropout_replay():
+def _attention_against_fp32(b, h, s, causal, tol_out=2e-2, tol_grad=3e-2):
+    from mini_train_sys_b200.ops import native_attention as na
+
+    fused = torch.randn(b, s, 3, h, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    q, k, v = (fused[:, :, j].transpose(1, 2) for j in range(3))
+    out = na.flash_attention(q, k, v, is_causal=causal, dropout_p=0.0)
+    d_o = torch.randn(b, h, s, 64, device=DEV, dtype=torch.bfloat16)
+    (g,) = torch.autograd.grad(out, fused, d_o)
+    f32 = fused.detach().float().requires_grad_()
+    q32, k32, v32 = (f32[:, :, j].transpose(1, 2) for j in range(3))
+    want = ref.attention_ref(q32, k32, v32, is_causal=causal)
+    (rg,) = torch.autograd.grad(want, f32, d_o.float())
+    assert_close(out, want, tol_out, f"out s={s}")
+    floor = 1e-3 * float(d_o.float().norm())
+    for j, name in enumerate("qkv"):
+        assert_close(g[:, :, j], rg[:, :, j], tol_grad, f"d{name} s={s}", floor=floor)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("b,h,s", [(24, 12, 512), (2, 12, 2048), (32, 12, 384), (40, 8, 200)])
+def test_flash_attention_many_items_per_cta(causal, b, h, s):
+    """Shapes with more work items than resident CTAs: the persistent forward walks several (query tile, batch x head) items per
+    CTA (barrier phases, the K / V buffers and the two O buffers in tensor memory wrap around), with an even and an odd number of
+    query tiles, a ragged last tile, and 16 key tiles per item."""
+
+    from mini_train_sys_b200.ops.native_backend import check_kernel_status
+
+    torch.manual_seed(31)
+    _attention_against_fp32(b, h, s, causal)
+    check_kernel_status()
+
+
+def test_flash_attention_every_length_up_to_130():
+    """Every sequence length from 1 to 130: all ragged-edge positions of the first and the second 128-row tile."""
+
+    from mini_train_sys_b200.ops.native_backend import check_kernel_status
+
+    torch.manual_seed(32)
+    for s in range(1, 131):
+        _attention_against_fp32(1, 2, s, True)
+    for s in (1, 2, 63, 64, 65, 127, 128, 129, 130):
+        _attention_against_fp32(1, 2, s, False)
+    check_kernel_status()
+
+
+@pytest.mark.parametrize("b,h,s,p", [(2, 2, 200, 0.1), (1, 3, 512, 0.1), (3, 2, 1000, 0.25)])
+def test_flash_attention_dropout_replay(b, h, s, p):
     from mini_train_sys_b200.ops import native_attention as na
 
     torch.manual_seed(14)
-    b, h, s, p, seed = 2, 2, 200, 0.1, 1234567
+    seed = 1234567
     q, k, v = (torch.randn(b, h, s, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
     out = na.flash_attention(q, k, v, is_causal=True, dropout_p=p, seed=seed)
     d_o = torch.randn_like(out)
