@@ -330,7 +330,9 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&v)[32]) {
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
-template <bool PAIR, bool A_MN, bool B_MN>
+// EPI (the epilogue) is a template parameter so that every instantiation holds one epilogue only: with all three behind a
+// run-time switch the register allocation of each was that of the largest.
+template <bool PAIR, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_aux, const KernelParams p) {
@@ -578,11 +580,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool row_ok = row < t.row_limit;
       // SwiGLU epilogues of the routed experts: this row's route weight (0 on padding rows) and, in backward, where the
       // gradient of that weight is accumulated
-      const float wrow = (p.row_scale != nullptr && p.epilogue != EPI_STORE && row_ok) ? __ldg(p.row_scale + row) : 1.f;
+      const float wrow = (p.row_scale != nullptr && EPI != EPI_STORE && row_ok) ? __ldg(p.row_scale + row) : 1.f;
       float wgrad_part = 0.f;
       if (t.k_blocks == 0) {
         // nothing was contracted: the product is zero
-        if (p.tma_store && p.epilogue == EPI_STORE && !p.accumulate && !p.atomic_out) {
+        if (p.tma_store && EPI == EPI_STORE && !p.accumulate && !p.atomic_out) {
           float z[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) z[j] = 0.f;
@@ -592,7 +594,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const int step = p.out_fp32 ? 32 : 64;
           for (int col = t.c_col + half_id * 128; col < t.c_col + half_id * 128 + 128; col += step)
             if (col < t.col_limit && row0 < t.row_limit) flush_box(&tm_out, stage, col, row0, t.out_group, false, lane);
-        } else if (p.epilogue == EPI_STORE && !p.accumulate && !p.atomic_out && row_ok) {
+        } else if (EPI == EPI_STORE && !p.accumulate && !p.atomic_out && row_ok) {
           float z[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) z[j] = 0.f;
@@ -611,7 +613,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       // other chunks are pulled into L2 meanwhile, and each is loaded one chunk ahead of its use.
       uint4 cg[4], cu[4];
       bool swb_fast = false;
-      if (p.tma_store && p.epilogue == EPI_SWIGLU_BWD) {
+      if (p.tma_store && EPI == EPI_SWIGLU_BWD) {
         const int colw = t.c_col + half_id * 128;
         const __nv_bfloat16* pre = reinterpret_cast<const __nv_bfloat16*>(p.aux);
         swb_fast = row0 < t.row_limit && aux_vec && colw + 128 <= p.N;
@@ -644,7 +646,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         released = true;
       };
 
-      if (p.tma_store && p.epilogue == EPI_STORE) {
+      if (p.tma_store && EPI == EPI_STORE) {
         uint32_t r0[32], r1[32], r2[32], r3[32];
         const int c0 = half_id * 4;
         tmem_ld_32x32(taddr + (c0 + 0) * 32, r0);
@@ -676,7 +678,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           regs_to_float(r3, v); stage_row_bf16(stage, lane, 4, v);
           if (box_rows && col0 + 64 < t.col_limit) flush_box(&tm_out, stage, col0 + 64, row0, t.out_group, false, lane);
         }
-      } else if (p.tma_store && p.epilogue == EPI_SWIGLU) {
+      } else if (p.tma_store && EPI == EPI_SWIGLU) {
         const int half = p.N / 2;
         uint32_t rg0[32], ru0[32], rg1[32], ru1[32];
         const int c0 = half_id * 2;
@@ -765,7 +767,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (box_ok) flush_box(&tm_out, stage, p.N + col0, row0, 0, false, lane);
           }
         }
-      } else if (p.epilogue == EPI_STORE) {
+      } else if (EPI == EPI_STORE) {
         // this warp's four chunks: one TMEM round trip
         uint32_t r0[32], r1[32], r2[32], r3[32];
         const int c0 = half_id * 4;
@@ -788,7 +790,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
         };
         put(r0, c0); put(r1, c0 + 1); put(r2, c0 + 2); put(r3, c0 + 3);
-      } else if (p.epilogue == EPI_SWIGLU) {
+      } else if (EPI == EPI_SWIGLU) {
         const int half = p.N / 2;
         uint32_t rg0[32], ru0[32], rg1[32], ru1[32];
         const int c0 = half_id * 2;
@@ -851,7 +853,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           put(ra, c0); put(rb, c0 + 1);
         }
       }
-      if (p.epilogue == EPI_SWIGLU_BWD && p.row_grad != nullptr && p.row_slot != nullptr && row_ok) {
+      if (EPI == EPI_SWIGLU_BWD && p.row_grad != nullptr && p.row_slot != nullptr && row_ok) {
         const int slot = __ldg(p.row_slot + row);
         if (slot >= 0) atomicAdd(p.row_grad + slot, wgrad_part);     // eight partial sums per row (column halves x N tiles)
       }
@@ -1045,23 +1047,28 @@ cudaError_t launch_gemm_sm100(const GemmArgs& a) {
   if (total < workers) workers = int(total);
 
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const KernelParams);
-  static const KernelFn kernels[2][2][2] = {
-      {{gemm_tcgen05_kernel<false, false, false>, gemm_tcgen05_kernel<false, false, true>},
-       {gemm_tcgen05_kernel<false, true, false>, gemm_tcgen05_kernel<false, true, true>}},
-      {{gemm_tcgen05_kernel<true, false, false>, gemm_tcgen05_kernel<true, false, true>},
-       {gemm_tcgen05_kernel<true, true, false>, gemm_tcgen05_kernel<true, true, true>}}};
+#define MTS_GEMM_EPI(P, A, B) {gemm_tcgen05_kernel<P, A, B, EPI_STORE>, gemm_tcgen05_kernel<P, A, B, EPI_SWIGLU>, \
+                              gemm_tcgen05_kernel<P, A, B, EPI_SWIGLU_BWD>}
+  static const KernelFn kernels[2][2][2][3] = {
+      {{MTS_GEMM_EPI(false, false, false), MTS_GEMM_EPI(false, false, true)},
+       {MTS_GEMM_EPI(false, true, false), MTS_GEMM_EPI(false, true, true)}},
+      {{MTS_GEMM_EPI(true, false, false), MTS_GEMM_EPI(true, false, true)},
+       {MTS_GEMM_EPI(true, true, false), MTS_GEMM_EPI(true, true, true)}}};
+#undef MTS_GEMM_EPI
+  static_assert(EPI_STORE == 0 && EPI_SWIGLU == 1 && EPI_SWIGLU_BWD == 2, "the kernel table is indexed by the epilogue code");
   static bool attr_set_on[64] = {};          // cudaFuncSetAttribute applies to the current device only
   bool& attr_set = attr_set_on[current_device()];
   if (!attr_set) {
-    for (int i = 0; i < 8; ++i) {
-      const bool pr = (i >> 2) & 1;
-      cudaError_t e = cudaFuncSetAttribute(kernels[pr][(i >> 1) & 1][i & 1], cudaFuncAttributeMaxDynamicSharedMemorySize,
+    for (int i = 0; i < 24; ++i) {
+      const bool pr = (i / 12) & 1;
+      cudaError_t e = cudaFuncSetAttribute(kernels[pr][(i / 6) & 1][(i / 3) & 1][i % 3], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            int(pr ? Cfg<true>::SMEM_BYTES : Cfg<false>::SMEM_BYTES));
       if (e != cudaSuccess) return e;
     }
     attr_set = true;
   }
-  const KernelFn kernel = kernels[pair ? 1 : 0][a.a_mn_major ? 1 : 0][a.b_mn_major ? 1 : 0];
+  if (a.epilogue < 0 || a.epilogue > 2) return cudaErrorInvalidValue;
+  const KernelFn kernel = kernels[pair ? 1 : 0][a.a_mn_major ? 1 : 0][a.b_mn_major ? 1 : 0][a.epilogue];
   (void)cudaGetLastError();   // do not attribute an earlier sticky error to this launch
   cudaError_t launch_err;
   if (pair) {
