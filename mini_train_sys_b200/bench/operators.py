@@ -110,7 +110,8 @@ def build_case(kernel: str, profile: OperatorProfile, tokens: int) -> BenchCase:
         def run(ops, a):
             if hasattr(ops, "router_logits"):
                 return ops.router_logits(a["x"], a["w"])
-            return torch.nn.functional.linear(a["x"].float(), a["w"].float())
+            with torch.autocast(a["x"].device.type, enabled=False):      # the router's logits are an fp32 product in every back end
+                return torch.nn.functional.linear(a["x"].float(), a["w"].float())
         return BenchCase(kernel, label, lambda d: {"x": _randn((t, h), d), "w": _randn((p.experts, h), d, dtype=torch.float32, scale=0.02)},
                          run, t, bytes_moved=t * h * 2 + t * p.experts * 4, atol=2e-2, rtol=2e-2, meta=meta)
     if kernel == "router":

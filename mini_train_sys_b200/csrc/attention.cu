@@ -197,6 +197,7 @@ constexpr int FWD_SMEM = TILE128 /*Q*/ + TILE128 /*K*/ + 2 * TILE128 /*V x 2*/ +
 // next item's first scores while the softmax warps write the current item's output, so the latency of an item's first
 // loads and the write-out of its last rows are no longer paid once per 128 query rows.  O is double-buffered in tensor
 // memory (columns 128..191 and 192..255) so that the next item's first P V does not wait for that write-out.
+template <bool DROPOUT>
 __global__ void __launch_bounds__(THREADS, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Params p) {
@@ -448,7 +449,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               e[i] = ex2(fmaf(__uint_as_float(rr[8 * g + i]), scale_log2, -m));   // masked entries are -inf -> 0
               rowsum[i] += e[i];
             }
-            if (drop.thresh != 0u) {
+            if (DROPOUT) {
 #pragma unroll
               for (int w = 0; w < 2; ++w) {
                 const uint32_t bits = drop.word(uint32_t(q_row), uint32_t(k0 + c * 32 + 8 * g + 4 * w) >> 2);
@@ -482,7 +483,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       epilogue_arrive(&o_free[n & 1], lane);       // O is in registers: the buffer may take the item after the next
       if (warp == 2 && n < 60) MTS_TRACE(7000 + 8 * n + 4);
       if (q_row < p.S) {
-        const float inv_l = l > 0.f ? (drop.thresh != 0u ? drop.inv_keep : 1.f) / l : 0.f;
+        const float inv_l = l > 0.f ? (DROPOUT ? drop.inv_keep : 1.f) / l : 0.f;
         __nv_bfloat16* dst = p.o + (long long)b * p.o_sb + (long long)h * p.o_sh + (long long)q_row * p.o_ss + half * 32;
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
@@ -516,6 +517,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // =====================================================================================================
 constexpr int BWD_KV_SMEM = 2 * TILE128 /*K,V*/ + 4 * TILE64 /*Q,dO x 2 stages*/ + 2 * TILE128 /*P^T, dS^T*/ + 2048 /*lse, delta*/ + 1024;
 
+template <bool DROPOUT>
 __global__ void __launch_bounds__(THREADS, 2)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do64, const Params p) {
@@ -692,7 +694,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
           for (int j = 0; j < 32; ++j) e[j] = (j < first || j >= end) ? 0.f : e[j];
         }
         uint32_t pa[16], pb[16];
-        if (drop.thresh != 0u) {
+        if (DROPOUT) {
           // Keep bits: one hashed word covers four consecutive keys of one query, i.e. the four lanes of a quad.
           // Each lane hashes the words of 8 of the 32 queries and the quad exchanges them by shuffle.
           uint32_t words[8];
@@ -756,7 +758,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
       }
       if (key < p.S && c == 0) {
         store_row64(p.dv + (long long)b * p.dv_sb + (long long)h * p.dv_sh + (long long)key * p.dv_ss, acc,
-                    drop.thresh != 0u ? drop.inv_keep : 1.f);
+                    DROPOUT ? drop.inv_keep : 1.f);
       } else if (key < p.S) {
         __nv_bfloat16* dst = p.dk + (long long)b * p.dk_sb + (long long)h * p.dk_sh + (long long)key * p.dk_ss;
         if (p.rope_cos != nullptr) store_row64_unrotated(dst, acc, p.scale, p.rope_cos + (long long)key * 64, p.rope_sin + (long long)key * 64);
@@ -780,6 +782,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q64, const __grid_c
 // =====================================================================================================
 constexpr int BWD_Q_SMEM = 2 * TILE128 /*Q,dO*/ + 4 * TILE64 /*K,V x 2 stages*/ + TILE128 /*dS*/ + 1024;
 
+template <bool DROPOUT>
 __global__ void __launch_bounds__(THREADS, 2)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k64,
                     const __grid_constant__ CUtensorMap tm_v64, const __grid_constant__ CUtensorMap tm_do, const Params p) {
@@ -911,7 +914,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
           for (int j = 0; j < 32; ++j) ds[j] = j > last ? 0.f : ds[j];
         }
-        if (drop.thresh != 0u) {
+        if (DROPOUT) {
 #pragma unroll
           for (int w = 0; w < 8; ++w) {
             const uint32_t bits = drop.word(uint32_t(q_row), uint32_t(kbase + c * 32 + 4 * w) >> 2);
@@ -1108,14 +1111,17 @@ cudaError_t launch_flash_fwd(const AttentionArgs& a) {
     return cudaErrorInvalidValue;
   static bool once = false;
   if (!once) {
-    cudaError_t e = set_smem(flash_fwd_kernel, FWD_SMEM);
+    cudaError_t e = set_smem(flash_fwd_kernel<false>, FWD_SMEM);
+    if (e == cudaSuccess) e = set_smem(flash_fwd_kernel<true>, FWD_SMEM);
     if (e != cudaSuccess) return e;
     once = true;
   }
   const long long pairs = (long long)(((a.S + 127) / 128 + 1) / 2) * a.B * a.H;      // see work_item()
   const int grid = int(pairs < 2LL * device_sm_count() ? pairs : 2LL * device_sm_count());     // two resident CTAs per SM
   (void)cudaGetLastError();
-  flash_fwd_kernel<<<grid, THREADS, FWD_SMEM, a.stream>>>(tq, tk, tv, make_params(a));
+  // the dropout arithmetic is compiled into an instantiation of its own: p = 0 runs (evaluation, most fine-tuning) carry none of it
+  if (a.dropout_p > 0.f) flash_fwd_kernel<true><<<grid, THREADS, FWD_SMEM, a.stream>>>(tq, tk, tv, make_params(a));
+  else flash_fwd_kernel<false><<<grid, THREADS, FWD_SMEM, a.stream>>>(tq, tk, tv, make_params(a));
   ++g_launch_count;
   return cudaGetLastError();
 }
@@ -1131,8 +1137,10 @@ cudaError_t launch_flash_bwd(const AttentionArgs& a) {
     return cudaErrorInvalidValue;
   static bool once = false;
   if (!once) {
-    cudaError_t e = set_smem(flash_bwd_dkdv_kernel, BWD_KV_SMEM);
-    if (e == cudaSuccess) e = set_smem(flash_bwd_dq_kernel, BWD_Q_SMEM);
+    cudaError_t e = set_smem(flash_bwd_dkdv_kernel<false>, BWD_KV_SMEM);
+    if (e == cudaSuccess) e = set_smem(flash_bwd_dkdv_kernel<true>, BWD_KV_SMEM);
+    if (e == cudaSuccess) e = set_smem(flash_bwd_dq_kernel<false>, BWD_Q_SMEM);
+    if (e == cudaSuccess) e = set_smem(flash_bwd_dq_kernel<true>, BWD_Q_SMEM);
     if (e != cudaSuccess) return e;
     once = true;
   }
@@ -1143,8 +1151,13 @@ cudaError_t launch_flash_bwd(const AttentionArgs& a) {
       a.d_o.sb, a.d_o.sh, a.d_o.ss, a.delta, a.B, a.H, a.S);
   const Params p = make_params(a);
   const dim3 grid((a.S + 127) / 128, a.B * a.H);
-  flash_bwd_dkdv_kernel<<<grid, THREADS, BWD_KV_SMEM, a.stream>>>(tq64, tk128, tv128, tdo64, p);
-  flash_bwd_dq_kernel<<<grid, THREADS, BWD_Q_SMEM, a.stream>>>(tq128, tk64, tv64, tdo128, p);
+  if (a.dropout_p > 0.f) {
+    flash_bwd_dkdv_kernel<true><<<grid, THREADS, BWD_KV_SMEM, a.stream>>>(tq64, tk128, tv128, tdo64, p);
+    flash_bwd_dq_kernel<true><<<grid, THREADS, BWD_Q_SMEM, a.stream>>>(tq128, tk64, tv64, tdo128, p);
+  } else {
+    flash_bwd_dkdv_kernel<false><<<grid, THREADS, BWD_KV_SMEM, a.stream>>>(tq64, tk128, tv128, tdo64, p);
+    flash_bwd_dq_kernel<false><<<grid, THREADS, BWD_Q_SMEM, a.stream>>>(tq128, tk64, tv64, tdo128, p);
+  }
   g_launch_count += 3;
   return cudaGetLastError();
 }
