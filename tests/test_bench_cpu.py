@@ -23,7 +23,8 @@ def test_close_stats_streams_and_flags_violations():
     assert not close_stats(torch.tensor([float("nan")]), torch.tensor([0.0]), atol=1.0, rtol=0.0)["passed"]
 
 
-@pytest.mark.parametrize("kernel", ["rmsnorm", "swiglu", "rope", "attention", "cross_entropy", "fused_linear_cross_entropy", "router", "fused_moe"])
+@pytest.mark.parametrize("kernel", ["embedding", "rmsnorm", "swiglu", "rope", "attention", "cross_entropy", "fused_linear_cross_entropy", "linear",
+                                    "router", "router_logits", "fused_moe"])
 def test_operator_cases_agree_between_library_and_oracle_back_ends(kernel):
     from mini_train_sys_b200.bench.measurement import correctness_stats
     from mini_train_sys_b200.bench.operators import OperatorProfile, build_case
