@@ -1100,6 +1100,14 @@ cudaError_t set_smem(K kernel, int bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
+// cudaFuncSetAttribute applies to the current device only: remember per device ordinal which launchers have raised their
+// shared-memory limit (a process that drives several GPUs would otherwise launch with the default limit on all but the first).
+bool* attr_done_slot(bool (&flags)[64]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  return &flags[dev];
+}
+
 }  // namespace
 
 cudaError_t launch_flash_fwd(const AttentionArgs& a) {
@@ -1109,12 +1117,14 @@ cudaError_t launch_flash_fwd(const AttentionArgs& a) {
   if (!encode_bhsd(&tq, a.q, a.B, a.H, a.S, 128) || !encode_bhsd(&tk, a.k, a.B, a.H, a.S, 128) ||
       !encode_bhsd(&tv, a.v, a.B, a.H, a.S, 128))
     return cudaErrorInvalidValue;
-  static bool once = false;
-  if (!once) {
+  static bool done_on[64] = {};
+  bool* done = attr_done_slot(done_on);
+  if (done == nullptr) { g_attn_last_error = "unexpected device ordinal"; return cudaErrorInvalidDevice; }
+  if (!*done) {
     cudaError_t e = set_smem(flash_fwd_kernel<false>, FWD_SMEM);
     if (e == cudaSuccess) e = set_smem(flash_fwd_kernel<true>, FWD_SMEM);
     if (e != cudaSuccess) return e;
-    once = true;
+    *done = true;
   }
   const long long pairs = (long long)(((a.S + 127) / 128 + 1) / 2) * a.B * a.H;      // see work_item()
   const int grid = int(pairs < 2LL * device_sm_count() ? pairs : 2LL * device_sm_count());     // two resident CTAs per SM
@@ -1135,14 +1145,16 @@ cudaError_t launch_flash_bwd(const AttentionArgs& a) {
       !encode_bhsd(&tv128, a.v, a.B, a.H, a.S, 128) || !encode_bhsd(&tv64, a.v, a.B, a.H, a.S, 64) ||
       !encode_bhsd(&tdo128, a.d_o, a.B, a.H, a.S, 128) || !encode_bhsd(&tdo64, a.d_o, a.B, a.H, a.S, 64))
     return cudaErrorInvalidValue;
-  static bool once = false;
-  if (!once) {
+  static bool done_on[64] = {};
+  bool* done = attr_done_slot(done_on);
+  if (done == nullptr) { g_attn_last_error = "unexpected device ordinal"; return cudaErrorInvalidDevice; }
+  if (!*done) {
     cudaError_t e = set_smem(flash_bwd_dkdv_kernel<false>, BWD_KV_SMEM);
     if (e == cudaSuccess) e = set_smem(flash_bwd_dkdv_kernel<true>, BWD_KV_SMEM);
     if (e == cudaSuccess) e = set_smem(flash_bwd_dq_kernel<false>, BWD_Q_SMEM);
     if (e == cudaSuccess) e = set_smem(flash_bwd_dq_kernel<true>, BWD_Q_SMEM);
     if (e != cudaSuccess) return e;
-    once = true;
+    *done = true;
   }
   (void)cudaGetLastError();
   const long long rows = (long long)a.B * a.H * a.S;
