@@ -9,7 +9,8 @@
   the rank's bf16 shard resident and pulls each unit from the owners' shards over peer memory into a two-slot staging
   buffer one unit ahead of its use (forward and backward); ``shard_grad_op`` keeps a bf16 replica per rank that the
   AdamW kernel refreshes on every rank by peer stores, so no gather runs during the step.  Options the fused engine
-  does not implement (CPU offload, ``no_shard`` / ``hybrid_shard``, fp16 loss scaling) are refused, not ignored.
+  does not implement (CPU offload, ``no_shard`` / ``hybrid_shard``, fp16 loss scaling) are never ignored: an explicit
+  ``engine: fused`` with one of them is refused, ``engine: auto`` selects the ``nccl`` engine, which honours them.
 """
 
 from __future__ import annotations
@@ -63,6 +64,28 @@ class FSDPStrategy(ProcessGroupMixin):
         self.engine = engine
         self.comm = comm
 
+    @staticmethod
+    def fused_unsupported(*, cpu_offload: bool, sharding_strategy: str, precision: str) -> list[str]:
+        """The requested options the fused engine does not implement (empty: it can run the configuration)."""
+
+        missing = []
+        if cpu_offload:
+            missing.append("cpu_offload")
+        if sharding_strategy not in ("full_shard", "shard_grad_op"):
+            missing.append(f"sharding_strategy={sharding_strategy}")
+        if precision == "fp16":
+            missing.append("precision=fp16 (loss scaling)")
+        return missing
+
+    @classmethod
+    def choose_engine(cls, requested: str, available: str, **options) -> str:
+        """Engine for an FSDP run: ``requested`` is what the configuration says (``auto`` / ``fused`` / ``nccl``),
+        ``available`` what the machine and back end allow.  ``auto`` never picks an engine that would have to refuse the run."""
+
+        if requested == "auto" and available == "fused" and cls.fused_unsupported(**options):
+            return "nccl"
+        return available
+
     def resolved_engine(self) -> str:
         return "fused" if self.engine in ("auto", "fused") else "nccl"
 
@@ -99,13 +122,8 @@ class FSDPStrategy(ProcessGroupMixin):
         if self.resolved_engine() == "fused":
             from mini_train_sys_b200.parallel.flat_engine import FlatDataParallel
 
-            unsupported = []
-            if self.cpu_offload:
-                unsupported.append("cpu_offload")
-            if self.sharding_strategy not in ("full_shard", "shard_grad_op"):
-                unsupported.append(f"sharding_strategy={self.sharding_strategy}")
-            if self.precision == "fp16":
-                unsupported.append("precision=fp16 (loss scaling)")
+            unsupported = self.fused_unsupported(cpu_offload=self.cpu_offload, sharding_strategy=self.sharding_strategy,
+                                                 precision=self.precision)
             if unsupported:
                 raise ValueError("parallel.comm.engine=fused does not implement: " + ", ".join(unsupported)
                                  + "; select parallel.comm.engine=nccl for these options")

@@ -47,8 +47,10 @@ def build_parallel_strategy(cfg: ExperimentConfig, *, resolved_precision: str | 
         from mini_train_sys_b200.parallel.fsdp import FSDPStrategy
 
         precision = resolved_precision or cfg.train.precision
-        return FSDPStrategy(**common, **vars(cfg.parallel.fsdp), precision=precision, engine=engine,
-                            comm=cfg.parallel.comm)
+        options = vars(cfg.parallel.fsdp)
+        engine = FSDPStrategy.choose_engine(cfg.parallel.comm.engine, engine, cpu_offload=bool(options.get("cpu_offload", False)),
+                                            sharding_strategy=str(options.get("sharding_strategy", "full_shard")), precision=precision)
+        return FSDPStrategy(**common, **options, precision=precision, engine=engine, comm=cfg.parallel.comm)
     if name == "ep":
         from mini_train_sys_b200.parallel.ep import ExpertParallelStrategy
 

@@ -203,6 +203,19 @@ def test_fused_fsdp_refuses_options_it_does_not_implement():
             strat.wrap_model(make_model(DENSE))
 
 
+def test_auto_engine_never_picks_one_that_would_refuse_the_run():
+    from mini_train_sys_b200.parallel.fsdp import FSDPStrategy
+
+    plain = dict(cpu_offload=False, sharding_strategy="full_shard", precision="bf16")
+    assert FSDPStrategy.choose_engine("auto", "fused", **plain) == "fused"
+    assert FSDPStrategy.choose_engine("auto", "nccl", **plain) == "nccl"
+    for change in ({"cpu_offload": True}, {"sharding_strategy": "no_shard"}, {"sharding_strategy": "hybrid_shard"}, {"precision": "fp16"}):
+        assert FSDPStrategy.choose_engine("auto", "fused", **{**plain, **change}) == "nccl"
+        assert FSDPStrategy.choose_engine("fused", "fused", **{**plain, **change}) == "fused"     # explicit: refused at wrap time
+    assert FSDPStrategy.fused_unsupported(cpu_offload=True, sharding_strategy="no_shard", precision="fp16") == [
+        "cpu_offload", "sharding_strategy=no_shard", "precision=fp16 (loss scaling)"]
+
+
 def _bytes_worker(rank, world, port, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
