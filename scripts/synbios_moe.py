@@ -23,6 +23,12 @@
     summarize-probe-batch-benchmarks   merge benchmark runs of several devices into one recommendation
     compare-formal-studies single vs multi5+permute probe studies: tidy table, headline means, Markdown
     diagnostic-report      oracle and routing evidence of both conditions side by side
+    bad-case-routes        experts chosen at the first two value tokens where Q-first is right and Q-whole wrong
+
+The command names of the reference's CLI are accepted as aliases (``validate-probe-oracle-first-token``,
+``validate-probe-bad-case-routes``, ``train-ground-truth-first-whole``, ``summarize-ground-truth-first-whole``,
+``benchmark-probe-batches``, ``benchmark-ground-truth-first-whole-batches``, ``summarize-probe-benchmarks``,
+``report-probe-diagnostics``).
 
 Evaluation and probing always build the model with the library (``torch``) operator back end in fp32 and load only the
 exported ``model.pt`` (reference: scripts/synbios_moe.py:141-168), independent of how training was sharded.
@@ -355,6 +361,21 @@ def cmd_oracle_first_token(args) -> int:
     return 0
 
 
+def cmd_bad_case_routes(args) -> int:
+    from experiments.synbios_moe.mechanisms.token_routes import bad_case_route_validation
+
+    codec = _codec(args)
+    sink = EventSink(args.log_dir, args.quiet)
+    model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
+    attributes = tuple(args.attributes.split(",")) if args.attributes else None
+    summary = bad_case_route_validation(model, codec, data_root=args.data, cache_root=args.probe_cache, probe_dir=args.probe_dir,
+                                        output_dir=args.output, device=args.device, attributes=attributes,
+                                        batch_size=args.batch_size, max_examples=args.max_examples, pair_limit=args.pair_limit,
+                                        progress=lambda name, done: sink({"event": "route_progress", "attribute": name, "done": done}))
+    print(json.dumps({k: summary[k] for k in ("protocol", "examples", "attributes", "layers")}))
+    return 0
+
+
 def cmd_ground_truth_first_whole(args) -> int:
     from experiments.synbios_moe.artifact_io import write_json
     from experiments.synbios_moe.mechanisms.first_token_intervention import train_ground_truth_first_whole_probe
@@ -528,12 +549,12 @@ def build_parser() -> argparse.ArgumentParser:
             p.add_argument(f"--{side}-{what}")
     p.add_argument("--output"); p.set_defaults(func=cmd_audit)
 
-    p = sub.add_parser("oracle-first-token"); common(p)
+    p = sub.add_parser("oracle-first-token", aliases=["validate-probe-oracle-first-token"]); common(p)
     p.add_argument("--data", required=True); p.add_argument("--probe-cache", required=True); p.add_argument("--probe-dir", required=True)
     p.add_argument("--output", required=True); p.add_argument("--attributes"); p.add_argument("--batch-size", type=int, default=256)
     p.add_argument("--max-examples", type=int); p.set_defaults(func=cmd_oracle_first_token)
 
-    p = sub.add_parser("ground-truth-first-whole"); common(p)
+    p = sub.add_parser("ground-truth-first-whole", aliases=["train-ground-truth-first-whole"]); common(p)
     p.add_argument("--probe-cache", required=True); p.add_argument("--probe-dir", required=True); p.add_argument("--output", required=True)
     p.add_argument("--attribute", required=True); p.add_argument("--steps", type=int, default=3000); p.add_argument("--seed", type=int, default=1337)
     p.add_argument("--batch-size", type=int, default=50); p.add_argument("--evaluation-batch-size", type=int, default=256)
@@ -541,29 +562,38 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--resume-probe", action=argparse.BooleanOptionalAction, default=True)
     p.add_argument("--max-validation-examples", type=int); p.set_defaults(func=cmd_ground_truth_first_whole)
 
-    p = sub.add_parser("ground-truth-first-report"); p.add_argument("--run-dir", required=True); p.add_argument("--probe-dir", required=True)
+    p = sub.add_parser("ground-truth-first-report", aliases=["summarize-ground-truth-first-whole"]); p.add_argument("--run-dir", "--run", dest="run_dir", required=True); p.add_argument("--probe-dir", required=True)
     p.add_argument("--output"); p.set_defaults(func=cmd_ground_truth_first_report)
 
     p = sub.add_parser("company-relation"); p.add_argument("--input-csv", required=True); p.add_argument("--output", required=True)
     p.add_argument("--condition", default="multi5_permute"); p.set_defaults(func=cmd_company_relation)
 
-    p = sub.add_parser("probe-batch-benchmark"); common(p)
-    p.add_argument("--probe-cache", required=True); p.add_argument("--output", required=True); p.add_argument("--probe-dir")
-    p.add_argument("--attribute", default="university"); p.add_argument("--target", choices=("first", "whole"), default="whole")
-    p.add_argument("--kinds", default="p,q"); p.add_argument("--mode", choices=("training", "validation"), default="training")
-    p.add_argument("--p-batch-sizes", default="25,50,100,200"); p.add_argument("--q-batch-sizes", default="100,200,400,800")
-    p.add_argument("--rank", type=int); p.add_argument("--warmup-steps", type=int, default=3); p.add_argument("--measure-steps", type=int, default=10)
-    p.add_argument("--memory-limit-percent", type=float, default=92.0); p.add_argument("--ground-truth-first", action="store_true")
-    p.set_defaults(func=cmd_probe_batch_benchmark)
+    for name, aliases, gtf in (("probe-batch-benchmark", ["benchmark-probe-batches"], False),
+                               ("benchmark-ground-truth-first-whole-batches", [], True)):
+        p = sub.add_parser(name, aliases=aliases); common(p)
+        p.add_argument("--probe-cache", required=True); p.add_argument("--output", required=True); p.add_argument("--probe-dir")
+        p.add_argument("--attribute", default="university"); p.add_argument("--target", choices=("first", "whole"), default="whole")
+        p.add_argument("--kinds", default="p" if gtf else "p,q"); p.add_argument("--mode", choices=("training", "validation"), default="training")
+        p.add_argument("--p-batch-sizes", default="25,50,100,200"); p.add_argument("--q-batch-sizes", default="100,200,400,800")
+        p.add_argument("--rank", type=int); p.add_argument("--warmup-steps", type=int, default=3); p.add_argument("--measure-steps", type=int, default=10)
+        p.add_argument("--memory-limit-percent", type=float, default=92.0)
+        p.add_argument("--ground-truth-first", action=argparse.BooleanOptionalAction, default=gtf)
+        p.set_defaults(func=cmd_probe_batch_benchmark)
 
-    p = sub.add_parser("summarize-probe-batch-benchmarks"); p.add_argument("results", nargs="+"); p.add_argument("--output", required=True)
+    p = sub.add_parser("bad-case-routes", aliases=["validate-probe-bad-case-routes"]); common(p)
+    p.add_argument("--data", required=True); p.add_argument("--probe-cache", required=True); p.add_argument("--probe-dir", required=True)
+    p.add_argument("--output", required=True); p.add_argument("--attributes"); p.add_argument("--batch-size", type=int, default=512)
+    p.add_argument("--max-examples", type=int); p.add_argument("--pair-limit", type=int, default=2000)
+    p.set_defaults(func=cmd_bad_case_routes)
+
+    p = sub.add_parser("summarize-probe-batch-benchmarks", aliases=["summarize-probe-benchmarks"]); p.add_argument("results", nargs="+"); p.add_argument("--output", required=True)
     p.set_defaults(func=cmd_summarize_probe_batch_benchmarks)
 
     p = sub.add_parser("compare-formal-studies"); p.add_argument("--single", required=True); p.add_argument("--multi", required=True)
     p.add_argument("--single-cache", required=True); p.add_argument("--multi-cache", required=True); p.add_argument("--output", required=True)
     p.set_defaults(func=cmd_compare_formal_studies)
 
-    p = sub.add_parser("diagnostic-report"); p.add_argument("--single", required=True); p.add_argument("--multi", required=True)
+    p = sub.add_parser("diagnostic-report", aliases=["report-probe-diagnostics"]); p.add_argument("--single", required=True); p.add_argument("--multi", required=True)
     p.add_argument("--output", required=True); p.set_defaults(func=cmd_diagnostic_report)
     return ap
 

@@ -252,3 +252,106 @@ def test_two_condition_audit_writes_lineage_and_notices_tampering(studies, tmp_p
         assert done.returncode == 1 and "shard_00000.bin differs" in done.stdout
     finally:
         shard.write_bytes(original)
+
+
+def test_pairwise_branching_separates_token_driven_routes():
+    """Synthetic cases: the route at t1 depends on t1 only, the route at t2 on t2 only.  Same-t2 pairs then overlap fully at both
+    positions, different-t2 pairs fully at t1 and not at all at t2: branching scores 0 and 1."""
+
+    from experiments.synbios_moe.mechanisms.token_routes import pairwise_branching
+
+    route_of = {7: [0, 1], 8: [2, 3], 9: [4, 5]}
+    cases = []
+    for n in range(12):
+        t2 = (7, 8, 9)[n % 3]
+        cases.append({"attribute": "university", "t1_id": 40, "t2_id": t2, "routes": [[[6, 7], [6, 7]], [route_of[t2], route_of[t2]]]})
+    rows = pairwise_branching(cases, layers=2, pair_limit=50, seed=3)
+    by = {(r["layer"], r["pair_group"]): r for r in rows}
+    assert set(by) == {(0, "same_t2"), (0, "different_t2"), (1, "same_t2"), (1, "different_t2")}
+    for layer in (0, 1):
+        assert by[(layer, "same_t2")]["branching_score"] == 0.0 and by[(layer, "same_t2")]["t2_route_overlap"] == 1.0
+        assert by[(layer, "different_t2")]["t1_route_overlap"] == 1.0 and by[(layer, "different_t2")]["branching_score"] == 1.0
+        assert by[(layer, "different_t2")]["pair_count"] == 50
+    # one t2 group only: nothing to contrast, and a single member gives no same-t2 pair either
+    assert pairwise_branching(cases[:1], layers=2) == []
+
+
+def test_routes_at_positions_match_a_full_capture():
+    from experiments.synbios_moe.mechanisms.routing import routes_for_batch
+    from experiments.synbios_moe.mechanisms.token_routes import routes_at_positions
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+
+    torch.manual_seed(1)
+    model = MiniTransformer(ModelConfig(**MODEL), get_ops_backend("torch"), activation_dtype=torch.float32).eval()
+    ids = torch.randint(0, 256, (3, 11))
+    pos = torch.tensor([[2, 3], [5, 6], [9, 10]])
+    got = routes_at_positions(model, ids, pos)
+    full = routes_for_batch(model, ids)
+    assert got.shape == (3, 2, MODEL["n_layers"], MODEL["experts_per_token"])
+    for b in range(3):
+        for j in range(2):
+            for layer in range(MODEL["n_layers"]):
+                assert got[b, j, layer].tolist() == full[layer][b, int(pos[b, j])].tolist()
+    dense = MiniTransformer(ModelConfig(**{**MODEL, "ffn_type": "dense"}), get_ops_backend("torch"), activation_dtype=torch.float32)
+    with pytest.raises(ValueError, match="routed experts"):
+        routes_at_positions(dense, ids, pos)
+
+
+def test_bad_case_routes_command_writes_the_protocol_files(studies):
+    s = studies["multi5_permute"]
+    out = studies["root"] / "bad_case_routes"
+    run("validate-probe-bad-case-routes", *studies["base"], "--data", str(s["data"]), "--probe-cache", str(s["cache"]),
+        "--probe-dir", str(s["probes"]), "--output", str(out), "--attributes", "university", "--batch-size", "5", "--pair-limit", "20")
+    summary = json.loads((out / "summary.json").read_text())
+    assert summary["protocol"] == "q_bad_case_t1_t2_route_branching_v1" and summary["parameters_updated"] is False
+    assert summary["experts"] == MODEL["num_experts"] and summary["top_k"] == 2
+    cases = (out / "bad_cases.csv").read_text().splitlines()
+    assert len(cases) == summary["examples"] + 1 == summary["attributes"]["university"] + 1
+    records = (out / "route_records.csv").read_text().splitlines()
+    assert len(records) - 1 == summary["examples"] * summary["layers"]
+    for name in ("pairwise_summary.csv", "token_nmi.csv"):
+        assert (out / name).is_file()
+
+
+def test_bad_case_route_validation_on_forced_bad_cases(tmp_path, monkeypatch):
+    """Predictions are injected (first token right, whole value wrong), so every record is a bad case: the routes recorded for it
+    are those of the frozen backbone at the two value-token positions of ``[EOS] name t1 t2 [EOS]``."""
+
+    from experiments.synbios_moe.codec import get_codec
+    from experiments.synbios_moe.mechanisms import q_readout, token_routes
+    from experiments.synbios_moe.mechanisms.routing import routes_for_batch
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+
+    codec = get_codec("bytes")
+    torch.manual_seed(2)
+    model = MiniTransformer(ModelConfig(**MODEL), get_ops_backend("torch"), activation_dtype=torch.float32).eval()
+    values = ["MIT", "MIT", "Ohio", "Yale", "M"]          # byte codec: t1 is the space, t2 the first letter
+    records = []
+    for n, value in enumerate(values):
+        name = codec.encode(f"Person {n}")
+        records.append(q_readout.QPrediction(
+            case_id=n, profile_index=n, person_id=f"p{n}", attribute="university", input_ids=(codec.eos, *name, codec.eos),
+            true_first_id=0, pred_first_id=0, true_first_token=str(codec.encode(" " + value)[0]), pred_first_token="x",
+            true_whole_id=1, pred_whole_id=2 if n != 3 else 1, true_whole_value=value, pred_whole_value="other",
+            whole_true_probability=0.1))
+    monkeypatch.setattr(q_readout, "collect_q_predictions", lambda *a, **k: (records, None))
+    summary = token_routes.bad_case_route_validation(model, codec, data_root=tmp_path, cache_root=tmp_path, probe_dir=tmp_path,
+                                                     output_dir=tmp_path / "out", attributes=("university",), batch_size=2, pair_limit=10)
+    assert summary["examples"] == 4 and summary["layers"] == MODEL["n_layers"]          # the correctly read "Yale" is not a bad case
+    import csv
+
+    cases = list(csv.DictReader(open(tmp_path / "out" / "bad_cases.csv")))
+    assert [c["true_whole_value"] for c in cases] == ["MIT", "MIT", "Ohio", "M"]
+    first = records[0]
+    t1, t2 = codec.encode(" MIT")[:2]
+    ids = torch.tensor([[*first.input_ids[:-1], t1, t2, codec.eos]])
+    full = routes_for_batch(model, ids)
+    at = len(first.input_ids) - 1
+    want_t1 = "|".join("+".join(str(e) for e in full[layer][0, at].tolist()) for layer in sorted(full))
+    want_t2 = "|".join("+".join(str(e) for e in full[layer][0, at + 1].tolist()) for layer in sorted(full))
+    assert cases[0]["t1_route_path"] == want_t1 and cases[0]["t2_route_path"] == want_t2
+    assert cases[0]["t1_id"] == str(t1) and cases[0]["t2_text"] == codec.decode([t2])
+    pairs = list(csv.DictReader(open(tmp_path / "out" / "pairwise_summary.csv")))
+    assert {p["pair_group"] for p in pairs} == {"same_t2", "different_t2"}                  # MIT / MIT / M share t2, Ohio does not
+    nmi = list(csv.DictReader(open(tmp_path / "out" / "token_nmi.csv")))
+    assert len(nmi) == MODEL["n_layers"] and all(0.0 <= float(r["t1_top1_token_nmi"]) <= 1.0 + 1e-9 for r in nmi)
