@@ -4,7 +4,7 @@ A study directory is a finished probe pipeline: ``pipeline.json`` plus ``trainin
 22 heads (11 tasks x {P, Q}).  The comparison is only meaningful when both studies probe the SAME people with the same
 hyper-parameters and differ in nothing but the augmentation of the pre-training corpus, so the loader and the matcher
 refuse anything else.  Outputs: a tidy table (one row per condition, task, split, position), the headline macro means
-with their multi-minus-single deltas, and a Markdown summary
+with their multi-minus-single deltas, a Markdown summary and the figures of ``probes/figures.py``
 (reference: experiments/synbios_moe/probes/comparison_report.py:59-310, 556-643).
 """
 
@@ -165,5 +165,9 @@ def build_formal_report_artifacts(single_root, multi_root, output_dir, *, single
     for key in head["single"]:
         lines.append(f"| {key} | {100 * head['single'][key]:.1f} | {100 * head['multi5_permute'][key]:.1f} | "
                      f"{100 * head['delta_multi_minus_single'][key]:+.1f} |")
+    from experiments.synbios_moe.probes.figures import write_probe_figures
+
+    figures = write_probe_figures(rows, head, out)
+    lines += ["", "Figures: " + ", ".join(f"`figures/{name}`" for name in figures if name.endswith(".svg"))]
     write_text(out / "report.md", "\n".join(lines) + "\n")
-    return {"rows": len(rows), "headline": head, "output": str(out.resolve())}
+    return {"rows": len(rows), "headline": head, "figures": figures, "output": str(out.resolve())}

@@ -189,6 +189,14 @@ def test_formal_comparison_requires_matched_complete_studies(studies, tmp_path):
     tidy = (out / "probe_metrics_tidy.csv").read_text().splitlines()
     # 2 conditions x (11 P heads x 6 + 11 Q heads x 1) positions x 2 splits (validation and train recall)
     assert len(tidy) - 1 == 2 * (11 * 6 + 11) * 2
+    # figures: labelled SVG grids (one value per attribute and position) with PNG twins, and the overview bars
+    figures = sorted(f.name for f in (out / "figures").iterdir())
+    assert figures == sorted(["overview.svg", "p_first_heatmaps.svg", "p_whole_heatmaps.svg", "q_first_table.svg", "q_whole_table.svg",
+                              "p_first_single.png", "p_first_multi5_permute.png", "p_whole_single.png", "p_whole_multi5_permute.png"])
+    svg = (out / "figures" / "p_first_heatmaps.svg").read_text()
+    assert svg.startswith("<svg") and svg.count("<rect") >= 2 * 36 and "birth date" in svg and ">P5<" in svg
+    assert (out / "figures" / "p_whole_single.png").read_bytes()[:8] == b"\x89PNG\r\n\x1a\n"
+    assert "figures/overview.svg" in (out / "report.md").read_text()
     # swapped conditions, different people and different hyper-parameters are all refused
     a = cr.load_formal_run("single", single, studies["single"]["cache"])
     b = cr.load_formal_run("multi5_permute", multi, studies["multi5_permute"]["cache"])
@@ -355,3 +363,22 @@ def test_bad_case_route_validation_on_forced_bad_cases(tmp_path, monkeypatch):
     assert {p["pair_group"] for p in pairs} == {"same_t2", "different_t2"}                  # MIT / MIT / M share t2, Ohio does not
     nmi = list(csv.DictReader(open(tmp_path / "out" / "token_nmi.csv")))
     assert len(nmi) == MODEL["n_layers"] and all(0.0 <= float(r["t1_top1_token_nmi"]) <= 1.0 + 1e-9 for r in nmi)
+
+
+def test_figure_grids_carry_values_labels_and_outlines():
+    from experiments.synbios_moe.probes import figures
+
+    frag, w, h = figures.grid_svg([[0.0, 0.5], [1.0, 0.123]], row_labels=["a", "b & c"], col_labels=["P0", "P1"], title="t <1>",
+                                  outlined=[(1, 0)])
+    assert ">0.0<" in frag and ">50.0<" in frag and ">100.0<" in frag and ">12.3<" in frag
+    assert "b &amp; c" in frag and "t &lt;1&gt;" in frag and frag.count("stroke-width='3'") == 1
+    assert w == 130 + 2 * 64 and h == 34 + 2 * 64 + 28
+    assert figures.accuracy_colour(-1.0) == figures.accuracy_colour(0.0) == (247, 251, 255)
+    assert figures.accuracy_colour(2.0) == figures.accuracy_colour(1.0) == (8, 88, 110)
+    with pytest.raises(ValueError):
+        figures.grid_svg([[0.1]], row_labels=["a", "b"], col_labels=["x"], title="")
+    png = figures.grid_png([[0.0, 1.0]], cell=4)
+    assert png[:8] == b"\x89PNG\r\n\x1a\n" and int.from_bytes(png[16:20], "big") == 8 and int.from_bytes(png[20:24], "big") == 4
+    head = {"single": {"a_b": 0.25, "c": 1.0}, "multi5_permute": {"a_b": 0.75, "c": 0.5}}
+    bars = figures.overview_svg(head)
+    assert bars.count("<rect") >= 1 + 4 + 2 and ">25.0<" in bars and ">75.0<" in bars
