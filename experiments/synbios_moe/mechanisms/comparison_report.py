@@ -1,9 +1,10 @@
 """Diagnostic evidence of two studies side by side: the oracle first-token intervention and the routing analyses.
 
 For each condition (``single``, ``multi5_permute``) a diagnostics directory holds ``oracle/summary.json`` (from the oracle
-first-token validation) and ``routes.json`` (from the router analysis).  The report checks that both sides ran the same
-protocol, tabulates the oracle outcome per attribute, and forms difference-in-differences of the route statistics per
-layer: how much more an attribute decides the expert under augmentation than without it
+first-token validation), ``routes.json`` (from the router analysis) and, optionally, ``bad_case_routes/`` (t1 / t2 route
+branching on the Q read-out's bad cases).  The report checks that both sides ran the same protocol, tabulates the oracle
+outcome per attribute, forms difference-in-differences of the route statistics per layer (how much more an attribute decides
+the expert under augmentation than without it) and reduces the branching tables to per-layer and headline figures
 (reference: experiments/synbios_moe/mechanisms/comparison_report.py:98-404, 755-844).
 """
 
@@ -11,8 +12,11 @@ from __future__ import annotations
 
 from pathlib import Path
 
+import csv
+
 from experiments.synbios_moe.artifact_io import read_json, write_csv, write_json, write_text
 from experiments.synbios_moe.mechanisms.oracle_first_token import PROTOCOL as ORACLE_PROTOCOL
+from experiments.synbios_moe.mechanisms.token_routes import ROUTE_PROTOCOL
 
 CONDITIONS = ("single", "multi5_permute")
 ORACLE_FIELDS = ("examples", "accuracy_before", "accuracy_after", "accuracy_delta", "recovery_rate", "harm_rate")
@@ -78,6 +82,91 @@ def route_rows(evidence: dict[str, dict]) -> list[dict]:
     return rows
 
 
+def _read_csv(path: Path) -> list[dict]:
+    with open(path, newline="") as fh:
+        return list(csv.DictReader(fh))
+
+
+def branching_evidence(summary: dict, pair_rows: list[dict], nmi_rows: list[dict]) -> tuple[list[dict], list[dict], dict]:
+    """Per-layer rows, per-(attribute, layer) rows and headline figures of one bad-case route run.
+
+    The tables must be complete for the topology and the attributes the summary names (every attribute x layer x pair group
+    with at least one pair), overlaps must lie in [0, 1] and every branching score must equal t1 overlap minus t2 overlap:
+    a truncated or edited run is refused instead of averaged.  ``difference_in_differences`` is the branching score of pairs
+    whose second token differs minus that of pairs whose second token agrees, pair-count weighted."""
+
+    if summary.get("protocol") != ROUTE_PROTOCOL or summary.get("parameters_updated") is not False:
+        raise ValueError(f"the route summary was not produced by protocol {ROUTE_PROTOCOL}")
+    counts = summary.get("attributes")
+    if not isinstance(counts, dict) or sum(int(v) for v in counts.values()) != int(summary["examples"]):
+        raise ValueError("route bad-case counts do not close")
+    layers, attributes = int(summary["layers"]), [a for a, n in counts.items() if int(n) > 0]
+    groups = ("same_t2", "different_t2")
+    pairs = {(r["attribute"], int(r["layer"]), r["pair_group"]): r for r in pair_rows}
+    expected = {(a, layer, g) for a in attributes for layer in range(layers) for g in groups}
+    if len(pairs) != len(pair_rows) or not expected <= set(pairs):
+        missing = sorted(expected - set(pairs))[:3]
+        raise ValueError(f"the pairwise table is not complete for {len(attributes)} attributes x {layers} layers x 2 groups (first gaps: {missing})")
+    for r in pair_rows:
+        if int(r["pair_count"]) <= 0:
+            raise ValueError("the pairwise table contains an empty group")
+        t1, t2 = float(r["t1_route_overlap"]), float(r["t2_route_overlap"])
+        if not (0.0 <= t1 <= 1.0 and 0.0 <= t2 <= 1.0):
+            raise ValueError(f"route overlap outside [0, 1]: {r}")
+        _assert_close(float(r["branching_score"]), t1 - t2, "route branching score", 1e-9)
+    nmi = {(r["attribute"], int(r["layer"])): r for r in nmi_rows}
+    if not {(a, layer) for a in attributes for layer in range(layers)} <= set(nmi):
+        raise ValueError("the token NMI table does not cover every attribute and layer")
+    for r in nmi_rows:
+        for field in ("t1_top1_token_nmi", "t2_top1_token_nmi"):
+            if not -1e-9 <= float(r[field]) <= 1.0 + 1e-9:
+                raise ValueError(f"route NMI outside [0, 1]: {r}")
+
+    def weighted(rows: list[dict], field: str) -> float:
+        total = sum(int(r["pair_count"]) for r in rows)
+        return sum(float(r[field]) * int(r["pair_count"]) for r in rows) / total
+
+    detail = []
+    for a in attributes:
+        for layer in range(layers):
+            same, diff = pairs[(a, layer, "same_t2")], pairs[(a, layer, "different_t2")]
+            detail.append({"attribute": a, "layer": layer, "same_t2_branching_score": float(same["branching_score"]),
+                           "different_t2_branching_score": float(diff["branching_score"]),
+                           "difference_in_differences": float(diff["branching_score"]) - float(same["branching_score"]),
+                           "same_t2_pair_count": int(same["pair_count"]), "different_t2_pair_count": int(diff["pair_count"]),
+                           "t1_top1_token_nmi": float(nmi[(a, layer)]["t1_top1_token_nmi"]),
+                           "t2_top1_token_nmi": float(nmi[(a, layer)]["t2_top1_token_nmi"])})
+    by_layer = []
+    for layer in range(layers):
+        row: dict = {"layer": layer}
+        for g in groups:
+            chosen = [pairs[(a, layer, g)] for a in attributes]
+            row[f"{g}_pair_count"] = sum(int(r["pair_count"]) for r in chosen)
+            for field in ("t1_route_overlap", "t2_route_overlap", "branching_score"):
+                row[f"{g}_{field}"] = weighted(chosen, field)
+        row["difference_in_differences"] = row["different_t2_branching_score"] - row["same_t2_branching_score"]
+        by_layer.append(row)
+    overall = {g: {"pair_count": sum(int(r["pair_count"]) for r in pair_rows if r["pair_group"] == g),
+                   **{f: weighted([r for r in pair_rows if r["pair_group"] == g], f)
+                      for f in ("t1_route_overlap", "t2_route_overlap", "branching_score")}} for g in groups} if attributes else {}
+    headline = {"bad_case_examples": int(summary["examples"]), "groups": overall,
+                "difference_in_differences": (overall["different_t2"]["branching_score"] - overall["same_t2"]["branching_score"]) if overall else None,
+                "all_layers_positive": bool(by_layer) and all(r["difference_in_differences"] > 0 for r in by_layer),
+                "max_t1_nmi_by_attribute": {a: max(float(nmi[(a, layer)]["t1_top1_token_nmi"]) for layer in range(layers)) for a in attributes},
+                "max_t2_nmi_by_attribute": {a: max(float(nmi[(a, layer)]["t2_top1_token_nmi"]) for layer in range(layers)) for a in attributes}}
+    return by_layer, detail, headline
+
+
+def load_branching_evidence(root: str | Path) -> tuple[list[dict], list[dict], dict] | None:
+    """``<root>/bad_case_routes`` reduced by ``branching_evidence``; ``None`` when the diagnostic was not run."""
+
+    folder = Path(root) / "bad_case_routes"
+    if not (folder / "summary.json").is_file():
+        return None
+    return branching_evidence(read_json(folder / "summary.json"), _read_csv(folder / "pairwise_branching.csv"),
+                              _read_csv(folder / "token_route_nmi.csv"))
+
+
 def build_diagnostic_report_artifacts(roots: dict[str, str | Path], output_dir: str | Path) -> dict:
     evidence = load_diagnostic_evidence(roots)
     o_rows, r_rows = oracle_rows(evidence), route_rows(evidence)
@@ -90,6 +179,16 @@ def build_diagnostic_report_artifacts(roots: dict[str, str | Path], output_dir: 
     summary = {"protocol": "synbios_diagnostic_report_v1", "oracle_overall": overall,
                "oracle_recovery_delta": overall["multi5_permute"]["recovery_rate"] - overall["single"]["recovery_rate"],
                "route_layers": len(r_rows)}
+    branching = {}
+    for condition in CONDITIONS:
+        reduced = load_branching_evidence(roots[condition])
+        if reduced is not None:
+            by_layer, detail, headline = reduced
+            write_csv(out / f"route_branching_by_layer_{condition}.csv", by_layer)
+            write_csv(out / f"route_branching_by_attribute_layer_{condition}.csv", detail)
+            branching[condition] = headline
+    if branching:
+        summary["route_branching"] = branching
     write_json(out / "summary.json", summary)
     lines = ["# Diagnostics: oracle first token and routing", "", "| condition | accuracy before % | after % | recovered errors % | harmed % |",
              "|---|---:|---:|---:|---:|"]

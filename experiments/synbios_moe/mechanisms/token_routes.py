@@ -176,7 +176,7 @@ def _label_nmi(experts: list[int], labels: list[int], num_experts: int) -> float
 def bad_case_route_validation(backbone, codec, *, data_root, cache_root, probe_dir, output_dir, device="cpu",
                               attributes=None, batch_size: int = 512, max_examples: int | None = None, pair_limit: int = 2000,
                               progress=None) -> dict:
-    """Writes ``bad_cases.csv``, ``route_records.csv``, ``pairwise_summary.csv``, ``token_nmi.csv`` and ``summary.json``."""
+    """Writes ``bad_cases.csv``, ``route_records.csv``, ``pairwise_branching.csv``, ``token_route_nmi.csv`` and ``summary.json``."""
 
     from pathlib import Path
 
@@ -255,7 +255,7 @@ def bad_case_route_validation(backbone, codec, *, data_root, cache_root, probe_d
                "experts": int(cfg.num_experts), "top_k": top_k}
     write_csv(out / "bad_cases.csv", case_rows)
     write_csv(out / "route_records.csv", route_rows)
-    write_csv(out / "pairwise_summary.csv", pair_rows)
-    write_csv(out / "token_nmi.csv", nmi_rows)
+    write_csv(out / "pairwise_branching.csv", pair_rows)
+    write_csv(out / "token_route_nmi.csv", nmi_rows)
     write_json(out / "summary.json", summary)
     return summary

@@ -317,7 +317,7 @@ def test_bad_case_routes_command_writes_the_protocol_files(studies):
     assert len(cases) == summary["examples"] + 1 == summary["attributes"]["university"] + 1
     records = (out / "route_records.csv").read_text().splitlines()
     assert len(records) - 1 == summary["examples"] * summary["layers"]
-    for name in ("pairwise_summary.csv", "token_nmi.csv"):
+    for name in ("pairwise_branching.csv", "token_route_nmi.csv"):
         assert (out / name).is_file()
 
 
@@ -359,9 +359,9 @@ def test_bad_case_route_validation_on_forced_bad_cases(tmp_path, monkeypatch):
     want_t2 = "|".join("+".join(str(e) for e in full[layer][0, at + 1].tolist()) for layer in sorted(full))
     assert cases[0]["t1_route_path"] == want_t1 and cases[0]["t2_route_path"] == want_t2
     assert cases[0]["t1_id"] == str(t1) and cases[0]["t2_text"] == codec.decode([t2])
-    pairs = list(csv.DictReader(open(tmp_path / "out" / "pairwise_summary.csv")))
+    pairs = list(csv.DictReader(open(tmp_path / "out" / "pairwise_branching.csv")))
     assert {p["pair_group"] for p in pairs} == {"same_t2", "different_t2"}                  # MIT / MIT / M share t2, Ohio does not
-    nmi = list(csv.DictReader(open(tmp_path / "out" / "token_nmi.csv")))
+    nmi = list(csv.DictReader(open(tmp_path / "out" / "token_route_nmi.csv")))
     assert len(nmi) == MODEL["n_layers"] and all(0.0 <= float(r["t1_top1_token_nmi"]) <= 1.0 + 1e-9 for r in nmi)
 
 
@@ -382,3 +382,35 @@ def test_figure_grids_carry_values_labels_and_outlines():
     head = {"single": {"a_b": 0.25, "c": 1.0}, "multi5_permute": {"a_b": 0.75, "c": 0.5}}
     bars = figures.overview_svg(head)
     assert bars.count("<rect") >= 1 + 4 + 2 and ">25.0<" in bars and ">75.0<" in bars
+
+
+def test_branching_evidence_reduces_complete_tables_and_refuses_broken_ones():
+    from experiments.synbios_moe.mechanisms.comparison_report import branching_evidence
+    from experiments.synbios_moe.mechanisms.token_routes import ROUTE_PROTOCOL
+
+    summary = {"protocol": ROUTE_PROTOCOL, "parameters_updated": False, "examples": 30, "attributes": {"university": 10, "major": 20, "company": 0},
+               "layers": 2, "experts": 4, "top_k": 2}
+    pair_rows, nmi_rows = [], []
+    for a, n in (("university", 10), ("major", 30)):
+        for layer in (0, 1):
+            pair_rows.append({"attribute": a, "layer": str(layer), "pair_group": "same_t2", "pair_count": str(n), "t1_route_overlap": "0.9",
+                              "t2_route_overlap": "0.8", "branching_score": "0.1"})
+            pair_rows.append({"attribute": a, "layer": str(layer), "pair_group": "different_t2", "pair_count": str(2 * n), "t1_route_overlap": "0.9",
+                              "t2_route_overlap": str(0.5 - 0.1 * layer), "branching_score": str(0.4 + 0.1 * layer)})
+            nmi_rows.append({"attribute": a, "layer": str(layer), "examples": "5", "t1_top1_token_nmi": str(0.2 + 0.1 * layer), "t2_top1_token_nmi": "0.5"})
+    by_layer, detail, head = branching_evidence(summary, pair_rows, nmi_rows)
+    assert [r["layer"] for r in by_layer] == [0, 1] and len(detail) == 4
+    assert by_layer[0]["same_t2_pair_count"] == 40 and by_layer[0]["different_t2_pair_count"] == 80
+    assert by_layer[0]["difference_in_differences"] == pytest.approx(0.3) and by_layer[1]["difference_in_differences"] == pytest.approx(0.4)
+    assert head["difference_in_differences"] == pytest.approx(0.35) and head["all_layers_positive"] and head["bad_case_examples"] == 30
+    assert head["max_t1_nmi_by_attribute"] == {"university": pytest.approx(0.3), "major": pytest.approx(0.3)}
+    with pytest.raises(ValueError, match="not complete"):
+        branching_evidence(summary, pair_rows[:-1], nmi_rows)
+    broken = [dict(r) for r in pair_rows]
+    broken[0]["branching_score"] = "0.3"
+    with pytest.raises(ValueError, match="branching score"):
+        branching_evidence(summary, broken, nmi_rows)
+    with pytest.raises(ValueError, match="do not close"):
+        branching_evidence({**summary, "examples": 31}, pair_rows, nmi_rows)
+    with pytest.raises(ValueError, match="protocol"):
+        branching_evidence({**summary, "protocol": "other"}, pair_rows, nmi_rows)
