@@ -114,9 +114,17 @@ def benchmark_probe_batches(backbone, dataset, *, kind: str, num_classes: int, r
             "recommendation_scope": f"{mode}_capacity_profile", "results": results}
 
 
+_IDENTITY_KEYS = ("attribute", "target", "rank", "checkpoint", "probe_cache", "ground_truth_first")
+
+
 def summarize_probe_benchmarks(paths: Sequence[str | Path]) -> dict:
     """Merge runs (e.g. one per GPU): per (kind, mode) keep batch sizes measured and safe in EVERY run, pick the one with the
-    best worst-case throughput."""
+    best worst-case throughput.
+
+    Replicas of one (kind, mode) must have measured the same candidates under the same memory limit on the same task,
+    otherwise their intersection would silently mean something else.  ``completeness`` says whether the result may be used
+    for a formal run: all four (kind, mode) cells measured, each at least twice, each with a recommendation that is not the
+    largest candidate tried (a recommendation at the edge of the search says the search stopped too early)."""
 
     payloads = [json.loads(Path(p).read_text(encoding="utf-8")) for p in paths]
     if not payloads:
@@ -124,13 +132,21 @@ def summarize_probe_benchmarks(paths: Sequence[str | Path]) -> dict:
     groups: dict[tuple[str, str], list[dict]] = {}
     for payload in payloads:
         for run in payload.get("benchmarks", [payload]):
-            groups.setdefault((run["kind"], run["mode"]), []).append(run)
+            groups.setdefault((run["kind"], run["mode"]), []).append({**{k: payload[k] for k in _IDENTITY_KEYS if k in payload}, **run})
     summary: dict = {"runs": [str(Path(p).resolve()) for p in paths], "recommendations": {}}
     for (kind, mode), runs in sorted(groups.items()):
-        limit = min(float(r["memory_limit_percent"]) for r in runs)
-        common = set.intersection(*[{int(x["batch_size"]) for x in r["results"]} for r in runs])
+        candidates = [tuple(sorted(int(x["batch_size"]) for x in r["results"])) for r in runs]
+        if any(c != candidates[0] for c in candidates[1:]):
+            raise ValueError(f"{kind}/{mode}: benchmark replicas used different batch-size candidates")
+        if len({float(r["memory_limit_percent"]) for r in runs}) != 1:
+            raise ValueError(f"{kind}/{mode}: benchmark replicas used different memory limits")
+        for key in _IDENTITY_KEYS:
+            seen = {json.dumps(r.get(key)) for r in runs if key in r}
+            if len(seen) > 1 or (seen and any(key not in r for r in runs)):
+                raise ValueError(f"{kind}/{mode}: benchmark replicas disagree on {key}")
+        limit = float(runs[0]["memory_limit_percent"])
         rows = []
-        for size in sorted(common):
+        for size in candidates[0]:
             cells = [next(x for x in r["results"] if int(x["batch_size"]) == size) for r in runs]
             ok = all(c["status"] == "completed" and float(c.get("peak_memory_percent", 0.0)) <= limit for c in cells)
             rows.append({"batch_size": size, "safe_everywhere": ok,
@@ -138,6 +154,29 @@ def summarize_probe_benchmarks(paths: Sequence[str | Path]) -> dict:
                          "max_peak_memory_percent": max(float(c.get("peak_memory_percent", 0.0)) for c in cells)})
         safe = [r for r in rows if r["safe_everywhere"]]
         best = max(safe, key=lambda r: r["min_examples_per_second"]) if safe else None
-        summary["recommendations"][f"{kind}_{mode}"] = {"replicas": len(runs), "memory_limit_percent": limit, "candidates": rows,
-                                                        "recommended_batch_size": best["batch_size"] if best else None}
+        summary["recommendations"][f"{kind}_{mode}"] = {
+            "replicas": len(runs), "memory_limit_percent": limit, "candidates": rows,
+            "largest_tested_batch_size": max(candidates[0]) if candidates[0] else None,
+            "recommended_batch_size": best["batch_size"] if best else None,
+            "recommended_is_search_boundary": bool(best and candidates[0] and best["batch_size"] == max(candidates[0]))}
+    cells = [f"{kind}_{mode}" for kind in ("p", "q") for mode in ("training", "validation")]
+    rec = summary["recommendations"]
+    completeness = {"missing": [c for c in cells if c not in rec],
+                    "single_replica": [c for c in cells if c in rec and rec[c]["replicas"] < 2],
+                    "no_recommendation": [c for c in cells if c in rec and rec[c]["recommended_batch_size"] is None],
+                    "at_search_boundary": [c for c in cells if c in rec and rec[c]["recommended_is_search_boundary"]]}
+    completeness["ready_for_formal"] = not any(completeness.values())
+    summary["completeness"] = completeness
     return summary
+
+
+def probe_batch_environment(summary: dict) -> str:
+    """Shell lines (``export P_BATCH_SIZE=...``) a launcher can source; only for a complete, bracketed benchmark
+    (reference: experiments/synbios_moe/probes/batch_benchmark.py:361-373)."""
+
+    if not summary.get("completeness", {}).get("ready_for_formal"):
+        raise ValueError("the probe batch benchmark is not complete enough for formal use: " + json.dumps(summary.get("completeness")))
+    rec = summary["recommendations"]
+    values = {"P_BATCH_SIZE": rec["p_training"], "Q_BATCH_SIZE": rec["q_training"], "P_VALIDATION_BATCH_SIZE": rec["p_validation"],
+              "Q_VALIDATION_BATCH_SIZE": rec["q_validation"]}
+    return "".join(f"export {name}={int(cell['recommended_batch_size'])}\n" for name, cell in values.items())

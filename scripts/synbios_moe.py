@@ -450,9 +450,18 @@ def cmd_summarize_probe_batch_benchmarks(args) -> int:
     from experiments.synbios_moe.artifact_io import write_json
     from experiments.synbios_moe.probes.batch_benchmark import summarize_probe_benchmarks
 
-    summary = summarize_probe_benchmarks(args.results)
+    summary = summarize_probe_benchmarks([*args.results, *(args.run or [])])
     write_json(args.output, summary)
-    print(json.dumps({k: v["recommended_batch_size"] for k, v in summary["recommendations"].items()}))
+    print(json.dumps({**{k: v["recommended_batch_size"] for k, v in summary["recommendations"].items()},
+                      "ready_for_formal": summary["completeness"]["ready_for_formal"]}))
+    if args.env_output:
+        from experiments.synbios_moe.artifact_io import write_text
+        from experiments.synbios_moe.probes.batch_benchmark import probe_batch_environment
+
+        write_text(args.env_output, probe_batch_environment(summary))          # raises unless the benchmark is complete
+    if args.require_complete_search and not summary["completeness"]["ready_for_formal"]:
+        print(json.dumps({"error": "benchmark incomplete", **summary["completeness"]}), file=sys.stderr)
+        return 2
     return 0
 
 
@@ -586,7 +595,10 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-examples", type=int); p.add_argument("--pair-limit", type=int, default=2000)
     p.set_defaults(func=cmd_bad_case_routes)
 
-    p = sub.add_parser("summarize-probe-batch-benchmarks", aliases=["summarize-probe-benchmarks"]); p.add_argument("results", nargs="+"); p.add_argument("--output", required=True)
+    p = sub.add_parser("summarize-probe-batch-benchmarks", aliases=["summarize-probe-benchmarks"]); p.add_argument("results", nargs="*")
+    p.add_argument("--run", action="append", help="a benchmark result (repeatable; same as a positional argument)")
+    p.add_argument("--output", required=True); p.add_argument("--env-output", help="write sourceable export lines of the recommended batch sizes")
+    p.add_argument("--require-complete-search", action="store_true", help="exit 2 unless every kind / mode was measured twice and bracketed")
     p.set_defaults(func=cmd_summarize_probe_batch_benchmarks)
 
     p = sub.add_parser("compare-formal-studies"); p.add_argument("--single", required=True); p.add_argument("--multi", required=True)

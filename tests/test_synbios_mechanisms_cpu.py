@@ -150,7 +150,50 @@ def test_probe_batch_benchmark_and_merge(studies, tmp_path):
     run("summarize-probe-batch-benchmarks", str(a), str(b), "--output", str(tmp_path / "merged.json"))
     merged = json.loads((tmp_path / "merged.json").read_text())
     assert merged["recommendations"]["p_training"]["replicas"] == 2 and merged["recommendations"]["q_training"]["recommended_batch_size"] in (2, 4)
-    from experiments.synbios_moe.probes.batch_benchmark import parse_batch_sizes
+    # validation cells were not measured, so the merge is not ready for a formal run and no environment file is written
+    assert merged["completeness"]["missing"] == ["p_validation", "q_validation"] and not merged["completeness"]["ready_for_formal"]
+    from experiments.synbios_moe.probes.batch_benchmark import parse_batch_sizes, probe_batch_environment, summarize_probe_benchmarks
+
+    with pytest.raises(ValueError, match="not complete"):
+        probe_batch_environment(merged)
+
+    def result(kind, mode, speeds, limit=92.0, **identity):
+        return {"kind": kind, "mode": mode, "memory_limit_percent": limit, **identity,
+                "results": [{"batch_size": b, "status": "completed", "examples_per_second": v, "peak_memory_percent": 10.0 * n}
+                            for n, (b, v) in enumerate(speeds.items(), start=1)]}
+
+    paths = []
+    for replica in range(2):
+        for kind in ("p", "q"):
+            for mode in ("training", "validation"):
+                path = tmp_path / f"{kind}-{mode}-{replica}.json"
+                path.write_text(json.dumps(result(kind, mode, {8: 100.0, 16: 180.0 + replica, 32: 150.0}, attribute="university")))
+                paths.append(path)
+    full = summarize_probe_benchmarks(paths)
+    assert full["completeness"]["ready_for_formal"] and full["recommendations"]["q_validation"]["recommended_batch_size"] == 16
+    assert probe_batch_environment(full) == ("export P_BATCH_SIZE=16\nexport Q_BATCH_SIZE=16\nexport P_VALIDATION_BATCH_SIZE=16\n"
+                                             "export Q_VALIDATION_BATCH_SIZE=16\n")
+    # the best candidate at the edge of the search, replicas that tried different candidates, limits or tasks: all flagged or refused
+    edge = tmp_path / "edge.json"
+    edge.write_text(json.dumps(result("p", "training", {8: 100.0, 16: 180.0, 32: 250.0}, attribute="university")))
+    assert summarize_probe_benchmarks([edge])["completeness"]["at_search_boundary"] == ["p_training"]
+    other = tmp_path / "other.json"
+    other.write_text(json.dumps(result("p", "training", {8: 100.0, 16: 180.0}, attribute="university")))
+    with pytest.raises(ValueError, match="different batch-size candidates"):
+        summarize_probe_benchmarks([paths[0], other])
+    other.write_text(json.dumps(result("p", "training", {8: 100.0, 16: 180.0, 32: 150.0}, limit=80.0, attribute="university")))
+    with pytest.raises(ValueError, match="memory limits"):
+        summarize_probe_benchmarks([paths[0], other])
+    other.write_text(json.dumps(result("p", "training", {8: 100.0, 16: 180.0, 32: 150.0}, attribute="major")))
+    with pytest.raises(ValueError, match="disagree on attribute"):
+        summarize_probe_benchmarks([paths[0], other])
+    env = tmp_path / "batch.env"
+    run("summarize-probe-benchmarks", *[a for p_ in paths for a in ("--run", str(p_))], "--output", str(tmp_path / "m2.json"),
+        "--env-output", str(env), "--require-complete-search")
+    assert env.read_text().startswith("export P_BATCH_SIZE=16")
+    done = subprocess.run([*CLI, "summarize-probe-benchmarks", str(a), str(b), "--output", str(tmp_path / "m3.json"), "--require-complete-search"],
+                          capture_output=True, text=True)
+    assert done.returncode == 2 and "benchmark incomplete" in done.stderr
 
     assert parse_batch_sizes("8, 2,8,4") == (2, 4, 8)
     with pytest.raises(ValueError):
