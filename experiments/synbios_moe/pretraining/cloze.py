@@ -100,3 +100,179 @@ def summarize_cloze(reports: dict[str, dict]) -> list[dict]:
             rows.append({"run": run, "attribute": attribute, **stats})
         rows.append({"run": run, "attribute": "overall", "exact_match": report["overall_exact_match"], "items": report["items"]})
     return rows
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Progressive cloze over the original biography
+#
+# All six holes of a biography are filled from left to right in one growing sequence: what the model generated for an
+# earlier fact stays in the context of the later ones, so mistakes propagate exactly as they would in free generation;
+# only the text between the facts comes from the source.  A value is generated greedily until the decoded continuation
+# contains the source text that follows the value up to and including the next full stop (or ``max_new_tokens`` ran out);
+# the prediction is what precedes that stop text (reference: experiments/synbios_moe/pretraining/cloze.py:36-392).
+# ---------------------------------------------------------------------------------------------------------------------
+PROGRESSIVE_PROTOCOL = "progressive_original_biography_cloze_greedy"
+FUZZY_THRESHOLDS = (0.5, 0.8, 0.9)
+
+
+def character_similarity(predicted: str, expected: str) -> float:
+    """1 - Levenshtein distance / longer length, on case-folded text with runs of white space collapsed."""
+
+    a, b = " ".join(predicted.casefold().split()), " ".join(expected.casefold().split())
+    if not a and not b:
+        return 1.0
+    row = list(range(len(b) + 1))
+    for i, ca in enumerate(a, start=1):
+        nxt = [i]
+        for j, cb in enumerate(b, start=1):
+            nxt.append(min(nxt[-1] + 1, row[j] + 1, row[j - 1] + (ca != cb)))
+        row = nxt
+    return 1.0 - row[-1] / max(len(a), len(b), 1)
+
+
+def biography_fields(codec, row: dict) -> tuple[list[int], list[dict]]:
+    """Token ids of ``[EOS] + text`` and the six value spans ``{attribute, lo, hi, expected}`` in textual order."""
+
+    text = str(row["text"])
+    ids, fields = None, []
+    for attribute in ATTRIBUTES:
+        start, end = (int(v) for v in row["attribute_spans"][attribute])
+        ids, lo, hi = token_span_of_chars(codec, text, start, end)
+        fields.append({"attribute": attribute, "lo": lo, "hi": hi, "expected": text[start:end]})
+    fields.sort(key=lambda f: f["lo"])
+    if any(f["lo"] >= f["hi"] for f in fields) or any(a["hi"] > b["lo"] for a, b in zip(fields, fields[1:])):
+        raise ValueError(f"biography of {row.get('person_id')}: empty or overlapping value spans")
+    return ids, fields
+
+
+@torch.no_grad()
+def generate_until(model, codec, prefixes: list[list[int]], stop_texts: list[str], *, device, max_new_tokens: int):
+    """Greedy continuation of every prefix until its stop text shows up in the decoded continuation.
+
+    Returns (generated token lists, terminated flags, model tokens processed).  Rows that are done leave the batch."""
+
+    limit = getattr(getattr(model, "cfg", None), "seq_len", 1 << 30)
+    seqs = [list(p) for p in prefixes]
+    made: list[list[int]] = [[] for _ in prefixes]
+    done = [False] * len(prefixes)
+    live = list(range(len(prefixes)))
+    processed = 0
+    for _ in range(max_new_tokens):
+        if not live:
+            break
+        width = max(len(seqs[i]) for i in live)
+        if width > limit:
+            raise ValueError(f"cloze prompt of {width} tokens exceeds seq_len={limit}")
+        batch = torch.full((len(live), width), codec.eos, dtype=torch.long, device=device)
+        ends = torch.empty(len(live), dtype=torch.long, device=device)
+        for r, i in enumerate(live):
+            batch[r, :len(seqs[i])] = torch.tensor(seqs[i], device=device)
+            ends[r] = len(seqs[i])
+        hidden = model.hidden_states(batch)
+        hidden = hidden[0] if isinstance(hidden, tuple) else hidden
+        nxt = model.lm_head(hidden[torch.arange(len(live), device=device), ends - 1]).argmax(-1).tolist()
+        processed += batch.numel()
+        still = []
+        for i, tok in zip(live, nxt):
+            seqs[i].append(int(tok))
+            made[i].append(int(tok))
+            if stop_texts[i] in codec.decode(made[i]):
+                done[i] = True
+            else:
+                still.append(i)
+        live = still
+    return made, done, processed
+
+
+def evaluate_progressive_cloze(model, codec, biographies: Iterable[dict], *, device="cpu", max_biographies: int, start_index: int = 0,
+                               batch_size: int = 16, max_new_tokens: int = 16, sample_biographies: int = 12) -> dict:
+    import time
+
+    if start_index < 0 or max_biographies <= 0 or batch_size <= 0 or max_new_tokens <= 0:
+        raise ValueError("start_index must be >= 0; max_biographies, batch_size and max_new_tokens must be positive")
+    model.eval()
+    hits = {a: 0 for a in ATTRIBUTES}
+    seen = {a: 0 for a in ATTRIBUTES}
+    similarity = {a: 0.0 for a in ATTRIBUTES}
+    fuzzy = {t: {a: 0 for a in ATTRIBUTES} for t in FUZZY_THRESHOLDS}
+    histogram = {n: 0 for n in range(len(ATTRIBUTES) + 1)}
+    counters = {"biographies": 0, "all_exact": 0, "unterminated": 0, "tokens": 0}
+    samples: list[dict] = []
+    t0 = time.perf_counter()
+
+    def run_batch(rows: list[dict]) -> None:
+        states = []
+        for row in rows:
+            ids, fields = biography_fields(codec, row)
+            states.append({"row": row, "ids": ids, "fields": fields, "cursor": 1, "seq": [codec.eos], "pred": {}, "ok": {}, "sim": {}})
+        for k in range(len(ATTRIBUTES)):
+            prefixes, stops = [], []
+            for st in states:
+                f = st["fields"][k]
+                st["seq"] += st["ids"][st["cursor"]:f["lo"]]
+                prefixes.append(st["seq"])
+                stops.append(codec.decode(st["ids"][f["hi"]:]).split(".", 1)[0] + ".")
+            made, done, processed = generate_until(model, codec, prefixes, stops, device=device, max_new_tokens=max_new_tokens)
+            counters["tokens"] += processed
+            for st, tokens, ended, stop in zip(states, made, done, stops):
+                f = st["fields"][k]
+                a = f["attribute"]
+                guess = codec.decode(tokens).split(stop, 1)[0].strip()
+                sim = character_similarity(guess, f["expected"])
+                seen[a] += 1
+                hits[a] += int(guess == f["expected"])
+                similarity[a] += sim
+                for t in FUZZY_THRESHOLDS:
+                    fuzzy[t][a] += int(sim >= t)
+                counters["unterminated"] += int(not ended)
+                st["pred"][a], st["ok"][a], st["sim"][a] = guess, guess == f["expected"], sim
+                st["seq"] += tokens
+                st["cursor"] = f["hi"]
+                if ended:       # the generation already wrote the sentence's full stop: skip the source tokens up to and including it
+                    skipped = ""
+                    while st["cursor"] < len(st["ids"]) and "." not in skipped:
+                        skipped += codec.decode([st["ids"][st["cursor"]]])
+                        st["cursor"] += 1
+        for st in states:
+            st["seq"] += st["ids"][st["cursor"]:]
+            exact = sum(bool(v) for v in st["ok"].values())
+            histogram[exact] += 1
+            counters["all_exact"] += int(exact == len(ATTRIBUTES))
+            counters["biographies"] += 1
+            if len(samples) < sample_biographies:
+                samples.append({"person_id": st["row"]["person_id"], "original_text": st["row"]["text"], "filled_text": codec.decode(st["seq"][1:]),
+                                "expected": {f["attribute"]: f["expected"] for f in st["fields"]}, "predicted": st["pred"],
+                                "correct": st["ok"], "character_similarity": st["sim"], "exact_fields": exact})
+
+    pending: list[dict] = []
+    for n, row in enumerate(biographies):
+        if n < start_index:
+            continue
+        if n >= start_index + max_biographies:
+            break
+        pending.append(row)
+        if len(pending) == batch_size:
+            run_batch(pending)
+            pending = []
+    if pending:
+        run_batch(pending)
+    n_bio, total = counters["biographies"], max(sum(seen.values()), 1)
+    elapsed = time.perf_counter() - t0
+    per_attribute = {a: {"items": seen[a], "exact_match": hits[a] / max(seen[a], 1),
+                         "mean_character_similarity": similarity[a] / max(seen[a], 1)} for a in ATTRIBUTES}
+    return {"protocol": PROGRESSIVE_PROTOCOL,
+            "protocol_note": "six holes per original biography filled left to right; generated earlier facts stay in the context",
+            "start_index": start_index, "biographies": n_bio, "fields": n_bio * len(ATTRIBUTES),
+            "attribute_accuracy": {a: hits[a] / max(seen[a], 1) for a in ATTRIBUTES},
+            "attribute_mean_character_similarity": {a: similarity[a] / max(seen[a], 1) for a in ATTRIBUTES},
+            "mean_character_similarity": sum(similarity.values()) / total,
+            "fuzzy_accuracy_by_threshold": {str(t): {a: fuzzy[t][a] / max(seen[a], 1) for a in ATTRIBUTES} for t in FUZZY_THRESHOLDS},
+            "micro_fuzzy_accuracy_by_threshold": {str(t): sum(fuzzy[t].values()) / total for t in FUZZY_THRESHOLDS},
+            "micro_field_accuracy": sum(hits.values()) / total, "biography_all_fields_accuracy": counters["all_exact"] / max(n_bio, 1),
+            "mean_correct_fields_per_biography": sum(k * v for k, v in histogram.items()) / max(n_bio, 1),
+            "biography_correct_field_count_histogram": {str(k): v for k, v in histogram.items()},
+            "correct_fields": hits, "total_fields": seen, "unterminated_fields": counters["unterminated"],
+            "elapsed_seconds": elapsed, "biographies_per_second": n_bio / max(elapsed, 1e-9), "model_tokens_processed": counters["tokens"],
+            # the keys the table builder and the probe pipeline's gate read, so that either protocol can feed them
+            "per_attribute": per_attribute, "overall_exact_match": sum(hits.values()) / total, "items": sum(seen.values()),
+            "samples": samples}

@@ -168,8 +168,16 @@ def cmd_cloze(args) -> int:
 
     codec = _codec(args)
     model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
-    report = evaluate_cloze(model, codec, read_jsonl(Path(args.data) / "biographies.jsonl"), device=args.device,
-                            batch_size=args.batch_size, max_items=args.max_items)
+    rows = read_jsonl(Path(args.data) / "biographies.jsonl")
+    if getattr(args, "protocol", "independent") == "progressive":
+        from experiments.synbios_moe.pretraining.cloze import evaluate_progressive_cloze
+
+        report = evaluate_progressive_cloze(model, codec, rows, device=args.device, batch_size=args.batch_size,
+                                            max_biographies=args.examples if args.max_items is None else args.max_items,
+                                            start_index=args.start_index, max_new_tokens=args.max_new_tokens,
+                                            sample_biographies=args.sample_biographies)
+    else:
+        report = evaluate_cloze(model, codec, rows, device=args.device, batch_size=args.batch_size, max_items=args.max_items)
     write_json(args.output, report)
     print(json.dumps({"overall_exact_match": report["overall_exact_match"], "items": report["items"]}))
     return 0
@@ -520,6 +528,12 @@ def build_parser() -> argparse.ArgumentParser:
         p = sub.add_parser(name); common(p)
         p.add_argument("--data", required=True); p.add_argument("--output", required=True)
         p.add_argument("--batch-size", type=int, default=32); p.add_argument("--max-items", type=int); p.set_defaults(func=fn)
+        if name == "cloze-evaluate":
+            # independent: every value from its true prefix, fixed length; progressive: the six holes of a biography filled left
+            # to right in one growing sequence, each value generated until the source's next full stop
+            p.add_argument("--protocol", choices=("independent", "progressive"), default="independent")
+            p.add_argument("--examples", type=int, default=1000); p.add_argument("--start-index", type=int, default=0)
+            p.add_argument("--max-new-tokens", type=int, default=16); p.add_argument("--sample-biographies", type=int, default=12)
 
     p = sub.add_parser("summarize-cloze"); p.add_argument("reports", nargs="+"); p.add_argument("--output", required=True)
     p.set_defaults(func=cmd_summarize_cloze)

@@ -104,6 +104,17 @@ def test_recall_cloze_and_router_reports(study):
     assert out.returncode == 0, out.stderr[-2000:]
     cloze = json.loads((study["root"] / "cloze.json").read_text())
     assert cloze["items"] == 36 and set(cloze["per_attribute"]) == {"birth_date", "birth_city", "university", "major", "company", "company_city"}
+    out = run("cloze-evaluate", *common, "--output", str(study["root"] / "cloze_progressive.json"), "--batch-size", "3", "--protocol",
+              "progressive", "--examples", "4", "--max-new-tokens", "6", "--sample-biographies", "2")
+    assert out.returncode == 0, out.stderr[-2000:]
+    prog = json.loads((study["root"] / "cloze_progressive.json").read_text())
+    # --max-items (6, from the common arguments) takes precedence over --examples
+    assert prog["protocol"] == "progressive_original_biography_cloze_greedy" and prog["biographies"] == 6 and prog["fields"] == 36
+    assert len(prog["samples"]) == 2 and set(prog["samples"][0]["predicted"]) == set(prog["per_attribute"])
+    assert sum(prog["biography_correct_field_count_histogram"].values()) == 6 and 0.0 <= prog["mean_character_similarity"] <= 1.0
+    out = run("summarize-cloze", str(study["root"] / "cloze.json"), str(study["root"] / "cloze_progressive.json"), "--output",
+              str(study["root"] / "cloze_table.csv"))
+    assert out.returncode == 0, out.stderr[-2000:]          # both protocols feed the same table
     out = run("analyze", *common, "--output", str(study["root"] / "routes.json"))
     assert out.returncode == 0, out.stderr[-2000:]
     routes = json.loads((study["root"] / "routes.json").read_text())
@@ -282,3 +293,72 @@ def test_gpt2_alignment_when_the_vocabulary_is_available():
     tokens, (pos,) = positions_before_chars(codec, text, [start])
     assert codec.decode(tokens[1:pos + 1]) == text[:start].rstrip(" ") or codec.decode(tokens[1:pos + 1]) == text[:start]
     assert codec.decode(tokens[pos + 1:pos + 2]).strip().startswith("Pr")
+
+
+def test_character_similarity_and_progressive_cloze_with_an_oracle_model(tmp_path):
+    """A stand-in model that always continues with the source text reproduces every field: the progressive protocol must then
+    score 6 / 6 per biography, terminate every field at the source's full stop and rebuild the original text."""
+
+    import torch
+
+    from experiments.synbios_moe.codec import get_codec
+    from experiments.synbios_moe.pretraining.cloze import biography_fields, character_similarity, evaluate_progressive_cloze
+    from dataclasses import asdict
+
+    from experiments.synbios_moe.pretraining.dataset import ATTRIBUTES, generate_profiles, iter_biographies
+
+    assert character_similarity("MIT", "mit") == 1.0 and character_similarity("", "") == 1.0
+    assert character_similarity("abcd", "abcf") == pytest.approx(0.75) and character_similarity("x", "") == 0.0
+    assert character_similarity("New   York", "new york") == 1.0
+
+    codec = get_codec("bytes")
+    profiles = generate_profiles(4, seed=5)
+    rows = [asdict(b) for b in iter_biographies(profiles, "single", 5)]
+    book = {}
+    for row in rows:
+        ids, fields = biography_fields(codec, row)
+        assert sorted(f["attribute"] for f in fields) == sorted(ATTRIBUTES) and [f["lo"] for f in fields] == sorted(f["lo"] for f in fields)
+        book[row["person_id"]] = ids
+
+    class Oracle(torch.nn.Module):
+        """hidden state = one-hot of the token that follows the prefix in the source biography; lm_head is the identity."""
+
+        class cfg:  # noqa: N801
+            seq_len = 4096
+
+        def __init__(self, wrong_for=None):
+            super().__init__()
+            self.wrong_for = wrong_for
+
+        def hidden_states(self, batch):
+            out = torch.zeros(*batch.shape, 257)
+            for r in range(batch.shape[0]):
+                seq = batch[r].tolist()
+
+                def shared(ids):
+                    n = 0
+                    while n < min(len(ids), len(seq)) and ids[n] == seq[n]:
+                        n += 1
+                    return n
+
+                source = max(book.values(), key=shared)           # the biography this row is a prefix of
+                for t in range(batch.shape[1]):
+                    nxt = source[t + 1] if t + 1 < len(source) else codec.eos
+                    out[r, t, nxt] = 1.0
+            return out
+
+        def lm_head(self, h):
+            return h
+
+    report = evaluate_progressive_cloze(Oracle(), codec, rows, max_biographies=3, start_index=1, batch_size=2, max_new_tokens=64)
+    assert report["protocol"] == "progressive_original_biography_cloze_greedy" and report["biographies"] == 3 and report["fields"] == 18
+    assert report["micro_field_accuracy"] == 1.0 and report["biography_all_fields_accuracy"] == 1.0 and report["unterminated_fields"] == 0
+    assert report["biography_correct_field_count_histogram"]["6"] == 3 and report["overall_exact_match"] == 1.0
+    assert set(report["per_attribute"]) == set(ATTRIBUTES)
+    for sample in report["samples"]:
+        assert sample["filled_text"] == sample["original_text"] and sample["exact_fields"] == 6
+    # too few new tokens: (almost) nothing reaches its full stop, predictions are truncated, similarity stays between 0 and 1
+    short = evaluate_progressive_cloze(Oracle(), codec, rows, max_biographies=2, batch_size=2, max_new_tokens=2)
+    assert short["unterminated_fields"] >= 10 and short["micro_field_accuracy"] < 0.5 and 0.0 < short["mean_character_similarity"] < 1.0
+    with pytest.raises(ValueError):
+        evaluate_progressive_cloze(Oracle(), codec, rows, max_biographies=0)
