@@ -129,6 +129,10 @@ def cmd_token_statistics(args) -> int:
     root = Path(args.data)
     stats = dataset_token_statistics(_codec(args), read_jsonl(root / "biographies.jsonl"), read_jsonl(root / "profiles.jsonl"))
     write_json(args.output, stats)
+    if args.distribution_dir:          # the per-attribute value-token distribution with its three tables
+        from experiments.synbios_moe.pretraining.token_statistics import attribute_token_distribution
+
+        attribute_token_distribution(_codec(args), read_jsonl(root / "profiles.jsonl"), args.distribution_dir)
     print(json.dumps({k: v for k, v in stats.items() if k != "attributes"}))
     return 0
 
@@ -515,7 +519,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-shard-tokens", type=int, default=10_000_000); p.set_defaults(func=cmd_prepare)
 
     p = sub.add_parser("token-statistics"); common(p, model=False, monitoring=False)
-    p.add_argument("--data", required=True); p.add_argument("--output", required=True); p.set_defaults(func=cmd_token_statistics)
+    p.add_argument("--data", required=True); p.add_argument("--output", required=True)
+    p.add_argument("--distribution-dir", help="also write the value-token distribution per attribute (summary.json and three CSV tables)")
+    p.set_defaults(func=cmd_token_statistics)
 
     p = sub.add_parser("cache-probes"); common(p, model=False, monitoring=False)
     p.add_argument("--data", required=True); p.add_argument("--output", required=True); p.add_argument("--force", action="store_true")

@@ -362,3 +362,32 @@ def test_character_similarity_and_progressive_cloze_with_an_oracle_model(tmp_pat
     assert short["unterminated_fields"] >= 10 and short["micro_field_accuracy"] < 0.5 and 0.0 < short["mean_character_similarity"] < 1.0
     with pytest.raises(ValueError):
         evaluate_progressive_cloze(Oracle(), codec, rows, max_biographies=0)
+
+
+def test_attribute_token_distribution_tables(tmp_path):
+    from experiments.synbios_moe.codec import get_codec
+    from experiments.synbios_moe.pretraining.dataset import ATTRIBUTES
+    from experiments.synbios_moe.pretraining.token_statistics import attribute_token_distribution, entropy_bits, percentile
+
+    from collections import Counter
+
+    assert entropy_bits(Counter({1: 2, 2: 2})) == pytest.approx(1.0) and entropy_bits(Counter()) == 0.0
+    assert percentile([1, 2, 3, 4, 5], 50) == 3 and percentile([1, 2], 95) == pytest.approx(1.95)
+    base = {a: "x" for a in ATTRIBUTES}
+    people = [{**base, "university": "MIT"}, {**base, "university": "MIT"}, {**base, "university": "Ohio"}, {**base, "university": "M"}]
+    report = attribute_token_distribution(get_codec("bytes"), people, tmp_path / "dist")
+    uni = report["attributes"]["university"]
+    # byte codec: " MIT" is 4 tokens, " Ohio" 5, " M" 2; every value starts with the space, so one first-token class holds all three
+    assert uni["unique_values"] == 3 and uni["token_length"]["minimum"] == 2 and uni["token_length"]["maximum"] == 5
+    assert uni["token_length"]["mean_profile_weighted"] == pytest.approx((4 + 4 + 5 + 2) / 4)
+    assert uni["first_token"]["unique_tokens_unique_values"] == 1 and uni["first_token"]["whole_classes_per_first_token"]["maximum"] == 3
+    assert uni["first_token"]["entropy_bits_profile_weighted"] == 0.0
+    assert uni["position_unique_token_counts"]["2"] == 2           # 'M' or 'O' at the second position
+    assert uni["position_entropy_bits_profile_weighted"]["2"] == pytest.approx(entropy_bits(Counter({77: 3, 79: 1})))
+    assert uni["leading_space_comparison"]["changed_fraction"] == 1.0 and uni["leading_space_comparison"]["bare_first_token_classes"] == 2
+    assert report["protocol"] == "synbios_attribute_leading_space_token_distribution_v1"
+    rows = (tmp_path / "dist" / "position_token_distribution.csv").read_text().splitlines()
+    assert rows[0].startswith("attribute,token_position,token_id,token_text") and any(",2,77,M,3,0.75,0.75,2" in r for r in rows)
+    lengths = (tmp_path / "dist" / "length_distribution.csv").read_text().splitlines()
+    assert "university,profile_weighted,4,2,0.5" in lengths and "university,unique_values,4,1,0.3333333333333333" in lengths
+    assert len((tmp_path / "dist" / "attribute_summary.csv").read_text().splitlines()) == 1 + len(ATTRIBUTES)
