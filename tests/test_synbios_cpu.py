@@ -391,3 +391,15 @@ def test_attribute_token_distribution_tables(tmp_path):
     lengths = (tmp_path / "dist" / "length_distribution.csv").read_text().splitlines()
     assert "university,profile_weighted,4,2,0.5" in lengths and "university,unique_values,4,1,0.3333333333333333" in lengths
     assert len((tmp_path / "dist" / "attribute_summary.csv").read_text().splitlines()) == 1 + len(ATTRIBUTES)
+
+
+def test_token_statistics_command_writes_both_reports(study):
+    out = study["run"]("token-statistics", "--data", str(study["data"]), "--codec", "bytes", "--output", str(study["root"] / "tokens.json"),
+                       "--distribution-dir", str(study["root"] / "token_distribution"))
+    assert out.returncode == 0, out.stderr[-2000:]
+    stats = json.loads((study["root"] / "tokens.json").read_text())
+    assert stats["biographies"] == 48 and set(stats["attributes"]) == {"birth_date", "birth_city", "university", "major", "company", "company_city"}
+    dist = json.loads((study["root"] / "token_distribution" / "summary.json").read_text())
+    assert dist["num_people"] == 24 and dist["attributes"]["major"]["profile_count"] == 24
+    for name in dist["artifacts"].values():
+        assert (study["root"] / "token_distribution" / name).is_file()
