@@ -88,4 +88,16 @@ def fit_company_pair(curves: Mapping[str, Sequence[float]], output_dir: str | Pa
         write_csv(out / "company_relation_metrics.csv", rows,
                   ["attribute", "baseline", "gain", "saturation", "rmse", "r_squared", "leave_one_out_rmse", "observed_p0", "observed_p5"])
         write_json(out / "company_relation.json", summary)
+        from experiments.synbios_moe.artifact_io import write_text
+        from experiments.synbios_moe.probes.figures import line_chart_svg
+
+        series, dashed = {}, []
+        for a in PAIR:
+            series[f"{a}: observed"] = [float(v) for v in curves[a]]
+            series[f"{a}: fit"] = [float(v) for v in fits[a]["prediction"]]
+            dashed.append(f"{a}: fit")
+        series["partner exposure"] = x.tolist()
+        dashed.append("partner exposure")
+        write_text(out / "company_relation.svg", line_chart_svg(series, title="P-whole accuracy of the paired attributes against partner exposure",
+                                                                x_labels=[f"P{i}" for i in range(6)], dashed=dashed))
     return summary

@@ -3,7 +3,7 @@
 Inputs: ``<run_dir>/<attribute>.json`` (one record per attribute from ``train_ground_truth_first_whole_probe``) and the
 pipeline root with the original ``p-<attribute>-first`` / ``p-<attribute>-whole`` results.  Output: one row per
 (attribute, source position) with the original first-token accuracy, the original whole accuracy, the whole accuracy after
-the true first token was appended and the gain in points; a CSV, a JSON summary and a Markdown table
+the true first token was appended and the gain in points; a CSV, a JSON summary, a Markdown table and a line figure
 (reference: experiments/synbios_moe/mechanisms/intervention_report.py:22-424).
 """
 
@@ -75,5 +75,17 @@ def summarize_ground_truth_first_whole(run_dir: str | Path, probe_root: str | Pa
                      f"{r['gain_points']:.1f} | {r['gain_points_p0']:.1f} | {r['gain_points_p5']:.1f} |")
     if missing:
         lines += ["", f"Not yet run: {', '.join(missing)}."]
+    if rows:
+        from experiments.synbios_moe.probes.figures import line_chart_svg
+
+        # one panel per attribute would need a layout engine; the mean over the reported attributes shows the effect, the CSV has the rest
+        def curve(key):
+            return [_mean(r[key] for r in rows if r["position"] == p) for p in range(6)]
+
+        series = {"whole, + true first token": curve("whole_accuracy_ground_truth_first"), "whole, original P probe": curve("whole_accuracy"),
+                  "first token, original P probe": curve("first_accuracy")}
+        write_text(out / "by_position.svg", line_chart_svg(series, title="Whole-value read-out by biography position (mean over attributes)",
+                                                           x_labels=[f"P{i}" for i in range(6)], dashed=("first token, original P probe",)))
+        lines += ["", "Figure: `by_position.svg`."]
     write_text(out / "report.md", "\n".join(lines) + "\n")
     return summary

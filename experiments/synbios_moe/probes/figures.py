@@ -178,3 +178,49 @@ def write_probe_figures(rows: Sequence[dict], headline: dict, output_dir: str | 
     write_text(out / "overview.svg", overview_svg(headline))
     written.append("overview.svg")
     return written
+
+
+_SERIES_COLOURS = ("#138a82", "#9b6a50", "#3b5ba5", "#c0392b", "#7d3c98", "#d68910", "#2e4053", "#1e8449")
+
+
+def line_chart_svg(series: dict[str, Sequence[float]], *, title: str, x_labels: Sequence[str], y_label: str = "Accuracy (%)",
+                   dashed: Sequence[str] = (), percent: bool = True, width: int = 640, height: int = 380) -> str:
+    """Curves over a shared categorical x axis (e.g. the six biography positions).  Values are fractions shown as percentages
+    when ``percent``; series named in ``dashed`` are drawn dashed (fits, baselines)."""
+
+    if not series or any(len(v) != len(x_labels) for v in series.values()):
+        raise ValueError("every series needs one value per x label")
+    left, top, right, bottom = 64, 50, 170, 46
+    plot_w, plot_h = width - left - right, height - top - bottom
+    scale = 100.0 if percent else 1.0
+    lo = min(0.0, min(min(v) for v in series.values()) * scale)
+    hi = max(max(max(v) for v in series.values()) * scale, lo + 1e-9)
+    if percent:
+        hi = max(hi, 100.0) if hi > 50.0 else hi * 1.1
+
+    def sx(i: int) -> float:
+        return left + (plot_w * i / max(len(x_labels) - 1, 1))
+
+    def sy(v: float) -> float:
+        return top + plot_h * (1.0 - (v * scale - lo) / (hi - lo))
+
+    parts = [f"<rect x='{left}' y='{top}' width='{plot_w}' height='{plot_h}' fill='#fbfcfe' stroke='#cccccc'/>"]
+    for k in range(5):
+        v = lo + (hi - lo) * k / 4
+        y = top + plot_h * (1 - k / 4)
+        parts.append(f"<line x1='{left}' y1='{y:.1f}' x2='{left + plot_w}' y2='{y:.1f}' stroke='#e4e7ec'/>")
+        parts.append(f"<text x='{left - 8}' y='{y + 4:.1f}' {_FONT} font-size='11' text-anchor='end'>{v:.0f}</text>")
+    for i, label in enumerate(x_labels):
+        parts.append(f"<text x='{sx(i):.1f}' y='{top + plot_h + 18}' {_FONT} font-size='12' text-anchor='middle'>{escape(label)}</text>")
+    parts.append(f"<text x='16' y='{top + plot_h / 2:.0f}' {_FONT} font-size='12' transform='rotate(-90 16 {top + plot_h / 2:.0f})' text-anchor='middle'>{escape(y_label)}</text>")
+    for n, (name, values) in enumerate(series.items()):
+        colour = _SERIES_COLOURS[n % len(_SERIES_COLOURS)]
+        points = " ".join(f"{sx(i):.1f},{sy(float(v)):.1f}" for i, v in enumerate(values))
+        dash = " stroke-dasharray='6 4'" if name in dashed else ""
+        parts.append(f"<polyline points='{points}' fill='none' stroke='{colour}' stroke-width='2'{dash}/>")
+        if name not in dashed:
+            parts += [f"<circle cx='{sx(i):.1f}' cy='{sy(float(v)):.1f}' r='3' fill='{colour}'/>" for i, v in enumerate(values)]
+        ly = top + 14 + 18 * n
+        parts.append(f"<line x1='{left + plot_w + 12}' y1='{ly - 4}' x2='{left + plot_w + 36}' y2='{ly - 4}' stroke='{colour}' stroke-width='2'{dash}/>")
+        parts.append(f"<text x='{left + plot_w + 42}' y='{ly}' {_FONT} font-size='11'>{escape(name)}</text>")
+    return wrap_svg("\n".join(parts), width, height, title)

@@ -457,3 +457,24 @@ def test_branching_evidence_reduces_complete_tables_and_refuses_broken_ones():
         branching_evidence({**summary, "examples": 31}, pair_rows, nmi_rows)
     with pytest.raises(ValueError, match="protocol"):
         branching_evidence({**summary, "protocol": "other"}, pair_rows, nmi_rows)
+
+
+def test_line_chart_and_the_reports_that_use_it(tmp_path):
+    import xml.etree.ElementTree as ET
+
+    from experiments.synbios_moe.mechanisms.company_relation import fit_company_pair, paired_exposure
+    from experiments.synbios_moe.pretraining.dataset import WHOLE_ATTRIBUTES
+    from experiments.synbios_moe.probes.figures import line_chart_svg
+
+    svg = line_chart_svg({"a": [0.1, 0.5, 0.9], "fit <b>": [0.2, 0.5, 0.8]}, title="t", x_labels=["P0", "P1", "P2"], dashed=("fit <b>",))
+    root = ET.fromstring(svg)
+    assert len(root.findall("{http://www.w3.org/2000/svg}polyline")) == 2 and svg.count("<circle") == 3 and "stroke-dasharray" in svg
+    assert "fit &lt;b&gt;" in svg
+    with pytest.raises(ValueError):
+        line_chart_svg({"a": [0.1]}, title="t", x_labels=["P0", "P1"])
+    x = paired_exposure()
+    curves = {a: (0.2 + 0.6 * x if a in ("company", "company_city") else 0.3 + 0.0 * x) for a in WHOLE_ATTRIBUTES}
+    out = fit_company_pair(curves, tmp_path / "company")
+    assert out["pair_mean_gain"] == pytest.approx(0.6, abs=1e-9)
+    figure = (tmp_path / "company" / "company_relation.svg").read_text()
+    assert ET.fromstring(figure).tag.endswith("svg") and "partner exposure" in figure and figure.count("<polyline") == 5
