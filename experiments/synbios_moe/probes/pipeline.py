@@ -149,11 +149,49 @@ def schedule_jobs(jobs: Sequence[JobSpec], devices: Sequence[str], state: Pipeli
     return results
 
 
+def estimate_phase_durations(previous: dict | None, jobs: Sequence[JobSpec], *, steps: int, device_count: int) -> dict[str, float]:
+    """Wall-clock seconds per phase of a stage, predicted from the finished prerequisite stage.
+
+    ``previous`` is that stage's ``pipeline.json``.  A phase is estimated only when the earlier stage ran exactly the same
+    jobs of that phase and all of them finished with a recorded duration: their seconds are summed (training scaled by the
+    ratio of step counts, which is what differs between stages), and divided over the devices that will share them
+    (reference: experiments/synbios_moe/probes/pipeline.py:635-675)."""
+
+    if not previous or device_count <= 0 or steps <= 0:
+        return {}
+    earlier_steps = (previous.get("settings") or {}).get("steps")
+    records = previous.get("jobs")
+    if not isinstance(records, dict):
+        return {}
+    out: dict[str, float] = {}
+    for phase in ("training", "validation"):
+        mine = {j.name for j in jobs if j.phase == phase}
+        theirs = {n: r for n, r in records.items() if r.get("phase") == phase}
+        if not mine or set(theirs) != mine:
+            continue
+        if any(r.get("status") not in ("done", "skipped") or not isinstance(r.get("seconds"), (int, float)) for r in theirs.values()):
+            continue
+        scale = 1.0
+        if phase == "training":
+            if not isinstance(earlier_steps, int) or earlier_steps <= 0:
+                continue
+            scale = steps / earlier_steps
+        out[phase] = sum(float(r["seconds"]) for r in theirs.values()) * scale / device_count
+    return out
+
+
 def run_pipeline(root: Path, training: Sequence[JobSpec], validation: Sequence[JobSpec], *, devices: Sequence[str], identity: str,
-                 heartbeat_seconds: float = 30.0, on_heartbeat=None, env=None) -> dict:
-    """Training phase, then validation of everything that trained; the summary is what ``pipeline.json`` ends with."""
+                 heartbeat_seconds: float = 30.0, on_heartbeat=None, env=None, settings: dict | None = None,
+                 estimates: dict[str, float] | None = None) -> dict:
+    """Training phase, then validation of everything that trained; the summary is what ``pipeline.json`` ends with.
+    ``settings`` (step count and the like) and ``estimates`` (predicted seconds per phase) are recorded beside the jobs."""
 
     state = PipelineState(root / "pipeline.json", identity, [*training, *validation])
+    if settings is not None:
+        state.data["settings"] = dict(settings)
+    if estimates:
+        state.data["estimated_phase_seconds"] = dict(estimates)
+    state.flush()
     first = schedule_jobs(training, devices, state, heartbeat_seconds=heartbeat_seconds, on_heartbeat=on_heartbeat, env=env)
     runnable = [v for v in validation if all(d.is_file() for d in v.dependencies)]
     second = schedule_jobs(runnable, devices, state, heartbeat_seconds=heartbeat_seconds, on_heartbeat=on_heartbeat, env=env)

@@ -286,8 +286,20 @@ def cmd_probe_pipeline(args) -> int:
     validation = [validation_job(root, j, data=args.data, probe_cache=args.probe_cache, model_config=args.model_config,
                                  checkpoint=args.checkpoint, codec=args.codec) for j in training]
     heartbeat = args.heartbeat_seconds or float(runtime.get("heartbeat_seconds", 30))
+    estimates = {}
+    if required and (root.parent / required / "pipeline.json").is_file():      # how long will this stage take, judging by the last one
+        from experiments.synbios_moe.artifact_io import read_json
+        from experiments.synbios_moe.probes.pipeline import estimate_phase_durations
+
+        estimates = estimate_phase_durations(read_json(root.parent / required / "pipeline.json"), [*training, *validation],
+                                             steps=int(steps), device_count=len(devices))
+        if estimates and not args.quiet:
+            print(json.dumps({"estimated_phase_seconds": estimates, "from_stage": required}), flush=True)
     summary = run_pipeline(root, training, validation, devices=devices, identity=identity, heartbeat_seconds=heartbeat,
+                           settings={"stage": args.stage, "steps": int(steps), "devices": len(devices)}, estimates=estimates,
                            on_heartbeat=None if args.quiet else (lambda name, ev: print(json.dumps({"job": name, "last_event": ev}), flush=True)))
+    if estimates:
+        summary["estimated_phase_seconds"] = estimates
     summary["results"] = summarize_probe_results(root)["mean_accuracy"]
     if summary["ok"]:
         (root / "STAGE_OK").write_text(identity + "\n")

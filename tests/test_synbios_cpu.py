@@ -403,3 +403,26 @@ def test_token_statistics_command_writes_both_reports(study):
     assert dist["num_people"] == 24 and dist["attributes"]["major"]["profile_count"] == 24
     for name in dist["artifacts"].values():
         assert (study["root"] / "token_distribution" / name).is_file()
+
+
+def test_phase_duration_estimates_scale_steps_and_devices(tmp_path):
+    from experiments.synbios_moe.probes.pipeline import estimate_phase_durations
+    from experiments.synbios_moe.probes.spec import JobSpec
+
+    def job(name, phase):
+        return JobSpec(name, ("x",), tmp_path / f"{name}.json", tmp_path / f"{name}.log", phase=phase)
+
+    jobs = [job("p-a", "training"), job("q-a", "training"), job("p-a.val", "validation"), job("q-a.val", "validation")]
+    previous = {"settings": {"steps": 100}, "jobs": {"p-a": {"phase": "training", "status": "done", "seconds": 10.0},
+                                                      "q-a": {"phase": "training", "status": "skipped", "seconds": 30.0},
+                                                      "p-a.val": {"phase": "validation", "status": "done", "seconds": 4.0},
+                                                      "q-a.val": {"phase": "validation", "status": "done", "seconds": 6.0}}}
+    est = estimate_phase_durations(previous, jobs, steps=1000, device_count=2)
+    assert est == {"training": pytest.approx((10.0 + 30.0) * 10 / 2), "validation": pytest.approx(5.0)}
+    # a different job set, an unfinished job or a missing step count: that phase is not estimated
+    assert "training" not in estimate_phase_durations(previous, jobs[1:], steps=1000, device_count=2)
+    broken = json.loads(json.dumps(previous)); broken["jobs"]["p-a"]["status"] = "failed"
+    assert estimate_phase_durations(broken, jobs, steps=1000, device_count=2) == {"validation": pytest.approx(5.0)}
+    nosteps = json.loads(json.dumps(previous)); del nosteps["settings"]
+    assert estimate_phase_durations(nosteps, jobs, steps=1000, device_count=2) == {"validation": pytest.approx(5.0)}
+    assert estimate_phase_durations(None, jobs, steps=10, device_count=1) == {} and estimate_phase_durations(previous, jobs, steps=10, device_count=0) == {}
