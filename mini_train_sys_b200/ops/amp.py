@@ -21,3 +21,8 @@ def cast_activations(*tensors: torch.Tensor) -> tuple[torch.Tensor, ...]:
     if dtype is None:
         return tensors
     return tuple(t.to(dtype) if (t.is_cuda and t.is_floating_point() and t.dtype != dtype) else t for t in tensors)
+
+
+# the names the reference's helper module uses (minitrain/kernels/amp.py:7-36)
+cuda_autocast_activation_dtype = lambda: autocast_dtype("cuda")   # noqa: E731
+cast_cuda_autocast_activations = cast_activations

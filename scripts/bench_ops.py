@@ -45,6 +45,7 @@ def _parser() -> argparse.ArgumentParser:
     s = sub.add_parser("summarize", help="merge cached scans into the headline table")
     s.add_argument("directory")
     s.add_argument("--format", choices=("json", "markdown"), default="markdown")
+    s.add_argument("--plots", default=None, help="directory for one SVG per kernel (latency and speed-up over the token sizes)")
     c = sub.add_parser("ncu-command", help="print the capture command of a registered kernel")
     c.add_argument("kernel")
     c.add_argument("--mode", choices=("launches", "roofline", "full"), default="full")
@@ -92,6 +93,10 @@ def main(argv=None) -> int:
         table = operators.headline_table(results)
         print(json.dumps(table, indent=1) if args.format == "json" else _markdown(table))
         print(json.dumps(operators.quality_gate(results)))
+        if args.plots:
+            from mini_train_sys_b200.bench.plots import write_kernel_plots
+
+            print(json.dumps({"plots": write_kernel_plots(table, args.plots)}))
         return 0
     if args.command == "ncu-command":
         print(nsight.command_for(args.kernel, "scripts/bench_ops.py", mode=args.mode, output=args.output))

@@ -153,3 +153,34 @@ def test_evidence_tooling_roundtrip(tmp_path):
     rows[1]["identity"] = "tampered"
     (tree / "distributed" / "weak" / "summary.json").write_text(json.dumps({"suite": "weak", "rows": rows, "weak": weak_scaling_table(rows)}))
     assert run(str(ROOT / "scripts" / "audit_results_export.py"), str(tree)).returncode == 1
+
+
+def test_operator_plots_are_well_formed_and_complete(tmp_path):
+    import xml.etree.ElementTree as ET
+
+    from mini_train_sys_b200.bench.plots import kernel_grid_svg, write_kernel_plots
+
+    table = []
+    for tokens in (512, 2048, 8192):
+        table.append({"kernel": "rmsnorm", "profile": "p", "tokens": tokens, "provider": "torch", "fwd_ms": tokens / 1000, "full_ms": tokens / 400,
+                      "bwd_ms": tokens / 700, "speedup_full": 1.0})
+        table.append({"kernel": "rmsnorm", "profile": "p", "tokens": tokens, "provider": "native", "fwd_ms": tokens / 9000, "full_ms": tokens / 4000,
+                      "bwd_ms": None, "speedup_full": 10.0})
+    table.append({"kernel": "rope", "profile": "p", "tokens": 512, "provider": "native", "fwd_ms": 0.1, "full_ms": 0.2, "bwd_ms": 0.1, "speedup_full": None})
+    svg = kernel_grid_svg(table, "rmsnorm")
+    root = ET.fromstring(svg)
+    ns = "{http://www.w3.org/2000/svg}"
+    assert len(root.findall(f"{ns}polyline")) == 2 + 2 + 1 + 2          # backward of `native` has no data
+    assert svg.count("<circle") == 3 * (2 + 2 + 1 + 2) and "stroke-dasharray" in svg and ">8192<" in svg
+    written = write_kernel_plots(table, tmp_path / "plots")
+    assert written == ["rmsnorm.svg", "rope.svg"] and "no data" in (tmp_path / "plots" / "rope.svg").read_text()
+    # the summarize command writes them from cached scans
+    cache = tmp_path / "scan"
+    cache.mkdir()
+    rows = [{"kernel": "swiglu", "tokens": t, "provider": pr, "fwd": {"p50_ms": 0.1 * t / 512}, "full": {"p50_ms": 0.3 * t / 512},
+             "bwd": {"p50_ms": 0.2 * t / 512}} for t in (512, 1024) for pr in ("torch", "native")]
+    (cache / "x.json").write_text(json.dumps({"k": {"status": "ok", "profile": "p", "rows": rows}}))
+    out = subprocess.run([sys.executable, str(ROOT / "scripts" / "bench_ops.py"), "summarize", str(cache), "--plots", str(tmp_path / "p2")],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert (tmp_path / "p2" / "swiglu.svg").is_file() and '"plots": ["swiglu.svg"]' in out.stdout
