@@ -157,7 +157,7 @@ def estimate_phase_durations(previous: dict | None, jobs: Sequence[JobSpec], *, 
     ratio of step counts, which is what differs between stages), and divided over the devices that will share them
     (reference: experiments/synbios_moe/probes/pipeline.py:635-675)."""
 
-    if not previous or device_count <= 0 or steps <= 0:
+    if not previous or device_count <= 0:
         return {}
     earlier_steps = (previous.get("settings") or {}).get("steps")
     records = previous.get("jobs")
@@ -173,7 +173,7 @@ def estimate_phase_durations(previous: dict | None, jobs: Sequence[JobSpec], *, 
             continue
         scale = 1.0
         if phase == "training":
-            if not isinstance(earlier_steps, int) or earlier_steps <= 0:
+            if not isinstance(earlier_steps, int) or earlier_steps <= 0 or steps <= 0:      # per-task step tables are not scaled
                 continue
             scale = steps / earlier_steps
         out[phase] = sum(float(r["seconds"]) for r in theirs.values()) * scale / device_count

@@ -292,11 +292,11 @@ def cmd_probe_pipeline(args) -> int:
         from experiments.synbios_moe.probes.pipeline import estimate_phase_durations
 
         estimates = estimate_phase_durations(read_json(root.parent / required / "pipeline.json"), [*training, *validation],
-                                             steps=int(steps), device_count=len(devices))
+                                             steps=steps if isinstance(steps, int) else 0, device_count=len(devices))
         if estimates and not args.quiet:
             print(json.dumps({"estimated_phase_seconds": estimates, "from_stage": required}), flush=True)
     summary = run_pipeline(root, training, validation, devices=devices, identity=identity, heartbeat_seconds=heartbeat,
-                           settings={"stage": args.stage, "steps": int(steps), "devices": len(devices)}, estimates=estimates,
+                           settings={"stage": args.stage, "steps": steps, "devices": len(devices)}, estimates=estimates,
                            on_heartbeat=None if args.quiet else (lambda name, ev: print(json.dumps({"job": name, "last_event": ev}), flush=True)))
     if estimates:
         summary["estimated_phase_seconds"] = estimates

@@ -426,3 +426,4 @@ def test_phase_duration_estimates_scale_steps_and_devices(tmp_path):
     nosteps = json.loads(json.dumps(previous)); del nosteps["settings"]
     assert estimate_phase_durations(nosteps, jobs, steps=1000, device_count=2) == {"validation": pytest.approx(5.0)}
     assert estimate_phase_durations(None, jobs, steps=10, device_count=1) == {} and estimate_phase_durations(previous, jobs, steps=10, device_count=0) == {}
+    assert estimate_phase_durations(previous, jobs, steps=0, device_count=2) == {"validation": pytest.approx(5.0)}     # a per-task step table
