@@ -427,3 +427,26 @@ def test_phase_duration_estimates_scale_steps_and_devices(tmp_path):
     assert estimate_phase_durations(nosteps, jobs, steps=1000, device_count=2) == {"validation": pytest.approx(5.0)}
     assert estimate_phase_durations(None, jobs, steps=10, device_count=1) == {} and estimate_phase_durations(previous, jobs, steps=10, device_count=0) == {}
     assert estimate_phase_durations(previous, jobs, steps=0, device_count=2) == {"validation": pytest.approx(5.0)}     # a per-task step table
+
+
+def test_probe_pipeline_cloze_gate_runs_once_and_can_refuse(study, tmp_path):
+    """The gate is the progressive cloze; its verdict is cached by checkpoint, data and settings, and a threshold the model
+    does not reach stops the stage before any probe job starts."""
+
+    run = study["run"]
+    cfg = tmp_path / "pipeline.yaml"
+    base = {"stages": {"smoke": {"requires": None, "steps": 2, "tasks": [{"attribute": "major", "kind": "q", "target": "first"}]}}}
+    cfg.write_text(json.dumps({**base, "gate": {"batch_size": 4, "examples": 5, "max_new_tokens": 4, "sample_biographies": 2, "threshold": 0.0}}))
+    args = ["probe-pipeline", "--data", str(study["data"]), "--probe-cache", str(study["cache"]), "--model-config", str(study["model_config"]),
+            "--checkpoint", str(study["checkpoint"]), "--codec", "bytes", "--device", "cpu", "--devices", "cpu", "--stage", "smoke",
+            "--config", str(cfg), "--output", str(tmp_path / "pipe"), "--heartbeat-seconds", "1", "--max-eval-items", "4", "--quiet"]
+    out = run(*args)
+    assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-1500:])
+    gate = json.loads((tmp_path / "pipe" / "gate.json").read_text())
+    assert gate["protocol"] == "progressive_original_biography_cloze_greedy" and gate["biographies"] == 5 and gate["items"] == 30
+    assert gate["passed"] and gate["reused"] is False and len(gate["samples"]) == 2
+    out = run(*args)
+    assert out.returncode == 0 and json.loads((tmp_path / "pipe" / "gate.json").read_text())["reused"] is True
+    cfg.write_text(json.dumps({**base, "gate": {"batch_size": 4, "examples": 5, "max_new_tokens": 4, "threshold": 0.99}}))
+    out = run(*[a if a != str(tmp_path / "pipe") else str(tmp_path / "pipe2") for a in args])
+    assert out.returncode == 3 and "cloze gate failed" in out.stdout and not (tmp_path / "pipe2" / "pipeline.json").exists()
