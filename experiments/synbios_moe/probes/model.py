@@ -202,6 +202,19 @@ def train_probe(backbone, cache_dir: str | Path, *, kind: str, attribute: str, t
     return result
 
 
+def active_parameter_estimate(model) -> dict[str, int]:
+    """Parameter count of the backbone and how many of them one token touches: with routed experts only ``top_k / experts``
+    of the expert weights are active (reference: experiments/synbios_moe/probes/model.py:575-583)."""
+
+    inner = getattr(model, "module", model)
+    total = sum(p.numel() for p in inner.parameters())
+    cfg = inner.cfg
+    if not cfg.is_moe:
+        return {"total": total, "active_estimate": total}
+    experts = sum(b.ffn.gate_up_proj.numel() + b.ffn.down_proj.numel() for b in inner.blocks if hasattr(b.ffn, "gate_up_proj"))
+    return {"total": total, "active_estimate": total - experts + experts * cfg.experts_per_token // cfg.num_experts}
+
+
 def save_probe_result(result: dict, json_path: str | Path, state_path: str | Path) -> None:
     """``training/<job>.pt`` (trainable weights) first, then ``training/<job>.json``: the marker is written last."""
 

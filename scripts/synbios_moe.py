@@ -199,7 +199,7 @@ def cmd_summarize_cloze(args) -> int:
 
 def cmd_probe(args) -> int:
     from experiments.synbios_moe.artifact_io import sha256_file
-    from experiments.synbios_moe.probes.model import save_probe_result, train_probe
+    from experiments.synbios_moe.probes.model import active_parameter_estimate, save_probe_result, train_probe
 
     sink = EventSink(args.log_dir, args.quiet)
     codec = _codec(args)
@@ -211,6 +211,9 @@ def cmd_probe(args) -> int:
                          recovery_checkpoint=args.recovery_checkpoint, checkpoint_interval_steps=args.checkpoint_interval_steps,
                          resume=args.resume_probe, evaluate_train=args.evaluate_train, skip_final_validation=args.skip_final_validation,
                          identity=identity, on_event=sink, max_eval_items=args.max_eval_items)
+    result["model_parameters"] = active_parameter_estimate(model)
+    result["checkpoint"] = str(Path(args.checkpoint).resolve())
+    result["checkpoint_bytes"] = Path(args.checkpoint).stat().st_size
     out = Path(args.output)
     save_probe_result(result, out, out.with_suffix(".pt"))
     sink({"event": "probe_done", "output": str(out), "validation": result.get("validation", {}).get("accuracy")})

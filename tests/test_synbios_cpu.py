@@ -209,6 +209,10 @@ def test_probe_pipeline_schedules_validates_and_skips_fresh_jobs(study, tmp_path
     assert summary["ok"] and set(summary["training"]) == {"p-major-first", "p-major-whole", "q-major-first", "q-major-whole"}
     state = json.loads((tmp_path / "pipe" / "pipeline.json").read_text())
     assert all(j["status"] == "done" for j in state["jobs"].values()) and len(state["jobs"]) == 8
+    trained = json.loads((tmp_path / "pipe" / "training" / "q-major-first.json").read_text())
+    # 2 layers x 4 experts x (2 * 32 * 32 + 32 * 32) expert weights, two of four active per token
+    assert trained["model_parameters"]["total"] - trained["model_parameters"]["active_estimate"] == 2 * 4 * 3 * 32 * 32 // 2
+    assert trained["checkpoint_bytes"] > 0 and trained["checkpoint"].endswith("model.pt")
     assert (tmp_path / "pipe" / "training" / "p-major-whole.pt").is_file() and (tmp_path / "pipe" / "validation" / "q-major-first.json").is_file()
     again = json.loads(run(*args).stdout.strip().splitlines()[-1])
     assert set(again["training"].values()) == {"skipped"} and set(again["validation"].values()) == {"skipped"}
