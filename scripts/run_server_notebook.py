@@ -9,6 +9,10 @@ outputs filled in.  The exit code is non-zero when any cell raised, which is wha
 acceptance tests (reference: scripts/run_server_notebook.py:1-125, which drives nbclient).
 
     python scripts/run_server_notebook.py examples/training_walkthrough.py --output runs/walkthrough.json
+
+``--export-ipynb PATH`` writes the cells of a ``.py`` walkthrough as a Jupyter notebook instead of running them
+(``# %% [markdown]`` blocks become markdown cells); ``examples/notebooks/*.ipynb`` are made this way and a test keeps
+them equal to their sources.
 """
 
 from __future__ import annotations
@@ -44,6 +48,53 @@ def load_cells(path: Path) -> list[str]:
     if current:
         cells.append("".join(current))
     return cells
+
+
+def percent_cells(text: str) -> list[tuple[str, str]]:
+    """(kind, source) for every ``# %%`` cell of a percent-format script; kind is "code" or "markdown".
+
+    Text before the first marker (a shebang, a module docstring) is a code cell of its own when it holds anything but
+    blank lines.  A markdown cell's source is its comment lines without the leading ``# ``.
+    """
+
+    cells: list[tuple[str, list[str]]] = [("code", [])]
+    for line in text.splitlines():
+        if line.startswith("# %%"):
+            cells.append(("markdown" if "[markdown]" in line else "code", []))
+        else:
+            cells[-1][1].append(line)
+    out = []
+    for kind, lines in cells:
+        if kind == "markdown":
+            lines = [ln[2:] if ln.startswith("# ") else ln.lstrip("#") for ln in lines]
+        while lines and not lines[0].strip():
+            lines.pop(0)
+        while lines and not lines[-1].strip():
+            lines.pop()
+        if lines and not (kind == "code" and all(ln.startswith("#!") for ln in lines)):
+            out.append((kind, "\n".join(lines)))
+    return out
+
+
+def notebook_from_script(text: str) -> dict:
+    """The notebook (nbformat 4.5, no outputs) with the cells of a percent-format script."""
+
+    cells = []
+    for index, (kind, source) in enumerate(percent_cells(text)):
+        cell = {"cell_type": kind, "id": f"cell-{index:03d}", "metadata": {}, "source": source.splitlines(keepends=True)}
+        if kind == "code":
+            cell.update(execution_count=None, outputs=[])
+        cells.append(cell)
+    return {"cells": cells, "nbformat": 4, "nbformat_minor": 5,
+            "metadata": {"kernelspec": {"display_name": "Python 3", "language": "python", "name": "python3"},
+                         "language_info": {"name": "python"}}}
+
+
+def export_notebook(source: Path, destination: Path) -> int:
+    notebook = notebook_from_script(source.read_text(encoding="utf-8"))
+    destination.parent.mkdir(parents=True, exist_ok=True)
+    destination.write_text(json.dumps(notebook, indent=1, ensure_ascii=False) + "\n", encoding="utf-8")
+    return len(notebook["cells"])
 
 
 def _strip_magics(source: str) -> str:
@@ -104,10 +155,16 @@ def main(argv=None) -> int:
     ap.add_argument("walkthrough", type=Path)
     ap.add_argument("--output", type=Path, help="JSON record (default: <walkthrough>.run.json)")
     ap.add_argument("--executed-notebook", type=Path, help="for .ipynb inputs: write a copy with the outputs filled in")
+    ap.add_argument("--export-ipynb", type=Path, help="for .py inputs: write the cells as a notebook and exit without running them")
     ap.add_argument("--keep-going", action="store_true", help="run the remaining cells after a failure")
     ap.add_argument("--quiet", action="store_true")
     args = ap.parse_args(argv)
     path = args.walkthrough.resolve()
+    if args.export_ipynb is not None:
+        if path.suffix != ".py":
+            ap.error("--export-ipynb wants a .py walkthrough")
+        print(json.dumps({"notebook": str(args.export_ipynb), "cells": export_notebook(path, args.export_ipynb)}))
+        return 0
     cells = load_cells(path)
     records = run_cells(cells, filename=str(path), keep_going=args.keep_going, echo=not args.quiet)
     failed = [r["cell"] for r in records if r["status"] == "error"]

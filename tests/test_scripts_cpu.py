@@ -123,6 +123,39 @@ def test_walkthrough_runner_records_cells_and_fails_on_errors(tmp_path):
     assert executed["cells"][2]["outputs"][0]["output_type"] == "error"
 
 
+def test_committed_notebooks_equal_their_percent_format_sources_and_run(tmp_path):
+    import importlib.util
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    spec = importlib.util.spec_from_file_location("run_server_notebook", root / "scripts" / "run_server_notebook.py")
+    runner = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(runner)
+    cells = runner.percent_cells("#!/usr/bin/env python\n# %% [markdown]\n# # Title\n#\n# text\n\n# %%\nx = 1\n\n\n# %% named\nprint(x)\n")
+    assert cells == [("markdown", "# Title\n\ntext"), ("code", "x = 1"), ("code", "print(x)")]
+    for name in ("training_walkthrough", "synbios_moe_walkthrough"):
+        source = root / "examples" / f"{name}.py"
+        committed = json.loads((root / "examples" / "notebooks" / f"{name}.ipynb").read_text(encoding="utf-8"))
+        assert committed == runner.notebook_from_script(source.read_text(encoding="utf-8")), f"regenerate {name}.ipynb with --export-ipynb"
+        kinds = [c["cell_type"] for c in committed["cells"]]
+        assert kinds[0] == "markdown" and kinds.count("code") >= 5 and all(c["outputs"] == [] for c in committed["cells"] if c["cell_type"] == "code")
+    notebook = root / "examples" / "notebooks" / "training_walkthrough.ipynb"
+    done = subprocess.run([sys.executable, str(root / "scripts" / "run_server_notebook.py"), str(notebook), "--output", str(tmp_path / "run.json"),
+                           "--executed-notebook", str(tmp_path / "executed.ipynb"), "--quiet"], capture_output=True, text=True, cwd=tmp_path)
+    assert done.returncode == 0, done.stderr[-2000:]
+    record = json.loads((tmp_path / "run.json").read_text())
+    assert record["failed_cells"] == [] and "walkthrough ok" in record["records"][-1]["stdout"]
+    executed = json.loads((tmp_path / "executed.ipynb").read_text())
+    assert any(o.get("text", "").startswith("[lr]") for c in executed["cells"] if c["cell_type"] == "code" for o in c["outputs"])
+    exported = tmp_path / "again.ipynb"
+    done = subprocess.run([sys.executable, str(root / "scripts" / "run_server_notebook.py"), str(root / "examples" / "training_walkthrough.py"),
+                           "--export-ipynb", str(exported)], capture_output=True, text=True)
+    assert done.returncode == 0 and json.loads(exported.read_text()) == json.loads(notebook.read_text())
+
+
 def test_ground_truth_first_audit_lists_every_violation(tmp_path):
     import json
     import subprocess
