@@ -1,7 +1,8 @@
 """Training entry point: config -> data/model/strategy -> Trainer -> TrainingRunner.
 
 Flags and emitted events (``init``, ``parallel_ready``, ``resume``, ``train``, ``checkpoint``)
-follow the reference entry point (scripts/train.py:57-281).  Launch one process per GPU with
+follow the reference entry point (scripts/train.py:57-281); ``ops_dispatch`` (native vs fallback calls per operator, at the
+end of a run with the native back end) is an addition.  Launch one process per GPU with
 ``torchrun --standalone --nproc_per_node N scripts/train.py --config ... --model-config ...``.
 """
 
@@ -132,6 +133,10 @@ def main(argv=None) -> None:
 
         TrainingRunner(cfg=cfg, trainer=trainer, dataloader=dataloader, strategy=strategy, logger=logger,
                        device=device, world_size=world_size).run(max_steps=max_steps, resume_path=resume_path)
+        if hasattr(ops, "dispatch_summary"):
+            # how often each operator ran natively and how often it fell back to the PyTorch implementation (eager calls;
+            # steps replayed from a CUDA graph repeat the captured step's choices)
+            logger.log_event({"event": "ops_dispatch", "step": trainer.state.step, "calls": ops.dispatch_summary()})
     finally:
         logger.close()
         strategy.teardown()
