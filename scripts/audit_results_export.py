@@ -4,13 +4,16 @@
 Checks: (1) each ``summary.json`` of the distributed harness lists only rows whose raw file exists and carries the same
 identity hash; (2) every successful row was device-timed with at least three warm-up steps; (3) weak-scaling
 efficiencies recompute from the rows; (4) operator caches contain no row without a parity verdict for a non-library
-provider.  Same role as the reference's ``scripts/audit_results_export.py``.
+provider; (5) text files that name a path of the machine they were made on (a home directory, a scratch mount) are listed
+as ``non_portable``: a warning, or a failure with ``--strict-paths``.  Same role as the reference's
+``scripts/audit_results_export.py``.
 """
 
 from __future__ import annotations
 
 import argparse
 import json
+import re
 import sys
 from pathlib import Path
 
@@ -53,12 +56,39 @@ def audit(root: Path) -> list[str]:
     return problems
 
 
+_TEXT_SUFFIXES = {".json", ".jsonl", ".md", ".csv", ".txt", ".svg", ".env", ".yaml", ".yml"}
+_MACHINE_PATH = re.compile(r"""(?:(?<![\w.:/-])/(?:home|root|Users|mnt|data|scratch|tmp)/[\w.@+-]+|[A-Za-z]:\\+Users\\+[\w.@+-]+)""")
+
+
+def non_portable_paths(root: Path, *, limit_per_file: int = 3) -> list[str]:
+    """``file: match`` for every text file under ``root`` that names a path of the machine it was made on."""
+
+    found = []
+    for path in sorted(p for p in root.rglob("*") if p.is_file() and p.suffix.lower() in _TEXT_SUFFIXES):
+        try:
+            text = path.read_text(encoding="utf-8")
+        except (OSError, UnicodeDecodeError):
+            continue
+        seen = []
+        for match in _MACHINE_PATH.finditer(text):
+            if match.group(0) not in seen:
+                seen.append(match.group(0))
+            if len(seen) == limit_per_file:
+                break
+        found += [f"{path.relative_to(root)}: {m}" for m in seen]
+    return found
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("root")
+    ap.add_argument("--strict-paths", action="store_true", help="machine paths inside exported text files fail the audit")
     args = ap.parse_args(argv)
     problems = audit(Path(args.root))
-    print(json.dumps({"ok": not problems, "problems": problems}, indent=1))
+    stray = non_portable_paths(Path(args.root))
+    if args.strict_paths:
+        problems += [f"machine path in {item}" for item in stray]
+    print(json.dumps({"ok": not problems, "problems": problems, "non_portable": stray}, indent=1))
     return 0 if not problems else 1
 
 

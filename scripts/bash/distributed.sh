@@ -8,12 +8,13 @@ CONFIG="${CONFIG:-configs/server/b200_180gb/runs/${STRATEGY}_${NPROC}gpu.yaml}"
 MODEL_CONFIG="${MODEL_CONFIG:-configs/synbios_moe/model.yaml}"
 cd "$REPO_ROOT"
 RESUME=()
-RUN_NAME="$("$PYTHON" - "$CONFIG" <<'PY'
+RUN_DIR="$("$PYTHON" - "$CONFIG" <<'PY'
 import sys
 sys.path.insert(0, ".")
 from mini_train_sys_b200.runtime.config import load_yaml_dict
-print(load_yaml_dict(sys.argv[1]).get("run", {}).get("name", "run"))
+cfg = load_yaml_dict(sys.argv[1])
+print((cfg.get("checkpoint") or {}).get("directory", "checkpoints") + "/" + (cfg.get("run") or {}).get("name", "run"))
 PY
 )"
-if compgen -G "checkpoints/${RUN_NAME}/epoch_*" > /dev/null; then RESUME=(--resume latest); fi
+if compgen -G "${RUN_DIR}/epoch_*" > /dev/null; then RESUME=(--resume latest); fi
 torchrun_local "$NPROC" scripts/train.py --config "$CONFIG" --model-config "$MODEL_CONFIG" "${RESUME[@]}" "$@"

@@ -54,9 +54,16 @@ def main(argv=None) -> int:
     ap.add_argument("--output", default=None)
     args = ap.parse_args(argv)
     root = Path(args.root)
-    entries = [e for p in sorted(root.rglob("*")) if p.is_file() and p.name != "CATALOG.json" for e in [describe(p)] if e]
+    entries = [e for p in sorted(root.rglob("*")) if p.is_file() and p.name not in ("CATALOG.json", "CATALOG.md") for e in [describe(p)] if e]
+    for entry in entries:      # the catalogue travels with the tree: paths are relative to it, and the root is named, not located
+        entry["path"] = Path(entry["path"]).relative_to(root).as_posix()
     out = Path(args.output) if args.output else root / "CATALOG.json"
-    out.write_text(json.dumps({"root": str(root), "entries": entries}, indent=1))
+    out.write_text(json.dumps({"root": root.name, "entries": entries}, indent=1))
+    lines = ["| path | kind | bytes | figures |", "|---|---|---|---|"]
+    for e in entries:
+        figures = ", ".join(f"{k}={v}" for k, v in e.items() if k not in ("path", "kind", "bytes") and v is not None)
+        lines.append(f"| `{e['path']}` | {e['kind']} | {e['bytes']} | {figures} |")
+    out.with_suffix(".md").write_text("\n".join(lines) + "\n")
     kinds: dict[str, int] = {}
     for e in entries:
         kinds[e["kind"]] = kinds.get(e["kind"], 0) + 1

@@ -145,6 +145,12 @@ def test_evidence_tooling_roundtrip(tmp_path):
     out = run(str(ROOT / "scripts" / "build_results_catalog.py"), str(tree))
     assert out.returncode == 0 and json.loads(out.stdout)["kinds"] == {"distributed/weak": 1, "bench": 1, "json": 2}, out.stdout + out.stderr
     assert run(str(ROOT / "scripts" / "audit_results_export.py"), str(tree)).returncode == 0
+    # a path of the machine inside an exported file: a warning, a failure only when asked for; URLs and relative paths are fine
+    (tree / "note.md").write_text("config /home/someone/run.yaml, see https://example.org/home/page and results/operators/a.json\n")
+    lenient = run(str(ROOT / "scripts" / "audit_results_export.py"), str(tree))
+    assert lenient.returncode == 0 and json.loads(lenient.stdout)["non_portable"] == ["note.md: /home/someone"]
+    assert run(str(ROOT / "scripts" / "audit_results_export.py"), str(tree), "--strict-paths").returncode == 1
+    (tree / "note.md").unlink()
     assert run(str(ROOT / "scripts" / "build_results_manifest.py"), str(tree)).returncode == 0
     assert run(str(ROOT / "scripts" / "build_results_manifest.py"), str(tree), "--check").returncode == 0
     (tree / "bench.json").write_text("{}")
