@@ -1,8 +1,11 @@
-"""Text codecs of the study: GPT-2 byte-level BPE (the formal setting) and a plain UTF-8 byte codec.
+"""Text codecs of the study: GPT-2 byte-level BPE (the formal setting), a byte-level BPE trained on the corpus itself,
+and a plain UTF-8 byte codec.
 
-Both expose the byte length of every token, which is what aligns character spans of attribute values with token
+All expose the byte length of every token, which is what aligns character spans of attribute values with token
 positions (reference: experiments/synbios_moe/probes/model.py:41-75).  The byte codec needs no vocabulary file, so
-the whole pipeline can be exercised on a machine without the GPT-2 tables.
+the whole pipeline can be exercised on a machine without the GPT-2 tables; ``bpe:<directory>`` names a tokenizer
+directory written by ``scripts/prepare_data.py train-tokenizer`` (or by ``synbios_moe.py prepare``, which trains one on the
+biographies when the directory does not exist yet): real multi-byte tokens with leading spaces, without a download.
 """
 
 from __future__ import annotations
@@ -45,12 +48,68 @@ class Gpt2Codec:
         return self.encoding.decode([t for t in tokens if t != self.eos])
 
 
+def byte_level_alphabet() -> dict[str, int]:
+    """Character -> byte of the byte-level BPE alphabet: printable bytes stand for themselves, the other 68 are shifted to
+    code points from 256 upwards, in byte order (the published GPT-2 convention, which the ``tokenizers`` ByteLevel
+    pre-tokenizer follows)."""
+
+    keep = [*range(ord("!"), ord("~") + 1), *range(0xA1, 0xAC + 1), *range(0xAE, 0xFF + 1)]
+    table, shifted = {}, 0
+    for byte in range(256):
+        if byte in keep:
+            table[chr(byte)] = byte
+        else:
+            table[chr(256 + shifted)] = byte
+            shifted += 1
+    return table
+
+
+class BpeCodec:
+    """A byte-level BPE trained with this repository's data tools (``data/tokenizer.py:ByteLevelBPETokenizer``)."""
+
+    def __init__(self, directory: str) -> None:
+        from mini_train_sys_b200.data.tokenizer import ByteLevelBPETokenizer
+
+        self.directory = str(directory)
+        self.name = f"bpe:{self.directory}"
+        self.tokenizer = ByteLevelBPETokenizer.load(self.directory)
+        self.eos = self.tokenizer.boundary_token_id
+        self.vocab_size = self.tokenizer.vocab_size
+        self.fingerprint = self.tokenizer.fingerprint
+        alphabet = byte_level_alphabet()
+        backend = self.tokenizer._backend
+        self._num_bytes = []
+        for token in range(self.vocab_size):
+            text = backend.id_to_token(token)
+            # a special token (the boundary) is not made of alphabet characters and covers no text
+            self._num_bytes.append(0 if token == self.eos or text is None or any(ch not in alphabet for ch in text) else len(text))
+
+    def encode(self, text: str) -> list[int]:
+        return self.tokenizer.encode(text)
+
+    def token_num_bytes(self, token: int) -> int:
+        return self._num_bytes[token]
+
+    def decode(self, tokens) -> str:
+        return self.tokenizer.decode([int(t) for t in tokens if int(t) != self.eos])
+
+
+def codec_argument(value: str) -> str:
+    """``argparse`` type of ``--codec``: ``gpt2``, ``bytes`` or ``bpe:<tokenizer directory>``."""
+
+    if value in ("gpt2", "bytes") or (value.startswith("bpe:") and len(value) > 4):
+        return value
+    raise ValueError(f"unknown codec {value!r} (expected 'gpt2', 'bytes' or 'bpe:<tokenizer directory>')")
+
+
 def get_codec(name: str):
     if name == "bytes":
         return ByteCodec()
     if name == "gpt2":
         return Gpt2Codec()
-    raise ValueError(f"unknown codec {name!r} (expected 'gpt2' or 'bytes')")
+    if name.startswith("bpe:") and len(name) > 4:
+        return BpeCodec(name[4:])
+    raise ValueError(f"unknown codec {name!r} (expected 'gpt2', 'bytes' or 'bpe:<tokenizer directory>')")
 
 
 def positions_before_chars(codec, text: str, char_indices: list[int]) -> tuple[list[int], list[int]]:

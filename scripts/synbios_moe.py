@@ -45,6 +45,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parents[1]
 sys.path.insert(0, str(ROOT))
 
+from experiments.synbios_moe.codec import codec_argument  # noqa: E402
 from experiments.synbios_moe.pretraining.dataset import ATTRIBUTES, VARIANTS  # noqa: E402
 
 
@@ -109,6 +110,20 @@ def cmd_prepare(args) -> int:
         from mini_train_sys_b200.data.tokenizer import TiktokenTokenizer
 
         tokenizer = TiktokenTokenizer("gpt2")
+    elif args.codec.startswith("bpe:"):
+        # a byte-level BPE of the corpus itself: trained on the biographies just written when the directory is new, so
+        # that the study has real multi-byte tokens on a machine without the GPT-2 vocabulary
+        from experiments.synbios_moe.artifact_io import read_jsonl
+        from mini_train_sys_b200.data.tokenizer import ByteLevelBPETokenizer, TOKENIZER_METADATA_FILE
+
+        directory = Path(args.codec[4:])
+        if not (directory / TOKENIZER_METADATA_FILE).is_file():
+            trained = ByteLevelBPETokenizer.train_from_iterator((row["text"] for row in read_jsonl(out / "biographies.jsonl")),
+                                                                vocab_size=args.bpe_vocab_size, min_frequency=2)
+            trained.save(directory)
+            sink({"event": "tokenizer_trained", "path": str(directory), "vocab_size": trained.vocab_size,
+                  "fingerprint": trained.fingerprint})
+        tokenizer = ByteLevelBPETokenizer.load(directory)
     else:
         from experiments.synbios_moe.codec import ShardTokenizer, get_codec
 
@@ -538,7 +553,7 @@ def build_parser() -> argparse.ArgumentParser:
     sub = ap.add_subparsers(dest="command", required=True)
 
     def common(p, *, model=True, monitoring=True):
-        p.add_argument("--codec", choices=("gpt2", "bytes"), default="gpt2")
+        p.add_argument("--codec", type=codec_argument, default="gpt2", metavar="{gpt2,bytes,bpe:<tokenizer directory>}")
         if model:
             p.add_argument("--model-config", required=True)
             p.add_argument("--checkpoint", required=True, help="exported model.pt")
@@ -551,6 +566,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--output", required=True); p.add_argument("--variant", default="single", choices=VARIANTS)
     p.add_argument("--num-people", type=int, default=100_000); p.add_argument("--seed", type=int, default=1337)
     p.add_argument("--max-shard-tokens", type=int, default=10_000_000); p.set_defaults(func=cmd_prepare)
+    p.add_argument("--bpe-vocab-size", type=int, default=8192, help="with --codec bpe:<dir>, when <dir> holds no tokenizer yet: train one of this size")
 
     p = sub.add_parser("token-statistics"); common(p, model=False, monitoring=False)
     p.add_argument("--data", required=True); p.add_argument("--output", required=True)

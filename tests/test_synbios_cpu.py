@@ -299,6 +299,64 @@ def test_gpt2_alignment_when_the_vocabulary_is_available():
     assert codec.decode(tokens[pos + 1:pos + 2]).strip().startswith("Pr")
 
 
+def test_trained_bpe_codec_aligns_every_attribute_span_and_drives_the_study(tmp_path):
+    """``--codec bpe:<dir>``: a byte-level BPE trained on the biographies themselves.  Real merges, tokens with leading
+    spaces, values of several tokens: the alignment contract is checked on every attribute of every biography, and the
+    commands that consume a codec run with it."""
+
+    pytest.importorskip("tokenizers")
+    from experiments.synbios_moe.artifact_io import read_json, read_jsonl
+    from experiments.synbios_moe.codec import byte_level_alphabet, get_codec, positions_before_chars, token_span_of_chars
+    from experiments.synbios_moe.pretraining.dataset import ATTRIBUTES
+
+    alphabet = byte_level_alphabet()
+    assert len(alphabet) == 256 and sorted(alphabet.values()) == list(range(256)) and alphabet["A"] == 65 and alphabet["\u0120"] == 32
+
+    data, tok = tmp_path / "data", tmp_path / "tok"
+    run = lambda *a: subprocess.run([*CLI, *a], capture_output=True, text=True, timeout=600)   # noqa: E731
+    out = run("prepare", "--output", str(data), "--variant", "multi2+permute", "--num-people", "60", "--codec", f"bpe:{tok}",
+              "--bpe-vocab-size", "700", "--quiet")
+    assert out.returncode == 0, out.stderr[-2000:]
+    codec = get_codec(f"bpe:{tok}")
+    assert codec.vocab_size == 700 and codec.token_num_bytes(codec.eos) == 0
+    shard_manifest = read_json(data / "token_shards" / "manifest.json")
+    assert shard_manifest["tokenizer_fingerprint"] == codec.fingerprint and shard_manifest["vocab_size"] == 700
+    multi_token_values = 0
+    for bio in read_jsonl(data / "biographies.jsonl"):
+        text = bio["text"]
+        ids = codec.encode(text)
+        assert sum(codec.token_num_bytes(t) for t in ids) == len(text.encode("utf-8")) and codec.decode(ids) == text
+        assert len(ids) < 0.6 * len(text)                                  # merges happened: this is not the byte codec
+        for attribute in ATTRIBUTES:
+            lo_c, hi_c = bio["attribute_spans"][attribute]
+            value = text[lo_c:hi_c]
+            tokens, lo, hi = token_span_of_chars(codec, text, lo_c, hi_c)
+            covered = codec.decode(tokens[lo:hi])
+            assert value in covered and codec.decode(tokens[1:lo]) + covered + codec.decode(tokens[hi:]) == text
+            # minimal cover: dropping the first or the last token of the range loses part of the value
+            assert value not in codec.decode(tokens[lo + 1:hi]) and value not in codec.decode(tokens[lo:hi - 1])
+            multi_token_values += hi - lo > 1
+            _, (pos,) = positions_before_chars(codec, text, [lo_c])
+            before = codec.decode(tokens[1:pos + 1])
+            assert text.startswith(before) and len(before) <= lo_c          # the read-out has seen nothing of the value
+            assert len(codec.decode(tokens[1:pos + 2])) > lo_c              # ... and the very next token reaches into it
+            assert pos + 1 == lo or covered.startswith(" ")                 # the value's first token may carry the space before it
+    assert multi_token_values > 100
+    # a second prepare with the same directory reuses the tokenizer instead of training another
+    before = (tok / "tokenizer.json").read_bytes()
+    assert run("prepare", "--output", str(tmp_path / "again"), "--variant", "single", "--num-people", "10", "--codec", f"bpe:{tok}",
+               "--quiet").returncode == 0 and (tok / "tokenizer.json").read_bytes() == before
+    out = run("cache-probes", "--data", str(data), "--output", str(tmp_path / "cache"), "--codec", f"bpe:{tok}")
+    assert out.returncode == 0, out.stderr[-2000:]
+    check = run("validate-probe-cache", "--probe-cache", str(tmp_path / "cache"), "--data", str(data))
+    assert check.returncode == 0 and json.loads(check.stdout)["ok"], check.stdout + check.stderr[-1000:]
+    manifest = read_json(tmp_path / "cache" / "manifest.json")
+    assert manifest["codec"] == f"bpe:{tok}" and manifest["vocab_size"] == 700
+    stats = run("token-statistics", "--data", str(data), "--output", str(tmp_path / "stats.json"), "--codec", f"bpe:{tok}")
+    assert stats.returncode == 0, stats.stderr[-2000:]
+    assert run("token-statistics", "--data", str(data), "--output", str(tmp_path / "x.json"), "--codec", "wordpiece").returncode != 0
+
+
 def test_character_similarity_and_progressive_cloze_with_an_oracle_model(tmp_path):
     """A stand-in model that always continues with the source text reproduces every field: the progressive protocol must then
     score 6 / 6 per biography, terminate every field at the source's full stop and rebuild the original text."""
