@@ -73,8 +73,10 @@ class FSDPStrategy(ProcessGroupMixin):
             missing.append("cpu_offload")
         if sharding_strategy not in ("full_shard", "shard_grad_op"):
             missing.append(f"sharding_strategy={sharding_strategy}")
-        if precision == "fp16":
-            missing.append("precision=fp16 (loss scaling)")
+        from mini_train_sys_b200.train.precision import precision_supports_fused_engine
+
+        if not precision_supports_fused_engine(precision):
+            missing.append(f"precision={precision} (loss scaling)")
         return missing
 
     @classmethod

@@ -244,6 +244,7 @@ class DataConfig:
     pin_memory: bool = True
     persistent_workers: bool = True
     drop_last: bool = True
+    device_prefetch: bool = False        # copy the next batch to the device on a side stream while the current step runs
 
     def __post_init__(self) -> None:
         _require(self.source in ("random", "tokens", "token_shards"),

@@ -194,7 +194,12 @@ class TrainingRunner:
             if hasattr(sampler, "set_epoch"):
                 sampler.set_epoch(epoch)   # every rank must see the same epoch number
             n_batches = len(self.dataloader)
-            stream = iter(self.dataloader)
+            source = self.dataloader
+            if self.cfg.data.device_prefetch:
+                from mini_train_sys_b200.data.dataloader import DevicePrefetcher
+
+                source = DevicePrefetcher(self.dataloader, self.device)     # a pass-through on a CPU device
+            stream = iter(source)
             finished_epoch = True
             for batch_index in range(1, n_batches + 1):
                 t_wait = time.perf_counter()

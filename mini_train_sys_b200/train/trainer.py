@@ -52,7 +52,7 @@ class Trainer:
         self.last_grad_norm: float | None = None
         self.last_grad_clip_coefficient = 1.0
         self.last_grad_was_clipped = False
-        if self.precision.grad_scaling_enabled and getattr(optimizer, "owns_clipping", False):
+        if not self.precision.fused_engine and getattr(optimizer, "owns_clipping", False):
             raise ValueError("precision=fp16 needs loss scaling, which an optimizer that clips inside its update kernel (the fused "
                              "sharding engine) does not implement: use bf16, or parallel.comm.engine=nccl")
         self.grad_scaler = torch.amp.GradScaler(device.type, enabled=self.precision.grad_scaling_enabled)

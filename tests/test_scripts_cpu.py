@@ -40,6 +40,26 @@ def test_debug_moe_run_reproduces_the_reference_loss_curve(tmp_path):
     assert len(train[0]["moe/expert_load_fraction_by_layer"]) == 2 and len(train[0]["moe/expert_load_fraction_by_layer"][0]) == 4
 
 
+def test_device_prefetch_option_feeds_the_same_batches(tmp_path):
+    """``data.device_prefetch`` routes the loader through the side-stream prefetcher (a pass-through on a CPU): same batches,
+    same order, same number of steps."""
+
+    losses = {}
+    for flag in (False, True):
+        cfg = yaml.safe_load((ROOT / "configs" / "train_debug.yaml").read_text())
+        cfg["run"]["name"] = f"prefetch_{flag}"
+        cfg["train"].update(max_steps=6, log_interval=1)
+        cfg["data"]["device_prefetch"] = flag
+        cfg["logging"]["tensorboard"] = False
+        work = tmp_path / str(flag)
+        work.mkdir()
+        (work / "run.yaml").write_text(yaml.safe_dump(cfg))
+        run([str(ROOT / "scripts" / "train.py"), "--config", "run.yaml", "--model-config", str(ROOT / "configs" / "model_debug_dense.yaml"),
+             "--device", "cpu"], work)
+        losses[flag] = [e["loss"] for e in events(work) if e["event"] == "train"]
+    assert len(losses[True]) == 6 and losses[True] == losses[False]
+
+
 @pytest.fixture()
 def run_cfg(tmp_path):
     cfg = yaml.safe_load((ROOT / "configs" / "train_debug.yaml").read_text())
@@ -136,12 +156,12 @@ def test_committed_notebooks_equal_their_percent_format_sources_and_run(tmp_path
     spec.loader.exec_module(runner)
     cells = runner.percent_cells("#!/usr/bin/env python\n# %% [markdown]\n# # Title\n#\n# text\n\n# %%\nx = 1\n\n\n# %% named\nprint(x)\n")
     assert cells == [("markdown", "# Title\n\ntext"), ("code", "x = 1"), ("code", "print(x)")]
-    for name in ("training_walkthrough", "synbios_moe_walkthrough"):
+    for name in ("training_walkthrough", "synbios_moe_walkthrough", "operator_benchmark_walkthrough", "distributed_benchmark_walkthrough"):
         source = root / "examples" / f"{name}.py"
         committed = json.loads((root / "examples" / "notebooks" / f"{name}.ipynb").read_text(encoding="utf-8"))
         assert committed == runner.notebook_from_script(source.read_text(encoding="utf-8")), f"regenerate {name}.ipynb with --export-ipynb"
         kinds = [c["cell_type"] for c in committed["cells"]]
-        assert kinds[0] == "markdown" and kinds.count("code") >= 5 and all(c["outputs"] == [] for c in committed["cells"] if c["cell_type"] == "code")
+        assert kinds[0] == "markdown" and kinds.count("code") >= 4 and all(c["outputs"] == [] for c in committed["cells"] if c["cell_type"] == "code")
     notebook = root / "examples" / "notebooks" / "training_walkthrough.ipynb"
     done = subprocess.run([sys.executable, str(root / "scripts" / "run_server_notebook.py"), str(notebook), "--output", str(tmp_path / "run.json"),
                            "--executed-notebook", str(tmp_path / "executed.ipynb"), "--quiet"], capture_output=True, text=True, cwd=tmp_path)
