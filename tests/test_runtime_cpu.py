@@ -229,3 +229,92 @@ def test_bounds_checking_profile_compiles_the_kernels_that_use_it(tmp_path):
                                "-DMTS_DEBUG_BOUNDS", "-I", str(CSRC), "-c", str(src), "-o", str(tmp_path / (src.stem + ".o"))],
                               capture_output=True, text=True, timeout=600)
         assert done.returncode == 0, done.stderr[-2000:]
+
+
+# ---- memory plan --------------------------------------------------------------------------------------------------------
+def _model_from(path: str) -> ModelConfig:
+    import yaml
+
+    return ModelConfig(**yaml.safe_load((ROOT / path).read_text())["model"])
+
+
+def test_memory_plan_static_part_equals_the_engine_buffers():
+    """The resident part of the plan against a real engine: every buffer the flat engine allocates for a model, summed."""
+
+    from mini_train_sys_b200.models import MiniTransformer, get_ops_backend
+    from mini_train_sys_b200.parallel.flat_engine import FlatDataParallel
+    from mini_train_sys_b200.runtime.memory_plan import plan_memory
+
+    for kind in ("dense", "moe"):
+        cfg = ModelConfig(vocab_size=1000, seq_len=32, n_layers=3, n_heads=4, hidden_size=128, intermediate_size=256, ffn_type=kind,
+                          num_experts=4, experts_per_token=2, tie_word_embeddings=(kind == "moe"))
+        torch.manual_seed(0)
+        engine = FlatDataParallel(MiniTransformer(cfg, get_ops_backend("torch")), mode="shard")
+        held = 0
+        for unit in engine.units:
+            tensors = [unit.master, unit.exp_avg, unit.exp_avg_sq, unit.grad_shard, unit.grad_full.tensor, unit.low_shard.tensor]
+            if unit.gathered is not None:
+                tensors.append(unit.gathered.tensor)
+            held += sum(t.numel() * t.element_size() for t in tensors)
+        # on a CPU the engine keeps its "low precision" buffers in fp32: plan with 4-byte weights
+        plan = plan_memory(cfg, strategy="single", low_bytes=4)
+        assert plan.static_bytes() == 28 * cfg.param_count()                       # 16 + 4 + 4 + 4 bytes per parameter
+        padding = len(engine.units) * 64 * 28                                      # units are padded to a multiple of 64 elements
+        assert plan.static_bytes() <= held <= plan.static_bytes() + padding, (kind, held, plan.static_bytes())
+
+
+def test_memory_plan_reproduces_the_measured_peaks():
+    """``max_memory_allocated`` (GiB) of benchmark runs of this repository on B200: model, strategy, ranks, sharding, local batch."""
+
+    from mini_train_sys_b200.runtime.memory_plan import GIB, plan_memory
+
+    moe293, dense125, moe125 = (_model_from(p) for p in ("configs/synbios_moe/model.yaml", "configs/model_125m_dense.yaml",
+                                                         "configs/model_125m_moe.yaml"))
+    measured = [
+        (moe293, "single", 1, "full_shard", 96, 30.51), (moe293, "single", 1, "full_shard", 24, 12.88),
+        (moe293, "fsdp", 2, "full_shard", 96, 26.23), (moe293, "fsdp", 2, "full_shard", 24, 8.61), (moe293, "fsdp", 2, "shard_grad_op", 96, 26.08),
+        (moe293, "fsdp", 4, "full_shard", 96, 25.14), (moe293, "fsdp", 4, "full_shard", 24, 7.52),
+        (moe293, "fsdp", 8, "full_shard", 96, 24.59), (moe293, "fsdp", 8, "full_shard", 24, 6.96),
+        (dense125, "ddp", 2, "full_shard", 32, 15.82), (dense125, "ddp", 4, "full_shard", 32, 15.20), (dense125, "ddp", 8, "full_shard", 32, 14.91),
+        (moe125, "fsdp", 2, "full_shard", 16, 13.95), (moe125, "fsdp", 4, "full_shard", 16, 12.22),
+        (moe125, "ep", 2, "full_shard", 16, 21.63), (moe125, "ep", 4, "full_shard", 16, 18.82),
+    ]
+    for model, strategy, world, sharding, batch, gib in measured:
+        plan = plan_memory(model, strategy=strategy, world_size=world, sharding=sharding, local_batch_hint=batch)
+        predicted = plan.total_bytes(batch, allocator_only=True) / GIB
+        assert predicted == pytest.approx(gib, rel=0.03), (strategy, world, sharding, batch, predicted, gib)
+        # what the allocator does not see: nothing on one rank, the symmetric buffers otherwise
+        hidden = plan.total_bytes(batch) - plan.total_bytes(batch, allocator_only=True)
+        assert (hidden == 0) == (world == 1) and hidden <= 7 * model.param_count() + plan.static.get("expert_exchange_regions", 0)
+
+
+def test_memory_plan_orderings_limits_and_cli(tmp_path):
+    import subprocess
+    import sys
+
+    from mini_train_sys_b200.runtime.memory_plan import GIB, plan_memory
+
+    model = _model_from("configs/synbios_moe/model.yaml")
+    full, grad_op = (plan_memory(model, strategy="fsdp", world_size=8, sharding=s) for s in ("full_shard", "shard_grad_op"))
+    assert full.static_bytes() < grad_op.static_bytes() < plan_memory(model).static_bytes()
+    assert plan_memory(model, activation_checkpointing=True).activation_bytes(1) < 0.5 * plan_memory(model).activation_bytes(1)
+    best = full.max_local_batch(180 * GIB)
+    assert 500 < best < 800 and full.total_bytes(best) <= 0.9 * 180 * GIB < full.total_bytes(best + 1)
+    assert full.max_local_batch(1 * GIB) == 0
+    # a model whose full-size fp32 gradient buffer alone exceeds the device: the plan says so instead of returning a batch
+    huge = ModelConfig(vocab_size=128000, seq_len=4096, n_layers=80, n_heads=64, hidden_size=8192, intermediate_size=28672)
+    plan = plan_memory(huge, strategy="fsdp", world_size=8)
+    assert plan.max_local_batch(180 * GIB) == 0 and any("gradient buffer" in n for n in plan.notes)
+    with pytest.raises(ValueError):
+        plan_memory(model, strategy="ep", world_size=3)
+    with pytest.raises(ValueError):
+        plan_memory(_model_from("configs/model_125m_dense.yaml"), strategy="ep", world_size=2)
+    done = subprocess.run([sys.executable, str(ROOT / "scripts" / "plan_memory.py"), "--config",
+                           str(ROOT / "configs" / "server" / "b200_180gb" / "runs" / "fsdp_8gpu.yaml"), "--model-config",
+                           str(ROOT / "configs" / "synbios_moe" / "model.yaml")], capture_output=True, text=True, timeout=120)
+    report = json.loads(done.stdout)
+    assert done.returncode == 0 and report["fits"] and report["world_size"] == 8 and report["local_batch"] == 96
+    assert report["max_memory_allocated_gib"] == pytest.approx(24.59, rel=0.03) and report["max_local_batch"] == best
+    tight = subprocess.run([sys.executable, str(ROOT / "scripts" / "plan_memory.py"), "--model-config", str(ROOT / "configs" / "synbios_moe" / "model.yaml"),
+                            "--local-batch", "96", "--device-gb", "24"], capture_output=True, text=True, timeout=120)
+    assert tight.returncode == 1 and not json.loads(tight.stdout)["fits"]
