@@ -31,6 +31,45 @@ def _capture(cmd: list[str]) -> tuple[int, str]:
     return done.returncode, (done.stdout.strip() or done.stderr.strip())
 
 
+def parse_nvlink_status(text: str) -> dict[int, dict[str, float]]:
+    """``nvidia-smi nvlink --status`` -> per GPU: active links, inactive links, and the summed per-direction rate in GB/s.
+
+    The listing has one ``GPU <n>: <name> (UUID: ...)`` line per device followed by ``Link <k>: <rate> GB/s`` or
+    ``Link <k>: <inactive>`` lines; anything else is ignored.
+    """
+
+    import re
+
+    status: dict[int, dict[str, float]] = {}
+    current = None
+    for line in text.splitlines():
+        head = re.match(r"\s*GPU\s+(\d+)\s*:", line)
+        if head:
+            current = status.setdefault(int(head.group(1)), {"active_links": 0, "inactive_links": 0, "gbs_per_direction": 0.0})
+            continue
+        link = re.match(r"\s*Link\s+\d+\s*:\s*(.+)$", line)
+        if link is None or current is None:
+            continue
+        rate = re.match(r"([0-9.]+)\s*GB/s", link.group(1).strip())
+        if rate:
+            current["active_links"] += 1
+            current["gbs_per_direction"] = round(current["gbs_per_direction"] + float(rate.group(1)), 3)
+        else:
+            current["inactive_links"] += 1
+    return status
+
+
+def nvlink_findings(status: dict[int, dict[str, float]], *, expected_links: int = 18) -> list[str]:
+    """Warnings for GPUs whose NVLink fabric is not whole (a B200 has 18 links; fewer active ones cost peer bandwidth)."""
+
+    found = []
+    for gpu, info in sorted(status.items()):
+        if info["inactive_links"] or 0 < info["active_links"] < expected_links:
+            found.append(f"GPU {gpu}: {int(info['active_links'])} of {expected_links} NVLink links active "
+                         f"({int(info['inactive_links'])} reported inactive)")
+    return found
+
+
 def find_checkout(start: str | Path | None = None) -> Path | None:
     here = Path(start or Path.cwd()).resolve()
     for cand in (here, *here.parents):
@@ -86,6 +125,12 @@ def collect_server_status(*, expected_gpus: int, min_free_disk_gb: float, requir
     rc_t, topo = _capture(["nvidia-smi", "topo", "-m"])
     if rc_l != 0:
         warnings.append("nvidia-smi -L failed")
+    nvlink: dict[int, dict[str, float]] = {}
+    if n_gpu > 1:
+        rc_n, listing = _capture(["nvidia-smi", "nvlink", "--status"])          # a read-only query
+        if rc_n == 0:
+            nvlink = parse_nvlink_status(listing)
+            warnings.extend(nvlink_findings(nvlink))
     nvcc = shutil.which("nvcc") or ("/usr/local/cuda/bin/nvcc" if Path("/usr/local/cuda/bin/nvcc").exists() else None)
     if nvcc is None and require_nvcc:
         errors.append("nvcc not found (needed to build the sm_100a extension)")
@@ -108,7 +153,7 @@ def collect_server_status(*, expected_gpus: int, min_free_disk_gb: float, requir
     return {"ok": not errors, "errors": errors, "warnings": warnings, "modules": modules, "python": sys.version.split()[0],
             "torch": torch.__version__, "cuda_runtime": torch.version.cuda, "gpu_count": n_gpu, "devices": devices,
             "peer_access_all_pairs": peer_ok, "nccl": nccl, "nvidia_smi": smi_list if rc_l == 0 else None,
-            "topology": topo if rc_t == 0 else None, "nvcc": nvcc, "extension_built": EXT_PATH.exists(),
+            "topology": topo if rc_t == 0 else None, "nvlink": {str(k): v for k, v in nvlink.items()}, "nvcc": nvcc, "extension_built": EXT_PATH.exists(),
             "checkout": str(checkout) if checkout else None, "storage_root": str(root), "free_disk_gb": round(free_gb, 1),
             "shm_free_gb": round(shm_gb, 1)}
 

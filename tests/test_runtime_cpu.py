@@ -318,3 +318,22 @@ def test_memory_plan_orderings_limits_and_cli(tmp_path):
     tight = subprocess.run([sys.executable, str(ROOT / "scripts" / "plan_memory.py"), "--model-config", str(ROOT / "configs" / "synbios_moe" / "model.yaml"),
                             "--local-batch", "96", "--device-gb", "24"], capture_output=True, text=True, timeout=120)
     assert tight.returncode == 1 and not json.loads(tight.stdout)["fits"]
+
+
+# ---- server preflight -----------------------------------------------------------------------------------------------------
+def test_server_check_reports_errors_on_a_machine_without_gpus_and_reads_nvlink_listings():
+    from mini_train_sys_b200.runtime.server_check import collect_server_status, nvlink_findings, parse_nvlink_status
+
+    listing = "\n".join(["GPU 0: NVIDIA B200 (UUID: GPU-00000000-0000-0000-0000-000000000000)",
+                         *[f"\t Link {k}: 53.125 GB/s" for k in range(18)],
+                         "GPU 1: NVIDIA B200 (UUID: GPU-11111111-1111-1111-1111-111111111111)",
+                         *[f"\t Link {k}: 53.125 GB/s" for k in range(16)], "\t Link 16: <inactive>", "\t Link 17: <inactive>", "unrelated line"])
+    status = parse_nvlink_status(listing)
+    assert status[0] == {"active_links": 18, "inactive_links": 0, "gbs_per_direction": pytest.approx(956.25)}
+    assert status[1]["active_links"] == 16 and status[1]["inactive_links"] == 2
+    assert nvlink_findings(status) == ["GPU 1: 16 of 18 NVLink links active (2 reported inactive)"]
+    assert parse_nvlink_status("") == {} and nvlink_findings({}) == []
+    if not torch.cuda.is_available():
+        report = collect_server_status(expected_gpus=1, min_free_disk_gb=0.0, require_nvcc=False)
+        assert not report["ok"] and "CUDA is not available" in report["errors"] and report["gpu_count"] == 0 and report["nvlink"] == {}
+        assert report["checkout"] is not None and isinstance(report["extension_built"], bool)

@@ -176,6 +176,21 @@ def test_committed_notebooks_equal_their_percent_format_sources_and_run(tmp_path
     assert done.returncode == 0 and json.loads(exported.read_text()) == json.loads(notebook.read_text())
 
 
+def test_operator_benchmark_walkthrough_runs_cell_by_cell_on_a_cpu(tmp_path):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    done = subprocess.run([sys.executable, str(root / "scripts" / "run_server_notebook.py"), str(root / "examples" / "operator_benchmark_walkthrough.py"),
+                           "--output", str(tmp_path / "run.json"), "--quiet"], capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0, done.stderr[-2000:]
+    record = json.loads((tmp_path / "run.json").read_text())
+    assert record["failed_cells"] == [] and "walkthrough ok" in record["records"][-1]["stdout"]
+    assert any("quality_gate_passed" in r["stdout"] for r in record["records"])
+
+
 def test_ground_truth_first_audit_lists_every_violation(tmp_path):
     import json
     import subprocess
