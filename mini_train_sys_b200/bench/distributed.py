@@ -226,6 +226,39 @@ class BenchmarkSettings:
     env: dict[str, str] = field(default_factory=dict)
 
 
+def planned_batch_ladder(config: str, model_config: str | None, *, strategies: tuple[str, ...], world_sizes: tuple[int, ...],
+                         device_gib: float = 180.0, headroom: float = 0.9, fractions: tuple[float, ...] = (0.125, 0.25, 0.5, 0.75, 0.9, 1.0)
+                         ) -> tuple[int, ...]:
+    """Batch sizes for a capacity sweep from the memory plan instead of a guess: fractions of the largest local batch that the
+    plan admits for EVERY (strategy, world size) of the sweep, rounded down to multiples of 8 (at least 1), ascending, unique.
+    The last rung is the planned maximum itself, so that the sweep brackets the limit from below."""
+
+    from mini_train_sys_b200.models.config import ModelConfig
+    from mini_train_sys_b200.runtime.config import load_yaml_dict
+    from mini_train_sys_b200.runtime.memory_plan import GIB, plan_memory
+
+    payload = load_yaml_dict(config)
+    model_payload = (load_yaml_dict(model_config).get("model") if model_config else None) or payload.get("model")
+    if not model_payload:
+        raise ValueError("the batch ladder needs a model: give --model-config or a config that embeds `model:`")
+    model = ModelConfig(**model_payload)
+    sharding = ((payload.get("parallel") or {}).get("fsdp") or {}).get("sharding_strategy", "full_shard")
+    sharding = sharding if sharding in ("full_shard", "shard_grad_op") else "full_shard"
+    limits = []
+    for strategy in strategies:
+        for world in world_sizes:
+            kind = "single" if world == 1 and strategy != "ep" else strategy
+            if kind == "ep" and (not model.is_moe or model.num_experts % world):
+                continue
+            plan = plan_memory(model, strategy=kind, world_size=world, sharding=sharding, local_batch_hint=64)
+            limits.append(plan.max_local_batch(device_gib * GIB, headroom=headroom))
+    if not limits or min(limits) < 1:
+        raise ValueError("the memory plan admits no batch for this sweep")
+    top = min(limits)
+    rungs = sorted({max(1, int(top * f) // 8 * 8 if top * f >= 8 else int(top * f)) for f in fractions})
+    return tuple(rungs)
+
+
 def case_identity(settings: BenchmarkSettings, *, strategy: str, world: int, ops: str, engine: str, batch: int, repeat: int,
                   fingerprint: str) -> str:
     from mini_train_sys_b200.runtime.config import load_yaml_dict

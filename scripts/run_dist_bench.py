@@ -29,6 +29,12 @@ def _ints(text: str) -> tuple[int, ...]:
     return tuple(int(t) for t in text.split(",") if t)
 
 
+def _batches(text: str):
+    """``--batch-sizes``: a comma-separated list, or ``auto`` (a ladder derived from the memory plan of the sweep's model)."""
+
+    return "auto" if text.strip() == "auto" else _ints(text)
+
+
 def _strs(text: str) -> tuple[str, ...]:
     return tuple(t for t in text.split(",") if t)
 
@@ -57,7 +63,9 @@ def _parser() -> argparse.ArgumentParser:
     r.add_argument("--world-sizes", type=_ints, default=(1, 2, 4, 8))
     r.add_argument("--ops-backends", type=_strs, default=("native",))
     r.add_argument("--engines", type=_strs, default=("fused",))
-    r.add_argument("--batch-sizes", type=_ints, default=(96,))
+    r.add_argument("--batch-sizes", type=_batches, default=(96,), help="comma-separated local batch sizes, or `auto`: fractions of "
+                   "the largest batch the memory plan admits for every case of the sweep (see docs/memory_planning.md)")
+    r.add_argument("--device-gb", type=float, default=180.0, help="device memory in GiB for `--batch-sizes auto`")
     r.add_argument("--repeats", type=int, default=2)
     r.add_argument("--warmup-steps", type=int, default=5)
     r.add_argument("--measure-steps", type=int, default=20)
@@ -97,6 +105,10 @@ def main(argv=None) -> int:
         print(json.dumps(result, indent=1))
         return 0 if result["passed"] else 1
     if args.command == "run":
+        if args.batch_sizes == "auto":
+            args.batch_sizes = db.planned_batch_ladder(args.config, args.model_config, strategies=args.strategies,
+                                                       world_sizes=args.world_sizes, device_gib=args.device_gb)
+            print(json.dumps({"planned_batch_sizes": list(args.batch_sizes)}), flush=True)
         settings = db.BenchmarkSettings(
             config=args.config, model_config=args.model_config, output_dir=args.output_dir, strategies=args.strategies,
             world_sizes=args.world_sizes, ops_backends=args.ops_backends, engines=args.engines, batch_sizes=args.batch_sizes,

@@ -190,3 +190,23 @@ def test_operator_plots_are_well_formed_and_complete(tmp_path):
                          capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr[-2000:]
     assert (tmp_path / "p2" / "swiglu.svg").is_file() and '"plots": ["swiglu.svg"]' in out.stdout
+
+
+def test_capacity_ladder_comes_from_the_memory_plan():
+    from mini_train_sys_b200.bench.distributed import planned_batch_ladder
+
+    config = str(ROOT / "configs" / "bench" / "synbios_moe_fsdp.yaml")
+    ladder = planned_batch_ladder(config, None, strategies=("fsdp",), world_sizes=(1, 8))
+    assert ladder == tuple(sorted(set(ladder))) and len(ladder) >= 5 and all(b % 8 == 0 for b in ladder)
+    assert 500 < ladder[-1] < 800 and ladder[0] <= ladder[-1] // 8 + 8           # brackets the planned limit of a 180 GiB device from below
+    small = planned_batch_ladder(config, None, strategies=("fsdp",), world_sizes=(1, 8), device_gib=40.0)
+    assert small[-1] < ladder[-1] / 4
+    with pytest.raises(ValueError):
+        planned_batch_ladder(config, None, strategies=("fsdp",), world_sizes=(1,), device_gib=2.0)     # not even the resident part fits
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("run_dist_bench", ROOT / "scripts" / "run_dist_bench.py")
+    cli = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(cli)
+    args = cli._parser().parse_args(["run", "--suite", "capacity", "--batch-sizes", "auto"])
+    assert args.batch_sizes == "auto" and cli._parser().parse_args(["run", "--suite", "weak", "--batch-sizes", "8,16"]).batch_sizes == (8, 16)
