@@ -337,3 +337,29 @@ def test_server_check_reports_errors_on_a_machine_without_gpus_and_reads_nvlink_
         report = collect_server_status(expected_gpus=1, min_free_disk_gb=0.0, require_nvcc=False)
         assert not report["ok"] and "CUDA is not available" in report["errors"] and report["gpu_count"] == 0 and report["nvlink"] == {}
         assert report["checkout"] is not None and isinstance(report["extension_built"], bool)
+
+
+# ---- step roofline ----------------------------------------------------------------------------------------------------------
+def test_step_roofline_counts_the_model_flops_and_every_pass_once():
+    import subprocess
+    import sys
+
+    from mini_train_sys_b200.runtime.step_model import step_roofline, step_work
+
+    peaks = {"hbm_gbs": 6553.9, "bf16_tflops": 1650.4, "bf16_tflops_sustained": 1371.8, "source": "test"}
+    for path, batch in (("configs/synbios_moe/model.yaml", 96), ("configs/model_125m_dense.yaml", 32), ("configs/model_debug_moe.yaml", 4)):
+        model = _model_from(path)
+        tokens = batch * model.seq_len
+        report = step_roofline(model, batch, peaks=peaks, measured_ms=100.0)
+        # the contractions of a step are 6 FLOPs per token and active matrix parameter (router and embedding gather aside)
+        matrix = model.active_param_count() - (model.n_layers * model.num_experts * model.hidden_size if model.is_moe else 0)
+        gemms = [w for w in step_work(model, batch) if w.kind == "gemm"]
+        assert sum(w.count * w.flops for w in gemms) == pytest.approx(6.0 * tokens * matrix, rel=1e-9)
+        assert len(gemms) == (6 + 6 + 3) and all(w.flops > 0 and w.bytes == 0 for w in gemms)
+        assert sum(report["bound_ms_by_kind"].values()) == pytest.approx(report["bound_ms_sustained"], abs=2e-3)
+        assert report["bound_ms_burst"] <= report["bound_ms_sustained"] and report["achieved_fraction_of_sustained_bound"] == pytest.approx(report["bound_ms_sustained"] / 100.0, abs=1e-3)
+    headline = step_roofline(_model_from("configs/synbios_moe/model.yaml"), 96, peaks=peaks)
+    assert headline["bound_ms_sustained"] == pytest.approx(36.4, abs=0.3) and headline["bound_ms_by_kind"]["gemm"] == pytest.approx(26.6, abs=0.2)
+    done = subprocess.run([sys.executable, str(ROOT / "scripts" / "step_roofline.py"), "--model-config", str(ROOT / "configs" / "synbios_moe" / "model.yaml"),
+                           "--local-batch", "96", "--measured-ms", "62.69"], capture_output=True, text=True, timeout=120)
+    assert done.returncode == 0 and "of the sustained bound" in done.stdout and "| logits | gemm | 1 |" in done.stdout
