@@ -108,3 +108,46 @@ def step_roofline(model: ModelConfig, local_batch: int, *, peaks: dict[str, floa
         out["achieved_fraction_of_sustained_bound"] = round(bound / measured_ms, 3)
         out["achieved_fraction_of_burst_bound"] = round(burst / measured_ms, 3)
     return out
+
+
+NVLINK_GBS_MEASURED = 770.0        # peer copy per direction per GPU on this pool (nominal 900)
+
+
+def comm_work(model: ModelConfig, local_batch: int, *, strategy: str, world_size: int, sharding: str = "full_shard",
+              multimem: bool = False, link_gbs: float = NVLINK_GBS_MEASURED) -> list[dict]:
+    """Bytes that cross NVLink per rank and step on each path of the fused engine, and the time they take alone at ``link_gbs``
+    per direction.  A path is bounded by the larger of what a rank receives and what it sends; overlap with compute is what
+    the engine is for, so these are the times to hide, not times to add to the step."""
+
+    w = world_size
+    if w <= 1 or strategy == "single":
+        return []
+    far = (w - 1) / w
+    params = model.param_count()
+    expert = model.n_layers * model.num_experts * 3 * model.hidden_size * model.intermediate_size if (strategy == "ep" and model.is_moe) else 0
+    shared = params - expert
+    paths = []
+
+    def add(name: str, received: float, sent: float, launches: int) -> None:
+        paths.append({"path": name, "launches": launches, "gb_in": round(received / 1e9, 4), "gb_out": round(sent / 1e9, 4),
+                      "alone_ms": round(max(received, sent) / (link_gbs * 1e9) * 1e3, 4)})
+
+    units = model.n_layers + 1
+    if multimem:
+        add("gradient reduce-scatter, summed inside the switch (multimem)", F32 * shared / w, 0.0, units)
+    else:
+        add("gradient reduce-scatter, pull of this rank's slice from every peer", far * F32 * shared, far * F32 * shared, units)
+    if strategy == "fsdp" and sharding == "full_shard":
+        add("parameter all-gather into staging slots, forward and backward", 2 * far * LOW * shared, 2 * far * LOW * shared, 2 * units - 2)
+        add("AdamW: bf16 result stored into the own shard only", 0.0, 0.0, 1)
+    else:
+        add("AdamW: bf16 shard pushed into every peer's replica", far * LOW * shared, far * LOW * shared, 1)
+    add("global gradient norm (one float per peer)", 4.0 * (w - 1), 4.0 * (w - 1), 1)
+    if strategy == "ep":
+        # per layer and pass a rank stores the rows of foreign experts at their owners and reads its results back, while its
+        # peers do the same with it: two row transfers in and two out
+        rows = local_batch * model.seq_len * model.experts_per_token
+        per_pass = 2 * model.n_layers * far * rows * model.hidden_size * LOW
+        add("expert dispatch and combine, forward (rows to the owners, results back)", per_pass, per_pass, 2 * model.n_layers)
+        add("expert dispatch and combine, backward (row gradients to the owners, input gradients back)", per_pass, per_pass, 2 * model.n_layers)
+    return paths

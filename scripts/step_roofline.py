@@ -22,7 +22,7 @@ if str(ROOT) not in sys.path:
 
 from mini_train_sys_b200.models.config import ModelConfig  # noqa: E402
 from mini_train_sys_b200.runtime.config import load_yaml_dict  # noqa: E402
-from mini_train_sys_b200.runtime.step_model import step_roofline  # noqa: E402
+from mini_train_sys_b200.runtime.step_model import NVLINK_GBS_MEASURED, comm_work, step_roofline  # noqa: E402
 
 
 def main(argv=None) -> int:
@@ -31,10 +31,17 @@ def main(argv=None) -> int:
     ap.add_argument("--local-batch", type=int, required=True)
     ap.add_argument("--measured-ms", type=float, default=None, help="device-timed milliseconds per step to compare with")
     ap.add_argument("--format", choices=("markdown", "json"), default="markdown")
+    ap.add_argument("--strategy", choices=("single", "ddp", "fsdp", "ep"), default="single", help="with --world-size: also list the NVLink traffic")
+    ap.add_argument("--world-size", type=int, default=1)
+    ap.add_argument("--sharding", choices=("full_shard", "shard_grad_op"), default="full_shard")
+    ap.add_argument("--multimem", action="store_true", help="gradient sums inside the switch (parallel.comm.use_multimem)")
+    ap.add_argument("--link-gbs", type=float, default=NVLINK_GBS_MEASURED, help="NVLink GB/s per direction per GPU (measured peer copy here: 770)")
     args = ap.parse_args(argv)
     payload = load_yaml_dict(args.model_config)
     model = ModelConfig(**(payload.get("model") or payload))
     report = step_roofline(model, args.local_batch, measured_ms=args.measured_ms)
+    report["nvlink_paths"] = comm_work(model, args.local_batch, strategy=args.strategy, world_size=args.world_size, sharding=args.sharding,
+                                       multimem=args.multimem, link_gbs=args.link_gbs)
     if args.format == "json":
         print(json.dumps(report, indent=1))
         return 0
@@ -48,6 +55,12 @@ def main(argv=None) -> int:
     kinds = report["bound_ms_by_kind"]
     print(f"\nbound: {report['bound_ms_sustained']:.2f} ms (GEMM {kinds['gemm']:.2f}, attention {kinds['attention']:.2f}, memory {kinds['memory']:.2f}); "
           f"{report['bound_ms_burst']:.2f} ms at the burst GEMM rate")
+    if report["nvlink_paths"]:
+        print(f"\nNVLink traffic per rank and step ({args.strategy}, {args.world_size} ranks, {args.link_gbs:.0f} GB/s per direction): time to hide, not to add")
+        print("| path | launches | GB in | GB out | ms alone |")
+        print("|---|---:|---:|---:|---:|")
+        for row in report["nvlink_paths"]:
+            print(f"| {row['path']} | {row['launches']} | {row['gb_in']} | {row['gb_out']} | {row['alone_ms']:.3f} |")
     if args.measured_ms:
         print(f"measured: {args.measured_ms:.2f} ms -> {report['achieved_fraction_of_sustained_bound']:.3f} of the sustained bound, "
               f"{report['achieved_fraction_of_burst_bound']:.3f} of the burst bound")

@@ -363,3 +363,25 @@ def test_step_roofline_counts_the_model_flops_and_every_pass_once():
     done = subprocess.run([sys.executable, str(ROOT / "scripts" / "step_roofline.py"), "--model-config", str(ROOT / "configs" / "synbios_moe" / "model.yaml"),
                            "--local-batch", "96", "--measured-ms", "62.69"], capture_output=True, text=True, timeout=120)
     assert done.returncode == 0 and "of the sustained bound" in done.stdout and "| logits | gemm | 1 |" in done.stdout
+
+
+def test_nvlink_traffic_per_path_matches_the_hand_count():
+    from mini_train_sys_b200.runtime.step_model import comm_work
+
+    model = _model_from("configs/synbios_moe/model.yaml")
+    grads, weights = 4 * model.param_count(), 2 * model.param_count()
+    assert comm_work(model, 96, strategy="single", world_size=1) == [] and comm_work(model, 96, strategy="fsdp", world_size=1) == []
+    full = {row["path"].split(",")[0]: row for row in comm_work(model, 96, strategy="fsdp", world_size=8)}
+    assert full["gradient reduce-scatter"]["gb_in"] == pytest.approx(7 / 8 * grads / 1e9, rel=1e-3)          # 1.027 GB
+    assert full["gradient reduce-scatter"]["alone_ms"] == pytest.approx(1.334, abs=2e-3) and full["gradient reduce-scatter"]["launches"] == 13
+    assert full["parameter all-gather into staging slots"]["gb_in"] == pytest.approx(2 * 7 / 8 * weights / 1e9, rel=1e-3)
+    resident = {row["path"].split(":")[0].split(",")[0]: row for row in comm_work(model, 96, strategy="fsdp", world_size=8, sharding="shard_grad_op")}
+    assert "parameter all-gather into staging slots" not in resident and resident["AdamW"]["gb_out"] == pytest.approx(7 / 8 * weights / 1e9, rel=1e-3)
+    switch = comm_work(model, 96, strategy="fsdp", world_size=8, multimem=True)[0]
+    assert switch["gb_in"] == pytest.approx(grads / 8 / 1e9, rel=1e-3) and switch["gb_out"] == 0.0
+    moe = _model_from("configs/model_125m_moe.yaml")
+    ep = comm_work(moe, 16, strategy="ep", world_size=4)
+    rows = 16 * moe.seq_len * moe.experts_per_token
+    assert ep[-1]["gb_in"] == pytest.approx(2 * moe.n_layers * 0.75 * rows * moe.hidden_size * 2 / 1e9, rel=1e-3) and ep[-1]["launches"] == 2 * moe.n_layers
+    experts = moe.n_layers * moe.num_experts * 3 * moe.hidden_size * moe.intermediate_size
+    assert ep[0]["gb_in"] == pytest.approx(0.75 * 4 * (moe.param_count() - experts) / 1e9, rel=1e-3)         # expert gradients stay local
