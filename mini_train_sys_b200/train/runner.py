@@ -68,6 +68,13 @@ class TrainingRunner:
         except (TypeError, ValueError):
             self._flops_per_token = 0.0
         self._peak_flops = measured_peaks()["bf16_tflops_sustained"] * 1e12
+        # what one step of this model and batch would take with every kernel at the machine's measured peak and no gaps
+        try:
+            from mini_train_sys_b200.runtime.step_model import step_roofline
+
+            self._step_bound_ms = float(step_roofline(ModelConfig(**cfg.model), cfg.train.batch_size)["bound_ms_sustained"]) if cfg.model else 0.0
+        except (TypeError, ValueError):
+            self._step_bound_ms = 0.0
 
     # ---- logging -----------------------------------------------------------------
     def _new_interval(self) -> _Interval:
@@ -111,6 +118,10 @@ class TrainingRunner:
             end.record()
             end.synchronize()
             event["device_step_time_ms"] = round(iv.device_start.elapsed_time(end) / steps, 3)
+            if self._step_bound_ms > 0 and event["device_step_time_ms"] > 0:
+                event["roofline_fraction"] = round(self._step_bound_ms / event["device_step_time_ms"], 4)
+        if self._step_bound_ms > 0:
+            event["roofline_step_bound_ms"] = round(self._step_bound_ms, 3)
         if self._flops_per_token and self.device.type == "cuda":
             event["mfu_percent"] = round(100 * estimate_mfu(tok_s / self.world_size, self._flops_per_token,
                                                             self._peak_flops), 2)

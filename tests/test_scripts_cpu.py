@@ -35,7 +35,7 @@ def test_debug_moe_run_reproduces_the_reference_loss_curve(tmp_path):
     # the unmodified reference prints 7.689 at step 1 and 7.662 at step 10 for this config and seed
     assert train[0]["loss"] == pytest.approx(7.68907, abs=2e-4) and train[-1]["loss"] == pytest.approx(7.66168, abs=2e-3)
     for key in ("lr", "tokens_seen", "tokens_per_sec", "step_time_ms", "data_wait_percent", "grad_norm", "moe/aux_loss",
-                "loss/lm_cross_entropy", "moe/expert_load_fraction_by_layer", "host_peak_memory_mb"):
+                "loss/lm_cross_entropy", "moe/expert_load_fraction_by_layer", "host_peak_memory_mb", "roofline_step_bound_ms"):
         assert key in train[0], key
     assert len(train[0]["moe/expert_load_fraction_by_layer"]) == 2 and len(train[0]["moe/expert_load_fraction_by_layer"][0]) == 4
 
