@@ -329,6 +329,17 @@ def main() -> None:
     if args.impl == "reference":
         record["config"]["ref_ops"] = args.ref_ops
     if args.impl == "own":
+        try:
+            # the step's roofline: every operator at the measured peak of the unit that bounds it, no gaps (runtime/step_model.py)
+            from mini_train_sys_b200.models.config import ModelConfig
+            from mini_train_sys_b200.runtime.step_model import step_roofline
+
+            bound = step_roofline(ModelConfig(**cfg.model), batch)
+            record["roofline"] = {"step_bound_ms_sustained": bound["bound_ms_sustained"], "step_bound_ms_burst": bound["bound_ms_burst"],
+                                  "fraction_of_sustained_bound": round(bound["bound_ms_sustained"] / (total_ms / steps), 3),
+                                  "denominators": bound["peaks"].get("source", "measured")}
+        except Exception:  # noqa: BLE001 - commentary on the number; it must never cost the benchmark its line
+            pass
         record["config"]["sharding"] = args.sharding if strategy_name == "fsdp" else None
         record["config"]["multimem"] = bool(args.multimem)
         record["config"]["cuda_graph"] = bool(getattr(trainer, "_graph", None) is not None)
