@@ -179,3 +179,29 @@ def plan_memory(model: ModelConfig, *, strategy: str = "single", world_size: int
     return MemoryPlan(strategy=strategy, world_size=w, sharding=sharding if strategy == "fsdp" else "n/a", tokens_per_sample=model.seq_len,
                       static=static, symmetric=frozenset(symmetric), per_token=per_token, workspace=WORKSPACE_BYTES + extra,
                       notes=tuple(notes))
+
+
+def memory_plan_event(cfg, *, world_size: int, device_bytes: float, headroom: float = 0.9) -> dict[str, object] | None:
+    """The ``memory_plan`` event of a training run: planned peak of the configured batch, whether it fits the device, and the
+    largest batch that would.  ``cfg`` is an ``ExperimentConfig``; ``None`` when the run is outside what the plan covers (no
+    model section, a strategy or sharding mode of the library engine only)."""
+
+    if not cfg.model:
+        return None
+    strategy = cfg.parallel.strategy
+    sharding = cfg.parallel.fsdp.sharding_strategy
+    if strategy not in STRATEGIES or (strategy == "fsdp" and sharding not in ("full_shard", "shard_grad_op")):
+        return None
+    try:
+        model = ModelConfig(**cfg.model)
+        plan = plan_memory(model, strategy=strategy, world_size=world_size, sharding=sharding if strategy == "fsdp" else "full_shard",
+                           local_batch_hint=cfg.train.batch_size,
+                           activation_checkpointing=bool(strategy == "fsdp" and cfg.parallel.fsdp.activation_checkpointing))
+    except (TypeError, ValueError):
+        return None
+    batch = cfg.train.batch_size
+    return {"event": "memory_plan", "local_batch": batch, "planned_peak_gib": round(plan.total_bytes(batch) / GIB, 2),
+            "planned_max_memory_allocated_gib": round(plan.total_bytes(batch, allocator_only=True) / GIB, 2),
+            "resident_gib": round(plan.static_bytes() / GIB, 2), "gib_per_sample": round(plan.activation_bytes(1) / GIB, 4),
+            "device_gib": round(device_bytes / GIB, 1), "fits": plan.total_bytes(batch) <= headroom * device_bytes,
+            "max_local_batch": plan.max_local_batch(device_bytes, headroom=headroom)}

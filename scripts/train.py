@@ -1,8 +1,8 @@
 """Training entry point: config -> data/model/strategy -> Trainer -> TrainingRunner.
 
 Flags and emitted events (``init``, ``parallel_ready``, ``resume``, ``train``, ``checkpoint``)
-follow the reference entry point (scripts/train.py:57-281); ``ops_dispatch`` (native vs fallback calls per operator, at the
-end of a run with the native back end) is an addition.  Launch one process per GPU with
+follow the reference entry point (scripts/train.py:57-281); ``memory_plan`` (planned device memory of the configured batch, on a GPU) and
+``ops_dispatch`` (native vs fallback calls per operator, at the end of a run with the native back end) are additions.  Launch one process per GPU with
 ``torchrun --standalone --nproc_per_node N scripts/train.py --config ... --model-config ...``.
 """
 
@@ -107,6 +107,13 @@ def main(argv=None) -> None:
                               "auto_wrap_policy": cfg.parallel.fsdp.auto_wrap_policy,
                               "sharding_strategy": cfg.parallel.fsdp.sharding_strategy,
                               "engine": strategy.resolved_engine()})
+        if device.type == "cuda" and cfg.backend.ops != "torch":
+            # what the configured batch will need under the fused engine, before the first step finds out the hard way
+            from mini_train_sys_b200.runtime.memory_plan import memory_plan_event
+
+            planned = memory_plan_event(cfg, world_size=world_size, device_bytes=torch.cuda.get_device_properties(device).total_memory)
+            if planned is not None:
+                logger.log_event(planned)
         max_steps = args.smoke_steps if args.smoke_steps > 0 else cfg.train.max_steps
         total_steps = resolve_total_steps(max_steps=max_steps, epochs=cfg.train.epochs, steps_per_epoch=len(dataloader))
         optimizer = build_optimizer(model, cfg=scale.optimizer)   # after wrapping: sees sharded parameters

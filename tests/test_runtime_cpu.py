@@ -385,3 +385,24 @@ def test_nvlink_traffic_per_path_matches_the_hand_count():
     assert ep[-1]["gb_in"] == pytest.approx(2 * moe.n_layers * 0.75 * rows * moe.hidden_size * 2 / 1e9, rel=1e-3) and ep[-1]["launches"] == 2 * moe.n_layers
     experts = moe.n_layers * moe.num_experts * 3 * moe.hidden_size * moe.intermediate_size
     assert ep[0]["gb_in"] == pytest.approx(0.75 * 4 * (moe.param_count() - experts) / 1e9, rel=1e-3)         # expert gradients stay local
+
+
+def test_memory_plan_event_of_shipped_run_files():
+    from mini_train_sys_b200.runtime.memory_plan import GIB, memory_plan_event
+
+    cfg = cfgmod.load_experiment(ROOT / "configs" / "server" / "b200_180gb" / "runs" / "fsdp_8gpu.yaml", ROOT / "configs" / "synbios_moe" / "model.yaml")
+    event = memory_plan_event(cfg, world_size=8, device_bytes=180 * GIB)
+    assert event["event"] == "memory_plan" and event["fits"] and event["local_batch"] == 96
+    assert event["planned_max_memory_allocated_gib"] == pytest.approx(24.59, rel=0.03) and event["max_local_batch"] > 500
+    assert not memory_plan_event(cfg, world_size=8, device_bytes=16 * GIB)["fits"]
+    json.dumps(event)                                                    # plain values only: it goes straight into the event log
+    for path in sorted((ROOT / "configs").rglob("*.yaml")):              # every shipped run file: an event or None, never an exception
+        try:
+            run = cfgmod.load_experiment(path)
+        except Exception:                                                # model files and fragments are not run files
+            continue
+        for world in (1, 2, 8):
+            out = memory_plan_event(run, world_size=world, device_bytes=180 * GIB)
+            assert out is None or (out["planned_peak_gib"] > 0 and isinstance(out["fits"], bool))
+    debug = cfgmod.load_experiment(ROOT / "configs" / "train_debug.yaml")
+    assert memory_plan_event(debug, world_size=1, device_bytes=180 * GIB) is None        # no model section: nothing to plan
