@@ -11,7 +11,7 @@ SUFFIXES = (".py", ".cu", ".cuh", ".cpp", ".h", ".yaml", ".md", ".sh", ".ps1", "
 def _documents():
     yield from sorted((ROOT / "docs").glob("*.md"))
     for name in ("README.md", "CONTRIBUTING.md", "configs/README.md", "scripts/README.md", "scripts/synbios_moe_runbook.md",
-                 "examples/README.md", "profiles/README.md"):
+                 "examples/README.md", "profiles/README.md", "experiments/synbios_moe/README.md"):
         yield ROOT / name
 
 
