@@ -203,6 +203,18 @@ class _RankShare:
     def set_epoch(self, epoch: int) -> None:
         self.epoch = epoch
 
+    def set_start(self, samples: int) -> None:
+        """Resume cursor: the next iteration leaves out this rank's first ``samples`` examples of the epoch (they were
+        trained on before the interruption); the one after that is a full epoch again."""
+
+        if samples < 0:
+            raise ValueError("samples must be non-negative")
+        self._start = int(samples)
+
+    def _take_start(self) -> int:
+        start, self._start = getattr(self, "_start", 0), 0
+        return min(start, self.num_samples)
+
     def _generator(self) -> torch.Generator:
         gen = torch.Generator(device="cpu")
         gen.manual_seed(self.seed + self.epoch)
@@ -242,10 +254,11 @@ class ShardAwareBlockSampler(_RankShare, Sampler):
                     yield w_lo + off
 
     def __iter__(self) -> Iterator[int]:
+        first = self._take_start() * self.world_size      # positions of the common stream that lie before the cursor
         for position, index in enumerate(self.global_order()):
             if position >= self.total_size:
                 return
-            if position % self.world_size == self.rank:
+            if position >= first and position % self.world_size == self.rank:
                 yield index
 
 
@@ -269,7 +282,7 @@ class RandomizedDocumentSampler(_RankShare, Sampler):
         spans = self.ordered_spans()
         stops = np.cumsum([n for _, n in spans]).tolist()
         seq = self.dataset.seq_len
-        for block in range(self.rank, self.total_size, self.world_size):
+        for block in range(self.rank + self._take_start() * self.world_size, self.total_size, self.world_size):
             pos = block * seq
             doc = bisect_right(stops, pos)
             inner = pos - (stops[doc - 1] if doc else 0)

@@ -185,7 +185,7 @@ def _full_model_state(model) -> dict[str, torch.Tensor]:
 
 
 def save_checkpoint(path: str | Path, model: torch.nn.Module, optimizer: torch.optim.Optimizer, step: int, *,
-                    epoch: int = 0, lr_step: int | None = None, tokens_seen: int = 0,
+                    epoch: int = 0, lr_step: int | None = None, tokens_seen: int = 0, epoch_batches_done: int = 0,
                     grad_scaler: torch.amp.GradScaler | None = None, lr_scheduler: Any | None = None,
                     precision: str | None = None, config: dict[str, Any] | None = None, export_model: bool = False,
                     cpu_offload: bool = True, write: bool | None = None) -> Path:
@@ -220,7 +220,7 @@ def save_checkpoint(path: str | Path, model: torch.nn.Module, optimizer: torch.o
         runtime: dict[str, Any] = {
             "format_version": FORMAT_VERSION,
             "trainer": {"step": step, "lr_step": step if lr_step is None else lr_step, "epoch": epoch,
-                        "tokens_seen": tokens_seen},
+                        "tokens_seen": tokens_seen, "epoch_batches_done": int(epoch_batches_done)},
             "saved_world_size": _world(), "precision": precision, "config": config,
         }
         if grad_scaler is not None:
@@ -242,7 +242,7 @@ def _counters(trainer: dict[str, Any], payload: dict[str, Any] | None = None) ->
     base = payload or {}
     step = int(trainer.get("step", base.get("step", 0)))
     return {"step": step, "lr_step": int(trainer.get("lr_step", step)), "epoch": int(trainer.get("epoch", 0)),
-            "tokens_seen": int(trainer.get("tokens_seen", 0))}
+            "tokens_seen": int(trainer.get("tokens_seen", 0)), "epoch_batches_done": int(trainer.get("epoch_batches_done", 0))}
 
 
 def _restore_single_file(path: Path, model, optimizer, grad_scaler, lr_scheduler, want_rng: bool) -> dict[str, Any]:

@@ -159,7 +159,7 @@ class TrainingRunner:
         export = ck.export_model and (force_model_export or every is None or epoch % every == 0)
         t0 = time.perf_counter()
         save_checkpoint(target, self.trainer.model, self.trainer.optimizer, st.step, epoch=epoch, lr_step=st.lr_step,
-                        tokens_seen=st.tokens_seen, grad_scaler=self.trainer.grad_scaler,
+                        tokens_seen=st.tokens_seen, epoch_batches_done=st.epoch_batches_done, grad_scaler=self.trainer.grad_scaler,
                         lr_scheduler=self.trainer.lr_scheduler, precision=self.trainer.precision.name,
                         config=asdict(self.cfg), export_model=export, cpu_offload=ck.cpu_offload)
         if self.rank == 0:
@@ -175,6 +175,16 @@ class TrainingRunner:
                 "removed_old_checkpoints": [str(p) for p in removed],
             })
         return target
+
+    def _skip_batches(self, sampler, batches: int) -> None:
+        """Position the data stream behind the first ``batches`` batches of the epoch: through the sampler's cursor when it
+        has one (nothing is read), else by drawing and dropping them."""
+
+        if hasattr(sampler, "set_start"):
+            sampler.set_start(batches * self.cfg.train.batch_size)
+            self._drop_batches = 0
+        else:
+            self._drop_batches = batches
 
     # ---- main loop ---------------------------------------------------------------
     def run(self, *, max_steps: int | None, resume_path: Path | None = None) -> None:
@@ -205,14 +215,21 @@ class TrainingRunner:
             if hasattr(sampler, "set_epoch"):
                 sampler.set_epoch(epoch)   # every rank must see the same epoch number
             n_batches = len(self.dataloader)
+            # a run that was interrupted inside this epoch continues behind the batches it already trained on
+            first_batch = min(st.epoch_batches_done, n_batches) if epoch == st.epoch + 1 else 0
+            if first_batch:
+                self._skip_batches(sampler, first_batch)
             source = self.dataloader
             if self.cfg.data.device_prefetch:
                 from mini_train_sys_b200.data.dataloader import DevicePrefetcher
 
                 source = DevicePrefetcher(self.dataloader, self.device)     # a pass-through on a CPU device
             stream = iter(source)
+            for _ in range(getattr(self, "_drop_batches", 0)):
+                next(stream)
+            self._drop_batches = 0
             finished_epoch = True
-            for batch_index in range(1, n_batches + 1):
+            for batch_index in range(first_batch + 1, n_batches + 1):
                 t_wait = time.perf_counter()
                 batch = next(stream)
                 iv.data_wait += time.perf_counter() - t_wait
@@ -225,6 +242,7 @@ class TrainingRunner:
                         self.logger.log_event({"event": "peer_lost", "step": st.step, "detail": str(exc)})
                         raise SystemExit(3) from exc
                 loss = self.trainer.train_step(batch)
+                st.epoch_batches_done = batch_index
                 if health is not None:
                     health.beat(st.step)
                 iv.add(iv.scalars, {"loss": loss})
@@ -245,8 +263,9 @@ class TrainingRunner:
                     done = True
                     break
 
-            if finished_epoch:   # a max_steps stop mid-epoch keeps the previous complete epoch
+            if finished_epoch:   # a max_steps stop mid-epoch keeps the previous complete epoch (and the cursor into this one)
                 st.epoch = epoch
+                st.epoch_batches_done = 0
             every = self.cfg.checkpoint.every_epochs
             if finished_epoch and every is not None and epoch % every == 0:
                 terminal = (epochs_limit is not None and epoch >= epochs_limit) or \

@@ -30,7 +30,8 @@ class TrainState:
     step: int = 0
     lr_step: int = 0       # schedule progress; remapped on elastic resume
     tokens_seen: int = 0   # local tokens; multiplied by world size when logged
-    epoch: int = 0
+    epoch: int = 0         # complete epochs
+    epoch_batches_done: int = 0   # batches of the epoch in progress (epoch + 1) that were already trained on: the resume cursor
 
 
 class Trainer:

@@ -131,8 +131,10 @@ def main(argv=None) -> None:
                                               lr_scheduler=scheduler, restore_rng=True)
             st = trainer.state
             st.step, st.epoch, st.tokens_seen, st.lr_step = got["step"], got["epoch"], got["tokens_seen"], got["lr_step"]
+            st.epoch_batches_done = int(got.get("epoch_batches_done", 0))      # continue inside the interrupted epoch
             if got.get("saved_world_size", world_size) != world_size:
                 st.lr_step = st.epoch * len(dataloader)    # re-express schedule progress in the new layout
+                st.epoch_batches_done = 0                  # the rank partition changed: the interrupted epoch starts over
             if not got["rng_restored"]:
                 seed_everything(cfg.run.seed + strategy.rank + st.step)
             scheduler.step(st.lr_step)

@@ -105,6 +105,19 @@ def test_random_shards_manifest_and_loaders(shards):
     assert rds[specs[0]]["input_ids"].shape == (64,)
 
 
+def test_document_sampler_cursor_resumes_inside_the_reordered_stream(shards):
+    rds = RandomizedDocumentBlockDataset(shards, split="train", seq_len=64)
+    for world in (1, 3):
+        for rank in range(world):
+            sampler = RandomizedDocumentSampler(rds, shuffle=True, seed=5, rank=rank, world_size=world)
+            sampler.set_epoch(2)
+            full = list(sampler)
+            sampler.set_start(7)
+            assert list(sampler) == full[7:] and list(sampler) == full           # one iteration only
+            sampler.set_start(len(full))
+            assert list(sampler) == []
+
+
 @pytest.mark.parametrize("world", [1, 2, 3, 8])
 def test_sampler_ranks_are_disjoint_equal_and_deterministic(shards, world):
     ds = ShardedTokenBlockDataset(shards, split="train", seq_len=32)

@@ -60,6 +60,63 @@ def test_device_prefetch_option_feeds_the_same_batches(tmp_path):
     assert len(losses[True]) == 6 and losses[True] == losses[False]
 
 
+def test_resume_inside_an_epoch_continues_behind_the_batches_already_seen(tmp_path):
+    """A run stopped in the middle of an epoch and resumed sees exactly the batches the uninterrupted run sees (the reference
+    restarts the interrupted epoch): same loss at every step, also across the next epoch boundary."""
+
+    def config(name, max_steps, packing=None):
+        cfg = yaml.safe_load((ROOT / "configs" / "train_debug.yaml").read_text())
+        cfg["run"]["name"] = name
+        cfg["train"].update(max_steps=max_steps, epochs=None, log_interval=1)
+        cfg["data"]["num_tokens"] = 64 * cfg["train"]["batch_size"] * 6 + 1            # six batches per epoch
+        cfg["checkpoint"] = {"directory": "ckpt", "every_epochs": 1, "export_model": False, "keep_last": 5, "save_final": True}
+        cfg["logging"]["tensorboard"] = False
+        return cfg
+
+    model_cfg = str(ROOT / "configs" / "model_debug_moe.yaml")
+    whole = tmp_path / "whole"
+    whole.mkdir()
+    (whole / "run.yaml").write_text(yaml.safe_dump(config("cursor", 10)))
+    run([str(ROOT / "scripts" / "train.py"), "--config", "run.yaml", "--model-config", model_cfg, "--device", "cpu"], whole)
+    want = {e["step"]: e["loss"] for e in events(whole) if e["event"] == "train"}
+    assert sorted(want) == list(range(1, 11))
+
+    parts = tmp_path / "parts"
+    parts.mkdir()
+    (parts / "run.yaml").write_text(yaml.safe_dump(config("cursor", 4)))                  # stops after batch 4 of 6 of the first epoch
+    run([str(ROOT / "scripts" / "train.py"), "--config", "run.yaml", "--model-config", model_cfg, "--device", "cpu"], parts)
+    (parts / "run.yaml").write_text(yaml.safe_dump(config("cursor", 10)))
+    run([str(ROOT / "scripts" / "train.py"), "--config", "run.yaml", "--model-config", model_cfg, "--device", "cpu", "--resume", "latest"], parts)
+    log = events(parts)
+    resumed = [e for e in log if e["event"] == "resume"]
+    assert len(resumed) == 1 and resumed[0]["step"] == 4 and resumed[0]["epoch"] == 0 and resumed[0]["epoch_batches_done"] == 4
+    got = {e["step"]: e["loss"] for e in log if e["event"] == "train"}
+    assert sorted(got) == list(range(1, 11))
+    for step in range(1, 11):
+        assert got[step] == pytest.approx(want[step], abs=1e-6), (step, got[step], want[step])
+    first_after = next(e for e in log if e["event"] == "train" and e["step"] == 5)
+    assert first_after["epoch"] == 1 and first_after["batch"] == 5 and first_after["batches_total"] == 6
+
+
+def test_sampler_cursor_skips_exactly_this_ranks_first_samples():
+    import torch
+
+    from mini_train_sys_b200.data.dataloader import ShardAwareBlockSampler, TokenBlockDataset
+
+    data = TokenBlockDataset(torch.arange(0, 16 * 40 + 1), 16)
+    for world in (1, 2, 3):
+        for rank in range(world):
+            sampler = ShardAwareBlockSampler(data, shuffle=True, seed=5, rank=rank, world_size=world, shuffle_window=7)
+            sampler.set_epoch(3)
+            full = list(sampler)
+            sampler.set_start(4)
+            assert list(sampler) == full[4:] and list(sampler) == full          # the cursor applies to one iteration only
+            sampler.set_start(10**6)
+            assert list(sampler) == []
+    with pytest.raises(ValueError):
+        sampler.set_start(-1)
+
+
 @pytest.fixture()
 def run_cfg(tmp_path):
     cfg = yaml.safe_load((ROOT / "configs" / "train_debug.yaml").read_text())
