@@ -201,6 +201,7 @@ class TrainConfig:
 class CheckpointConfig:
     directory: str = "checkpoints"
     every_epochs: int | None = 1
+    every_steps: int | None = None       # also save inside an epoch; such a checkpoint resumes behind the batches it saw
     keep_last: int | None = None
     keep_safety: int = 0
     safety_every_epochs: int | None = None
@@ -213,6 +214,7 @@ class CheckpointConfig:
 
     def __post_init__(self) -> None:
         _positive_or_none(self.every_epochs, "checkpoint.every_epochs must be positive or null")
+        _positive_or_none(self.every_steps, "checkpoint.every_steps must be positive or null")
         _positive_or_none(self.keep_last, "checkpoint.keep_last must be positive or null")
         _require(self.keep_safety >= 0, "checkpoint.keep_safety must be non-negative")
         if self.keep_safety:

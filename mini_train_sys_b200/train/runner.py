@@ -151,12 +151,12 @@ class TrainingRunner:
         if callable(checker):
             checker()
 
-    def _save(self, *, epoch: int, force_model_export: bool = False) -> Path:
+    def _save(self, *, epoch: int, force_model_export: bool = False, inside_epoch: bool = False) -> Path:
         self._check_device_status()
         ck, st = self.cfg.checkpoint, self.trainer.state
         target = checkpoint_path(ck.directory, self.cfg.run.name, epoch=epoch, step=st.step)
         every = ck.export_model_every_epochs
-        export = ck.export_model and (force_model_export or every is None or epoch % every == 0)
+        export = ck.export_model and not inside_epoch and (force_model_export or every is None or epoch % every == 0)
         t0 = time.perf_counter()
         save_checkpoint(target, self.trainer.model, self.trainer.optimizer, st.step, epoch=epoch, lr_step=st.lr_step,
                         tokens_seen=st.tokens_seen, epoch_batches_done=st.epoch_batches_done, grad_scaler=self.trainer.grad_scaler,
@@ -262,6 +262,9 @@ class TrainingRunner:
                     finished_epoch = batch_index == n_batches
                     done = True
                     break
+                every_steps = self.cfg.checkpoint.every_steps
+                if every_steps is not None and st.step % every_steps == 0 and batch_index < n_batches:
+                    last_saved = self._save(epoch=st.epoch, inside_epoch=True)       # the cursor into the epoch goes with it; no model export
 
             if finished_epoch:   # a max_steps stop mid-epoch keeps the previous complete epoch (and the cursor into this one)
                 st.epoch = epoch

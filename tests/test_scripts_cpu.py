@@ -97,6 +97,27 @@ def test_resume_inside_an_epoch_continues_behind_the_batches_already_seen(tmp_pa
     first_after = next(e for e in log if e["event"] == "train" and e["step"] == 5)
     assert first_after["epoch"] == 1 and first_after["batch"] == 5 and first_after["batches_total"] == 6
 
+    # periodic checkpoints inside an epoch (checkpoint.every_steps): resume from the one at step 4 as after a crash at step 5
+    periodic = tmp_path / "periodic"
+    periodic.mkdir()
+    cfg = config("cursor", 5)
+    cfg["checkpoint"]["every_steps"] = 2
+    (periodic / "run.yaml").write_text(yaml.safe_dump(cfg))
+    run([str(ROOT / "scripts" / "train.py"), "--config", "run.yaml", "--model-config", model_cfg, "--device", "cpu"], periodic)
+    saved = sorted(p.name for p in (periodic / "ckpt" / "cursor").iterdir())
+    assert saved == ["epoch_000000_step_000000002", "epoch_000000_step_000000004", "epoch_000000_step_000000005"], saved
+    assert not (periodic / "ckpt" / "cursor" / saved[0] / "model.pt").exists()
+    cfg["train"]["max_steps"] = 10
+    (periodic / "run.yaml").write_text(yaml.safe_dump(cfg))
+    run([str(ROOT / "scripts" / "train.py"), "--config", "run.yaml", "--model-config", model_cfg, "--device", "cpu", "--resume",
+         str(periodic / "ckpt" / "cursor" / saved[1])], periodic)
+    after = {}
+    for e in events(periodic):
+        if e["event"] == "train":
+            after[e["step"]] = e["loss"]            # the second session overwrites step 5 of the first
+    for step in range(1, 11):
+        assert after[step] == pytest.approx(want[step], abs=1e-6), (step, after[step], want[step])
+
 
 def test_sampler_cursor_skips_exactly_this_ranks_first_samples():
     import torch
