@@ -65,6 +65,15 @@ class ProcessGroupMixin:
         kwargs = {}
         if backend == "nccl":
             kwargs["device_id"] = torch.device("cuda", self.local_rank)
+        attempt = int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0") or 0)
+        if attempt > 0 and os.environ.get("MASTER_ADDR") and os.environ.get("MASTER_PORT"):
+            # Restarted by the launcher after a rank failed (torchrun --max-restarts).  The launcher's store outlives the
+            # failed workers; with the stock env:// rendezvous the restarted Gloo ranks found the dead ranks' addresses there
+            # ("connection refused" in connectFullMesh).  Keys of this attempt go under a prefix of their own instead.
+            store = dist.PrefixStore(f"mts/attempt_{attempt}",
+                                     dist.TCPStore(os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]),
+                                                   int(os.environ["WORLD_SIZE"]), False, timedelta(minutes=self.timeout_minutes)))
+            kwargs.update(store=store, rank=int(os.environ["RANK"]), world_size=int(os.environ["WORLD_SIZE"]))
         dist.init_process_group(backend=backend, timeout=timedelta(minutes=self.timeout_minutes), **kwargs)
 
     def barrier(self) -> None:

@@ -85,11 +85,15 @@ def _committed_dirs(run_dir: Path) -> list[Path]:
     return [p for p in run_dir.glob("epoch_*_step_*") if is_committed(p)]
 
 
-def resolve_resume_checkpoint(resume_from: str | Path, *, checkpoint_dir: str | Path, run_name: str) -> Path:
-    """``latest`` / ``safety`` pick among committed checkpoints of the run; anything else is a path."""
+def resolve_resume_checkpoint(resume_from: str | Path, *, checkpoint_dir: str | Path, run_name: str) -> Path | None:
+    """``latest`` / ``safety`` pick among committed checkpoints of the run; ``auto`` is ``latest`` when the run has one and
+    ``None`` (start from scratch) when it has none, which is what a restarted launcher wants; anything else is a path."""
 
     selector = str(resume_from).lower()
     run_dir = Path(checkpoint_dir) / run_name
+    if selector == "auto":
+        found = sorted([*_committed_dirs(run_dir), *run_dir.glob("epoch_*_step_*.pt")])
+        return found[-1] if found else None
     if selector == "safety":
         anchors = sorted(p for p in _committed_dirs(run_dir) if (p / "SAFETY").is_file())
         if not anchors:

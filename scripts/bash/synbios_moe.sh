@@ -15,7 +15,7 @@ if [[ ! -f "$DATA/manifest.json" ]]; then
 fi
 CONFIG="${CONFIG:-configs/synbios_moe/runs/${VARIANT//+/_}_${STRATEGY}.yaml}"
 [[ -f "$CONFIG" ]] || CONFIG="configs/synbios_moe/runs/single_${STRATEGY}.yaml"
-RESUME=(); if compgen -G "artifacts/synbios_moe/checkpoints/${RUN}/epoch_*" > /dev/null; then RESUME=(--resume latest); fi
+RESUME=(--resume auto)      # latest committed checkpoint when there is one; also what a torchrun restart (MAX_RESTARTS) needs
 if [[ "$STRATEGY" == single ]]; then
   "$PYTHON" scripts/train.py --config "$CONFIG" "${RESUME[@]}"
 else

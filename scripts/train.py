@@ -41,8 +41,9 @@ def parse_args(argv=None) -> argparse.Namespace:
     ap.add_argument("--model-config", default="configs/model_default.yaml")
     ap.add_argument("--smoke-steps", type=int, default=0)
     ap.add_argument("--device", choices=["auto", "cpu", "cuda"], default="auto")
-    ap.add_argument("--resume", nargs="?", const="latest", default=None, metavar="PATH|latest|safety",
-                    help="resume from a checkpoint; no value means latest, 'safety' uses the retained fallback anchor")
+    ap.add_argument("--resume", nargs="?", const="latest", default=None, metavar="PATH|latest|safety|auto",
+                    help="resume from a checkpoint; no value means latest, 'safety' uses the retained fallback anchor, 'auto' is "
+                         "latest when the run has a checkpoint and a fresh start when it has none (for launchers that restart)")
     return ap.parse_args(argv)
 
 
@@ -127,6 +128,7 @@ def main(argv=None) -> None:
         resume_path = None
         if resume is not None:
             resume_path = resolve_resume_checkpoint(resume, checkpoint_dir=cfg.checkpoint.directory, run_name=cfg.run.name)
+        if resume_path is not None:
             got = restore_training_checkpoint(resume_path, model, optimizer, grad_scaler=trainer.grad_scaler,
                                               lr_scheduler=scheduler, restore_rng=True)
             st = trainer.state

@@ -99,3 +99,63 @@ def test_rank_health_against_a_fake_store_and_clock():
         assert "preempted" in err.value.lost[1]
     finally:
         dist.PrefixStore = real
+
+
+def test_a_crashed_rank_is_restarted_and_the_run_continues_from_the_last_checkpoint(tmp_path):
+    """torchrun --max-restarts + ``--resume auto`` + ``checkpoint.every_steps``: rank 1 dies after step 3; the launcher stops
+    rank 0 and starts both again; they resume from the checkpoint of step 2 inside the epoch and finish with the losses of a
+    run that never crashed."""
+
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import yaml
+
+    root = Path(__file__).resolve().parents[1]
+    cfg = yaml.safe_load((root / "configs" / "train_debug.yaml").read_text())
+    cfg["run"]["name"] = "restart"
+    cfg["parallel"].update(strategy="ddp", process_group_backend="gloo", timeout_minutes=1)
+    cfg["train"].update(max_steps=7, epochs=None, log_interval=1)
+    cfg["data"].update(num_tokens=64 * cfg["train"]["batch_size"] * 2 * 5 + 1, num_workers=0, persistent_workers=False)   # five batches per epoch and rank
+    cfg["checkpoint"] = {"directory": "ckpt", "every_epochs": 1, "every_steps": 2, "export_model": False, "keep_last": 8, "save_final": True}
+    cfg["logging"]["tensorboard"] = False
+
+    def launch(work: Path, script: Path, port: int, extra_env: dict, restarts: int):
+        work.mkdir()
+        (work / "run.yaml").write_text(yaml.safe_dump(cfg))
+        env = {**os.environ, "PYTHONPATH": str(root), **extra_env}
+        # the c10d rendezvous (hosted by the launcher, a fresh key prefix per restart), not a static master address: after a
+        # restart the workers must not find the dead workers' addresses in the store
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--rdzv-backend", "c10d",
+               "--rdzv-endpoint", f"127.0.0.1:{port}", "--local-addr", "127.0.0.1", "--max-restarts", str(restarts), str(script),
+               "--config", "run.yaml", "--model-config",
+               str(root / "configs" / "model_debug_moe.yaml"), "--device", "cpu", "--resume", "auto"]
+        done = subprocess.run(cmd, cwd=work, env=env, capture_output=True, text=True, timeout=600)
+        log = [json.loads(line) for f in sorted(work.rglob("events.jsonl")) for line in f.read_text().splitlines()]
+        return done, log
+
+    done, log = launch(tmp_path / "whole", root / "scripts" / "train.py", 29731, {}, 0)
+    assert done.returncode == 0, done.stderr[-2000:]
+    want = {e["step"]: e["loss"] for e in log if e["event"] == "train"}
+    assert sorted(want) == list(range(1, 8)) and not [e for e in log if e["event"] == "resume"]
+
+    marker = tmp_path / "crashed"
+    done, log = launch(tmp_path / "crash", root / "tests" / "restart_train_worker.py", 29732,
+                       {"CRASH_AFTER_STEP": "3", "CRASH_MARKER": str(marker)}, 1)
+    assert done.returncode == 0, done.stderr[-3000:]
+    assert marker.exists()
+    resumed = [e for e in log if e["event"] == "resume"]
+    assert len(resumed) == 1 and resumed[0]["step"] == 2 and resumed[0]["epoch_batches_done"] == 2
+    got = {}
+    for e in log:
+        if e["event"] == "train":
+            got[e["step"]] = e["loss"]                    # step 3 appears twice: before the crash and after the restart
+    assert sorted(got) == list(range(1, 8))
+    for step, loss in want.items():
+        assert got[step] == pytest.approx(loss, abs=1e-6), (step, got[step], loss)
+    # without restarts the same crash ends the job with an error
+    done, _ = launch(tmp_path / "fatal", root / "tests" / "restart_train_worker.py", 29733,
+                     {"CRASH_AFTER_STEP": "3", "CRASH_MARKER": str(tmp_path / "crashed_again")}, 0)
+    assert done.returncode != 0
