@@ -12,16 +12,19 @@ The plan is arithmetic over the same rules the engine and the operators follow, 
   Expert parallelism keeps ``E / W`` experts per rank as rank-local units (24 bytes per parameter) and four exchange
   regions.
 * **activations** (what the autograd functions of ``ops/native_backend.py`` save), in bf16 per token and block: the block
-  input, the two normalised inputs, the fused QKV projection, the attention output, the post-attention residual, and for
-  the feed-forward either ``gate, up, silu(gate) * up`` (dense) or, per route, the gathered row, the ``[gate | up]``
-  pre-activations, the SwiGLU output and the expert output (MoE); dropout saves nothing (masks are recomputed).  Once per
-  token: the final norm's input and output and the bf16 logits; and, at the peak, the gradients of one block's saved
-  tensors.  With activation checkpointing only block inputs stay and one block is live at a time.
+  input, the two normalised inputs, the fused QKV projection, the attention output (twice: as written and made contiguous
+  for the output projection), the post-attention residual and one more hidden-sized copy; for the feed-forward either
+  ``gate, up, silu(gate) * up`` (dense) or, per route, the gathered row, the ``[gate | up]`` pre-activations, the SwiGLU
+  output and the expert output (MoE); dropout saves nothing (masks are recomputed).  The peak is reached inside the fused
+  loss at the end of the forward pass: on top of everything saved there are the bf16 logits of one chunk (at most 65,536
+  rows, ``MTS_FUSED_CE_CHUNK_ROWS``; they are gone before backward starts), the gradient of the final hidden states and the
+  fp32 gradient of the output matrix.  With activation checkpointing only block inputs stay and one block is live at a time.
 
 Against ``max_memory_allocated`` of this repository's benchmark runs on B200 the plan is within 2.5 % on all sixteen
 recorded points: the 293M MoE on 1 to 8 GPUs at local batch 24 and 96 under both sharding modes, the 125M dense preset under
 ``ddp`` on 2, 4 and 8, the 125M MoE preset under ``fsdp`` and ``ep`` on 2 and 4 (``tests/test_runtime_cpu.py`` holds the points).
-One constant is fitted (``WORKSPACE_BYTES``); everything else is counted.  The reference has no counterpart: it finds the largest batch by running a sweep
+One constant is fitted (``WORKSPACE_BYTES``, 0.15 GiB) and one count is taken from the measured slope (seven hidden-sized
+tensors per block where the operators need five); everything else is counted.  The reference has no counterpart: it finds the largest batch by running a sweep
 (benchmarks/distributed/workflow.py ``run_capacity``), which this repository's capacity suite also does; the plan says where
 to start that sweep and why a configuration does not fit.
 """
@@ -38,7 +41,7 @@ LOW_BYTES = 2                      # bf16
 STRATEGIES = ("single", "ddp", "fsdp", "ep")
 # caching-allocator slack, cuBLAS-free workspaces, router statistics, routing plans, CUDA-graph pools: fitted once as the
 # intercept left over on the measured points, identical for every model size tried
-WORKSPACE_BYTES = int(0.3 * GIB)
+WORKSPACE_BYTES = int(0.15 * GIB)
 
 
 def _units(model: ModelConfig) -> tuple[int, int]:
@@ -60,6 +63,8 @@ class MemoryPlan:
     static: dict[str, int]                                  # bytes, by buffer
     symmetric: frozenset[str]                               # static entries outside the caching allocator (world > 1)
     per_token: dict[str, int]                               # activation bytes per token, by part
+    logits_bytes_per_token: int = 0                         # bf16 logits of the fused loss: a buffer of at most `logits_chunk_rows` rows
+    logits_chunk_rows: int = 65536
     workspace: int = WORKSPACE_BYTES
     notes: tuple[str, ...] = field(default_factory=tuple)
 
@@ -67,7 +72,8 @@ class MemoryPlan:
         return sum(v for k, v in self.static.items() if not (allocator_only and k in self.symmetric))
 
     def activation_bytes(self, local_batch: int) -> int:
-        return local_batch * self.tokens_per_sample * sum(self.per_token.values())
+        tokens = local_batch * self.tokens_per_sample
+        return tokens * sum(self.per_token.values()) + min(tokens, self.logits_chunk_rows) * self.logits_bytes_per_token
 
     def total_bytes(self, local_batch: int, *, allocator_only: bool = False) -> int:
         """Peak bytes at ``local_batch``; ``allocator_only`` gives what ``torch.cuda.max_memory_allocated`` reports."""
@@ -77,16 +83,24 @@ class MemoryPlan:
     def max_local_batch(self, device_bytes: float, *, headroom: float = 0.9) -> int:
         """Largest local batch whose peak stays under ``headroom`` of the device (0 when even the static part does not fit)."""
 
-        free = headroom * device_bytes - self.static_bytes() - self.workspace
-        per_sample = self.activation_bytes(1)
-        return max(0, int(free // per_sample)) if per_sample > 0 else 0
+        limit = headroom * device_bytes
+        if self.total_bytes(1) > limit:
+            return 0
+        low, high = 1, 2
+        while self.total_bytes(high) <= limit and high < 1 << 24:
+            low, high = high, high * 2
+        while high - low > 1:                                # peak memory grows monotonically with the batch: bisect
+            mid = (low + high) // 2
+            low, high = (mid, high) if self.total_bytes(mid) <= limit else (low, mid)
+        return low
 
     def summary(self, local_batch: int) -> dict[str, object]:
         return {"strategy": self.strategy, "world_size": self.world_size, "sharding": self.sharding, "local_batch": local_batch,
                 "static_gib": {k: round(v / GIB, 3) for k, v in self.static.items()},
                 "static_total_gib": round(self.static_bytes() / GIB, 3),
                 "outside_caching_allocator_gib": round((self.static_bytes() - self.static_bytes(allocator_only=True)) / GIB, 3),
-                "activation_bytes_per_token": dict(self.per_token), "activation_gib_per_sample": round(self.activation_bytes(1) / GIB, 4),
+                "activation_bytes_per_token": {**self.per_token, "logits_up_to_chunk": self.logits_bytes_per_token},
+                "activation_gib_per_sample": round(self.activation_bytes(1) / GIB, 4),
                 "activations_gib": round(self.activation_bytes(local_batch) / GIB, 3), "workspace_gib": round(self.workspace / GIB, 3),
                 "total_gib": round(self.total_bytes(local_batch) / GIB, 3),
                 "max_memory_allocated_gib": round(self.total_bytes(local_batch, allocator_only=True) / GIB, 3), "notes": list(self.notes)}
@@ -102,23 +116,23 @@ def activation_bytes_per_token(model: ModelConfig, *, moe_row_factor: float = 1.
         router = model.num_experts * 4 * 3 + model.experts_per_token * 10          # fp32 logits, probabilities, gradients' inputs; routes
     else:
         ffn, router = 3 * i * low_bytes, 0
-    block = {"residual_and_normalised_inputs": 5 * h * low_bytes, "qkv": 3 * h * low_bytes, "feed_forward": int(ffn), "router": router,
+    # seven hidden-sized tensors per block: the block input, both normalised inputs, the attention output as the kernel wrote it
+    # and as the output projection reads it (made contiguous), the post-attention residual, and one more layout copy on the
+    # feed-forward side; five of them are what the operators need, two are copies (measured: the slope over the batch fits 7)
+    block = {"hidden_sized_tensors": 7 * h * low_bytes, "qkv": 3 * h * low_bytes, "feed_forward": int(ffn), "router": router,
              "statistics": 4 * (2 + model.n_heads)}
     if activation_checkpointing:
         # every block keeps its input; the tensors of ONE block exist while it is recomputed and differentiated
         parts = {"checkpointed_block_inputs": layers * h * low_bytes, "one_live_block": sum(block.values())}
     else:
         parts = {k: layers * v for k, v in block.items()}
-    # while a block is differentiated, the gradient of each of its saved tensors exists for a moment: one block's worth
-    parts["backward_transients_of_one_block"] = sum(block.values())
-    parts["final_norm"] = 2 * h * low_bytes
-    parts["logits"] = model.vocab_size * low_bytes
+    parts["final_norm_and_loss_input_gradient"] = 3 * h * low_bytes        # final norm's input and output; d(hidden) from the fused loss
     return parts
 
 
 def plan_memory(model: ModelConfig, *, strategy: str = "single", world_size: int = 1, sharding: str = "full_shard",
                 local_batch_hint: int = 1, activation_checkpointing: bool = False, ep_region_factor: float = 2.0,
-                low_bytes: int = LOW_BYTES) -> MemoryPlan:
+                low_bytes: int = LOW_BYTES, logits_chunk_rows: int = 65536) -> MemoryPlan:
     """Plan for the fused engine (``parallel.comm.engine: fused`` with ``backend.ops: native``).
 
     ``local_batch_hint`` only sizes the expert-parallel exchange regions, which the engine allocates for the batch it sees.
@@ -168,6 +182,10 @@ def plan_memory(model: ModelConfig, *, strategy: str = "single", world_size: int
                      f"({moe_row_factor:.2f} x the routes of this rank); regions sized for local batch {local_batch_hint}")
     per_token = activation_bytes_per_token(model, moe_row_factor=moe_row_factor, activation_checkpointing=activation_checkpointing,
                                            low_bytes=low_bytes)
+    if strategy == "ep":
+        # the combine keeps the rows it pulled back (one per route) for its backward pass
+        per_token["expert_parallel_pulled_rows"] = ((1 if activation_checkpointing else model.n_layers)
+                                                    * model.experts_per_token * model.hidden_size * low_bytes)
     # every expert's segment of the routing plan is padded to the GEMM's 256-row tile: on average half a tile per expert and layer
     extra = 0
     if model.is_moe:
@@ -176,9 +194,11 @@ def plan_memory(model: ModelConfig, *, strategy: str = "single", world_size: int
     if 4 * total > 0.5 * 180 * GIB:
         notes.append("the fp32 gradient buffer is full-size on every rank (4 bytes per parameter): it, not the optimizer state, "
                      "bounds the model size per 180 GB device")
+    loss_weight_gradient = 4 * model.vocab_size * model.hidden_size       # fp32 dW of the fused loss, made during the forward pass
     return MemoryPlan(strategy=strategy, world_size=w, sharding=sharding if strategy == "fsdp" else "n/a", tokens_per_sample=model.seq_len,
-                      static=static, symmetric=frozenset(symmetric), per_token=per_token, workspace=WORKSPACE_BYTES + extra,
-                      notes=tuple(notes))
+                      static=static, symmetric=frozenset(symmetric), per_token=per_token,
+                      logits_bytes_per_token=model.vocab_size * low_bytes, logits_chunk_rows=logits_chunk_rows,
+                      workspace=WORKSPACE_BYTES + extra + loss_weight_gradient, notes=tuple(notes))
 
 
 def memory_plan_event(cfg, *, world_size: int, device_bytes: float, headroom: float = 0.9) -> dict[str, object] | None:

@@ -282,7 +282,7 @@ def test_memory_plan_reproduces_the_measured_peaks():
     for model, strategy, world, sharding, batch, gib in measured:
         plan = plan_memory(model, strategy=strategy, world_size=world, sharding=sharding, local_batch_hint=batch)
         predicted = plan.total_bytes(batch, allocator_only=True) / GIB
-        assert predicted == pytest.approx(gib, rel=0.03), (strategy, world, sharding, batch, predicted, gib)
+        assert predicted == pytest.approx(gib, rel=0.02), (strategy, world, sharding, batch, predicted, gib)
         # what the allocator does not see: nothing on one rank, the symmetric buffers otherwise
         hidden = plan.total_bytes(batch) - plan.total_bytes(batch, allocator_only=True)
         assert (hidden == 0) == (world == 1) and hidden <= 7 * model.param_count() + plan.static.get("expert_exchange_regions", 0)
