@@ -12,8 +12,8 @@ The plan is arithmetic over the same rules the engine and the operators follow, 
   Expert parallelism keeps ``E / W`` experts per rank as rank-local units (24 bytes per parameter) and four exchange
   regions.
 * **activations** (what the autograd functions of ``ops/native_backend.py`` save), in bf16 per token and block: the block
-  input, the two normalised inputs, the fused QKV projection, the attention output (twice: as written and made contiguous
-  for the output projection), the post-attention residual and one more hidden-sized copy; for the feed-forward either
+  input, the two normalised inputs, the fused QKV projection and the rotated q and k beside it, the attention output, the
+  post-attention residual; for the feed-forward either
   ``gate, up, silu(gate) * up`` (dense) or, per route, the gathered row, the ``[gate | up]`` pre-activations, the SwiGLU
   output and the expert output (MoE); dropout saves nothing (masks are recomputed).  The peak is reached inside the fused
   loss at the end of the forward pass: on top of everything saved there are the bf16 logits of one chunk (at most 65,536
@@ -23,8 +23,7 @@ The plan is arithmetic over the same rules the engine and the operators follow, 
 Against ``max_memory_allocated`` of this repository's benchmark runs on B200 the plan is within 2.5 % on all sixteen
 recorded points: the 293M MoE on 1 to 8 GPUs at local batch 24 and 96 under both sharding modes, the 125M dense preset under
 ``ddp`` on 2, 4 and 8, the 125M MoE preset under ``fsdp`` and ``ep`` on 2 and 4 (``tests/test_runtime_cpu.py`` holds the points).
-One constant is fitted (``WORKSPACE_BYTES``, 0.15 GiB) and one count is taken from the measured slope (seven hidden-sized
-tensors per block where the operators need five); everything else is counted.  The reference has no counterpart: it finds the largest batch by running a sweep
+One constant is fitted (``WORKSPACE_BYTES``, 0.15 GiB); everything else is counted.  The reference has no counterpart: it finds the largest batch by running a sweep
 (benchmarks/distributed/workflow.py ``run_capacity``), which this repository's capacity suite also does; the plan says where
 to start that sweep and why a configuration does not fit.
 """
@@ -116,9 +115,9 @@ def activation_bytes_per_token(model: ModelConfig, *, moe_row_factor: float = 1.
         router = model.num_experts * 4 * 3 + model.experts_per_token * 10          # fp32 logits, probabilities, gradients' inputs; routes
     else:
         ffn, router = 3 * i * low_bytes, 0
-    # seven hidden-sized tensors per block: the block input, both normalised inputs, the attention output as the kernel wrote it
-    # and as the output projection reads it (made contiguous), the post-attention residual, and one more layout copy on the
-    # feed-forward side; five of them are what the operators need, two are copies (measured: the slope over the batch fits 7)
+    # seven hidden-sized tensors per block: the block input, both normalised inputs, the attention output, the post-attention
+    # residual, and the rotated q and k that the fused RoPE + attention node keeps beside the projection it was given
+    # (``_QKVAttentionFn`` saves ``qr, kr, fused``; recomputing the rotation in backward would trade them for two RoPE passes)
     block = {"hidden_sized_tensors": 7 * h * low_bytes, "qkv": 3 * h * low_bytes, "feed_forward": int(ffn), "router": router,
              "statistics": 4 * (2 + model.n_heads)}
     if activation_checkpointing:
