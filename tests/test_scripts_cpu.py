@@ -234,7 +234,8 @@ def test_committed_notebooks_equal_their_percent_format_sources_and_run(tmp_path
     spec.loader.exec_module(runner)
     cells = runner.percent_cells("#!/usr/bin/env python\n# %% [markdown]\n# # Title\n#\n# text\n\n# %%\nx = 1\n\n\n# %% named\nprint(x)\n")
     assert cells == [("markdown", "# Title\n\ntext"), ("code", "x = 1"), ("code", "print(x)")]
-    for name in ("training_walkthrough", "synbios_moe_walkthrough", "operator_benchmark_walkthrough", "distributed_benchmark_walkthrough"):
+    for name in ("training_walkthrough", "synbios_moe_walkthrough", "operator_benchmark_walkthrough", "distributed_benchmark_walkthrough",
+                 "planning_walkthrough"):
         source = root / "examples" / f"{name}.py"
         committed = json.loads((root / "examples" / "notebooks" / f"{name}.ipynb").read_text(encoding="utf-8"))
         assert committed == runner.notebook_from_script(source.read_text(encoding="utf-8")), f"regenerate {name}.ipynb with --export-ipynb"
@@ -252,6 +253,20 @@ def test_committed_notebooks_equal_their_percent_format_sources_and_run(tmp_path
     done = subprocess.run([sys.executable, str(root / "scripts" / "run_server_notebook.py"), str(root / "examples" / "training_walkthrough.py"),
                            "--export-ipynb", str(exported)], capture_output=True, text=True)
     assert done.returncode == 0 and json.loads(exported.read_text()) == json.loads(notebook.read_text())
+
+
+def test_planning_walkthrough_notebook_runs(tmp_path):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    done = subprocess.run([sys.executable, str(root / "scripts" / "run_server_notebook.py"), str(root / "examples" / "notebooks" / "planning_walkthrough.ipynb"),
+                           "--output", str(tmp_path / "run.json"), "--quiet"], capture_output=True, text=True, timeout=300, cwd=tmp_path)
+    assert done.returncode == 0, done.stderr[-2000:]
+    record = json.loads((tmp_path / "run.json").read_text())
+    assert record["failed_cells"] == [] and "walkthrough ok" in record["records"][-1]["stdout"]
 
 
 def test_operator_benchmark_walkthrough_runs_cell_by_cell_on_a_cpu(tmp_path):
