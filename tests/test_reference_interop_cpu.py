@@ -1,0 +1,177 @@
+"""Interoperability with the unmodified reference package (installed under ``baseline/_ref``; skipped where it is not):
+the same weights give the same numbers, the same seeds the same batches, the same schedule the same learning rates."""
+
+import contextlib
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+REF = ROOT / "baseline" / "_ref"
+pytestmark = pytest.mark.skipif(not (REF / "minitrain").is_dir(), reason="reference package not installed")
+
+
+@contextlib.contextmanager
+def reference_on_path():
+    sys.path.insert(0, str(REF))
+    try:
+        yield
+    finally:
+        sys.path.remove(str(REF))
+
+
+MODEL_SHAPES = {
+    "dense": dict(vocab_size=211, seq_len=24, n_layers=2, n_heads=4, hidden_size=64, intermediate_size=96, ffn_type="dense", dropout=0.0),
+    "moe": dict(vocab_size=211, seq_len=24, n_layers=2, n_heads=4, hidden_size=64, intermediate_size=48, ffn_type="moe", num_experts=4,
+                experts_per_token=2, dropout=0.0, tie_word_embeddings=True),
+}
+
+
+@pytest.mark.parametrize("kind", sorted(MODEL_SHAPES))
+def test_same_weights_give_the_same_loss_gradients_and_metrics(kind):
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+
+    with reference_on_path():
+        from minitrain.model.config import ModelConfig as RefConfig
+        from minitrain.model.ops import get_ops_backend as ref_backend
+        from minitrain.model.transformer import MiniTransformer as RefTransformer
+
+        torch.manual_seed(3)
+        theirs = RefTransformer(RefConfig(**MODEL_SHAPES[kind]), ref_backend("torch"))
+    ours = MiniTransformer(ModelConfig(**MODEL_SHAPES[kind]), get_ops_backend("torch"))
+    state = theirs.state_dict()
+    assert list(state) == list(ours.state_dict())                     # same names in the same order: checkpoints are exchangeable
+    ours.load_state_dict(state)
+    tokens = torch.randint(0, 211, (3, 25), generator=torch.Generator().manual_seed(4))
+    ids, targets = tokens[:, :-1], tokens[:, 1:]
+    for fused in (False, True):
+        for model in (theirs, ours):
+            model.zero_grad(set_to_none=True)
+        loss_t, _ = theirs(ids, targets=targets, use_fused_loss=fused)
+        loss_o, _ = ours(ids, targets=targets, use_fused_loss=fused)
+        assert float(loss_o.detach()) == pytest.approx(float(loss_t.detach()), abs=1e-6)
+        loss_t.backward()
+        loss_o.backward()
+        for (name, pt), (_, po) in zip(theirs.named_parameters(), ours.named_parameters()):
+            assert torch.allclose(po.grad, pt.grad, atol=2e-6, rtol=1e-5), (fused, name)
+    shared = set(theirs.last_training_metrics) & set(ours.last_training_metrics)
+    assert {"loss/lm_cross_entropy", "loss/total"} <= shared
+    for key in shared:
+        assert torch.allclose(ours.last_training_metrics[key].float(), theirs.last_training_metrics[key].float(), atol=1e-5), key
+    assert set(theirs.last_training_metrics) <= set(ours.last_training_metrics)        # every reference metric is published here too
+    _, logits_t = theirs(ids)
+    _, logits_o = ours(ids)
+    assert torch.allclose(logits_o, logits_t, atol=1e-5)
+
+
+def test_same_seed_gives_the_same_batches(tmp_path):
+    from mini_train_sys_b200.data.dataloader import (RandomizedDocumentBlockDataset, RandomizedDocumentSampler, ShardAwareBlockSampler,
+                                                     ShardedTokenBlockDataset)
+    from mini_train_sys_b200.data.preprocess import write_random_token_shards
+
+    shards = write_random_token_shards(tmp_path / "data", vocab_size=300, num_tokens=12_000, seed=1, document_tokens=211,
+                                       max_shard_tokens=2_500).parent
+    with reference_on_path():
+        from minitrain.data import dataloader as ref
+
+    for world in (1, 3):
+        for rank in range(world):
+            for epoch in (0, 2):
+                mine = ShardAwareBlockSampler(ShardedTokenBlockDataset(shards, split="train", seq_len=32), shuffle=True, seed=9, rank=rank,
+                                              world_size=world, shuffle_window=13)
+                theirs = ref.ShardAwareBlockSampler(ref.ShardedTokenBlockDataset(shards, split="train", seq_len=32), shuffle=True, seed=9,
+                                                    rank=rank, world_size=world, shuffle_window=13)
+                mine.set_epoch(epoch)
+                theirs.set_epoch(epoch)
+                assert list(mine) == list(theirs)
+                docs_mine = RandomizedDocumentSampler(RandomizedDocumentBlockDataset(shards, split="train", seq_len=32), shuffle=True, seed=9,
+                                                      rank=rank, world_size=world)
+                ref_ds = ref.RandomizedDocumentBlockDataset(shards, split="train", seq_len=32)
+                docs_theirs = ref.RandomizedDocumentSampler(ref_ds, shuffle=True, seed=9, rank=rank, world_size=world)
+                docs_mine.set_epoch(epoch)
+                docs_theirs.set_epoch(epoch)
+                a, b = list(docs_mine), list(docs_theirs)
+                assert [s.segments for s in a] == [tuple(map(tuple, s.segments)) for s in b]
+                first = docs_mine.dataset[a[0]]
+                assert torch.equal(first["input_ids"], ref_ds[b[0]]["input_ids"])
+
+
+def test_same_schedule_gives_the_same_learning_rates():
+    from mini_train_sys_b200.runtime.config import LRSchedulerConfig
+    from mini_train_sys_b200.train.lr_scheduler import LearningRateScheduler
+
+    with reference_on_path():
+        from minitrain.runtime.config import LRSchedulerConfig as RefSchedule
+        from minitrain.train.lr_scheduler import LearningRateScheduler as RefScheduler
+
+    for options in (dict(schedule="cosine", warmup_steps=7, min_lr_ratio=0.1), dict(schedule="constant", warmup_steps=3),
+                    dict(schedule="cosine", warmup_steps=0, decay_steps=20, min_lr_ratio=0.0)):
+        rates = []
+        for scheduler_type, config_type in ((LearningRateScheduler, LRSchedulerConfig), (RefScheduler, RefSchedule)):
+            optimizer = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=2e-3)
+            scheduler = scheduler_type(optimizer, config_type(**options), total_steps=40)
+            seen = []
+            for step in range(45):
+                scheduler.step(step)
+                seen.append(optimizer.param_groups[0]["lr"])
+            rates.append(seen)
+        assert rates[0] == pytest.approx(rates[1], rel=1e-12), options
+
+
+@pytest.mark.parametrize("writer", ["reference", "this repository"])
+def test_checkpoints_are_exchangeable_in_both_directions(tmp_path, writer):
+    """A checkpoint directory written by one package (weights, AdamW moments, counters) resumes in the other and the next
+    optimizer step gives the same loss: same layout (DCP payload, ``runtime.pt``, RNG side car, ``COMMITTED``), same keys."""
+
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+    from mini_train_sys_b200.train import checkpoint as ours_ckpt
+    from mini_train_sys_b200.train.optim import build_optimizer
+
+    with reference_on_path():
+        from minitrain.model.config import ModelConfig as RefConfig
+        from minitrain.model.ops import get_ops_backend as ref_backend
+        from minitrain.model.transformer import MiniTransformer as RefTransformer
+        from minitrain.train import checkpoint as ref_ckpt
+        from minitrain.train.optim import build_optimizer as ref_build_optimizer
+
+    shape = MODEL_SHAPES["moe"]
+    tokens = torch.randint(0, 211, (4, 4, 25), generator=torch.Generator().manual_seed(8))
+
+    def make(side):
+        torch.manual_seed(5)
+        if side == "reference":
+            model = RefTransformer(RefConfig(**shape), ref_backend("torch"))
+            return model, ref_build_optimizer(model, lr=1e-2, weight_decay=0.1)
+        model = MiniTransformer(ModelConfig(**shape), get_ops_backend("torch"))
+        return model, build_optimizer(model, lr=1e-2, weight_decay=0.1)
+
+    def step(model, optimizer, batch):
+        optimizer.zero_grad(set_to_none=True)
+        loss, _ = model(batch[:, :-1], targets=batch[:, 1:])
+        loss.backward()
+        optimizer.step()
+        return float(loss.detach())
+
+    reader = "this repository" if writer == "reference" else "reference"
+    module = {"reference": ref_ckpt, "this repository": ours_ckpt}
+    source_model, source_opt = make(writer)
+    for i in range(2):
+        step(source_model, source_opt, tokens[i])
+    path = tmp_path / "run" / "epoch_000001_step_000000002"
+    module[writer].save_checkpoint(path, source_model, source_opt, 2, epoch=1, tokens_seen=192, export_model=True)
+    assert {p.name for p in path.iterdir()} >= {"distributed", "runtime.pt", "COMMITTED", "model.pt", "rng_rank_00000.pt"}
+
+    target_model, target_opt = make(reader)
+    with torch.no_grad():
+        for p in target_model.parameters():
+            p.add_(1.0)                                   # make sure the restore is what equalises them
+    got = module[reader].restore_training_checkpoint(path, target_model, target_opt)
+    assert got["step"] == 2 and got["epoch"] == 1 and got["tokens_seen"] == 192
+    for (name, a), (_, b) in zip(source_model.named_parameters(), target_model.named_parameters()):
+        assert torch.equal(a, b), name
+    assert step(target_model, target_opt, tokens[2]) == pytest.approx(step(source_model, source_opt, tokens[2]), abs=1e-7)
+    assert step(target_model, target_opt, tokens[3]) == pytest.approx(step(source_model, source_opt, tokens[3]), abs=1e-6)   # moments came along
+    exported = module[reader].load_model_state_dict_from_checkpoint(path)
+    assert list(exported) == list(target_model.state_dict())
