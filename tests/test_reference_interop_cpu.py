@@ -175,3 +175,78 @@ def test_checkpoints_are_exchangeable_in_both_directions(tmp_path, writer):
     assert step(target_model, target_opt, tokens[3]) == pytest.approx(step(source_model, source_opt, tokens[3]), abs=1e-6)   # moments came along
     exported = module[reader].load_model_state_dict_from_checkpoint(path)
     assert list(exported) == list(target_model.state_dict())
+
+
+def test_tokenizer_and_shard_writer_produce_the_same_files(tmp_path):
+    """One corpus, one tokenizer directory: both packages load it (same fingerprint, same ids) and write byte-identical shards,
+    document indices and, apart from nothing, identical manifests."""
+
+    pytest.importorskip("tokenizers")
+    import json
+
+    from mini_train_sys_b200.data.documents import CleaningConfig
+    from mini_train_sys_b200.data.preprocess import prepare_token_shards
+    from mini_train_sys_b200.data.tokenizer import ByteLevelBPETokenizer, load_tokenizer
+
+    with reference_on_path():
+        from minitrain.data.documents import CleaningConfig as RefCleaning
+        from minitrain.data.preprocess import prepare_token_shards as ref_prepare
+        from minitrain.data.tokenizer import load_tokenizer as ref_load_tokenizer
+
+    words = ["alpha", "beta", "gamma", "delta", "epsilon", "zeta", "eta", "theta", "iota", "kappa", "Zürich", "naïve"]
+    gen = torch.Generator().manual_seed(2)
+    texts = [" ".join(words[int(i)] for i in torch.randint(0, len(words), (int(n),), generator=gen)) + f". Document {d}."
+             for d, n in enumerate(torch.randint(20, 400, (120,), generator=gen))]
+    texts.append(texts[0])                                                       # an exact duplicate: both cleaners must drop it
+    corpus = tmp_path / "docs.jsonl"
+    corpus.write_text("\n".join(json.dumps({"id": f"d{i}", "text": t}) for i, t in enumerate(texts)), encoding="utf-8")
+    tokenizer = ByteLevelBPETokenizer.train_from_iterator(iter(texts), vocab_size=400)
+    tokenizer.save(tmp_path / "tok")
+    mine, theirs = load_tokenizer(tmp_path / "tok"), ref_load_tokenizer(tmp_path / "tok")
+    assert mine.fingerprint == theirs.fingerprint and mine.vocab_size == theirs.vocab_size and mine.boundary_token_id == theirs.boundary_token_id
+    assert all(mine.encode(t) == theirs.encode(t) for t in texts[:10])
+
+    options = dict(max_document_chars=900, max_shard_tokens=3000, validation_fraction=0.1, split_seed=7)
+    ours_manifest = prepare_token_shards([corpus], output_dir=tmp_path / "ours", tokenizer=mine, cleaning=CleaningConfig(min_chars=8), **options)
+    ref_manifest = ref_prepare([corpus], output_dir=tmp_path / "theirs", tokenizer=theirs, cleaning=RefCleaning(min_chars=8), **options)
+    a, b = json.loads(Path(ours_manifest).read_text()), json.loads(Path(ref_manifest).read_text())
+    assert a == b                                                                 # dtype, counts, sha256 of every shard and index, cleaning statistics
+    assert a["cleaning_stats"]["rejected_duplicate"] == 1 and len(a["splits"]["train"]["shards"]) > 1
+    for split in ("train", "validation"):
+        for record in [*a["splits"][split]["shards"], a["splits"][split]["document_index"]]:
+            assert (tmp_path / "ours" / record["path"]).read_bytes() == (tmp_path / "theirs" / record["path"]).read_bytes(), record["path"]
+
+
+def test_run_files_resolve_to_the_same_settings_in_both_loaders():
+    """Every shipped run file that the reference's loader accepts resolves (``extends`` included) to the same values here, key
+    by key, for the keys the reference knows."""
+
+    from dataclasses import asdict
+
+    from mini_train_sys_b200.runtime.config import load_experiment
+
+    with reference_on_path():
+        from minitrain.runtime.config import experiment_config_from_dict as ref_from_dict
+        from minitrain.runtime.config import load_yaml_dict as ref_yaml
+
+    def ref_load(path):
+        return ref_from_dict(ref_yaml(path))
+
+    compared = 0
+    for path in sorted((ROOT / "configs").rglob("*.yaml")):
+        try:
+            theirs = ref_load(path)
+        except Exception:                      # model files, fragments, and run files that use this repository's additions
+            continue
+        ours = load_experiment(path)
+        for section, value in asdict(theirs).items():
+            mine = getattr(ours, section)
+            mine = mine if isinstance(mine, dict) else asdict(mine)
+            for key, expected in (value.items() if isinstance(value, dict) else ()):
+                if isinstance(expected, dict):                 # parallel.ddp / parallel.fsdp
+                    for inner, inner_expected in expected.items():
+                        assert mine[key][inner] == inner_expected, (path.name, section, key, inner)
+                else:
+                    assert mine[key] == expected, (path.name, section, key)
+        compared += 1
+    assert compared >= 20, compared
