@@ -250,3 +250,59 @@ def test_run_files_resolve_to_the_same_settings_in_both_loaders():
                     assert mine[key] == expected, (path.name, section, key)
         compared += 1
     assert compared >= 20, compared
+
+
+def _run_reference(code: str, *args: str) -> str:
+    """Run ``code`` in a process that sees only the reference package (its ``experiments`` package has the same name as ours)."""
+
+    import os
+    import subprocess
+
+    env = {**os.environ, "PYTHONPATH": str(REF)}
+    done = subprocess.run([sys.executable, "-c", code, *args], capture_output=True, text=True, timeout=600, env=env, cwd=str(REF))
+    assert done.returncode == 0, done.stderr[-3000:]
+    return done.stdout
+
+
+def test_study_layer_contracts_and_a_reference_dataset_feeds_our_tools(tmp_path):
+    """The study layer keeps the reference's contracts (variants, attribute order, template counts, pool sizes, person split),
+    and a dataset written by the reference's generator goes through this repository's cache builder, validator, statistics
+    and lineage audit unchanged."""
+
+    import json
+
+    from experiments.synbios_moe.audit import audit_dataset
+    from experiments.synbios_moe.artifact_io import read_jsonl
+    from experiments.synbios_moe.codec import get_codec
+    from experiments.synbios_moe.pretraining import dataset as ours
+    from experiments.synbios_moe.pretraining.token_statistics import dataset_token_statistics
+    from experiments.synbios_moe.probes.dataset import build_probe_cache, validate_probe_cache
+
+    out = tmp_path / "reference_data"
+    facts = json.loads(_run_reference(
+        "import json, sys\n"
+        "from experiments.synbios_moe.pretraining import dataset as d\n"
+        "d.write_dataset(sys.argv[1], num_people=30, variant='multi2+permute', seed=5)\n"
+        "pools = d.candidate_pools()\n"
+        "variants = ['single', 'single+fullname', 'single+permute1', 'single+permute5', 'multi2', 'multi5', 'multi2+permute', 'multi5+permute', 'multi5+permute+fullname']\n"
+        "print(json.dumps({'attributes': list(d.ATTRIBUTES), 'templates': list(d.TEMPLATE_COUNTS), 'pools': {k: len(v) for k, v in pools.items()},\n"
+        "                  'entries': {v: d.entries_per_person(v) for v in variants},\n"
+        "                  'split': [d.split_for_person(i, 1337) for i in range(200)]}))\n", str(out)))
+    assert facts["attributes"] == list(ours.ATTRIBUTES) and facts["templates"] == [ours.TEMPLATE_COUNTS[a] for a in ours.ATTRIBUTES]
+    assert facts["entries"] == {v: ours.entries_per_person(v) for v in ours.VARIANTS}
+    assert facts["split"] == [ours.split_for_person(i, 1337) for i in range(200)]
+    mine = {k: len(v) for k, v in ours.candidate_pools().items()}
+    assert {k: mine[k] for k in facts["pools"] if k in mine} == {k: v for k, v in facts["pools"].items() if k in mine} and len(mine) >= 5
+
+    rows = list(read_jsonl(out / "biographies.jsonl"))
+    assert len(rows) == 60 and set(rows[0]["attribute_spans"]) == set(ours.ATTRIBUTES)
+    lo, hi = rows[0]["attribute_spans"]["university"]
+    profile = next(p for p in read_jsonl(out / "profiles.jsonl") if p["person_id"] == rows[0]["person_id"])
+    assert rows[0]["text"][lo:hi] == profile["university"]
+    cache = build_probe_cache(out, tmp_path / "cache", codec_name="bytes")
+    report = validate_probe_cache(cache, out)
+    assert report["ok"], report
+    stats = dataset_token_statistics(get_codec("bytes"), read_jsonl(out / "biographies.jsonl"), read_jsonl(out / "profiles.jsonl"))
+    assert stats["biographies"] == 60
+    problems = audit_dataset(out)
+    assert problems == [], problems
