@@ -306,3 +306,38 @@ def test_study_layer_contracts_and_a_reference_dataset_feeds_our_tools(tmp_path)
     assert stats["biographies"] == 60
     problems = audit_dataset(out)
     assert problems == [], problems
+
+
+@pytest.mark.parametrize("kind", ["p", "q"])
+def test_probe_heads_are_exchangeable(tmp_path, kind):
+    """A probe of the reference (backbone weights, rank-r embedding change, normaliser, classifier) loads into this
+    repository's probe class under the same names and reads out the same logits."""
+
+    from experiments.synbios_moe.probes.model import AttributeProbe
+    from mini_train_sys_b200.models import MiniTransformer, ModelConfig, get_ops_backend
+
+    blob = tmp_path / "probe.pt"
+    _run_reference(
+        "import sys, torch\n"
+        "from minitrain.model.config import ModelConfig\n"
+        "from minitrain.model.ops import get_ops_backend\n"
+        "from minitrain.model.transformer import MiniTransformer\n"
+        "from experiments.synbios_moe.probes.model import AttributeProbe\n"
+        "shape = dict(vocab_size=211, seq_len=24, n_layers=2, n_heads=4, hidden_size=64, intermediate_size=48, ffn_type='moe', num_experts=4, experts_per_token=2, dropout=0.0)\n"
+        "torch.manual_seed(11)\n"
+        "probe = AttributeProbe(MiniTransformer(ModelConfig(**shape), get_ops_backend('torch')), 9, rank=3, kind=sys.argv[2])\n"
+        "torch.nn.init.normal_(probe.delta.b.weight, std=0.5)\n"
+        "probe.eval()\n"
+        "ids = torch.randint(0, 211, (5, 20)); positions = torch.randint(0, 20, (5, 6 if sys.argv[2] == 'p' else 1))\n"
+        "with torch.no_grad():\n"
+        "    logits = probe(ids, positions)\n"
+        "torch.save({'shape': shape, 'state': probe.state_dict(), 'ids': ids, 'positions': positions, 'logits': logits}, sys.argv[1])\n",
+        str(blob), kind)
+    data = torch.load(blob, weights_only=False)
+    probe = AttributeProbe(MiniTransformer(ModelConfig(**data["shape"]), get_ops_backend("torch")), 9, rank=3, kind=kind)
+    assert list(probe.state_dict()) == list(data["state"])
+    probe.load_state_dict(data["state"])
+    probe.eval()
+    with torch.no_grad():
+        logits = probe(data["ids"], data["positions"])
+    assert logits.shape == data["logits"].shape and torch.allclose(logits, data["logits"], atol=1e-5)
