@@ -341,3 +341,33 @@ def test_probe_heads_are_exchangeable(tmp_path, kind):
     with torch.no_grad():
         logits = probe(data["ids"], data["positions"])
     assert logits.shape == data["logits"].shape and torch.allclose(logits, data["logits"], atol=1e-5)
+
+
+def test_console_lines_are_the_reference_s_lines():
+    """Tools that grep the console log of a run keep working: the same event payload prints the same line in both packages."""
+
+    from mini_train_sys_b200.runtime.logger import format_console_event
+
+    with reference_on_path():
+        from minitrain.runtime.logger import format_console_event as ref_format
+
+    train = {"event": "train", "step": 120, "step_total": 1000, "epoch": 2, "epochs_total": 10, "batch": 20, "batches_total": 100, "loss": 3.14159,
+             "lr": 3e-4, "grad_norm": 1.2345, "tokens_per_sec": 123456.7, "data_wait_percent": 0.4, "progress_percent": 12.0, "eta_seconds": 3725.0,
+             "elapsed_seconds": 100.0, "tokens_seen": 5_000_000, "tokens_goal": 40_000_000, "gpu_peak_memory_allocated_mb": 30500.0,
+             "gpu_memory_allocated_mb": 20000.0, "gpu_compute_utilization_percent_mean": 97.0, "host_peak_memory_mb": 12.5}
+    payloads = [train, {k: v for k, v in train.items() if not k.startswith("gpu_")},
+                {"event": "checkpoint", "path": "ckpt/x/epoch_000001_step_000000100"},
+                {"event": "resume", "path": "ckpt/x", "epoch": 1, "step": 100, "saved_world_size": 4},
+                {"event": "init", "run": "r", "device": "cuda:0", "parallel": "fsdp", "world_size": 8, "params": 293494272},
+                {"event": "probe_train", "step": 10, "steps_total": 100, "loss": 1.5, "accuracy_running": 0.5, "progress_percent": 10.0, "eta_seconds": 50},
+                {"event": "probe_validation", "example": 40, "examples_total": 400, "accuracy_running": 0.25, "progress_percent": 10.0, "eta_seconds": 9},
+                {"event": "evaluate", "batch": 3, "batches_total": 30, "progress_percent": 10.0, "eta_seconds": 5},
+                {"event": "probe_checkpoint", "step": 10, "steps_total": 100, "path": "p.pt"},
+                {"event": "probe_pipeline", "phase": "training", "step": 3, "steps_total": 22, "tasks_running": 2, "tasks_queued": 17, "tasks_failed": 0,
+                 "task": "p-major-first", "action": "finished", "device": "cuda:1", "eta_seconds": 600},
+                {"event": "parallel_ready", "strategy": "fsdp", "fsdp_units": 13}]
+    for payload in payloads:
+        assert format_console_event(payload) == ref_format(payload), payload["event"]
+    # what this repository adds to a train event shows up as an extra cell and changes nothing else
+    extended = format_console_event({**train, "mfu_percent": 41.2})
+    assert "mfu 41.2%" in extended and extended.replace(" | mfu 41.2%", "") == ref_format(train)
