@@ -223,6 +223,9 @@ class BenchmarkSettings:
     master_port: int = 29541
     reuse_stale_results: bool = False
     reuse_failures: bool = False
+    rerun_existing: bool = False                  # measure every case again although a stored result matches
+    memory_limit: float = 0.92                    # capacity suite: share of device memory a candidate batch may reserve
+    min_repeats: int = 2                          # capacity and backend suites: repeats a row needs to count
     env: dict[str, str] = field(default_factory=dict)
 
 
@@ -341,7 +344,8 @@ def run_suite(settings: BenchmarkSettings, suite: str, script: Path) -> dict[str
                                                   repeat=repeat, fingerprint=fingerprint)
                             path = raw / f"{name}.json"
                             prev = json.loads(path.read_text()) if path.exists() else None
-                            reusable = prev is not None and (prev.get("identity") == ident or settings.reuse_stale_results) and \
+                            reusable = prev is not None and not settings.rerun_existing and \
+                                (prev.get("identity") == ident or settings.reuse_stale_results) and \
                                 (prev.get("status") == "ok" or settings.reuse_failures)
                             if reusable:
                                 rec = prev
@@ -357,9 +361,9 @@ def run_suite(settings: BenchmarkSettings, suite: str, script: Path) -> dict[str
     if suite == "weak":
         summary["weak"] = weak_scaling_table(rows)
     elif suite == "capacity":
-        summary["capacity"] = present_capacity(rows)
+        summary["capacity"] = present_capacity(rows, memory_limit=settings.memory_limit, min_repeats=settings.min_repeats)
     else:
-        summary["backend"] = present_backend(rows)
+        summary["backend"] = present_backend(rows, min_repeats=settings.min_repeats)
     summary["quality_gates"] = quality_gates(summary, repeats=settings.repeats)
     (out_dir / "summary.json").write_text(json.dumps(summary, indent=1, default=str))
     return summary

@@ -81,14 +81,23 @@ def non_portable_paths(root: Path, *, limit_per_file: int = 3) -> list[str]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("root")
+    ap.add_argument("root", nargs="?")
+    ap.add_argument("--results", help="the results tree (same as the positional argument; default: results)")
+    ap.add_argument("--artifacts", help="accepted for the reference's command lines: the audit reads the results tree only")
+    ap.add_argument("--repo-root", help="accepted for the reference's command lines")
+    ap.add_argument("--output", help="also write the report as JSON to this file")
     ap.add_argument("--strict-paths", action="store_true", help="machine paths inside exported text files fail the audit")
     args = ap.parse_args(argv)
-    problems = audit(Path(args.root))
-    stray = non_portable_paths(Path(args.root))
+    root = Path(args.root or args.results or "results")
+    problems = audit(root)
+    stray = non_portable_paths(root)
     if args.strict_paths:
         problems += [f"machine path in {item}" for item in stray]
-    print(json.dumps({"ok": not problems, "problems": problems, "non_portable": stray}, indent=1))
+    report = json.dumps({"ok": not problems, "problems": problems, "non_portable": stray}, indent=1)
+    if args.output:
+        Path(args.output).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.output).write_text(report + "\n", encoding="utf-8")
+    print(report)
     return 0 if not problems else 1
 
 

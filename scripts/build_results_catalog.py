@@ -50,10 +50,12 @@ def describe(path: Path) -> dict | None:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("root")
+    ap.add_argument("root", nargs="?")
+    ap.add_argument("--results", help="the results tree (same as the positional argument; default: results)")
+    ap.add_argument("--artifacts", help="accepted for the reference's command lines: what is catalogued here is the results tree only")
     ap.add_argument("--output", default=None)
     args = ap.parse_args(argv)
-    root = Path(args.root)
+    root = Path(args.root or args.results or "results")
     entries = [e for p in sorted(root.rglob("*")) if p.is_file() and p.name not in ("CATALOG.json", "CATALOG.md") for e in [describe(p)] if e]
     for entry in entries:      # the catalogue travels with the tree: paths are relative to it, and the root is named, not located
         entry["path"] = Path(entry["path"]).relative_to(root).as_posix()

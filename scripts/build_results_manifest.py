@@ -33,10 +33,11 @@ def build(root: Path) -> dict[str, dict]:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("root")
+    ap.add_argument("root", nargs="?")
+    ap.add_argument("--results", help="the results tree (same as the positional argument; default: results)")
     ap.add_argument("--check", action="store_true")
     args = ap.parse_args(argv)
-    root = Path(args.root)
+    root = Path(args.root or args.results or "results")
     current = build(root)
     path = root / NAME
     if not args.check:

@@ -39,14 +39,19 @@ def resolve_inputs(items: list[str]) -> list[Path]:
 
 
 def cleaning_from(args) -> CleaningConfig:
-    return CleaningConfig(enabled=not args.no_clean, min_chars=args.min_chars, exact_dedup=not args.no_dedup)
+    return CleaningConfig(enabled=not args.no_clean, min_chars=args.min_chars, min_alpha_ratio=args.min_alpha_ratio,
+                          max_control_ratio=args.max_control_ratio, max_repeated_line_fraction=args.max_repeated_line_fraction,
+                          exact_dedup=not args.no_dedup)
 
 
 def add_cleaning_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--text-field", default="text")
     ap.add_argument("--no-clean", action="store_true")
-    ap.add_argument("--no-dedup", action="store_true")
+    ap.add_argument("--no-dedup", "--no-exact-dedup", dest="no_dedup", action="store_true")
     ap.add_argument("--min-chars", type=int, default=32)
+    ap.add_argument("--min-alpha-ratio", type=float, default=0.05, help="letters among the visible characters")
+    ap.add_argument("--max-control-ratio", type=float, default=0.01, help="control characters in the raw text")
+    ap.add_argument("--max-repeated-line-fraction", type=float, default=0.5)
     ap.add_argument("--max-document-chars", type=int, default=100_000)
 
 

@@ -69,7 +69,10 @@ def _parser() -> argparse.ArgumentParser:
     r.add_argument("--repeats", type=int, default=2)
     r.add_argument("--warmup-steps", type=int, default=5)
     r.add_argument("--measure-steps", type=int, default=20)
-    r.add_argument("--timeout", type=float, default=1800.0)
+    r.add_argument("--timeout", "--case-timeout-seconds", dest="timeout", type=float, default=1800.0, help="limit per case (seconds)")
+    r.add_argument("--rerun-existing", action="store_true", help="measure every case again although a stored result has the same identity")
+    r.add_argument("--memory-limit-percent", type=float, default=92.0, help="capacity suite: share of device memory a candidate batch may reserve")
+    r.add_argument("--min-repeats", type=int, default=2, help="capacity and backend suites: repeats a row needs to count")
     r.add_argument("--master-port", type=int, default=29541)
     r.add_argument("--reuse-stale-results", action="store_true")
     r.add_argument("--reuse-failures", action="store_true")
@@ -113,7 +116,8 @@ def main(argv=None) -> int:
             config=args.config, model_config=args.model_config, output_dir=args.output_dir, strategies=args.strategies,
             world_sizes=args.world_sizes, ops_backends=args.ops_backends, engines=args.engines, batch_sizes=args.batch_sizes,
             repeats=args.repeats, warmup_steps=args.warmup_steps, measure_steps=args.measure_steps, timeout_s=args.timeout,
-            master_port=args.master_port, reuse_stale_results=args.reuse_stale_results, reuse_failures=args.reuse_failures)
+            master_port=args.master_port, reuse_stale_results=args.reuse_stale_results, reuse_failures=args.reuse_failures,
+            rerun_existing=args.rerun_existing, memory_limit=args.memory_limit_percent / 100.0, min_repeats=args.min_repeats)
         summary = db.run_suite(settings, args.suite, Path(__file__).resolve())
         key = args.suite
         body = summary[key]["selected"] if key == "capacity" else summary[key]

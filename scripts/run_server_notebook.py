@@ -103,7 +103,33 @@ def _strip_magics(source: str) -> str:
     return "".join(("# " + line) if line.lstrip().startswith(("%", "!")) else line for line in source.splitlines(keepends=True))
 
 
-def run_cells(cells: list[str], *, filename: str, keep_going: bool = False, echo: bool = False) -> list[dict]:
+class CellTimeout(Exception):
+    pass
+
+
+@contextlib.contextmanager
+def _cell_deadline(seconds: float):
+    """Raise ``CellTimeout`` inside the cell when it runs longer than ``seconds`` (main thread, POSIX timers; <= 0: no limit)."""
+
+    import signal
+
+    if seconds is None or seconds <= 0 or not hasattr(signal, "setitimer"):
+        yield
+        return
+
+    def expired(signum, frame):
+        raise CellTimeout(f"cell ran longer than {seconds:g} s")
+
+    previous = signal.signal(signal.SIGALRM, expired)
+    signal.setitimer(signal.ITIMER_REAL, seconds)
+    try:
+        yield
+    finally:
+        signal.setitimer(signal.ITIMER_REAL, 0)
+        signal.signal(signal.SIGALRM, previous)
+
+
+def run_cells(cells: list[str], *, filename: str, keep_going: bool = False, echo: bool = False, timeout_seconds: float = -1) -> list[dict]:
     namespace: dict = {"__name__": "__main__", "__file__": filename}
     records = []
     for index, source in enumerate(cells):
@@ -112,7 +138,7 @@ def run_cells(cells: list[str], *, filename: str, keep_going: bool = False, echo
         record = {"cell": index, "source": source, "status": "ok", "error": None}
         try:
             code = compile(_strip_magics(source), f"{filename}#cell{index}", "exec")
-            with contextlib.redirect_stdout(out), contextlib.redirect_stderr(err):
+            with contextlib.redirect_stdout(out), contextlib.redirect_stderr(err), _cell_deadline(timeout_seconds):
                 exec(code, namespace)      # noqa: S102 - executing the user's own walkthrough is the purpose of this tool
         except SystemExit as exc:          # a walkthrough that ends with sys.exit(main())
             if exc.code not in (None, 0):
@@ -157,6 +183,10 @@ def main(argv=None) -> int:
     ap.add_argument("--executed-notebook", type=Path, help="for .ipynb inputs: write a copy with the outputs filled in")
     ap.add_argument("--export-ipynb", type=Path, help="for .py inputs: write the cells as a notebook and exit without running them")
     ap.add_argument("--keep-going", action="store_true", help="run the remaining cells after a failure")
+    ap.add_argument("--output-dir", type=Path, help="write <name>.run.json and, for notebooks, <name>.executed.ipynb into this directory "
+                                                    "(the reference's option; --output / --executed-notebook name the files one by one)")
+    ap.add_argument("--timeout-seconds", type=float, default=-1, help="limit per cell; -1: none")
+    ap.add_argument("--kernel", help="accepted for the reference's command lines: cells run in this process, no Jupyter kernel is started")
     ap.add_argument("--quiet", action="store_true")
     args = ap.parse_args(argv)
     path = args.walkthrough.resolve()
@@ -166,10 +196,14 @@ def main(argv=None) -> int:
         print(json.dumps({"notebook": str(args.export_ipynb), "cells": export_notebook(path, args.export_ipynb)}))
         return 0
     cells = load_cells(path)
-    records = run_cells(cells, filename=str(path), keep_going=args.keep_going, echo=not args.quiet)
+    records = run_cells(cells, filename=str(path), keep_going=args.keep_going, echo=not args.quiet, timeout_seconds=args.timeout_seconds)
     failed = [r["cell"] for r in records if r["status"] == "error"]
     report = {"walkthrough": str(path), "cells": len(cells), "executed": len(records), "failed_cells": failed,
               "seconds": round(sum(r["seconds"] for r in records), 3), "records": records}
+    if args.output_dir is not None:
+        args.output = args.output or args.output_dir / f"{path.stem}.run.json"
+        if path.suffix == ".ipynb" and args.executed_notebook is None:
+            args.executed_notebook = args.output_dir / f"{path.stem}.executed.ipynb"
     output = args.output or path.with_suffix(".run.json")
     output.parent.mkdir(parents=True, exist_ok=True)
     output.write_text(json.dumps(report, indent=1), encoding="utf-8")

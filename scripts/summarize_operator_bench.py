@@ -18,22 +18,46 @@ sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 def summarize(directory: str | Path) -> dict:
     from mini_train_sys_b200.bench import operators
 
-    results = []
-    for path in sorted(Path(directory).glob("*.json")):
-        results += list(json.loads(path.read_text()).values())
+    results = _records(directory)
     return {"table": operators.headline_table(results), "quality_gate": operators.quality_gate(results)}
+
+
+def _records(source) -> list[dict]:
+    """Case records of one source: a cache directory, or a single cache / record file."""
+
+    path = Path(source)
+    files = sorted(path.glob("*.json")) if path.is_dir() else [path] if path.is_file() else []
+    records = []
+    for file in files:
+        data = json.loads(file.read_text())
+        if isinstance(data, dict) and "rows" in data and "status" in data:
+            records.append(data)                                    # one case record
+        elif isinstance(data, dict):
+            records += [v for v in data.values() if isinstance(v, dict) and "rows" in v]
+    return records
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("directory", help="cache directory written by `bench_ops.py run --out`")
-    ap.add_argument("--output", help="write {table, quality_gate} as JSON")
+    ap.add_argument("directory", nargs="?", help="cache directory written by `bench_ops.py run --out`")
+    # the reference keeps its sweeps in separate places and names each; here they are further sources merged into one table
+    for name in ("dense", "moe", "extensions", "capacity"):
+        ap.add_argument(f"--{name}", help="a further cache directory or file (the reference's per-sweep option)")
+    ap.add_argument("--output", help="write {table, quality_gate} as JSON (a directory gets summary.json)")
     ap.add_argument("--plots", help="directory for one SVG per kernel")
     args = ap.parse_args(argv)
-    summary = summarize(args.directory)
+    sources = [s for s in (args.directory, args.dense, args.moe, args.extensions, args.capacity) if s]
+    if not sources:
+        ap.error("give a cache directory, or --dense / --moe / --extensions / --capacity")
+    from mini_train_sys_b200.bench import operators
+
+    results = [record for source in sources for record in _records(source)]
+    summary = {"table": operators.headline_table(results), "quality_gate": operators.quality_gate(results)}
     if args.output:
-        Path(args.output).parent.mkdir(parents=True, exist_ok=True)
-        Path(args.output).write_text(json.dumps(summary, indent=1))
+        target = Path(args.output)
+        target = target / "summary.json" if target.is_dir() or not target.suffix else target
+        target.parent.mkdir(parents=True, exist_ok=True)
+        target.write_text(json.dumps(summary, indent=1))
     if args.plots:
         from mini_train_sys_b200.bench.plots import write_kernel_plots
 

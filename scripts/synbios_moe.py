@@ -73,18 +73,39 @@ def load_backbone(model_config: str, checkpoint: str, device: str, *, codec_voca
 class EventSink:
     """``events.jsonl`` under ``--log-dir`` (the scheduler's heartbeat source) plus optional console lines."""
 
-    def __init__(self, log_dir: str | None, quiet: bool) -> None:
+    def __init__(self, log_dir: str | None, quiet: bool, *, log_interval: int = 1, tensorboard: bool = False) -> None:
         self.quiet = quiet
+        self.log_interval = max(int(log_interval or 1), 1)
         self.handle = None
+        self.writer = None
         if log_dir:
             Path(log_dir).mkdir(parents=True, exist_ok=True)
             self.handle = open(Path(log_dir) / "events.jsonl", "a", buffering=1)
+            if tensorboard:
+                try:
+                    from torch.utils.tensorboard import SummaryWriter
+
+                    self.writer = SummaryWriter(log_dir=str(log_dir))
+                except Exception:       # noqa: BLE001 - event files are an extra; the JSONL log is the record
+                    self.writer = None
+
+    @classmethod
+    def from_args(cls, args) -> "EventSink":
+        return cls(getattr(args, "log_dir", None), getattr(args, "quiet", False), log_interval=getattr(args, "log_interval", 1) or 1,
+                   tensorboard=bool(getattr(args, "tensorboard", False)))
 
     def __call__(self, event: dict) -> None:
         event = {"time": time.time(), **event}
         if self.handle:
             self.handle.write(json.dumps(event, default=str) + "\n")
-        if not self.quiet:
+        step = event.get("step")
+        if self.writer is not None and isinstance(step, int):
+            for key, value in event.items():
+                if key not in ("time", "step") and isinstance(value, (int, float)) and not isinstance(value, bool):
+                    self.writer.add_scalar(f"{event.get('event', 'event')}/{key}", value, step)
+        # the console shows every log_interval-th progress event (and every event that is not a progress event); the file all
+        thin = isinstance(step, int) and self.log_interval > 1 and step % self.log_interval != 0 and step != event.get("steps_total")
+        if not self.quiet and not thin:
             print(json.dumps(event, default=str), flush=True)
 
 
@@ -103,7 +124,7 @@ def cmd_prepare(args) -> int:
     from mini_train_sys_b200.data.documents import CleaningConfig
     from mini_train_sys_b200.data.preprocess import prepare_token_shards
 
-    sink = EventSink(args.log_dir, args.quiet)
+    sink = EventSink.from_args(args)
     out = write_dataset(args.output, num_people=args.num_people, variant=args.variant, seed=args.seed)
     sink({"event": "dataset_written", "path": str(out)})
     if args.codec == "gpt2":
@@ -206,7 +227,11 @@ def cmd_summarize_cloze(args) -> int:
     from experiments.synbios_moe.artifact_io import read_json, write_csv
     from experiments.synbios_moe.pretraining.cloze import summarize_cloze
 
-    rows = summarize_cloze({Path(p).stem: read_json(p) for p in args.reports})
+    reports = [*args.reports, *args.run]
+    if not reports:
+        print(json.dumps({"error": "give cloze reports as arguments or with --run"}))
+        return 2
+    rows = summarize_cloze({Path(p).stem: read_json(p) for p in reports})
     write_csv(args.output, rows, ["run", "attribute", "exact_match", "first_token", "token_accuracy", "items"])
     print(json.dumps({"rows": len(rows), "output": args.output}))
     return 0
@@ -216,7 +241,7 @@ def cmd_probe(args) -> int:
     from experiments.synbios_moe.artifact_io import sha256_file
     from experiments.synbios_moe.probes.model import active_parameter_estimate, save_probe_result, train_probe
 
-    sink = EventSink(args.log_dir, args.quiet)
+    sink = EventSink.from_args(args)
     codec = _codec(args)
     model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
     cache = args.probe_cache or str(Path(args.data) / "probe_cache")
@@ -241,7 +266,19 @@ def cmd_validate_probe(args) -> int:
 
     codec = _codec(args)
     model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
-    verdict = validate_saved_probe(model, args.probe_cache, args.probe_state, device=args.device, max_items=args.max_eval_items)
+    import torch as _torch
+
+    from experiments.synbios_moe.artifact_io import sha256_file
+
+    trained_on = (_torch.load(args.probe_state, map_location="cpu", weights_only=False).get("identity") or {}).get("checkpoint_sha256")
+    if trained_on and not args.allow_checkpoint_mismatch:
+        current = args.checkpoint_model_sha256 or sha256_file(args.checkpoint)
+        if current != trained_on:
+            print(json.dumps({"error": "the probe was trained on another backbone checkpoint (pass --allow-checkpoint-mismatch to evaluate anyway)",
+                              "probe_checkpoint_sha256": trained_on, "given_checkpoint_sha256": current}))
+            return 3
+    verdict = validate_saved_probe(model, args.probe_cache, args.probe_state, device=args.device, batch_size=args.batch_size,
+                                   max_items=args.max_eval_items)
     write_json(args.output, verdict)
     if not args.quiet:
         print(json.dumps(verdict["validation"]))
@@ -261,7 +298,29 @@ def cmd_probe_pipeline(args) -> int:
 
     settings = yaml.safe_load(Path(args.config).read_text()) if args.config else {}
     stage = settings.get("stages", {}).get(args.stage, {})
-    runtime = settings.get("runtime", {})
+    runtime = dict(settings.get("runtime", {}))
+    # command-line overrides of the pipeline file (the reference's option names)
+    if args.num_gpus:
+        args.devices = ",".join(f"cuda:{i}" for i in range(args.num_gpus))
+    for kind in ("p", "q"):
+        if getattr(args, f"{kind}_batch_size"):
+            runtime["training_batch_sizes"] = {**runtime.get("training_batch_sizes", {}), kind: getattr(args, f"{kind}_batch_size")}
+        if getattr(args, f"{kind}_validation_batch_size"):
+            runtime["validation_batch_sizes"] = {**runtime.get("validation_batch_sizes", {}), kind: getattr(args, f"{kind}_validation_batch_size")}
+    if args.evaluate_train is not None:
+        runtime["evaluate_train"] = bool(args.evaluate_train)
+    if args.require_coverage:
+        from experiments.synbios_moe.probes.dataset import validate_probe_cache
+
+        from experiments.synbios_moe.artifact_io import read_json
+
+        checked = validate_probe_cache(args.probe_cache, args.data)
+        recorded = read_json(Path(args.probe_cache) / "manifest.json").get("coverage", {})
+        unseen = {task: c for task, c in recorded.items() if c.get("validation_only_classes")}
+        if not checked.get("ok") or unseen:
+            print(json.dumps({"error": "the probe cache fails validation, or its validation half has classes the training half never shows",
+                              "errors": checked.get("errors", []), "validation_only_classes": unseen}))
+            return 3
     steps = args.steps or stage.get("steps", {"smoke": 20, "pilot": 2000, "formal": 30000}[args.stage])
     root = Path(args.output)
     root.mkdir(parents=True, exist_ok=True)
@@ -270,6 +329,8 @@ def cmd_probe_pipeline(args) -> int:
         print(json.dumps({"error": f"stage {args.stage!r} requires a finished {required!r} stage at {root.parent / required}"}))
         return 3
     gate = settings.get("gate")
+    if gate and args.gate_threshold is not None:
+        gate = {**gate, "threshold": args.gate_threshold}
     if gate and not args.skip_gate:
         # The gate is the progressive cloze over the original biographies: a model that cannot regenerate the facts it was
         # trained on has nothing for a probe to find.  A gate file of the same checkpoint, data and settings is reused.
@@ -284,7 +345,8 @@ def cmd_probe_pipeline(args) -> int:
         gate_id = hashlib.sha256(json.dumps(wanted, sort_keys=True).encode()).hexdigest()[:16]
         path = root / "gate.json"
         cached = read_json(path) if path.is_file() else {}
-        if cached.get("protocol") == PROGRESSIVE_PROTOCOL and cached.get("identity") == gate_id and isinstance(cached.get("exact_match"), (int, float)):
+        if (not args.force_gate and cached.get("protocol") == PROGRESSIVE_PROTOCOL and cached.get("identity") == gate_id
+                and isinstance(cached.get("exact_match"), (int, float))):
             verdict = {**cached, "reused": True}
         else:
             codec = _codec(args)
@@ -348,6 +410,24 @@ def cmd_summarize_probes(args) -> int:
     from experiments.synbios_moe.artifact_io import write_csv
     from experiments.synbios_moe.probes.results import summarize_probe_results
 
+    if args.run:
+        # the reference's form: NAME=DIRECTORY per study; the tables of all of them go into one file with a `run` column
+        rows, means = [], {}
+        for value in args.run:
+            name, _, path = value.partition("=")
+            if not name or not path:
+                print(json.dumps({"error": "--run must use NAME=DIRECTORY"}))
+                return 2
+            one = summarize_probe_results(path[:-len("/validation")] if path.rstrip("/").endswith("/validation") else path)
+            rows += [{"run": name, **row} for row in one["rows"]]
+            means[name] = one.get("mean_accuracy")
+        if args.output:
+            write_csv(args.output, rows)
+        print(json.dumps({"runs": list(means), "rows": len(rows), "mean_accuracy": means}))
+        return 0
+    if not args.root:
+        print(json.dumps({"error": "give a pipeline stage directory, or --run NAME=DIRECTORY"}))
+        return 2
     summary = summarize_probe_results(args.root)
     if args.output:
         write_csv(args.output, summary["rows"])
@@ -376,6 +456,25 @@ def cmd_report(args) -> int:
     from experiments.synbios_moe.artifact_io import read_json, write_json
     from experiments.synbios_moe.probes.results import summarize_probe_results
 
+    if args.single and args.multi:
+        from experiments.synbios_moe.probes.comparison_report import build_formal_report_artifacts
+
+        caches = {}
+        for side, root_dir, given in (("single", args.single, args.single_cache), ("multi", args.multi, args.multi_cache)):
+            caches[side] = Path(given) if given else Path(root_dir).resolve().parent / "cache"
+            if not (caches[side] / "manifest.json").is_file():
+                print(json.dumps({"error": f"no probe cache at {caches[side]}: pass --{side}-cache"}))
+                return 2
+        out = build_formal_report_artifacts(args.single, args.multi, args.output, single_cache=caches["single"], multi_cache=caches["multi"])
+        cloze = {name: read_json(path) for name, path in (("single", args.single_cloze), ("multi5_permute", args.multi_cloze)) if path and Path(path).is_file()}
+        if cloze:
+            write_json(Path(args.output) / "cloze_gate.json", {k: {f: v.get(f) for f in ("micro_field_accuracy", "biography_all_fields_accuracy", "overall_exact_match", "biographies", "items") if f in v}
+                                                               for k, v in cloze.items()})
+        print(json.dumps({"status": "completed", "output": out["output"], "headline_metrics": out["headline"]["delta_multi_minus_single"]}))
+        return 0
+    if not args.root:
+        print(json.dumps({"error": "give a study directory, or --single and --multi5-permute (two finished formal stages)"}))
+        return 2
     root = Path(args.root)
     report = {"probes": summarize_probe_results(root / "probes") if (root / "probes" / "training").is_dir() else None}
     for name in ("cloze", "recall", "routes", "token_statistics"):
@@ -409,9 +508,9 @@ def cmd_oracle_first_token(args) -> int:
     from experiments.synbios_moe.mechanisms.oracle_first_token import oracle_first_token_validation
 
     codec = _codec(args)
-    sink = EventSink(args.log_dir, args.quiet)
+    sink = EventSink.from_args(args)
     model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
-    attributes = tuple(args.attributes.split(",")) if args.attributes else None
+    attributes = tuple(args.attributes.split(",")) if args.attributes else (tuple(args.attribute) if getattr(args, "attribute", None) else None)
     kwargs = {"attributes": attributes} if attributes else {}
     summary = oracle_first_token_validation(model, data_root=args.data, cache_root=args.probe_cache, probe_dir=args.probe_dir,
                                             output_dir=args.output, device=args.device, batch_size=args.batch_size,
@@ -426,9 +525,9 @@ def cmd_bad_case_routes(args) -> int:
     from experiments.synbios_moe.mechanisms.token_routes import bad_case_route_validation
 
     codec = _codec(args)
-    sink = EventSink(args.log_dir, args.quiet)
+    sink = EventSink.from_args(args)
     model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
-    attributes = tuple(args.attributes.split(",")) if args.attributes else None
+    attributes = tuple(args.attributes.split(",")) if args.attributes else (tuple(args.attribute) if getattr(args, "attribute", None) else None)
     summary = bad_case_route_validation(model, codec, data_root=args.data, cache_root=args.probe_cache, probe_dir=args.probe_dir,
                                         output_dir=args.output, device=args.device, attributes=attributes,
                                         batch_size=args.batch_size, max_examples=args.max_examples, pair_limit=args.pair_limit,
@@ -443,7 +542,7 @@ def cmd_ground_truth_first_whole(args) -> int:
     from experiments.synbios_moe.probes.model import _atomic_torch_save, CHECKPOINT_VERSION
 
     codec = _codec(args)
-    sink = EventSink(args.log_dir, args.quiet)
+    sink = EventSink.from_args(args)
     model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
     result = train_ground_truth_first_whole_probe(
         model, cache_root=args.probe_cache, probe_dir=args.probe_dir, attribute=args.attribute, codec=codec, device=args.device,
@@ -481,9 +580,13 @@ def cmd_probe_batch_benchmark(args) -> int:
     from experiments.synbios_moe.probes.model import DEFAULT_RANK
 
     codec = _codec(args)
-    sink = EventSink(args.log_dir, args.quiet)
+    sink = EventSink.from_args(args)
     model = load_backbone(args.model_config, args.checkpoint, args.device, codec_vocab=codec.vocab_size)
     runs = []
+    if args.kind:
+        args.kinds = args.kind
+        if args.batch_sizes:
+            setattr(args, f"{args.kind}_batch_sizes", args.batch_sizes)
     for kind in args.kinds.split(","):
         split = "train" if args.mode == "training" else "validation"
         data = CachedProbeDataset(args.probe_cache, kind=kind, attribute=args.attribute, target=args.target, split=split)
@@ -537,7 +640,16 @@ def cmd_compare_formal_studies(args) -> int:
 def cmd_diagnostic_report(args) -> int:
     from experiments.synbios_moe.mechanisms.comparison_report import build_diagnostic_report_artifacts
 
-    print(json.dumps(build_diagnostic_report_artifacts({"single": args.single, "multi5_permute": args.multi}, args.output)))
+    single, multi = args.single, args.multi
+    if args.diagnostics and not (single and multi):          # the reference's form: one root, a directory per condition
+        single, multi = str(Path(args.diagnostics) / "single"), str(Path(args.diagnostics) / "multi5_permute")
+    if not (single and multi):
+        print(json.dumps({"error": "give --single and --multi (diagnostics directories), or --diagnostics with single/ and multi5_permute/ inside"}))
+        return 2
+    result = build_diagnostic_report_artifacts({"single": single, "multi5_permute": multi}, args.output)
+    if args.single_formal or args.multi_formal:
+        result["formal_stages"] = {"single": args.single_formal, "multi5_permute": args.multi_formal}
+    print(json.dumps(result))
     return 0
 
 
@@ -561,6 +673,9 @@ def build_parser() -> argparse.ArgumentParser:
         if monitoring:
             p.add_argument("--log-dir")
             p.add_argument("--quiet", action="store_true")
+            p.add_argument("--log-interval", type=int, default=1, help="console: show every N-th progress event (the event file keeps all)")
+            p.add_argument("--tensorboard", action=argparse.BooleanOptionalAction, default=False,
+                           help="also write numeric event fields as TensorBoard scalars under --log-dir")
 
     p = sub.add_parser("prepare"); common(p, model=False)
     p.add_argument("--output", required=True); p.add_argument("--variant", default="single", choices=VARIANTS)
@@ -584,6 +699,12 @@ def build_parser() -> argparse.ArgumentParser:
         p = sub.add_parser(name); common(p)
         p.add_argument("--data", required=True); p.add_argument("--output", required=True)
         p.add_argument("--batch-size", type=int, default=32); p.add_argument("--max-items", type=int); p.set_defaults(func=fn)
+        if name != "cloze-evaluate":
+            p.add_argument("--examples", type=int, dest="max_items", help="same as --max-items (the reference's name)")
+        if name == "analyze":
+            # the reference analyses one probe task per call; here every attribute is analysed in one pass and these select nothing
+            p.add_argument("--attribute", choices=ATTRIBUTES); p.add_argument("--target", choices=("first", "whole"), default="first")
+            p.add_argument("--probe-cache")
         if name == "cloze-evaluate":
             # independent: every value from its true prefix, fixed length; progressive: the six holes of a biography filled left
             # to right in one growing sequence, each value generated until the source's next full stop
@@ -591,7 +712,8 @@ def build_parser() -> argparse.ArgumentParser:
             p.add_argument("--examples", type=int, default=1000); p.add_argument("--start-index", type=int, default=0)
             p.add_argument("--max-new-tokens", type=int, default=16); p.add_argument("--sample-biographies", type=int, default=12)
 
-    p = sub.add_parser("summarize-cloze"); p.add_argument("reports", nargs="+"); p.add_argument("--output", required=True)
+    p = sub.add_parser("summarize-cloze"); p.add_argument("reports", nargs="*"); p.add_argument("--output", required=True)
+    p.add_argument("--run", action="append", default=[], help="a cloze report (repeatable; same as a positional argument)")
     p.set_defaults(func=cmd_summarize_cloze)
 
     p = sub.add_parser("probe"); common(p)
@@ -607,30 +729,46 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-eval-items", type=int); p.set_defaults(func=cmd_probe)
 
     p = sub.add_parser("validate-probe"); common(p)
-    p.add_argument("--probe-cache", required=True); p.add_argument("--probe-state", required=True); p.add_argument("--output", required=True)
+    p.add_argument("--probe-cache", required=True); p.add_argument("--probe-state", "--probe-checkpoint", dest="probe_state", required=True)
+    p.add_argument("--output", required=True); p.add_argument("--data", help="accepted for the reference's command lines; the cache names its dataset")
+    p.add_argument("--batch-size", type=int, default=200); p.add_argument("--checkpoint-model-sha256", help=argparse.SUPPRESS)
+    p.add_argument("--allow-checkpoint-mismatch", action="store_true", help="evaluate although the probe was trained on another backbone checkpoint")
     p.add_argument("--max-eval-items", type=int); p.set_defaults(func=cmd_validate_probe)
 
     p = sub.add_parser("probe-pipeline"); common(p)
     p.add_argument("--data", required=True); p.add_argument("--probe-cache", required=True); p.add_argument("--output", required=True)
-    p.add_argument("--stage", choices=("smoke", "pilot", "formal"), required=True); p.add_argument("--config")
+    p.add_argument("--stage", choices=("smoke", "pilot", "formal"), required=True); p.add_argument("--config", "--pipeline-config", dest="config")
+    p.add_argument("--num-gpus", type=int, help="use cuda:0 .. cuda:N-1 (instead of --devices)")
+    p.add_argument("--gate-threshold", type=float, help="override the cloze gate's threshold"); p.add_argument("--force-gate", action="store_true", help="run the cloze gate again although a cached verdict matches")
+    p.add_argument("--require-coverage", action="store_true", help="refuse a probe cache whose validation half lacks a class")
+    p.add_argument("--quiet-workers", action="store_true", help="accepted: workers always log to files here")
+    for kind in ("p", "q"):
+        p.add_argument(f"--{kind}-batch-size", type=int); p.add_argument(f"--{kind}-validation-batch-size", type=int)
+    p.add_argument("--evaluate-train", action=argparse.BooleanOptionalAction, default=None)
     p.add_argument("--devices", default=default_device); p.add_argument("--kinds", default="p,q"); p.add_argument("--attributes")
     p.add_argument("--steps", type=int); p.add_argument("--seed", type=int, default=1337)
     p.add_argument("--checkpoint-interval-steps", type=int); p.add_argument("--heartbeat-seconds", type=float)
     p.add_argument("--p-rank", type=int); p.add_argument("--q-rank", type=int)
-    p.add_argument("--skip-gate", action="store_true"); p.add_argument("--skip-requirements", action="store_true")
+    p.add_argument("--skip-gate", action="store_true"); p.add_argument("--skip-requirements", "--ignore-prerequisite", dest="skip_requirements", action="store_true")
     p.add_argument("--max-eval-items", type=int); p.set_defaults(func=cmd_probe_pipeline)
 
-    p = sub.add_parser("summarize-probes"); p.add_argument("root"); p.add_argument("--output"); p.set_defaults(func=cmd_summarize_probes)
-    p = sub.add_parser("report-formal-study"); p.add_argument("root"); p.add_argument("--output", required=True); p.set_defaults(func=cmd_report)
+    p = sub.add_parser("summarize-probes"); p.add_argument("root", nargs="?"); p.add_argument("--output"); p.set_defaults(func=cmd_summarize_probes)
+    p.add_argument("--run", action="append", default=[], help="NAME=DIRECTORY of a finished pipeline stage (repeatable; the reference's form)")
+    p = sub.add_parser("report-formal-study"); p.add_argument("root", nargs="?"); p.add_argument("--output", required=True); p.set_defaults(func=cmd_report)
+    # the reference's form: two finished formal stages (and their cloze reports) -> the comparison artifacts of compare-formal-studies
+    p.add_argument("--single"); p.add_argument("--multi5-permute", dest="multi"); p.add_argument("--single-cloze"); p.add_argument("--multi5-permute-cloze", dest="multi_cloze")
+    p.add_argument("--single-cache", help="default: <single>/../cache"); p.add_argument("--multi-cache", help="default: <multi5-permute>/../cache")
     p = sub.add_parser("audit-synbios-repository"); p.add_argument("--data"); p.add_argument("--probe-cache"); p.add_argument("--pipeline")
     for side in ("single", "multi"):
         for what in ("data", "cache", "pipeline", "model"):
             p.add_argument(f"--{side}-{what}")
+    p.add_argument("--repo-root", default=".", help="accepted for the reference's command lines; paths here are given explicitly")
     p.add_argument("--output"); p.set_defaults(func=cmd_audit)
 
     p = sub.add_parser("oracle-first-token", aliases=["validate-probe-oracle-first-token"]); common(p)
     p.add_argument("--data", required=True); p.add_argument("--probe-cache", required=True); p.add_argument("--probe-dir", required=True)
     p.add_argument("--output", required=True); p.add_argument("--attributes"); p.add_argument("--batch-size", type=int, default=256)
+    p.add_argument("--attribute", action="append", choices=ATTRIBUTES, help="one attribute (repeatable; the reference's form of --attributes)")
     p.add_argument("--max-examples", type=int); p.set_defaults(func=cmd_oracle_first_token)
 
     p = sub.add_parser("ground-truth-first-whole", aliases=["train-ground-truth-first-whole"]); common(p)
@@ -639,6 +777,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--batch-size", type=int, default=50); p.add_argument("--evaluation-batch-size", type=int, default=256)
     p.add_argument("--recovery-checkpoint"); p.add_argument("--checkpoint-interval-steps", type=int)
     p.add_argument("--resume-probe", action=argparse.BooleanOptionalAction, default=True)
+    p.add_argument("--data", help="accepted for the reference's command lines; the cache names its dataset")
+    p.add_argument("--evaluate-train", action="store_true", help="accepted: the report of this command is validation accuracy by source position")
     p.add_argument("--max-validation-examples", type=int); p.set_defaults(func=cmd_ground_truth_first_whole)
 
     p = sub.add_parser("ground-truth-first-report", aliases=["summarize-ground-truth-first-whole"]); p.add_argument("--run-dir", "--run", dest="run_dir", required=True); p.add_argument("--probe-dir", required=True)
@@ -657,11 +797,15 @@ def build_parser() -> argparse.ArgumentParser:
         p.add_argument("--rank", type=int); p.add_argument("--warmup-steps", type=int, default=3); p.add_argument("--measure-steps", type=int, default=10)
         p.add_argument("--memory-limit-percent", type=float, default=92.0)
         p.add_argument("--ground-truth-first", action=argparse.BooleanOptionalAction, default=gtf)
+        p.add_argument("--data", help="accepted for the reference's command lines; the cache names its dataset")
+        p.add_argument("--kind", choices=("p", "q"), help="one probe kind (the reference's form of --kinds)")
+        p.add_argument("--batch-sizes", help="candidates for --kind (the reference's form of --p-batch-sizes / --q-batch-sizes)")
         p.set_defaults(func=cmd_probe_batch_benchmark)
 
     p = sub.add_parser("bad-case-routes", aliases=["validate-probe-bad-case-routes"]); common(p)
     p.add_argument("--data", required=True); p.add_argument("--probe-cache", required=True); p.add_argument("--probe-dir", required=True)
     p.add_argument("--output", required=True); p.add_argument("--attributes"); p.add_argument("--batch-size", type=int, default=512)
+    p.add_argument("--attribute", action="append", choices=ATTRIBUTES, help="one attribute (repeatable; the reference's form of --attributes)")
     p.add_argument("--max-examples", type=int); p.add_argument("--pair-limit", type=int, default=2000)
     p.set_defaults(func=cmd_bad_case_routes)
 
@@ -675,7 +819,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--single-cache", required=True); p.add_argument("--multi-cache", required=True); p.add_argument("--output", required=True)
     p.set_defaults(func=cmd_compare_formal_studies)
 
-    p = sub.add_parser("diagnostic-report", aliases=["report-probe-diagnostics"]); p.add_argument("--single", required=True); p.add_argument("--multi", required=True)
+    p = sub.add_parser("diagnostic-report", aliases=["report-probe-diagnostics"]); p.add_argument("--single"); p.add_argument("--multi")
+    # the reference's form: one diagnostics root with a directory per condition, and the two formal stages (recorded in the report)
+    p.add_argument("--diagnostics"); p.add_argument("--single-formal"); p.add_argument("--multi5-permute-formal", dest="multi_formal")
     p.add_argument("--output", required=True); p.set_defaults(func=cmd_diagnostic_report)
     return ap
 

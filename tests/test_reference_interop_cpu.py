@@ -371,3 +371,37 @@ def test_console_lines_are_the_reference_s_lines():
     # what this repository adds to a train event shows up as an extra cell and changes nothing else
     extended = format_console_event({**train, "mfu_percent": 41.2})
     assert "mfu 41.2%" in extended and extended.replace(" | mfu 41.2%", "") == ref_format(train)
+
+
+def test_every_command_and_most_options_of_the_reference_study_cli_exist_here():
+    """``scripts/synbios_moe.py`` accepts every sub-command name of the reference's CLI, and for each the option strings the
+    reference defines, so that a launcher written for one parses under the other."""
+
+    import importlib.util
+    import json
+
+    out = _run_reference(
+        "import argparse, json\n"
+        "from pathlib import Path\n"
+        "from experiments.synbios_moe import cli\n"
+        "parser = cli.build_parser(project_root=Path('.'), handlers={name: (lambda args: 0) for name in cli.PUBLIC_COMMANDS}, default_device='cpu')\n"
+        "sub = next(a for a in parser._actions if isinstance(a, argparse._SubParsersAction))\n"
+        "print(json.dumps({name: sorted(s for a in p._actions for s in a.option_strings if s.startswith('--') and s != '--help') for name, p in sub.choices.items()}))\n")
+    theirs = json.loads(out)
+    spec = importlib.util.spec_from_file_location("synbios_cli", ROOT / "scripts" / "synbios_moe.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    import argparse
+
+    parser = module.build_parser()
+    sub = next(a for a in parser._actions if isinstance(a, argparse._SubParsersAction))
+    assert set(theirs) <= set(sub.choices), sorted(set(theirs) - set(sub.choices))
+    missing = {}
+    total = 0
+    for name, options in theirs.items():
+        mine = {s for a in sub.choices[name]._actions for s in a.option_strings}
+        total += len(options)
+        gone = [o for o in options if o not in mine]
+        if gone:
+            missing[name] = gone
+    assert total > 200 and missing == {}, missing

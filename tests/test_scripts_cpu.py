@@ -219,6 +219,16 @@ def test_walkthrough_runner_records_cells_and_fails_on_errors(tmp_path):
     assert rec["executed"] == 2 and rec["failed_cells"] == [1] and "ValueError: boom" in rec["records"][1]["error"]
     executed = json.loads((tmp_path / "bad.out.ipynb").read_text())
     assert executed["cells"][2]["outputs"][0]["output_type"] == "error"
+    # the reference's options: everything into one directory, a limit per cell
+    slow = tmp_path / "slow.ipynb"
+    slow.write_text(json.dumps({"cells": [{"cell_type": "code", "source": "print('fast')", "outputs": []},
+                                          {"cell_type": "code", "source": "import time\ntime.sleep(30)", "outputs": []}], "metadata": {}, "nbformat": 4}))
+    done = subprocess.run([*runner, str(slow), "--output-dir", str(tmp_path / "out"), "--timeout-seconds", "1", "--kernel", "ignored", "--quiet"],
+                          capture_output=True, text=True, timeout=60)
+    assert done.returncode == 1
+    rec = json.loads((tmp_path / "out" / "slow.run.json").read_text())
+    assert rec["failed_cells"] == [1] and "CellTimeout" in rec["records"][1]["error"] and rec["records"][1]["seconds"] < 10
+    assert (tmp_path / "out" / "slow.executed.ipynb").is_file()
 
 
 def test_committed_notebooks_equal_their_percent_format_sources_and_run(tmp_path):

@@ -512,3 +512,48 @@ def test_probe_pipeline_cloze_gate_runs_once_and_can_refuse(study, tmp_path):
     cfg.write_text(json.dumps({**base, "gate": {"batch_size": 4, "examples": 5, "max_new_tokens": 4, "threshold": 0.99}}))
     out = run(*[a if a != str(tmp_path / "pipe") else str(tmp_path / "pipe2") for a in args])
     assert out.returncode == 3 and "cloze gate failed" in out.stdout and not (tmp_path / "pipe2" / "pipeline.json").exists()
+
+
+def test_option_names_of_the_reference_cli_do_what_they_say(study, tmp_path):
+    """The reference's spellings: --examples, --probe-checkpoint, --run, --num-gpus-free overrides, --attribute (repeatable),
+    --log-interval / --tensorboard; each through the command that accepts it."""
+
+    run = study["run"]
+    common = ["--data", str(study["data"]), "--model-config", str(study["model_config"]), "--checkpoint", str(study["checkpoint"]), "--codec", "bytes",
+              "--device", "cpu"]
+    out = run("evaluate", *common, "--output", str(tmp_path / "recall.json"), "--examples", "6", "--log-interval", "5", "--no-tensorboard")
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert json.loads((tmp_path / "recall.json").read_text())["overall"]["values"] == 36                 # six biographies x six attributes
+    probe_json = tmp_path / "probe" / "q-major-first.json"
+    out = run("probe", *common, "--probe-cache", str(study["cache"]), "--attribute", "major", "--target", "first", "--kind", "q", "--steps", "4",
+              "--batch-size", "8", "--output", str(probe_json), "--max-eval-items", "8", "--log-dir", str(tmp_path / "events"), "--log-interval", "2",
+              "--tensorboard")
+    assert out.returncode == 0, out.stderr[-2000:]
+    shown = [json.loads(line) for line in out.stdout.splitlines() if line.startswith("{") and '"probe_train"' in line]
+    logged = [json.loads(line) for line in (tmp_path / "events" / "events.jsonl").read_text().splitlines() if '"probe_train"' in line]
+    assert len(logged) >= len(shown) and all(e["step"] % 2 == 0 or e["step"] == e.get("steps_total") for e in shown)
+    assert any(p.name.startswith("events.out.tfevents") for p in (tmp_path / "events").iterdir())
+    # the reference's name of the saved head, its batch size option, and the guard against another backbone
+    verdict = tmp_path / "verdict.json"
+    out = run("validate-probe", *common, "--probe-cache", str(study["cache"]), "--probe-checkpoint", str(probe_json.with_suffix(".pt")), "--batch-size", "4",
+              "--output", str(verdict), "--max-eval-items", "8", "--quiet")
+    assert out.returncode == 0 and "validation" in json.loads(verdict.read_text()), out.stderr[-2000:]
+    other = tmp_path / "other_model.pt"
+    state = torch.load(study["checkpoint"], weights_only=False)
+    torch.save({k: (v + 1 if v.is_floating_point() else v) for k, v in state.items()}, other)
+    mismatch = [a if a != str(study["checkpoint"]) else str(other) for a in common]
+    out = run("validate-probe", *mismatch, "--probe-cache", str(study["cache"]), "--probe-checkpoint", str(probe_json.with_suffix(".pt")),
+              "--output", str(tmp_path / "v2.json"), "--max-eval-items", "8", "--quiet")
+    assert out.returncode == 3 and "another backbone" in out.stdout
+    out = run("validate-probe", *mismatch, "--probe-cache", str(study["cache"]), "--probe-checkpoint", str(probe_json.with_suffix(".pt")),
+              "--output", str(tmp_path / "v2.json"), "--max-eval-items", "8", "--quiet", "--allow-checkpoint-mismatch")
+    assert out.returncode == 0
+    # NAME=DIRECTORY runs
+    stage = tmp_path / "stage"
+    (stage / "training").mkdir(parents=True)
+    (stage / "training" / "q-major-first.json").write_text(probe_json.read_text())
+    out = run("summarize-probes", "--run", f"mine={stage}", "--run", f"again={stage / 'validation'}", "--output", str(tmp_path / "runs.csv"))
+    assert out.returncode == 0 and json.loads(out.stdout)["runs"] == ["mine", "again"], out.stdout + out.stderr[-1000:]
+    table = (tmp_path / "runs.csv").read_text().splitlines()
+    assert "run" in table[0].split(",") and len(table) == 3
+    assert run("summarize-probes", "--run", "broken").returncode == 2

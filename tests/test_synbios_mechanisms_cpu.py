@@ -478,3 +478,25 @@ def test_line_chart_and_the_reports_that_use_it(tmp_path):
     assert out["pair_mean_gain"] == pytest.approx(0.6, abs=1e-9)
     figure = (tmp_path / "company" / "company_relation.svg").read_text()
     assert ET.fromstring(figure).tag.endswith("svg") and "partner exposure" in figure and figure.count("<polyline") == 5
+
+
+def test_ground_truth_first_protocol_audit_on_real_artifacts(studies, tmp_path):
+    """The reference script's command line: the protocol is audited on the artifacts a run would use.  The fixture holds the
+    original P-whole probe of one attribute only, so that task passes and the other four are reported as not ready."""
+
+    s = studies["single"]
+    out = tmp_path / "audit" / "protocol.json"
+    done = subprocess.run([sys.executable, str(ROOT / "scripts" / "audit_ground_truth_first_probe.py"), "--data", str(s["data"]), "--probe-cache", str(s["cache"]),
+                           "--probe-dir", str(s["probes"]), "--model-config", studies["model_config"], "--checkpoint", studies["checkpoint"],
+                           "--device", "cpu", "--codec", "bytes", "--output", str(out)], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 1, done.stdout[-1500:] + done.stderr[-2500:]               # four of five tasks have no reference probe yet
+    record = json.loads(out.read_text())
+    assert record["protocol"] == "ground_truth_first_whole_rank_matched_v1" and not record["quality_gate_passed"] and len(record["tasks"]) == 5
+    by_attribute = {t["attribute"]: t for t in record["tasks"]}
+    good = by_attribute["university"]
+    assert good["passed"] and good["errors"] == [] and good["sampled_items_checked"] >= 12 and good["rank"] == 2
+    assert good["trainable_parameters"] == ["delta.a.weight", "delta.b.weight", "normalizer.weight", "normalizer.bias", "classifier.weight", "classifier.bias"]
+    assert good["expanded_train_examples"] == 6 * good["train_sources"] and len(good["reference_whole_probe_sha256"]) == 64
+    assert all(not by_attribute[a]["passed"] and by_attribute[a]["errors"] for a in ("birth_city", "major", "company", "company_city"))
+    # record mode still wants records
+    assert subprocess.run([sys.executable, str(ROOT / "scripts" / "audit_ground_truth_first_probe.py")], capture_output=True, text=True).returncode == 2
