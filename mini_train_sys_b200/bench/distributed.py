@@ -483,7 +483,7 @@ def quality_gates(summary: dict[str, Any], *, repeats: int, min_efficiency: floa
     return gates
 
 
-def validate_backend(device_index: int = 0) -> dict[str, Any]:
+def validate_backend(device_index: int = 0, *, batch: int = 2, sequence_length: int = 512) -> dict[str, Any]:
     """Native attention against the library back end (forward, dq, dk, dv), a dropout run, and the dispatch counters."""
 
     import torch
@@ -493,7 +493,7 @@ def validate_backend(device_index: int = 0) -> dict[str, Any]:
     dev = torch.device("cuda", device_index)
     native, lib = get_ops_backend("native"), get_ops_backend("torch")
     torch.manual_seed(0)
-    shape = (2, 12, 512, 64)
+    shape = (batch, 12, sequence_length, 64)
     base = [torch.randn(shape, device=dev, dtype=torch.bfloat16) for _ in range(3)]
     grad = torch.randn(shape, device=dev, dtype=torch.bfloat16)
     results = {}

@@ -210,3 +210,53 @@ def test_capacity_ladder_comes_from_the_memory_plan():
     spec.loader.exec_module(cli)
     args = cli._parser().parse_args(["run", "--suite", "capacity", "--batch-sizes", "auto"])
     assert args.batch_sizes == "auto" and cli._parser().parse_args(["run", "--suite", "weak", "--batch-sizes", "8,16"]).batch_sizes == (8, 16)
+
+
+def test_distributed_benchmark_cli_takes_the_reference_spellings(tmp_path, capsys):
+    """Space-separated lists, ``--output`` / ``--case-config`` / ``--local-batch`` on ``run``; ``--input`` / ``--output`` and the
+    capacity limits on the presenters; a failed validation verdict blocks ``present-backend``."""
+
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("run_dist_bench", ROOT / "scripts" / "run_dist_bench.py")
+    cli = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(cli)
+    args = cli._parser().parse_args(["run", "--suite", "weak", "--world-sizes", "1", "2", "4", "--strategies", "ddp", "fsdp", "--ops-backends",
+                                     "torch,native", "--batch-sizes", "8", "16", "--output", "out", "--case-config", "c.yaml", "--local-batch", "4",
+                                     "--case-timeout-seconds", "60"])
+    assert (args.world_sizes, args.strategies, args.ops_backends, args.batch_sizes) == ((1, 2, 4), ("ddp", "fsdp"), ("torch", "native"), (8, 16))
+    assert (args.output_dir, args.config, args.local_batch, args.timeout) == ("out", "c.yaml", 4, 60.0)
+
+    from mini_train_sys_b200.bench import distributed as db
+
+    rows = [_rows(1, 100.0, batch=1), _rows(1, 101.0, batch=1), _rows(1, 150.0, batch=16), _rows(1, 151.0, batch=16), _rows(1, 500.0, batch=64)]
+    suite_dir = tmp_path / "capacity"
+    suite_dir.mkdir()
+    (suite_dir / "summary.json").write_text(json.dumps({"suite": "capacity", "rows": rows, "capacity": db.present_capacity(rows),
+                                                       "quality_gates": {"passed": True}}))
+    table = tmp_path / "tables" / "capacity.md"
+    assert cli.main(["present-capacity", "--input", str(suite_dir / "summary.json"), "--output", str(table), "--require-batch-one"]) == 0
+    assert "common fixed batch: 16" in table.read_text() and "| 16 |" in table.read_text()
+    # one repeat is enough under --min-repeats 1, so the single row at 64 now wins; the directory form of --input works too
+    assert cli.main(["present-capacity", "--input", str(suite_dir), "--min-repeats", "1", "--output", str(table)]) == 0
+    assert "common fixed batch: 64" in table.read_text()
+    no_one = [r for r in rows if r["batch_size"] != 1]
+    (suite_dir / "summary.json").write_text(json.dumps({"suite": "capacity", "rows": no_one, "capacity": db.present_capacity(no_one),
+                                                       "quality_gates": {"passed": True}}))
+    assert cli.main(["present-capacity", str(tmp_path), "--require-batch-one"]) == 1
+
+    back_rows = [_rows(1, 100.0), _rows(1, 100.0), _rows(1, 300.0, ops="native", dispatch={"attention:native": 4}),
+                 _rows(1, 300.0, ops="native", dispatch={"attention:native": 4})]
+    (tmp_path / "backend").mkdir()
+    (tmp_path / "backend" / "summary.json").write_text(json.dumps({"suite": "backend", "rows": back_rows, "backend": db.present_backend(back_rows),
+                                                                  "quality_gates": {"passed": True}}))
+    verdict = tmp_path / "validation.json"
+    verdict.write_text(json.dumps({"passed": False}))
+    assert cli.main(["present-backend", "--input", str(tmp_path / "backend"), "--validation", str(verdict)]) == 1
+    verdict.write_text(json.dumps({"passed": True}))
+    assert cli.main(["present-backend", "--input", str(tmp_path / "backend"), "--validation", str(verdict), "--output", str(tmp_path / "b.md")]) == 0
+    assert "speedup_vs_torch" in (tmp_path / "b.md").read_text()
+
+    assert cli.main(["inventory", "--output", str(tmp_path / "inv")]) == 0
+    assert "source_fingerprint" in json.loads((tmp_path / "inv" / "inventory.json").read_text())
+    capsys.readouterr()
