@@ -165,9 +165,15 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-nvcc", action="store_true")
     ap.add_argument("--storage-root", default=None)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--require-nvcc", action="store_true", help="nvcc is required unless --skip-nvcc is given; accepted so that command "
+                    "lines written for the reference's check keep working")
+    ap.add_argument("--output", help="also write the full report as JSON to this file")
     args = ap.parse_args(argv)
     status = collect_server_status(expected_gpus=args.expected_gpus, min_free_disk_gb=args.min_free_disk_gb,
                                    require_nvcc=not args.skip_nvcc, storage_root=args.storage_root)
+    if args.output:
+        Path(args.output).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.output).write_text(json.dumps(status, indent=2, default=str) + "\n")
     if args.json:
         print(json.dumps(status, indent=2))
     else:

@@ -1,6 +1,12 @@
 # Shared helpers of the launchers: repository root, python, torchrun wrapper (always on 127.0.0.1 for single-node runs).
 set -euo pipefail
 REPO_ROOT="$(cd "$(dirname "${BASH_SOURCE[0]}")/../.." && pwd)"
+# storage settings of this checkout (data disk, caches, TMPDIR), written by setup_storage.sh; a file left by the reference's
+# setup script under its own name is honoured too
+for _env in "$REPO_ROOT/.minitrain-storage.env" "$REPO_ROOT/.mts-storage.env"; do
+  if [[ -f "$_env" ]]; then source "$_env"; fi
+done
+unset _env
 PYTHON="${PYTHON:-python}"
 MASTER_PORT="${MASTER_PORT:-29500}"
 

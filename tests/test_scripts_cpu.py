@@ -318,3 +318,85 @@ def test_ground_truth_first_audit_lists_every_violation(tmp_path):
     done = subprocess.run(cmd, capture_output=True, text=True)
     errors = json.loads(done.stdout)["errors"]
     assert done.returncode == 1 and len(errors) >= 3 and any("frozen" in e for e in errors) and any("resumed" in e for e in errors)
+
+
+def _launcher_sandbox(tmp_path):
+    """A copy of the bash launchers under a scratch checkout whose `python` prints its arguments instead of running them."""
+
+    import shutil
+    import stat
+
+    checkout = tmp_path / "checkout"
+    shutil.copytree(ROOT / "scripts" / "bash", checkout / "scripts" / "bash")
+    shutil.copytree(ROOT / "configs", checkout / "configs")
+    stub = tmp_path / "python_stub"
+    stub.write_text('#!/usr/bin/env bash\necho "ARGS: $*"\necho "TMPDIR=${TMPDIR:-} STORAGE=${MTS_STORAGE_ROOT:-}"\n')
+    stub.chmod(stub.stat().st_mode | stat.S_IEXEC)
+    env = {"PATH": os.environ["PATH"], "PYTHON": str(stub), "HOME": str(tmp_path)}
+    run = lambda script, *args, **extra: subprocess.run(["bash", str(checkout / "scripts" / "bash" / script), *args], capture_output=True,   # noqa: E731
+                                                        text=True, timeout=120, env={**env, **extra})
+    return checkout, run
+
+
+def test_storage_setup_links_artifacts_to_the_data_disk_and_launchers_pick_it_up(tmp_path):
+    checkout, run = _launcher_sandbox(tmp_path)
+    disk = tmp_path / "disk"
+    disk.mkdir()
+    refused = run("setup_storage.sh", str(disk))
+    if refused.returncode == 0:
+        pytest.skip("the scratch directory is on a filesystem of its own")
+    assert refused.returncode == 2 and "root filesystem" in refused.stderr and not (checkout / "artifacts").exists()
+    assert run("setup_storage.sh", "relative/path").returncode == 2
+    done = run("setup_storage.sh", str(disk), ALLOW_SYSTEM_DISK_STORAGE="1")
+    assert done.returncode == 0, done.stderr
+    store = disk / "mini-train-sys"
+    assert (checkout / "artifacts").is_symlink() and (checkout / "artifacts").resolve() == (store / "artifacts").resolve()
+    assert (store / "artifacts" / "synbios_moe" / "checkpoints").is_dir() and (store / "cache" / "torch_extensions").is_dir() and (store / "tmp").is_dir()
+    settings = (checkout / ".mts-storage.env").read_text()
+    assert f"export MTS_STORAGE_ROOT={store}" in settings and f"export TMPDIR={store}/tmp" in settings
+    assert run("setup_storage.sh", str(disk), ALLOW_SYSTEM_DISK_STORAGE="1").returncode == 0            # a second run changes nothing
+    # a storage root outside the disk, and a link that points elsewhere, are refused
+    assert run("setup_storage.sh", str(disk), ALLOW_SYSTEM_DISK_STORAGE="1", MTS_STORAGE_ROOT=str(tmp_path / "elsewhere")).returncode == 2
+    other = tmp_path / "disk2"
+    other.mkdir()
+    clash = run("setup_storage.sh", str(other), ALLOW_SYSTEM_DISK_STORAGE="1")
+    assert clash.returncode == 2 and "already links" in clash.stderr
+    # the launchers read the settings
+    out = run("train.sh")
+    assert out.returncode == 0 and f"TMPDIR={store}/tmp STORAGE={store}" in out.stdout, out.stdout + out.stderr
+    # files already in a real artifacts directory are never moved
+    (checkout / "artifacts").unlink()
+    (checkout / "artifacts").mkdir()
+    (checkout / "artifacts" / "keep.txt").write_text("x")
+    kept = run("setup_storage.sh", str(disk), ALLOW_SYSTEM_DISK_STORAGE="1")
+    assert kept.returncode == 2 and "left alone" in kept.stderr and (checkout / "artifacts" / "keep.txt").exists()
+
+
+def test_launchers_take_their_settings_from_the_environment(tmp_path):
+    checkout, run = _launcher_sandbox(tmp_path)
+    out = run("train.sh", CONFIG="configs/train_debug.yaml", MODEL_CONFIG="configs/model_debug_moe.yaml", DEVICE="cpu", RESUME="latest")
+    assert "scripts/train.py --config configs/train_debug.yaml --device cpu --model-config configs/model_debug_moe.yaml --resume latest" in out.stdout, out.stdout + out.stderr
+    out = run("train.sh", "configs/train_single.yaml", "--max-steps", "3")
+    assert "--config configs/train_single.yaml --device auto --max-steps 3" in out.stdout
+    out = run("distributed.sh", "fsdp", NPROC="4", MASTER_PORT="29777")
+    assert out.returncode == 0 and "--nproc-per-node 4 --master-addr 127.0.0.1 --master-port 29777 scripts/train.py --config configs/server/b200_180gb/runs/fsdp_4gpu.yaml " \
+        "--model-config configs/synbios_moe/model.yaml --resume auto" in out.stdout, out.stdout + out.stderr
+    out = run("distributed.sh", "ddp", "2", "--max-steps", "5", RESUME="safety", MAX_RESTARTS="2")
+    assert "--rdzv-backend c10d" in out.stdout and "--max-restarts 2" in out.stdout and "ddp_2gpu.yaml" in out.stdout and "--resume safety --max-steps 5" in out.stdout
+    assert run("distributed.sh", "zero3", "2").returncode == 2 and run("distributed.sh", "fsdp", "3").returncode == 2
+    # the study launcher: data present -> no prepare; AUTO_RESUME=0 drops --resume; people that differ across variants stop it
+    data = checkout / "artifacts" / "synbios_moe" / "data"
+    for variant, people in (("single", "a\n"), ("multi5_permute", "a\n")):
+        (data / variant).mkdir(parents=True)
+        (data / variant / "manifest.json").write_text("{}")
+        (data / variant / "profiles.jsonl").write_text(people)
+    out = run("synbios_moe.sh", "single", "fsdp", NPROC="8")
+    assert out.returncode == 0 and "prepare" not in out.stdout and "--nproc-per-node 8" in out.stdout and "--resume auto" in out.stdout, out.stdout + out.stderr
+    out = run("synbios_moe.sh", "single", "single", AUTO_RESUME="0")
+    assert out.returncode == 0 and "--resume" not in out.stdout and "single_single.yaml" in out.stdout
+    (checkout / "artifacts" / "synbios_moe" / "checkpoints" / "synbios_moe_single_fsdp" / "epoch_000001_step_000000010").mkdir(parents=True)
+    forced = run("synbios_moe.sh", "single", "fsdp", "8", FORCE_PREPARE="1")
+    assert forced.returncode == 2 and "refusing" in forced.stderr
+    (data / "multi5_permute" / "profiles.jsonl").write_text("b\n")
+    differ = run("synbios_moe.sh", "single", "fsdp", "8")
+    assert differ.returncode == 2 and "differ" in differ.stderr
