@@ -16,3 +16,12 @@ for DEVICE in "${DEVICES[@]}"; do
 done
 for p in "${pids[@]}"; do wait "$p"; done
 "$PYTHON" scripts/synbios_moe.py summarize-probe-batch-benchmarks "${results[@]}" --output "$OUT/summary.json"
+# once both modes have been measured: one file of `export P_BATCH_SIZE=...` lines for synbios_probes.sh (PROBE_BATCH_ENV); it
+# is written only when the merged benchmark is complete (every kind bracketed by a slower or infeasible larger batch)
+PARENT="$(dirname "$OUT")"
+if compgen -G "$PARENT/training/c*.json" > /dev/null && compgen -G "$PARENT/validation/c*.json" > /dev/null; then
+  "$PYTHON" scripts/synbios_moe.py summarize-probe-batch-benchmarks "$PARENT"/training/c*.json "$PARENT"/validation/c*.json \
+    --output "$PARENT/summary.json" --env-output "$PARENT/recommended.env" > /dev/null 2>&1 \
+    && echo "batch sizes for the probe launcher: PROBE_BATCH_ENV=$PARENT/recommended.env" \
+    || echo "no recommended.env yet: the merged benchmark is incomplete (see $PARENT/summary.json)" >&2
+fi

@@ -826,8 +826,29 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
+def exported_model_file(checkpoint: str) -> str:
+    """``--checkpoint`` names an exported ``model.pt`` or, as in the reference's launchers, a committed checkpoint directory
+    (``latest`` inside a run directory picks its newest committed one); the directory form resolves to the export inside it."""
+
+    path = Path(checkpoint)
+    if path.name == "latest" and not path.exists():
+        committed = sorted(d.parent for d in path.parent.glob("*/COMMITTED"))
+        if not committed:
+            raise SystemExit(f"no committed checkpoint under {path.parent}")
+        path = committed[-1]
+    if path.is_dir():
+        if not (path / "COMMITTED").exists():
+            raise SystemExit(f"{path} is not a committed checkpoint")
+        if not (path / "model.pt").exists():
+            raise SystemExit(f"{path} holds no model export (a checkpoint saved inside an epoch): use one saved at the end of an epoch")
+        path = path / "model.pt"
+    return str(path)
+
+
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
+    if isinstance(getattr(args, "checkpoint", None), str) and (Path(args.checkpoint).is_dir() or Path(args.checkpoint).name == "latest"):
+        args.checkpoint = exported_model_file(args.checkpoint)
     return int(args.func(args) or 0)
 
 

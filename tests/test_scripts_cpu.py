@@ -400,3 +400,49 @@ def test_launchers_take_their_settings_from_the_environment(tmp_path):
     (data / "multi5_permute" / "profiles.jsonl").write_text("b\n")
     differ = run("synbios_moe.sh", "single", "fsdp", "8")
     assert differ.returncode == 2 and "differ" in differ.stderr
+
+
+def test_probe_launcher_takes_both_call_forms_and_the_study_cli_resolves_checkpoint_directories(tmp_path):
+    checkout, run = _launcher_sandbox(tmp_path)
+    data = checkout / "artifacts" / "synbios_moe" / "data" / "single"
+    data.mkdir(parents=True)
+    batches = tmp_path / "recommended.env"
+    batches.write_text("P_BATCH_SIZE=64\nQ_BATCH_SIZE=32\n")
+    out = run("synbios_probes.sh", "single", "fsdp", STAGE="pilot", PROBE_DEVICES="cuda:0,cuda:1", PROBE_BATCH_ENV=str(batches),
+              SKIP_PRETRAIN_GATE="1", PROBE_LOG_INTERVAL="50")
+    assert out.returncode == 0, out.stdout + out.stderr
+    lines = [line for line in out.stdout.splitlines() if line.startswith("ARGS:")]
+    # the stub python "validates" any cache, so only a missing manifest leads to cache-probes
+    assert "cache-probes --data artifacts/synbios_moe/data/single" in lines[0] and lines[0].endswith("--codec gpt2 --require-coverage")
+    pipeline = [line for line in lines if "probe-pipeline" in line]
+    assert len(pipeline) == 1 and "--stage pilot" in pipeline[0] and "--devices cuda:0,cuda:1" in pipeline[0]
+    assert "--checkpoint artifacts/synbios_moe/checkpoints/synbios_moe_single_fsdp/latest" in pipeline[0]
+    assert pipeline[0].endswith("--quiet --require-coverage --skip-gate --p-batch-size 64 --q-batch-size 32 --log-interval 50")
+    assert not any("summarize-probes" in line for line in lines)                 # no formal stage, no summary
+    out = run("synbios_probes.sh", str(data), "weights/model.pt", REQUIRE_COVERAGE="0", PROBE_GPUS="0", OUT=str(tmp_path / "study"))
+    stages = [line for line in out.stdout.splitlines() if "probe-pipeline" in line]
+    assert [s.split("--stage ")[1].split()[0] for s in stages] == ["smoke", "pilot", "formal"] and all("--devices cpu" in s and s.endswith("--quiet") for s in stages)
+    assert run("synbios_probes.sh", "multi5_permute", "fsdp").returncode == 2          # no such dataset yet
+    assert run("synbios_probes.sh", "single", "fsdp", PROBE_BATCH_ENV=str(tmp_path / "absent.env")).returncode == 2
+
+    sys.path.insert(0, str(ROOT / "scripts"))
+    try:
+        import synbios_moe as cli
+    finally:
+        sys.path.pop(0)
+    run_dir = tmp_path / "run"
+    for step, exported in ((10, True), (20, True), (25, False)):
+        ckpt = run_dir / f"epoch_{step // 10:06d}_step_{step:09d}"
+        ckpt.mkdir(parents=True)
+        if exported:
+            (ckpt / "model.pt").write_text("x")
+        if step != 25:
+            (ckpt / "COMMITTED").write_text("ok\n")
+    assert cli.exported_model_file(str(run_dir / "latest")) == str(run_dir / "epoch_000002_step_000000020" / "model.pt")
+    assert cli.exported_model_file(str(run_dir / "epoch_000001_step_000000010")).endswith("step_000000010/model.pt")
+    assert cli.exported_model_file("some/model.pt") == "some/model.pt"
+    with pytest.raises(SystemExit, match="not a committed checkpoint"):
+        cli.exported_model_file(str(run_dir / "epoch_000002_step_000000025"))
+    (run_dir / "epoch_000002_step_000000020" / "model.pt").unlink()
+    with pytest.raises(SystemExit, match="no model export"):
+        cli.exported_model_file(str(run_dir / "latest"))
