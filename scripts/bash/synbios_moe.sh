@@ -14,7 +14,7 @@ if [[ "${FORCE_PREPARE:-0}" == 1 || ! -f "$DATA/manifest.json" ]]; then
   if compgen -G "artifacts/synbios_moe/checkpoints/${RUN}*/epoch_*" > /dev/null; then
     echo "checkpoints of $RUN exist: refusing to (re)generate $DATA under them; move the checkpoints away first" >&2; exit 2
   fi
-  "$PYTHON" scripts/synbios_moe.py prepare --output "$DATA" --variant "$VARIANT" --num-people "$NUM_PEOPLE" --seed "$SEED" --codec "$CODEC"
+  "$PYTHON" scripts/synbios_moe.py prepare --output "$DATA" --variant "${VARIANT//_/+}" --num-people "$NUM_PEOPLE" --seed "$SEED" --codec "$CODEC"
 fi
 for other in artifacts/synbios_moe/data/*/profiles.jsonl; do       # every variant describes the same people
   if [[ -f "$other" && -f "$DATA/profiles.jsonl" ]] && ! cmp -s "$other" "$DATA/profiles.jsonl"; then

@@ -446,3 +446,24 @@ def test_probe_launcher_takes_both_call_forms_and_the_study_cli_resolves_checkpo
     (run_dir / "epoch_000002_step_000000020" / "model.pt").unlink()
     with pytest.raises(SystemExit, match="no model export"):
         cli.exported_model_file(str(run_dir / "latest"))
+
+
+def test_full_experiment_launcher_wants_a_confirmation_and_runs_both_variants(tmp_path):
+    checkout, run = _launcher_sandbox(tmp_path)
+    assert run("synbios_full_experiment.sh", "fsdp").returncode == 2                                   # both variants: not without the confirmation
+    refused = run("synbios_full_experiment.sh", "fsdp", CONFIRM_FULL_EXPERIMENT="1")
+    assert refused.returncode == 2 and "PROBE_BATCH_ENV" in refused.stderr                             # several GPUs: measured probe batches
+    assert run("synbios_full_experiment.sh", "zero3", CONFIRM_FULL_EXPERIMENT="1").returncode == 2
+    for variant in ("single", "multi5_permute"):                                                       # a finished pretraining of each variant
+        (checkout / "artifacts" / "synbios_moe" / "checkpoints" / f"synbios_moe_{variant}_fsdp" / "epoch_000001_step_000000010").mkdir(parents=True)
+        data = checkout / "artifacts" / "synbios_moe" / "data" / variant
+        data.mkdir(parents=True)
+        (data / "manifest.json").write_text("{}")
+    out = run("synbios_full_experiment.sh", "fsdp", CONFIRM_FULL_EXPERIMENT="1", ALLOW_DEFAULT_PROBE_BATCHES="1", NPROC="8", PROBE_GPUS="8")
+    assert out.returncode == 0, out.stdout + out.stderr
+    calls = [line for line in out.stdout.splitlines() if line.startswith("ARGS:")]
+    trainings = [c for c in calls if "scripts/train.py" in c]
+    assert len(trainings) == 2 and "single_fsdp.yaml" in trainings[0] and "multi5_permute_fsdp.yaml" in trainings[1]
+    assert sum("probe-pipeline" in c for c in calls) == 6 and sum("report-formal-study" in c for c in calls) == 2
+    assert "compare-formal-studies --single artifacts/synbios_moe/studies/synbios_moe_single_fsdp/probes/formal --multi " \
+        "artifacts/synbios_moe/studies/synbios_moe_multi5_permute_fsdp/probes/formal" in calls[-1]
